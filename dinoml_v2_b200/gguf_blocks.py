@@ -1,0 +1,51 @@
+"""GGUF block-layout tables for the three quantization types on the hot path.
+
+The byte layouts are the ones the reference declares in
+kernels/rocm/src/ck_gguf_q8_gemm.hip:20-25 (Q8_0), :34-41 (Q4_K), :71-78 (Q6_K);
+`qtype_value` is the ggml type id the reference records in constant storage
+metadata (src/dinoml/constant_sources.py:88-108).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class QType:
+    name: str          # "Q8_0" | "Q4_K" | "Q6_K"
+    value: int         # ggml enum
+    block_size: int    # weights per block
+    block_bytes: int   # bytes per block
+    symbol: str        # lower-case tag used in kernel symbol names
+
+
+Q8_0 = QType("Q8_0", 8, 32, 34, "q8_0")
+Q4_K = QType("Q4_K", 12, 256, 144, "q4_k")
+Q6_K = QType("Q6_K", 14, 256, 210, "q6_k")
+
+QTYPES = {q.name: q for q in (Q8_0, Q4_K, Q6_K)}
+QTYPES_BY_VALUE = {q.value: q for q in QTYPES.values()}
+
+
+def qtype_of(which) -> QType:
+    """Accepts a QType, a name ("Q4_K", case-insensitive) or a ggml enum value."""
+    if isinstance(which, QType):
+        return which
+    if isinstance(which, str):
+        key = which.upper()
+        if key in QTYPES:
+            return QTYPES[key]
+    elif int(which) in QTYPES_BY_VALUE:
+        return QTYPES_BY_VALUE[int(which)]
+    raise ValueError(f"unsupported GGUF qtype {which!r}; supported: {sorted(QTYPES)}")
+
+
+def row_bytes(qtype, n_per_row: int) -> int:
+    q = qtype_of(qtype)
+    if n_per_row <= 0 or n_per_row % q.block_size:
+        raise ValueError(f"n_per_row={n_per_row} is not a positive multiple of the {q.name} block size {q.block_size}")
+    return n_per_row // q.block_size * q.block_bytes
+
+
+def encoded_nbytes(qtype, rows: int, n_per_row: int) -> int:
+    return int(rows) * row_bytes(qtype, n_per_row)
