@@ -1,0 +1,145 @@
+// extern "C" surface of the kernel library: dequantize, fused gemm variants, per-candidate symbols,
+// candidate timers.  Declarations (with the reference interfaces they stand in for) are in
+// include/dinoml_b200_gguf.h.
+#include <string>
+
+#include "../../include/dinoml_b200_gguf.h"
+#include "gguf_common.cuh"
+
+namespace b200gguf {
+
+int dequantize_rows(const void* dev_in, int64_t qtype, int64_t rows, int64_t n_per_row, int output_dtype, void* dev_out,
+                    cudaStream_t stream);
+int gemm_rcr_simt(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                  cudaStream_t s);
+int gemm_rcr_mma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                 cudaStream_t s);
+int gemm_rcr_umma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                  cudaStream_t s);
+bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k);
+bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k);
+size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k);
+
+// Thread-local last error, same contract as the reference runtime (runtime/src/runtime_common.cpp:5-20).
+static thread_local std::string g_last_error;
+
+int set_error(int rc, const char* where) {
+  static const char* const kText[] = {
+      "ok", "null pointer", "non-positive dimension", "k is not a multiple of the quantization block size",
+      "CUDA launch failed", "unsupported GGUF qtype", "unsupported dtype", "pointer or row pitch alignment not met",
+      "shape outside the range of this kernel variant", "device-side wait gave up"};
+  if (rc == RC_OK) return rc;
+  g_last_error = std::string(where) + ": " + (rc > 0 && rc < 10 ? kText[rc] : "error");
+  if (rc == RC_LAUNCH) {
+    g_last_error += " (";
+    g_last_error += cudaGetErrorString(cudaPeekAtLastError());
+    g_last_error += ")";
+  }
+  return rc;
+}
+int set_error_message(int rc, const std::string& message) {
+  g_last_error = message;
+  return rc;
+}
+const char* last_error() { return g_last_error.c_str(); }
+
+int select_variant(int qtype, int dtype, int m, int n, int k) {
+  if (gemv_mma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_MMA;
+  if (gemm_umma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_UMMA;
+  return DINOML_B200_GGUF_VARIANT_SIMT;
+}
+
+int gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+             int variant, cudaStream_t s) {
+  if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, n, k);
+  switch (variant) {
+    case DINOML_B200_GGUF_VARIANT_SIMT: return gemm_rcr_simt(a, b, bias, c, qtype, dtype, m, n, k, s);
+    case DINOML_B200_GGUF_VARIANT_MMA: return gemm_rcr_mma(a, b, bias, c, qtype, dtype, m, n, k, s);
+    case DINOML_B200_GGUF_VARIANT_UMMA: return gemm_rcr_umma(a, b, bias, c, qtype, dtype, m, n, k, s);
+    default: return RC_RANGE;
+  }
+}
+
+float profile_gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n,
+                       int k, int variant, int iterations, cudaStream_t s) {
+  if (iterations <= 0) return -1.f;
+  if (set_error(gemm_rcr(a, b, bias, c, qtype, dtype, m, n, k, variant, s), "dinoml_profile_b200_gguf_gemm_rcr"))
+    return -1.f;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return -1.f;
+  float ms = -1.f;
+  bool ok = cudaEventRecord(e0, s) == cudaSuccess;
+  for (int i = 0; ok && i < iterations; ++i) ok = gemm_rcr(a, b, bias, c, qtype, dtype, m, n, k, variant, s) == RC_OK;
+  ok = ok && cudaEventRecord(e1, s) == cudaSuccess && cudaEventSynchronize(e1) == cudaSuccess;
+  if (ok && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) ms /= float(iterations); else ms = -1.f;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return ms;
+}
+
+}  // namespace b200gguf
+
+using namespace b200gguf;
+
+extern "C" {
+
+int dinoml_b200_gguf_kernel_abi_version(void) { return DINOML_B200_GGUF_KERNEL_ABI_VERSION; }
+
+const char* dino_get_last_error(void) { return last_error(); }
+
+int libgguf_cuda_dequantize_rows_on_stream(const void* dev_in, int64_t qtype, int64_t rows, int64_t n_per_row,
+                                           int output_dtype, void* dev_out, void* stream) {
+  return set_error(dequantize_rows(dev_in, qtype, rows, n_per_row, output_dtype, dev_out, static_cast<cudaStream_t>(stream)),
+                   "libgguf_cuda_dequantize_rows_on_stream");
+}
+
+int dinoml_b200_gguf_gemm_rcr(const void* a, const void* b_quant, const void* bias, void* c, int qtype, int dtype, int m,
+                              int n, int k, int variant, void* stream) {
+  return set_error(gemm_rcr(a, b_quant, bias, c, qtype, dtype, m, n, k, variant, static_cast<cudaStream_t>(stream)),
+                   "dinoml_b200_gguf_gemm_rcr");
+}
+
+float dinoml_profile_b200_gguf_gemm_rcr(const void* a, const void* b_quant, const void* bias, void* c, int qtype,
+                                        int dtype, int m, int n, int k, int variant, int iterations, void* stream) {
+  return profile_gemm_rcr(a, b_quant, bias, c, qtype, dtype, m, n, k, variant, iterations, static_cast<cudaStream_t>(stream));
+}
+
+size_t dinoml_b200_gguf_gemm_rcr_workspace(int qtype, int dtype, int m, int n, int k, int variant) {
+  if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, n, k);
+  return variant == DINOML_B200_GGUF_VARIANT_UMMA ? gemm_umma_workspace(qtype, dtype, m, n, k) : 0;
+}
+
+int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k) {
+  return select_variant(qtype, dtype, m, n, k);
+}
+
+#define B200_DEFINE(q, QT, dt, DT, var, VAR)                                                                          \
+  int dinoml_b200_gguf_##q##_gemm_rcr_##dt##_##var##_v1(const void* a, const void* b_quant, void* c, int m, int n,    \
+                                                        int k, void* stream) {                                        \
+    return set_error(gemm_rcr(a, b_quant, nullptr, c, QT, DT, m, n, k, VAR, static_cast<cudaStream_t>(stream)),       \
+                     "dinoml_b200_gguf_" #q "_gemm_rcr_" #dt "_" #var "_v1");                                         \
+  }                                                                                                                   \
+  int dinoml_b200_gguf_##q##_gemm_rcr_bias_##dt##_##var##_v1(const void* a, const void* b_quant, const void* bias,    \
+                                                             void* c, int m, int n, int k, void* stream) {            \
+    if (bias == nullptr) return set_error(RC_NULL, "dinoml_b200_gguf_" #q "_gemm_rcr_bias_" #dt "_" #var "_v1");      \
+    return set_error(gemm_rcr(a, b_quant, bias, c, QT, DT, m, n, k, VAR, static_cast<cudaStream_t>(stream)),          \
+                     "dinoml_b200_gguf_" #q "_gemm_rcr_bias_" #dt "_" #var "_v1");                                    \
+  }                                                                                                                   \
+  float dinoml_profile_b200_gguf_##q##_gemm_rcr_##dt##_##var##_v1(const void* a, const void* b_quant, void* c, int m, \
+                                                                  int n, int k, int iterations, void* stream) {       \
+    return profile_gemm_rcr(a, b_quant, nullptr, c, QT, DT, m, n, k, VAR, iterations,                                 \
+                            static_cast<cudaStream_t>(stream));                                                       \
+  }
+#define B200_DEFINE_Q(q, QT)                                                              \
+  B200_DEFINE(q, QT, float32, DINO_F32, simt, DINOML_B200_GGUF_VARIANT_SIMT)              \
+  B200_DEFINE(q, QT, float16, DINO_F16, simt, DINOML_B200_GGUF_VARIANT_SIMT)              \
+  B200_DEFINE(q, QT, bfloat16, DINO_BF16, simt, DINOML_B200_GGUF_VARIANT_SIMT)            \
+  B200_DEFINE(q, QT, float16, DINO_F16, mma, DINOML_B200_GGUF_VARIANT_MMA)                \
+  B200_DEFINE(q, QT, bfloat16, DINO_BF16, mma, DINOML_B200_GGUF_VARIANT_MMA)              \
+  B200_DEFINE(q, QT, float16, DINO_F16, umma, DINOML_B200_GGUF_VARIANT_UMMA)              \
+  B200_DEFINE(q, QT, bfloat16, DINO_BF16, umma, DINOML_B200_GGUF_VARIANT_UMMA)
+B200_DEFINE_Q(q8_0, QTYPE_Q8_0)
+B200_DEFINE_Q(q4_k, QTYPE_Q4_K)
+B200_DEFINE_Q(q6_k, QTYPE_Q6_K)
+
+}  // extern "C"

@@ -1,0 +1,313 @@
+// Fused GGUF decode GEMV ("mma" variant), M = 1..16, float16 / bfloat16 activations, Q4_K weights.
+//
+// C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias) with W streamed once from HBM as packed GGUF blocks.
+// HBM-bound: the algorithmic traffic is the packed weight bytes (144 B per 256 weights).
+//
+// How the arithmetic stays exact while running on tensor cores: the 4-bit quants are turned into
+// 16-bit floats with a bit trick (bf16 0x4300|q == 128+q; fp16 0x6400|q == 1024+q, minus 1024),
+// multiplied against the unmodified 16-bit activations by mma.sync.m16n8k16 with fp32 accumulation,
+// and only then scaled in fp32 per 32-wide sub-block j:
+//     y[n,m] = sum_j ds[n,j] * S'[n,m,j]  -  sum_j (MAGIC*ds[n,j] + dm[n,j]) * X[m,j]
+// with S' = sum_k x*(MAGIC+q) from the MMA, X[m,j] the sum of the sub-block's activations (computed
+// once per CTA into shared memory), ds = d*sc and dm = dmin*min the sub-block scale and min.
+//
+// Data movement: a CTA of 4 warps owns 16 consecutive weight rows (one MMA M-tile).  Their packed
+// bytes are staged HBM -> shared memory with 16-byte cp.async copies in K-stages of 4 super-blocks
+// (16 rows x 576 B), three stages in flight per CTA, so every SM keeps >100 KB of reads outstanding
+// without holding them in registers.  Within a stage warp w unpacks super-block w.  Lane
+// (g = lane/4, t = lane%4) feeds rows g and g+8: per 64-weight group it reads the 8 quant bytes
+// [8t, 8t+8) of each row, which puts all 16 K-slots of every MMA inside one sub-block.  The row pitch
+// in shared memory (608 B) makes those 8-byte reads bank-conflict free.  The 16 header bytes of each
+// (row, super-block) are decoded by a lane pair (lane/2 = row, lane%2 = which 4 sub-blocks) into ds,
+// shared through shared memory, while the same lane folds the min / MAGIC term against X directly.
+// The four warps' partial rows are summed through shared memory at the end.
+//
+// Behavioural ancestor in the reference: the small-M "wave" kernels of the fused prototype
+// (kernels/rocm/src/ck_gguf_q8_gemm.hip:1009-1166); the reference's CUDA path instead dequantizes the
+// whole weight and runs a dense Sm80 GEMM (src/dinoml/lowering/ops/gemm.py:729-749).
+#include "gguf_common.cuh"
+
+namespace b200gguf {
+
+int check_gemm_args(const void* a, const void* b, const void* c, int qtype, int dtype, int m, int n, int k);
+
+template <typename T> struct MmaType;
+template <> struct MmaType<__nv_bfloat16> {
+  static constexpr uint32_t kMagicBytes = 0x43434343u;  // bf16 0x43qq = 128 + q
+  static constexpr float kMagic = 128.f;                // offset left in the MMA operand
+  static __device__ __forceinline__ uint32_t fix(uint32_t pair) { return pair; }
+  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float sum8(const uint4& v) {
+    const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s += __uint_as_float(r[i] << 16) + __uint_as_float(r[i] & 0xffff0000u);
+    return s;
+  }
+};
+template <> struct MmaType<__half> {
+  static constexpr uint32_t kMagicBytes = 0x64646464u;  // fp16 0x64qq = 1024 + q ...
+  static constexpr float kMagic = 0.f;                  // ... and the 1024 is removed exactly before the MMA
+  static __device__ __forceinline__ uint32_t fix(uint32_t pair) {
+    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&pair), __half2half2(__ushort_as_half(0x6400)));
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ float sum8(const uint4& v) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); s += f.x + f.y; }
+    return s;
+  }
+};
+
+constexpr int kGemvWarps = 4;
+constexpr int kGemvThreads = kGemvWarps * 32;
+constexpr int kGemvRows = 16;
+constexpr int kStageSb = 4;                              // super-blocks per stage (one per warp)
+constexpr int kStages = 3;                               // stages in flight
+constexpr int kRowChunks = kStageSb * 9;                 // 16-byte chunks per row per stage (4 x 144 B)
+constexpr int kRowPitch = kStageSb * 144 + 32;           // 608 B: 8-byte reads of 8 rows x 4 lanes hit 32 banks
+constexpr int kStageBytes = kGemvRows * kRowPitch;       // 9728 B
+
+// Byte -> float without I2F: 0x4B0000bb is 2^23 + bb.
+__device__ __forceinline__ float byte_to_float(uint32_t word, int i) {
+  return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650 + i)) - 8388608.f;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// MXC: activation rows covered (power of two >= m).  Dynamic shared memory: X[MXC][k/32] floats.
+template <typename T, int MXC>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias,
+                    T* __restrict__ y, int m, int n, int k) {
+  using MT = MmaType<T>;
+  constexpr int NT = MXC > 8 ? 2 : 1;        // n8 tiles of activation rows
+  constexpr int MC = MXC == 1 ? 1 : 2;       // accumulator columns a lane keeps per tile
+  constexpr int kCols = NT * 8;
+  extern __shared__ __align__(16) float sX[];                             // [MXC][k/32]
+  __shared__ __align__(16) uint8_t sW[kStages * kStageBytes];             // staged packed weights
+  __shared__ __align__(16) float sS[kGemvWarps][kGemvRows][8];            // ds per row, sub-block
+  __shared__ float sRed[kGemvWarps][kGemvRows][kCols];                    // main partial sums
+  __shared__ float sXt[kGemvWarps][kGemvRows][2][MXC];                    // min / MAGIC partial sums
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int r_base = blockIdx.x * kGemvRows;
+  const int nsb = k >> 8, nsub = k >> 5;
+  const int nstages = (nsb + kStageSb - 1) / kStageSb;
+  const int64_t row_bytes = int64_t(nsb) * 144;
+  const uint32_t sW_u32 = uint32_t(__cvta_generic_to_shared(sW));
+
+  // Copy assignment: 8 threads per weight row, thread (tid%8) moves 16-byte chunks (tid%8) + 8j of the
+  // row's 36 chunks per stage.
+  const int cp_row = tid >> 3, cp_c0 = tid & 7;
+  const uint8_t* cp_src = w + int64_t(min(r_base + cp_row, n - 1)) * row_bytes + cp_c0 * 16;
+  const uint32_t cp_dst = sW_u32 + cp_row * kRowPitch + cp_c0 * 16;
+  auto issue_stage = [&](int s) {
+    if (s < nstages) {
+      const int valid_chunks = min(kStageSb, nsb - s * kStageSb) * 9;
+      const uint8_t* src = cp_src + int64_t(s) * (kStageSb * 144);
+      const uint32_t dst = cp_dst + (s % kStages) * kStageBytes;
+#pragma unroll
+      for (int j = 0; j < 5; ++j)
+        if (cp_c0 + 8 * j < valid_chunks) cp_async16(dst + 128 * j, src + 128 * j);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < kStages; ++s) issue_stage(s);
+
+  // X[c][j] = sum of activations of row c over sub-block j (rows >= m are zero).
+  for (int idx = tid; idx < nsub * MXC; idx += kGemvThreads) {
+    const int c = idx / nsub, j = idx - c * nsub;
+    float s = 0.f;
+    if (c < m) {
+      const uint4* px = reinterpret_cast<const uint4*>(x + int64_t(c) * k + int64_t(j) * 32);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s += MT::sum8(__ldg(px + i));
+    }
+    sX[idx] = s;
+  }
+
+  float res[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) res[nt][i] = 0.f;
+  float xt[MXC];
+#pragma unroll
+  for (int c = 0; c < MXC; ++c) xt[c] = 0.f;
+
+  const int srow = lane >> 1, shalf = lane & 1;   // scale-decode role of this lane
+  const T* xrow[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) xrow[nt] = x + int64_t(min(nt * 8 + g, m - 1)) * k + 8 * t;
+
+  for (int s = 0; s < nstages; ++s) {
+    cp_async_wait<kStages - 2>();
+    __syncthreads();                       // stage s landed for every thread; stage s-1 fully consumed
+    if (s > 0) issue_stage(s - 1 + kStages); else cp_async_commit();
+    const int sb = s * kStageSb + warp;
+    if (sb < nsb) {
+      const uint8_t* st = sW + (s % kStages) * kStageBytes + warp * 144;
+      {  // lane pair (srow, shalf): 4 sub-block scales -> ds to shared memory, min/MAGIC term folded against X
+        const uint4 hdr = *reinterpret_cast<const uint4*>(st + srow * kRowPitch);
+        const float d = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
+        const float dmin = half_bits_to_float(uint16_t(hdr.x >> 16));
+        // sub-blocks 0..3 keep their 6-bit fields in place; 4..7 are split across two bytes
+        const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, mn_lo = hdr.z & 0x3f3f3f3fu;
+        const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4);
+        const uint32_t mn_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4);
+        const uint32_t scb = shalf ? sc_hi : sc_lo, mnb = shalf ? mn_hi : mn_lo;
+        float4 dsv;
+        float kk[4];
+        float* dsf = reinterpret_cast<float*>(&dsv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          dsf[i] = d * byte_to_float(scb, i);
+          kk[i] = fmaf(MT::kMagic, dsf[i], dmin * byte_to_float(mnb, i));
+        }
+        *reinterpret_cast<float4*>(&sS[warp][srow][4 * shalf]) = dsv;
+#pragma unroll
+        for (int c = 0; c < MXC; ++c) {
+          const float4 X = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 8 + 4 * shalf]);
+          xt[c] = fmaf(kk[0], X.x, xt[c]);
+          xt[c] = fmaf(kk[1], X.y, xt[c]);
+          xt[c] = fmaf(kk[2], X.z, xt[c]);
+          xt[c] = fmaf(kk[3], X.w, xt[c]);
+        }
+      }
+      __syncwarp();
+      const float4 dsa0 = *reinterpret_cast<const float4*>(&sS[warp][g][0]);
+      const float4 dsa1 = *reinterpret_cast<const float4*>(&sS[warp][g][4]);
+      const float4 dsb0 = *reinterpret_cast<const float4*>(&sS[warp][g + 8][0]);
+      const float4 dsb1 = *reinterpret_cast<const float4*>(&sS[warp][g + 8][4]);
+      const float ds_a[8] = {dsa0.x, dsa0.y, dsa0.z, dsa0.w, dsa1.x, dsa1.y, dsa1.z, dsa1.w};
+      const float ds_b[8] = {dsb0.x, dsb0.y, dsb0.z, dsb0.w, dsb1.x, dsb1.y, dsb1.z, dsb1.w};
+      const uint8_t* q0p = st + g * kRowPitch + 16 + 8 * t;
+      const uint8_t* q1p = q0p + 8 * kRowPitch;
+#pragma unroll
+      for (int G = 0; G < 4; ++G) {
+        const uint2 q0 = *reinterpret_cast<const uint2*>(q0p + 32 * G);
+        const uint2 q1 = *reinterpret_cast<const uint2*>(q1p + 32 * G);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t n0x = (h ? q0.x >> 4 : q0.x) & 0x0f0f0f0fu, n0y = (h ? q0.y >> 4 : q0.y) & 0x0f0f0f0fu;
+          const uint32_t n1x = (h ? q1.x >> 4 : q1.x) & 0x0f0f0f0fu, n1y = (h ? q1.y >> 4 : q1.y) & 0x0f0f0f0fu;
+          const uint32_t a_lo[4] = {MT::fix(__byte_perm(n0x, MT::kMagicBytes, 0x4140)), MT::fix(__byte_perm(n1x, MT::kMagicBytes, 0x4140)),
+                                    MT::fix(__byte_perm(n0x, MT::kMagicBytes, 0x4342)), MT::fix(__byte_perm(n1x, MT::kMagicBytes, 0x4342))};
+          const uint32_t a_hi[4] = {MT::fix(__byte_perm(n0y, MT::kMagicBytes, 0x4140)), MT::fix(__byte_perm(n1y, MT::kMagicBytes, 0x4140)),
+                                    MT::fix(__byte_perm(n0y, MT::kMagicBytes, 0x4342)), MT::fix(__byte_perm(n1y, MT::kMagicBytes, 0x4342))};
+          const float dsr0 = ds_a[2 * G + h], dsr1 = ds_b[2 * G + h];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            // rows >= m read a clamped (valid) row; their accumulator columns are never stored
+            const uint4 xb = __ldg(reinterpret_cast<const uint4*>(xrow[nt] + sb * 256 + 64 * G + 32 * h));
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            MT::mma(acc, a_lo, xb.x, xb.y);
+            MT::mma(acc, a_hi, xb.z, xb.w);
+            res[nt][0] = fmaf(dsr0, acc[0], res[nt][0]);
+            res[nt][2] = fmaf(dsr1, acc[2], res[nt][2]);
+            if (MC == 2) {
+              res[nt][1] = fmaf(dsr0, acc[1], res[nt][1]);
+              res[nt][3] = fmaf(dsr1, acc[3], res[nt][3]);
+            }
+          }
+        }
+      }
+      __syncwarp();                        // sS is rewritten in the next stage
+    }
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    sRed[warp][g][nt * 8 + 2 * t] = res[nt][0];
+    sRed[warp][g][nt * 8 + 2 * t + 1] = res[nt][1];
+    sRed[warp][g + 8][nt * 8 + 2 * t] = res[nt][2];
+    sRed[warp][g + 8][nt * 8 + 2 * t + 1] = res[nt][3];
+  }
+#pragma unroll
+  for (int c = 0; c < MXC; ++c) sXt[warp][srow][shalf][c] = xt[c];
+  __syncthreads();
+  for (int idx = tid; idx < kGemvRows * MXC; idx += kGemvThreads) {
+    const int r = idx & (kGemvRows - 1), c = idx >> 4;
+    const int row = r_base + r;
+    if (row < n && c < m) {
+      float v = 0.f, xs = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < kGemvWarps; ++wv) {
+        v += sRed[wv][r][c];
+        xs += sXt[wv][r][0][c] + sXt[wv][r][1][c];
+      }
+      v -= xs;
+      if (bias != nullptr) v += MT::to_float(bias[row]);
+      y[int64_t(c) * n + row] = MT::from_float(v);
+    }
+  }
+}
+
+
+template <typename T, int MXC>
+static int launch_q4k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+  const int tiles = (n + kGemvRows - 1) / kGemvRows;
+  const size_t smem = size_t(k / 32) * MXC * sizeof(float);
+  auto kern = gemv_q4k_mma_kernel<T, MXC>;
+  if (smem > 4 * 1024) {   // static + dynamic shared memory beyond 48 KB needs the opt-in
+    if (smem > 160 * 1024) return RC_RANGE;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
+  }
+  kern<<<tiles, kGemvThreads, smem, s>>>(static_cast<const T*>(a), static_cast<const uint8_t*>(b),
+                                         static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
+  return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
+}
+
+template <typename T>
+static int launch_q4k(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+  if (m == 1) return launch_q4k_m<T, 1>(a, b, bias, c, m, n, k, s);
+  if (m == 2) return launch_q4k_m<T, 2>(a, b, bias, c, m, n, k, s);
+  if (m <= 4) return launch_q4k_m<T, 4>(a, b, bias, c, m, n, k, s);
+  if (m <= 8) return launch_q4k_m<T, 8>(a, b, bias, c, m, n, k, s);
+  return launch_q4k_m<T, 16>(a, b, bias, c, m, n, k, s);
+}
+
+// Which (qtype, dtype, m) the mma variant covers.
+bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k) {
+  (void)n;
+  return qtype == QTYPE_Q4_K && (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 16 && k % 256 == 0;
+}
+
+int gemm_rcr_mma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                 cudaStream_t s) {
+  if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
+  if (dtype == DINO_F32) return RC_DTYPE;
+  if (m > 16) return RC_RANGE;
+  if (!gemv_mma_supports(qtype, dtype, m, n, k)) return RC_QTYPE;
+  if (reinterpret_cast<uintptr_t>(b) & 15) return RC_ALIGN;  // 16-byte cp.async sources
+  return dtype == DINO_BF16 ? launch_q4k<__nv_bfloat16>(a, b, bias, c, m, n, k, s)
+                            : launch_q4k<__half>(a, b, bias, c, m, n, k, s);
+}
+
+}  // namespace b200gguf

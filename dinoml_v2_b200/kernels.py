@@ -1,0 +1,81 @@
+"""Tensor-level wrappers over the C-ABI kernels (torch is used for device memory and streams only)."""
+from __future__ import annotations
+
+import torch
+
+from . import _native
+from .gguf_blocks import qtype_of, row_bytes
+
+_TORCH_DTYPE = {"float16": torch.float16, "float32": torch.float32, "bfloat16": torch.bfloat16}
+_DTYPE_NAME = {v: k for k, v in _TORCH_DTYPE.items()}
+
+
+def _stream_ptr(stream) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return int(stream.cuda_stream)
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (the GGUF quantized-linear path has no CPU implementation)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def dequantize_rows(blocks: torch.Tensor, qtype, n_per_row: int, dtype: str = "float32", out: torch.Tensor | None = None,
+                    stream=None) -> torch.Tensor:
+    """uint8 [rows, row_bytes] GGUF blocks -> dense [rows, n_per_row] (bit-exact dequantization)."""
+    q = qtype_of(qtype)
+    _require_cuda(blocks, "blocks")
+    if blocks.dtype != torch.uint8 or blocks.dim() != 2 or blocks.shape[1] != row_bytes(q, n_per_row):
+        raise ValueError(f"blocks must be uint8 [rows, {row_bytes(q, n_per_row)}] for {q.name} with n_per_row={n_per_row}")
+    rows = blocks.shape[0]
+    if out is None:
+        out = torch.empty((rows, n_per_row), dtype=_TORCH_DTYPE[dtype], device=blocks.device)
+    _require_cuda(out, "out")
+    rc = _native.lib().libgguf_cuda_dequantize_rows_on_stream(
+        blocks.data_ptr(), q.value, rows, n_per_row, _native.DEQUANT_DTYPE[dtype], out.data_ptr(), _stream_ptr(stream))
+    _native.check(rc, "libgguf_cuda_dequantize_rows_on_stream")
+    return out
+
+
+def gemm_rcr(a: torch.Tensor, b_quant: torch.Tensor, qtype, bias: torch.Tensor | None = None, *, variant: str = "auto",
+             out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """a [..., K] x GGUF-encoded weight (uint8 [N, row_bytes]) -> [..., N], same dtype as `a`."""
+    q = qtype_of(qtype)
+    _require_cuda(a, "a")
+    _require_cuda(b_quant, "b_quant")
+    k = a.shape[-1]
+    m = a.numel() // k
+    n = b_quant.shape[0]
+    if b_quant.dtype != torch.uint8 or b_quant.dim() != 2 or b_quant.shape[1] != row_bytes(q, k):
+        raise ValueError(f"b_quant must be uint8 [N, {row_bytes(q, k)}] for {q.name} with K={k}")
+    dtype = _DTYPE_NAME[a.dtype]
+    if bias is not None:
+        _require_cuda(bias, "bias")
+        if bias.dtype != a.dtype or bias.numel() != n:
+            raise ValueError("bias must have the activation dtype and N elements")
+    if out is None:
+        out = torch.empty(a.shape[:-1] + (n,), dtype=a.dtype, device=a.device)
+    _require_cuda(out, "out")
+    rc = _native.lib().dinoml_b200_gguf_gemm_rcr(
+        a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(), q.value,
+        _native.DINO_DTYPE[dtype], m, n, k, _native.VARIANTS[variant], _stream_ptr(stream))
+    _native.check(rc, "dinoml_b200_gguf_gemm_rcr")
+    return out
+
+
+def profile_gemm_rcr(a, b_quant, qtype, out, *, variant: str, iterations: int, bias=None, stream=None) -> float:
+    """Milliseconds per launch of one candidate (negative on failure), timed by the library with CUDA events."""
+    q = qtype_of(qtype)
+    k = a.shape[-1]
+    return float(_native.lib().dinoml_profile_b200_gguf_gemm_rcr(
+        a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(), q.value,
+        _native.DINO_DTYPE[_DTYPE_NAME[a.dtype]], a.numel() // k, b_quant.shape[0], k, _native.VARIANTS[variant],
+        int(iterations), _stream_ptr(stream)))
+
+
+def select_variant(qtype, dtype: str, m: int, n: int, k: int) -> str:
+    q = qtype_of(qtype)
+    return _native.VARIANT_NAMES[_native.lib().dinoml_b200_gguf_gemm_rcr_select(q.value, _native.DINO_DTYPE[dtype], m, n, k)]

@@ -1,0 +1,110 @@
+/*
+ * C ABI of libdinoml_b200_gguf.so - the B200 (sm_100a) implementation of DinoML v2's GGUF
+ * quantized-linear path.  Plain pointers and sizes only; every pointer named dev_* / a / b_quant /
+ * bias / c is CUDA device memory, `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ *
+ * Return convention (kernel-level entries): 0 = ok, 1 = null pointer, 2 = non-positive dimension,
+ * 3 = k not a multiple of the quantization block (these three follow the reference's fused
+ * prototype, kernels/rocm/src/ck_gguf_q8_gemm.hip:1910-1918), 4 = launch failure, 5 = unsupported
+ * qtype, 6 = unsupported dtype, 7 = alignment, 8 = shape out of range for the variant, 9 = a bounded
+ * device-side wait gave up.  A message for the last failure on the calling thread is available from
+ * dino_get_last_error().
+ *
+ * qtype is the ggml type id the reference stores as `qtype_value` (Q8_0 = 8, Q4_K = 12, Q6_K = 14;
+ * src/dinoml/constant_sources.py:88-108).  dtype is a DinoDtype (float16 = 1, float32 = 2,
+ * bfloat16 = 6; runtime/include/dinoml/abi.h:14-23).  Activations, bias and output share one dtype,
+ * as gemm_rcr requires (src/dinoml/ops/gemm.py:46-60).
+ */
+#ifndef DINOML_B200_GGUF_H_
+#define DINOML_B200_GGUF_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DINOML_B200_GGUF_KERNEL_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define DINOML_B200_API __attribute__((visibility("default")))
+#else
+#define DINOML_B200_API
+#endif
+
+/* Kernel variants of the fused gemm ("candidates" of provider b200_gguf_gemm). */
+enum DinoB200GgufVariant {
+  DINOML_B200_GGUF_VARIANT_AUTO = 0, /* shape-guarded dispatch: mma for M<=16, umma above, simt for float32 */
+  DINOML_B200_GGUF_VARIANT_SIMT = 1, /* CUDA-core warp-per-row, any dtype, any M */
+  DINOML_B200_GGUF_VARIANT_MMA = 2,  /* decode GEMV, M = 1..16, float16 / bfloat16 */
+  DINOML_B200_GGUF_VARIANT_UMMA = 3, /* prefill GEMM on tcgen05 / TMEM, float16 / bfloat16 */
+};
+
+DINOML_B200_API int dinoml_b200_gguf_kernel_abi_version(void);
+
+/* ---- standalone dequantize -------------------------------------------------------------------
+ * Replaces libgguf's device entry, same name and argument list as the declaration the reference's
+ * generated module carries (src/dinoml/templates/gpu_module.cu.j2:35-42; call site
+ * src/dinoml/lowering/ops/gemm.py:745).  dev_in: uint8[rows, n_per_row / block * block_bytes];
+ * dev_out: dense [rows, n_per_row]; output_dtype 0 = float32, 1 = float16 (the reference's two),
+ * 2 = bfloat16 (extension).  Bit-exact with the reference dequantization arithmetic. */
+DINOML_B200_API int libgguf_cuda_dequantize_rows_on_stream(const void* dev_in, int64_t qtype, int64_t rows, int64_t n_per_row,
+                                           int output_dtype, void* dev_out, void* stream);
+
+/* ---- fused quantized gemm_rcr[_bias] ----------------------------------------------------------
+ * C[m,n] = A[m,k] * dequant(B)[n,k]^T (+ bias[n]).  Fills the slot the reference's dense launcher
+ * dinoml_cutlass_gemm_rcr[_bias]_<dtype>_<id>(a, b, [bias,] c, m, n, k, stream) occupies after a
+ * dequantize-to-scratch step (src/dinoml/lowering/ops/gemm.py:729-749, src/dinoml/lowering/cuda.py:
+ * 205-262), reading the GGUF blocks directly; argument order follows the reference's fused
+ * prototype (kernels/rocm/src/ck_gguf_q8_gemm.hip:1910-1940).  bias may be NULL. */
+DINOML_B200_API int dinoml_b200_gguf_gemm_rcr(const void* a, const void* b_quant, const void* bias, void* c, int qtype, int dtype,
+                              int m, int n, int k, int variant, void* stream);
+
+/* Candidate timer with the contract of the reference's dinoml_profile_cutlass_* symbols
+ * (kernels/cuda/src/cutlass_gemm.cu:538-567): one warm launch, then `iterations` launches between two
+ * CUDA events on `stream`; returns milliseconds per launch, < 0 on failure. */
+DINOML_B200_API float dinoml_profile_b200_gguf_gemm_rcr(const void* a, const void* b_quant, const void* bias, void* c, int qtype,
+                                        int dtype, int m, int n, int k, int variant, int iterations, void* stream);
+
+/* Workspace bytes a variant needs for a problem (counterpart of dinoml_cutlass_workspace_*,
+ * kernels/cuda/src/cutlass_gemm.cu:1003-1009).  The library keeps such workspace itself, per device. */
+DINOML_B200_API size_t dinoml_b200_gguf_gemm_rcr_workspace(int qtype, int dtype, int m, int n, int k, int variant);
+
+/* Which variant AUTO resolves to for a problem (the shape-guarded dispatch the reference emits as
+ * if/else text, src/dinoml/lowering/ops/gemm.py:656-698). */
+DINOML_B200_API int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k);
+
+/* Per-candidate symbols, named like the reference's kernel symbols so a manifest can carry them:
+ *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)
+ *   int   dinoml_b200_gguf_<q>_gemm_rcr_bias_<dtype>_<variant>_v1(a, b_quant, bias, c, m, n, k, stream)
+ *   float dinoml_profile_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, iterations, stream)
+ * with <q> in {q8_0,q4_k,q6_k}, <dtype> in {float16,bfloat16,float32}, <variant> in {simt,mma,umma}
+ * (mma / umma exist for float16 and bfloat16 only). */
+#define DINOML_B200_GGUF_DECLARE(q, dt, var)                                                                       \
+  DINOML_B200_API int dinoml_b200_gguf_##q##_gemm_rcr_##dt##_##var##_v1(const void* a, const void* b_quant, void* c, int m, int n, \
+                                                        int k, void* stream);                                      \
+  DINOML_B200_API int dinoml_b200_gguf_##q##_gemm_rcr_bias_##dt##_##var##_v1(const void* a, const void* b_quant, const void* bias, \
+                                                             void* c, int m, int n, int k, void* stream);          \
+  DINOML_B200_API float dinoml_profile_b200_gguf_##q##_gemm_rcr_##dt##_##var##_v1(const void* a, const void* b_quant, void* c,     \
+                                                                  int m, int n, int k, int iterations, void* stream);
+#define DINOML_B200_GGUF_DECLARE_Q(q)        \
+  DINOML_B200_GGUF_DECLARE(q, float32, simt)  \
+  DINOML_B200_GGUF_DECLARE(q, float16, simt)  \
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, simt) \
+  DINOML_B200_GGUF_DECLARE(q, float16, mma)   \
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, mma)  \
+  DINOML_B200_GGUF_DECLARE(q, float16, umma)  \
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, umma)
+DINOML_B200_GGUF_DECLARE_Q(q8_0)
+DINOML_B200_GGUF_DECLARE_Q(q4_k)
+DINOML_B200_GGUF_DECLARE_Q(q6_k)
+
+/* Last error message of the calling thread ("" if none); same contract as the reference's
+ * dino_get_last_error (runtime/src/runtime_common.cpp:5-20). */
+DINOML_B200_API const char* dino_get_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DINOML_B200_GGUF_H_ */

@@ -1,0 +1,184 @@
+"""GPU parity tests (run on the B200 box): every CUDA kernel, called through the C ABI, against the
+CPU oracle and the committed golden fixtures.
+
+Bars: dequantization bit-exact; matmul max relative error <= 1e-3 for float32/float16 outputs and
+<= 2e-2 for bfloat16 outputs, measured with the reference's own metric |d| / max(1, |expected|)
+(tools/bench_ck_gguf_q8_gemm.hip:798-808) AND normalised by max|expected|."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from dinoml_v2_b200 import kernels, synthetic as S
+from dinoml_v2_b200.gguf_blocks import qtype_of
+
+pytestmark = pytest.mark.gpu
+
+QT = ("Q8_0", "Q4_K", "Q6_K")
+TOL = {"float32": 1e-3, "float16": 1e-3, "bfloat16": 2e-2}
+TDT = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need the CUDA device"
+    return torch.device("cuda:0")
+
+
+def _bits(t: torch.Tensor) -> np.ndarray:
+    if t.dtype == torch.float32:
+        return t.cpu().numpy().view(np.uint32)
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("qtype", QT)
+def test_dequant_golden_bit_exact(dev, golden_dir, qtype):
+    kat = np.load(golden_dir / "gguf_dequant_kat.npz")
+    blocks = torch.from_numpy(kat[f"{qtype}_blocks"]).to(dev)
+    k = int(kat[f"{qtype}_n_per_row"])
+    for dtype, key in (("float32", "f32_bits"), ("float16", "f16_bits"), ("bfloat16", "bf16_bits")):
+        got = kernels.dequantize_rows(blocks, qtype, k, dtype)
+        assert np.array_equal(_bits(got), kat[f"{qtype}_{key}"]), (qtype, dtype)
+
+
+@pytest.mark.parametrize("qtype", QT)
+@pytest.mark.parametrize("rows,nblk", [(1, 1), (3, 5), (257, 7), (64, 16)])
+def test_dequant_random_bit_exact(dev, qtype, rows, nblk):
+    k = nblk * qtype_of(qtype).block_size
+    blocks = S.random_blocks(qtype, rows, k, seed=100 + rows + nblk)
+    got = kernels.dequantize_rows(torch.from_numpy(blocks).to(dev), qtype, k, "float32")
+    assert np.array_equal(_bits(got), oracle.dequantize(blocks, qtype, k).view(np.uint32))
+    got16 = kernels.dequantize_rows(torch.from_numpy(blocks).to(dev), qtype, k, "bfloat16")
+    assert np.array_equal(_bits(got16), oracle.dequantize(blocks, qtype, k, "bfloat16"))
+
+
+def test_dequant_full_size_checksum(dev):
+    """Config-2 sized tensor (Q4_K 11008x4096): compare a sampled set of rows bit for bit and an
+    order-independent checksum of all output bit patterns against the oracle on those rows."""
+    n, k = 11008, 4096
+    blocks = S.random_blocks("Q4_K", n, k, seed=2000)
+    got = kernels.dequantize_rows(torch.from_numpy(blocks).to(dev), "Q4_K", k, "float32")
+    rows = np.r_[0:8, 5000:5008, n - 8:n]
+    want = oracle.dequantize(blocks[rows], "Q4_K", k)
+    assert np.array_equal(_bits(got[torch.from_numpy(rows).to(dev)]), want.view(np.uint32))
+    # idempotence / determinism: second call gives identical bits
+    again = kernels.dequantize_rows(torch.from_numpy(blocks).to(dev), "Q4_K", k, "float32")
+    assert torch.equal(got.view(torch.int32), again.view(torch.int32))
+    want_all = oracle.dequantize(blocks, "Q4_K", k)
+    assert int(got.view(torch.int32).to(torch.int64).sum().item()) == int(want_all.view(np.int32).astype(np.int64).sum())
+
+
+def _activations(m, k, seed, dtype, dev):
+    x = S.random_activations(m, k, seed, "float32")
+    xt = torch.from_numpy(x).to(dev).to(TDT[dtype])
+    return xt, xt.float().cpu().numpy()          # device tensor and its exact float32 value
+
+
+def _check(y: torch.Tensor, ref: np.ndarray, dtype: str, what):
+    got = y.float().cpu().numpy()
+    _, rel, norm = oracle.max_errors(ref, got)
+    assert rel <= TOL[dtype] and norm <= TOL[dtype], (what, rel, norm)
+    return rel, norm
+
+
+SHAPES = [  # (m, n, k-blocks)
+    (1, 16, 1), (1, 48, 4), (2, 33, 2), (3, 17, 3), (4, 64, 8), (5, 100, 2), (8, 40, 4), (9, 31, 1), (16, 64, 4), (17, 24, 2),
+]
+
+
+@pytest.mark.parametrize("qtype", QT)
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("variant", ["simt", "auto"])
+def test_gemm_small_shapes(dev, qtype, dtype, variant):
+    q = qtype_of(qtype)
+    for (m, n, kb) in SHAPES:
+        k = kb * 256
+        blocks = S.random_blocks(qtype, n, k, seed=300 + m * 7 + n)
+        x, xf = _activations(m, k, 400 + m + n, dtype, dev)
+        ref = oracle.gemm_quant(xf, blocks, qtype, n, k)
+        y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), qtype, variant=variant)
+        assert y.shape == (m, n) and y.dtype == TDT[dtype]
+        _check(y, ref, dtype, (qtype, dtype, variant, m, n, k))
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_gemv_mma_q4k(dev, dtype):
+    for (m, n, k) in [(1, 16, 256), (1, 1000, 1024), (2, 50, 512), (4, 128, 4096), (7, 33, 768), (8, 64, 2048),
+                      (9, 48, 512), (13, 17, 1024), (16, 160, 4096)]:
+        blocks = S.random_blocks("Q4_K", n, k, seed=500 + m + n)
+        x, xf = _activations(m, k, 600 + m, dtype, dev)
+        ref = oracle.gemm_quant(xf, blocks, "Q4_K", n, k)
+        y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), "Q4_K", variant="mma")
+        # the tensor-core path keeps integer products exact: hold it to the fp32 bar before output rounding
+        got = y.float().cpu().numpy()
+        _, rel, norm = oracle.max_errors(ref, got)
+        bound = 4e-3 if dtype == "bfloat16" else 6e-4     # output rounding of bf16 (2^-9) / fp16 (2^-11)
+        assert norm <= bound, (dtype, m, n, k, rel, norm)
+        _check(y, ref, dtype, ("mma", m, n, k))
+
+
+def test_gemm_bias_and_batch_dims(dev):
+    n, k = 48, 512
+    blocks = S.random_blocks("Q4_K", n, k, seed=700)
+    x = torch.randn(2, 3, k, device=dev, dtype=torch.bfloat16)
+    bias = torch.randn(n, device=dev, dtype=torch.bfloat16)
+    ref = oracle.gemm_quant(x.float().cpu().numpy().reshape(6, k), blocks, "Q4_K", n, k) + bias.float().cpu().numpy()
+    for variant in ("simt", "mma"):
+        y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), "Q4_K", bias, variant=variant)
+        assert y.shape == (2, 3, n)
+        _check(y.reshape(6, n), ref, "bfloat16", variant)
+
+
+def test_gemm_matches_reference_cpu_artifact_outputs(dev, golden_dir):
+    """Same seeded inputs the reference's CPU artifact was run on (fixtures made by tests/golden/make_golden.py).
+
+    For 16-bit dtypes the reference CPU path first rounds the dequantized weights to the storage dtype
+    (src/dinoml/constant_sources.py:72), the fused kernels keep them in fp32, so elements near zero differ
+    by that rounding.  Bars: normalised max error <= TOL, and the reference harness's own acceptance rule
+    for a 16-bit-dequantized comparison, max_abs <= 1e-1 or max_rel <= 3e-2
+    (tools/bench_ck_gguf_q8_gemm.hip:2945-2950); float32 is held to 1e-3 on both metrics."""
+    g = np.load(golden_dir / "gemm_rcr_reference_cpu.npz")
+    for i, case in enumerate(g["cases"]):
+        qtype, dtype, m, n, k = str(case).split("|")
+        m, n, k = int(m), int(n), int(k)
+        x = torch.from_numpy(g[f"case{i}_x_f32"]).to(dev).to(TDT[dtype])
+        y = kernels.gemm_rcr(x, torch.from_numpy(g[f"case{i}_blocks"]).to(dev), qtype)
+        ref = np.asarray(g[f"case{i}_y"], dtype=np.float32)
+        max_abs, rel, norm = oracle.max_errors(ref, y.float().cpu().numpy())
+        assert norm <= TOL[dtype], (i, qtype, dtype, norm)
+        if dtype == "float32":
+            assert rel <= 1e-3, (i, rel)
+        else:
+            assert max_abs <= 1e-1 or rel <= 3e-2, (i, qtype, dtype, max_abs, rel)
+
+
+def test_gemv_full_size_config2(dev):
+    """Config 2 (Q4_K 11008x4096, bf16, M in {1,4,16}) against the oracle on the full output."""
+    n, k = 11008, 4096
+    blocks = S.random_blocks("Q4_K", n, k, seed=2000)
+    bq = torch.from_numpy(blocks).to(dev)
+    for m in (1, 4, 16):
+        x, xf = _activations(m, k, 2001 + m, "bfloat16", dev)
+        ref = oracle.gemm_quant(xf, blocks, "Q4_K", n, k)
+        for variant in ("mma", "simt"):
+            y = kernels.gemm_rcr(x, bq, "Q4_K", variant=variant)
+            _check(y, ref, "bfloat16", (variant, m))
+    # linearity (size-independent property): f(x1 + x2) == f(x1) + f(x2) within rounding, float16 to keep sums exact-ish
+    x1 = torch.randn(1, k, device=dev, dtype=torch.float32)
+    x2 = torch.randn(1, k, device=dev, dtype=torch.float32)
+    f = lambda t: kernels.gemm_rcr(t, bq, "Q4_K", variant="simt").double()
+    lhs, rhs = f(x1 + x2), f(x1) + f(x2)
+    assert float((lhs - rhs).abs().max() / rhs.abs().max()) < 1e-5
+
+
+def test_error_paths(dev):
+    blocks = torch.from_numpy(S.random_blocks("Q4_K", 16, 256, seed=1)).to(dev)
+    x = torch.randn(1, 256, device=dev, dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        kernels.gemm_rcr(x.cpu(), blocks, "Q4_K")
+    with pytest.raises(ValueError):
+        kernels.gemm_rcr(x[:, :128].contiguous(), blocks, "Q4_K")
+    with pytest.raises(RuntimeError, match="shape outside"):
+        kernels.gemm_rcr(torch.randn(17, 256, device=dev, dtype=torch.bfloat16), blocks, "Q4_K", variant="mma")
+    with pytest.raises(RuntimeError, match="unsupported dtype"):
+        kernels.gemm_rcr(x.float(), blocks, "Q4_K", variant="mma")
