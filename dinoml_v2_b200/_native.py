@@ -45,6 +45,7 @@ def lib() -> ctypes.CDLL:
     L.dinoml_b200_gguf_gemm_rcr_workspace.restype = ctypes.c_size_t
     L.dinoml_b200_gguf_gemm_rcr_select.argtypes = [ci, ci, ci, ci, ci]
     L.dinoml_b200_gguf_gemm_rcr_select.restype = ci
+    L.dinoml_b200_gguf_device_status.restype = ci
     _lib = L
     return L
 

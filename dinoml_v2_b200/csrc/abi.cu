@@ -19,6 +19,7 @@ int gemm_rcr_umma(const void* a, const void* b, const void* bias, void* c, int q
 bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k);
 bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k);
 size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k);
+int umma_device_status();
 
 // Thread-local last error, same contract as the reference runtime (runtime/src/runtime_common.cpp:5-20).
 static thread_local std::string g_last_error;
@@ -107,6 +108,11 @@ float dinoml_profile_b200_gguf_gemm_rcr(const void* a, const void* b_quant, cons
 size_t dinoml_b200_gguf_gemm_rcr_workspace(int qtype, int dtype, int m, int n, int k, int variant) {
   if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, n, k);
   return variant == DINOML_B200_GGUF_VARIANT_UMMA ? gemm_umma_workspace(qtype, dtype, m, n, k) : 0;
+}
+
+int dinoml_b200_gguf_device_status(void) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  return umma_device_status();
 }
 
 int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k) {

@@ -1,7 +1,636 @@
-// placeholder until the tcgen05 kernel lands
+// Fused GGUF prefill GEMM ("umma" variant) on tcgen05 tensor cores with TMEM accumulators, M >= 17.
+//
+// C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), float16 / bfloat16, Q4_K and Q6_K weights.
+// Tensor-core bound for M >= 512 (Q6_K 4096x14336: 1248 FLOP per weight byte at M = 512).
+//
+// Swap-AB: the weight tile is the UMMA "A" operand (128 rows = UMMA M), the activation tile is "B"
+// (BM rows = UMMA N, 64..256), so D[n, m] lives in TMEM as 128 lanes x BM fp32 columns and one CTA
+// reuses every dequantized weight tile across BM activation rows.  Per CTA:
+//   * 16 producer warps (512 threads): stage the packed bytes of 128 weight rows x one 256-weight
+//     super-block global -> shared with 16-byte cp.async, copy their own words to registers, start the
+//     next super-block's copy, then unpack.  Warps 0-7 produce the two 64-wide K stages of the first
+//     half of the super-block, warps 8-15 those of the second half; thread (row = 32*(warp%4)+lane,
+//     half = (warp%8)/4) unpacks 32 weights per stage with 32-bit logic + packed bf16x2/f16x2 math and
+//     stores them as the K-major, 128-byte-swizzled tile UMMA reads (4 x 16-byte stores, conflict
+//     free); `fence.proxy.async` + mbarrier arrive.
+//   * warp 16, one lane: TMA (cp.async.bulk.tensor.2d, SWIZZLE_128B, no multicast) of the BM x 64
+//     activation tile per stage; rows past M are zero-filled by the tensor map.
+//   * warp 17, one lane: tcgen05.mma.cta_group::1.kind::f16 (128 x BM x 16, four per stage), then
+//     tcgen05.commit onto the stage's "empty" barrier; after the last stage onto the accumulator barrier.
+//   * epilogue: the 16 producer warps read TMEM (tcgen05.ld 32x32b.x16; warp%4 picks the lane quarter,
+//     warp/4 the column quarter), add bias, convert and store; or store fp32 partials for split-K.
+// Split-K (grid.z) fills the machine when (M/BM)*(N/128) < #SMs; partials go to a library-owned fp32
+// workspace and a second kernel sums them, adds bias and converts.
+//
+// Every mbarrier wait is bounded: after kSpinLimit polls the waiter records a code in a device status
+// word, raises a CTA-wide abort flag and every role falls through to the common teardown (outstanding
+// cp.async / TMA copies are waited for, TMEM is freed).  Nothing traps or spins forever.
+//
+// The reference has no counterpart kernel: its CUDA path dequantizes the whole weight to a dense
+// scratch and calls an Sm80 mma.sync CUTLASS GEMM (src/dinoml/lowering/ops/gemm.py:729-749,
+// kernels/cuda/src/cutlass_gemm.cu:56-89); the tile-level dequantize-then-MMA idea follows its
+// prototype WMMA kernels (kernels/rocm/src/ck_gguf_q8_gemm.hip:1209-1618).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
 #include "gguf_common.cuh"
+
 namespace b200gguf {
-bool gemm_umma_supports(int, int, int, int, int) { return false; }
-size_t gemm_umma_workspace(int, int, int, int, int) { return 0; }
-int gemm_rcr_umma(const void*, const void*, const void*, void*, int, int, int, int, int, cudaStream_t) { return RC_RANGE; }
+
+int check_gemm_args(const void* a, const void* b, const void* c, int qtype, int dtype, int m, int n, int k);
+
+namespace umma {
+
+constexpr int kRowsW = 128;            // weight rows per CTA (UMMA M)
+constexpr int kBK = 64;                // K per pipeline stage (one 128-byte swizzle atom of 16-bit values)
+constexpr int kProducerThreads = 512;
+constexpr int kGroupThreads = 256;     // producers of one K stage
+constexpr int kThreads = kProducerThreads + 64;
+constexpr int kWTileBytes = kRowsW * kBK * 2;   // 16 KiB
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+enum : int { ST_OK = 0, ST_EMPTY_TIMEOUT = 1, ST_FULL_TIMEOUT = 2, ST_ACC_TIMEOUT = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after flagging) if the phase never completes or the CTA is aborting.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) {
+      if (*abort_flag) return false;
+      __nanosleep(40);
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+// Bounded wait with no flagging, for teardown paths.
+__device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (i > 64) __nanosleep(40);
+  }
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void producer_bar_sync() { asm volatile("bar.sync 1, 512;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// K-major, SWIZZLE_128B shared-memory matrix descriptor: rows of 128 B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return uint64_t((addr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+         (uint64_t(2) << 61);
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// 16-bit pair arithmetic used to turn quants into MMA operand values.
+template <typename T> struct Pair;
+template <> struct Pair<__nv_bfloat16> {
+  static constexpr uint32_t kMagicBytes = 0x43434343u;   // 0x43qq = 128 + q
+  static constexpr float kMagic = 128.f;
+  static constexpr uint32_t kFormat = 1;                  // UMMA F16F32Format::BF16
+  static constexpr CUtensorMapDataType kTmaType = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  using V = __nv_bfloat162;
+  static __device__ __forceinline__ V splat(float f) { return __float2bfloat162_rn(f); }
+  static __device__ __forceinline__ __nv_bfloat16 cvt(float f) { return __float2bfloat16_rn(f); }
+  static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
+};
+template <> struct Pair<__half> {
+  static constexpr uint32_t kMagicBytes = 0x64646464u;   // 0x64qq = 1024 + q
+  static constexpr float kMagic = 1024.f;
+  static constexpr uint32_t kFormat = 0;                  // UMMA F16F32Format::F16
+  static constexpr CUtensorMapDataType kTmaType = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  using V = __half2;
+  static __device__ __forceinline__ V splat(float f) { return __float2half2_rn(f); }
+  static __device__ __forceinline__ __half cvt(float f) { return __float2half_rn(f); }
+  static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
+};
+template <typename V> __device__ __forceinline__ V as_pair(uint32_t r) { return *reinterpret_cast<V*>(&r); }
+template <typename V> __device__ __forceinline__ uint32_t as_u32(V v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// 4 quant bytes (values 0..255, here < 64) -> two pairs of (value - offset) * scale [+ addend].
+template <typename T>
+__device__ __forceinline__ void bytes_to_pairs(uint32_t u, typename Pair<T>::V off, typename Pair<T>::V scale, typename Pair<T>::V add,
+                                               uint32_t& p01, uint32_t& p23) {
+  using V = typename Pair<T>::V;
+  const V a = __hsub2(as_pair<V>(__byte_perm(u, Pair<T>::kMagicBytes, 0x4140)), off);
+  const V b = __hsub2(as_pair<V>(__byte_perm(u, Pair<T>::kMagicBytes, 0x4342)), off);
+  p01 = as_u32<V>(__hfma2(a, scale, add));
+  p23 = as_u32<V>(__hfma2(b, scale, add));
+}
+
+// 16 packed bytes starting S*2 bytes past a 16-byte aligned shared address, as four 32-bit words.  Q6_K
+// blocks are only 2-byte aligned, so their fields sit at one of 8 byte phases inside the staged chunks;
+// S is that phase (uniform across a warp whenever the weight rows are 16-byte multiples).
+template <int S>
+__device__ __forceinline__ void fetch16(const uint8_t* aligned, uint32_t* out) {
+  const uint4 c0 = *reinterpret_cast<const uint4*>(aligned);
+  if (S == 0) {
+    out[0] = c0.x; out[1] = c0.y; out[2] = c0.z; out[3] = c0.w;
+    return;
+  }
+  const uint4 c1 = *reinterpret_cast<const uint4*>(aligned + 16);
+  const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  constexpr int j = S >> 1;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) out[i] = (S & 1) ? __funnelshift_r(w[j + i], w[j + i + 1], 16) : w[j + i];
+}
+template <int S>
+__device__ __forceinline__ void q6k_fetch(const uint8_t* rowbase, int hb, int lhalf, uint32_t* qw) {
+  fetch16<S>(rowbase + 64 * hb + 16 * lhalf, qw);             // ql, quads 0/2
+  fetch16<S>(rowbase + 64 * hb + 32 + 16 * lhalf, qw + 4);    // ql, quads 1/3
+  fetch16<S>(rowbase + 128 + 32 * hb + 16 * lhalf, qw + 8);   // qh
+}
+
+__device__ __forceinline__ void sts_chunk(uint8_t* tile, int row, int chunk, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(a, b, c, d);
+}
+
+template <int QT> struct RawGeom;
+template <> struct RawGeom<QTYPE_Q4_K> { static constexpr int kPitch = 144, kChunks = 9; };
+template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240, kChunks = 14; };   // 15 chunks: 16-byte reads of 8 rows hit 32 banks
+
+template <int BM> constexpr int stage_bytes() { return kWTileBytes + BM * kBK * 2; }
+template <int BM> constexpr int num_stages() { return 4; }
+template <int QT, int BM> constexpr size_t smem_bytes() {
+  return 1024 + size_t(num_stages<BM>()) * stage_bytes<BM>() + size_t(kRowsW) * RawGeom<QT>::kPitch + 256;
+}
+
+struct Params {
+  const uint8_t* w;       // packed GGUF blocks [n, k/256 * block_bytes]
+  const void* bias;       // [n] or null (ignored when partial != null)
+  void* out;              // [m, n] in the activation dtype
+  float* partial;         // split-K workspace [splits, m, n] or null
+  int* status;            // device status word
+  int m, n, k;
+  int sb_per_split;       // super-blocks per grid.z slice
+};
+
+template <int QT, typename T, int BM>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
+  using P = Pair<T>;
+  using V = typename P::V;
+  constexpr int NS = num_stages<BM>();
+  constexpr int kStage = stage_bytes<BM>();
+  constexpr int kPitch = RawGeom<QT>::kPitch;
+  constexpr int kBlockBytes = QTraits<QT>::kBytes;
+  constexpr uint32_t kIdesc = (1u << 4) | (P::kFormat << 7) | (P::kFormat << 10) | (uint32_t(BM >> 3) << 17) | (uint32_t(kRowsW >> 4) << 24);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* raw = smem + NS * kStage;                                  // [128][kPitch]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRowsW * kPitch);
+  // bars[0..NS) wfull, [NS..2NS) xfull, [2NS..3NS) empty, [3NS] accumulator, [3NS+1] drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * NS + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto wfull = [&](int s) { return bar0 + 8u * s; };
+  auto xfull = [&](int s) { return bar0 + 8u * (NS + s); };
+  auto empty = [&](int s) { return bar0 + 8u * (2 * NS + s); };
+  const uint32_t accbar = bar0 + 8u * (3 * NS), drainbar = bar0 + 8u * (3 * NS + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * kRowsW;
+  const int nsb = p.k >> 8;
+  const int sb0 = blockIdx.z * p.sb_per_split, sb1 = min(nsb, sb0 + p.sb_per_split);
+  const int nstage_total = (sb1 - sb0) * 4;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(wfull(s), kGroupThreads);
+      mbar_init(xfull(s), 1);
+      mbar_init(empty(s), 1);
+    }
+    mbar_init(accbar, 1);
+    mbar_init(drainbar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 17) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(uint32_t(BM)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 16) {
+    // ------------------------------------------------------------------ producers
+    const int grp = warp >> 3;                                  // which half of the super-block (two K stages)
+    const int row = 32 * (warp & 3) + lane, lhalf = (warp >> 2) & 1;
+    const int64_t row_bytes = int64_t(nsb) * kBlockBytes;
+    const uint8_t* wrow = p.w + int64_t(min(n0 + row, p.n - 1)) * row_bytes;
+    // raw copy role: 4 threads per row, each up to 4 16-byte chunks
+    const int cp_row = tid >> 2, cp_q = tid & 3;
+    const uint8_t* cp_wrow = p.w + int64_t(min(n0 + cp_row, p.n - 1)) * row_bytes;
+    auto issue_raw = [&](int sb) {
+      if (sb < sb1) {
+        const uint8_t* src = cp_wrow + int64_t(sb) * kBlockBytes;
+        const uint32_t shift = uint32_t(reinterpret_cast<uintptr_t>(src) & 15);
+        const int nchunk = int(shift + kBlockBytes + 15) >> 4;
+        const uint8_t* src16 = src - shift;
+        const uint32_t dst = smem_u32(raw + cp_row * kPitch);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = cp_q * 4 + j;
+          if (c < nchunk) cp_async16(dst + 16 * c, src16 + 16 * c);
+        }
+      }
+      cp_async_commit();
+    };
+    issue_raw(sb0);
+    bool alive = true;
+    for (int sb = sb0; sb < sb1 && alive; ++sb) {
+      cp_async_wait<0>();
+      producer_bar_sync();                 // super-block sb landed and is visible to all producers
+      const uint8_t* blk = raw + row * kPitch + (reinterpret_cast<uintptr_t>(wrow + int64_t(sb) * kBlockBytes) & 15);
+      // ---- copy this thread's packed words to registers
+      uint32_t qw[12];
+      float dscale, dmin = 0.f;
+      float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3; Q4_K: (ds, dm) of the two groups
+      if (QT == QTYPE_Q4_K) {
+        const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+        dscale = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
+        dmin = half_bits_to_float(uint16_t(hdr.x >> 16));
+        // sub-blocks 4*grp .. 4*grp+3 belong to this thread's two groups
+        const uint32_t scw = grp == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4));
+        const uint32_t mnw = grp == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4));
+        qw[8] = scw;
+        qw[9] = mnw;
+#pragma unroll
+        for (int ls = 0; ls < 2; ++ls) {
+          const uint4 q = *reinterpret_cast<const uint4*>(blk + 16 + 32 * (2 * grp + ls) + 16 * lhalf);
+          qw[4 * ls] = q.x; qw[4 * ls + 1] = q.y; qw[4 * ls + 2] = q.z; qw[4 * ls + 3] = q.w;
+        }
+        sub_scale[0] = sub_scale[1] = sub_scale[2] = sub_scale[3] = 0.f;
+      } else {
+        const int hb = grp;
+        dscale = half_bits_to_float(uint16_t(*reinterpret_cast<const uint16_t*>(blk + 208)));
+        const uint8_t* rowbase = raw + row * kPitch;
+        switch (int(blk - rowbase) >> 1) {
+          case 0: q6k_fetch<0>(rowbase, hb, lhalf, qw); break;
+          case 1: q6k_fetch<1>(rowbase, hb, lhalf, qw); break;
+          case 2: q6k_fetch<2>(rowbase, hb, lhalf, qw); break;
+          case 3: q6k_fetch<3>(rowbase, hb, lhalf, qw); break;
+          case 4: q6k_fetch<4>(rowbase, hb, lhalf, qw); break;
+          case 5: q6k_fetch<5>(rowbase, hb, lhalf, qw); break;
+          case 6: q6k_fetch<6>(rowbase, hb, lhalf, qw); break;
+          default: q6k_fetch<7>(rowbase, hb, lhalf, qw); break;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          sub_scale[i] = float(int(*reinterpret_cast<const int8_t*>(blk + 192 + 8 * hb + 2 * i + lhalf)));
+      }
+      producer_bar_sync();                 // every producer holds its words: the raw buffer may be refilled
+      issue_raw(sb + 1);
+#pragma unroll
+      for (int ls = 0; ls < 2; ++ls) {
+        const int st = 2 * grp + ls;
+        const int gs = (sb - sb0) * 4 + st;
+        const int slot = gs % NS, use = gs / NS;
+        if (use > 0 && !mbar_wait(empty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) { alive = false; break; }
+        uint8_t* tile = smem + slot * kStage;
+        if (QT == QTYPE_Q4_K) {
+          // stage = 64-weight group: low nibbles -> sub-block 2*st (k' 0..31), high -> 2*st+1 (k' 32..63)
+          const int sh = 16 * ls;
+          const float sc0 = float((qw[8] >> sh) & 0xff), sc1 = float((qw[8] >> (sh + 8)) & 0xff);
+          const float mn0 = float((qw[9] >> sh) & 0xff), mn1 = float((qw[9] >> (sh + 8)) & 0xff);
+          const V off = P::splat(P::kMagic);
+          const V s_lo = P::splat(dscale * sc0), a_lo = P::splat(-(dmin * mn0));
+          const V s_hi = P::splat(dscale * sc1), a_hi = P::splat(-(dmin * mn1));
+          uint32_t lo[8], hi[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            bytes_to_pairs<T>(qw[4 * ls + i] & 0x0f0f0f0fu, off, s_lo, a_lo, lo[2 * i], lo[2 * i + 1]);
+            bytes_to_pairs<T>((qw[4 * ls + i] >> 4) & 0x0f0f0f0fu, off, s_hi, a_hi, hi[2 * i], hi[2 * i + 1]);
+          }
+          sts_chunk(tile, row, 2 * lhalf, lo[0], lo[1], lo[2], lo[3]);
+          sts_chunk(tile, row, 2 * lhalf + 1, lo[4], lo[5], lo[6], lo[7]);
+          sts_chunk(tile, row, 4 + 2 * lhalf, hi[0], hi[1], hi[2], hi[3]);
+          sts_chunk(tile, row, 4 + 2 * lhalf + 1, hi[4], hi[5], hi[6], hi[7]);
+        } else {
+          // stage = (half block grp, quad pair ls): quads 2*ls (k' 0..31) and 2*ls+1 (k' 32..63)
+          const V off = P::splat(P::kMagic + 32.f);
+          const V zero = P::splat(0.f);
+#pragma unroll
+          for (int qo = 0; qo < 2; ++qo) {
+            const int quad = 2 * ls + qo;
+            const V s2 = P::splat(dscale * sub_scale[quad]);
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t l4 = (qw[4 * qo + i] >> (4 * ls)) & 0x0f0f0f0fu;
+              const uint32_t h2 = ((qw[8 + i] >> (2 * quad)) & 0x03030303u) << 4;
+              bytes_to_pairs<T>(l4 | h2, off, s2, zero, o[2 * i], o[2 * i + 1]);
+            }
+            sts_chunk(tile, row, 4 * qo + 2 * lhalf, o[0], o[1], o[2], o[3]);
+            sts_chunk(tile, row, 4 * qo + 2 * lhalf + 1, o[4], o[5], o[6], o[7]);
+          }
+        }
+        fence_proxy_async();
+        mbar_arrive(wfull(slot));
+      }
+    }
+    cp_async_wait<0>();
+
+    // ------------------------------------------------------------------ epilogue
+    if (alive && nstage_total > 0 && mbar_wait(accbar, 0, abort_flag, p.status, ST_ACC_TIMEOUT)) {
+      tcgen05_fence_after();
+      const int n_row = n0 + row;
+      const float bias_v = (p.partial == nullptr && p.bias != nullptr && n_row < p.n) ? P::up(static_cast<const T*>(p.bias)[n_row]) : 0.f;
+      constexpr int kColsPerWarp = BM / 4;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
+        const int col = (warp >> 2) * kColsPerWarp + c0;
+        uint32_t r[16];
+        tmem_ld16(tmem_base + (uint32_t(32 * (warp & 3)) << 16) + uint32_t(col), r);
+        tmem_ld_wait();
+        if (n_row < p.n) {
+          if (p.partial != nullptr) {
+            float* dst = p.partial + (int64_t(blockIdx.z) * p.m + m0 + col) * p.n + n_row;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (m0 + col + j < p.m) dst[int64_t(j) * p.n] = __uint_as_float(r[j]);
+          } else {
+            T* dst = static_cast<T*>(p.out) + int64_t(m0 + col) * p.n + n_row;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (m0 + col + j < p.m) dst[int64_t(j) * p.n] = P::cvt(__uint_as_float(r[j]) + bias_v);
+          }
+        }
+      }
+      tcgen05_fence_before();
+    }
+  } else if (warp == 16) {
+    // ------------------------------------------------------------------ activation TMA
+    if (lane == 0) {
+      int issued = 0;
+      for (int gs = 0; gs < nstage_total; ++gs) {
+        const int slot = gs % NS, use = gs / NS;
+        if (use > 0 && !mbar_wait(empty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
+        mbar_arrive_expect_tx(xfull(slot), uint32_t(BM * kBK * 2));
+        tma_load_2d(smem_u32(smem + slot * kStage + kWTileBytes), &x_map, xfull(slot), sb0 * 256 + gs * kBK, m0);
+        issued = gs + 1;
+      }
+      if (*abort_flag) {   // make sure no bulk copy is still writing this CTA's shared memory at exit
+        for (int gs = max(0, issued - NS); gs < issued; ++gs) mbar_wait_plain(xfull(gs % NS), uint32_t(gs / NS) & 1u);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      bool ok = true;
+      for (int gs = 0; gs < nstage_total && ok; ++gs) {
+        const int slot = gs % NS, use = gs / NS;
+        ok = mbar_wait(wfull(slot), uint32_t(use) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) &&
+             mbar_wait(xfull(slot), uint32_t(use) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_u32(smem + slot * kStage), b_addr = a_addr + kWTileBytes;
+        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
+#pragma unroll
+        for (int kk = 0; kk < kBK / 16; ++kk)
+          umma_f16_ss(tmem_base, da + uint64_t(2 * kk), db + uint64_t(2 * kk), kIdesc, (gs > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(empty(slot));
+      }
+      if (ok && nstage_total > 0) {
+        umma_commit(accbar);
+      } else if (nstage_total > 0) {   // aborting: let every MMA already issued finish before TMEM is freed
+        umma_commit(drainbar);
+        mbar_wait_plain(drainbar, 0);
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 17) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(uint32_t(BM)) : "memory");
+  }
+}
+
+// Split-K finish: out[m,n] = sum_z partial[z,m,n] + bias[n], converted to the activation dtype.
+template <typename T>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, const T* __restrict__ bias, T* __restrict__ out, int64_t mn,
+                                     int n, int splits) {
+  const int64_t i = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i >= mn) return;   // mn % 4 == 0 because n % 4 == 0 is required by the launcher
+  float4 acc = *reinterpret_cast<const float4*>(partial + i);
+  for (int z = 1; z < splits; ++z) {
+    const float4 v = *reinterpret_cast<const float4*>(partial + int64_t(z) * mn + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if (bias != nullptr) {
+    const int col = int(i % n);
+    acc.x += Pair<T>::up(bias[col]); acc.y += Pair<T>::up(bias[col + 1]);
+    acc.z += Pair<T>::up(bias[col + 2]); acc.w += Pair<T>::up(bias[col + 3]);
+  }
+  T* o = out + i;
+  o[0] = Pair<T>::cvt(acc.x); o[1] = Pair<T>::cvt(acc.y); o[2] = Pair<T>::cvt(acc.z); o[3] = Pair<T>::cvt(acc.w);
+}
+
+// ---------------------------------------------------------------------------------------- host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess) return EncodeTiledFn(nullptr);
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+struct DeviceState {
+  int* status = nullptr;
+  float* workspace = nullptr;
+  size_t workspace_bytes = 0;
+};
+static std::mutex g_mutex;
+static std::unordered_map<int, DeviceState> g_state;
+
+static DeviceState* device_state(size_t need_workspace) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceState& st = g_state[dev];
+  if (st.status == nullptr) {
+    if (cudaMalloc(&st.status, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(st.status, 0, sizeof(int));
+  }
+  if (need_workspace > st.workspace_bytes) {
+    // Grown outside of stream capture only: callers warm a shape up once before capturing a graph.
+    if (st.workspace != nullptr) { cudaDeviceSynchronize(); cudaFree(st.workspace); st.workspace = nullptr; st.workspace_bytes = 0; }
+    if (cudaMalloc(&st.workspace, need_workspace) != cudaSuccess) return nullptr;
+    st.workspace_bytes = need_workspace;
+  }
+  return &st;
+}
+
+struct Plan { int bm, splits, sb_per_split; };
+
+static Plan make_plan(int m, int n, int k) {
+  Plan pl;
+  pl.bm = m <= 64 ? 64 : m <= 128 ? 128 : 256;
+  const int tiles = ((m + pl.bm - 1) / pl.bm) * ((n + kRowsW - 1) / kRowsW);
+  const int nsb = k / 256;
+  int sm_count = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  int splits = 1;
+  while (splits < 8 && tiles * splits * 2 <= sm_count && nsb / (splits * 2) >= 4) splits *= 2;
+  if (n % 4) splits = 1;   // the reduce kernel works on float4
+  pl.sb_per_split = (nsb + splits - 1) / splits;
+  pl.splits = (nsb + pl.sb_per_split - 1) / pl.sb_per_split;
+  return pl;
+}
+
+template <int QT, typename T, int BM>
+static int launch(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const Plan& pl, cudaStream_t s) {
+  EncodeTiledFn enc = encode_tiled();
+  if (enc == nullptr) return RC_LAUNCH;
+  const size_t ws = pl.splits > 1 ? size_t(pl.splits) * m * n * sizeof(float) : 0;
+  DeviceState* st = device_state(ws);
+  if (st == nullptr) return RC_LAUNCH;
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(m)};
+  const cuuint64_t strides[1] = {cuuint64_t(k) * 2};
+  const cuuint32_t box[2] = {cuuint32_t(kBK), cuuint32_t(BM)};
+  const cuuint32_t estr[2] = {1, 1};
+  if (enc(&map, Pair<T>::kTmaType, 2, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return RC_LAUNCH;
+  auto kern = gemm_umma_kernel<QT, T, BM>;
+  constexpr size_t smem = smem_bytes<QT, BM>();
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
+    attr_set = true;
+  }
+  Params p;
+  p.w = static_cast<const uint8_t*>(b);
+  p.bias = bias;
+  p.out = c;
+  p.partial = pl.splits > 1 ? st->workspace : nullptr;
+  p.status = st->status;
+  p.m = m; p.n = n; p.k = k;
+  p.sb_per_split = pl.sb_per_split;
+  const dim3 grid((m + BM - 1) / BM, (n + kRowsW - 1) / kRowsW, pl.splits);
+  kern<<<grid, kThreads, smem, s>>>(map, p);
+  if (cudaGetLastError() != cudaSuccess) return RC_LAUNCH;
+  if (pl.splits > 1) {
+    const int64_t mn = int64_t(m) * n;
+    const int threads = 256;
+    const int64_t blocks = (mn / 4 + threads - 1) / threads;
+    splitk_reduce_kernel<T><<<unsigned(blocks), threads, 0, s>>>(st->workspace, static_cast<const T*>(bias), static_cast<T*>(c), mn, n,
+                                                                 pl.splits);
+    if (cudaGetLastError() != cudaSuccess) return RC_LAUNCH;
+  }
+  return RC_OK;
+}
+
+template <int QT, typename T>
+static int launch_bm(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+  const Plan pl = make_plan(m, n, k);
+  switch (pl.bm) {
+    case 64: return launch<QT, T, 64>(a, b, bias, c, m, n, k, pl, s);
+    case 128: return launch<QT, T, 128>(a, b, bias, c, m, n, k, pl, s);
+    default: return launch<QT, T, 256>(a, b, bias, c, m, n, k, pl, s);
+  }
+}
+
+}  // namespace umma
+
+bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k) {
+  (void)n;
+  return (qtype == QTYPE_Q4_K || qtype == QTYPE_Q6_K) && (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 17 && k % 256 == 0;
+}
+
+size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k) {
+  if (!gemm_umma_supports(qtype, dtype, m, n, k)) return 0;
+  const umma::Plan pl = umma::make_plan(m, n, k);
+  return pl.splits > 1 ? size_t(pl.splits) * m * n * sizeof(float) : 0;
+}
+
+int gemm_rcr_umma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                  cudaStream_t s) {
+  if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
+  if (dtype == DINO_F32) return RC_DTYPE;
+  if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
+  if (reinterpret_cast<uintptr_t>(b) & 15) return RC_ALIGN;        // 16-byte cp.async sources
+  if ((int64_t(k) * 2) & 15) return RC_ALIGN;                       // TMA row pitch
+  if (dtype == DINO_BF16)
+    return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, s)
+                               : umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, s);
+  return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, s)
+                             : umma::launch_bm<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, s);
+}
+
+// Reads (and clears) the device status word the bounded waits write; 0 = no wait ever gave up.
+int umma_device_status() {
+  int dev = 0, value = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  std::lock_guard<std::mutex> lock(umma::g_mutex);
+  auto it = umma::g_state.find(dev);
+  if (it == umma::g_state.end() || it->second.status == nullptr) return 0;
+  if (cudaMemcpy(&value, it->second.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (value != 0) cudaMemset(it->second.status, 0, sizeof(int));
+  return value;
+}
+
+}  // namespace b200gguf

@@ -79,3 +79,8 @@ def profile_gemm_rcr(a, b_quant, qtype, out, *, variant: str, iterations: int, b
 def select_variant(qtype, dtype: str, m: int, n: int, k: int) -> str:
     q = qtype_of(qtype)
     return _native.VARIANT_NAMES[_native.lib().dinoml_b200_gguf_gemm_rcr_select(q.value, _native.DINO_DTYPE[dtype], m, n, k)]
+
+
+def device_status() -> int:
+    """Synchronizes and returns the status word written by bounded device-side waits (0 = none gave up)."""
+    return int(_native.lib().dinoml_b200_gguf_device_status())

@@ -75,6 +75,12 @@ DINOML_B200_API size_t dinoml_b200_gguf_gemm_rcr_workspace(int qtype, int dtype,
  * if/else text, src/dinoml/lowering/ops/gemm.py:656-698). */
 DINOML_B200_API int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k);
 
+/* The tcgen05 kernel bounds every barrier wait; a wait that gives up records a code in a per-device
+ * status word instead of hanging or trapping.  Synchronizes the device, returns the word (0 = never
+ * happened; 1 / 2 / 3 = a stage-free / stage-ready / accumulator wait gave up; < 0 = CUDA error) and clears it.
+ * No counterpart in the reference. */
+DINOML_B200_API int dinoml_b200_gguf_device_status(void);
+
 /* Per-candidate symbols, named like the reference's kernel symbols so a manifest can carry them:
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_bias_<dtype>_<variant>_v1(a, b_quant, bias, c, m, n, k, stream)
