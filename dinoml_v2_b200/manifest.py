@@ -1,0 +1,180 @@
+"""Kernel manifest for GGUF quantized linears: provider `b200_gguf_gemm`, its candidate catalogue, the
+per-node `gguf_direct` plan and the execution-plan overlay.
+
+Schema follows the reference so its tooling reads the same keys: a required-kernel item like
+src/dinoml/kernels/manifest.py:265-321, candidates like src/dinoml/kernels/providers/cutlass/gemm.py:
+517-554 (the `cutlass{...}` tuning block is replaced by a `b200{...}` block), the plan object like
+`_gguf_runtime_dequant_gemm_rhs_plan` (src/dinoml/kernels/manifest.py:754-817) and `apply_execution_plan`
+like src/dinoml/kernels/manifest.py:1034-1131.  What changes: kind is `gguf_direct_dequantize_in_kernel`,
+there is no dequantization scratch and so no `session_resources` entry of that kind, bfloat16 is
+admitted, and the quantization type is part of every cache key."""
+from __future__ import annotations
+
+import hashlib
+import json
+from typing import Any, Mapping
+
+from .constant_sources import GGUF_MATERIALIZATION_DIRECT_DEQUANTIZE_IN_KERNEL, validate_gguf_constant_policy
+from .gguf_blocks import qtype_of
+
+KERNEL_LIBRARY = "b200_gguf_gemm"
+KERNEL_MANIFEST_SCHEMA_VERSION = 4
+KERNEL_ABI_VERSION = 1
+PROFILE_CACHE_SCHEMA_VERSION = 9
+EXECUTION_PLAN_KERNEL_LIBRARIES = (KERNEL_LIBRARY,)          # src/dinoml/kernels/manifest.py:98-105
+SUPPORTED_OPS = ("gemm_rcr", "gemm_rcr_bias")
+VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3}
+
+_B200_TUNING = {
+    "simt": {"kind": "gemv_simt", "rows_per_warp": 1, "activation_rows_per_pass": 4, "staging": "ldg", "tensor_cores": "none"},
+    "mma": {"kind": "gemv", "rows_per_cta": 16, "k_slices": 4, "stages": 3, "staging": "cp_async16",
+            "tensor_cores": "mma.sync.m16n8k16", "max_m": 16},
+    "umma": {"kind": "umma_gemm", "tile_n": 128, "tile_m": [64, 128, 256], "tile_k": 64, "stages": 4, "staging": "cp_async16+tma",
+             "tensor_cores": "tcgen05.mma.cta_group::1.kind::f16", "accumulator": "tmem", "split_k": "auto", "min_m": 17},
+}
+
+
+def canonical_json(obj: Any) -> str:
+    return json.dumps(obj, sort_keys=True, separators=(",", ":"))
+
+
+def sha256_of(obj: Any) -> str:
+    return hashlib.sha256(canonical_json(obj).encode("utf-8")).hexdigest()
+
+
+def candidate_variants(qtype: str, dtype: str) -> list[str]:
+    """Which kernel variants exist for a (qtype, dtype)."""
+    variants = ["simt"]
+    if dtype in ("float16", "bfloat16"):
+        if qtype == "Q4_K":
+            variants.append("mma")
+        if qtype in ("Q4_K", "Q6_K"):
+            variants.append("umma")
+    return variants
+
+
+def variant_supports(variant: str, m: int) -> bool:
+    return {"simt": True, "mma": 1 <= m <= 16, "umma": m >= 17}[variant]
+
+
+def kernel_symbol(qtype: str, op: str, dtype: str, variant: str, *, profile: bool = False) -> str:
+    q = qtype_of(qtype)
+    return f"dinoml_{'profile_' if profile else ''}b200_gguf_{q.symbol}_{op}_{dtype}_{variant}_v1"
+
+
+def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, Any]:
+    q = qtype_of(qtype)
+    has_bias = op.endswith("_bias")
+    cand = {
+        "candidate_id": f"b200_gguf_{q.symbol}_{dtype}_{variant}_v1",
+        "symbol_id": f"{q.symbol}_{variant}_v1",
+        "provider": KERNEL_LIBRARY, "family": "gemm", "op": op, "dtype": dtype, "qtype": q.name,
+        "layouts": {"a": "row", "b": "column", "c": "row"},
+        "epilogue": "linear_combination_bias" if has_bias else "linear_combination",
+        "epilogue_config": {"name": "bias" if has_bias else "identity", "inputs": ["bias"] if has_bias else [], "activation": None,
+                            "bias_axis": "n" if has_bias else None, "accumulator_dtype": "float32", "output_dtype": dtype,
+                            "launch_abi": "gguf_gemm_rcr_bias_v1" if has_bias else "gguf_gemm_rcr_v1"},
+        "accumulator_dtype": "float32", "optional": variant != "simt",
+        "launch_abi": "gguf_gemm_rcr_bias_v1" if has_bias else "gguf_gemm_rcr_v1",
+        "split_k_values": [1], "split_k_default": 1, "supports_split_k": False, "workspace_nbytes": 0,
+        "b200": dict(_B200_TUNING[variant]),
+        "kernel_symbol": kernel_symbol(q.name, op, dtype, variant),
+        "profiler_symbol": kernel_symbol(q.name, "gemm_rcr", dtype, variant, profile=True),
+        "variant": variant, "variant_code": VARIANT_CODES[variant],
+    }
+    cand["candidate_config_key"] = sha256_of({k: cand[k] for k in ("provider", "op", "dtype", "qtype", "variant", "b200", "launch_abi")})
+    return cand
+
+
+def gguf_candidate_set(qtype: str, op: str, dtype: str) -> dict[str, Any]:
+    cands = [gguf_candidate(qtype, op, dtype, v) for v in candidate_variants(qtype, dtype)]
+    set_id = f"{KERNEL_LIBRARY}_{qtype_of(qtype).symbol}_{op}_{dtype}_v1"
+    return {"candidate_set_id": set_id, "candidates": cands,
+            "candidate_set_key": sha256_of({"id": set_id, "configs": [c["candidate_config_key"] for c in cands]})}
+
+
+def validate_gguf_direct_admission(node: Mapping[str, Any], const: Mapping[str, Any], target: str) -> None:
+    """Counterpart of _validate_gguf_runtime_dequant_admission (src/dinoml/compiler.py:903-972)."""
+    storage = const.get("storage") or {}
+    if target != "cuda":
+        raise NotImplementedError(f"GGUF-encoded constants are only lowered for the cuda target, got {target!r}")
+    if node["op"] not in SUPPORTED_OPS:
+        raise NotImplementedError(f"GGUF-encoded weights are supported for {SUPPORTED_OPS}, got {node['op']!r}")
+    if node["inputs"].index(const["name"]) != 1:
+        raise NotImplementedError("a GGUF-encoded constant must be the B (weight) operand of gemm_rcr")
+    if const["dtype"] not in ("float16", "float32", "bfloat16"):
+        raise NotImplementedError(f"unsupported logical dtype {const['dtype']!r}")
+    if storage.get("materialization") != GGUF_MATERIALIZATION_DIRECT_DEQUANTIZE_IN_KERNEL:
+        raise NotImplementedError(f"materialization {storage.get('materialization')!r} is not lowered; use "
+                                  f"{GGUF_MATERIALIZATION_DIRECT_DEQUANTIZE_IN_KERNEL!r}")
+    validate_gguf_constant_policy(storage["materialization"], storage["residency"], require_runtime_supported=True)
+
+
+def gguf_direct_plan(node: Mapping[str, Any], const: Mapping[str, Any]) -> dict[str, Any]:
+    st = const["storage"]
+    return {
+        "schema_version": 1, "kind": "gguf_direct_dequantize_in_kernel", "status": "lowered_fused_kernel",
+        "node_id": node["id"], "op": node["op"], "operand": "b", "constant": const["name"], "storage_kind": "gguf",
+        "materialization": st["materialization"], "residency": st["residency"], "qtype": st["qtype"], "qtype_value": st["qtype_value"],
+        "encoded_nbytes": st["encoded_nbytes"], "n_per_row": st["n_per_row"], "logical_dtype": const["dtype"],
+        "logical_shape": list(const["shape"]), "scratch_nbytes": 0, "dequant_scratch": None, "dense_launcher": None,
+    }
+
+
+def build_kernel_manifest(graph: Mapping[str, Any], target: Mapping[str, Any]) -> dict[str, Any]:
+    consts = {c["name"]: c for c in graph["constants"]}
+    required = []
+    for node in graph["nodes"]:
+        if node["op"] not in SUPPORTED_OPS:
+            raise NotImplementedError(f"op {node['op']!r} is outside the quantized-linear path")
+        weight = consts.get(node["inputs"][1])
+        if weight is None or (weight.get("storage") or {}).get("kind") != "gguf":
+            raise NotImplementedError(f"node {node['id']}: the weight of {node['op']} must be a GGUF-encoded constant "
+                                      "(dense GEMMs are outside this runtime)")
+        validate_gguf_direct_admission(node, weight, target["name"])
+        qtype, dtype = weight["storage"]["qtype"], weight["dtype"]
+        cset = gguf_candidate_set(qtype, node["op"], dtype)
+        required.append({
+            "node_id": node["id"], "op": node["op"], "dtype": dtype, "qtype": qtype,
+            "kernel_symbol": "dinoml_b200_gguf_gemm_rcr", "kernel_library": KERNEL_LIBRARY,
+            "profiler_symbol": "dinoml_profile_b200_gguf_gemm_rcr", "has_profiler": True,
+            "support_archive": "libdinoml_b200_gguf.so",
+            "selected_candidate_id": None, "selection": "shape_guarded_auto",
+            "candidates": cset["candidates"], "candidate_set_id": cset["candidate_set_id"], "candidate_set_key": cset["candidate_set_key"],
+            "gguf_direct": gguf_direct_plan(node, weight), "execution_plan_dispatch": [],
+        })
+    manifest = {"schema_version": KERNEL_MANIFEST_SCHEMA_VERSION, "kernel_abi_version": KERNEL_ABI_VERSION,
+                "profile_cache_schema_version": PROFILE_CACHE_SCHEMA_VERSION, "target": dict(target), "required_kernels": required,
+                "codegen_strategy": "interpreted_launch_plan", "profiler_strategy": "native_candidate_timer", "session_resources": []}
+    manifest["cache_key"] = sha256_of(manifest)
+    return manifest
+
+
+def apply_execution_plan(manifest: Mapping[str, Any], plan: Mapping[str, Any]) -> dict[str, Any]:
+    """Overlays profiled selections: one static candidate per node when every profiled shape agreed, else a guarded
+    per-shape dispatch list (src/dinoml/kernels/manifest.py:1086-1116)."""
+    out = json.loads(json.dumps(manifest))
+    if plan.get("kind") != "dinoml.execution_plan":
+        raise ValueError("not an execution plan")
+    by_node: dict[str, list[dict[str, Any]]] = {}
+    for sel in plan.get("selections", []):
+        if sel.get("kernel_library") in EXECUTION_PLAN_KERNEL_LIBRARIES:
+            by_node.setdefault(sel["node_id"], []).append(sel)
+    for item in out["required_kernels"]:
+        sels = by_node.get(item["node_id"], [])
+        valid = {c["candidate_id"]: c for c in item["candidates"]}
+        sels = [s for s in sels if s["selected_candidate_id"] in valid and s["candidate_set_key"] == item["candidate_set_key"]]
+        if not sels:
+            continue
+        chosen = {s["selected_candidate_id"] for s in sels}
+        if len(chosen) == 1:
+            item["selected_candidate_id"] = next(iter(chosen))
+            item["execution_plan_selection"] = "static"
+        item["execution_plan_dispatch"] = [
+            {"m": s["shape"]["m"], "n": s["shape"]["n"], "k": s["shape"]["k"], "candidate_id": s["selected_candidate_id"],
+             "variant": valid[s["selected_candidate_id"]]["variant"], "variant_code": valid[s["selected_candidate_id"]]["variant_code"],
+             "confident": bool(s.get("confidence", {}).get("confident", False))} for s in sels]
+    out["execution_plan_key"] = plan.get("execution_plan_key")
+    out.pop("cache_key", None)
+    out["cache_key"] = sha256_of(out)
+    return out

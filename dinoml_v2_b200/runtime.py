@@ -1,0 +1,270 @@
+"""Python runtime loader: `runtime.load(artifact)` -> RuntimeModule -> Session, over the `dino_*` C ABI with ctypes.
+
+Same surface as the reference loader for this path (src/dinoml/runtime.py): ABI check (:141,160), deferred module
+load (:165), `load_constants` (:213-232), `load_encoded_constants` with its load plan (:249-346), H2D staging +
+`dino_module_set_encoded_constant` (:660-703), sessions (:209-211, 888-909), `run_numpy` / `run_torch` /
+`run_device_pointers` (:942, :1371-1431, :1172-1192) and the native benchmark with its summary
+(:966-977, 1311-1369, 1854-1866).  torch is used only to own device buffers and streams."""
+from __future__ import annotations
+
+import ctypes
+import json
+import statistics
+import weakref
+from pathlib import Path
+from typing import Any, Mapping
+
+import numpy as np
+
+from .frontend import DTYPE_ENUM, DTYPE_NBYTES, RUNTIME_ABI_VERSION
+
+DEVICE_CUDA = 1
+FLAG_CONTIGUOUS = 1
+
+
+class _DinoTensor(ctypes.Structure):      # runtime/include/dinoml/abi.h:36-57
+    _fields_ = [("data", ctypes.c_void_p), ("shape", ctypes.POINTER(ctypes.c_int64)), ("ndim", ctypes.c_size_t),
+                ("dtype", ctypes.c_int), ("strides", ctypes.POINTER(ctypes.c_int64)), ("byte_offset", ctypes.c_size_t),
+                ("nbytes", ctypes.c_size_t), ("device_type", ctypes.c_int), ("flags", ctypes.c_uint32),
+                ("alignment", ctypes.c_size_t)]
+
+
+def _configure(lib: ctypes.CDLL) -> None:
+    vp, sz, ci = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    T = ctypes.POINTER(_DinoTensor)
+    lib.dino_abi_version.restype = ci
+    lib.dino_get_last_error.restype = ctypes.c_char_p
+    for name, args in {
+        "dino_module_load": [ctypes.c_char_p, ctypes.POINTER(vp)], "dino_module_load_deferred": [ctypes.c_char_p, ctypes.POINTER(vp)],
+        "dino_module_load_constants": [vp, ctypes.c_char_p], "dino_module_unload_constants": [vp],
+        "dino_module_set_constant": [vp, ctypes.c_char_p, T], "dino_module_set_encoded_constant": [vp, ctypes.c_char_p, vp, sz],
+        "dino_module_free": [vp], "dino_session_create": [vp, ctypes.POINTER(vp)], "dino_session_destroy": [vp],
+        "dino_session_set_stream": [vp, vp],
+        "dino_session_get_output_shape": [vp, sz, ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(sz)],
+        "dino_session_run": [vp, T, sz, T, sz],
+        "dino_session_benchmark": [vp, T, sz, T, sz, sz, sz, ctypes.POINTER(ctypes.c_double), sz],
+        "dino_device_malloc": [ctypes.POINTER(vp), sz], "dino_device_free": [vp], "dino_copy_host_to_device": [vp, vp, sz],
+    }.items():
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = args, ci
+    lib.dino_module_get_metadata_json.argtypes = [vp]
+    lib.dino_module_get_metadata_json.restype = ctypes.c_char_p
+
+
+def _tensor_struct(ptr: int, shape, dtype: str, keep: list) -> _DinoTensor:
+    arr = (ctypes.c_int64 * len(shape))(*[int(d) for d in shape])
+    keep.append(arr)
+    numel = 1
+    for d in shape:
+        numel *= int(d)
+    return _DinoTensor(ptr, arr, len(shape), DTYPE_ENUM[dtype], None, 0, numel * DTYPE_NBYTES[dtype], DEVICE_CUDA, FLAG_CONTIGUOUS, 0)
+
+
+def load(path: str | Path, *, load_constants: bool | None = None) -> "RuntimeModule":
+    return RuntimeModule(Path(path), load_constants=load_constants)
+
+
+class RuntimeModule:
+    def __init__(self, path: Path, load_constants: bool | None = None):
+        self.path = Path(path)
+        manifest = json.loads((self.path / "manifest.json").read_text())
+        if manifest.get("runtime_abi_version") != RUNTIME_ABI_VERSION:
+            raise RuntimeError(f"artifact ABI {manifest.get('runtime_abi_version')} != runtime ABI {RUNTIME_ABI_VERSION}")
+        module_path = self.path / manifest.get("module", "module.so")
+        if not module_path.exists():
+            raise RuntimeError(f"{module_path} is missing: the CUDA library was not built (there is no CPU fallback)")
+        self._lib = ctypes.CDLL(str(module_path))
+        _configure(self._lib)
+        if self._lib.dino_abi_version() != RUNTIME_ABI_VERSION:
+            raise RuntimeError(f"module.so reports ABI {self._lib.dino_abi_version()}, expected {RUNTIME_ABI_VERSION}")
+        self._handle = ctypes.c_void_p()
+        self._sessions: "weakref.WeakSet[Session]" = weakref.WeakSet()
+        self._check(self._lib.dino_module_load_deferred(str(self.path).encode(), ctypes.byref(self._handle)))
+        try:
+            self.metadata = json.loads(self._lib.dino_module_get_metadata_json(self._handle).decode())
+            policy = self.metadata.get("constant_load_policy", "eager")
+            if load_constants if load_constants is not None else policy == "eager":
+                self.load_constants()
+        except Exception:
+            self.close()
+            raise
+
+    # -- errors
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise RuntimeError((self._lib.dino_get_last_error() or b"unknown error").decode("utf-8", "replace"))
+
+    # -- constants
+    def load_constants(self, path: str | Path | None = None) -> None:
+        """Dense constants and eagerly-resident encoded ones; `manual_runtime_load` GGUF constants are skipped."""
+        self._check(self._lib.dino_module_load_constants(self._handle, str(path or self.path / "constants.bin").encode()))
+
+    def unload_constants(self) -> None:
+        self._check(self._lib.dino_module_unload_constants(self._handle))
+
+    def encoded_constant_load_plan(self) -> list[dict[str, Any]]:
+        plan = []
+        for c in self.metadata["constants"]:
+            st = c.get("storage") or {}
+            if st.get("kind") != "gguf":
+                continue
+            plan.append({"name": c["name"], "qtype": st["qtype"], "encoded_nbytes": c["nbytes"], "offset": c["offset"],
+                         "residency": st["residency"], "materialization": st["materialization"],
+                         "action": "upload_encoded" if st["residency"] == "manual_runtime_load" else "loaded_with_constants",
+                         "status": "runtime_supported"})
+        return plan
+
+    def load_encoded_constants(self, sources: Mapping[str, np.ndarray] | None = None) -> list[dict[str, Any]]:
+        """Uploads the raw GGUF bytes of every `manual_runtime_load` constant (from `sources`, else from the artifact's
+        constants.bin): device malloc, H2D, `dino_module_set_encoded_constant` (device-to-device copy into the module's own
+        buffer), free the staging buffer."""
+        done = []
+        for entry in self.encoded_constant_load_plan():
+            if entry["action"] != "upload_encoded":
+                continue
+            if sources is not None and entry["name"] in sources:
+                raw = np.ascontiguousarray(sources[entry["name"]], dtype=np.uint8).reshape(-1)
+            else:
+                raw = np.fromfile(self.path / "constants.bin", dtype=np.uint8, count=entry["encoded_nbytes"], offset=entry["offset"])
+            self.set_encoded_constant_host_bytes(entry["name"], raw)
+            done.append(entry)
+        return done
+
+    def set_encoded_constant_host_bytes(self, name: str, raw: np.ndarray) -> None:
+        staging = ctypes.c_void_p()
+        self._check(self._lib.dino_device_malloc(ctypes.byref(staging), raw.nbytes))
+        try:
+            self._check(self._lib.dino_copy_host_to_device(staging, raw.ctypes.data, raw.nbytes))
+            self._check(self._lib.dino_module_set_encoded_constant(self._handle, name.encode(), staging, raw.nbytes))
+        finally:
+            self._lib.dino_device_free(staging)
+
+    def set_encoded_constant_device(self, name: str, device_ptr: int, nbytes: int) -> None:
+        self._check(self._lib.dino_module_set_encoded_constant(self._handle, name.encode(), ctypes.c_void_p(device_ptr), nbytes))
+
+    def set_constant_torch(self, name: str, tensor) -> None:
+        keep: list = []
+        dtype = str(tensor.dtype).replace("torch.", "")
+        t = _tensor_struct(tensor.data_ptr(), tuple(tensor.shape), dtype, keep)
+        self._check(self._lib.dino_module_set_constant(self._handle, name.encode(), ctypes.byref(t)))
+
+    # -- sessions
+    def create_session(self) -> "Session":
+        s = Session(self)
+        self._sessions.add(s)
+        return s
+
+    def close(self) -> None:
+        for s in list(self._sessions):
+            s.close()
+        if getattr(self, "_handle", None):
+            self._lib.dino_module_free(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Session:
+    def __init__(self, module: RuntimeModule):
+        self.module = module
+        self._lib = module._lib
+        self._handle = ctypes.c_void_p()
+        module._check(self._lib.dino_session_create(module._handle, ctypes.byref(self._handle)))
+        self._pinned: dict[str, Any] = {}
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.dino_session_destroy(self._handle)
+            self._handle = None
+
+    def set_stream(self, stream_ptr: int | None) -> None:
+        self.module._check(self._lib.dino_session_set_stream(self._handle, ctypes.c_void_p(stream_ptr or 0)))
+
+    # -- shapes
+    def _output_shapes(self, in_shapes: Mapping[str, tuple[int, ...]]) -> dict[str, tuple[int, ...]]:
+        """Output shapes from the graph (each gemm output is a.shape[:-1] + [N])."""
+        graph = json.loads((self.module.path / "graph.dinoir.json").read_text()) if not hasattr(self, "_graph") else self._graph
+        self._graph = graph
+        shapes = dict(in_shapes)
+        consts = {c["name"]: c for c in graph["constants"]}
+        for node in graph["nodes"]:
+            a = shapes[node["inputs"][0]]
+            shapes[node["outputs"][0]] = tuple(a[:-1]) + (consts[node["inputs"][1]]["shape"][0],)
+        return {o["name"]: shapes[o["name"]] for o in graph["outputs"]}
+
+    def _pack(self, inputs: Mapping[str, tuple[int, tuple[int, ...], str]], outputs: Mapping[str, tuple[int, tuple[int, ...], str]]):
+        keep: list = []
+        meta = self.module.metadata
+        ins = (_DinoTensor * len(meta["inputs"]))(*[_tensor_struct(*inputs[i["name"]], keep) for i in meta["inputs"]])
+        outs = (_DinoTensor * len(meta["outputs"]))(*[_tensor_struct(*outputs[o["name"]], keep) for o in meta["outputs"]])
+        return ins, outs, keep
+
+    # -- run
+    def run_device_pointers(self, inputs, outputs) -> None:
+        """inputs / outputs: name -> (device pointer, shape, dtype name).  Zero-copy."""
+        ins, outs, keep = self._pack(inputs, outputs)
+        self.module._check(self._lib.dino_session_run(self._handle, ins, len(ins), outs, len(outs)))
+
+    def run_torch(self, inputs: Mapping[str, Any], outputs: Mapping[str, Any] | None = None) -> dict[str, Any]:
+        import torch
+        meta = self.module.metadata
+        out_shapes = self._output_shapes({k: tuple(v.shape) for k, v in inputs.items()})
+        if outputs is None:
+            dev = next(iter(inputs.values())).device
+            outputs = {o["name"]: torch.empty(out_shapes[o["name"]], dtype=getattr(torch, o["dtype"]), device=dev) for o in meta["outputs"]}
+        dt = lambda t: str(t.dtype).replace("torch.", "")
+        self.run_device_pointers({k: (v.data_ptr(), tuple(v.shape), dt(v)) for k, v in inputs.items()},
+                                 {k: (v.data_ptr(), tuple(v.shape), dt(v)) for k, v in outputs.items()})
+        return dict(outputs)
+
+    def run_numpy(self, inputs: Mapping[str, np.ndarray]) -> dict[str, np.ndarray]:
+        """Host arrays in, host arrays out: pinned staging, H2D, run, D2H.  bfloat16 travels as uint16 bit patterns or as
+        float32 arrays (rounded to nearest even), and comes back as float32."""
+        import torch
+        meta = self.module.metadata
+        dev_in = {}
+        for spec in meta["inputs"]:
+            arr = np.asarray(inputs[spec["name"]])
+            tdt = getattr(torch, spec["dtype"])
+            key = (spec["name"], arr.shape)
+            if spec["dtype"] == "bfloat16" and arr.dtype == np.uint16:
+                host = torch.from_numpy(arr.view(np.int16)).view(torch.bfloat16)
+            else:
+                host = torch.from_numpy(np.ascontiguousarray(arr)).to(tdt)
+            pin = self._pinned.get(key)
+            if pin is None or pin.dtype != tdt:
+                pin = torch.empty(arr.shape, dtype=tdt).pin_memory()
+                self._pinned[key] = pin
+            pin.copy_(host)
+            dev_in[spec["name"]] = pin.to("cuda", non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        outs = self.run_torch(dev_in)
+        return {k: (v.float() if v.dtype == torch.bfloat16 else v).cpu().numpy() for k, v in outs.items()}
+
+    # -- benchmark
+    def benchmark_torch(self, inputs: Mapping[str, Any], warmup: int = 5, iterations: int = 20) -> dict[str, Any]:
+        """Native benchmark loop (CUDA-graph replay + events per iteration); summary like src/dinoml/runtime.py:1854-1866."""
+        import torch
+        meta = self.module.metadata
+        out_shapes = self._output_shapes({k: tuple(v.shape) for k, v in inputs.items()})
+        dev = next(iter(inputs.values())).device
+        outputs = {o["name"]: torch.empty(out_shapes[o["name"]], dtype=getattr(torch, o["dtype"]), device=dev) for o in meta["outputs"]}
+        dt = lambda t: str(t.dtype).replace("torch.", "")
+        ins, outs, keep = self._pack({k: (v.data_ptr(), tuple(v.shape), dt(v)) for k, v in inputs.items()},
+                                     {k: (v.data_ptr(), tuple(v.shape), dt(v)) for k, v in outputs.items()})
+        ms = (ctypes.c_double * iterations)()
+        self.module._check(self._lib.dino_session_benchmark(self._handle, ins, len(ins), outs, len(outs), warmup, iterations, ms, iterations))
+        return summarize_ms(list(ms), native_entrypoint="dino_session_benchmark", timing_source="cuda_events", graph_replay=True,
+                            warmup=warmup)
+
+
+def summarize_ms(values: list[float], **metadata) -> dict[str, Any]:
+    out = {"iterations": len(values), "mean_ms": statistics.fmean(values), "median_ms": statistics.median(values),
+           "min_ms": min(values), "max_ms": max(values), "stddev_ms": statistics.pstdev(values) if len(values) > 1 else 0.0,
+           "elapsed_ms": values}
+    out.update(metadata)
+    return out

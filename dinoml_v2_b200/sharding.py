@@ -1,0 +1,74 @@
+"""Tensor-parallel sharding of GGUF-encoded linears across the GPUs of one node (one process per GPU, NCCL).
+
+The reference has no distributed code at all; this covers the Llama-70B-shaped FFN configuration:
+* N-split (gate / up): packed rows are independent and contiguous, so rank r keeps rows [r*N/G, (r+1)*N/G) - a plain
+  byte slice - computes y_r[M, N/G] and the ranks all-gather;
+* K-split (down): shards are cut at 256-weight super-block granularity; rank r needs blocks [r*nb/G, (r+1)*nb/G) of
+  EVERY row, a one-time strided repack at load into a dense [N, nb/G] block matrix, computes a partial [M, N] and the
+  ranks all-reduce.  The N-shard of gate/up on rank r is exactly the K-slice rank r needs for down.
+Collectives go through torch.distributed (NCCL over NVLink) on the compute stream; nothing here uses peer pointers."""
+from __future__ import annotations
+
+import numpy as np
+
+from .gguf_blocks import qtype_of, row_bytes
+
+
+def shard_rows(blocks: np.ndarray, rank: int, world: int) -> np.ndarray:
+    """N-split: contiguous slice of rows.  blocks: uint8 [N, row_bytes]."""
+    n = blocks.shape[0]
+    if n % world:
+        raise ValueError(f"N={n} is not divisible by world size {world}")
+    per = n // world
+    return np.ascontiguousarray(blocks[rank * per:(rank + 1) * per])
+
+
+def shard_k(blocks: np.ndarray, qtype, k: int, rank: int, world: int) -> tuple[np.ndarray, int]:
+    """K-split at block granularity.  Returns (uint8 [N, row_bytes(k/world)], k/world)."""
+    q = qtype_of(qtype)
+    nb = k // q.block_size
+    if blocks.shape[1] != row_bytes(q, k):
+        raise ValueError("blocks do not match (qtype, k)")
+    if nb % world:
+        raise ValueError(f"K={k} has {nb} {q.name} blocks per row, not divisible by world size {world}")
+    per = nb // world
+    if (per * q.block_bytes) % 16:
+        raise ValueError(f"a K-shard row of {per} {q.name} blocks is {per * q.block_bytes} B, not 16-byte aligned; "
+                         "choose a world size that keeps shard rows 16-byte multiples")
+    n = blocks.shape[0]
+    shard = blocks.reshape(n, nb, q.block_bytes)[:, rank * per:(rank + 1) * per, :]
+    return np.ascontiguousarray(shard).reshape(n, per * q.block_bytes), per * q.block_size
+
+
+class ShardedFFN:
+    """gate / up N-split + all-gather, down K-split + all-reduce, for one rank.  Device tensors are torch tensors."""
+
+    def __init__(self, gate_shard, up_shard, down_shard, qtype, hidden: int, ffn: int, group=None):
+        import torch.distributed as dist
+        self.gate, self.up, self.down = gate_shard, up_shard, down_shard
+        self.qtype, self.hidden, self.ffn = qtype, hidden, ffn
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+
+    def gate_up(self, x, out_gate, out_up, gathered_gate, gathered_up):
+        """x [M, hidden] replicated.  gathered_* are [world, M, ffn/world] (rank-major, no transpose kernel)."""
+        import torch.distributed as dist
+
+        from . import kernels
+        kernels.gemm_rcr(x, self.gate, self.qtype, out=out_gate)
+        kernels.gemm_rcr(x, self.up, self.qtype, out=out_up)
+        if self.world > 1:
+            dist.all_gather_into_tensor(gathered_gate.view(-1, out_gate.shape[-1]), out_gate, group=self.group)
+            dist.all_gather_into_tensor(gathered_up.view(-1, out_up.shape[-1]), out_up, group=self.group)
+        return gathered_gate, gathered_up
+
+    def down_proj(self, h_slice, out):
+        """h_slice [M, ffn/world] = this rank's K-slice of the down-projection input; out [M, hidden] is summed in place."""
+        import torch.distributed as dist
+
+        from . import kernels
+        kernels.gemm_rcr(h_slice, self.down, self.qtype, out=out)
+        if self.world > 1:
+            dist.all_reduce(out, group=self.group)
+        return out
