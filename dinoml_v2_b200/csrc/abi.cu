@@ -20,6 +20,9 @@ bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k);
 bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k);
 size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k);
 int umma_device_status();
+int gemm_rcr_umma_static(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                         cudaStream_t s);
+size_t gemm_umma_static_scratch_bytes();
 
 // Thread-local last error, same contract as the reference runtime (runtime/src/runtime_common.cpp:5-20).
 static thread_local std::string g_last_error;
@@ -109,6 +112,21 @@ size_t dinoml_b200_gguf_gemm_rcr_workspace(int qtype, int dtype, int m, int n, i
   if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, n, k);
   return variant == DINOML_B200_GGUF_VARIANT_UMMA ? gemm_umma_workspace(qtype, dtype, m, n, k) : 0;
 }
+
+int dinoml_b200_gguf_gemm_rcr_prealloc(const void* a, const void* b_quant, const void* bias, void* c, int qtype, int dtype,
+                                       int m, int n, int k, void* stream) {
+  const int rc = gemm_rcr_umma_static(a, b_quant, bias, c, qtype, dtype, m, n, k, static_cast<cudaStream_t>(stream));
+  if (rc == RC_RANGE) {
+    const size_t need = gemm_umma_workspace(qtype, dtype, m, n, k);
+    if (need > gemm_umma_static_scratch_bytes())
+      return set_error_message(rc, "dinoml_b200_gguf_gemm_rcr_prealloc: this problem needs " + std::to_string(need) +
+                                       " bytes of split-K scratch, the built-in scratch holds " +
+                                       std::to_string(gemm_umma_static_scratch_bytes()) + "; use dinoml_b200_gguf_gemm_rcr");
+  }
+  return set_error(rc, "dinoml_b200_gguf_gemm_rcr_prealloc");
+}
+
+size_t dinoml_b200_gguf_prealloc_scratch_bytes(void) { return gemm_umma_static_scratch_bytes(); }
 
 int dinoml_b200_gguf_device_status(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;

@@ -540,13 +540,14 @@ static Plan make_plan(int m, int n, int k) {
   return pl;
 }
 
+// Where a launch finds its split-K workspace and status word.
+struct Scratch { float* workspace; int* status; };
+
 template <int QT, typename T, int BM>
-static int launch(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const Plan& pl, cudaStream_t s) {
+static int launch(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const Plan& pl, Scratch sc,
+                  cudaStream_t s) {
   EncodeTiledFn enc = encode_tiled();
   if (enc == nullptr) return RC_LAUNCH;
-  const size_t ws = pl.splits > 1 ? size_t(pl.splits) * m * n * sizeof(float) : 0;
-  DeviceState* st = device_state(ws);
-  if (st == nullptr) return RC_LAUNCH;
   CUtensorMap map;
   const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(m)};
   const cuuint64_t strides[1] = {cuuint64_t(k) * 2};
@@ -566,8 +567,8 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
   p.w = static_cast<const uint8_t*>(b);
   p.bias = bias;
   p.out = c;
-  p.partial = pl.splits > 1 ? st->workspace : nullptr;
-  p.status = st->status;
+  p.partial = pl.splits > 1 ? sc.workspace : nullptr;
+  p.status = sc.status;
   p.m = m; p.n = n; p.k = k;
   p.sb_per_split = pl.sb_per_split;
   const dim3 grid((m + BM - 1) / BM, (n + kRowsW - 1) / kRowsW, pl.splits);
@@ -577,20 +578,63 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
     const int64_t mn = int64_t(m) * n;
     const int threads = 256;
     const int64_t blocks = (mn / 4 + threads - 1) / threads;
-    splitk_reduce_kernel<T><<<unsigned(blocks), threads, 0, s>>>(st->workspace, static_cast<const T*>(bias), static_cast<T*>(c), mn, n,
+    splitk_reduce_kernel<T><<<unsigned(blocks), threads, 0, s>>>(sc.workspace, static_cast<const T*>(bias), static_cast<T*>(c), mn, n,
                                                                  pl.splits);
     if (cudaGetLastError() != cudaSuccess) return RC_LAUNCH;
   }
   return RC_OK;
 }
 
+// ---- allocation-free scratch -------------------------------------------------------------------
+// Split-K workspace and status word that live in the library's own device image instead of cudaMalloc'ed
+// memory.  Every GPU that loads the library carries these 16 MiB until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+static __device__ int g_static_status;
+
+constexpr int kMaxDevices = 64;
+struct StaticScratch { float* workspace = nullptr; int* status = nullptr; bool ready = false; };
+static StaticScratch g_static[kMaxDevices];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address; the address the kernels
+// need is looked up once per device, with that device current.
+static int static_scratch(Scratch* out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return RC_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  StaticScratch& st = g_static[dev];
+  if (!st.ready) {
+    void* ws = nullptr;
+    void* status = nullptr;
+    if (cudaGetSymbolAddress(&ws, g_static_scratch) != cudaSuccess) return RC_LAUNCH;
+    if (cudaGetSymbolAddress(&status, g_static_status) != cudaSuccess) return RC_LAUNCH;
+    st.workspace = static_cast<float*>(ws);
+    st.status = static_cast<int*>(status);
+    st.ready = true;
+  }
+  out->workspace = st.workspace;
+  out->status = st.status;
+  return RC_OK;
+}
+
 template <int QT, typename T>
-static int launch_bm(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+static int launch_bm(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, bool use_static, cudaStream_t s) {
   const Plan pl = make_plan(m, n, k);
+  const size_t ws = pl.splits > 1 ? size_t(pl.splits) * m * n * sizeof(float) : 0;
+  Scratch sc{nullptr, nullptr};
+  if (use_static) {
+    if (ws > kStaticScratchBytes) return RC_RANGE;
+    if (int rc = static_scratch(&sc)) return rc;
+  } else {
+    DeviceState* st = device_state(ws);
+    if (st == nullptr) return RC_LAUNCH;
+    sc.workspace = st->workspace;
+    sc.status = st->status;
+  }
   switch (pl.bm) {
-    case 64: return launch<QT, T, 64>(a, b, bias, c, m, n, k, pl, s);
-    case 128: return launch<QT, T, 128>(a, b, bias, c, m, n, k, pl, s);
-    default: return launch<QT, T, 256>(a, b, bias, c, m, n, k, pl, s);
+    case 64: return launch<QT, T, 64>(a, b, bias, c, m, n, k, pl, sc, s);
+    case 128: return launch<QT, T, 128>(a, b, bias, c, m, n, k, pl, sc, s);
+    default: return launch<QT, T, 256>(a, b, bias, c, m, n, k, pl, sc, s);
   }
 }
 
@@ -607,19 +651,32 @@ size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k) {
   return pl.splits > 1 ? size_t(pl.splits) * m * n * sizeof(float) : 0;
 }
 
-int gemm_rcr_umma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
-                  cudaStream_t s) {
+static int gemm_rcr_umma_impl(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                              bool use_static, cudaStream_t s) {
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
   if (reinterpret_cast<uintptr_t>(b) & 15) return RC_ALIGN;        // 16-byte cp.async sources
   if ((int64_t(k) * 2) & 15) return RC_ALIGN;                       // TMA row pitch
   if (dtype == DINO_BF16)
-    return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, s)
-                               : umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, s);
-  return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, s)
-                             : umma::launch_bm<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, s);
+    return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, s)
+                               : umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, s);
+  return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, use_static, s)
+                             : umma::launch_bm<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, use_static, s);
 }
+
+int gemm_rcr_umma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                  cudaStream_t s) {
+  return gemm_rcr_umma_impl(a, b, bias, c, qtype, dtype, m, n, k, false, s);
+}
+
+// Same kernel, scratch in the library's static device array: no cudaMalloc / cudaFree anywhere on this path.
+int gemm_rcr_umma_static(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                         cudaStream_t s) {
+  if (m < 17) return RC_RANGE;   // small M belongs to the GEMV kernels, which need no scratch
+  return gemm_rcr_umma_impl(a, b, bias, c, qtype, dtype, m, n, k, true, s);
+}
+size_t gemm_umma_static_scratch_bytes() { return umma::kStaticScratchBytes; }
 
 // Reads (and clears) the device status word the bounded waits write; 0 = no wait ever gave up.
 int umma_device_status() {
@@ -627,9 +684,14 @@ int umma_device_status() {
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
   std::lock_guard<std::mutex> lock(umma::g_mutex);
   auto it = umma::g_state.find(dev);
-  if (it == umma::g_state.end() || it->second.status == nullptr) return 0;
-  if (cudaMemcpy(&value, it->second.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  if (value != 0) cudaMemset(it->second.status, 0, sizeof(int));
+  if (it != umma::g_state.end() && it->second.status != nullptr) {
+    if (cudaMemcpy(&value, it->second.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (value != 0) cudaMemset(it->second.status, 0, sizeof(int));
+  }
+  if (value == 0 && dev >= 0 && dev < umma::kMaxDevices && umma::g_static[dev].ready) {   // the static-scratch path's word
+    if (cudaMemcpy(&value, umma::g_static[dev].status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (value != 0) cudaMemset(umma::g_static[dev].status, 0, sizeof(int));
+  }
   return value;
 }
 
