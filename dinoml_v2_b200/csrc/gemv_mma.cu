@@ -13,8 +13,11 @@
 //
 // Data movement: a CTA of 4 warps owns 16 consecutive weight rows (one MMA M-tile).  Their packed
 // bytes are staged HBM -> shared memory with 16-byte cp.async copies in K-stages of 4 super-blocks
-// (16 rows x 576 B), three stages in flight per CTA, so every SM keeps >100 KB of reads outstanding
-// without holding them in registers.  Within a stage warp w unpacks super-block w.  Lane
+// (16 rows x 576 B), four stages in flight per CTA (the whole row set for K = 4096), so every SM keeps
+// >150 KB of reads outstanding without holding them in registers.  The kernel is launched with programmatic
+// stream serialization: it prefetches its (constant) weights first and only then waits for the preceding
+// kernel in the stream (`griddepcontrol.wait`) before touching activations or outputs, so consecutive
+// quantized linears overlap one launch's ramp-up with the previous one's tail.  Within a stage warp w unpacks super-block w.  Lane
 // (g = lane/4, t = lane%4) feeds rows g and g+8: per 64-weight group it reads the 8 quant bytes
 // [8t, 8t+8) of each row, which puts all 16 K-slots of every MMA inside one sub-block.  The row pitch
 // in shared memory (608 B) makes those 8-byte reads bank-conflict free.  The 16 header bytes of each
@@ -80,10 +83,9 @@ constexpr int kGemvWarps = 4;
 constexpr int kGemvThreads = kGemvWarps * 32;
 constexpr int kGemvRows = 16;
 constexpr int kStageSb = 4;                              // super-blocks per stage (one per warp)
-constexpr int kStages = 3;                               // stages in flight
 constexpr int kRowChunks = kStageSb * 9;                 // 16-byte chunks per row per stage (4 x 144 B)
 constexpr int kRowPitch = kStageSb * 144 + 32;           // 608 B: 8-byte reads of 8 rows x 4 lanes hit 32 banks
-constexpr int kStageBytes = kGemvRows * kRowPitch;       // 9728 B
+constexpr int kStageBytes = kGemvRows * kRowPitch;       // 9728 B per stage slot
 
 // Byte -> float without I2F: 0x4B0000bb is 2^23 + bb.
 __device__ __forceinline__ float byte_to_float(uint32_t word, int i) {
@@ -97,39 +99,49 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-// MXC: activation rows covered (power of two >= m).  Dynamic shared memory: X[MXC][k/32] floats.
-template <typename T, int MXC>
-__global__ void __launch_bounds__(kGemvThreads)
+// MXC: activation rows covered (power of two >= m).  NW: warps per CTA (4 or 8); each group of 4 warps walks its own
+// sequence of K-stages (group p takes stages p, p + NW/4, ...), so an 8-warp CTA unpacks two stages at a time.
+// NSTAGE: shared-memory stage slots.  Dynamic shared memory: weight stages, then X[MXC][k/32] floats.
+template <typename T, int MXC, int NW, int NSTAGE>
+__global__ void __launch_bounds__(NW * 32)
 gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias,
                     T* __restrict__ y, int m, int n, int k) {
   using MT = MmaType<T>;
   constexpr int NT = MXC > 8 ? 2 : 1;        // n8 tiles of activation rows
   constexpr int MC = MXC == 1 ? 1 : 2;       // accumulator columns a lane keeps per tile
   constexpr int kCols = NT * 8;
-  extern __shared__ __align__(16) float sX[];                             // [MXC][k/32]
-  __shared__ __align__(16) uint8_t sW[kStages * kStageBytes];             // staged packed weights
-  __shared__ __align__(16) float sS[kGemvWarps][kGemvRows][8];            // ds per row, sub-block
-  __shared__ float sRed[kGemvWarps][kGemvRows][kCols];                    // main partial sums
-  __shared__ float sXt[kGemvWarps][kGemvRows][2][MXC];                    // min / MAGIC partial sums
+  constexpr int SPI = NW / 4;                // stages per iteration (one per warp group)
+  constexpr int D = NSTAGE / SPI;            // stage slots per warp group
+  static_assert(NSTAGE % SPI == 0 && D >= 2, "each warp group needs at least two stage slots");
+  extern __shared__ __align__(16) uint8_t smem_dyn[];
+  uint8_t* sW = smem_dyn;                                                 // staged packed weights, NSTAGE x kStageBytes
+  float* sX = reinterpret_cast<float*>(smem_dyn + NSTAGE * kStageBytes);  // [MXC][k/32]
+  __shared__ __align__(16) float sS[NW][kGemvRows][8];                    // ds per row, sub-block
+  // the cross-warp reduction buffers reuse the stage slots once every warp is done with them
+  float (*sRed)[kGemvRows][kCols] = reinterpret_cast<float (*)[kGemvRows][kCols]>(smem_dyn);
+  float (*sXt)[kGemvRows][2][MXC] = reinterpret_cast<float (*)[kGemvRows][2][MXC]>(smem_dyn + NW * kGemvRows * kCols * sizeof(float));
+  static_assert(NW * kGemvRows * (kCols + 2 * MXC) * sizeof(float) <= size_t(NSTAGE) * kStageBytes, "reduction buffers must fit");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = warp >> 2, wq = warp & 3, gtid = tid & 127;   // warp group, warp within it, thread within it
   const int g = lane >> 2, t = lane & 3;
   const int r_base = blockIdx.x * kGemvRows;
   const int nsb = k >> 8, nsub = k >> 5;
   const int nstages = (nsb + kStageSb - 1) / kStageSb;
+  const int niter = (nstages + SPI - 1) / SPI;
   const int64_t row_bytes = int64_t(nsb) * 144;
   const uint32_t sW_u32 = uint32_t(__cvta_generic_to_shared(sW));
 
-  // Copy assignment: 8 threads per weight row, thread (tid%8) moves 16-byte chunks (tid%8) + 8j of the
-  // row's 36 chunks per stage.
-  const int cp_row = tid >> 3, cp_c0 = tid & 7;
+  // Copy assignment inside a warp group: 8 threads per weight row, thread (gtid%8) moves 16-byte chunks
+  // (gtid%8) + 8j of the row's 36 chunks per stage.
+  const int cp_row = gtid >> 3, cp_c0 = gtid & 7;
   const uint8_t* cp_src = w + int64_t(min(r_base + cp_row, n - 1)) * row_bytes + cp_c0 * 16;
   const uint32_t cp_dst = sW_u32 + cp_row * kRowPitch + cp_c0 * 16;
   auto issue_stage = [&](int s) {
     if (s < nstages) {
       const int valid_chunks = min(kStageSb, nsb - s * kStageSb) * 9;
       const uint8_t* src = cp_src + int64_t(s) * (kStageSb * 144);
-      const uint32_t dst = cp_dst + (s % kStages) * kStageBytes;
+      const uint32_t dst = cp_dst + (s % NSTAGE) * kStageBytes;
 #pragma unroll
       for (int j = 0; j < 5; ++j)
         if (cp_c0 + 8 * j < valid_chunks) cp_async16(dst + 128 * j, src + 128 * j);
@@ -137,10 +149,14 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
     cp_async_commit();
   };
 #pragma unroll
-  for (int s = 0; s < kStages; ++s) issue_stage(s);
+  for (int d = 0; d < D; ++d) issue_stage(d * SPI + grp);
+  // Weights are constants: they were safe to prefetch.  Everything below reads activations / writes outputs that a
+  // preceding kernel in the stream may still be producing / consuming.
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
   // X[c][j] = sum of activations of row c over sub-block j (rows >= m are zero).
-  for (int idx = tid; idx < nsub * MXC; idx += kGemvThreads) {
+  for (int idx = tid; idx < nsub * MXC; idx += NW * 32) {
     const int c = idx / nsub, j = idx - c * nsub;
     float s = 0.f;
     if (c < m) {
@@ -165,13 +181,14 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) xrow[nt] = x + int64_t(min(nt * 8 + g, m - 1)) * k + 8 * t;
 
-  for (int s = 0; s < nstages; ++s) {
-    cp_async_wait<kStages - 2>();
-    __syncthreads();                       // stage s landed for every thread; stage s-1 fully consumed
-    if (s > 0) issue_stage(s - 1 + kStages); else cp_async_commit();
-    const int sb = s * kStageSb + warp;
-    if (sb < nsb) {
-      const uint8_t* st = sW + (s % kStages) * kStageBytes + warp * 144;
+  for (int it = 0; it < niter; ++it) {
+    cp_async_wait<D - 2>();
+    __syncthreads();                       // this iteration's stages landed; the previous ones are fully consumed
+    if (it > 0) issue_stage((it - 1 + D) * SPI + grp); else cp_async_commit();
+    const int s = it * SPI + grp;
+    const int sb = s * kStageSb + wq;
+    if (s < nstages && sb < nsb) {
+      const uint8_t* st = sW + (s % NSTAGE) * kStageBytes + wq * 144;
       {  // lane pair (srow, shalf): 4 sub-block scales -> ds to shared memory, min/MAGIC term folded against X
         const uint4 hdr = *reinterpret_cast<const uint4*>(st + srow * kRowPitch);
         const float d = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
@@ -237,10 +254,11 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
           }
         }
       }
-      __syncwarp();                        // sS is rewritten in the next stage
+      __syncwarp();                        // sS is rewritten in the next iteration
     }
   }
   cp_async_wait<0>();
+  __syncthreads();                         // every warp is done with the stage slots: reuse them for the reduction
 
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
@@ -252,13 +270,13 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
 #pragma unroll
   for (int c = 0; c < MXC; ++c) sXt[warp][srow][shalf][c] = xt[c];
   __syncthreads();
-  for (int idx = tid; idx < kGemvRows * MXC; idx += kGemvThreads) {
+  for (int idx = tid; idx < kGemvRows * MXC; idx += NW * 32) {
     const int r = idx & (kGemvRows - 1), c = idx >> 4;
     const int row = r_base + r;
     if (row < n && c < m) {
       float v = 0.f, xs = 0.f;
 #pragma unroll
-      for (int wv = 0; wv < kGemvWarps; ++wv) {
+      for (int wv = 0; wv < NW; ++wv) {
         v += sRed[wv][r][c];
         xs += sXt[wv][r][0][c] + sXt[wv][r][1][c];
       }
@@ -269,19 +287,39 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   }
 }
 
+template <typename T, int MXC, int NW, int NSTAGE>
+static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+  const int tiles = (n + kGemvRows - 1) / kGemvRows;
+  const size_t smem = size_t(NSTAGE) * kStageBytes + size_t(k / 32) * MXC * sizeof(float);
+  if (smem > 200 * 1024) return RC_RANGE;
+  auto kern = gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE>;
+  static size_t opted_in = 0;        // dynamic shared memory beyond 48 KB in total needs the opt-in, once per size
+  if (smem > opted_in) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
+    opted_in = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles);
+  cfg.blockDim = dim3(NW * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
+                                             static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
+  return err == cudaSuccess ? RC_OK : RC_LAUNCH;
+}
 
+// M <= 2: 8 warps and 4 stage slots (5 CTAs per SM still fit, one wave for N = 11008); larger M needs more shared
+// memory for X and the reduction, so it keeps 4 warps and 3 slots to stay at 5 CTAs per SM.
 template <typename T, int MXC>
 static int launch_q4k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
-  const int tiles = (n + kGemvRows - 1) / kGemvRows;
-  const size_t smem = size_t(k / 32) * MXC * sizeof(float);
-  auto kern = gemv_q4k_mma_kernel<T, MXC>;
-  if (smem > 4 * 1024) {   // static + dynamic shared memory beyond 48 KB needs the opt-in
-    if (smem > 160 * 1024) return RC_RANGE;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
-  }
-  kern<<<tiles, kGemvThreads, smem, s>>>(static_cast<const T*>(a), static_cast<const uint8_t*>(b),
-                                         static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
-  return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
+  if (MXC <= 2 && k >= 2048) return launch_q4k_cfg<T, MXC, 8, 4>(a, b, bias, c, m, n, k, s);
+  if (MXC <= 2) return launch_q4k_cfg<T, MXC, 4, 4>(a, b, bias, c, m, n, k, s);
+  return launch_q4k_cfg<T, MXC, 4, 3>(a, b, bias, c, m, n, k, s);
 }
 
 template <typename T>

@@ -185,10 +185,12 @@ __device__ __forceinline__ void fetch16(const uint8_t* aligned, uint32_t* out) {
   for (int i = 0; i < 4; ++i) out[i] = (S & 1) ? __funnelshift_r(w[j + i], w[j + i + 1], 16) : w[j + i];
 }
 template <int S>
-__device__ __forceinline__ void q6k_fetch(const uint8_t* rowbase, int hb, int lhalf, uint32_t* qw) {
+__device__ __forceinline__ void q6k_fetch(const uint8_t* rowbase, int hb, int lhalf, uint32_t* qw, uint32_t* tail) {
   fetch16<S>(rowbase + 64 * hb + 16 * lhalf, qw);             // ql, quads 0/2
   fetch16<S>(rowbase + 64 * hb + 32 + 16 * lhalf, qw + 4);    // ql, quads 1/3
   fetch16<S>(rowbase + 128 + 32 * hb + 16 * lhalf, qw + 8);   // qh
+  fetch16<S>(rowbase + 192, tail);                            // 16 int8 scales
+  fetch16<S>(rowbase + 208, tail + 4);                        // d (first 2 bytes)
 }
 
 __device__ __forceinline__ void sts_chunk(uint8_t* tile, int row, int chunk, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -316,21 +318,26 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
         sub_scale[0] = sub_scale[1] = sub_scale[2] = sub_scale[3] = 0.f;
       } else {
         const int hb = grp;
-        dscale = half_bits_to_float(uint16_t(*reinterpret_cast<const uint16_t*>(blk + 208)));
         const uint8_t* rowbase = raw + row * kPitch;
+        uint32_t tail[8];                     // bytes 192..223 of the block: 16 int8 scales, then d
         switch (int(blk - rowbase) >> 1) {
-          case 0: q6k_fetch<0>(rowbase, hb, lhalf, qw); break;
-          case 1: q6k_fetch<1>(rowbase, hb, lhalf, qw); break;
-          case 2: q6k_fetch<2>(rowbase, hb, lhalf, qw); break;
-          case 3: q6k_fetch<3>(rowbase, hb, lhalf, qw); break;
-          case 4: q6k_fetch<4>(rowbase, hb, lhalf, qw); break;
-          case 5: q6k_fetch<5>(rowbase, hb, lhalf, qw); break;
-          case 6: q6k_fetch<6>(rowbase, hb, lhalf, qw); break;
-          default: q6k_fetch<7>(rowbase, hb, lhalf, qw); break;
+          case 0: q6k_fetch<0>(rowbase, hb, lhalf, qw, tail); break;
+          case 1: q6k_fetch<1>(rowbase, hb, lhalf, qw, tail); break;
+          case 2: q6k_fetch<2>(rowbase, hb, lhalf, qw, tail); break;
+          case 3: q6k_fetch<3>(rowbase, hb, lhalf, qw, tail); break;
+          case 4: q6k_fetch<4>(rowbase, hb, lhalf, qw, tail); break;
+          case 5: q6k_fetch<5>(rowbase, hb, lhalf, qw, tail); break;
+          case 6: q6k_fetch<6>(rowbase, hb, lhalf, qw, tail); break;
+          default: q6k_fetch<7>(rowbase, hb, lhalf, qw, tail); break;
         }
+        dscale = half_bits_to_float(uint16_t(tail[4] & 0xffffu));
+        // scale byte of quad i: 8*hb + 2*i + lhalf -> word 2*hb + i/2, byte 2*(i%2) + lhalf
+        const uint32_t sw0 = hb ? tail[2] : tail[0], sw1 = hb ? tail[3] : tail[1];
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          sub_scale[i] = float(int(*reinterpret_cast<const int8_t*>(blk + 192 + 8 * hb + 2 * i + lhalf)));
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t wsel = i < 2 ? sw0 : sw1;
+          sub_scale[i] = float(int(int8_t(wsel >> (8 * (2 * (i & 1) + lhalf)))));
+        }
       }
       producer_bar_sync();                 // every producer holds its words: the raw buffer may be refilled
       issue_raw(sb + 1);
@@ -371,8 +378,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const uint32_t l4 = (qw[4 * qo + i] >> (4 * ls)) & 0x0f0f0f0fu;
-              const uint32_t h2 = ((qw[8 + i] >> (2 * quad)) & 0x03030303u) << 4;
-              bytes_to_pairs<T>(l4 | h2, off, s2, zero, o[2 * i], o[2 * i + 1]);
+              // the two high bits of quad q sit at bit 2q of the qh byte; they belong at bit 4
+              const uint32_t hs = quad == 0 ? qw[8 + i] << 4 : quad == 1 ? qw[8 + i] << 2 : quad == 2 ? qw[8 + i] : qw[8 + i] >> 2;
+              bytes_to_pairs<T>(l4 | (hs & 0x30303030u), off, s2, zero, o[2 * i], o[2 * i + 1]);
             }
             sts_chunk(tile, row, 4 * qo + 2 * lhalf, o[0], o[1], o[2], o[3]);
             sts_chunk(tile, row, 4 * qo + 2 * lhalf + 1, o[4], o[5], o[6], o[7]);
