@@ -5,14 +5,17 @@
 //
 // Swap-AB: the weight tile is the UMMA "A" operand (128 rows = UMMA M), the activation tile is "B"
 // (BM rows = UMMA N, 64..256), so D[n, m] lives in TMEM as 128 lanes x BM fp32 columns and one CTA
-// reuses every dequantized weight tile across BM activation rows.  Per CTA:
+// reuses every dequantized weight tile across BM activation rows.  The weight operand is fed from TENSOR MEMORY
+// (tcgen05.mma with A in TMEM): a 128 x 64 bf16 tile is 128 lanes x 32 columns, four such slots sit behind the
+// accumulator columns, so the dequantized weights never touch shared memory - at 128 x 256 x 16 per instruction
+// the MMA's shared-memory reads alone would otherwise take 3/4 of the SM's shared-memory bandwidth.  Per CTA:
 //   * 16 producer warps (512 threads): stage the packed bytes of 128 weight rows x one 256-weight
 //     super-block global -> shared with 16-byte cp.async, copy their own words to registers, start the
 //     next super-block's copy, then unpack.  Warps 0-7 produce the two 64-wide K stages of the first
 //     half of the super-block, warps 8-15 those of the second half; thread (row = 32*(warp%4)+lane,
 //     half = (warp%8)/4) unpacks 32 weights per stage with 32-bit logic + packed bf16x2/f16x2 math and
-//     stores them as the K-major, 128-byte-swizzled tile UMMA reads (4 x 16-byte stores, conflict
-//     free); `fence.proxy.async` + mbarrier arrive.
+//     writes them to its TMEM lane with two tcgen05.st.32x32b.x8 (16 columns of 2 x 16-bit);
+//     tcgen05.wait::st + mbarrier arrive.
 //   * warp 16, one lane: TMA (cp.async.bulk.tensor.2d, SWIZZLE_128B, no multicast) of the BM x 64
 //     activation tile per stage; rows past M are zero-filled by the tensor map.
 //   * warp 17, one lane: tcgen05.mma.cta_group::1.kind::f16 (128 x BM x 16, four per stage), then
@@ -48,7 +51,6 @@ constexpr int kBK = 64;                // K per pipeline stage (one 128-byte swi
 constexpr int kProducerThreads = 512;
 constexpr int kGroupThreads = 256;     // producers of one K stage
 constexpr int kThreads = kProducerThreads + 64;
-constexpr int kWTileBytes = kRowsW * kBK * 2;   // 16 KiB
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 enum : int { ST_OK = 0, ST_EMPTY_TIMEOUT = 1, ST_FULL_TIMEOUT = 2, ST_ACC_TIMEOUT = 3 };
@@ -92,7 +94,6 @@ __device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
     if (i > 64) __nanosleep(40);
   }
 }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -106,12 +107,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
       "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -131,6 +126,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+               "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+// A operand from tensor memory, B from shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 // 16-bit pair arithmetic used to turn quants into MMA operand values.
 template <typename T> struct Pair;
@@ -193,18 +201,19 @@ __device__ __forceinline__ void q6k_fetch(const uint8_t* rowbase, int hb, int lh
   fetch16<S>(rowbase + 208, tail + 4);                        // d (first 2 bytes)
 }
 
-__device__ __forceinline__ void sts_chunk(uint8_t* tile, int row, int chunk, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(a, b, c, d);
-}
-
 template <int QT> struct RawGeom;
 template <> struct RawGeom<QTYPE_Q4_K> { static constexpr int kPitch = 144, kChunks = 9; };
 template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240, kChunks = 14; };   // 15 chunks: 16-byte reads of 8 rows hit 32 banks
 
-template <int BM> constexpr int stage_bytes() { return kWTileBytes + BM * kBK * 2; }
-template <int BM> constexpr int num_stages() { return 4; }
+// Rings: 4 weight-tile slots in TMEM (32 columns each, right after the BM accumulator columns), NSX activation
+// tiles in shared memory (TMA), and two raw super-block buffers (packed bytes prefetched two super-blocks ahead).
+constexpr int kWSlots = 4;
+constexpr int kWSlotCols = kBK / 2;     // 64 16-bit values per lane = 32 columns
+template <int BM> constexpr int x_slots() { return BM >= 256 ? 5 : 6; }
+template <int BM> constexpr int x_tile_bytes() { return BM * kBK * 2; }
+template <int BM> constexpr int tmem_cols() { return BM + kWSlots * kWSlotCols > 256 ? 512 : 256; }
 template <int QT, int BM> constexpr size_t smem_bytes() {
-  return 1024 + size_t(num_stages<BM>()) * stage_bytes<BM>() + size_t(kRowsW) * RawGeom<QT>::kPitch + 256;
+  return 1024 + size_t(x_slots<BM>()) * x_tile_bytes<BM>() + 2 * size_t(kRowsW) * RawGeom<QT>::kPitch + 256;
 }
 
 struct Params {
@@ -222,24 +231,27 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
   using P = Pair<T>;
   using V = typename P::V;
-  constexpr int NS = num_stages<BM>();
-  constexpr int kStage = stage_bytes<BM>();
+  constexpr int NSW = kWSlots, NSX = x_slots<BM>();
+  constexpr int kXTile = x_tile_bytes<BM>();
+  constexpr uint32_t kTmemCols = tmem_cols<BM>();
   constexpr int kPitch = RawGeom<QT>::kPitch;
   constexpr int kBlockBytes = QTraits<QT>::kBytes;
   constexpr uint32_t kIdesc = (1u << 4) | (P::kFormat << 7) | (P::kFormat << 10) | (uint32_t(BM >> 3) << 17) | (uint32_t(kRowsW >> 4) << 24);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* raw = smem + NS * kStage;                                  // [128][kPitch]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + kRowsW * kPitch);
-  // bars[0..NS) wfull, [NS..2NS) xfull, [2NS..3NS) empty, [3NS] accumulator, [3NS+1] drain
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * NS + 2);
+  uint8_t* xtiles = smem;                                              // NSX x [BM][128 B]
+  uint8_t* raw = xtiles + NSX * kXTile;                                // 2 x [128][kPitch]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * kRowsW * kPitch);
+  // bars: wfull[NSW], wempty[NSW], xfull[NSX], xempty[NSX], accumulator, drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSW + 2 * NSX + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto wfull = [&](int s) { return bar0 + 8u * s; };
-  auto xfull = [&](int s) { return bar0 + 8u * (NS + s); };
-  auto empty = [&](int s) { return bar0 + 8u * (2 * NS + s); };
-  const uint32_t accbar = bar0 + 8u * (3 * NS), drainbar = bar0 + 8u * (3 * NS + 1);
+  auto wempty = [&](int s) { return bar0 + 8u * (NSW + s); };
+  auto xfull = [&](int s) { return bar0 + 8u * (2 * NSW + s); };
+  auto xempty = [&](int s) { return bar0 + 8u * (2 * NSW + NSX + s); };
+  const uint32_t accbar = bar0 + 8u * (2 * NSW + 2 * NSX), drainbar = accbar + 8u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * kRowsW;
@@ -248,10 +260,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
   const int nstage_total = (sb1 - sb0) * 4;
 
   if (tid == 0) {
-    for (int s = 0; s < NS; ++s) {
+    for (int s = 0; s < NSW; ++s) {
       mbar_init(wfull(s), kGroupThreads);
+      mbar_init(wempty(s), 1);
+    }
+    for (int s = 0; s < NSX; ++s) {
       mbar_init(xfull(s), 1);
-      mbar_init(empty(s), 1);
+      mbar_init(xempty(s), 1);
     }
     mbar_init(accbar, 1);
     mbar_init(drainbar, 1);
@@ -259,7 +274,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 17) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(uint32_t(BM)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
   tcgen05_fence_before();
@@ -282,7 +297,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
         const uint32_t shift = uint32_t(reinterpret_cast<uintptr_t>(src) & 15);
         const int nchunk = int(shift + kBlockBytes + 15) >> 4;
         const uint8_t* src16 = src - shift;
-        const uint32_t dst = smem_u32(raw + cp_row * kPitch);
+        const uint32_t dst = smem_u32(raw + ((sb - sb0) & 1) * (kRowsW * kPitch) + cp_row * kPitch);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int c = cp_q * 4 + j;
@@ -292,11 +307,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
       cp_async_commit();
     };
     issue_raw(sb0);
+    issue_raw(sb0 + 1);
     bool alive = true;
+    const uint32_t tmem_lane = tmem_base + (uint32_t(32 * (warp & 3)) << 16) + uint32_t(BM);   // this warp's lanes, first A column
     for (int sb = sb0; sb < sb1 && alive; ++sb) {
-      cp_async_wait<0>();
-      producer_bar_sync();                 // super-block sb landed and is visible to all producers
-      const uint8_t* blk = raw + row * kPitch + (reinterpret_cast<uintptr_t>(wrow + int64_t(sb) * kBlockBytes) & 15);
+      cp_async_wait<1>();                  // everything but the newest copy group: super-block sb has landed
+      producer_bar_sync();                 // ... and is visible to all producers
+      const uint8_t* rawbuf = raw + ((sb - sb0) & 1) * (kRowsW * kPitch);
+      const uint8_t* blk = rawbuf + row * kPitch + (reinterpret_cast<uintptr_t>(wrow + int64_t(sb) * kBlockBytes) & 15);
       // ---- copy this thread's packed words to registers
       uint32_t qw[12];
       float dscale, dmin = 0.f;
@@ -318,7 +336,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
         sub_scale[0] = sub_scale[1] = sub_scale[2] = sub_scale[3] = 0.f;
       } else {
         const int hb = grp;
-        const uint8_t* rowbase = raw + row * kPitch;
+        const uint8_t* rowbase = rawbuf + row * kPitch;
         uint32_t tail[8];                     // bytes 192..223 of the block: 16 int8 scales, then d
         switch (int(blk - rowbase) >> 1) {
           case 0: q6k_fetch<0>(rowbase, hb, lhalf, qw, tail); break;
@@ -339,15 +357,21 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
           sub_scale[i] = float(int(int8_t(wsel >> (8 * (2 * (i & 1) + lhalf)))));
         }
       }
-      producer_bar_sync();                 // every producer holds its words: the raw buffer may be refilled
-      issue_raw(sb + 1);
+      producer_bar_sync();                 // every producer holds its words: this raw buffer may be refilled
+      issue_raw(sb + 2);
 #pragma unroll
       for (int ls = 0; ls < 2; ++ls) {
         const int st = 2 * grp + ls;
         const int gs = (sb - sb0) * 4 + st;
-        const int slot = gs % NS, use = gs / NS;
-        if (use > 0 && !mbar_wait(empty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) { alive = false; break; }
-        uint8_t* tile = smem + slot * kStage;
+        const int slot = gs % NSW, use = gs / NSW;
+        if (use > 0) {                       // one lane polls the barrier, the warp follows
+          int ok = 1;
+          if (lane == 0) ok = mbar_wait(wempty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) { alive = false; break; }
+          tcgen05_fence_after();
+        }
+        const uint32_t tile = tmem_lane + uint32_t(slot * kWSlotCols);   // column k'/2 of this slot
         if (QT == QTYPE_Q4_K) {
           // stage = 64-weight group: low nibbles -> sub-block 2*st (k' 0..31), high -> 2*st+1 (k' 32..63)
           const int sh = 16 * ls;
@@ -362,10 +386,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
             bytes_to_pairs<T>(qw[4 * ls + i] & 0x0f0f0f0fu, off, s_lo, a_lo, lo[2 * i], lo[2 * i + 1]);
             bytes_to_pairs<T>((qw[4 * ls + i] >> 4) & 0x0f0f0f0fu, off, s_hi, a_hi, hi[2 * i], hi[2 * i + 1]);
           }
-          sts_chunk(tile, row, 2 * lhalf, lo[0], lo[1], lo[2], lo[3]);
-          sts_chunk(tile, row, 2 * lhalf + 1, lo[4], lo[5], lo[6], lo[7]);
-          sts_chunk(tile, row, 4 + 2 * lhalf, hi[0], hi[1], hi[2], hi[3]);
-          sts_chunk(tile, row, 4 + 2 * lhalf + 1, hi[4], hi[5], hi[6], hi[7]);
+          tmem_st8(tile + 8 * lhalf, lo);            // k' = 16*lhalf .. +15
+          tmem_st8(tile + 16 + 8 * lhalf, hi);       // k' = 32 + 16*lhalf .. +15
         } else {
           // stage = (half block grp, quad pair ls): quads 2*ls (k' 0..31) and 2*ls+1 (k' 32..63)
           const V off = P::splat(P::kMagic + 32.f);
@@ -382,11 +404,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
               const uint32_t hs = quad == 0 ? qw[8 + i] << 4 : quad == 1 ? qw[8 + i] << 2 : quad == 2 ? qw[8 + i] : qw[8 + i] >> 2;
               bytes_to_pairs<T>(l4 | (hs & 0x30303030u), off, s2, zero, o[2 * i], o[2 * i + 1]);
             }
-            sts_chunk(tile, row, 4 * qo + 2 * lhalf, o[0], o[1], o[2], o[3]);
-            sts_chunk(tile, row, 4 * qo + 2 * lhalf + 1, o[4], o[5], o[6], o[7]);
+            tmem_st8(tile + 16 * qo + 8 * lhalf, o);   // k' = 32*qo + 16*lhalf .. +15
           }
         }
-        fence_proxy_async();
+        tmem_st_wait();
+        tcgen05_fence_before();
         mbar_arrive(wfull(slot));
       }
     }
@@ -425,14 +447,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
     if (lane == 0) {
       int issued = 0;
       for (int gs = 0; gs < nstage_total; ++gs) {
-        const int slot = gs % NS, use = gs / NS;
-        if (use > 0 && !mbar_wait(empty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
-        mbar_arrive_expect_tx(xfull(slot), uint32_t(BM * kBK * 2));
-        tma_load_2d(smem_u32(smem + slot * kStage + kWTileBytes), &x_map, xfull(slot), sb0 * 256 + gs * kBK, m0);
+        const int slot = gs % NSX, use = gs / NSX;
+        if (use > 0 && !mbar_wait(xempty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
+        mbar_arrive_expect_tx(xfull(slot), uint32_t(kXTile));
+        tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, xfull(slot), sb0 * 256 + gs * kBK, m0);
         issued = gs + 1;
       }
       if (*abort_flag) {   // make sure no bulk copy is still writing this CTA's shared memory at exit
-        for (int gs = max(0, issued - NS); gs < issued; ++gs) mbar_wait_plain(xfull(gs % NS), uint32_t(gs / NS) & 1u);
+        for (int gs = max(0, issued - NSX); gs < issued; ++gs) mbar_wait_plain(xfull(gs % NSX), uint32_t(gs / NSX) & 1u);
       }
     }
   } else {
@@ -440,17 +462,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
     if (lane == 0) {
       bool ok = true;
       for (int gs = 0; gs < nstage_total && ok; ++gs) {
-        const int slot = gs % NS, use = gs / NS;
-        ok = mbar_wait(wfull(slot), uint32_t(use) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) &&
-             mbar_wait(xfull(slot), uint32_t(use) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
+        const int wslot = gs % NSW, xslot = gs % NSX;
+        ok = mbar_wait(wfull(wslot), uint32_t(gs / NSW) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) &&
+             mbar_wait(xfull(xslot), uint32_t(gs / NSX) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t a_addr = smem_u32(smem + slot * kStage), b_addr = a_addr + kWTileBytes;
-        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
+        const uint32_t a_tmem = tmem_base + uint32_t(BM + wslot * kWSlotCols);
+        const uint64_t db = smem_desc_sw128(smem_u32(xtiles + xslot * kXTile));
 #pragma unroll
-        for (int kk = 0; kk < kBK / 16; ++kk)
-          umma_f16_ss(tmem_base, da + uint64_t(2 * kk), db + uint64_t(2 * kk), kIdesc, (gs > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(empty(slot));
+        for (int kk = 0; kk < kBK / 16; ++kk)      // 16 K values = 8 TMEM columns of A, 32 bytes of each B row
+          umma_f16_ts(tmem_base, a_tmem + uint32_t(8 * kk), db + uint64_t(2 * kk), kIdesc, (gs > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(wempty(wslot));
+        umma_commit(xempty(xslot));
       }
       if (ok && nstage_total > 0) {
         umma_commit(accbar);
@@ -465,7 +488,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
   __syncthreads();
   if (warp == 17) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(uint32_t(BM)) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
