@@ -9,13 +9,15 @@
 // (tcgen05.mma with A in TMEM): a 128 x 64 bf16 tile is 128 lanes x 32 columns, four such slots sit behind the
 // accumulator columns, so the dequantized weights never touch shared memory - at 128 x 256 x 16 per instruction
 // the MMA's shared-memory reads alone would otherwise take 3/4 of the SM's shared-memory bandwidth.  Per CTA:
-//   * 16 producer warps (512 threads): stage the packed bytes of 128 weight rows x one 256-weight
-//     super-block global -> shared with 16-byte cp.async, copy their own words to registers, start the
-//     next super-block's copy, then unpack.  Warps 0-7 produce the two 64-wide K stages of the first
+//   * warp 18, one lane: TMA of the PACKED bytes of 128 weight rows x one 256-weight super-block (a 2-D byte
+//     tensor map over the weight, box = 128 rows x the 16-byte aligned window around the block) into a
+//     3-deep shared-memory ring.  One instruction per 18-30 KB: no thread spends issue slots on the copy.
+//   * 16 producer warps (512 threads): wait for the packed super-block, copy their own words to registers,
+//     release the ring slot, then unpack.  Warps 0-7 produce the two 64-wide K stages of the first
 //     half of the super-block, warps 8-15 those of the second half; thread (row = 32*(warp%4)+lane,
 //     half = (warp%8)/4) unpacks 32 weights per stage with 32-bit logic + packed bf16x2/f16x2 math and
 //     writes them to its TMEM lane with two tcgen05.st.32x32b.x8 (16 columns of 2 x 16-bit);
-//     tcgen05.wait::st + mbarrier arrive.
+//     tcgen05.wait::st + mbarrier arrive.  The two groups only meet at mbarriers, never at a CTA barrier.
 //   * warp 16, one lane: TMA (cp.async.bulk.tensor.2d, SWIZZLE_128B, no multicast) of the BM x 64
 //     activation tile per stage; rows past M are zero-filled by the tensor map.
 //   * warp 17, one lane: tcgen05.mma.cta_group::1.kind::f16 (128 x BM x 16, four per stage), then
@@ -24,10 +26,12 @@
 //     warp/4 the column quarter), add bias, convert and store; or store fp32 partials for split-K.
 // Split-K (grid.z) fills the machine when (M/BM)*(N/128) < #SMs; partials go to a library-owned fp32
 // workspace and a second kernel sums them, adds bias and converts.
+// The packed-weight tensor map needs weight rows that are multiples of 16 bytes: any K for Q4_K (144-byte
+// blocks), K % 2048 == 0 for Q6_K (210-byte blocks).  Other shapes are served by the other variants.
 //
 // Every mbarrier wait is bounded: after kSpinLimit polls the waiter records a code in a device status
 // word, raises a CTA-wide abort flag and every role falls through to the common teardown (outstanding
-// cp.async / TMA copies are waited for, TMEM is freed).  Nothing traps or spins forever.
+// TMA copies are waited for, TMEM is freed).  Nothing traps or spins forever.
 //
 // The reference has no counterpart kernel: its CUDA path dequantizes the whole weight to a dense
 // scratch and calls an Sm80 mma.sync CUTLASS GEMM (src/dinoml/lowering/ops/gemm.py:729-749,
@@ -50,8 +54,8 @@ constexpr int kRowsW = 128;            // weight rows per CTA (UMMA M)
 constexpr int kBK = 64;                // K per pipeline stage (one 128-byte swizzle atom of 16-bit values)
 constexpr int kProducerThreads = 512;
 constexpr int kGroupThreads = 256;     // producers of one K stage
-constexpr int kThreads = kProducerThreads + 64;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kThreads = kProducerThreads + 96;   // + activation TMA warp, MMA warp, packed-weight TMA warp
+constexpr uint32_t kSpinLimit = 1u << 24;   // try_wait polls before a wait gives up (each poll suspends ~tens of ns or more)
 
 enum : int { ST_OK = 0, ST_EMPTY_TIMEOUT = 1, ST_FULL_TIMEOUT = 2, ST_ACC_TIMEOUT = 3 };
 
@@ -75,13 +79,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false (after flagging) if the phase never completes or the CTA is aborting.
+// Only one lane per warp polls (18 pollers per CTA), so there is no sleep back-off: try_wait itself suspends the
+// thread for a hardware-defined slice.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) {
-      if (*abort_flag) return false;
-      __nanosleep(40);
-    }
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicCAS(status, 0, code);
@@ -96,12 +99,6 @@ __device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void producer_bar_sync() { asm volatile("bar.sync 1, 512;\n" ::: "memory"); }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
   asm volatile(
@@ -201,23 +198,32 @@ __device__ __forceinline__ void q6k_fetch(const uint8_t* rowbase, int hb, int lh
   fetch16<S>(rowbase + 208, tail + 4);                        // d (first 2 bytes)
 }
 
+// Packed super-block window in shared memory: the 16-byte aligned span that contains one block of every row.
+// Q4_K blocks (144 B) are always aligned; a Q6_K block (210 B) starts 0..14 bytes into its window and the last
+// field read (d, through a 32-byte fetch at +208) ends at byte 240.  Both pitches are an odd number of 16-byte
+// chunks, so 16-byte reads of 8 consecutive rows hit all 32 banks.
 template <int QT> struct RawGeom;
-template <> struct RawGeom<QTYPE_Q4_K> { static constexpr int kPitch = 144, kChunks = 9; };
-template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240, kChunks = 14; };   // 15 chunks: 16-byte reads of 8 rows hit 32 banks
+template <> struct RawGeom<QTYPE_Q4_K> { static constexpr int kPitch = 144; };
+template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240; };
 
 // Rings: 4 weight-tile slots in TMEM (32 columns each, right after the BM accumulator columns), NSX activation
-// tiles in shared memory (TMA), and two raw super-block buffers (packed bytes prefetched two super-blocks ahead).
+// tiles and kRawSlots packed super-blocks in shared memory (both TMA).
 constexpr int kWSlots = 4;
 constexpr int kWSlotCols = kBK / 2;     // 64 16-bit values per lane = 32 columns
-template <int BM> constexpr int x_slots() { return BM >= 256 ? 5 : 6; }
+constexpr int kRawSlots = 3;
+constexpr int kSmemBudget = 227 * 1024;
 template <int BM> constexpr int x_tile_bytes() { return BM * kBK * 2; }
+template <int QT> constexpr int raw_slot_bytes() { return kRowsW * RawGeom<QT>::kPitch; }
+template <int QT, int BM> constexpr int x_slots() {
+  constexpr int fit = (kSmemBudget - 1024 - 512 - kRawSlots * raw_slot_bytes<QT>()) / x_tile_bytes<BM>();
+  return fit > 6 ? 6 : fit;
+}
 template <int BM> constexpr int tmem_cols() { return BM + kWSlots * kWSlotCols > 256 ? 512 : 256; }
 template <int QT, int BM> constexpr size_t smem_bytes() {
-  return 1024 + size_t(x_slots<BM>()) * x_tile_bytes<BM>() + 2 * size_t(kRowsW) * RawGeom<QT>::kPitch + 256;
+  return 1024 + size_t(x_slots<QT, BM>()) * x_tile_bytes<BM>() + size_t(kRawSlots) * raw_slot_bytes<QT>() + 512;
 }
 
 struct Params {
-  const uint8_t* w;       // packed GGUF blocks [n, k/256 * block_bytes]
   const void* bias;       // [n] or null (ignored when partial != null)
   void* out;              // [m, n] in the activation dtype
   float* partial;         // split-K workspace [splits, m, n] or null
@@ -228,32 +234,38 @@ struct Params {
 
 template <int QT, typename T, int BM>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
+gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const Params p) {
   using P = Pair<T>;
   using V = typename P::V;
-  constexpr int NSW = kWSlots, NSX = x_slots<BM>();
+  constexpr int NSW = kWSlots, NSX = x_slots<QT, BM>(), NSR = kRawSlots;
   constexpr int kXTile = x_tile_bytes<BM>();
   constexpr uint32_t kTmemCols = tmem_cols<BM>();
   constexpr int kPitch = RawGeom<QT>::kPitch;
+  constexpr int kRawBytes = raw_slot_bytes<QT>();
   constexpr int kBlockBytes = QTraits<QT>::kBytes;
-  constexpr uint32_t kIdesc = (1u << 4) | (P::kFormat << 7) | (P::kFormat << 10) | (uint32_t(BM >> 3) << 17) | (uint32_t(kRowsW >> 4) << 24);
+  constexpr uint32_t kIdesc = (1u << 4) | (P::kFormat << 7) | (P::kFormat << 10) | (uint32_t(BM >> 3) << 17) |
+                              (uint32_t(kRowsW >> 4) << 24);
+  constexpr uint32_t kWarpArrivals = kGroupThreads / 32;     // one elected arrive per producer warp of a group
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* xtiles = smem;                                              // NSX x [BM][128 B]
-  uint8_t* raw = xtiles + NSX * kXTile;                                // 2 x [128][kPitch]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * kRowsW * kPitch);
-  // bars: wfull[NSW], wempty[NSW], xfull[NSX], xempty[NSX], accumulator, drain
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSW + 2 * NSX + 2);
+  uint8_t* raw = xtiles + NSX * kXTile;                                // NSR x [128][kPitch]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(raw + NSR * kRawBytes);
+  // bars: wfull[NSW], wempty[NSW], xfull[NSX], xempty[NSX], rawfull[NSR], rawfree[NSR], accumulator, drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSW + 2 * NSX + 2 * NSR + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto wfull = [&](int s) { return bar0 + 8u * s; };
   auto wempty = [&](int s) { return bar0 + 8u * (NSW + s); };
   auto xfull = [&](int s) { return bar0 + 8u * (2 * NSW + s); };
   auto xempty = [&](int s) { return bar0 + 8u * (2 * NSW + NSX + s); };
-  const uint32_t accbar = bar0 + 8u * (2 * NSW + 2 * NSX), drainbar = accbar + 8u;
+  auto rawfull = [&](int s) { return bar0 + 8u * (2 * NSW + 2 * NSX + s); };
+  auto rawfree = [&](int s) { return bar0 + 8u * (2 * NSW + 2 * NSX + NSR + s); };
+  const uint32_t accbar = bar0 + 8u * (2 * NSW + 2 * NSX + 2 * NSR), drainbar = accbar + 8u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // grid.x walks activation tiles, so CTAs that share a weight panel run together
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * kRowsW;
   const int nsb = p.k >> 8;
   const int sb0 = blockIdx.z * p.sb_per_split, sb1 = min(nsb, sb0 + p.sb_per_split);
@@ -261,12 +273,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
 
   if (tid == 0) {
     for (int s = 0; s < NSW; ++s) {
-      mbar_init(wfull(s), kGroupThreads);
+      mbar_init(wfull(s), kWarpArrivals);
       mbar_init(wempty(s), 1);
     }
     for (int s = 0; s < NSX; ++s) {
       mbar_init(xfull(s), 1);
       mbar_init(xempty(s), 1);
+    }
+    for (int s = 0; s < NSR; ++s) {
+      mbar_init(rawfull(s), 1);
+      mbar_init(rawfree(s), kProducerThreads / 32);
     }
     mbar_init(accbar, 1);
     mbar_init(drainbar, 1);
@@ -286,59 +302,41 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
     // ------------------------------------------------------------------ producers
     const int grp = warp >> 3;                                  // which half of the super-block (two K stages)
     const int row = 32 * (warp & 3) + lane, lhalf = (warp >> 2) & 1;
-    const int64_t row_bytes = int64_t(nsb) * kBlockBytes;
-    const uint8_t* wrow = p.w + int64_t(min(n0 + row, p.n - 1)) * row_bytes;
-    // raw copy role: 4 threads per row, each up to 4 16-byte chunks
-    const int cp_row = tid >> 2, cp_q = tid & 3;
-    const uint8_t* cp_wrow = p.w + int64_t(min(n0 + cp_row, p.n - 1)) * row_bytes;
-    auto issue_raw = [&](int sb) {
-      if (sb < sb1) {
-        const uint8_t* src = cp_wrow + int64_t(sb) * kBlockBytes;
-        const uint32_t shift = uint32_t(reinterpret_cast<uintptr_t>(src) & 15);
-        const int nchunk = int(shift + kBlockBytes + 15) >> 4;
-        const uint8_t* src16 = src - shift;
-        const uint32_t dst = smem_u32(raw + ((sb - sb0) & 1) * (kRowsW * kPitch) + cp_row * kPitch);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int c = cp_q * 4 + j;
-          if (c < nchunk) cp_async16(dst + 16 * c, src16 + 16 * c);
-        }
-      }
-      cp_async_commit();
-    };
-    issue_raw(sb0);
-    issue_raw(sb0 + 1);
     bool alive = true;
     const uint32_t tmem_lane = tmem_base + (uint32_t(32 * (warp & 3)) << 16) + uint32_t(BM);   // this warp's lanes, first A column
     for (int sb = sb0; sb < sb1 && alive; ++sb) {
-      cp_async_wait<1>();                  // everything but the newest copy group: super-block sb has landed
-      producer_bar_sync();                 // ... and is visible to all producers
-      const uint8_t* rawbuf = raw + ((sb - sb0) & 1) * (kRowsW * kPitch);
-      const uint8_t* blk = rawbuf + row * kPitch + (reinterpret_cast<uintptr_t>(wrow + int64_t(sb) * kBlockBytes) & 15);
+      const int ri = sb - sb0, rslot = ri % NSR;
+      {
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(rawfull(rslot), uint32_t(ri / NSR) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { alive = false; break; }
+      }
+      const uint8_t* rowbase = raw + rslot * kRawBytes + row * kPitch;
       // ---- copy this thread's packed words to registers
       uint32_t qw[12];
       float dscale, dmin = 0.f;
-      float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3; Q4_K: (ds, dm) of the two groups
+      float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3
       if (QT == QTYPE_Q4_K) {
-        const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+        const uint4 hdr = *reinterpret_cast<const uint4*>(rowbase);
         dscale = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
         dmin = half_bits_to_float(uint16_t(hdr.x >> 16));
-        // sub-blocks 4*grp .. 4*grp+3 belong to this thread's two groups
+        // sub-blocks 4*grp .. 4*grp+3 belong to this thread's two stages
         const uint32_t scw = grp == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4));
         const uint32_t mnw = grp == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4));
         qw[8] = scw;
         qw[9] = mnw;
 #pragma unroll
         for (int ls = 0; ls < 2; ++ls) {
-          const uint4 q = *reinterpret_cast<const uint4*>(blk + 16 + 32 * (2 * grp + ls) + 16 * lhalf);
+          const uint4 q = *reinterpret_cast<const uint4*>(rowbase + 16 + 64 * grp + 32 * ls + 16 * lhalf);
           qw[4 * ls] = q.x; qw[4 * ls + 1] = q.y; qw[4 * ls + 2] = q.z; qw[4 * ls + 3] = q.w;
         }
         sub_scale[0] = sub_scale[1] = sub_scale[2] = sub_scale[3] = 0.f;
       } else {
         const int hb = grp;
-        const uint8_t* rowbase = rawbuf + row * kPitch;
         uint32_t tail[8];                     // bytes 192..223 of the block: 16 int8 scales, then d
-        switch (int(blk - rowbase) >> 1) {
+        // rows are 16-byte multiples, so the block's phase inside its window is the same for every row
+        switch (((sb * kBlockBytes) & 15) >> 1) {
           case 0: q6k_fetch<0>(rowbase, hb, lhalf, qw, tail); break;
           case 1: q6k_fetch<1>(rowbase, hb, lhalf, qw, tail); break;
           case 2: q6k_fetch<2>(rowbase, hb, lhalf, qw, tail); break;
@@ -357,8 +355,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
           sub_scale[i] = float(int(int8_t(wsel >> (8 * (2 * (i & 1) + lhalf)))));
         }
       }
-      producer_bar_sync();                 // every producer holds its words: this raw buffer may be refilled
-      issue_raw(sb + 2);
+      __syncwarp();                          // every lane holds its words: the ring slot may be refilled
+      if (lane == 0) mbar_arrive(rawfree(rslot));
 #pragma unroll
       for (int ls = 0; ls < 2; ++ls) {
         const int st = 2 * grp + ls;
@@ -409,10 +407,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
         }
         tmem_st_wait();
         tcgen05_fence_before();
-        mbar_arrive(wfull(slot));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(wfull(slot));
       }
     }
-    cp_async_wait<0>();
 
     // ------------------------------------------------------------------ epilogue
     if (alive && nstage_total > 0 && mbar_wait(accbar, 0, abort_flag, p.status, ST_ACC_TIMEOUT)) {
@@ -453,8 +451,24 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const Params p) {
         tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, xfull(slot), sb0 * 256 + gs * kBK, m0);
         issued = gs + 1;
       }
-      if (*abort_flag) {   // make sure no bulk copy is still writing this CTA's shared memory at exit
+      if (*abort_flag) {   // make sure no bulk copy is still writing shared memory at exit
         for (int gs = max(0, issued - NSX); gs < issued; ++gs) mbar_wait_plain(xfull(gs % NSX), uint32_t(gs / NSX) & 1u);
+      }
+    }
+  } else if (warp == 18) {
+    // ------------------------------------------------------------------ packed-weight TMA
+    if (lane == 0) {
+      int issued = 0;
+      for (int ri = 0; ri < sb1 - sb0; ++ri) {
+        const int slot = ri % NSR, use = ri / NSR;
+        if (use > 0 && !mbar_wait(rawfree(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
+        mbar_arrive_expect_tx(rawfull(slot), uint32_t(kRawBytes));
+        // x coordinate = block start rounded down to 16 bytes; rows past N and bytes past the row end read as zero
+        tma_load_2d(smem_u32(raw + slot * kRawBytes), &w_map, rawfull(slot), ((sb0 + ri) * kBlockBytes) & ~15, n0);
+        issued = ri + 1;
+      }
+      if (*abort_flag) {
+        for (int ri = max(0, issued - NSR); ri < issued; ++ri) mbar_wait_plain(rawfull(ri % NSR), uint32_t(ri / NSR) & 1u);
       }
     }
   } else {
@@ -579,23 +593,34 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
                   cudaStream_t s) {
   EncodeTiledFn enc = encode_tiled();
   if (enc == nullptr) return RC_LAUNCH;
-  CUtensorMap map;
-  const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(m)};
-  const cuuint64_t strides[1] = {cuuint64_t(k) * 2};
-  const cuuint32_t box[2] = {cuuint32_t(kBK), cuuint32_t(BM)};
   const cuuint32_t estr[2] = {1, 1};
-  if (enc(&map, Pair<T>::kTmaType, 2, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return RC_LAUNCH;
+  CUtensorMap x_map, w_map;
+  {   // activations [m, k], 16-bit: box = one K stage x BM rows, 128-byte swizzle (the MMA's B operand layout)
+    const cuuint64_t dims[2] = {cuuint64_t(k), cuuint64_t(m)};
+    const cuuint64_t strides[1] = {cuuint64_t(k) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(kBK), cuuint32_t(BM)};
+    if (enc(&x_map, Pair<T>::kTmaType, 2, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return RC_LAUNCH;
+  }
+  {   // packed weight as bytes [n, row_bytes]: box = the aligned window around one block x 128 rows, no swizzle
+    const cuuint64_t row_bytes = cuuint64_t(k / 256) * QTraits<QT>::kBytes;
+    const cuuint64_t dims[2] = {row_bytes, cuuint64_t(n)};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {cuuint32_t(RawGeom<QT>::kPitch), cuuint32_t(kRowsW)};
+    if (enc(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(b), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return RC_LAUNCH;
+  }
   auto kern = gemm_umma_kernel<QT, T, BM>;
   constexpr size_t smem = smem_bytes<QT, BM>();
+  static_assert(smem <= size_t(kSmemBudget), "shared-memory rings exceed the per-CTA limit");
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
     attr_set = true;
   }
   Params p;
-  p.w = static_cast<const uint8_t*>(b);
   p.bias = bias;
   p.out = c;
   p.partial = pl.splits > 1 ? sc.workspace : nullptr;
@@ -603,7 +628,7 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
   p.m = m; p.n = n; p.k = k;
   p.sb_per_split = pl.sb_per_split;
   const dim3 grid((m + BM - 1) / BM, (n + kRowsW - 1) / kRowsW, pl.splits);
-  kern<<<grid, kThreads, smem, s>>>(map, p);
+  kern<<<grid, kThreads, smem, s>>>(x_map, w_map, p);
   if (cudaGetLastError() != cudaSuccess) return RC_LAUNCH;
   if (pl.splits > 1) {
     const int64_t mn = int64_t(m) * n;
@@ -673,7 +698,9 @@ static int launch_bm(const void* a, const void* b, const void* bias, void* c, in
 
 bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k) {
   (void)n;
-  return (qtype == QTYPE_Q4_K || qtype == QTYPE_Q6_K) && (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 17 && k % 256 == 0;
+  if (!(qtype == QTYPE_Q4_K || qtype == QTYPE_Q6_K) || !(dtype == DINO_BF16 || dtype == DINO_F16) || m < 17 || k % 256 != 0) return false;
+  const int64_t row_bytes = int64_t(k / 256) * (qtype == QTYPE_Q4_K ? 144 : 210);
+  return row_bytes % 16 == 0;   // the packed-weight tensor map needs 16-byte row pitches
 }
 
 size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k) {
@@ -687,8 +714,9 @@ static int gemm_rcr_umma_impl(const void* a, const void* b, const void* bias, vo
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
-  if (reinterpret_cast<uintptr_t>(b) & 15) return RC_ALIGN;        // 16-byte cp.async sources
-  if ((int64_t(k) * 2) & 15) return RC_ALIGN;                       // TMA row pitch
+  if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;   // tensor-map bases
+  if ((int64_t(k) * 2) & 15) return RC_ALIGN;                       // activation row pitch
+  if ((int64_t(k / 256) * (qtype == QTYPE_Q4_K ? 144 : 210)) & 15) return RC_ALIGN;   // packed-weight row pitch
   if (dtype == DINO_BF16)
     return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, s)
                                : umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, s);

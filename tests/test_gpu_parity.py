@@ -124,8 +124,13 @@ def test_gemv_mma_q4k(dev, dtype):
 
 UMMA_SHAPES = [  # (m, n, k)
     (17, 128, 256), (64, 256, 512), (100, 200, 1024), (128, 384, 768), (200, 130, 512), (256, 128, 2048),
-    (300, 512, 4096), (513, 256, 1024),
+    (300, 512, 4096), (513, 256, 1024), (150, 256, 6144),
 ]
+
+
+def _umma_k(qtype, k):
+    """The umma variant needs 16-byte weight rows: any K for Q4_K, K % 2048 == 0 for Q6_K (210-byte blocks)."""
+    return k if qtype == "Q4_K" else -(-k // 2048) * 2048
 
 
 @pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K"])
@@ -133,6 +138,7 @@ UMMA_SHAPES = [  # (m, n, k)
 def test_gemm_umma(dev, qtype, dtype):
     """tcgen05 / TMEM prefill GEMM against the oracle (fp32 weights, fp32 accumulation)."""
     for (m, n, k) in UMMA_SHAPES:
+        k = _umma_k(qtype, k)
         blocks = S.random_blocks(qtype, n, k, seed=800 + m + n)
         x, xf = _activations(m, k, 900 + m, dtype, dev)
         ref = oracle.gemm_quant(xf, blocks, qtype, n, k)
@@ -152,7 +158,7 @@ def test_gemm_umma(dev, qtype, dtype):
 
 
 def test_gemm_umma_bias_and_auto_dispatch(dev):
-    n, k, m = 256, 1024, 96
+    n, k, m = 256, 2048, 96
     blocks = S.random_blocks("Q6_K", n, k, seed=990)
     x, xf = _activations(m, k, 991, "bfloat16", dev)
     bias = torch.randn(n, device=dev, dtype=torch.bfloat16)
@@ -162,6 +168,11 @@ def test_gemm_umma_bias_and_auto_dispatch(dev):
     _, _, norm = oracle.max_errors(ref, y.float().cpu().numpy())
     assert norm <= 2e-2, norm
     assert kernels.device_status() == 0
+    # Q6_K rows that are not 16-byte multiples are outside the umma variant: dispatch avoids it, asking for it fails
+    assert kernels.select_variant("Q6_K", "bfloat16", m, n, 1024) == "simt"
+    with pytest.raises(RuntimeError, match="alignment"):
+        kernels.gemm_rcr(x[:, :1024].contiguous(), torch.from_numpy(S.random_blocks("Q6_K", n, 1024, seed=1)).to(dev), "Q6_K",
+                         variant="umma")
 
 
 def test_gemm_bias_and_batch_dims(dev):
