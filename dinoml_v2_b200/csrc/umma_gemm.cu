@@ -90,6 +90,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   atomicCAS(status, 0, code);
   return false;
 }
+// The same wait made by a whole converged warp, with one answer for all lanes.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code) ? 1 : 0) != 0;
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}\n" : "=r"(pred));
+  return pred != 0;
+}
 // Bounded wait with no flagging, for teardown paths.
 __device__ __forceinline__ void mbar_wait_plain(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
@@ -442,60 +451,70 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     }
   } else if (warp == 16) {
     // ------------------------------------------------------------------ activation TMA
-    if (lane == 0) {
-      int issued = 0;
-      for (int gs = 0; gs < nstage_total; ++gs) {
-        const int slot = gs % NSX, use = gs / NSX;
-        if (use > 0 && !mbar_wait(xempty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
+    // The three control warps stay converged: every lane runs the loop and polls the barriers, one elected lane issues
+    // the asynchronous instructions.  Inside a divergent `if (lane == 0)` region the compiler cannot keep descriptors,
+    // coordinates and barrier addresses in uniform registers, and each tcgen05.mma / bulk copy then costs tens of cycles
+    // of register shuffling on the one thread the whole pipeline waits for.
+    int issued = 0;
+    for (int gs = 0; gs < nstage_total; ++gs) {
+      const int slot = gs % NSX, use = gs / NSX;
+      if (use > 0 && !warp_wait(xempty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
+      if (elect_one()) {
         mbar_arrive_expect_tx(xfull(slot), uint32_t(kXTile));
         tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, xfull(slot), sb0 * 256 + gs * kBK, m0);
-        issued = gs + 1;
       }
-      if (*abort_flag) {   // make sure no bulk copy is still writing shared memory at exit
-        for (int gs = max(0, issued - NSX); gs < issued; ++gs) mbar_wait_plain(xfull(gs % NSX), uint32_t(gs / NSX) & 1u);
-      }
+      __syncwarp();
+      issued = gs + 1;
+    }
+    if (*abort_flag) {   // make sure no bulk copy is still writing shared memory at exit
+      for (int gs = max(0, issued - NSX); gs < issued; ++gs) mbar_wait_plain(xfull(gs % NSX), uint32_t(gs / NSX) & 1u);
     }
   } else if (warp == 18) {
     // ------------------------------------------------------------------ packed-weight TMA
-    if (lane == 0) {
-      int issued = 0;
-      for (int ri = 0; ri < sb1 - sb0; ++ri) {
-        const int slot = ri % NSR, use = ri / NSR;
-        if (use > 0 && !mbar_wait(rawfree(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
+    int issued = 0;
+    for (int ri = 0; ri < sb1 - sb0; ++ri) {
+      const int slot = ri % NSR, use = ri / NSR;
+      if (use > 0 && !warp_wait(rawfree(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
+      if (elect_one()) {
         mbar_arrive_expect_tx(rawfull(slot), uint32_t(kRawBytes));
         // x coordinate = block start rounded down to 16 bytes; rows past N and bytes past the row end read as zero
         tma_load_2d(smem_u32(raw + slot * kRawBytes), &w_map, rawfull(slot), ((sb0 + ri) * kBlockBytes) & ~15, n0);
-        issued = ri + 1;
       }
-      if (*abort_flag) {
-        for (int ri = max(0, issued - NSR); ri < issued; ++ri) mbar_wait_plain(rawfull(ri % NSR), uint32_t(ri / NSR) & 1u);
-      }
+      __syncwarp();
+      issued = ri + 1;
+    }
+    if (*abort_flag) {
+      for (int ri = max(0, issued - NSR); ri < issued; ++ri) mbar_wait_plain(rawfull(ri % NSR), uint32_t(ri / NSR) & 1u);
     }
   } else {
     // ------------------------------------------------------------------ MMA issue
-    if (lane == 0) {
-      bool ok = true;
-      for (int gs = 0; gs < nstage_total && ok; ++gs) {
-        const int wslot = gs % NSW, xslot = gs % NSX;
-        ok = mbar_wait(wfull(wslot), uint32_t(gs / NSW) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) &&
-             mbar_wait(xfull(xslot), uint32_t(gs / NSX) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
-        if (!ok) break;
-        tcgen05_fence_after();
-        const uint32_t a_tmem = tmem_base + uint32_t(BM + wslot * kWSlotCols);
-        const uint64_t db = smem_desc_sw128(smem_u32(xtiles + xslot * kXTile));
+    bool ok = true;
+    for (int gs = 0; gs < nstage_total; ++gs) {
+      const int wslot = gs % NSW, xslot = gs % NSX;
+      ok = warp_wait(wfull(wslot), uint32_t(gs / NSW) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) &&
+           warp_wait(xfull(xslot), uint32_t(gs / NSX) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t a_tmem = tmem_base + uint32_t(BM + wslot * kWSlotCols);
+      const uint64_t db = smem_desc_sw128(smem_u32(xtiles + xslot * kXTile));
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < kBK / 16; ++kk)      // 16 K values = 8 TMEM columns of A, 32 bytes of each B row
           umma_f16_ts(tmem_base, a_tmem + uint32_t(8 * kk), db + uint64_t(2 * kk), kIdesc, (gs > 0 || kk > 0) ? 1u : 0u);
         umma_commit(wempty(wslot));
         umma_commit(xempty(xslot));
       }
-      if (ok && nstage_total > 0) {
+      __syncwarp();
+    }
+    if (nstage_total > 0 && elect_one()) {
+      if (ok) {
         umma_commit(accbar);
-      } else if (nstage_total > 0) {   // aborting: let every MMA already issued finish before TMEM is freed
+      } else {                         // aborting: let every MMA already issued finish before TMEM is freed
         umma_commit(drainbar);
         mbar_wait_plain(drainbar, 0);
       }
     }
+    __syncwarp();
   }
 
   tcgen05_fence_before();
