@@ -215,21 +215,17 @@ template <int QT> struct RawGeom;
 template <> struct RawGeom<QTYPE_Q4_K> { static constexpr int kPitch = 144; };
 template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240; };
 
-// Rings: 4 weight-tile slots in TMEM (32 columns each, right after the BM accumulator columns), NSX activation
-// tiles and kRawSlots packed super-blocks in shared memory (both TMA).
+// Rings: 4 stages = weight-tile slots in TMEM (32 columns each, right after the BM accumulator columns) paired with
+// activation tiles in shared memory, and kRawSlots packed super-blocks in shared memory (both TMA).
 constexpr int kWSlots = 4;
 constexpr int kWSlotCols = kBK / 2;     // 64 16-bit values per lane = 32 columns
 constexpr int kRawSlots = 3;
 constexpr int kSmemBudget = 227 * 1024;
 template <int BM> constexpr int x_tile_bytes() { return BM * kBK * 2; }
 template <int QT> constexpr int raw_slot_bytes() { return kRowsW * RawGeom<QT>::kPitch; }
-template <int QT, int BM> constexpr int x_slots() {
-  constexpr int fit = (kSmemBudget - 1024 - 512 - kRawSlots * raw_slot_bytes<QT>()) / x_tile_bytes<BM>();
-  return fit > 6 ? 6 : fit;
-}
 template <int BM> constexpr int tmem_cols() { return BM + kWSlots * kWSlotCols > 256 ? 512 : 256; }
 template <int QT, int BM> constexpr size_t smem_bytes() {
-  return 1024 + size_t(x_slots<QT, BM>()) * x_tile_bytes<BM>() + size_t(kRawSlots) * raw_slot_bytes<QT>() + 512;
+  return 1024 + size_t(kWSlots) * x_tile_bytes<BM>() + size_t(kRawSlots) * raw_slot_bytes<QT>() + 512;
 }
 
 struct Params {
@@ -246,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const Params p) {
   using P = Pair<T>;
   using V = typename P::V;
-  constexpr int NSW = kWSlots, NSX = x_slots<QT, BM>(), NSR = kRawSlots;
+  constexpr int NS = kWSlots, NSR = kRawSlots;    // stage ring (weight tile in TMEM + activation tile in smem), packed ring
   constexpr int kXTile = x_tile_bytes<BM>();
   constexpr uint32_t kTmemCols = tmem_cols<BM>();
   constexpr int kPitch = RawGeom<QT>::kPitch;
@@ -258,20 +254,20 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* xtiles = smem;                                              // NSX x [BM][128 B]
-  uint8_t* raw = xtiles + NSX * kXTile;                                // NSR x [128][kPitch]
+  uint8_t* xtiles = smem;                                              // NS x [BM][128 B]
+  uint8_t* raw = xtiles + NS * kXTile;                                 // NSR x [128][kPitch]
   uint64_t* bars = reinterpret_cast<uint64_t*>(raw + NSR * kRawBytes);
-  // bars: wfull[NSW], wempty[NSW], xfull[NSX], xempty[NSX], rawfull[NSR], rawfree[NSR], accumulator, drain
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSW + 2 * NSX + 2 * NSR + 2);
+  // bars: full[NS], empty[NS], rawfull[NSR], rawfree[NSR], accumulator, drain.  A stage is "full" when its 8 producer
+  // warps have written the weight tile AND the activation tile's bytes have landed (one barrier, one wait for the MMA
+  // warp); it is "empty" when the MMAs that read it have completed (one tcgen05.commit, watched by producers and TMA).
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NS + 2 * NSR + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
-  auto wfull = [&](int s) { return bar0 + 8u * s; };
-  auto wempty = [&](int s) { return bar0 + 8u * (NSW + s); };
-  auto xfull = [&](int s) { return bar0 + 8u * (2 * NSW + s); };
-  auto xempty = [&](int s) { return bar0 + 8u * (2 * NSW + NSX + s); };
-  auto rawfull = [&](int s) { return bar0 + 8u * (2 * NSW + 2 * NSX + s); };
-  auto rawfree = [&](int s) { return bar0 + 8u * (2 * NSW + 2 * NSX + NSR + s); };
-  const uint32_t accbar = bar0 + 8u * (2 * NSW + 2 * NSX + 2 * NSR), drainbar = accbar + 8u;
+  auto full = [&](int s) { return bar0 + 8u * s; };
+  auto empty = [&](int s) { return bar0 + 8u * (NS + s); };
+  auto rawfull = [&](int s) { return bar0 + 8u * (2 * NS + s); };
+  auto rawfree = [&](int s) { return bar0 + 8u * (2 * NS + NSR + s); };
+  const uint32_t accbar = bar0 + 8u * (2 * NS + 2 * NSR), drainbar = accbar + 8u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // grid.x walks activation tiles, so CTAs that share a weight panel run together
@@ -281,13 +277,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   const int nstage_total = (sb1 - sb0) * 4;
 
   if (tid == 0) {
-    for (int s = 0; s < NSW; ++s) {
-      mbar_init(wfull(s), kWarpArrivals);
-      mbar_init(wempty(s), 1);
-    }
-    for (int s = 0; s < NSX; ++s) {
-      mbar_init(xfull(s), 1);
-      mbar_init(xempty(s), 1);
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(full(s), kWarpArrivals + 1);   // + the TMA lane's arrive.expect_tx
+      mbar_init(empty(s), 1);
     }
     for (int s = 0; s < NSR; ++s) {
       mbar_init(rawfull(s), 1);
@@ -370,10 +362,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
       for (int ls = 0; ls < 2; ++ls) {
         const int st = 2 * grp + ls;
         const int gs = (sb - sb0) * 4 + st;
-        const int slot = gs % NSW, use = gs / NSW;
+        const int slot = gs % NS, use = gs / NS;
         if (use > 0) {                       // one lane polls the barrier, the warp follows
           int ok = 1;
-          if (lane == 0) ok = mbar_wait(wempty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT) ? 1 : 0;
+          if (lane == 0) ok = mbar_wait(empty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT) ? 1 : 0;
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) { alive = false; break; }
           tcgen05_fence_after();
@@ -417,7 +409,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         tmem_st_wait();
         tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(wfull(slot));
+        if (lane == 0) mbar_arrive(full(slot));
       }
     }
 
@@ -455,20 +447,20 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     // the asynchronous instructions.  Inside a divergent `if (lane == 0)` region the compiler cannot keep descriptors,
     // coordinates and barrier addresses in uniform registers, and each tcgen05.mma / bulk copy then costs tens of cycles
     // of register shuffling on the one thread the whole pipeline waits for.
-    int issued = 0;
     for (int gs = 0; gs < nstage_total; ++gs) {
-      const int slot = gs % NSX, use = gs / NSX;
-      if (use > 0 && !warp_wait(xempty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
+      const int slot = gs % NS, use = gs / NS;
+      if (use > 0 && !warp_wait(empty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
       if (elect_one()) {
-        mbar_arrive_expect_tx(xfull(slot), uint32_t(kXTile));
-        tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, xfull(slot), sb0 * 256 + gs * kBK, m0);
+        mbar_arrive_expect_tx(full(slot), uint32_t(kXTile));
+        tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, full(slot), sb0 * 256 + gs * kBK, m0);
       }
       __syncwarp();
-      issued = gs + 1;
     }
-    if (*abort_flag) {   // make sure no bulk copy is still writing shared memory at exit
-      for (int gs = max(0, issued - NSX); gs < issued; ++gs) mbar_wait_plain(xfull(gs % NSX), uint32_t(gs / NSX) & 1u);
-    }
+    // Aborting: up to NS activation copies may still be writing shared memory, and their barrier also counts producer
+    // arrivals that will never come, so it cannot be waited on.  A copy of this size lands within microseconds; give
+    // the last ones a millisecond before the CTA may exit.
+    if (*abort_flag)
+      for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   } else if (warp == 18) {
     // ------------------------------------------------------------------ packed-weight TMA
     int issued = 0;
@@ -490,19 +482,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     // ------------------------------------------------------------------ MMA issue
     bool ok = true;
     for (int gs = 0; gs < nstage_total; ++gs) {
-      const int wslot = gs % NSW, xslot = gs % NSX;
-      ok = warp_wait(wfull(wslot), uint32_t(gs / NSW) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) &&
-           warp_wait(xfull(xslot), uint32_t(gs / NSX) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
+      const int slot = gs % NS;
+      ok = warp_wait(full(slot), uint32_t(gs / NS) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
       if (!ok) break;
       tcgen05_fence_after();
-      const uint32_t a_tmem = tmem_base + uint32_t(BM + wslot * kWSlotCols);
-      const uint64_t db = smem_desc_sw128(smem_u32(xtiles + xslot * kXTile));
+      const uint32_t a_tmem = tmem_base + uint32_t(BM + slot * kWSlotCols);
+      const uint64_t db = smem_desc_sw128(smem_u32(xtiles + slot * kXTile));
       if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < kBK / 16; ++kk)      // 16 K values = 8 TMEM columns of A, 32 bytes of each B row
           umma_f16_ts(tmem_base, a_tmem + uint32_t(8 * kk), db + uint64_t(2 * kk), kIdesc, (gs > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(wempty(wslot));
-        umma_commit(xempty(xslot));
+        umma_commit(empty(slot));
       }
       __syncwarp();
     }
