@@ -120,7 +120,7 @@ int dinoml_b200_gguf_gemm_rcr_prealloc(const void* a, const void* b_quant, const
     const size_t need = gemm_umma_workspace(qtype, dtype, m, n, k);
     if (need > gemm_umma_static_scratch_bytes())
       return set_error_message(rc, "dinoml_b200_gguf_gemm_rcr_prealloc: this problem needs " + std::to_string(need) +
-                                       " bytes of split-K scratch, the built-in scratch holds " +
+                                       " bytes of partial-tile scratch, the built-in scratch holds " +
                                        std::to_string(gemm_umma_static_scratch_bytes()) + "; use dinoml_b200_gguf_gemm_rcr");
   }
   return set_error(rc, "dinoml_b200_gguf_gemm_rcr_prealloc");

@@ -23,9 +23,11 @@
 //   * warp 17, one lane: tcgen05.mma.cta_group::1.kind::f16 (128 x BM x 16, four per stage), then
 //     tcgen05.commit onto the stage's "empty" barrier; after the last stage onto the accumulator barrier.
 //   * epilogue: the 16 producer warps read TMEM (tcgen05.ld 32x32b.x16; warp%4 picks the lane quarter,
-//     warp/4 the column quarter), add bias, convert and store; or store fp32 partials for split-K.
-// Split-K (grid.z) fills the machine when (M/BM)*(N/128) < #SMs; partials go to a library-owned fp32
-// workspace and a second kernel sums them, adds bias and converts.
+//     warp/4 the column quarter), add bias, convert and store.
+// Work split is stream-K: one CTA per SM, each with the same number of (tile, super-block) units, so the tensor cores
+// of every SM are busy for the whole launch whatever (M/BM)*(N/128) is.  A tile whose K range is cut between CTAs is
+// finished by the CTA that holds its end: the others leave fp32 partial tiles in a library-owned workspace and raise a
+// flag, the finisher adds them in a fixed order (see Walk below).  No second kernel, bit-reproducible results.
 // The packed-weight tensor map needs weight rows that are multiples of 16 bytes: any K for Q4_K (144-byte
 // blocks), K % 2048 == 0 for Q6_K (210-byte blocks).  Other shapes are served by the other variants.
 //
@@ -57,7 +59,8 @@ constexpr int kGroupThreads = 256;     // producers of one K stage
 constexpr int kThreads = kProducerThreads + 96;   // + activation TMA warp, MMA warp, packed-weight TMA warp
 constexpr uint32_t kSpinLimit = 1u << 24;   // try_wait polls before a wait gives up (each poll suspends ~tens of ns or more)
 
-enum : int { ST_OK = 0, ST_EMPTY_TIMEOUT = 1, ST_FULL_TIMEOUT = 2, ST_ACC_TIMEOUT = 3 };
+enum : int { ST_OK = 0, ST_EMPTY_TIMEOUT = 1, ST_FULL_TIMEOUT = 2, ST_ACC_TIMEOUT = 3, ST_PEER_TIMEOUT = 4 };
+constexpr uint32_t kFlagSpinLimit = 1u << 22;   // polls (200 ns apart) of another CTA's partial-tile flag
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -217,7 +220,7 @@ template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240; };
 
 // Rings: 4 stages = weight-tile slots in TMEM (32 columns each, right after the BM accumulator columns) paired with
 // activation tiles in shared memory, and kRawSlots packed super-blocks in shared memory (both TMA).
-constexpr int kWSlots = 4;
+constexpr int kWSlots = 4;          // = stages per 256-weight super-block: the MMA loop relies on it
 constexpr int kWSlotCols = kBK / 2;     // 64 16-bit values per lane = 32 columns
 constexpr int kRawSlots = 3;
 constexpr int kSmemBudget = 227 * 1024;
@@ -229,13 +232,44 @@ template <int QT, int BM> constexpr size_t smem_bytes() {
 }
 
 struct Params {
-  const void* bias;       // [n] or null (ignored when partial != null)
+  const void* bias;       // [n] or null
   void* out;              // [m, n] in the activation dtype
-  float* partial;         // split-K workspace [splits, m, n] or null
+  float* partial;         // one fp32 tile [BM][128] per CTA (stream-K partial sums)
+  int* flags;             // one word per CTA: 1 = that CTA's partial tile is complete in `partial`
   int* status;            // device status word
   int m, n, k;
-  int sb_per_split;       // super-blocks per grid.z slice
+  int m_tiles;            // activation tiles per weight panel
+  long long units;        // output tiles x super-blocks
 };
+
+// Stream-K work split.  The work of the launch is a line of units (tile t, super-block sb), tile-major; CTA c of G owns
+// the contiguous range [start(c), start(c+1)), so every SM gets the same amount of tensor-core work whatever the tile
+// count.  A CTA walks its range from the HIGHEST tile down; the segment that holds the end of a tile is therefore the
+// last thing its CTA does, and the other pieces of that tile belong to lower-numbered CTAs that computed them first.
+// Those CTAs store an fp32 partial tile and raise a flag; the CTA with the end of the tile adds the partials in CTA
+// order to its own accumulator, applies bias and stores (deterministic summation order).  Dependencies only point to
+// lower-numbered CTAs, which are dispatched first, and every flag wait is bounded.
+__device__ __forceinline__ long long unit_start(int c, long long units, int ctas) { return (static_cast<long long>(c) * units) / ctas; }
+__device__ __forceinline__ int unit_owner(long long u, long long units, int ctas) { return int(((u + 1) * ctas - 1) / units); }
+
+struct Walk {
+  long long u0, u1;
+  int nsb;
+  __device__ __forceinline__ int tile_hi() const { return int((u1 - 1) / nsb); }
+  __device__ __forceinline__ int tile_lo() const { return int(u0 / nsb); }
+  __device__ __forceinline__ void segment(int t, int& sb_b, int& sb_e) const {
+    const long long base = static_cast<long long>(t) * nsb;
+    sb_b = int((u0 > base ? u0 : base) - base);
+    sb_e = int((u1 < base + nsb ? u1 : base + nsb) - base);
+  }
+};
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(int* p, int v) { asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory"); }
 
 template <int QT, typename T, int BM>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -257,24 +291,28 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   uint8_t* xtiles = smem;                                              // NS x [BM][128 B]
   uint8_t* raw = xtiles + NS * kXTile;                                 // NSR x [128][kPitch]
   uint64_t* bars = reinterpret_cast<uint64_t*>(raw + NSR * kRawBytes);
-  // bars: full[NS], empty[NS], rawfull[NSR], rawfree[NSR], accumulator, drain.  A stage is "full" when its 8 producer
-  // warps have written the weight tile AND the activation tile's bytes have landed (one barrier, one wait for the MMA
-  // warp); it is "empty" when the MMAs that read it have completed (one tcgen05.commit, watched by producers and TMA).
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NS + 2 * NSR + 2);
+  // bars: full[NS], empty[NS], rawfull[NSR], rawfree[NSR], accumulator full, accumulator free, drain, epilogue.  A stage is "full"
+  // when its 8 producer warps have written the weight tile AND the activation tile's bytes have landed (one barrier, one
+  // wait for the MMA warp); it is "empty" when the MMAs that read it have completed (one tcgen05.commit, watched by
+  // producers and TMA).
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NS + 2 * NSR + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (NS + s); };
   auto rawfull = [&](int s) { return bar0 + 8u * (2 * NS + s); };
   auto rawfree = [&](int s) { return bar0 + 8u * (2 * NS + NSR + s); };
-  const uint32_t accbar = bar0 + 8u * (2 * NS + 2 * NSR), drainbar = accbar + 8u;
+  const uint32_t accbar = bar0 + 8u * (2 * NS + 2 * NSR), accfree = accbar + 8u, drainbar = accbar + 16u, epibar = accbar + 24u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // grid.x walks activation tiles, so CTAs that share a weight panel run together
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * kRowsW;
+  const int cta = blockIdx.x, ctas = gridDim.x;
   const int nsb = p.k >> 8;
-  const int sb0 = blockIdx.z * p.sb_per_split, sb1 = min(nsb, sb0 + p.sb_per_split);
-  const int nstage_total = (sb1 - sb0) * 4;
+  Walk walk;
+  walk.u0 = unit_start(cta, p.units, ctas);
+  walk.u1 = unit_start(cta + 1, p.units, ctas);
+  walk.nsb = nsb;
+  const bool has_work = walk.u1 > walk.u0;
+  const int tile_hi = has_work ? walk.tile_hi() : -1, tile_lo = has_work ? walk.tile_lo() : 0;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -286,7 +324,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
       mbar_init(rawfree(s), kProducerThreads / 32);
     }
     mbar_init(accbar, 1);
+    mbar_init(accfree, kProducerThreads / 32);
     mbar_init(drainbar, 1);
+    mbar_init(epibar, kProducerThreads / 32);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -305,119 +345,47 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     const int row = 32 * (warp & 3) + lane, lhalf = (warp >> 2) & 1;
     bool alive = true;
     const uint32_t tmem_lane = tmem_base + (uint32_t(32 * (warp & 3)) << 16) + uint32_t(BM);   // this warp's lanes, first A column
-    for (int sb = sb0; sb < sb1 && alive; ++sb) {
-      const int ri = sb - sb0, rslot = ri % NSR;
+    int it = 0, segi = 0;                                       // super-blocks / segments done by this CTA so far
+    uint32_t epi_phase = 0;
+    // Barrier over the 16 producer warps on an mbarrier, so that it is bounded like every other wait (a plain bar.sync
+    // would hang the warps that reached it if another warp had given up).
+    auto producer_sync = [&]() -> bool {
+      __syncwarp();
+      int ok = 1;
+      if (lane == 0) {
+        mbar_arrive(epibar);
+        ok = mbar_wait(epibar, epi_phase & 1u, abort_flag, p.status, ST_ACC_TIMEOUT) ? 1 : 0;
+      }
+      ++epi_phase;
+      return __shfl_sync(0xffffffffu, ok, 0) != 0;
+    };
+    // Epilogue of one segment (tile t, super-blocks [sb_b, sb_e), the segi-th of this CTA).  false = a wait gave up.
+    auto epilogue = [&](int t, int sb_b, int sb_e, int segi) -> bool {
       {
         int ok = 1;
-        if (lane == 0) ok = mbar_wait(rawfull(rslot), uint32_t(ri / NSR) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) ? 1 : 0;
+        if (lane == 0) ok = mbar_wait(accbar, uint32_t(segi) & 1u, abort_flag, p.status, ST_ACC_TIMEOUT) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { alive = false; break; }
+        if (!ok) return false;
       }
-      const uint8_t* rowbase = raw + rslot * kRawBytes + row * kPitch;
-      // ---- copy this thread's packed words to registers
-      uint32_t qw[12];
-      float dscale, dmin = 0.f;
-      float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3
-      if (QT == QTYPE_Q4_K) {
-        const uint4 hdr = *reinterpret_cast<const uint4*>(rowbase);
-        dscale = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
-        dmin = half_bits_to_float(uint16_t(hdr.x >> 16));
-        // sub-blocks 4*grp .. 4*grp+3 belong to this thread's two stages
-        const uint32_t scw = grp == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4));
-        const uint32_t mnw = grp == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4));
-        qw[8] = scw;
-        qw[9] = mnw;
-#pragma unroll
-        for (int ls = 0; ls < 2; ++ls) {
-          const uint4 q = *reinterpret_cast<const uint4*>(rowbase + 16 + 64 * grp + 32 * ls + 16 * lhalf);
-          qw[4 * ls] = q.x; qw[4 * ls + 1] = q.y; qw[4 * ls + 2] = q.z; qw[4 * ls + 3] = q.w;
-        }
-        sub_scale[0] = sub_scale[1] = sub_scale[2] = sub_scale[3] = 0.f;
-      } else {
-        const int hb = grp;
-        uint32_t tail[8];                     // bytes 192..223 of the block: 16 int8 scales, then d
-        // rows are 16-byte multiples, so the block's phase inside its window is the same for every row
-        switch (((sb * kBlockBytes) & 15) >> 1) {
-          case 0: q6k_fetch<0>(rowbase, hb, lhalf, qw, tail); break;
-          case 1: q6k_fetch<1>(rowbase, hb, lhalf, qw, tail); break;
-          case 2: q6k_fetch<2>(rowbase, hb, lhalf, qw, tail); break;
-          case 3: q6k_fetch<3>(rowbase, hb, lhalf, qw, tail); break;
-          case 4: q6k_fetch<4>(rowbase, hb, lhalf, qw, tail); break;
-          case 5: q6k_fetch<5>(rowbase, hb, lhalf, qw, tail); break;
-          case 6: q6k_fetch<6>(rowbase, hb, lhalf, qw, tail); break;
-          default: q6k_fetch<7>(rowbase, hb, lhalf, qw, tail); break;
-        }
-        dscale = half_bits_to_float(uint16_t(tail[4] & 0xffffu));
-        // scale byte of quad i: 8*hb + 2*i + lhalf -> word 2*hb + i/2, byte 2*(i%2) + lhalf
-        const uint32_t sw0 = hb ? tail[2] : tail[0], sw1 = hb ? tail[3] : tail[1];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t wsel = i < 2 ? sw0 : sw1;
-          sub_scale[i] = float(int(int8_t(wsel >> (8 * (2 * (i & 1) + lhalf)))));
-        }
-      }
-      __syncwarp();                          // every lane holds its words: the ring slot may be refilled
-      if (lane == 0) mbar_arrive(rawfree(rslot));
-#pragma unroll
-      for (int ls = 0; ls < 2; ++ls) {
-        const int st = 2 * grp + ls;
-        const int gs = (sb - sb0) * 4 + st;
-        const int slot = gs % NS, use = gs / NS;
-        if (use > 0) {                       // one lane polls the barrier, the warp follows
-          int ok = 1;
-          if (lane == 0) ok = mbar_wait(empty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT) ? 1 : 0;
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) { alive = false; break; }
-          tcgen05_fence_after();
-        }
-        const uint32_t tile = tmem_lane + uint32_t(slot * kWSlotCols);   // column k'/2 of this slot
-        if (QT == QTYPE_Q4_K) {
-          // stage = 64-weight group: low nibbles -> sub-block 2*st (k' 0..31), high -> 2*st+1 (k' 32..63)
-          const int sh = 16 * ls;
-          const float sc0 = float((qw[8] >> sh) & 0xff), sc1 = float((qw[8] >> (sh + 8)) & 0xff);
-          const float mn0 = float((qw[9] >> sh) & 0xff), mn1 = float((qw[9] >> (sh + 8)) & 0xff);
-          const V off = P::splat(P::kMagic);
-          const V s_lo = P::splat(dscale * sc0), a_lo = P::splat(-(dmin * mn0));
-          const V s_hi = P::splat(dscale * sc1), a_hi = P::splat(-(dmin * mn1));
-          uint32_t lo[8], hi[8];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            bytes_to_pairs<T>(qw[4 * ls + i] & 0x0f0f0f0fu, off, s_lo, a_lo, lo[2 * i], lo[2 * i + 1]);
-            bytes_to_pairs<T>((qw[4 * ls + i] >> 4) & 0x0f0f0f0fu, off, s_hi, a_hi, hi[2 * i], hi[2 * i + 1]);
-          }
-          tmem_st8(tile + 8 * lhalf, lo);            // k' = 16*lhalf .. +15
-          tmem_st8(tile + 16 + 8 * lhalf, hi);       // k' = 32 + 16*lhalf .. +15
-        } else {
-          // stage = (half block grp, quad pair ls): quads 2*ls (k' 0..31) and 2*ls+1 (k' 32..63)
-          const V off = P::splat(P::kMagic + 32.f);
-          const V zero = P::splat(0.f);
-#pragma unroll
-          for (int qo = 0; qo < 2; ++qo) {
-            const int quad = 2 * ls + qo;
-            const V s2 = P::splat(dscale * sub_scale[quad]);
-            uint32_t o[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint32_t l4 = (qw[4 * qo + i] >> (4 * ls)) & 0x0f0f0f0fu;
-              // the two high bits of quad q sit at bit 2q of the qh byte; they belong at bit 4
-              const uint32_t hs = quad == 0 ? qw[8 + i] << 4 : quad == 1 ? qw[8 + i] << 2 : quad == 2 ? qw[8 + i] : qw[8 + i] >> 2;
-              bytes_to_pairs<T>(l4 | (hs & 0x30303030u), off, s2, zero, o[2 * i], o[2 * i + 1]);
-            }
-            tmem_st8(tile + 16 * qo + 8 * lhalf, o);   // k' = 32*qo + 16*lhalf .. +15
-          }
-        }
-        tmem_st_wait();
-        tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full(slot));
-      }
-    }
-
-    // ------------------------------------------------------------------ epilogue
-    if (alive && nstage_total > 0 && mbar_wait(accbar, 0, abort_flag, p.status, ST_ACC_TIMEOUT)) {
       tcgen05_fence_after();
+      const int n0 = (t / p.m_tiles) * kRowsW, m0 = (t % p.m_tiles) * BM;
       const int n_row = n0 + row;
-      const float bias_v = (p.partial == nullptr && p.bias != nullptr && n_row < p.n) ? P::up(static_cast<const T*>(p.bias)[n_row]) : 0.f;
+      const bool whole = sb_b == 0 && sb_e == nsb;
+      const bool finishes = sb_e == nsb;            // this CTA stores the tile (after adding the others' partial sums)
+      int peer0 = cta;                              // first CTA with a piece of this tile; peers are peer0 .. cta-1
+      if (finishes && !whole) {
+        peer0 = unit_owner(static_cast<long long>(t) * nsb, p.units, ctas);
+        if (tid < cta - peer0) {
+          bool seen = false;
+          for (uint32_t i = 0; i < kFlagSpinLimit && !seen; ++i) {
+            seen = ld_acquire(p.flags + peer0 + tid) != 0;
+            if (!seen) __nanosleep(200);
+          }
+          if (!seen) { *abort_flag = 1; atomicCAS(p.status, 0, ST_PEER_TIMEOUT); }
+        }
+        if (!producer_sync()) return false;
+      }
+      const float bias_v = (finishes && p.bias != nullptr && n_row < p.n) ? P::up(static_cast<const T*>(p.bias)[n_row]) : 0.f;
       constexpr int kColsPerWarp = BM / 4;
 #pragma unroll 1
       for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
@@ -425,13 +393,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         uint32_t r[16];
         tmem_ld16(tmem_base + (uint32_t(32 * (warp & 3)) << 16) + uint32_t(col), r);
         tmem_ld_wait();
-        if (n_row < p.n) {
-          if (p.partial != nullptr) {
-            float* dst = p.partial + (int64_t(blockIdx.z) * p.m + m0 + col) * p.n + n_row;
+        if (!finishes) {
+          float* dst = p.partial + (static_cast<size_t>(cta) * BM + col) * kRowsW + row;     // tile-local [BM][128]
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (m0 + col + j < p.m) dst[int64_t(j) * p.n] = __uint_as_float(r[j]);
-          } else {
+          for (int j = 0; j < 16; ++j) dst[j * kRowsW] = __uint_as_float(r[j]);
+        } else {
+          for (int peer = peer0; peer < cta; ++peer) {
+            const float* src = p.partial + (static_cast<size_t>(peer) * BM + col) * kRowsW + row;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(src + j * kRowsW));
+          }
+          if (n_row < p.n) {
             T* dst = static_cast<T*>(p.out) + int64_t(m0 + col) * p.n + n_row;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
@@ -439,22 +411,162 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
           }
         }
       }
+      if (!finishes) {
+        __threadfence();                               // this thread's partial sums are visible device-wide ...
+        if (!producer_sync()) return false;
+        if (tid == 0) st_release(p.flags + cta, 1);    // ... before the flag is
+      } else if (!whole) {
+        if (!producer_sync()) return false;    // every thread has read the peers' tiles
+        if (tid < cta - peer0) p.flags[peer0 + tid] = 0;   // leave the flags clear for the next launch
+      }
       tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(accfree);             // the accumulator columns may be overwritten
+      return true;
+    };
+    int pend_t = -1, pend_b = 0, pend_e = 0;                    // segment whose epilogue has not run yet
+    for (int t = tile_hi; t >= tile_lo && alive; --t, ++segi) {
+      int sb_b, sb_e;
+      walk.segment(t, sb_b, sb_e);
+      for (int sb = sb_b; sb < sb_e && alive; ++sb, ++it) {
+        const int rslot = it % NSR;
+        {
+          int ok = 1;
+          if (lane == 0) ok = mbar_wait(rawfull(rslot), uint32_t(it / NSR) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) { alive = false; break; }
+        }
+        const uint8_t* rowbase = raw + rslot * kRawBytes + row * kPitch;
+        // ---- copy this thread's packed words to registers
+        uint32_t qw[12];
+        float dscale, dmin = 0.f;
+        float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3
+        if (QT == QTYPE_Q4_K) {
+          const uint4 hdr = *reinterpret_cast<const uint4*>(rowbase);
+          dscale = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
+          dmin = half_bits_to_float(uint16_t(hdr.x >> 16));
+          // sub-blocks 4*grp .. 4*grp+3 belong to this thread's two stages
+          const uint32_t scw = grp == 0 ? (hdr.y & 0x3f3f3f3fu) : ((hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4));
+          const uint32_t mnw = grp == 0 ? (hdr.z & 0x3f3f3f3fu) : (((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4));
+          qw[8] = scw;
+          qw[9] = mnw;
+#pragma unroll
+          for (int ls = 0; ls < 2; ++ls) {
+            const uint4 q = *reinterpret_cast<const uint4*>(rowbase + 16 + 64 * grp + 32 * ls + 16 * lhalf);
+            qw[4 * ls] = q.x; qw[4 * ls + 1] = q.y; qw[4 * ls + 2] = q.z; qw[4 * ls + 3] = q.w;
+          }
+          sub_scale[0] = sub_scale[1] = sub_scale[2] = sub_scale[3] = 0.f;
+        } else {
+          const int hb = grp;
+          uint32_t tail[8];                     // bytes 192..223 of the block: 16 int8 scales, then d
+          // rows are 16-byte multiples, so the block's phase inside its window is the same for every row
+          switch (((sb * kBlockBytes) & 15) >> 1) {
+            case 0: q6k_fetch<0>(rowbase, hb, lhalf, qw, tail); break;
+            case 1: q6k_fetch<1>(rowbase, hb, lhalf, qw, tail); break;
+            case 2: q6k_fetch<2>(rowbase, hb, lhalf, qw, tail); break;
+            case 3: q6k_fetch<3>(rowbase, hb, lhalf, qw, tail); break;
+            case 4: q6k_fetch<4>(rowbase, hb, lhalf, qw, tail); break;
+            case 5: q6k_fetch<5>(rowbase, hb, lhalf, qw, tail); break;
+            case 6: q6k_fetch<6>(rowbase, hb, lhalf, qw, tail); break;
+            default: q6k_fetch<7>(rowbase, hb, lhalf, qw, tail); break;
+          }
+          dscale = half_bits_to_float(uint16_t(tail[4] & 0xffffu));
+          // scale byte of quad i: 8*hb + 2*i + lhalf -> word 2*hb + i/2, byte 2*(i%2) + lhalf
+          const uint32_t sw0 = hb ? tail[2] : tail[0], sw1 = hb ? tail[3] : tail[1];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t wsel = i < 2 ? sw0 : sw1;
+            sub_scale[i] = float(int(int8_t(wsel >> (8 * (2 * (i & 1) + lhalf)))));
+          }
+        }
+        __syncwarp();                          // every lane holds its words: the ring slot may be refilled
+        if (lane == 0) mbar_arrive(rawfree(rslot));
+#pragma unroll
+        for (int ls = 0; ls < 2; ++ls) {
+          const int slot = 2 * grp + ls;       // stage ring slot = K stage inside the super-block
+          if (it > 0) {                        // one lane polls the barrier, the warp follows
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(empty(slot), uint32_t(it - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { alive = false; break; }
+            tcgen05_fence_after();
+          }
+          const uint32_t tile = tmem_lane + uint32_t(slot * kWSlotCols);   // column k'/2 of this slot
+          if (QT == QTYPE_Q4_K) {
+            // stage = 64-weight group: low nibbles -> sub-block 2*slot (k' 0..31), high -> 2*slot+1 (k' 32..63)
+            const int sh = 16 * ls;
+            const float sc0 = float((qw[8] >> sh) & 0xff), sc1 = float((qw[8] >> (sh + 8)) & 0xff);
+            const float mn0 = float((qw[9] >> sh) & 0xff), mn1 = float((qw[9] >> (sh + 8)) & 0xff);
+            const V off = P::splat(P::kMagic);
+            const V s_lo = P::splat(dscale * sc0), a_lo = P::splat(-(dmin * mn0));
+            const V s_hi = P::splat(dscale * sc1), a_hi = P::splat(-(dmin * mn1));
+            uint32_t lo[8], hi[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              bytes_to_pairs<T>(qw[4 * ls + i] & 0x0f0f0f0fu, off, s_lo, a_lo, lo[2 * i], lo[2 * i + 1]);
+              bytes_to_pairs<T>((qw[4 * ls + i] >> 4) & 0x0f0f0f0fu, off, s_hi, a_hi, hi[2 * i], hi[2 * i + 1]);
+            }
+            tmem_st8(tile + 8 * lhalf, lo);            // k' = 16*lhalf .. +15
+            tmem_st8(tile + 16 + 8 * lhalf, hi);       // k' = 32 + 16*lhalf .. +15
+          } else {
+            // stage = (half block grp, quad pair ls): quads 2*ls (k' 0..31) and 2*ls+1 (k' 32..63)
+            const V off = P::splat(P::kMagic + 32.f);
+            const V zero = P::splat(0.f);
+#pragma unroll
+            for (int qo = 0; qo < 2; ++qo) {
+              const int quad = 2 * ls + qo;
+              const V s2 = P::splat(dscale * sub_scale[quad]);
+              uint32_t o[8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t l4 = (qw[4 * qo + i] >> (4 * ls)) & 0x0f0f0f0fu;
+                // the two high bits of quad q sit at bit 2q of the qh byte; they belong at bit 4
+                const uint32_t hs = quad == 0 ? qw[8 + i] << 4 : quad == 1 ? qw[8 + i] << 2 : quad == 2 ? qw[8 + i] : qw[8 + i] >> 2;
+                bytes_to_pairs<T>(l4 | (hs & 0x30303030u), off, s2, zero, o[2 * i], o[2 * i + 1]);
+              }
+              tmem_st8(tile + 16 * qo + 8 * lhalf, o);   // k' = 32*qo + 16*lhalf .. +15
+            }
+          }
+          tmem_st_wait();
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(full(slot));
+        }
+        if (!alive) break;
+        // The previous segment's epilogue runs only now, after the first super-block of this segment has been unpacked:
+        // the MMA warp finds its next weight tiles ready the moment the accumulator is handed back.
+        if (sb == sb_b && pend_t >= 0) {
+          if (!epilogue(pend_t, pend_b, pend_e, segi - 1)) { alive = false; break; }
+          pend_t = -1;
+        }
+      }
+      if (!alive) break;
+      pend_t = t; pend_b = sb_b; pend_e = sb_e;
     }
+    if (alive && pend_t >= 0) epilogue(pend_t, pend_b, pend_e, segi - 1);
   } else if (warp == 16) {
     // ------------------------------------------------------------------ activation TMA
     // The three control warps stay converged: every lane runs the loop and polls the barriers, one elected lane issues
     // the asynchronous instructions.  Inside a divergent `if (lane == 0)` region the compiler cannot keep descriptors,
     // coordinates and barrier addresses in uniform registers, and each tcgen05.mma / bulk copy then costs tens of cycles
     // of register shuffling on the one thread the whole pipeline waits for.
-    for (int gs = 0; gs < nstage_total; ++gs) {
-      const int slot = gs % NS, use = gs / NS;
-      if (use > 0 && !warp_wait(empty(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
-      if (elect_one()) {
-        mbar_arrive_expect_tx(full(slot), uint32_t(kXTile));
-        tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, full(slot), sb0 * 256 + gs * kBK, m0);
+    int it = 0;
+    bool ok = true;
+    for (int t = tile_hi; t >= tile_lo && ok; --t) {
+      int sb_b, sb_e;
+      walk.segment(t, sb_b, sb_e);
+      const int m0 = (t % p.m_tiles) * BM;
+      for (int sb = sb_b; sb < sb_e && ok; ++sb, ++it) {
+#pragma unroll
+        for (int slot = 0; slot < NS; ++slot) {
+          if (it > 0 && !warp_wait(empty(slot), uint32_t(it - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) { ok = false; break; }
+          if (elect_one()) {
+            mbar_arrive_expect_tx(full(slot), uint32_t(kXTile));
+            tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, full(slot), sb * 256 + slot * kBK, m0);
+          }
+          __syncwarp();
+        }
       }
-      __syncwarp();
     }
     // Aborting: up to NS activation copies may still be writing shared memory, and their barrier also counts producer
     // arrivals that will never come, so it cannot be waited on.  A copy of this size lands within microseconds; give
@@ -463,46 +575,62 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
       for (int i = 0; i < 1000; ++i) __nanosleep(1000);
   } else if (warp == 18) {
     // ------------------------------------------------------------------ packed-weight TMA
-    int issued = 0;
-    for (int ri = 0; ri < sb1 - sb0; ++ri) {
-      const int slot = ri % NSR, use = ri / NSR;
-      if (use > 0 && !warp_wait(rawfree(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) break;
-      if (elect_one()) {
-        mbar_arrive_expect_tx(rawfull(slot), uint32_t(kRawBytes));
-        // x coordinate = block start rounded down to 16 bytes; rows past N and bytes past the row end read as zero
-        tma_load_2d(smem_u32(raw + slot * kRawBytes), &w_map, rawfull(slot), ((sb0 + ri) * kBlockBytes) & ~15, n0);
+    int it = 0;
+    bool ok = true;
+    for (int t = tile_hi; t >= tile_lo && ok; --t) {
+      int sb_b, sb_e;
+      walk.segment(t, sb_b, sb_e);
+      const int n0 = (t / p.m_tiles) * kRowsW;
+      for (int sb = sb_b; sb < sb_e; ++sb, ++it) {
+        const int slot = it % NSR, use = it / NSR;
+        if (use > 0 && !warp_wait(rawfree(slot), uint32_t(use - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) { ok = false; break; }
+        if (elect_one()) {
+          mbar_arrive_expect_tx(rawfull(slot), uint32_t(kRawBytes));
+          // x coordinate = block start rounded down to 16 bytes; rows past N and bytes past the row end read as zero
+          tma_load_2d(smem_u32(raw + slot * kRawBytes), &w_map, rawfull(slot), (sb * kBlockBytes) & ~15, n0);
+        }
+        __syncwarp();
       }
-      __syncwarp();
-      issued = ri + 1;
     }
     if (*abort_flag) {
-      for (int ri = max(0, issued - NSR); ri < issued; ++ri) mbar_wait_plain(rawfull(ri % NSR), uint32_t(ri / NSR) & 1u);
+      for (int i = max(0, it - NSR); i < it; ++i) mbar_wait_plain(rawfull(i % NSR), uint32_t(i / NSR) & 1u);
     }
   } else {
     // ------------------------------------------------------------------ MMA issue
     bool ok = true;
-    for (int gs = 0; gs < nstage_total; ++gs) {
-      const int slot = gs % NS;
-      ok = warp_wait(full(slot), uint32_t(gs / NS) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
-      if (!ok) break;
-      tcgen05_fence_after();
-      const uint32_t a_tmem = tmem_base + uint32_t(BM + slot * kWSlotCols);
-      const uint64_t db = smem_desc_sw128(smem_u32(xtiles + slot * kXTile));
-      if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < kBK / 16; ++kk)      // 16 K values = 8 TMEM columns of A, 32 bytes of each B row
-          umma_f16_ts(tmem_base, a_tmem + uint32_t(8 * kk), db + uint64_t(2 * kk), kIdesc, (gs > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(empty(slot));
+    const uint64_t db0 = smem_desc_sw128(smem_u32(xtiles));
+    int it = 0, segi = 0;
+    for (int t = tile_hi; t >= tile_lo && ok; --t, ++segi) {
+      int sb_b, sb_e;
+      walk.segment(t, sb_b, sb_e);
+      if (segi > 0) {                        // the previous segment's accumulator has been read out
+        ok = warp_wait(accfree, uint32_t(segi - 1) & 1u, abort_flag, p.status, ST_ACC_TIMEOUT);
+        if (!ok) break;
+        tcgen05_fence_after();
       }
+      // one super-block = NS stages per trip: slot numbers, TMEM columns and descriptor offsets are compile-time constants
+      for (int sb = sb_b; sb < sb_e && ok; ++sb, ++it) {
+#pragma unroll
+        for (int slot = 0; slot < NS; ++slot) {
+          ok = warp_wait(full(slot), uint32_t(it) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
+          if (!ok) break;
+          tcgen05_fence_after();
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk)      // 16 K values = 8 TMEM columns of A, 32 bytes of each B row
+              umma_f16_ts(tmem_base, tmem_base + uint32_t(BM + slot * kWSlotCols + 8 * kk), db0 + uint64_t((slot * kXTile) >> 4) + uint64_t(2 * kk),
+                          kIdesc, (sb > sb_b || slot > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(empty(slot));
+          }
+          __syncwarp();
+        }
+      }
+      if (ok && elect_one()) umma_commit(accbar);
       __syncwarp();
     }
-    if (nstage_total > 0 && elect_one()) {
-      if (ok) {
-        umma_commit(accbar);
-      } else {                         // aborting: let every MMA already issued finish before TMEM is freed
-        umma_commit(drainbar);
-        mbar_wait_plain(drainbar, 0);
-      }
+    if (!ok && has_work && elect_one()) {   // aborting: let every MMA already issued finish before TMEM is freed
+      umma_commit(drainbar);
+      mbar_wait_plain(drainbar, 0);
     }
     __syncwarp();
   }
@@ -513,26 +641,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
-}
-
-// Split-K finish: out[m,n] = sum_z partial[z,m,n] + bias[n], converted to the activation dtype.
-template <typename T>
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, const T* __restrict__ bias, T* __restrict__ out, int64_t mn,
-                                     int n, int splits) {
-  const int64_t i = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
-  if (i >= mn) return;   // mn % 4 == 0 because n % 4 == 0 is required by the launcher
-  float4 acc = *reinterpret_cast<const float4*>(partial + i);
-  for (int z = 1; z < splits; ++z) {
-    const float4 v = *reinterpret_cast<const float4*>(partial + int64_t(z) * mn + i);
-    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-  }
-  if (bias != nullptr) {
-    const int col = int(i % n);
-    acc.x += Pair<T>::up(bias[col]); acc.y += Pair<T>::up(bias[col + 1]);
-    acc.z += Pair<T>::up(bias[col + 2]); acc.w += Pair<T>::up(bias[col + 3]);
-  }
-  T* o = out + i;
-  o[0] = Pair<T>::cvt(acc.x); o[1] = Pair<T>::cvt(acc.y); o[2] = Pair<T>::cvt(acc.z); o[3] = Pair<T>::cvt(acc.w);
 }
 
 // ---------------------------------------------------------------------------------------- host side
@@ -550,8 +658,10 @@ static EncodeTiledFn encode_tiled() {
   return fn;
 }
 
+constexpr int kMaxCtas = 1024;      // flag words per device; the grid never exceeds the SM count
+
 struct DeviceState {
-  int* status = nullptr;
+  int* status = nullptr;            // [0] = status word, [1 .. kMaxCtas] = partial-tile flags
   float* workspace = nullptr;
   size_t workspace_bytes = 0;
 };
@@ -564,8 +674,8 @@ static DeviceState* device_state(size_t need_workspace) {
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceState& st = g_state[dev];
   if (st.status == nullptr) {
-    if (cudaMalloc(&st.status, sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(st.status, 0, sizeof(int));
+    if (cudaMalloc(&st.status, sizeof(int) * (1 + kMaxCtas)) != cudaSuccess) return nullptr;
+    cudaMemset(st.status, 0, sizeof(int) * (1 + kMaxCtas));
   }
   if (need_workspace > st.workspace_bytes) {
     // Grown outside of stream capture only: callers warm a shape up once before capturing a graph.
@@ -576,26 +686,31 @@ static DeviceState* device_state(size_t need_workspace) {
   return &st;
 }
 
-struct Plan { int bm, splits, sb_per_split; };
+// Tile shape and stream-K grid of one problem.
+struct Plan {
+  int bm, m_tiles, ctas;
+  long long units;
+  size_t workspace_bytes;     // fp32 partial tiles, one per CTA; 0 when every CTA range ends on a tile boundary
+};
 
 static Plan make_plan(int m, int n, int k) {
   Plan pl;
   pl.bm = m <= 64 ? 64 : m <= 128 ? 128 : 256;
-  const int tiles = ((m + pl.bm - 1) / pl.bm) * ((n + kRowsW - 1) / kRowsW);
+  pl.m_tiles = (m + pl.bm - 1) / pl.bm;
+  const long long tiles = static_cast<long long>(pl.m_tiles) * ((n + kRowsW - 1) / kRowsW);
   const int nsb = k / 256;
+  pl.units = tiles * nsb;
   int sm_count = 148;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  int splits = 1;
-  while (splits < 8 && tiles * splits * 2 <= sm_count && nsb / (splits * 2) >= 4) splits *= 2;
-  if (n % 4) splits = 1;   // the reduce kernel works on float4
-  pl.sb_per_split = (nsb + splits - 1) / splits;
-  pl.splits = (nsb + pl.sb_per_split - 1) / pl.sb_per_split;
+  if (sm_count > kMaxCtas) sm_count = kMaxCtas;
+  pl.ctas = int(pl.units < sm_count ? pl.units : sm_count);
+  pl.workspace_bytes = tiles % pl.ctas == 0 ? 0 : size_t(pl.ctas) * pl.bm * kRowsW * sizeof(float);
   return pl;
 }
 
-// Where a launch finds its split-K workspace and status word.
-struct Scratch { float* workspace; int* status; };
+// Where a launch finds its partial-tile workspace, flags and status word.
+struct Scratch { float* workspace; int* flags; int* status; };
 
 template <int QT, typename T, int BM>
 static int launch(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const Plan& pl, Scratch sc,
@@ -632,30 +747,22 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
   Params p;
   p.bias = bias;
   p.out = c;
-  p.partial = pl.splits > 1 ? sc.workspace : nullptr;
+  p.partial = sc.workspace;
+  p.flags = sc.flags;
   p.status = sc.status;
   p.m = m; p.n = n; p.k = k;
-  p.sb_per_split = pl.sb_per_split;
-  const dim3 grid((m + BM - 1) / BM, (n + kRowsW - 1) / kRowsW, pl.splits);
-  kern<<<grid, kThreads, smem, s>>>(x_map, w_map, p);
-  if (cudaGetLastError() != cudaSuccess) return RC_LAUNCH;
-  if (pl.splits > 1) {
-    const int64_t mn = int64_t(m) * n;
-    const int threads = 256;
-    const int64_t blocks = (mn / 4 + threads - 1) / threads;
-    splitk_reduce_kernel<T><<<unsigned(blocks), threads, 0, s>>>(sc.workspace, static_cast<const T*>(bias), static_cast<T*>(c), mn, n,
-                                                                 pl.splits);
-    if (cudaGetLastError() != cudaSuccess) return RC_LAUNCH;
-  }
-  return RC_OK;
+  p.m_tiles = pl.m_tiles;
+  p.units = pl.units;
+  kern<<<pl.ctas, kThreads, smem, s>>>(x_map, w_map, p);
+  return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
 // ---- allocation-free scratch -------------------------------------------------------------------
-// Split-K workspace and status word that live in the library's own device image instead of cudaMalloc'ed
+// Partial-tile workspace, flags and status word that live in the library's own device image instead of cudaMalloc'ed
 // memory.  Every GPU that loads the library carries these 16 MiB until the process exits.
 constexpr size_t kStaticScratchBytes = size_t(16) << 20;
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
-static __device__ int g_static_status;
+static __device__ int g_static_status[1 + kMaxCtas];     // zero-initialised like any static device array
 
 constexpr int kMaxDevices = 64;
 struct StaticScratch { float* workspace = nullptr; int* status = nullptr; bool ready = false; };
@@ -679,22 +786,23 @@ static int static_scratch(Scratch* out) {
   }
   out->workspace = st.workspace;
   out->status = st.status;
+  out->flags = st.status + 1;
   return RC_OK;
 }
 
 template <int QT, typename T>
 static int launch_bm(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, bool use_static, cudaStream_t s) {
   const Plan pl = make_plan(m, n, k);
-  const size_t ws = pl.splits > 1 ? size_t(pl.splits) * m * n * sizeof(float) : 0;
-  Scratch sc{nullptr, nullptr};
+  Scratch sc{nullptr, nullptr, nullptr};
   if (use_static) {
-    if (ws > kStaticScratchBytes) return RC_RANGE;
+    if (pl.workspace_bytes > kStaticScratchBytes) return RC_RANGE;
     if (int rc = static_scratch(&sc)) return rc;
   } else {
-    DeviceState* st = device_state(ws);
+    DeviceState* st = device_state(pl.workspace_bytes);
     if (st == nullptr) return RC_LAUNCH;
     sc.workspace = st->workspace;
     sc.status = st->status;
+    sc.flags = st->status + 1;
   }
   switch (pl.bm) {
     case 64: return launch<QT, T, 64>(a, b, bias, c, m, n, k, pl, sc, s);
@@ -714,8 +822,7 @@ bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k) {
 
 size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k) {
   if (!gemm_umma_supports(qtype, dtype, m, n, k)) return 0;
-  const umma::Plan pl = umma::make_plan(m, n, k);
-  return pl.splits > 1 ? size_t(pl.splits) * m * n * sizeof(float) : 0;
+  return umma::make_plan(m, n, k).workspace_bytes;
 }
 
 static int gemm_rcr_umma_impl(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
@@ -746,7 +853,8 @@ int gemm_rcr_umma_static(const void* a, const void* b, const void* bias, void* c
 }
 size_t gemm_umma_static_scratch_bytes() { return umma::kStaticScratchBytes; }
 
-// Reads (and clears) the device status word the bounded waits write; 0 = no wait ever gave up.
+// Reads (and clears) the device status word the bounded waits write; 0 = no wait ever gave up.  A launch that gave up
+// may have left partial-tile flags raised, so they are cleared with the word.
 int umma_device_status() {
   int dev = 0, value = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
@@ -754,11 +862,11 @@ int umma_device_status() {
   auto it = umma::g_state.find(dev);
   if (it != umma::g_state.end() && it->second.status != nullptr) {
     if (cudaMemcpy(&value, it->second.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (value != 0) cudaMemset(it->second.status, 0, sizeof(int));
+    if (value != 0) cudaMemset(it->second.status, 0, sizeof(int) * (1 + umma::kMaxCtas));
   }
   if (value == 0 && dev >= 0 && dev < umma::kMaxDevices && umma::g_static[dev].ready) {   // the static-scratch path's word
     if (cudaMemcpy(&value, umma::g_static[dev].status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (value != 0) cudaMemset(umma::g_static[dev].status, 0, sizeof(int));
+    if (value != 0) cudaMemset(umma::g_static[dev].status, 0, sizeof(int) * (1 + umma::kMaxCtas));
   }
   return value;
 }

@@ -80,21 +80,23 @@ DINOML_B200_API int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m
  * inside a host that has already handed every byte of HBM to its own arena (so cudaMalloc would fail), or a serving
  * loop that bans cudaMalloc / cudaFree on its hot path because they can stall the whole device.  It is the tensor-core
  * GEMM of dinoml_b200_gguf_gemm_rcr(variant = UMMA) - same shapes (m >= 17, Q4_K / Q6_K, float16 / bfloat16), same
- * arguments minus `variant`, same results - except that its split-K partial sums and its status word live in a
- * 16 MiB array that is part of the library image on every GPU that loads it (dinoml_b200_gguf_prealloc_scratch_bytes()),
+ * arguments minus `variant`, same results - except that its partial tiles (fp32 sums of K ranges that the kernel's
+ * stream-K work split cut between SMs) and its flag / status words live in a 16 MiB array plus a 4 KiB one that is part of the library image on every GPU that loads it (dinoml_b200_gguf_prealloc_scratch_bytes()),
  * and that it calls no cudaMalloc, cudaFree or allocating library routine.  The caller still provides a, b_quant,
  * bias and c.  A problem whose partial sums do not fit is refused with code 8 and a message naming both sizes.
  * The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device current); make
  * that first call before starting any stream capture.  All calls on a device share the one array: the kernel
- * overwrites the part it uses before reading it back, so nothing needs clearing between calls, but two calls that
- * overlap on the GPU (different streams, no dependency) race on it - serialize them. */
+ * overwrites the part it uses before reading it back and lowers every flag it raised, so nothing needs clearing
+ * between calls, but two calls that overlap on the GPU (different streams, no dependency) race on it - serialize
+ * them. */
 DINOML_B200_API int dinoml_b200_gguf_gemm_rcr_prealloc(const void* a, const void* b_quant, const void* bias, void* c, int qtype,
                                                        int dtype, int m, int n, int k, void* stream);
 DINOML_B200_API size_t dinoml_b200_gguf_prealloc_scratch_bytes(void);
 
 /* The tcgen05 kernel bounds every barrier wait; a wait that gives up records a code in a per-device
  * status word instead of hanging or trapping.  Synchronizes the device, returns the word (0 = never
- * happened; 1 / 2 / 3 = a stage-free / stage-ready / accumulator wait gave up; < 0 = CUDA error) and clears it.
+ * happened; 1 / 2 / 3 / 4 = a stage-free / stage-ready / accumulator / partial-tile wait gave up; < 0 = CUDA error) and
+ * clears it together with the partial-tile flags.
  * No counterpart in the reference. */
 DINOML_B200_API int dinoml_b200_gguf_device_status(void);
 

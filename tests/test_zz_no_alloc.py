@@ -53,7 +53,7 @@ def _run_pair(lib, qtype, m, n, k, seed, bias):
 def test_prealloc_entry_matches_regular_entry_twice_in_a_row():
     lib = _entry_points()
     assert lib.dinoml_b200_gguf_prealloc_scratch_bytes() == 16 << 20
-    # both shapes take the split-K route (few output tiles, long K), i.e. they really use the scratch
+    # both shapes have few output tiles and a long K, so their tiles are cut between SMs: they really use the scratch
     first = _run_pair(lib, "Q4_K", 96, 256, 4096, 31, bias=False)
     second = _run_pair(lib, "Q6_K", 40, 384, 8192, 47, bias=True)
     assert first == 0.0 and second == 0.0            # identical kernel and summation order
@@ -62,13 +62,15 @@ def test_prealloc_entry_matches_regular_entry_twice_in_a_row():
 def test_prealloc_entry_refuses_problems_beyond_its_scratch():
     lib = _entry_points()
     dev = torch.device("cuda:0")
-    m, n, k = 512, 4608, 2048                         # 2 K-splits x 512 x 4608 fp32 partials = 18.9 MB > 16 MiB
+    m, n, k = 512, 4608, 2048                         # one 256 x 128 fp32 partial tile per SM: 148 x 128 KiB > 16 MiB
     w = torch.from_numpy(S.random_blocks("Q4_K", n, k, 5)).to(dev)
     x = torch.zeros(m, k, device=dev, dtype=torch.bfloat16)
     y = torch.zeros(m, n, device=dev, dtype=torch.bfloat16)
     rc = lib.dinoml_b200_gguf_gemm_rcr_prealloc(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), 12, BF16, m, n, k, None)
     assert rc == 8
     msg = _native.last_error()
-    assert "18874368" in msg and str(16 << 20) in msg, msg
+    lib.dinoml_b200_gguf_gemm_rcr_workspace.restype = ctypes.c_size_t
+    need = lib.dinoml_b200_gguf_gemm_rcr_workspace(12, BF16, m, n, k, UMMA)
+    assert need > (16 << 20) and str(need) in msg and str(16 << 20) in msg, msg
     # small-M problems belong to the GEMV kernels, not to this entry point
     assert lib.dinoml_b200_gguf_gemm_rcr_prealloc(x.data_ptr(), w.data_ptr(), None, y.data_ptr(), 12, BF16, 4, n, k, None) != 0
