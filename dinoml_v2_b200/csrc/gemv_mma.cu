@@ -1,4 +1,5 @@
-// Fused GGUF decode GEMV ("mma" variant), M = 1..16, float16 / bfloat16 activations, Q4_K weights.
+// Fused GGUF decode GEMV ("mma" variant), M = 1..16, float16 / bfloat16 activations, Q4_K weights (the Q6_K kernel
+// is in gemv_q6k_mma.cu; the variant's dispatch is at the end of this file).
 //
 // C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias) with W streamed once from HBM as packed GGUF blocks.
 // HBM-bound: the algorithmic traffic is the packed weight bytes (144 B per 256 weights).
@@ -28,56 +29,13 @@
 // Behavioural ancestor in the reference: the small-M "wave" kernels of the fused prototype
 // (kernels/rocm/src/ck_gguf_q8_gemm.hip:1009-1166); the reference's CUDA path instead dequantizes the
 // whole weight and runs a dense Sm80 GEMM (src/dinoml/lowering/ops/gemm.py:729-749).
-#include "gguf_common.cuh"
+#include "gemv_mma_common.cuh"
 
 namespace b200gguf {
 
 int check_gemm_args(const void* a, const void* b, const void* c, int qtype, int dtype, int m, int n, int k);
-
-template <typename T> struct MmaType;
-template <> struct MmaType<__nv_bfloat16> {
-  static constexpr uint32_t kMagicBytes = 0x43434343u;  // bf16 0x43qq = 128 + q
-  static constexpr float kMagic = 128.f;                // offset left in the MMA operand
-  static __device__ __forceinline__ uint32_t fix(uint32_t pair) { return pair; }
-  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-  static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
-  static __device__ __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
-  static __device__ __forceinline__ float sum8(const uint4& v) {
-    const uint32_t r[4] = {v.x, v.y, v.z, v.w};
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) s += __uint_as_float(r[i] << 16) + __uint_as_float(r[i] & 0xffff0000u);
-    return s;
-  }
-};
-template <> struct MmaType<__half> {
-  static constexpr uint32_t kMagicBytes = 0x64646464u;  // fp16 0x64qq = 1024 + q ...
-  static constexpr float kMagic = 0.f;                  // ... and the 1024 is removed exactly before the MMA
-  static __device__ __forceinline__ uint32_t fix(uint32_t pair) {
-    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&pair), __half2half2(__ushort_as_half(0x6400)));
-    return *reinterpret_cast<const uint32_t*>(&v);
-  }
-  static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-  }
-  static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
-  static __device__ __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
-  static __device__ __forceinline__ float sum8(const uint4& v) {
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); s += f.x + f.y; }
-    return s;
-  }
-};
+bool gemv_q6k_mma_supports(int dtype, int m, int k);
+int gemv_q6k_mma(const void* a, const void* b, const void* bias, void* c, int dtype, int m, int n, int k, cudaStream_t s);
 
 constexpr int kGemvWarps = 4;
 constexpr int kGemvThreads = kGemvWarps * 32;
@@ -87,23 +45,12 @@ constexpr int kRowChunks = kStageSb * 9;                 // 16-byte chunks per r
 constexpr int kRowPitch = kStageSb * 144 + 32;           // 608 B: 8-byte reads of 8 rows x 4 lanes hit 32 banks
 constexpr int kStageBytes = kGemvRows * kRowPitch;       // 9728 B per stage slot
 
-// Byte -> float without I2F: 0x4B0000bb is 2^23 + bb.
-__device__ __forceinline__ float byte_to_float(uint32_t word, int i) {
-  return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650 + i)) - 8388608.f;
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
 // MXC: activation rows covered (power of two >= m).  NW: warps per CTA (4 or 8); each group of 4 warps walks its own
 // sequence of K-stages (group p takes stages p, p + NW/4, ...), so an 8-warp CTA unpacks two stages at a time.
 // NSTAGE: shared-memory stage slots.  Dynamic shared memory: weight stages, then X[MXC][k/32] floats.
 template <typename T, int MXC, int NW, int NSTAGE>
-__global__ void __launch_bounds__(NW * 32)
+// 3 resident CTAs per SM for the 8-warp configuration: measured best for the 11008 x 4096 decode shape (688 CTAs)
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1)
 gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias,
                     T* __restrict__ y, int m, int n, int k) {
   using MT = MmaType<T>;
@@ -127,7 +74,12 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   const int g = lane >> 2, t = lane & 3;
   const int r_base = blockIdx.x * kGemvRows;
   const int nsb = k >> 8, nsub = k >> 5;
-  const int nstages = (nsb + kStageSb - 1) / kStageSb;
+  const int nstages_all = (nsb + kStageSb - 1) / kStageSb;
+  // K slice of this CTA (grid.y = cluster size = slices per row tile)
+  const int ks = gridDim.y, kr = ks > 1 ? int(cluster_rank()) : 0;
+  const int per_slice = (nstages_all + ks - 1) / ks;
+  const int s_first = kr * per_slice;
+  const int nstages = max(0, min(nstages_all, s_first + per_slice) - s_first);
   const int niter = (nstages + SPI - 1) / SPI;
   const int64_t row_bytes = int64_t(nsb) * 144;
   const uint32_t sW_u32 = uint32_t(__cvta_generic_to_shared(sW));
@@ -137,11 +89,12 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   const int cp_row = gtid >> 3, cp_c0 = gtid & 7;
   const uint8_t* cp_src = w + int64_t(min(r_base + cp_row, n - 1)) * row_bytes + cp_c0 * 16;
   const uint32_t cp_dst = sW_u32 + cp_row * kRowPitch + cp_c0 * 16;
-  auto issue_stage = [&](int s) {
-    if (s < nstages) {
+  auto issue_stage = [&](int ls) {                                     // ls: stage index inside this CTA's slice
+    if (ls < nstages) {
+      const int s = s_first + ls;
       const int valid_chunks = min(kStageSb, nsb - s * kStageSb) * 9;
       const uint8_t* src = cp_src + int64_t(s) * (kStageSb * 144);
-      const uint32_t dst = cp_dst + (s % NSTAGE) * kStageBytes;
+      const uint32_t dst = cp_dst + (ls % NSTAGE) * kStageBytes;
 #pragma unroll
       for (int j = 0; j < 5; ++j)
         if (cp_c0 + 8 * j < valid_chunks) cp_async16(dst + 128 * j, src + 128 * j);
@@ -155,9 +108,11 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
-  // X[c][j] = sum of activations of row c over sub-block j (rows >= m are zero).
-  for (int idx = tid; idx < nsub * MXC; idx += NW * 32) {
-    const int c = idx / nsub, j = idx - c * nsub;
+  // X[c][j] = sum of activations of row c over sub-block j (rows >= m are zero), for the sub-blocks of this K slice.
+  const int j_first = s_first * (kStageSb * 8), j_count = min(nsub - j_first, nstages * (kStageSb * 8));
+  for (int i = tid; i < j_count * MXC; i += NW * 32) {
+    const int c = i / j_count, j = j_first + (i - c * j_count);
+    const int idx = c * nsub + j;
     float s = 0.f;
     if (c < m) {
       const uint4* px = reinterpret_cast<const uint4*>(x + int64_t(c) * k + int64_t(j) * 32);
@@ -185,10 +140,10 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
     cp_async_wait<D - 2>();
     __syncthreads();                       // this iteration's stages landed; the previous ones are fully consumed
     if (it > 0) issue_stage((it - 1 + D) * SPI + grp); else cp_async_commit();
-    const int s = it * SPI + grp;
-    const int sb = s * kStageSb + wq;
-    if (s < nstages && sb < nsb) {
-      const uint8_t* st = sW + (s % NSTAGE) * kStageBytes + wq * 144;
+    const int ls = it * SPI + grp;
+    const int sb = (s_first + ls) * kStageSb + wq;
+    if (ls < nstages && sb < nsb) {
+      const uint8_t* st = sW + (ls % NSTAGE) * kStageBytes + wq * 144;
       {  // lane pair (srow, shalf): 4 sub-block scales -> ds to shared memory, min/MAGIC term folded against X
         const uint4 hdr = *reinterpret_cast<const uint4*>(st + srow * kRowPitch);
         const float d = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
@@ -270,21 +225,31 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
 #pragma unroll
   for (int c = 0; c < MXC; ++c) sXt[warp][srow][shalf][c] = xt[c];
   __syncthreads();
+  __shared__ float sOut[kGemvRows * MXC];  // this CTA's sums; read by the rank-0 CTA of the cluster when K is sliced
   for (int idx = tid; idx < kGemvRows * MXC; idx += NW * 32) {
     const int r = idx & (kGemvRows - 1), c = idx >> 4;
-    const int row = r_base + r;
-    if (row < n && c < m) {
-      float v = 0.f, xs = 0.f;
+    float v = 0.f, xs = 0.f;
 #pragma unroll
-      for (int wv = 0; wv < NW; ++wv) {
-        v += sRed[wv][r][c];
-        xs += sXt[wv][r][0][c] + sXt[wv][r][1][c];
+    for (int wv = 0; wv < NW; ++wv) {
+      v += sRed[wv][r][c];
+      xs += sXt[wv][r][0][c] + sXt[wv][r][1][c];
+    }
+    sOut[idx] = v - xs;
+  }
+  if (ks > 1) cluster_barrier(); else __syncthreads();
+  if (kr == 0) {
+    for (int idx = tid; idx < kGemvRows * MXC; idx += NW * 32) {
+      const int r = idx & (kGemvRows - 1), c = idx >> 4;
+      const int row = r_base + r;
+      if (row < n && c < m) {
+        float v = sOut[idx];
+        for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
+        if (bias != nullptr) v += MT::to_float(bias[row]);
+        y[int64_t(c) * n + row] = MT::from_float(v);
       }
-      v -= xs;
-      if (bias != nullptr) v += MT::to_float(bias[row]);
-      y[int64_t(c) * n + row] = MT::from_float(v);
     }
   }
+  if (ks > 1) cluster_barrier();           // peers keep their shared memory alive until rank 0 has read it
 }
 
 template <typename T, int MXC, int NW, int NSTAGE>
@@ -298,18 +263,9 @@ static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
     opted_in = smem;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles);
-  cfg.blockDim = dim3(NW * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
-                                             static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
+  const int ks = gemv_k_slices(tiles, ((k >> 8) + kStageSb - 1) / kStageSb, NSTAGE);
+  const cudaError_t err = gemv_launch(kern, tiles, ks, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
+                                      static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
@@ -331,9 +287,10 @@ static int launch_q4k(const void* a, const void* b, const void* bias, void* c, i
   return launch_q4k_m<T, 16>(a, b, bias, c, m, n, k, s);
 }
 
-// Which (qtype, dtype, m) the mma variant covers.
+// Which (qtype, dtype, m, k) the mma variant covers.
 bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k) {
   (void)n;
+  if (qtype == QTYPE_Q6_K) return gemv_q6k_mma_supports(dtype, m, k);
   return qtype == QTYPE_Q4_K && (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 16 && k % 256 == 0;
 }
 
@@ -342,8 +299,10 @@ int gemm_rcr_mma(const void* a, const void* b, const void* bias, void* c, int qt
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (m > 16) return RC_RANGE;
-  if (!gemv_mma_supports(qtype, dtype, m, n, k)) return RC_QTYPE;
-  if (reinterpret_cast<uintptr_t>(b) & 15) return RC_ALIGN;  // 16-byte cp.async sources
+  if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
+  if (!gemv_mma_supports(qtype, dtype, m, n, k)) return RC_ALIGN;   // Q6_K rows that are not 16-byte multiples
+  if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;  // 16-byte cp.async sources, vector loads
+  if (qtype == QTYPE_Q6_K) return gemv_q6k_mma(a, b, bias, c, dtype, m, n, k, s);
   return dtype == DINO_BF16 ? launch_q4k<__nv_bfloat16>(a, b, bias, c, m, n, k, s)
                             : launch_q4k<__half>(a, b, bias, c, m, n, k, s);
 }

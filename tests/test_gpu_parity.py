@@ -122,6 +122,28 @@ def test_gemv_mma_q4k(dev, dtype):
         _check(y, ref, dtype, ("mma", m, n, k))
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_gemv_mma_q6k(dev, dtype):
+    """Q6_K decode GEMV on mma.sync: K % 2048 == 0 (16-byte rows); ragged N, every M bucket, odd and even blocks."""
+    for (m, n, k) in [(1, 16, 2048), (1, 1000, 4096), (2, 50, 2048), (3, 129, 6144), (4, 128, 4096), (7, 33, 2048), (8, 64, 8192),
+                      (9, 48, 2048), (13, 17, 4096), (16, 160, 4096)]:
+        blocks = S.random_blocks("Q6_K", n, k, seed=520 + m + n)
+        x, xf = _activations(m, k, 620 + m, dtype, dev)
+        ref = oracle.gemm_quant(xf, blocks, "Q6_K", n, k)
+        assert kernels.select_variant("Q6_K", dtype, m, n, k) == "mma"
+        y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), "Q6_K", variant="mma")
+        got = y.float().cpu().numpy()
+        _, rel, norm = oracle.max_errors(ref, got)
+        bound = 4e-3 if dtype == "bfloat16" else 6e-4     # output rounding of bf16 (2^-9) / fp16 (2^-11)
+        assert norm <= bound, (dtype, m, n, k, rel, norm)
+        _check(y, ref, dtype, ("mma q6k", m, n, k))
+    # rows that are not 16-byte multiples stay with the simt variant
+    assert kernels.select_variant("Q6_K", dtype, 1, 64, 1024) == "simt"
+    with pytest.raises(RuntimeError, match="alignment"):
+        kernels.gemm_rcr(torch.zeros(1, 1024, device=dev, dtype=TDT[dtype]),
+                         torch.from_numpy(S.random_blocks("Q6_K", 64, 1024, seed=1)).to(dev), "Q6_K", variant="mma")
+
+
 UMMA_SHAPES = [  # (m, n, k)
     (17, 128, 256), (64, 256, 512), (100, 200, 1024), (128, 384, 768), (200, 130, 512), (256, 128, 2048),
     (300, 512, 4096), (513, 256, 1024), (150, 256, 6144),
