@@ -48,9 +48,9 @@ constexpr int kStageBytes = kGemvRows * kRowPitch;       // 9728 B per stage slo
 // MXC: activation rows covered (power of two >= m).  NW: warps per CTA (4 or 8); each group of 4 warps walks its own
 // sequence of K-stages (group p takes stages p, p + NW/4, ...), so an 8-warp CTA unpacks two stages at a time.
 // NSTAGE: shared-memory stage slots.  Dynamic shared memory: weight stages, then X[MXC][k/32] floats.
-template <typename T, int MXC, int NW, int NSTAGE>
-// 3 resident CTAs per SM for the 8-warp configuration: measured best for the 11008 x 4096 decode shape (688 CTAs)
-__global__ void __launch_bounds__(NW * 32, NW == 8 ? 3 : 1)
+// SLICED: grid.y K slices per row tile, reduced through the cluster's distributed shared memory (see gemv_mma_common.cuh).
+template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
+__global__ void __launch_bounds__(NW * 32)
 gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias,
                     T* __restrict__ y, int m, int n, int k) {
   using MT = MmaType<T>;
@@ -76,7 +76,7 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   const int nsb = k >> 8, nsub = k >> 5;
   const int nstages_all = (nsb + kStageSb - 1) / kStageSb;
   // K slice of this CTA (grid.y = cluster size = slices per row tile)
-  const int ks = gridDim.y, kr = ks > 1 ? int(cluster_rank()) : 0;
+  const int ks = SLICED ? int(gridDim.y) : 1, kr = SLICED ? int(cluster_rank()) : 0;
   const int per_slice = (nstages_all + ks - 1) / ks;
   const int s_first = kr * per_slice;
   const int nstages = max(0, min(nstages_all, s_first + per_slice) - s_first);
@@ -236,46 +236,48 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
     }
     sOut[idx] = v - xs;
   }
-  if (ks > 1) cluster_barrier(); else __syncthreads();
+  if (SLICED) cluster_barrier(); else __syncthreads();
   if (kr == 0) {
     for (int idx = tid; idx < kGemvRows * MXC; idx += NW * 32) {
       const int r = idx & (kGemvRows - 1), c = idx >> 4;
       const int row = r_base + r;
       if (row < n && c < m) {
         float v = sOut[idx];
-        for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
+        if (SLICED)
+          for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
         if (bias != nullptr) v += MT::to_float(bias[row]);
         y[int64_t(c) * n + row] = MT::from_float(v);
       }
     }
   }
-  if (ks > 1) cluster_barrier();           // peers keep their shared memory alive until rank 0 has read it
+  if (SLICED) cluster_barrier();           // peers keep their shared memory alive until rank 0 has read it
 }
 
-template <typename T, int MXC, int NW, int NSTAGE>
+template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
 static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
   const int tiles = (n + kGemvRows - 1) / kGemvRows;
   const size_t smem = size_t(NSTAGE) * kStageBytes + size_t(k / 32) * MXC * sizeof(float);
   if (smem > 200 * 1024) return RC_RANGE;
-  auto kern = gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE>;
+  auto kern = gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE, SLICED>;
   static size_t opted_in = 0;        // dynamic shared memory beyond 48 KB in total needs the opt-in, once per size
   if (smem > opted_in) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
     opted_in = smem;
   }
-  const int ks = gemv_k_slices(tiles, ((k >> 8) + kStageSb - 1) / kStageSb, NSTAGE);
+  const int ks = SLICED ? gemv_k_slices(tiles, ((k >> 8) + kStageSb - 1) / kStageSb, NSTAGE) : 1;
   const cudaError_t err = gemv_launch(kern, tiles, ks, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
                                       static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
-// M <= 2: 8 warps and 4 stage slots (5 CTAs per SM still fit, one wave for N = 11008); larger M needs more shared
-// memory for X and the reduction, so it keeps 4 warps and 3 slots to stay at 5 CTAs per SM.
+// M <= 2: 8 warps and 4 stage slots, one CTA per row tile over the whole K (78 registers: 3 CTAs per SM).  Larger M
+// needs more shared memory for X and the reduction: 4 warps, 3 slots, K sliced across a cluster so that a CTA's whole
+// slice is in flight from its first instruction on.
 template <typename T, int MXC>
 static int launch_q4k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
-  if (MXC <= 2 && k >= 2048) return launch_q4k_cfg<T, MXC, 8, 4>(a, b, bias, c, m, n, k, s);
-  if (MXC <= 2) return launch_q4k_cfg<T, MXC, 4, 4>(a, b, bias, c, m, n, k, s);
-  return launch_q4k_cfg<T, MXC, 4, 3>(a, b, bias, c, m, n, k, s);
+  if (MXC <= 2 && k >= 2048) return launch_q4k_cfg<T, MXC, 8, 4, false>(a, b, bias, c, m, n, k, s);
+  if (MXC <= 2) return launch_q4k_cfg<T, MXC, 4, 4, false>(a, b, bias, c, m, n, k, s);
+  return launch_q4k_cfg<T, MXC, 4, 3, true>(a, b, bias, c, m, n, k, s);
 }
 
 template <typename T>

@@ -126,7 +126,8 @@ __device__ __forceinline__ void q6k_superblock(const uint8_t* st, float (*sS)[16
 
 // MXC: activation rows covered (power of two >= m).  NW: warps per CTA (4 or 8); each group of 4 warps walks its own
 // sequence of K-stages.  NSTAGE: shared-memory stage slots (dynamic shared memory).
-template <typename T, int MXC, int NW, int NSTAGE>
+// SLICED: grid.y K slices per row tile, reduced through the cluster's distributed shared memory (see gemv_mma_common.cuh).
+template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
 __global__ void __launch_bounds__(NW * 32)
 gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y, int m,
                     int n, int k) {
@@ -151,7 +152,7 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   const int nsb = k >> 8;
   const int nstages_all = nsb / kQ6StageSb;          // K % 2048 == 0: whole stages only
   // K slice of this CTA (grid.y = cluster size = slices per row tile)
-  const int ks = gridDim.y, kr = ks > 1 ? int(cluster_rank()) : 0;
+  const int ks = SLICED ? int(gridDim.y) : 1, kr = SLICED ? int(cluster_rank()) : 0;
   const int per_slice = (nstages_all + ks - 1) / ks;
   const int s_first = kr * per_slice;
   const int nstages = max(0, min(nstages_all, s_first + per_slice) - s_first);
@@ -227,33 +228,34 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
     for (int wv = 0; wv < NW; ++wv) v += sRed[wv][r][c];
     sOut[idx] = v;
   }
-  if (ks > 1) cluster_barrier(); else __syncthreads();
+  if (SLICED) cluster_barrier(); else __syncthreads();
   if (kr == 0) {
     for (int idx = tid; idx < kQ6Rows * MXC; idx += NW * 32) {
       const int r = idx & (kQ6Rows - 1), c = idx >> 4;
       const int row = r_base + r;
       if (row < n && c < m) {
         float v = sOut[idx];
-        for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
+        if (SLICED)
+          for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
         if (bias != nullptr) v += MT::to_float(bias[row]);
         y[int64_t(c) * n + row] = MT::from_float(v);
       }
     }
   }
-  if (ks > 1) cluster_barrier();           // peers keep their shared memory alive until rank 0 has read it
+  if (SLICED) cluster_barrier();           // peers keep their shared memory alive until rank 0 has read it
 }
 
-template <typename T, int MXC, int NW, int NSTAGE>
+template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
 static int launch_q6k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
   const int tiles = (n + kQ6Rows - 1) / kQ6Rows;
   constexpr size_t smem = size_t(NSTAGE) * kQ6StageBytes;
-  auto kern = gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE>;
+  auto kern = gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED>;
   static bool opted_in = false;        // dynamic shared memory beyond 48 KB needs the opt-in
   if (!opted_in) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
     opted_in = true;
   }
-  const int ks = gemv_k_slices(tiles, (k >> 8) / kQ6StageSb, NSTAGE);
+  const int ks = SLICED ? gemv_k_slices(tiles, (k >> 8) / kQ6StageSb, NSTAGE) : 1;
   const cudaError_t err = gemv_launch(kern, tiles, ks, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
                                       static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
@@ -261,8 +263,15 @@ static int launch_q6k_cfg(const void* a, const void* b, const void* bias, void* 
 
 template <typename T, int MXC>
 static int launch_q6k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
-  if (MXC <= 2) return launch_q6k_cfg<T, MXC, 8, 4>(a, b, bias, c, m, n, k, s);
-  return launch_q6k_cfg<T, MXC, 4, 3>(a, b, bias, c, m, n, k, s);
+  if constexpr (MXC <= 2) {
+    // Few row tiles (all CTAs resident at two per SM): six stage slots per CTA keep more bytes in flight.  Many row
+    // tiles: four slots, so that three CTAs fit on an SM.
+    int sm_count = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if ((n + kQ6Rows - 1) / kQ6Rows <= 2 * sm_count) return launch_q6k_cfg<T, MXC, 8, 6, false>(a, b, bias, c, m, n, k, s);
+    return launch_q6k_cfg<T, MXC, 8, 4, false>(a, b, bias, c, m, n, k, s);
+  }
+  return launch_q6k_cfg<T, MXC, 4, 3, true>(a, b, bias, c, m, n, k, s);
 }
 
 template <typename T>
