@@ -48,6 +48,9 @@ int set_error_message(int rc, const std::string& message) {
 const char* last_error() { return g_last_error.c_str(); }
 
 int select_variant(int qtype, int dtype, int m, int n, int k) {
+  // M = 9..16 is served by both tensor-core kernels: the tcgen05 one costs the same whatever M is and wins there once
+  // the weight is large enough to spread over the SMs; the mma.sync GEMV does twice the MMA work of M <= 8.
+  if (m >= 9 && m <= 16 && n >= 2048 && gemm_umma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_UMMA;
   if (gemv_mma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_MMA;
   if (gemm_umma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_UMMA;
   return DINOML_B200_GGUF_VARIANT_SIMT;

@@ -1,4 +1,4 @@
-// Fused GGUF prefill GEMM ("umma" variant) on tcgen05 tensor cores with TMEM accumulators, M >= 17.
+// Fused GGUF prefill GEMM ("umma" variant) on tcgen05 tensor cores with TMEM accumulators, M >= 9.
 //
 // C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), float16 / bfloat16, Q4_K and Q6_K weights.
 // Tensor-core bound for M >= 512 (Q6_K 4096x14336: 1248 FLOP per weight byte at M = 512).
@@ -387,34 +387,40 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
       }
       const float bias_v = (finishes && p.bias != nullptr && n_row < p.n) ? P::up(static_cast<const T*>(p.bias)[n_row]) : 0.f;
       constexpr int kColsPerWarp = BM / 4;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kColsPerWarp; c0 += 16) {
+      constexpr int CH = kColsPerWarp >= 32 ? 32 : 16;   // columns per round: enough independent loads / stores in flight
+#pragma unroll
+      for (int c0 = 0; c0 < kColsPerWarp; c0 += CH) {
         const int col = (warp >> 2) * kColsPerWarp + c0;
-        uint32_t r[16];
-        tmem_ld16(tmem_base + (uint32_t(32 * (warp & 3)) << 16) + uint32_t(col), r);
+        uint32_t r[CH];
+#pragma unroll
+        for (int q = 0; q < CH / 16; ++q)
+          tmem_ld16(tmem_base + (uint32_t(32 * (warp & 3)) << 16) + uint32_t(col + 16 * q), *reinterpret_cast<uint32_t(*)[16]>(&r[16 * q]));
         tmem_ld_wait();
         if (!finishes) {
           float* dst = p.partial + (static_cast<size_t>(cta) * BM + col) * kRowsW + row;     // tile-local [BM][128]
 #pragma unroll
-          for (int j = 0; j < 16; ++j) dst[j * kRowsW] = __uint_as_float(r[j]);
+          for (int j = 0; j < CH; ++j) dst[j * kRowsW] = __uint_as_float(r[j]);
         } else {
           for (int peer = peer0; peer < cta; ++peer) {
             const float* src = p.partial + (static_cast<size_t>(peer) * BM + col) * kRowsW + row;
+            float v[CH];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(src + j * kRowsW));
+            for (int j = 0; j < CH; ++j) v[j] = __ldcg(src + j * kRowsW);
+#pragma unroll
+            for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + v[j]);
           }
           if (n_row < p.n) {
             T* dst = static_cast<T*>(p.out) + int64_t(m0 + col) * p.n + n_row;
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
+            for (int j = 0; j < CH; ++j)
               if (m0 + col + j < p.m) dst[int64_t(j) * p.n] = P::cvt(__uint_as_float(r[j]) + bias_v);
           }
         }
       }
       if (!finishes) {
-        __threadfence();                               // this thread's partial sums are visible device-wide ...
+        // every producer thread's partial sums happen before the barrier; the release below is cumulative over them
         if (!producer_sync()) return false;
-        if (tid == 0) st_release(p.flags + cta, 1);    // ... before the flag is
+        if (tid == 0) { __threadfence(); st_release(p.flags + cta, 1); }
       } else if (!whole) {
         if (!producer_sync()) return false;    // every thread has read the peers' tiles
         if (tid < cta - peer0) p.flags[peer0 + tid] = 0;   // leave the flags clear for the next launch
@@ -704,7 +710,9 @@ static Plan make_plan(int m, int n, int k) {
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   if (sm_count > kMaxCtas) sm_count = kMaxCtas;
-  pl.ctas = int(pl.units < sm_count ? pl.units : sm_count);
+  // at least four super-blocks per CTA: a small problem is not cut into more pieces than its finishers can add up quickly
+  const long long most = pl.units / 4 > 1 ? pl.units / 4 : 1;
+  pl.ctas = int(most < sm_count ? most : sm_count);
   pl.workspace_bytes = tiles % pl.ctas == 0 ? 0 : size_t(pl.ctas) * pl.bm * kRowsW * sizeof(float);
   return pl;
 }
@@ -815,7 +823,7 @@ static int launch_bm(const void* a, const void* b, const void* bias, void* c, in
 
 bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k) {
   (void)n;
-  if (!(qtype == QTYPE_Q4_K || qtype == QTYPE_Q6_K) || !(dtype == DINO_BF16 || dtype == DINO_F16) || m < 17 || k % 256 != 0) return false;
+  if (!(qtype == QTYPE_Q4_K || qtype == QTYPE_Q6_K) || !(dtype == DINO_BF16 || dtype == DINO_F16) || m < 9 || k % 256 != 0) return false;
   const int64_t row_bytes = int64_t(k / 256) * (qtype == QTYPE_Q4_K ? 144 : 210);
   return row_bytes % 16 == 0;   // the packed-weight tensor map needs 16-byte row pitches
 }

@@ -27,10 +27,11 @@ VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3}
 
 _B200_TUNING = {
     "simt": {"kind": "gemv_simt", "rows_per_warp": 1, "activation_rows_per_pass": 4, "staging": "ldg", "tensor_cores": "none"},
-    "mma": {"kind": "gemv", "rows_per_cta": 16, "k_slices": 4, "stages": 3, "staging": "cp_async16",
-            "tensor_cores": "mma.sync.m16n8k16", "max_m": 16},
-    "umma": {"kind": "umma_gemm", "tile_n": 128, "tile_m": [64, 128, 256], "tile_k": 64, "stages": 4, "staging": "cp_async16+tma",
-             "tensor_cores": "tcgen05.mma.cta_group::1.kind::f16", "accumulator": "tmem", "split_k": "auto", "min_m": 17},
+    "mma": {"kind": "gemv", "rows_per_cta": 16, "stage_super_blocks": 4, "stages": [3, 4, 6], "staging": "cp_async16",
+            "k_slices": "cluster_dsmem for m > 2", "tensor_cores": "mma.sync.m16n8k16", "max_m": 16},
+    "umma": {"kind": "umma_gemm", "tile_n": 128, "tile_m": [64, 128, 256], "tile_k": 64, "stages": 4, "staging": "tma",
+             "tensor_cores": "tcgen05.mma.cta_group::1.kind::f16", "weight_operand": "tmem", "accumulator": "tmem",
+             "work_split": "stream_k", "min_m": 9},
 }
 
 
@@ -46,7 +47,7 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
     """Which kernel variants exist for a (qtype, dtype)."""
     variants = ["simt"]
     if dtype in ("float16", "bfloat16"):
-        if qtype == "Q4_K":
+        if qtype in ("Q4_K", "Q6_K"):
             variants.append("mma")
         if qtype in ("Q4_K", "Q6_K"):
             variants.append("umma")
@@ -54,7 +55,7 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
 
 
 def variant_supports(variant: str, m: int) -> bool:
-    return {"simt": True, "mma": 1 <= m <= 16, "umma": m >= 17}[variant]
+    return {"simt": True, "mma": 1 <= m <= 16, "umma": m >= 9}[variant]
 
 
 def kernel_symbol(qtype: str, op: str, dtype: str, variant: str, *, profile: bool = False) -> str:
