@@ -361,12 +361,18 @@ def run_single(args):
         b = bench_gemm(qtype, n, k, m, extra_steps, extra_warm, l2)
         extras[f"cfg2_q4k_m{m}"] = {"us_per_launch": b["us_per_launch"], "weight_gbs": nbytes / b["us_per_launch"] / 1e3,
                                     "tflops": 2.0 * m * n * k / b["us_per_launch"] / 1e6, "variant": b["variant"]}
+    for m in (1, 16):
+        b = bench_gemm(CFG3["qtype"], CFG3["n"], CFG3["k"], m, extra_steps, extra_warm, l2, copies=4)
+        extras[f"cfg3_q6k_m{m}"] = {"us_per_launch": b["us_per_launch"], "weight_gbs": b["weight_bytes"] / b["us_per_launch"] / 1e3,
+                                    "variant": b["variant"]}
     prefill = {}
     for m in (64, 512, 2048):
         b = bench_gemm(CFG3["qtype"], CFG3["n"], CFG3["k"], m, extra_steps, extra_warm, l2, copies=3)
         tf = 2.0 * m * CFG3["n"] * CFG3["k"] / b["us_per_launch"] / 1e6
         prefill[f"m{m}"] = {"us_per_launch": b["us_per_launch"], "tflops": tf, "variant": b["variant"],
-                            "frac_of_measured_burst": tf / peaks["bf16_tflops"], "frac_of_nominal_2250": tf / 2250.0}
+                            "frac_of_measured_burst": tf / peaks["bf16_tflops"],
+                            "frac_of_measured_sustained": tf / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
+                            "frac_of_nominal_2250": tf / 2250.0}
     extras["cfg3_q6k_prefill"] = prefill
     extras["cfg1_q8_0_m1_gpu"] = (lambda b: {"us_per_launch": b["us_per_launch"], "weight_gbs": b["weight_bytes"] / b["us_per_launch"] / 1e3,
                                              "variant": b["variant"]})(bench_gemm("Q8_0", 4096, 4096, 1, extra_steps, extra_warm, l2))
@@ -402,6 +408,47 @@ def run_single(args):
         "device": {"name": props.name, "sms": props.multi_processor_count, "l2_bytes": l2},
     }
     print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------- profiling cases
+PROFILE_CASES = {  # name -> (qtype, n, k, m, variant, weight copies): small, eager, few launches; inputs exceed the L2
+    "gemv_q4k_m1": ("Q4_K", 11008, 4096, 1, "mma", 6),
+    "gemv_q6k_m1": ("Q6_K", 4096, 14336, 1, "mma", 3),
+    "gemm_umma_q6k_m512": ("Q6_K", 4096, 14336, 512, "umma", 3),
+    "gemm_umma_q4k_m256": ("Q4_K", 11008, 4096, 256, "umma", 6),
+    "dequant_q4k_f16": ("Q4_K", 11008, 4096, 0, "dequant", 3),
+}
+
+
+def run_profile_case(args):
+    """One warm-up pass and one measured pass of a single kernel over distinct weight copies, launched eagerly: the
+    command an `ncu -k <kernel> -c <n>` capture wraps.  Prints a short JSON line of its own (not the benchmark line)."""
+    import torch
+
+    from dinoml_v2_b200 import kernels, synthetic
+    from dinoml_v2_b200.gguf_blocks import encoded_nbytes
+    qtype, n, k, m, variant, copies = PROFILE_CASES[args.only]
+    dev = torch.device("cuda")
+    ws = [synthetic.random_blocks_torch(qtype, n, k, 1000 + i, dev) for i in range(copies)]
+    if variant == "dequant":
+        outs = [torch.empty(n, k, device=dev, dtype=torch.float16) for _ in range(copies)]
+        launch = lambda i: kernels.dequantize_rows(ws[i], qtype, k, "float16", out=outs[i])
+    else:
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        outs = [torch.empty(m, n, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+        launch = lambda i: kernels.gemm_rcr(x, ws[i], qtype, variant=variant, out=outs[i])
+    for i in range(copies):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(copies):
+        launch(i)
+    e1.record()
+    torch.cuda.synchronize()
+    assert kernels.device_status() == 0
+    print(json.dumps({"case": args.only, "launches": 2 * copies, "us_per_launch_eager": e0.elapsed_time(e1) * 1e3 / copies,
+                      "weight_bytes": encoded_nbytes(qtype, n, k), "device_bytes": copies * encoded_nbytes(qtype, n, k)}))
 
 
 # ----------------------------------------------------------------------------------------------- multi GPU
@@ -492,10 +539,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for the cpu_baseline leg")
+    ap.add_argument("--only", choices=sorted(PROFILE_CASES), help="run one small single-kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.only:
+        return run_profile_case(args)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1 or args.gpus > 1:
         if "RANK" not in os.environ:
             raise SystemExit("--gpus > 1 must be launched with torchrun (one rank per GPU)")
