@@ -46,6 +46,10 @@ def lib() -> ctypes.CDLL:
     L.dinoml_b200_gguf_gemm_rcr_select.argtypes = [ci, ci, ci, ci, ci]
     L.dinoml_b200_gguf_gemm_rcr_select.restype = ci
     L.dinoml_b200_gguf_device_status.restype = ci
+    L.dinoml_b200_gguf_gemv_rcr_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, ci, ci, ci, ci, ci, vp]
+    L.dinoml_b200_gguf_gemv_rcr_scatter.restype = ci
+    L.dinoml_b200_peer_exchange.argtypes = [ctypes.POINTER(vp), ci, ci, ctypes.c_uint, vp, vp, i64, ci, vp]
+    L.dinoml_b200_peer_exchange.restype = ci
     _lib = L
     return L
 

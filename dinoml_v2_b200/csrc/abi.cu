@@ -20,6 +20,12 @@ bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k);
 bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k);
 size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k);
 int umma_device_status();
+int peer_device_status();
+struct PeerOut { void* ptr[8]; int count; };   // layout of gemv_mma_common.cuh
+int gemm_rcr_mma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                       const PeerOut* peer_out, cudaStream_t s);
+int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch, const void* slots, void* out, int64_t count, int dtype,
+                  cudaStream_t s);
 int gemm_rcr_umma_static(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                          cudaStream_t s);
 size_t gemm_umma_static_scratch_bytes();
@@ -133,7 +139,28 @@ size_t dinoml_b200_gguf_prealloc_scratch_bytes(void) { return gemm_umma_static_s
 
 int dinoml_b200_gguf_device_status(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  return umma_device_status();
+  const int peer = peer_device_status();   // read both so that both are cleared
+  const int gemm = umma_device_status();
+  return gemm != 0 ? gemm : peer;
+}
+
+int dinoml_b200_gguf_gemv_rcr_scatter(const void* a, const void* b_quant, const void* bias, void* c, void* const* peer_c, int n_peers,
+                                      int qtype, int dtype, int m, int n, int k, void* stream) {
+  if (n_peers < 0 || n_peers > 8 || (n_peers > 0 && peer_c == nullptr))
+    return set_error(RC_RANGE, "dinoml_b200_gguf_gemv_rcr_scatter");
+  PeerOut peers;
+  for (int i = 0; i < 8; ++i) peers.ptr[i] = i < n_peers ? peer_c[i] : nullptr;
+  peers.count = n_peers;
+  for (int i = 0; i < n_peers; ++i)
+    if (peers.ptr[i] == nullptr) return set_error(RC_NULL, "dinoml_b200_gguf_gemv_rcr_scatter");
+  return set_error(gemm_rcr_mma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, static_cast<cudaStream_t>(stream)),
+                   "dinoml_b200_gguf_gemv_rcr_scatter");
+}
+
+int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, unsigned int epoch, const void* slots, void* out,
+                              int64_t count, int dtype, void* stream) {
+  return set_error(peer_exchange(signal_ptrs, world, rank, epoch, slots, out, count, dtype, static_cast<cudaStream_t>(stream)),
+                   "dinoml_b200_peer_exchange");
 }
 
 int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k) {

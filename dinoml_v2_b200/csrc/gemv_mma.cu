@@ -35,7 +35,7 @@ namespace b200gguf {
 
 int check_gemm_args(const void* a, const void* b, const void* c, int qtype, int dtype, int m, int n, int k);
 bool gemv_q6k_mma_supports(int dtype, int m, int k);
-int gemv_q6k_mma(const void* a, const void* b, const void* bias, void* c, int dtype, int m, int n, int k, cudaStream_t s);
+int gemv_q6k_mma(const void* a, const void* b, const void* bias, void* c, int dtype, int m, int n, int k, const PeerOut& peers, cudaStream_t s);
 
 constexpr int kGemvWarps = 4;
 constexpr int kGemvThreads = kGemvWarps * 32;
@@ -49,10 +49,11 @@ constexpr int kStageBytes = kGemvRows * kRowPitch;       // 9728 B per stage slo
 // sequence of K-stages (group p takes stages p, p + NW/4, ...), so an 8-warp CTA unpacks two stages at a time.
 // NSTAGE: shared-memory stage slots.  Dynamic shared memory: weight stages, then X[MXC][k/32] floats.
 // SLICED: grid.y K slices per row tile, reduced through the cluster's distributed shared memory (see gemv_mma_common.cuh).
-template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
+// SCATTER: the result also goes to the extra destinations in `peers` (see PeerOut).
+template <typename T, int MXC, int NW, int NSTAGE, bool SLICED, bool SCATTER>
 __global__ void __launch_bounds__(NW * 32)
 gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias,
-                    T* __restrict__ y, int m, int n, int k) {
+                    T* __restrict__ y, int m, int n, int k, const PeerOut peers) {
   using MT = MmaType<T>;
   constexpr int NT = MXC > 8 ? 2 : 1;        // n8 tiles of activation rows
   constexpr int MC = MXC == 1 ? 1 : 2;       // accumulator columns a lane keeps per tile
@@ -246,7 +247,13 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
         if (SLICED)
           for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
         if (bias != nullptr) v += MT::to_float(bias[row]);
-        y[int64_t(c) * n + row] = MT::from_float(v);
+        const T out = MT::from_float(v);
+        y[int64_t(c) * n + row] = out;
+        if (SCATTER) {
+#pragma unroll
+          for (int pi = 0; pi < 8; ++pi)
+            if (pi < peers.count) static_cast<T*>(peers.ptr[pi])[int64_t(c) * n + row] = out;
+        }
       }
     }
   }
@@ -254,19 +261,20 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
 }
 
 template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
-static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
   const int tiles = (n + kGemvRows - 1) / kGemvRows;
   const size_t smem = size_t(NSTAGE) * kStageBytes + size_t(k / 32) * MXC * sizeof(float);
   if (smem > 200 * 1024) return RC_RANGE;
-  auto kern = gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE, SLICED>;
-  static size_t opted_in = 0;        // dynamic shared memory beyond 48 KB in total needs the opt-in, once per size
-  if (smem > opted_in) {
+  auto kern = peers.count > 0 ? gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true> : gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false>;
+  static size_t opted_in[2] = {0, 0};   // dynamic shared memory beyond 48 KB in total needs the opt-in, once per kernel and size
+  size_t& done = opted_in[peers.count > 0 ? 1 : 0];
+  if (smem > done) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
-    opted_in = smem;
+    done = smem;
   }
   const int ks = SLICED ? gemv_k_slices(tiles, ((k >> 8) + kStageSb - 1) / kStageSb, NSTAGE) : 1;
   const cudaError_t err = gemv_launch(kern, tiles, ks, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
-                                      static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
+                                      static_cast<const T*>(bias), static_cast<T*>(c), m, n, k, peers);
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
@@ -274,19 +282,19 @@ static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* 
 // needs more shared memory for X and the reduction: 4 warps, 3 slots, K sliced across a cluster so that a CTA's whole
 // slice is in flight from its first instruction on.
 template <typename T, int MXC>
-static int launch_q4k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
-  if (MXC <= 2 && k >= 2048) return launch_q4k_cfg<T, MXC, 8, 4, false>(a, b, bias, c, m, n, k, s);
-  if (MXC <= 2) return launch_q4k_cfg<T, MXC, 4, 4, false>(a, b, bias, c, m, n, k, s);
-  return launch_q4k_cfg<T, MXC, 4, 3, true>(a, b, bias, c, m, n, k, s);
+static int launch_q4k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
+  if (MXC <= 2 && k >= 2048) return launch_q4k_cfg<T, MXC, 8, 4, false>(a, b, bias, c, m, n, k, peers, s);
+  if (MXC <= 2) return launch_q4k_cfg<T, MXC, 4, 4, false>(a, b, bias, c, m, n, k, peers, s);
+  return launch_q4k_cfg<T, MXC, 4, 3, true>(a, b, bias, c, m, n, k, peers, s);
 }
 
 template <typename T>
-static int launch_q4k(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
-  if (m == 1) return launch_q4k_m<T, 1>(a, b, bias, c, m, n, k, s);
-  if (m == 2) return launch_q4k_m<T, 2>(a, b, bias, c, m, n, k, s);
-  if (m <= 4) return launch_q4k_m<T, 4>(a, b, bias, c, m, n, k, s);
-  if (m <= 8) return launch_q4k_m<T, 8>(a, b, bias, c, m, n, k, s);
-  return launch_q4k_m<T, 16>(a, b, bias, c, m, n, k, s);
+static int launch_q4k(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
+  if (m == 1) return launch_q4k_m<T, 1>(a, b, bias, c, m, n, k, peers, s);
+  if (m == 2) return launch_q4k_m<T, 2>(a, b, bias, c, m, n, k, peers, s);
+  if (m <= 4) return launch_q4k_m<T, 4>(a, b, bias, c, m, n, k, peers, s);
+  if (m <= 8) return launch_q4k_m<T, 8>(a, b, bias, c, m, n, k, peers, s);
+  return launch_q4k_m<T, 16>(a, b, bias, c, m, n, k, peers, s);
 }
 
 // Which (qtype, dtype, m, k) the mma variant covers.
@@ -296,17 +304,24 @@ bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k) {
   return qtype == QTYPE_Q4_K && (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 16 && k % 256 == 0;
 }
 
-int gemm_rcr_mma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
-                 cudaStream_t s) {
+// peers: extra destinations of the result (null = none); see PeerOut.
+int gemm_rcr_mma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                       const PeerOut* peer_out, cudaStream_t s) {
+  const PeerOut peers = peer_out != nullptr ? *peer_out : no_peers();
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (m > 16) return RC_RANGE;
   if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
   if (!gemv_mma_supports(qtype, dtype, m, n, k)) return RC_ALIGN;   // Q6_K rows that are not 16-byte multiples
   if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;  // 16-byte cp.async sources, vector loads
-  if (qtype == QTYPE_Q6_K) return gemv_q6k_mma(a, b, bias, c, dtype, m, n, k, s);
-  return dtype == DINO_BF16 ? launch_q4k<__nv_bfloat16>(a, b, bias, c, m, n, k, s)
-                            : launch_q4k<__half>(a, b, bias, c, m, n, k, s);
+  if (qtype == QTYPE_Q6_K) return gemv_q6k_mma(a, b, bias, c, dtype, m, n, k, peers, s);
+  return dtype == DINO_BF16 ? launch_q4k<__nv_bfloat16>(a, b, bias, c, m, n, k, peers, s)
+                            : launch_q4k<__half>(a, b, bias, c, m, n, k, peers, s);
+}
+
+int gemm_rcr_mma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                 cudaStream_t s) {
+  return gemm_rcr_mma_peers(a, b, bias, c, qtype, dtype, m, n, k, nullptr, s);
 }
 
 }  // namespace b200gguf

@@ -93,6 +93,20 @@ inline int gemv_k_slices(int tiles, int nstages, int slots) {
   return ks < 1 ? 1 : ks;
 }
 
+// Extra destinations of a GEMV result: up to 8 more [M, N] buffers (typically the same slot of a gather buffer in
+// every peer GPU's memory, mapped into this process) that receive the same values as the primary output, written
+// by the same threads with plain stores.  count = 0: none.
+struct PeerOut {
+  void* ptr[8];
+  int count;
+};
+inline PeerOut no_peers() {
+  PeerOut p;
+  for (int i = 0; i < 8; ++i) p.ptr[i] = nullptr;
+  p.count = 0;
+  return p;
+}
+
 // Launch with programmatic stream serialization and, for ks > 1, clusters of ks CTAs along grid.y.
 template <typename Kernel, typename... Args>
 inline cudaError_t gemv_launch(Kernel kern, int tiles, int ks, int threads, size_t smem, cudaStream_t s, Args... args) {

@@ -127,10 +127,11 @@ __device__ __forceinline__ void q6k_superblock(const uint8_t* st, float (*sS)[16
 // MXC: activation rows covered (power of two >= m).  NW: warps per CTA (4 or 8); each group of 4 warps walks its own
 // sequence of K-stages.  NSTAGE: shared-memory stage slots (dynamic shared memory).
 // SLICED: grid.y K slices per row tile, reduced through the cluster's distributed shared memory (see gemv_mma_common.cuh).
-template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
+// SCATTER: the result also goes to the extra destinations in `peers` (see PeerOut).
+template <typename T, int MXC, int NW, int NSTAGE, bool SLICED, bool SCATTER>
 __global__ void __launch_bounds__(NW * 32)
 gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y, int m,
-                    int n, int k) {
+                    int n, int k, const PeerOut peers) {
   using MT = MmaType<T>;
   constexpr int NT = MXC > 8 ? 2 : 1;        // n8 tiles of activation rows
   constexpr int MC = MXC == 1 ? 1 : 2;       // accumulator columns a lane keeps per tile
@@ -238,7 +239,13 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
         if (SLICED)
           for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
         if (bias != nullptr) v += MT::to_float(bias[row]);
-        y[int64_t(c) * n + row] = MT::from_float(v);
+        const T out = MT::from_float(v);
+        y[int64_t(c) * n + row] = out;
+        if (SCATTER) {
+#pragma unroll
+          for (int pi = 0; pi < 8; ++pi)
+            if (pi < peers.count) static_cast<T*>(peers.ptr[pi])[int64_t(c) * n + row] = out;
+        }
       }
     }
   }
@@ -246,41 +253,42 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
 }
 
 template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
-static int launch_q6k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+static int launch_q6k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
   const int tiles = (n + kQ6Rows - 1) / kQ6Rows;
   constexpr size_t smem = size_t(NSTAGE) * kQ6StageBytes;
-  auto kern = gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED>;
-  static bool opted_in = false;        // dynamic shared memory beyond 48 KB needs the opt-in
-  if (!opted_in) {
+  auto kern = peers.count > 0 ? gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true> : gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false>;
+  static bool opted_in[2] = {false, false};   // dynamic shared memory beyond 48 KB needs the opt-in, once per kernel
+  bool& done = opted_in[peers.count > 0 ? 1 : 0];
+  if (!done) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
-    opted_in = true;
+    done = true;
   }
   const int ks = SLICED ? gemv_k_slices(tiles, (k >> 8) / kQ6StageSb, NSTAGE) : 1;
   const cudaError_t err = gemv_launch(kern, tiles, ks, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
-                                      static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
+                                      static_cast<const T*>(bias), static_cast<T*>(c), m, n, k, peers);
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
 template <typename T, int MXC>
-static int launch_q6k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+static int launch_q6k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
   if constexpr (MXC <= 2) {
     // Few row tiles (all CTAs resident at two per SM): six stage slots per CTA keep more bytes in flight.  Many row
     // tiles: four slots, so that three CTAs fit on an SM.
     int sm_count = 148, dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    if ((n + kQ6Rows - 1) / kQ6Rows <= 2 * sm_count) return launch_q6k_cfg<T, MXC, 8, 6, false>(a, b, bias, c, m, n, k, s);
-    return launch_q6k_cfg<T, MXC, 8, 4, false>(a, b, bias, c, m, n, k, s);
+    if ((n + kQ6Rows - 1) / kQ6Rows <= 2 * sm_count) return launch_q6k_cfg<T, MXC, 8, 6, false>(a, b, bias, c, m, n, k, peers, s);
+    return launch_q6k_cfg<T, MXC, 8, 4, false>(a, b, bias, c, m, n, k, peers, s);
   }
-  return launch_q6k_cfg<T, MXC, 4, 3, true>(a, b, bias, c, m, n, k, s);
+  return launch_q6k_cfg<T, MXC, 4, 3, true>(a, b, bias, c, m, n, k, peers, s);
 }
 
 template <typename T>
-static int launch_q6k(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
-  if (m == 1) return launch_q6k_m<T, 1>(a, b, bias, c, m, n, k, s);
-  if (m == 2) return launch_q6k_m<T, 2>(a, b, bias, c, m, n, k, s);
-  if (m <= 4) return launch_q6k_m<T, 4>(a, b, bias, c, m, n, k, s);
-  if (m <= 8) return launch_q6k_m<T, 8>(a, b, bias, c, m, n, k, s);
-  return launch_q6k_m<T, 16>(a, b, bias, c, m, n, k, s);
+static int launch_q6k(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
+  if (m == 1) return launch_q6k_m<T, 1>(a, b, bias, c, m, n, k, peers, s);
+  if (m == 2) return launch_q6k_m<T, 2>(a, b, bias, c, m, n, k, peers, s);
+  if (m <= 4) return launch_q6k_m<T, 4>(a, b, bias, c, m, n, k, peers, s);
+  if (m <= 8) return launch_q6k_m<T, 8>(a, b, bias, c, m, n, k, peers, s);
+  return launch_q6k_m<T, 16>(a, b, bias, c, m, n, k, peers, s);
 }
 
 // Rows must be 16-byte multiples: 210 * (k / 256) % 16 == 0  <=>  k % 2048 == 0.
@@ -288,8 +296,8 @@ bool gemv_q6k_mma_supports(int dtype, int m, int k) {
   return (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 16 && k % 2048 == 0;
 }
 
-int gemv_q6k_mma(const void* a, const void* b, const void* bias, void* c, int dtype, int m, int n, int k, cudaStream_t s) {
-  return dtype == DINO_BF16 ? launch_q6k<__nv_bfloat16>(a, b, bias, c, m, n, k, s) : launch_q6k<__half>(a, b, bias, c, m, n, k, s);
+int gemv_q6k_mma(const void* a, const void* b, const void* bias, void* c, int dtype, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
+  return dtype == DINO_BF16 ? launch_q6k<__nv_bfloat16>(a, b, bias, c, m, n, k, peers, s) : launch_q6k<__half>(a, b, bias, c, m, n, k, peers, s);
 }
 
 }  // namespace b200gguf

@@ -1,0 +1,123 @@
+// Peer-memory exchange for the sharded (tensor-parallel) decode path: one process per GPU, buffers of every rank mapped
+// into every process (CUDA IPC), no library collective.
+//
+// The GEMV kernels store their result into slot [rank] of a gather buffer on EVERY GPU (PeerOut in
+// gemv_mma_common.cuh).  What is left of an all-gather is then a barrier, and what is left of an all-reduce is a
+// barrier followed by the sum of the `world` slots; this kernel does either:
+//   * block 0, thread p != rank:  fence, then store `epoch` into word [rank] of rank p's signal array
+//     ("everything this GPU wrote before this kernel is complete");
+//   * every block, thread p != rank:  poll word [p] of the local signal array until it reaches `epoch`;
+//   * count > 0:  out[i] = sum over r of slots[r][i] (fp32 accumulation, r ascending - identical on every rank).
+// The poll is bounded: after kSpinLimit tries the kernel records a code in the status word and carries on, so a rank
+// that never arrives cannot hang this GPU.  Epochs increase by one per call on every rank (host-side counter).
+//
+// The reference has no distributed code; the N-split / K-split scheme this serves is in dinoml_v2_b200/sharding.py.
+#include "gguf_common.cuh"
+
+namespace b200gguf {
+
+constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls, 200 ns apart: about one second
+enum : int { PEER_ST_TIMEOUT = 6 };
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+
+struct PeerSignals {
+  uint32_t* ptr[8];       // signal array [8] of every rank, mapped here; ptr[rank] is the local one
+};
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+peer_exchange_kernel(const PeerSignals sig, int world, int rank, uint32_t epoch, const T* __restrict__ slots, T* __restrict__ out,
+                     int64_t count, int* status) {
+  const int tid = threadIdx.x;
+  if (tid < world && tid != rank) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys(sig.ptr[tid] + rank, epoch);
+    }
+    bool seen = false;
+    for (uint32_t i = 0; i < kPeerSpinLimit && !seen; ++i) {
+      seen = int32_t(ld_acquire_sys(sig.ptr[rank] + tid) - epoch) >= 0;     // wrap-safe "reached"
+      if (!seen) __nanosleep(200);
+    }
+    if (!seen) atomicCAS(status, 0, PEER_ST_TIMEOUT);
+  }
+  __syncthreads();
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + tid; i < count; i += int64_t(gridDim.x) * blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < world; ++r) acc += to_f32<T>(__ldcg(slots + int64_t(r) * count + i));
+    out[i] = from_f32<T>(acc);
+  }
+}
+
+static __device__ int g_peer_status;
+static int* peer_status_ptr() {
+  static int* ptr[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_peer_status) != cudaSuccess) return nullptr;
+    ptr[dev] = static_cast<int*>(p);
+  }
+  return ptr[dev];
+}
+
+int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch, const void* slots, void* out, int64_t count, int dtype,
+                  cudaStream_t s) {
+  if (signal_ptrs == nullptr || world < 1 || world > 8 || rank < 0 || rank >= world) return RC_RANGE;
+  if (count < 0 || (count > 0 && (slots == nullptr || out == nullptr))) return RC_NULL;
+  int* status = peer_status_ptr();
+  if (status == nullptr) return RC_LAUNCH;
+  PeerSignals sig;
+  for (int i = 0; i < 8; ++i) sig.ptr[i] = i < world ? static_cast<uint32_t*>(signal_ptrs[i]) : nullptr;
+  for (int i = 0; i < world; ++i)
+    if (sig.ptr[i] == nullptr) return RC_NULL;
+  int64_t blocks = (count + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 64) blocks = 64;
+  switch (dtype) {
+    case DINO_BF16:
+      peer_exchange_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const __nv_bfloat16*>(slots),
+                                                                             static_cast<__nv_bfloat16*>(out), count, status);
+      break;
+    case DINO_F16:
+      peer_exchange_kernel<__half><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const __half*>(slots),
+                                                                    static_cast<__half*>(out), count, status);
+      break;
+    case DINO_F32:
+      peer_exchange_kernel<float><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const float*>(slots),
+                                                                   static_cast<float*>(out), count, status);
+      break;
+    default: return RC_DTYPE;
+  }
+  return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
+}
+
+// Reads (and clears) the exchange status word of the current device.
+int peer_device_status() {
+  int* status = peer_status_ptr();
+  int value = 0;
+  if (status == nullptr) return -1;
+  if (cudaMemcpy(&value, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (value != 0) cudaMemset(status, 0, sizeof(int));
+  return value;
+}
+
+}  // namespace b200gguf

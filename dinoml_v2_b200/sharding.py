@@ -6,7 +6,10 @@ The reference has no distributed code at all; this covers the Llama-70B-shaped F
 * K-split (down): shards are cut at 256-weight super-block granularity; rank r needs blocks [r*nb/G, (r+1)*nb/G) of
   EVERY row, a one-time strided repack at load into a dense [N, nb/G] block matrix, computes a partial [M, N] and the
   ranks all-reduce.  The N-shard of gate/up on rank r is exactly the K-slice rank r needs for down.
-Collectives go through torch.distributed (NCCL over NVLink) on the compute stream; nothing here uses peer pointers."""
+Two ways to finish the collectives: torch.distributed (NCCL over NVLink) on the compute stream, or - for decode
+(M <= 16) - the peer-memory path of `peer.PeerExchange`, where gate and up are one stacked weight, the GEMV kernels
+store their results straight into every GPU's gather buffer and one small kernel per collective does the barrier
+(all-gather) or the barrier + sum (all-reduce)."""
 from __future__ import annotations
 
 import numpy as np
@@ -62,6 +65,30 @@ class ShardedFFN:
             dist.all_gather_into_tensor(gathered_gate.view(-1, out_gate.shape[-1]), out_gate, group=self.group)
             dist.all_gather_into_tensor(gathered_up.view(-1, out_up.shape[-1]), out_up, group=self.group)
         return gathered_gate, gathered_up
+
+    # ---- peer-memory path (decode, M <= 16) ----------------------------------------------------------------------
+    def enable_peer_path(self, m: int, dtype):
+        """Stacks gate and up into one [2 * ffn / world, hidden] weight (one launch, one gather) and maps the exchange
+        buffers of all ranks.  Collective call: every rank must make it."""
+        import torch
+
+        from .peer import PeerExchange
+        self.gate_up_stacked = torch.cat([self.gate, self.up], dim=0).contiguous()
+        self.peer_m = int(m)
+        self.xchg_gate_up = PeerExchange(self.peer_m * self.gate_up_stacked.shape[0], dtype, self.group)
+        self.xchg_down = PeerExchange(self.peer_m * self.hidden, dtype, self.group)
+
+    def gate_up_peer(self, x):
+        """Returns [world, M, 2 * ffn / world]: per rank, its gate rows then its up rows."""
+        self.xchg_gate_up.scatter_gemv(x, self.gate_up_stacked, self.qtype)
+        g = self.xchg_gate_up.finish_gather()
+        return g.view(self.world, self.peer_m, self.gate_up_stacked.shape[0])
+
+    def down_proj_peer(self, h_slice, out):
+        """out [M, hidden] = sum over ranks of h_slice_r @ down_r^T, identical bits on every rank."""
+        self.xchg_down.scatter_gemv(h_slice, self.down, self.qtype)
+        self.xchg_down.finish_reduce(out)
+        return out
 
     def down_proj(self, h_slice, out):
         """h_slice [M, ffn/world] = this rank's K-slice of the down-projection input; out [M, hidden] is summed in place."""

@@ -95,10 +95,27 @@ DINOML_B200_API size_t dinoml_b200_gguf_prealloc_scratch_bytes(void);
 
 /* The tcgen05 kernel bounds every barrier wait; a wait that gives up records a code in a per-device
  * status word instead of hanging or trapping.  Synchronizes the device, returns the word (0 = never
- * happened; 1 / 2 / 3 / 4 = a stage-free / stage-ready / accumulator / partial-tile wait gave up; < 0 = CUDA error) and
+ * happened; 1 / 2 / 3 / 4 = a stage-free / stage-ready / accumulator / partial-tile wait gave up; 6 = a peer never signalled
+ * in dinoml_b200_peer_exchange; < 0 = CUDA error) and
  * clears it together with the partial-tile flags.
  * No counterpart in the reference. */
 DINOML_B200_API int dinoml_b200_gguf_device_status(void);
+
+/* ---- sharded decode over peer memory (no counterpart in the reference, which is single-GPU) ----------------------
+ * dinoml_b200_gguf_gemv_rcr_scatter: the mma GEMV (M <= 16, Q4_K / Q6_K, float16 / bfloat16; same checks and codes as
+ * dinoml_b200_gguf_gemm_rcr with variant = MMA) whose epilogue stores the [M, N] result to `c` AND to `n_peers` (<= 8)
+ * further buffers - the same slot of a gather buffer on the other GPUs, mapped into this process (CUDA IPC / peer
+ * access).  One kernel computes and distributes; there is no separate all-gather.
+ * dinoml_b200_peer_exchange: what remains of the collective.  signal_ptrs[r] = the 8-word signal array of rank r
+ * (signal_ptrs[rank] is local, zero-initialised once); every rank calls with the same, ever increasing `epoch`.  The
+ * kernel publishes "rank's earlier stores are complete" to every peer, waits (bounded, about a second; a rank that
+ * never arrives sets device status 6 instead of hanging the GPU) for every peer's signal, and, if count > 0, writes
+ * out[i] = sum over r < world of slots[r * count + i] (fp32 accumulation, fixed order): barrier only = all-gather
+ * completion, barrier + sum = one-shot all-reduce of GEMV partial results. */
+DINOML_B200_API int dinoml_b200_gguf_gemv_rcr_scatter(const void* a, const void* b_quant, const void* bias, void* c, void* const* peer_c,
+                                                      int n_peers, int qtype, int dtype, int m, int n, int k, void* stream);
+DINOML_B200_API int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, unsigned int epoch, const void* slots,
+                                              void* out, int64_t count, int dtype, void* stream);
 
 /* Per-candidate symbols, named like the reference's kernel symbols so a manifest can carry them:
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)

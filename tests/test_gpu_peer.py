@@ -1,0 +1,65 @@
+"""Scatter GEMV and peer exchange kernels on ONE GPU: the extra destinations and the "peer" signal arrays are local
+buffers, and the signals a peer would send are written beforehand, so nothing waits on another process."""
+import ctypes
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from dinoml_v2_b200 import _native, kernels, synthetic as S   # noqa: E402
+from dinoml_v2_b200.gguf_blocks import qtype_of                # noqa: E402
+
+pytestmark = pytest.mark.gpu
+BF16 = 6
+
+
+@pytest.mark.parametrize("qtype,k", [("Q4_K", 1024), ("Q6_K", 2048)])
+def test_scatter_gemv_writes_every_destination(qtype, k):
+    dev = torch.device("cuda:0")
+    lib = _native.lib()
+    n = 100
+    w = torch.from_numpy(S.random_blocks(qtype, n, k, seed=11)).to(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    for m in (1, 2, 4, 9, 16):
+        x = torch.from_numpy(S.random_activations(m, k, 12 + m, "float32")).to(dev).to(torch.bfloat16)
+        want = kernels.gemm_rcr(x, w, qtype, variant="mma")
+        dst = [torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(4)]
+        peers = (ctypes.c_void_p * 3)(*[t.data_ptr() for t in dst[1:]])
+        rc = lib.dinoml_b200_gguf_gemv_rcr_scatter(x.data_ptr(), w.data_ptr(), None, dst[0].data_ptr(), peers, 3, qtype_of(qtype).value,
+                                                   BF16, m, n, k, stream)
+        assert rc == 0, _native.last_error()
+        torch.cuda.synchronize()
+        for t in dst:
+            assert torch.equal(t.view(torch.int16), want.view(torch.int16)), (qtype, m)
+    # more than 8 extra destinations is refused, M > 16 belongs to the other variants
+    assert lib.dinoml_b200_gguf_gemv_rcr_scatter(x.data_ptr(), w.data_ptr(), None, dst[0].data_ptr(), peers, 9, qtype_of(qtype).value,
+                                                 BF16, 1, n, k, stream) == 8
+    assert lib.dinoml_b200_gguf_gemv_rcr_scatter(x.data_ptr(), w.data_ptr(), None, dst[0].data_ptr(), peers, 3, qtype_of(qtype).value,
+                                                 BF16, 17, n, k, stream) == 8
+
+
+def test_peer_exchange_barrier_and_sum_single_process():
+    dev = torch.device("cuda:0")
+    lib = _native.lib()
+    world, rank, epoch, count = 3, 1, 7, 5000
+    local = torch.zeros(8, dtype=torch.int32, device=dev)
+    local[0], local[2] = epoch, epoch + 1                 # what ranks 0 and 2 would have stored (later epochs count too)
+    fake = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(2)]
+    sig = (ctypes.c_void_p * 3)(fake[0].data_ptr(), local.data_ptr(), fake[1].data_ptr())
+    slots = torch.randn(world, count, device=dev).to(torch.bfloat16)
+    out = torch.empty(count, device=dev, dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = lib.dinoml_b200_peer_exchange(sig, world, rank, epoch, slots.data_ptr(), out.data_ptr(), count, BF16, stream)
+    assert rc == 0, _native.last_error()
+    torch.cuda.synchronize()
+    assert kernels.device_status() == 0
+    want = (slots[0].float() + slots[1].float() + slots[2].float()).to(torch.bfloat16)     # same order, fp32 accumulation
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    for f in fake:                                         # this rank's signal landed in word [rank] of both peers
+        assert f.cpu().tolist() == [0, epoch, 0, 0, 0, 0, 0, 0]
+    # barrier only (count = 0), and argument checks
+    assert lib.dinoml_b200_peer_exchange(sig, world, rank, epoch, None, None, 0, BF16, stream) == 0
+    assert lib.dinoml_b200_peer_exchange(sig, 9, rank, epoch, None, None, 0, BF16, stream) == 8
+    torch.cuda.synchronize()
+    assert kernels.device_status() == 0
