@@ -488,12 +488,37 @@ def run_multi(args):
         gg, gu = (torch.empty(world, m, n_shard, device=dev, dtype=torch.bfloat16) for _ in range(2))
         od = torch.empty(m, hidden, device=dev, dtype=torch.bfloat16)
 
-        def step():
+        def step_nccl():
             for f in ffns:
                 f.gate_up(x, og, ou, gg, gu)
                 f.down_proj(h_slice, od)
 
+        def step_peer():
+            for f in ffns:
+                f.gate_up_peer(x)
+                f.down_proj_peer(h_slice, od)
+
         stream = torch.cuda.current_stream()
+        # Decode sizes go over peer memory (the GEMV kernel stores into every GPU's gather buffer, one small kernel
+        # finishes each collective); NCCL is the fallback and is timed beside it.
+        step, mode, nccl_ms = step_nccl, "nccl", None
+        if m <= 16:
+            try:
+                for f in ffns:
+                    f.enable_peer_path(m, torch.bfloat16, share_with=ffns[0] if f is not ffns[0] else None)
+                step_nccl(); step_peer()
+                torch.cuda.synchronize()
+                ref = od.clone()
+                ffns[-1].down_proj(h_slice, od)
+                torch.cuda.synchronize()
+                # fp32 accumulation in rank order here, NCCL's own order and precision there: equal up to bf16 rounding
+                assert float((ref.float() - od.float()).abs().max()) <= 2e-2 * float(od.float().abs().max()), "peer all-reduce differs from NCCL"
+                nccl_ms = time_steps(step_nccl, max(3, K // 2), W, stream, barrier=dist.barrier)
+                step, mode = step_peer, "peer"
+            except Exception as exc:                        # pragma: no cover - no symmetric memory on this box
+                if rank == 0:
+                    print(f"peer path unavailable ({type(exc).__name__}: {str(exc)[:200]}); using NCCL", file=sys.stderr)
+                step, mode = step_nccl, "nccl"
         clock_ctx = ClockSampler(local) if (m == 1 and rank == 0) else None
         if clock_ctx:
             clock_ctx.__enter__()
@@ -504,7 +529,11 @@ def run_multi(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)            # max over ranks
         ms_step = float(t.item()) / K
         results[m] = {"ms_per_step": ms_step, "ms_per_ffn": ms_step / r, "weight_gbs": r * total_bytes / ms_step / 1e6,
-                      "tflops": r * 6.0 * m * hidden * ffn / ms_step / 1e9}
+                      "tflops": r * 6.0 * m * hidden * ffn / ms_step / 1e9, "collectives": mode}
+        if nccl_ms is not None:
+            tn = torch.tensor([nccl_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tn, op=dist.ReduceOp.MAX)
+            results[m]["nccl_ms_per_ffn"] = float(tn.item()) / max(3, K // 2) / r
         if m == 1:
             clocks = clock_ctx.summary() if clock_ctx else None
         del ffns
@@ -518,16 +547,18 @@ def run_multi(args):
             "metric": "GGUF qmatmul weight GB/s at M=1 (Llama-70B FFN sharded, Q4_K gate/up/down)", "value": r1["weight_gbs"], "unit": "GB/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": r1["ms_per_step"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "cfg5 Llama-3-70B FFN: Q4_K gate,up [28672x8192] N-split + NCCL all-gather; down [8192x28672] K-split + "
-                                   "NCCL all-reduce (bf16); M=1", "parallelism": f"tp{world}", "ffns_per_step": r,
+            "config": {"workload": "cfg5 Llama-3-70B FFN: Q4_K gate,up [28672x8192] N-split + all-gather; down [8192x28672] K-split + "
+                                   "all-reduce (bf16); M=1; collectives: " + ("GEMV epilogue stores into peer GPUs' buffers + one "
+                                   "barrier / barrier-and-sum kernel each" if r1["collectives"] == "peer" else "NCCL"),
+                       "parallelism": f"tp{world}", "ffns_per_step": r,
                        "l2_policy": f"each step walks {r} distinct shard sets ({r * shard_bytes / 1e6:.0f} MB per GPU > 2 x L2)",
                        "timing": "eager launches + NCCL on one stream, CUDA events, max over ranks"},
-            "roofline": {"kernel": "gemv_q4k_mma_kernel + NCCL", "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "roofline": {"kernel": "gemv_q4k_mma_kernel (scatter) + peer_exchange_kernel" if r1["collectives"] == "peer" else "gemv_q4k_mma_kernel + NCCL", "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / peaks["hbm_gbs"], "peak_kind": f"per GPU, of {peak_kind} copy bandwidth", "traffic": None},
             "cpu_baseline": None,
             "e2e": {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "the artifact / session API is single-GPU; the sharded FFN is measured at the kernel + collective level"},
-            "gpu_launches": K * r * 3, "clocks": clocks, "extras": {f"m{m}": v for m, v in results.items()}}))
+            "gpu_launches": K * r * (4 if r1["collectives"] == "peer" else 3), "clocks": clocks, "extras": {f"m{m}": v for m, v in results.items()}}))
     dist.barrier()
     dist.destroy_process_group()
 

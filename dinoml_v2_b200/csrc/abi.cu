@@ -21,6 +21,7 @@ bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k);
 size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k);
 int umma_device_status();
 int peer_device_status();
+int peer_enable_access(int peer_device);
 struct PeerOut { void* ptr[8]; int count; };   // layout of gemv_mma_common.cuh
 int gemm_rcr_mma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                        const PeerOut* peer_out, cudaStream_t s);
@@ -155,6 +156,10 @@ int dinoml_b200_gguf_gemv_rcr_scatter(const void* a, const void* b_quant, const 
     if (peers.ptr[i] == nullptr) return set_error(RC_NULL, "dinoml_b200_gguf_gemv_rcr_scatter");
   return set_error(gemm_rcr_mma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, static_cast<cudaStream_t>(stream)),
                    "dinoml_b200_gguf_gemv_rcr_scatter");
+}
+
+int dinoml_b200_peer_enable_access(int peer_device) {
+  return set_error(peer_enable_access(peer_device), "dinoml_b200_peer_enable_access");
 }
 
 int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, unsigned int epoch, const void* slots, void* out,

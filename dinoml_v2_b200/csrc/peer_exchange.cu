@@ -110,6 +110,18 @@ int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch,
   return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
+// Lets kernels of the current device load / store memory of `peer_device` (needed before a pointer mapped from another
+// GPU is handed to a kernel).  Already enabled counts as success.
+int peer_enable_access(int peer_device) {
+  int dev = -1, can = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return RC_LAUNCH;
+  if (peer_device == dev) return RC_OK;
+  if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || !can) return RC_RANGE;
+  const cudaError_t err = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (err == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return RC_OK; }
+  return err == cudaSuccess ? RC_OK : RC_LAUNCH;
+}
+
 // Reads (and clears) the exchange status word of the current device.
 int peer_device_status() {
   int* status = peer_status_ptr();

@@ -1,27 +1,18 @@
 """Peer-memory buffers for the sharded decode path: one process per GPU on one node, every rank's gather buffer and
-signal words mapped into every process through CUDA IPC (torch's storage sharing), so that a GEMV kernel can store its
-result straight into the other GPUs' memory (`dinoml_b200_gguf_gemv_rcr_scatter`) and a small kernel finishes the
-collective (`dinoml_b200_peer_exchange`).  The reference is single-GPU; nothing here has a counterpart there.
+signal words mapped into every process (torch's symmetric memory: CUDA virtual-memory allocations whose handles the
+ranks exchange and map with access for the local GPU), so that a GEMV kernel can store its result straight into the
+other GPUs' memory (`dinoml_b200_gguf_gemv_rcr_scatter`) and a small kernel finishes the collective
+(`dinoml_b200_peer_exchange`).  The reference is single-GPU; nothing here has a counterpart there.
 
 Only plain peer stores / loads are used: no TMA, no multicast, no multimem.  Every device-side wait is bounded."""
 from __future__ import annotations
 
 import ctypes
+import os
 
 from . import _native
 
-
-def _open_peer_tensor(meta, shape, dtype):
-    """Maps a tensor another rank exported with `_export_tensor` and returns it (a view of the peer GPU's memory)."""
-    import torch
-    storage = torch.UntypedStorage._new_shared_cuda(*meta["storage"])
-    t = torch.empty(0, dtype=dtype, device=storage.device)
-    return t.set_(storage, meta["offset"], shape)
-
-
-def _export_tensor(t):
-    storage = t.untyped_storage()
-    return {"storage": storage._share_cuda_(), "offset": t.storage_offset()}
+_SIGNAL_BYTES = 256      # 8 signal words, padded so that the slots start on a 256-byte boundary
 
 
 class PeerExchange:
@@ -40,29 +31,25 @@ class PeerExchange:
             raise ValueError("peer exchange supports up to 8 ranks")
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dtype, self.slot_elems = dtype, int(slot_elems)
-        # own allocations (not sub-ranges of a cached block that other tensors share)
-        self.slots = torch.zeros(self.world * self.slot_elems, dtype=dtype, device=dev)
-        self.signals = torch.zeros(8, dtype=torch.int32, device=dev)
+        esize = torch.empty(0, dtype=dtype).element_size()
+        # plain peer stores only: keep the allocation off NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        nbytes = _SIGNAL_BYTES + self.world * self.slot_elems * esize
+        self._buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)      # [signals | slot 0 | slot 1 | ...]
+        self._buffer.zero_()
         torch.cuda.synchronize()
-        metas = [None] * self.world
-        dist.all_gather_object(metas, {"slots": _export_tensor(self.slots), "signals": _export_tensor(self.signals),
-                                       "device": dev.index}, group=group)
-        self.peer_slots, self.peer_signals = [], []
-        for r, meta in enumerate(metas):
-            if r == self.rank:
-                self.peer_slots.append(self.slots)
-                self.peer_signals.append(self.signals)
-                continue
-            if not torch.cuda.can_device_access_peer(dev.index, meta["device"]):
-                raise RuntimeError(f"GPU {dev.index} cannot access GPU {meta['device']} as a peer")
-            self.peer_slots.append(_open_peer_tensor(meta["slots"], (self.world * self.slot_elems,), dtype))
-            self.peer_signals.append(_open_peer_tensor(meta["signals"], (8,), torch.int32))
-        self._signal_ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.peer_signals])
-        esize = self.slots.element_size()
+        self._handle = symm_mem.rendezvous(self._buffer, dist.group.WORLD if group is None else group)
+        base = [int(p) for p in self._handle.buffer_ptrs]                           # every rank's buffer, mapped here
+        if len(base) != self.world or base[self.rank] != self._buffer.data_ptr():
+            raise RuntimeError("symmetric memory rendezvous returned an unexpected mapping")
+        self.signals = self._buffer[:32].view(torch.int32)
+        self.slots = self._buffer[_SIGNAL_BYTES:].view(dtype)
+        self._signal_ptrs = (ctypes.c_void_p * self.world)(*base)
         others = [r for r in range(self.world) if r != self.rank]
         # where THIS rank's result lives in every other rank's buffer
         self._peer_dst = (ctypes.c_void_p * max(1, len(others)))(
-            *[self.peer_slots[r].data_ptr() + self.rank * self.slot_elems * esize for r in others])
+            *[base[r] + _SIGNAL_BYTES + self.rank * self.slot_elems * esize for r in others])
         self._n_peers = len(others)
         self.epoch = 0
         dist.barrier(group=group)          # every rank has mapped every buffer before anyone writes

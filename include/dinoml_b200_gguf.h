@@ -111,9 +111,13 @@ DINOML_B200_API int dinoml_b200_gguf_device_status(void);
  * kernel publishes "rank's earlier stores are complete" to every peer, waits (bounded, about a second; a rank that
  * never arrives sets device status 6 instead of hanging the GPU) for every peer's signal, and, if count > 0, writes
  * out[i] = sum over r < world of slots[r * count + i] (fp32 accumulation, fixed order): barrier only = all-gather
- * completion, barrier + sum = one-shot all-reduce of GEMV partial results. */
+ * completion, barrier + sum = one-shot all-reduce of GEMV partial results.
+ * dinoml_b200_peer_enable_access: cudaDeviceEnablePeerAccess for the current device towards `peer_device` (success if
+ * it was enabled already; code 8 if the GPUs are not peers).  Call it once per peer before passing that GPU's memory
+ * to the two entry points above. */
 DINOML_B200_API int dinoml_b200_gguf_gemv_rcr_scatter(const void* a, const void* b_quant, const void* bias, void* c, void* const* peer_c,
                                                       int n_peers, int qtype, int dtype, int m, int n, int k, void* stream);
+DINOML_B200_API int dinoml_b200_peer_enable_access(int peer_device);
 DINOML_B200_API int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, unsigned int epoch, const void* slots,
                                               void* out, int64_t count, int dtype, void* stream);
 

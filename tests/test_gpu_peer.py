@@ -39,6 +39,24 @@ def test_scatter_gemv_writes_every_destination(qtype, k):
                                                  BF16, 17, n, k, stream) == 8
 
 
+def test_scatter_gemv_full_size_shard_shapes():
+    """The stacked gate/up shard [2 * 14336, 8192] and the down shard [8192, 14336] of the 2-GPU sharded FFN."""
+    dev = torch.device("cuda:0")
+    lib = _native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    for (n, k) in ((28672, 8192), (8192, 14336)):
+        w = S.random_blocks_torch("Q4_K", n, k, 21, dev)
+        for m in (1, 4):
+            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            want = kernels.gemm_rcr(x, w, "Q4_K", variant="mma")
+            dst = [torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(2)]
+            peers = (ctypes.c_void_p * 1)(dst[1].data_ptr())
+            rc = lib.dinoml_b200_gguf_gemv_rcr_scatter(x.data_ptr(), w.data_ptr(), None, dst[0].data_ptr(), peers, 1, 12, BF16, m, n, k, stream)
+            assert rc == 0, _native.last_error()
+            torch.cuda.synchronize()
+            assert torch.equal(dst[0].view(torch.int16), want.view(torch.int16)) and torch.equal(dst[1].view(torch.int16), want.view(torch.int16))
+
+
 def test_peer_exchange_barrier_and_sum_single_process():
     dev = torch.device("cuda:0")
     lib = _native.lib()
