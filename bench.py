@@ -502,7 +502,7 @@ def run_multi(args):
         # Decode sizes go over peer memory (the GEMV kernel stores into every GPU's gather buffer, one small kernel
         # finishes each collective); NCCL is the fallback and is timed beside it.
         step, mode, nccl_ms = step_nccl, "nccl", None
-        if m <= 16:
+        if m <= 8:                                          # the sizes the mma GEMV serves best (M = 9..16 run on the tcgen05 kernel)
             try:
                 for f in ffns:
                     f.enable_peer_path(m, torch.bfloat16, share_with=ffns[0] if f is not ffns[0] else None)
@@ -552,7 +552,7 @@ def run_multi(args):
                                    "barrier / barrier-and-sum kernel each" if r1["collectives"] == "peer" else "NCCL"),
                        "parallelism": f"tp{world}", "ffns_per_step": r,
                        "l2_policy": f"each step walks {r} distinct shard sets ({r * shard_bytes / 1e6:.0f} MB per GPU > 2 x L2)",
-                       "timing": "eager launches + NCCL on one stream, CUDA events, max over ranks"},
+                       "timing": "eager launches on one stream, CUDA events, max over ranks"},
             "roofline": {"kernel": "gemv_q4k_mma_kernel (scatter) + peer_exchange_kernel" if r1["collectives"] == "peer" else "gemv_q4k_mma_kernel + NCCL", "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / peaks["hbm_gbs"], "peak_kind": f"per GPU, of {peak_kind} copy bandwidth", "traffic": None},
             "cpu_baseline": None,

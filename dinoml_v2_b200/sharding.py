@@ -66,7 +66,7 @@ class ShardedFFN:
             dist.all_gather_into_tensor(gathered_up.view(-1, out_up.shape[-1]), out_up, group=self.group)
         return gathered_gate, gathered_up
 
-    # ---- peer-memory path (decode, M <= 16) ----------------------------------------------------------------------
+    # ---- peer-memory path (decode, M <= 16; pays off for M <= 8, where the mma GEMV is the kernel of choice) ----------------------------------------------------------------------
     def enable_peer_path(self, m: int, dtype, share_with=None):
         """Stacks gate and up into one [2 * ffn / world, hidden] weight (one launch, one gather) and maps the exchange
         buffers of all ranks (or reuses those of `share_with`, another ShardedFFN of the same shape that runs on the
