@@ -175,6 +175,8 @@ class Session:
         self._handle = ctypes.c_void_p()
         module._check(self._lib.dino_session_create(module._handle, ctypes.byref(self._handle)))
         self._pinned: dict[str, Any] = {}
+        self._numpy_plans: dict[Any, dict[str, Any]] = {}
+        self._user_stream = 0
 
     def close(self) -> None:
         if self._handle:
@@ -182,7 +184,11 @@ class Session:
             self._handle = None
 
     def set_stream(self, stream_ptr: int | None) -> None:
-        self.module._check(self._lib.dino_session_set_stream(self._handle, ctypes.c_void_p(stream_ptr or 0)))
+        self._user_stream = stream_ptr or 0
+        self._set_stream_raw(self._user_stream)
+
+    def _set_stream_raw(self, stream_ptr: int) -> None:
+        self.module._check(self._lib.dino_session_set_stream(self._handle, ctypes.c_void_p(stream_ptr)))
 
     # -- shapes
     def _output_shapes(self, in_shapes: Mapping[str, tuple[int, ...]]) -> dict[str, tuple[int, ...]]:
@@ -222,28 +228,78 @@ class Session:
         return dict(outputs)
 
     def run_numpy(self, inputs: Mapping[str, np.ndarray]) -> dict[str, np.ndarray]:
-        """Host arrays in, host arrays out: pinned staging, H2D, run, D2H.  bfloat16 travels as uint16 bit patterns or as
-        float32 arrays (rounded to nearest even), and comes back as float32."""
+        """Host arrays in, host arrays out.  All inputs of a call are packed into ONE pinned arena and go to the device
+        in one copy, the module runs on the same stream, all outputs come back in one copy from one device arena, and
+        the host waits once.  Arenas, tensor descriptors and the stream are cached per set of input shapes.
+        bfloat16 travels as uint16 bit patterns or as float32 arrays (rounded to nearest even), and comes back as
+        float32; float16 / float32 keep their numpy dtypes."""
+        meta = self.module.metadata
+        arrays = {spec["name"]: np.asarray(inputs[spec["name"]]) for spec in meta["inputs"]}
+        key = tuple((name, arr.shape) for name, arr in arrays.items())
+        plan = self._numpy_plans.get(key)
+        if plan is None:
+            plan = self._numpy_plans[key] = self._make_numpy_plan(arrays)
+        for spec in meta["inputs"]:
+            arr, view = arrays[spec["name"]], plan["in_views"][spec["name"]]
+            if spec["dtype"] == "bfloat16":
+                view[...] = arr if arr.dtype == np.uint16 else _f32_to_bf16_bits(arr)
+            else:
+                view[...] = arr                                   # numpy converts to the view's dtype
+        stream = plan["stream"]
+        import torch
+        # run on the plan's stream: the copies and the kernels are ordered on it and the host waits once at the end
+        self._set_stream_raw(stream.cuda_stream)
+        try:
+            with torch.cuda.stream(stream):
+                plan["dev_in"].copy_(plan["pin_in"], non_blocking=True)
+                self.module._check(self._lib.dino_session_run(self._handle, plan["ins"], len(plan["ins"]), plan["outs"], len(plan["outs"])))
+                plan["pin_out"].copy_(plan["dev_out"], non_blocking=True)
+            stream.synchronize()
+        finally:
+            self._set_stream_raw(self._user_stream)
+        out = {}
+        for o in meta["outputs"]:
+            view = plan["out_views"][o["name"]]
+            if o["dtype"] == "bfloat16":
+                out[o["name"]] = (view.astype(np.uint32) << np.uint32(16)).view(np.float32)
+            else:
+                out[o["name"]] = view.copy()
+        return out
+
+    def _make_numpy_plan(self, arrays: Mapping[str, np.ndarray]) -> dict[str, Any]:
         import torch
         meta = self.module.metadata
-        dev_in = {}
-        for spec in meta["inputs"]:
-            arr = np.asarray(inputs[spec["name"]])
-            tdt = getattr(torch, spec["dtype"])
-            key = (spec["name"], arr.shape)
-            if spec["dtype"] == "bfloat16" and arr.dtype == np.uint16:
-                host = torch.from_numpy(arr.view(np.int16)).view(torch.bfloat16)
-            else:
-                host = torch.from_numpy(np.ascontiguousarray(arr)).to(tdt)
-            pin = self._pinned.get(key)
-            if pin is None or pin.dtype != tdt:
-                pin = torch.empty(arr.shape, dtype=tdt).pin_memory()
-                self._pinned[key] = pin
-            pin.copy_(host)
-            dev_in[spec["name"]] = pin.to("cuda", non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        outs = self.run_torch(dev_in)
-        return {k: (v.float() if v.dtype == torch.bfloat16 else v).cpu().numpy() for k, v in outs.items()}
+        np_dt = {"bfloat16": np.uint16, "float16": np.float16, "float32": np.float32}
+        esize = {"bfloat16": 2, "float16": 2, "float32": 4}
+        out_shapes = self._output_shapes({k: tuple(v.shape) for k, v in arrays.items()})
+
+        def layout(entries):
+            offs, total = {}, 0
+            for name, shape, dtype in entries:
+                offs[name] = total
+                total += -(-int(np.prod(shape)) * esize[dtype] // 256) * 256      # 256-byte aligned slices
+            return offs, max(total, 256)
+
+        in_entries = [(i["name"], tuple(arrays[i["name"]].shape), i["dtype"]) for i in meta["inputs"]]
+        out_entries = [(o["name"], tuple(out_shapes[o["name"]]), o["dtype"]) for o in meta["outputs"]]
+        in_off, in_bytes = layout(in_entries)
+        out_off, out_bytes = layout(out_entries)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        plan = {"pin_in": torch.empty(in_bytes, dtype=torch.uint8).pin_memory(), "dev_in": torch.empty(in_bytes, dtype=torch.uint8, device=dev),
+                "pin_out": torch.empty(out_bytes, dtype=torch.uint8).pin_memory(), "dev_out": torch.empty(out_bytes, dtype=torch.uint8, device=dev),
+                "stream": torch.cuda.Stream(device=dev), "keep": []}
+        host_in, host_out = plan["pin_in"].numpy(), plan["pin_out"].numpy()
+
+        def views(entries, offs, host):
+            return {name: host[offs[name]:offs[name] + int(np.prod(shape)) * esize[dtype]].view(np_dt[dtype]).reshape(shape)
+                    for name, shape, dtype in entries}
+
+        plan["in_views"], plan["out_views"] = views(in_entries, in_off, host_in), views(out_entries, out_off, host_out)
+        plan["ins"] = (_DinoTensor * len(in_entries))(*[_tensor_struct(plan["dev_in"].data_ptr() + in_off[n], s, d, plan["keep"])
+                                                        for n, s, d in in_entries])
+        plan["outs"] = (_DinoTensor * len(out_entries))(*[_tensor_struct(plan["dev_out"].data_ptr() + out_off[n], s, d, plan["keep"])
+                                                          for n, s, d in out_entries])
+        return plan
 
     # -- benchmark
     def benchmark_torch(self, inputs: Mapping[str, Any], warmup: int = 5, iterations: int = 20) -> dict[str, Any]:
@@ -260,6 +316,13 @@ class Session:
         self.module._check(self._lib.dino_session_benchmark(self._handle, ins, len(ins), outs, len(outs), warmup, iterations, ms, iterations))
         return summarize_ms(list(ms), native_entrypoint="dino_session_benchmark", timing_source="cuda_events", graph_replay=True,
                             warmup=warmup)
+
+
+def _f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even bfloat16 storage of a float array (src/dinoml/ir.py:68-73)."""
+    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    lsb = (bits >> np.uint32(16)) & np.uint32(1)
+    return ((bits + np.uint32(0x7FFF) + lsb) >> np.uint32(16)).astype(np.uint16)
 
 
 def summarize_ms(values: list[float], **metadata) -> dict[str, Any]:
