@@ -502,7 +502,7 @@ def run_multi(args):
         # Decode sizes go over peer memory (the GEMV kernel stores into every GPU's gather buffer, one small kernel
         # finishes each collective); NCCL is the fallback and is timed beside it.
         step, mode, nccl_ms = step_nccl, "nccl", None
-        if m <= 8:                                          # the sizes the mma GEMV serves best (M = 9..16 run on the tcgen05 kernel)
+        if m <= 64:                                         # decode and small-batch sizes: mma GEMV or tcgen05 kernel, both with a scatter epilogue
             try:
                 for f in ffns:
                     f.enable_peer_path(m, torch.bfloat16, share_with=ffns[0] if f is not ffns[0] else None)

@@ -25,6 +25,8 @@ int peer_enable_access(int peer_device);
 struct PeerOut { void* ptr[8]; int count; };   // layout of gemv_mma_common.cuh
 int gemm_rcr_mma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                        const PeerOut* peer_out, cudaStream_t s);
+int gemm_rcr_umma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                        const PeerOut* peer_out, cudaStream_t s);
 int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch, const void* slots, void* out, int64_t count, int dtype,
                   cudaStream_t s);
 int gemm_rcr_umma_static(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
@@ -156,6 +158,22 @@ int dinoml_b200_gguf_gemv_rcr_scatter(const void* a, const void* b_quant, const 
     if (peers.ptr[i] == nullptr) return set_error(RC_NULL, "dinoml_b200_gguf_gemv_rcr_scatter");
   return set_error(gemm_rcr_mma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, static_cast<cudaStream_t>(stream)),
                    "dinoml_b200_gguf_gemv_rcr_scatter");
+}
+
+int dinoml_b200_gguf_gemm_rcr_scatter(const void* a, const void* b_quant, const void* bias, void* c, void* const* peer_c, int n_peers,
+                                      int qtype, int dtype, int m, int n, int k, int variant, void* stream) {
+  const char* where = "dinoml_b200_gguf_gemm_rcr_scatter";
+  if (n_peers < 0 || n_peers > 8 || (n_peers > 0 && peer_c == nullptr)) return set_error(RC_RANGE, where);
+  PeerOut peers;
+  for (int i = 0; i < 8; ++i) peers.ptr[i] = i < n_peers ? peer_c[i] : nullptr;
+  peers.count = n_peers;
+  for (int i = 0; i < n_peers; ++i)
+    if (peers.ptr[i] == nullptr) return set_error(RC_NULL, where);
+  if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, n, k);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (variant == DINOML_B200_GGUF_VARIANT_MMA) return set_error(gemm_rcr_mma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, s), where);
+  if (variant == DINOML_B200_GGUF_VARIANT_UMMA) return set_error(gemm_rcr_umma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, s), where);
+  return set_error(RC_RANGE, where);     // the simt variant has no scatter epilogue
 }
 
 int dinoml_b200_peer_enable_access(int peer_device) {

@@ -44,7 +44,7 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "gguf_common.cuh"
+#include "gemv_mma_common.cuh"
 
 namespace b200gguf {
 
@@ -240,6 +240,7 @@ struct Params {
   int m, n, k;
   int m_tiles;            // activation tiles per weight panel
   long long units;        // output tiles x super-blocks
+  PeerOut peers;          // extra destinations of the output (SCATTER kernels only)
 };
 
 // Stream-K work split.  The work of the launch is a line of units (tile t, super-block sb), tile-major; CTA c of G owns
@@ -271,7 +272,8 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
 }
 __device__ __forceinline__ void st_release(int* p, int v) { asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory"); }
 
-template <int QT, typename T, int BM>
+// SCATTER: finished tiles are also stored to the extra destinations in p.peers (other GPUs' gather buffers).
+template <int QT, typename T, int BM, bool SCATTER>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const Params p) {
   using P = Pair<T>;
@@ -413,7 +415,15 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             T* dst = static_cast<T*>(p.out) + int64_t(m0 + col) * p.n + n_row;
 #pragma unroll
             for (int j = 0; j < CH; ++j)
-              if (m0 + col + j < p.m) dst[int64_t(j) * p.n] = P::cvt(__uint_as_float(r[j]) + bias_v);
+              if (m0 + col + j < p.m) {
+                const T v = P::cvt(__uint_as_float(r[j]) + bias_v);
+                dst[int64_t(j) * p.n] = v;
+                if (SCATTER) {
+#pragma unroll
+                  for (int pi = 0; pi < 8; ++pi)
+                    if (pi < p.peers.count) static_cast<T*>(p.peers.ptr[pi])[int64_t(m0 + col + j) * p.n + n_row] = v;
+                }
+              }
           }
         }
       }
@@ -722,7 +732,7 @@ struct Scratch { float* workspace; int* flags; int* status; };
 
 template <int QT, typename T, int BM>
 static int launch(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const Plan& pl, Scratch sc,
-                  cudaStream_t s) {
+                  const PeerOut& peers, cudaStream_t s) {
   EncodeTiledFn enc = encode_tiled();
   if (enc == nullptr) return RC_LAUNCH;
   const cuuint32_t estr[2] = {1, 1};
@@ -744,13 +754,14 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return RC_LAUNCH;
   }
-  auto kern = gemm_umma_kernel<QT, T, BM>;
+  const bool scatter = peers.count > 0;
+  auto kern = scatter ? gemm_umma_kernel<QT, T, BM, true> : gemm_umma_kernel<QT, T, BM, false>;
   constexpr size_t smem = smem_bytes<QT, BM>();
   static_assert(smem <= size_t(kSmemBudget), "shared-memory rings exceed the per-CTA limit");
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[scatter]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
-    attr_set = true;
+    attr_set[scatter] = true;
   }
   Params p;
   p.bias = bias;
@@ -761,6 +772,7 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
   p.m = m; p.n = n; p.k = k;
   p.m_tiles = pl.m_tiles;
   p.units = pl.units;
+  p.peers = peers;
   kern<<<pl.ctas, kThreads, smem, s>>>(x_map, w_map, p);
   return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
@@ -799,7 +811,8 @@ static int static_scratch(Scratch* out) {
 }
 
 template <int QT, typename T>
-static int launch_bm(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, bool use_static, cudaStream_t s) {
+static int launch_bm(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, bool use_static, const PeerOut& peers,
+                     cudaStream_t s) {
   const Plan pl = make_plan(m, n, k);
   Scratch sc{nullptr, nullptr, nullptr};
   if (use_static) {
@@ -813,9 +826,9 @@ static int launch_bm(const void* a, const void* b, const void* bias, void* c, in
     sc.flags = st->status + 1;
   }
   switch (pl.bm) {
-    case 64: return launch<QT, T, 64>(a, b, bias, c, m, n, k, pl, sc, s);
-    case 128: return launch<QT, T, 128>(a, b, bias, c, m, n, k, pl, sc, s);
-    default: return launch<QT, T, 256>(a, b, bias, c, m, n, k, pl, sc, s);
+    case 64: return launch<QT, T, 64>(a, b, bias, c, m, n, k, pl, sc, peers, s);
+    case 128: return launch<QT, T, 128>(a, b, bias, c, m, n, k, pl, sc, peers, s);
+    default: return launch<QT, T, 256>(a, b, bias, c, m, n, k, pl, sc, peers, s);
   }
 }
 
@@ -834,7 +847,7 @@ size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k) {
 }
 
 static int gemm_rcr_umma_impl(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
-                              bool use_static, cudaStream_t s) {
+                              bool use_static, const PeerOut& peers, cudaStream_t s) {
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
@@ -842,22 +855,28 @@ static int gemm_rcr_umma_impl(const void* a, const void* b, const void* bias, vo
   if ((int64_t(k) * 2) & 15) return RC_ALIGN;                       // activation row pitch
   if ((int64_t(k / 256) * (qtype == QTYPE_Q4_K ? 144 : 210)) & 15) return RC_ALIGN;   // packed-weight row pitch
   if (dtype == DINO_BF16)
-    return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, s)
-                               : umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, s);
-  return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, use_static, s)
-                             : umma::launch_bm<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, use_static, s);
+    return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s)
+                               : umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
+  return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s)
+                             : umma::launch_bm<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
 }
 
 int gemm_rcr_umma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                   cudaStream_t s) {
-  return gemm_rcr_umma_impl(a, b, bias, c, qtype, dtype, m, n, k, false, s);
+  return gemm_rcr_umma_impl(a, b, bias, c, qtype, dtype, m, n, k, false, no_peers(), s);
+}
+
+// Same kernel, finished tiles also stored to the extra destinations (see PeerOut).
+int gemm_rcr_umma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
+                        const PeerOut* peers, cudaStream_t s) {
+  return gemm_rcr_umma_impl(a, b, bias, c, qtype, dtype, m, n, k, false, peers != nullptr ? *peers : no_peers(), s);
 }
 
 // Same kernel, scratch in the library's static device array: no cudaMalloc / cudaFree anywhere on this path.
 int gemm_rcr_umma_static(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                          cudaStream_t s) {
   if (m < 17) return RC_RANGE;   // small M belongs to the GEMV kernels, which need no scratch
-  return gemm_rcr_umma_impl(a, b, bias, c, qtype, dtype, m, n, k, true, s);
+  return gemm_rcr_umma_impl(a, b, bias, c, qtype, dtype, m, n, k, true, no_peers(), s);
 }
 size_t gemm_umma_static_scratch_bytes() { return umma::kStaticScratchBytes; }
 

@@ -62,8 +62,8 @@ class PeerExchange:
         """[world, slot_elems] view of the local buffer (valid after `finish_gather`)."""
         return self.slots.view(self.world, self.slot_elems)
 
-    def scatter_gemv(self, a, b_quant, qtype, bias=None):
-        """y = a @ dequant(b_quant)^T (M <= 16) stored into slot [rank] of every rank's buffer, by one kernel."""
+    def scatter_gemv(self, a, b_quant, qtype, bias=None, variant: str = "auto"):
+        """y = a @ dequant(b_quant)^T stored into slot [rank] of every rank's buffer, by one kernel (mma or umma variant)."""
         import torch
 
         from .gguf_blocks import qtype_of
@@ -73,11 +73,11 @@ class PeerExchange:
         if m * n != self.slot_elems:
             raise ValueError(f"result [{m}, {n}] does not fill a slot of {self.slot_elems} elements")
         lib = _native.lib()
-        rc = lib.dinoml_b200_gguf_gemv_rcr_scatter(
+        rc = lib.dinoml_b200_gguf_gemm_rcr_scatter(
             a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, self.local_slot().data_ptr(),
             self._peer_dst, self._n_peers, q.value, _native.DINO_DTYPE[str(a.dtype).replace("torch.", "")], m, n, k,
-            torch.cuda.current_stream().cuda_stream)
-        _native.check(rc, "dinoml_b200_gguf_gemv_rcr_scatter")
+            _native.VARIANTS[variant], torch.cuda.current_stream().cuda_stream)
+        _native.check(rc, "dinoml_b200_gguf_gemm_rcr_scatter")
 
     def _exchange(self, out, count):
         import torch

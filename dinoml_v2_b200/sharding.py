@@ -7,7 +7,7 @@ The reference has no distributed code at all; this covers the Llama-70B-shaped F
   EVERY row, a one-time strided repack at load into a dense [N, nb/G] block matrix, computes a partial [M, N] and the
   ranks all-reduce.  The N-shard of gate/up on rank r is exactly the K-slice rank r needs for down.
 Two ways to finish the collectives: torch.distributed (NCCL over NVLink) on the compute stream, or - for decode
-(M <= 16) - the peer-memory path of `peer.PeerExchange`, where gate and up are one stacked weight, the GEMV kernels
+and small batches - the peer-memory path of `peer.PeerExchange`, where gate and up are one stacked weight, the GEMV kernels
 store their results straight into every GPU's gather buffer and one small kernel per collective does the barrier
 (all-gather) or the barrier + sum (all-reduce)."""
 from __future__ import annotations
@@ -66,7 +66,7 @@ class ShardedFFN:
             dist.all_gather_into_tensor(gathered_up.view(-1, out_up.shape[-1]), out_up, group=self.group)
         return gathered_gate, gathered_up
 
-    # ---- peer-memory path (decode, M <= 16; pays off for M <= 8, where the mma GEMV is the kernel of choice) ----------------------------------------------------------------------
+    # ---- peer-memory path (decode and small batches; the variant is chosen by shape as for gemm_rcr) ----------------------------------------------------------------------
     def enable_peer_path(self, m: int, dtype, share_with=None):
         """Stacks gate and up into one [2 * ffn / world, hidden] weight (one launch, one gather) and maps the exchange
         buffers of all ranks (or reuses those of `share_with`, another ShardedFFN of the same shape that runs on the

@@ -106,6 +106,8 @@ DINOML_B200_API int dinoml_b200_gguf_device_status(void);
  * dinoml_b200_gguf_gemm_rcr with variant = MMA) whose epilogue stores the [M, N] result to `c` AND to `n_peers` (<= 8)
  * further buffers - the same slot of a gather buffer on the other GPUs, mapped into this process (CUDA IPC / peer
  * access).  One kernel computes and distributes; there is no separate all-gather.
+ * dinoml_b200_gguf_gemm_rcr_scatter: the same for any M - `variant` as in dinoml_b200_gguf_gemm_rcr (AUTO picks mma or
+ * umma by shape; shapes only the simt variant serves are refused with code 8).
  * dinoml_b200_peer_exchange: what remains of the collective.  signal_ptrs[r] = the 8-word signal array of rank r
  * (signal_ptrs[rank] is local, zero-initialised once); every rank calls with the same, ever increasing `epoch`.  The
  * kernel publishes "rank's earlier stores are complete" to every peer, waits (bounded, about a second; a rank that
@@ -117,6 +119,8 @@ DINOML_B200_API int dinoml_b200_gguf_device_status(void);
  * to the two entry points above. */
 DINOML_B200_API int dinoml_b200_gguf_gemv_rcr_scatter(const void* a, const void* b_quant, const void* bias, void* c, void* const* peer_c,
                                                       int n_peers, int qtype, int dtype, int m, int n, int k, void* stream);
+DINOML_B200_API int dinoml_b200_gguf_gemm_rcr_scatter(const void* a, const void* b_quant, const void* bias, void* c, void* const* peer_c,
+                                                      int n_peers, int qtype, int dtype, int m, int n, int k, int variant, void* stream);
 DINOML_B200_API int dinoml_b200_peer_enable_access(int peer_device);
 DINOML_B200_API int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, unsigned int epoch, const void* slots,
                                               void* out, int64_t count, int dtype, void* stream);

@@ -57,6 +57,31 @@ def test_scatter_gemv_full_size_shard_shapes():
             assert torch.equal(dst[0].view(torch.int16), want.view(torch.int16)) and torch.equal(dst[1].view(torch.int16), want.view(torch.int16))
 
 
+def test_scatter_gemm_umma_writes_every_destination():
+    """The tcgen05 kernel's scatter epilogue (finished tiles, including tiles finished after a stream-K reduction)."""
+    dev = torch.device("cuda:0")
+    lib = _native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    for (qtype, m, n, k) in (("Q4_K", 16, 2048, 1024), ("Q4_K", 64, 384, 4096), ("Q6_K", 200, 130, 2048)):
+        w = torch.from_numpy(S.random_blocks(qtype, n, k, seed=31)).to(dev)
+        x = torch.from_numpy(S.random_activations(m, k, 32, "float32")).to(dev).to(torch.bfloat16)
+        want = kernels.gemm_rcr(x, w, qtype, variant="umma")
+        dst = [torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(3)]
+        peers = (ctypes.c_void_p * 2)(dst[1].data_ptr(), dst[2].data_ptr())
+        rc = lib.dinoml_b200_gguf_gemm_rcr_scatter(x.data_ptr(), w.data_ptr(), None, dst[0].data_ptr(), peers, 2, qtype_of(qtype).value, BF16,
+                                                   m, n, k, 0, stream)
+        assert rc == 0, _native.last_error()
+        torch.cuda.synchronize()
+        assert kernels.device_status() == 0
+        for t in dst:
+            assert torch.equal(t.view(torch.int16), want.view(torch.int16)), (qtype, m, n, k)
+    # a shape only the simt variant serves has no scatter epilogue
+    w8 = torch.from_numpy(S.random_blocks("Q8_0", 64, 256, seed=1)).to(dev)
+    x8 = torch.zeros(1, 256, device=dev, dtype=torch.bfloat16)
+    y8 = torch.zeros(1, 64, device=dev, dtype=torch.bfloat16)
+    assert lib.dinoml_b200_gguf_gemm_rcr_scatter(x8.data_ptr(), w8.data_ptr(), None, y8.data_ptr(), peers, 2, 8, BF16, 1, 64, 256, 0, stream) == 8
+
+
 def test_peer_exchange_barrier_and_sum_single_process():
     dev = torch.device("cuda:0")
     lib = _native.lib()
