@@ -4,11 +4,15 @@
 // src/dinoml/templates/gpu_module.cu.j2:35-42 and calls from src/dinoml/lowering/ops/gemm.py:745,
 // keeping its name and argument list so the generated launch text links unchanged.
 //
-// HBM-bound and write-dominated (Q4_K -> f32 writes 7.1 bytes per byte read).  One thread owns one
-// "unit" of 8 consecutive outputs: it reads the few packed bytes that unit needs (the block header
-// is shared by the 32 units of a K-quant block and is served by L1), decodes with explicitly rounded
-// fp32 operations, and issues one 32-byte (f32) or 16-byte (f16/bf16) store.  Consecutive threads own
-// consecutive units, so a warp writes 1 KiB (f32) contiguous per store instruction.
+// HBM-bound and write-dominated (Q4_K -> f32 writes 7.1 bytes per byte read).  Every packed byte is loaded once:
+//   Q4_K: a thread owns 8 quant bytes = the low nibbles (8 weights of sub-block 2g) and the high nibbles (8 weights
+//         of sub-block 2g+1) of one 64-weight group; 16 threads per block, the 16-byte header is one broadcast load;
+//   Q6_K: a thread owns 8 positions l of one 128-weight half: 8 ql bytes, the 8 ql bytes 32 further, 8 qh bytes ->
+//         four runs of 8 weights (one per quad); 8 threads per block;
+//   Q8_0: a thread owns 8 consecutive weights.
+// Decoding uses explicitly rounded fp32 operations (bit-exact), and each run of 8 outputs is one 32-byte (f32) or
+// 16-byte (f16 / bf16) streaming store.  Float outputs (write bound) keep the simpler one-unit-per-thread kernel, which
+// measured faster there (Q4_K -> f32 4.77 vs 4.35 TB/s); 16-bit outputs gain 8 % (Q4_K) to 35 % (Q6_K).
 #include "gguf_common.cuh"
 
 namespace b200gguf {
@@ -47,8 +51,8 @@ template <> struct Pack8<__nv_bfloat16> {
 constexpr int kDequantThreads = 256;
 constexpr int kUnitsPerThread = 4;
 
-// total_units = rows * n_per_row / 8.  Units are numbered in output order, so unit u covers
-// outputs [8u, 8u+8) and lives in block u / (kBlock/8).
+// Q8_0 and every float output: total_units = rows * n_per_row / 8.  Units are numbered in output order, so unit u
+// covers outputs [8u, 8u+8) and lives in block u / (kBlock/8).
 template <int QT, typename T>
 __global__ void __launch_bounds__(kDequantThreads)
 dequant_rows_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_t total_units) {
@@ -67,9 +71,108 @@ dequant_rows_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_t
   }
 }
 
+// Q4_K: item = (block, 64-weight group g, 8-byte piece p of the group's 32 quant bytes); 16 items per block.
+// Formula per weight: (d * sc) * q - (dmin * m), each product / difference rounded (as decode8<QTYPE_Q4_K>).
+template <typename T>
+__global__ void __launch_bounds__(kDequantThreads)
+dequant_q4k_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_t total_items) {
+  const int64_t base = (int64_t(blockIdx.x) * 2) * kDequantThreads + threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int64_t it = base + int64_t(i) * kDequantThreads;
+    if (it >= total_items) continue;
+    const int64_t blk = it >> 4;
+    const int g = int(it & 15) >> 2, piece = int(it & 3);
+    const uint8_t* b = in + blk * 144;                     // 4-byte aligned (checked by the launcher)
+    const uint32_t* hdr = reinterpret_cast<const uint32_t*>(b);
+    const uint32_t dd = __ldg(hdr), s0 = __ldg(hdr + 1), s1 = __ldg(hdr + 2), s2 = __ldg(hdr + 3);
+    const float d = half_bits_to_float(uint16_t(dd & 0xffffu)), dmin = half_bits_to_float(uint16_t(dd >> 16));
+    // 6-bit (scale, min) of sub-blocks 2g (low nibbles) and 2g+1 (high nibbles): bytes j, j+4 for j < 4, split fields after
+    int sc[2], mn[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int j = 2 * g + h;
+      if (j < 4) {
+        sc[h] = int(s0 >> (8 * j)) & 63;
+        mn[h] = int(s1 >> (8 * j)) & 63;
+      } else {
+        sc[h] = (int(s2 >> (8 * (j - 4))) & 0x0f) | ((int(s0 >> (8 * (j - 4))) >> 6 & 3) << 4);
+        mn[h] = (int(s2 >> (8 * (j - 4))) >> 4 & 0x0f) | ((int(s1 >> (8 * (j - 4))) >> 6 & 3) << 4);
+      }
+    }
+    const uint32_t* qp = reinterpret_cast<const uint32_t*>(b + 16 + 32 * g + 8 * piece);
+    const uint2 q = make_uint2(__ldg(qp), __ldg(qp + 1));
+    T* dst = out + blk * 256 + 64 * g + 8 * piece;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float ds = __fmul_rn(d, float(sc[h])), dm = __fmul_rn(dmin, float(mn[h]));
+      const uint32_t q0 = q.x >> (4 * h), q1 = q.y >> (4 * h);
+      float w[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        w[e] = __fsub_rn(__fmul_rn(ds, float((q0 >> (8 * e)) & 0x0f)), dm);
+        w[4 + e] = __fsub_rn(__fmul_rn(ds, float((q1 >> (8 * e)) & 0x0f)), dm);
+      }
+      Pack8<T>::store(dst + 32 * h, w);
+    }
+  }
+}
+
+// Q6_K: item = (block, 128-weight half hb, 8 positions l0..l0+7); 8 items per block.  Weight 128*hb + 32*quad + l is
+// (d * scale[8*hb + 2*quad + l/16]) * (q - 32) with q = nibble of ql | two bits of qh (as decode8<QTYPE_Q6_K>).
+template <typename T>
+__global__ void __launch_bounds__(kDequantThreads)
+dequant_q6k_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_t total_items) {
+  const int64_t base = (int64_t(blockIdx.x) * 2) * kDequantThreads + threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int64_t it = base + int64_t(i) * kDequantThreads;
+    if (it >= total_items) continue;
+    const int64_t blk = it >> 3;
+    const int hb = int(it & 7) >> 2, l0 = 8 * int(it & 3);
+    const uint8_t* b = in + blk * 210;                     // 2-byte aligned
+    const float d = half_bits_to_float(uint16_t(ld_u16(b + 208)));
+    const uint32_t la[2] = {ld_u32_a2(b + 64 * hb + l0), ld_u32_a2(b + 64 * hb + l0 + 4)};
+    const uint32_t lb[2] = {ld_u32_a2(b + 64 * hb + 32 + l0), ld_u32_a2(b + 64 * hb + 32 + l0 + 4)};
+    const uint32_t hh[2] = {ld_u32_a2(b + 128 + 32 * hb + l0), ld_u32_a2(b + 128 + 32 * hb + l0 + 4)};
+    const int8_t* scales = reinterpret_cast<const int8_t*>(b + 192) + 8 * hb + (l0 >> 4);
+    T* dst = out + blk * 256 + 128 * hb + l0;
+#pragma unroll
+    for (int quad = 0; quad < 4; ++quad) {
+      const float ds = __fmul_rn(d, float(int(scales[2 * quad])));
+      float w[8];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t l4 = ((quad & 1) ? lb[h] : la[h]) >> ((quad & 2) ? 4 : 0);
+        const uint32_t h4 = hh[h] >> (2 * quad);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int qv = int(((l4 >> (8 * e)) & 0x0f) | (((h4 >> (8 * e)) & 0x03) << 4)) - 32;
+          w[4 * h + e] = __fmul_rn(ds, float(qv));
+        }
+      }
+      Pack8<T>::store(dst + 32 * quad, w);
+    }
+  }
+}
+
 template <int QT, typename T>
 static int launch_dequant(const void* in, void* out, int64_t rows, int64_t n_per_row, cudaStream_t stream) {
-  const int64_t total_units = rows * n_per_row / 8;
+  const int64_t weights = rows * n_per_row;
+  // 16-bit outputs: the every-byte-once kernels; float outputs are write bound and measured faster with one 8-output
+  // unit per thread (a warp then writes 1 KiB contiguous per pair of store instructions)
+  if ((QT == QTYPE_Q4_K || QT == QTYPE_Q6_K) && sizeof(T) == 2) {
+    const int64_t items = QT == QTYPE_Q4_K ? weights / 16 : weights / 32;
+    const int64_t per_cta = int64_t(kDequantThreads) * 2;
+    const int64_t grid = (items + per_cta - 1) / per_cta;
+    if (grid > 0x7fffffffLL) return RC_RANGE;
+    if (QT == QTYPE_Q4_K)
+      dequant_q4k_kernel<T><<<dim3(unsigned(grid)), kDequantThreads, 0, stream>>>(static_cast<const uint8_t*>(in), static_cast<T*>(out), items);
+    else
+      dequant_q6k_kernel<T><<<dim3(unsigned(grid)), kDequantThreads, 0, stream>>>(static_cast<const uint8_t*>(in), static_cast<T*>(out), items);
+    return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
+  }
+  const int64_t total_units = weights / 8;
   const int64_t per_cta = int64_t(kDequantThreads) * kUnitsPerThread;
   const int64_t grid = (total_units + per_cta - 1) / per_cta;
   if (grid > 0x7fffffffLL) return RC_RANGE;

@@ -32,6 +32,7 @@ constexpr int kQ6StageSrc = kQ6StageSb * 210;            // 840 B of each row pe
 constexpr int kQ6Chunks = 53;                            // 16-byte chunks of the aligned window (840 + up to 8 B lead)
 constexpr int kQ6Pitch = 912;                            // pitch % 128 == 16: 4-byte reads of 8 rows x 4 lanes hit 32 banks
 constexpr int kQ6StageBytes = kQ6Rows * kQ6Pitch;        // 14592 B per stage slot
+constexpr int kQ6ScalePitch = 20;                        // floats per row of the scale scratch: 16 + 4 so that the 16-byte reads of 8 rows hit all banks
 
 template <typename T> struct Q6Offset;
 template <> struct Q6Offset<__nv_bfloat16> { static constexpr uint32_t kPair = 0x43204320u; };   // 160 = 128 + 32
@@ -60,7 +61,7 @@ __device__ __forceinline__ uint32_t lds_word(const uint8_t* p) {
 
 // One super-block of 16 rows on one warp.  st: the warp's block of row 0 in the stage (row r at st + r * pitch).
 template <typename T, int NT, int MC, bool ODD>
-__device__ __forceinline__ void q6k_superblock(const uint8_t* st, float (*sS)[16], const T* const (&xrow)[NT], int sb, int lane,
+__device__ __forceinline__ void q6k_superblock(const uint8_t* st, float (*sS)[kQ6ScalePitch], const T* const (&xrow)[NT], int sb, int lane,
                                                float (&res)[NT][4]) {
   using MT = MmaType<T>;
   const int g = lane >> 2, t = lane & 3;
@@ -141,7 +142,7 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   static_assert(NSTAGE % SPI == 0 && D >= 2, "each warp group needs at least two stage slots");
   extern __shared__ __align__(16) uint8_t smem_dyn[];
   uint8_t* sW = smem_dyn;                                               // staged packed weights, NSTAGE x kQ6StageBytes
-  __shared__ __align__(16) float sS[NW][kQ6Rows][16];                   // d * sc per row, sub-block
+  __shared__ __align__(16) float sS[NW][kQ6Rows][kQ6ScalePitch];        // d * sc per row, sub-block
   // the cross-warp reduction buffer reuses the stage slots once every warp is done with them
   float (*sRed)[kQ6Rows][kCols] = reinterpret_cast<float (*)[kQ6Rows][kCols]>(smem_dyn);
   static_assert(NW * kQ6Rows * kCols * sizeof(float) <= size_t(NSTAGE) * kQ6StageBytes, "reduction buffer must fit");

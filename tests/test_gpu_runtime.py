@@ -51,6 +51,33 @@ def test_session_run_numpy_matches_oracle(tmp_path, qtype):
     mod.close()
 
 
+@pytest.mark.parametrize("dtype", ["float16", "float32"])
+def test_session_run_numpy_other_dtypes_and_shape_changes(tmp_path, dtype):
+    """float16 / float32 modules keep their numpy dtypes; a new input shape gets its own cached arenas; a stream the
+    caller set stays in place after run_numpy."""
+    n, k = 80, 512
+    art, blocks, _ = _artifact(tmp_path, "Q4_K", n, k, dtype=dtype)
+    mod = dml.runtime.load(art.path)
+    mod.load_encoded_constants()
+    sess = mod.create_session()
+    stream = torch.cuda.Stream()
+    sess.set_stream(stream.cuda_stream)
+    for m in (1, 5, 1, 33):
+        x = S.random_activations(m, k, 40 + m, dtype)
+        y = sess.run_numpy({"x": x})["t0"]
+        assert y.dtype == np.dtype(dtype) and y.shape == (m, n)
+        ref = oracle.gemm_quant(x.astype(np.float32), blocks, "Q4_K", n, k)
+        _, _, norm = oracle.max_errors(ref, y.astype(np.float32))
+        assert norm <= (2e-2 if dtype == "float16" else 1e-4), (dtype, m, norm)
+    assert len(sess._numpy_plans) == 3 and sess._user_stream == stream.cuda_stream
+    # the result does not alias the pinned arena: a second call must not change the first result
+    a = sess.run_numpy({"x": S.random_activations(1, k, 1, dtype)})["t0"]
+    keep = a.copy()
+    sess.run_numpy({"x": S.random_activations(1, k, 2, dtype)})
+    assert np.array_equal(a, keep)
+    mod.close()
+
+
 def test_session_benchmark_and_external_stream(tmp_path):
     n, k = 256, 1024
     art, blocks, _ = _artifact(tmp_path, "Q4_K", n, k)
