@@ -682,13 +682,23 @@ struct DeviceState {
   size_t workspace_bytes = 0;
 };
 static std::mutex g_mutex;
-static std::unordered_map<int, DeviceState> g_state;
+// One workspace + flag set per (device, stream): launches on one stream are ordered and may share them, launches on
+// different streams may overlap on the GPU and must not.
+struct StateKey {
+  int dev;
+  cudaStream_t stream;
+  bool operator==(const StateKey& o) const { return dev == o.dev && stream == o.stream; }
+};
+struct StateKeyHash {
+  size_t operator()(const StateKey& k) const { return std::hash<void*>()(static_cast<void*>(k.stream)) * 31u + size_t(k.dev); }
+};
+static std::unordered_map<StateKey, DeviceState, StateKeyHash> g_state;
 
-static DeviceState* device_state(size_t need_workspace) {
+static DeviceState* device_state(size_t need_workspace, cudaStream_t stream) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
   std::lock_guard<std::mutex> lock(g_mutex);
-  DeviceState& st = g_state[dev];
+  DeviceState& st = g_state[StateKey{dev, stream}];
   if (st.status == nullptr) {
     if (cudaMalloc(&st.status, sizeof(int) * (1 + kMaxCtas)) != cudaSuccess) return nullptr;
     cudaMemset(st.status, 0, sizeof(int) * (1 + kMaxCtas));
@@ -819,7 +829,7 @@ static int launch_bm(const void* a, const void* b, const void* bias, void* c, in
     if (pl.workspace_bytes > kStaticScratchBytes) return RC_RANGE;
     if (int rc = static_scratch(&sc)) return rc;
   } else {
-    DeviceState* st = device_state(pl.workspace_bytes);
+    DeviceState* st = device_state(pl.workspace_bytes, s);
     if (st == nullptr) return RC_LAUNCH;
     sc.workspace = st->workspace;
     sc.status = st->status;
@@ -886,10 +896,14 @@ int umma_device_status() {
   int dev = 0, value = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
   std::lock_guard<std::mutex> lock(umma::g_mutex);
-  auto it = umma::g_state.find(dev);
-  if (it != umma::g_state.end() && it->second.status != nullptr) {
-    if (cudaMemcpy(&value, it->second.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (value != 0) cudaMemset(it->second.status, 0, sizeof(int) * (1 + umma::kMaxCtas));
+  for (auto& entry : umma::g_state) {           // every stream's word on this device; the first non-zero one is reported
+    if (entry.first.dev != dev || entry.second.status == nullptr) continue;
+    int word = 0;
+    if (cudaMemcpy(&word, entry.second.status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (word != 0) {
+      cudaMemset(entry.second.status, 0, sizeof(int) * (1 + umma::kMaxCtas));
+      if (value == 0) value = word;
+    }
   }
   if (value == 0 && dev >= 0 && dev < umma::kMaxDevices && umma::g_static[dev].ready) {   // the static-scratch path's word
     if (cudaMemcpy(&value, umma::g_static[dev].status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;

@@ -197,6 +197,28 @@ def test_gemm_umma_bias_and_auto_dispatch(dev):
                          variant="umma")
 
 
+def test_gemm_umma_on_two_streams_at_once(dev):
+    """Each stream has its own partial-tile workspace and flags: launches that overlap on the GPU do not disturb each
+    other (shapes whose tiles are cut between SMs, so the workspace is really used)."""
+    cases = [("Q4_K", 96, 256, 4096), ("Q6_K", 40, 384, 8192)]
+    work = []
+    for i, (qtype, m, n, k) in enumerate(cases):
+        w = torch.from_numpy(S.random_blocks(qtype, n, k, seed=1200 + i)).to(dev)
+        x, _ = _activations(m, k, 1300 + i, "bfloat16", dev)
+        want = kernels.gemm_rcr(x, w, qtype, variant="umma")
+        work.append((qtype, w, x, want, torch.cuda.Stream(), [torch.empty_like(want) for _ in range(8)]))
+    torch.cuda.synchronize()
+    for it in range(8):
+        for (qtype, w, x, want, stream, outs) in work:
+            with torch.cuda.stream(stream):
+                kernels.gemm_rcr(x, w, qtype, variant="umma", out=outs[it])
+    torch.cuda.synchronize()
+    assert kernels.device_status() == 0
+    for (qtype, w, x, want, stream, outs) in work:
+        for o in outs:
+            assert torch.equal(o.view(torch.int16), want.view(torch.int16)), qtype
+
+
 def test_gemm_bias_and_batch_dims(dev):
     n, k = 48, 512
     blocks = S.random_blocks("Q4_K", n, k, seed=700)
