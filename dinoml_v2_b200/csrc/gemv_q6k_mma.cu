@@ -272,7 +272,7 @@ static int launch_q6k_cfg(const void* a, const void* b, const void* bias, void* 
 
 template <typename T, int MXC>
 static int launch_q6k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
-  if constexpr (MXC <= 2) {
+  if constexpr (MXC <= 8) {
     // Few row tiles (all CTAs resident at two per SM): six stage slots per CTA keep more bytes in flight.  Many row
     // tiles: four slots, so that three CTAs fit on an SM.
     int sm_count = 148, dev = 0;
