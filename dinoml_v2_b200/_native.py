@@ -14,6 +14,7 @@ LIB_PATH = PKG / "lib" / "libdinoml_b200_gguf.so"
 VARIANTS = {"auto": 0, "simt": 1, "mma": 2, "umma": 3}
 VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
 DINO_DTYPE = {"float16": 1, "float32": 2, "bfloat16": 6}
+ACTIVATIONS = {"silu": 1, "fast_gelu": 2}
 DEQUANT_DTYPE = {"float32": 0, "float16": 1, "bfloat16": 2}
 
 _lib = None
@@ -50,6 +51,8 @@ def lib() -> ctypes.CDLL:
     L.dinoml_b200_gguf_gemv_rcr_scatter.restype = ci
     L.dinoml_b200_gguf_gemm_rcr_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, ci, ci, ci, ci, ci, ci, vp]
     L.dinoml_b200_gguf_gemm_rcr_scatter.restype = ci
+    L.dinoml_b200_gguf_dual_gemm_rcr.argtypes = [vp, vp, vp, ctypes.POINTER(vp), ci, ci, ci, ci, ci, ci, ci, ci, vp]
+    L.dinoml_b200_gguf_dual_gemm_rcr.restype = ci
     L.dinoml_b200_peer_exchange.argtypes = [ctypes.POINTER(vp), ci, ci, ctypes.c_uint, vp, vp, i64, ci, vp]
     L.dinoml_b200_peer_exchange.restype = ci
     L.dinoml_b200_peer_enable_access.argtypes = [ci]

@@ -22,7 +22,7 @@ size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k);
 int umma_device_status();
 int peer_device_status();
 int peer_enable_access(int peer_device);
-struct PeerOut { void* ptr[8]; int count; };   // layout of gemv_mma_common.cuh
+struct PeerOut { void* ptr[8]; int count; int act; };   // layout of gemv_mma_common.cuh
 int gemm_rcr_mma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                        const PeerOut* peer_out, cudaStream_t s);
 int gemm_rcr_umma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
@@ -74,6 +74,28 @@ int gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype,
     case DINOML_B200_GGUF_VARIANT_UMMA: return gemm_rcr_umma(a, b, bias, c, qtype, dtype, m, n, k, s);
     default: return RC_RANGE;
   }
+}
+
+// Gated dual GEMM on a row-interleaved weight (see dinoml_b200_gguf_dual_gemm_rcr in the header); n = output columns.
+int dual_gemm_rcr_peers(const void* a, const void* b01, void* c, const PeerOut& dst, int qtype, int dtype, int m, int n, int k,
+                        int activation, int variant, cudaStream_t s) {
+  if (activation != 1 && activation != 2) return RC_RANGE;
+  if (n <= 0 || n % 8 != 0 || n > 0x3fffffff) return RC_RANGE;       // whole groups of 8 rows per matrix
+  PeerOut peers = dst;
+  peers.act = activation;
+  const int rows = 2 * n;                                              // rows of the interleaved weight
+  if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, rows, k);
+  if (variant == DINOML_B200_GGUF_VARIANT_MMA) return gemm_rcr_mma_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, &peers, s);
+  if (variant == DINOML_B200_GGUF_VARIANT_UMMA) return gemm_rcr_umma_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, &peers, s);
+  return RC_RANGE;                                                     // the simt variant has no gated epilogue
+}
+int dual_gemm_rcr(const void* a, const void* b01, void* c, int qtype, int dtype, int m, int n, int k, int activation, int variant,
+                  cudaStream_t s) {
+  PeerOut none;
+  for (int i = 0; i < 8; ++i) none.ptr[i] = nullptr;
+  none.count = 0;
+  none.act = 0;
+  return dual_gemm_rcr_peers(a, b01, c, none, qtype, dtype, m, n, k, activation, variant, s);
 }
 
 float profile_gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n,
@@ -154,6 +176,7 @@ int dinoml_b200_gguf_gemv_rcr_scatter(const void* a, const void* b_quant, const 
   PeerOut peers;
   for (int i = 0; i < 8; ++i) peers.ptr[i] = i < n_peers ? peer_c[i] : nullptr;
   peers.count = n_peers;
+  peers.act = 0;
   for (int i = 0; i < n_peers; ++i)
     if (peers.ptr[i] == nullptr) return set_error(RC_NULL, "dinoml_b200_gguf_gemv_rcr_scatter");
   return set_error(gemm_rcr_mma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, static_cast<cudaStream_t>(stream)),
@@ -167,6 +190,7 @@ int dinoml_b200_gguf_gemm_rcr_scatter(const void* a, const void* b_quant, const 
   PeerOut peers;
   for (int i = 0; i < 8; ++i) peers.ptr[i] = i < n_peers ? peer_c[i] : nullptr;
   peers.count = n_peers;
+  peers.act = 0;
   for (int i = 0; i < n_peers; ++i)
     if (peers.ptr[i] == nullptr) return set_error(RC_NULL, where);
   if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, n, k);
@@ -174,6 +198,20 @@ int dinoml_b200_gguf_gemm_rcr_scatter(const void* a, const void* b_quant, const 
   if (variant == DINOML_B200_GGUF_VARIANT_MMA) return set_error(gemm_rcr_mma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, s), where);
   if (variant == DINOML_B200_GGUF_VARIANT_UMMA) return set_error(gemm_rcr_umma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, s), where);
   return set_error(RC_RANGE, where);     // the simt variant has no scatter epilogue
+}
+
+int dinoml_b200_gguf_dual_gemm_rcr(const void* a, const void* b01_interleaved, void* c, void* const* peer_c, int n_peers, int qtype,
+                                   int dtype, int m, int n, int k, int activation, int variant, void* stream) {
+  const char* where = "dinoml_b200_gguf_dual_gemm_rcr";
+  if (n_peers < 0 || n_peers > 8 || (n_peers > 0 && peer_c == nullptr)) return set_error(RC_RANGE, where);
+  PeerOut peers;
+  for (int i = 0; i < 8; ++i) peers.ptr[i] = i < n_peers ? peer_c[i] : nullptr;
+  peers.count = n_peers;
+  peers.act = 0;
+  for (int i = 0; i < n_peers; ++i)
+    if (peers.ptr[i] == nullptr) return set_error(RC_NULL, where);
+  return set_error(dual_gemm_rcr_peers(a, b01_interleaved, c, peers, qtype, dtype, m, n, k, activation, variant,
+                                       static_cast<cudaStream_t>(stream)), where);
 }
 
 int dinoml_b200_peer_enable_access(int peer_device) {

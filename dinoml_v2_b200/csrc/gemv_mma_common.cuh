@@ -99,12 +99,21 @@ inline int gemv_k_slices(int tiles, int nstages, int slots) {
 struct PeerOut {
   void* ptr[8];
   int count;
+  int act;      // 0: plain output.  1 / 2: gated output silu(g) * u / fast_gelu(g) * u of a weight whose rows interleave the
+                // two matrices in groups of 8 (rows 16t..16t+7 = rows 8t..8t+7 of the first, 16t+8..16t+15 = of the second)
 };
 inline PeerOut no_peers() {
   PeerOut p;
   for (int i = 0; i < 8; ++i) p.ptr[i] = nullptr;
   p.count = 0;
+  p.act = 0;
   return p;
+}
+enum : int { ACT_NONE = 0, ACT_SILU = 1, ACT_FAST_GELU = 2 };
+// left activation of the reference's dual GEMM (src/dinoml/lowering/ops/templates/dual_gemm_cpu.cpp.j2:66-70), in fp32
+__device__ __forceinline__ float gate_activation(float g, int act) {
+  if (act == ACT_SILU) return g / (1.0f + expf(-g));
+  return 0.5f * g * (1.0f + tanhf(0.7978845608f * g * (1.0f + 0.044715f * g * g)));
 }
 
 // Launch with programmatic stream serialization and, for ks > 1, clusters of ks CTAs along grid.y.

@@ -235,18 +235,28 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
     for (int idx = tid; idx < kQ6Rows * MXC; idx += NW * 32) {
       const int r = idx & (kQ6Rows - 1), c = idx >> 4;
       const int row = r_base + r;
-      if (row < n && c < m) {
-        float v = sOut[idx];
+      if (row >= n || c >= m) continue;
+      float v = sOut[idx];
+      if (SLICED)
+        for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
+      int64_t at = int64_t(c) * n + row;
+      if (peers.act != ACT_NONE) {
+        // gated pair: rows r < 8 of the tile belong to the first matrix, r + 8 to the second; output has n / 2 columns
+        if (r >= 8) continue;
+        float u = sOut[idx + 8];
         if (SLICED)
-          for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
-        if (bias != nullptr) v += MT::to_float(bias[row]);
-        const T out = MT::from_float(v);
-        y[int64_t(c) * n + row] = out;
-        if (SCATTER) {
+          for (int peer = 1; peer < ks; ++peer) u += ld_cluster_f32(&sOut[idx + 8], uint32_t(peer));
+        v = gate_activation(v, peers.act) * u;
+        at = int64_t(c) * (n >> 1) + (blockIdx.x * 8 + r);
+      } else if (bias != nullptr) {
+        v += MT::to_float(bias[row]);
+      }
+      const T out = MT::from_float(v);
+      y[at] = out;
+      if (SCATTER) {
 #pragma unroll
-          for (int pi = 0; pi < 8; ++pi)
-            if (pi < peers.count) static_cast<T*>(peers.ptr[pi])[int64_t(c) * n + row] = out;
-        }
+        for (int pi = 0; pi < 8; ++pi)
+          if (pi < peers.count) static_cast<T*>(peers.ptr[pi])[at] = out;
       }
     }
   }

@@ -12,7 +12,8 @@
 //   tensor <name> input|output|temp <DinoDtype> <ndim> <dim>...          dim = N  or  ?min:max
 //   constant <name> dense <DinoDtype> <offset> <nbytes> <ndim> <dim>...
 //   constant <name> gguf <qtype_value> <offset> <nbytes> <rows> <n_per_row> <residency>
-//   node gemm_rcr <a> <b> <bias|-> <out> <variant>
+//   node gemm_rcr <a> <b> <bias|-> <out> <variant>                       also gemm_rcr_bias; dual_gemm_rcr_silu / _fast_gelu with
+//                                                                         <b> = the two weights' rows interleaved in groups of 8
 //   dispatch <node_index> <m> <n> <k> <variant>                          shape-guarded selection
 #include <cstdio>
 #include <cstdlib>
@@ -28,6 +29,8 @@
 namespace b200gguf {
 int set_error_message(int rc, const std::string& message);
 const char* last_error();
+int dual_gemm_rcr(const void* a, const void* b01, void* c, int qtype, int dtype, int m, int n, int k, int activation, int variant,
+                  cudaStream_t s);
 int gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
              int variant, cudaStream_t s);
 }  // namespace b200gguf
@@ -79,6 +82,7 @@ struct NodeSpec {
   int a = -1, out = -1;       // tensor indices
   int b = -1, bias = -1;      // constant indices
   int variant = 0;
+  int activation = 0;         // 0: gemm_rcr[_bias]; 1 / 2: dual_gemm_rcr_silu / _fast_gelu on a row-interleaved weight
 };
 struct DispatchSpec { int node, m, n, k, variant; };
 
@@ -193,7 +197,10 @@ int parse_plan(DinoModule* mod, const std::string& path) {
       std::string op, a, b, bias, out;
       NodeSpec n;
       if (!(ls >> op >> a >> b >> bias >> out >> n.variant)) return fail(where + "malformed node record");
-      if (op != "gemm_rcr" && op != "gemm_rcr_bias") return fail(where + "unsupported op " + op);
+      if (op == "dual_gemm_rcr_silu") n.activation = 1;
+      else if (op == "dual_gemm_rcr_fast_gelu") n.activation = 2;
+      else if (op != "gemm_rcr" && op != "gemm_rcr_bias") return fail(where + "unsupported op " + op);
+      if (n.activation != 0 && bias != "-") return fail(where + "dual_gemm_rcr takes no bias");
       n.a = find_tensor(*mod, a);
       n.out = find_tensor(*mod, out);
       n.b = find_constant(*mod, b);
@@ -306,7 +313,8 @@ int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTe
     const int64_t k = ashape.back();
     int64_t m = 1;
     for (size_t i = 0; i + 1 < ashape.size(); ++i) m *= ashape[i];
-    const int64_t n = w.shape[0];
+    if (node.activation != 0 && w.shape[0] % 16 != 0) return fail("dual_gemm_rcr weight must hold 2N rows with N % 8 == 0");
+    const int64_t n = node.activation != 0 ? w.shape[0] / 2 : w.shape[0];
     if (k != w.shape[1]) return fail("gemm_rcr K dimension " + std::to_string(k) + " does not match n_per_row " + std::to_string(w.shape[1]));
     if (m > 0x7fffffff || n > 0x7fffffff || k > 0x7fffffff) return fail("gemm_rcr dimension exceeds int range");
     std::vector<int64_t> oshape(ashape.begin(), ashape.end() - 1);
@@ -330,8 +338,11 @@ int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTe
       if (d.node == int(ni) && d.m == m && d.n == n && d.k == k) { variant = d.variant; break; }
     const void* bias = node.bias >= 0 ? mod.constants[node.bias].device : nullptr;
     if (node.bias >= 0 && mod.constants[node.bias].shape.back() != n) return fail("bias length does not match N");
-    const int rc = b200gguf::gemm_rcr(ptr[node.a], w.device, bias, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
-                                      variant, s->stream);
+    const int rc = node.activation != 0
+                       ? b200gguf::dual_gemm_rcr(ptr[node.a], w.device, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
+                                                 node.activation, variant, s->stream)
+                       : b200gguf::gemm_rcr(ptr[node.a], w.device, bias, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
+                                            variant, s->stream);
     if (rc != 0) {
       static const char* const kText[] = {"ok", "null pointer", "non-positive dimension", "k not a multiple of the block",
                                           "CUDA launch failed", "unsupported qtype", "unsupported dtype", "alignment",

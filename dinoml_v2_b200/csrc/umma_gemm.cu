@@ -411,7 +411,27 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
 #pragma unroll
             for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + v[j]);
           }
-          if (n_row < p.n) {
+          if (p.peers.act != ACT_NONE) {
+            // gated pair: within every 16 weight rows the first 8 belong to the first matrix, the next 8 to the second;
+            // lane l and lane l ^ 8 hold the two halves, the output has n / 2 columns
+            const int out_row = ((n_row >> 4) << 3) + (n_row & 7);
+            const int64_t n_out = p.n >> 1;
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const float mine = __uint_as_float(r[j]);
+              const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+              if ((lane & 8) == 0 && n_row < p.n && m0 + col + j < p.m) {
+                const T v = P::cvt(gate_activation(mine, p.peers.act) * other);
+                const int64_t at = int64_t(m0 + col + j) * n_out + out_row;
+                static_cast<T*>(p.out)[at] = v;
+                if (SCATTER) {
+#pragma unroll
+                  for (int pi = 0; pi < 8; ++pi)
+                    if (pi < p.peers.count) static_cast<T*>(p.peers.ptr[pi])[at] = v;
+                }
+              }
+            }
+          } else if (n_row < p.n) {
             T* dst = static_cast<T*>(p.out) + int64_t(m0 + col) * p.n + n_row;
 #pragma unroll
             for (int j = 0; j < CH; ++j)

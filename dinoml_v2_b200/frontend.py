@@ -135,6 +135,37 @@ def _to_storage(value: np.ndarray, dtype: str) -> np.ndarray:
     return np.ascontiguousarray(value, dtype={"float16": np.float16, "float32": np.float32}[dtype])
 
 
+def _fuse_dual_gemm_weights(nodes: list[dict[str, Any]], bound: dict[str, tuple]) -> None:
+    """A dual GEMM node reads its two GGUF weights as ONE constant whose rows alternate in groups of 8 (rows 16t..16t+7 from
+    B0, 16t+8..16t+15 from B1): that order puts a gate row and its up row into the same thread of the fused kernels.  The
+    node is rewritten to [a, fused]; source constants no other node reads are dropped from the artifact."""
+    for node in nodes:
+        if not node["op"].startswith("dual_gemm_rcr_"):
+            continue
+        _, n0, n1 = node["inputs"]
+        (dt0, sh0, a0, st0), (dt1, sh1, a1, st1) = bound[n0], bound[n1]
+        if not (st0 and st1 and st0.get("kind") == "gguf" and st1.get("kind") == "gguf"):
+            raise NotImplementedError(f"{node['op']}: both weights must be GGUF-encoded constants")
+        if st0["qtype"] != st1["qtype"] or sh0 != sh1 or dt0 != dt1 or sh0[0] % 8:
+            raise NotImplementedError(f"{node['op']}: the two weights need one qtype, one shape and N % 8 == 0")
+        n, k = sh0
+        rb = a0.size // n
+        fused = np.ascontiguousarray(np.stack((a0.reshape(n // 8, 8, rb), a1.reshape(n // 8, 8, rb)), axis=1).reshape(-1))
+        storage = dict(st0)
+        storage.update({"tensor": f"{st0['tensor']}+{st1['tensor']}", "shape": [2 * n, k], "encoded_nbytes": int(fused.nbytes),
+                        "gguf_shape": [k, 2 * n], "derived": {"kind": "interleave_rows8", "sources": [n0, n1],
+                                                               "source_paths": [st0.get("path"), st1.get("path")]}})
+        name = f"{n0}+{n1}.rows8"
+        bound[name] = (dt0, (2 * n, k), fused, storage)
+        node["inputs"] = [node["inputs"][0], name]
+        node["attrs"]["sources"] = [n0, n1]
+    used = {name for node in nodes for name in node["inputs"]}
+    for node in nodes:
+        for src in node["attrs"].get("sources", []):
+            if src not in used:
+                bound.pop(src, None)
+
+
 def trace(module: Module, inputs: Mapping[str, TensorSpec], constants: Mapping[str, Any] | None = None,
           name: str = "model") -> ModelSpec:
     """Runs `module.forward` on symbolic tensors and binds constants.  A constant may be a numpy array (dense) or a
@@ -175,7 +206,7 @@ def trace(module: Module, inputs: Mapping[str, TensorSpec], constants: Mapping[s
         outputs = [outputs]
     outputs = list(outputs)
 
-    const_entries, arrays, offset = [], {}, 0
+    bound = {}                                                # name -> (dtype, shape, array, storage)
     for key, p in params.items():
         dtype, shape = normalize_dtype(p.dtype), tuple(int(d) for d in p.shape)
         value = constants[key]
@@ -187,6 +218,11 @@ def trace(module: Module, inputs: Mapping[str, TensorSpec], constants: Mapping[s
             if tuple(arr.shape) != shape:
                 raise ValueError(f"constant {key!r} has shape {tuple(arr.shape)}, expected {shape}")
             storage = None
+        bound[key] = (dtype, shape, arr, storage)
+    _fuse_dual_gemm_weights(builder.nodes, bound)
+
+    const_entries, arrays, offset = [], {}, 0
+    for key, (dtype, shape, arr, storage) in bound.items():
         strides, acc = [], 1
         for d in reversed(shape):
             strides.insert(0, acc)

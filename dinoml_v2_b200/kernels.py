@@ -66,6 +66,44 @@ def gemm_rcr(a: torch.Tensor, b_quant: torch.Tensor, qtype, bias: torch.Tensor |
     return out
 
 
+def interleave_rows8(b0, b1):
+    """Row order the gated dual GEMM expects: rows 16t..16t+7 = rows 8t..8t+7 of b0, rows 16t+8..16t+15 = of b1.
+    b0, b1: uint8 [N, row_bytes] (torch tensors or numpy arrays), N % 8 == 0.  Blocks are not touched."""
+    if b0.shape != b1.shape or b0.shape[0] % 8:
+        raise ValueError("both weights must have the same shape and a row count that is a multiple of 8")
+    n, rb = b0.shape
+    if isinstance(b0, torch.Tensor):
+        return torch.stack((b0.view(n // 8, 8, rb), b1.view(n // 8, 8, rb)), dim=1).reshape(2 * n, rb).contiguous()
+    import numpy as np
+    return np.ascontiguousarray(np.stack((b0.reshape(n // 8, 8, rb), b1.reshape(n // 8, 8, rb)), axis=1).reshape(2 * n, rb))
+
+
+def dual_gemm_rcr(a: torch.Tensor, b01_interleaved: torch.Tensor, qtype, activation: str = "silu", *, variant: str = "auto",
+                  out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """act(a @ dequant(B0)^T) * (a @ dequant(B1)^T) in one launch; `b01_interleaved` = interleave_rows8(B0, B1).
+    a [..., K] -> [..., N] with N = rows of each matrix.  Mirrors dml.ops.dual_gemm_rcr_silu / _fast_gelu of the reference
+    (src/dinoml/ops/gemm.py:63-121) for GGUF weights."""
+    q = qtype_of(qtype)
+    _require_cuda(a, "a")
+    _require_cuda(b01_interleaved, "b01_interleaved")
+    k = a.shape[-1]
+    m = a.numel() // k
+    rows = b01_interleaved.shape[0]
+    if b01_interleaved.dtype != torch.uint8 or b01_interleaved.dim() != 2 or b01_interleaved.shape[1] != row_bytes(q, k) or rows % 16:
+        raise ValueError(f"b01_interleaved must be uint8 [2N, {row_bytes(q, k)}] with N % 8 == 0 for {q.name} with K={k}")
+    n = rows // 2
+    if activation not in _native.ACTIVATIONS:
+        raise ValueError(f"activation must be one of {sorted(_native.ACTIVATIONS)}")
+    if out is None:
+        out = torch.empty(a.shape[:-1] + (n,), dtype=a.dtype, device=a.device)
+    _require_cuda(out, "out")
+    rc = _native.lib().dinoml_b200_gguf_dual_gemm_rcr(
+        a.data_ptr(), b01_interleaved.data_ptr(), out.data_ptr(), None, 0, q.value, _native.DINO_DTYPE[_DTYPE_NAME[a.dtype]], m, n, k,
+        _native.ACTIVATIONS[activation], _native.VARIANTS[variant], _stream_ptr(stream))
+    _native.check(rc, "dinoml_b200_gguf_dual_gemm_rcr")
+    return out
+
+
 def profile_gemm_rcr(a, b_quant, qtype, out, *, variant: str, iterations: int, bias=None, stream=None) -> float:
     """Milliseconds per launch of one candidate (negative on failure), timed by the library with CUDA events."""
     q = qtype_of(qtype)

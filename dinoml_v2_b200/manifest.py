@@ -22,7 +22,8 @@ KERNEL_MANIFEST_SCHEMA_VERSION = 4
 KERNEL_ABI_VERSION = 1
 PROFILE_CACHE_SCHEMA_VERSION = 9
 EXECUTION_PLAN_KERNEL_LIBRARIES = (KERNEL_LIBRARY,)          # src/dinoml/kernels/manifest.py:98-105
-SUPPORTED_OPS = ("gemm_rcr", "gemm_rcr_bias")
+SUPPORTED_OPS = ("gemm_rcr", "gemm_rcr_bias", "dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu")
+DUAL_OPS = ("dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu")
 VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3}
 
 _B200_TUNING = {
@@ -66,6 +67,7 @@ def kernel_symbol(qtype: str, op: str, dtype: str, variant: str, *, profile: boo
 def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, Any]:
     q = qtype_of(qtype)
     has_bias = op.endswith("_bias")
+    dual_act = op[len("dual_gemm_rcr_"):] if op.startswith("dual_gemm_rcr_") else None
     cand = {
         "candidate_id": f"b200_gguf_{q.symbol}_{dtype}_{variant}_v1",
         "symbol_id": f"{q.symbol}_{variant}_v1",
@@ -83,6 +85,13 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
         "profiler_symbol": kernel_symbol(q.name, "gemm_rcr", dtype, variant, profile=True),
         "variant": variant, "variant_code": VARIANT_CODES[variant],
     }
+    if dual_act:      # one generic entry point (activation and variant are arguments); epilogue named as in the reference
+        cand.update({"family": "dual_gemm", "layouts": {"a": "row", "b0": "column", "b1": "column", "c": "row"},
+                     "epilogue": f"left_{dual_act}_and_mul", "launch_abi": "gguf_dual_gemm_rcr_v1",
+                     "kernel_symbol": "dinoml_b200_gguf_dual_gemm_rcr", "profiler_symbol": None})
+        cand["epilogue_config"] = {"name": f"left_{dual_act}_and_mul", "inputs": [], "activation": dual_act, "bias_axis": None,
+                                   "accumulator_dtype": "float32", "output_dtype": dtype, "launch_abi": "gguf_dual_gemm_rcr_v1",
+                                   "weight_rows": "interleave_rows8"}
     cand["candidate_config_key"] = sha256_of({k: cand[k] for k in ("provider", "op", "dtype", "qtype", "variant", "b200", "launch_abi")})
     return cand
 
@@ -135,10 +144,15 @@ def build_kernel_manifest(graph: Mapping[str, Any], target: Mapping[str, Any]) -
         validate_gguf_direct_admission(node, weight, target["name"])
         qtype, dtype = weight["storage"]["qtype"], weight["dtype"]
         cset = gguf_candidate_set(qtype, node["op"], dtype)
+        dual = node["op"] in DUAL_OPS
+        if dual:      # only the tensor-core variants have the gated epilogue; selection is the built-in shape guard
+            cset = dict(cset, candidates=[c for c in cset["candidates"] if c["variant"] != "simt"])
+            if not cset["candidates"]:
+                raise NotImplementedError(f"{node['op']} needs a tensor-core variant: {qtype} / {dtype} has none")
         required.append({
             "node_id": node["id"], "op": node["op"], "dtype": dtype, "qtype": qtype,
-            "kernel_symbol": "dinoml_b200_gguf_gemm_rcr", "kernel_library": KERNEL_LIBRARY,
-            "profiler_symbol": "dinoml_profile_b200_gguf_gemm_rcr", "has_profiler": True,
+            "kernel_symbol": "dinoml_b200_gguf_dual_gemm_rcr" if dual else "dinoml_b200_gguf_gemm_rcr", "kernel_library": KERNEL_LIBRARY,
+            "profiler_symbol": None if dual else "dinoml_profile_b200_gguf_gemm_rcr", "has_profiler": not dual,
             "support_archive": "libdinoml_b200_gguf.so",
             "selected_candidate_id": None, "selection": "shape_guarded_auto",
             "candidates": cset["candidates"], "candidate_set_id": cset["candidate_set_id"], "candidate_set_key": cset["candidate_set_key"],

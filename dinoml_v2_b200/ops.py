@@ -35,3 +35,30 @@ def gemm_rcr(a: Tensor, b: Tensor) -> Tensor:
 
 def gemm_rcr_bias(a: Tensor, b: Tensor, bias: Tensor) -> Tensor:
     return _gemm("gemm_rcr_bias", a, b, bias)
+
+
+DUAL_GEMM_ACTIVATIONS = ("silu", "fast_gelu")     # the two the reference's CPU template implements (dual_gemm_cpu.cpp.j2:66-70)
+
+
+def _dual_gemm(activation: str, a: Tensor, b0: Tensor, b1: Tensor) -> Tensor:
+    """act(a @ b0^T) * (a @ b1^T) - dml.ops.dual_gemm_rcr_<activation> (src/dinoml/ops/gemm.py:63-121,
+    src/dinoml/kernels/families/dual_gemm.py:36-76).  Here b0 and b1 must both be [N, K] (no [1, K] broadcast)."""
+    op = f"dual_gemm_rcr_{activation}"
+    if len(a.shape) < 1 or len(b0.shape) != 2 or len(b1.shape) != 2:
+        raise ValueError(f"{op} expects A[..., K] and rank-2 B0 / B1 tensors")
+    if a.dtype not in GEMM_SUPPORTED_DTYPES or a.dtype != b0.dtype or a.dtype != b1.dtype:
+        raise ValueError(f"{op} operands must share one supported dtype, got {a.dtype}, {b0.dtype}, {b1.dtype}")
+    k = _static(a.shape[-1])
+    if k is None or k != _static(b0.shape[1]) or k != _static(b1.shape[1]):
+        raise ValueError(f"{op} expected B0[N, K] and B1[N, K] with K = {a.shape[-1]}, got {b0.shape} and {b1.shape}")
+    if tuple(b0.shape) != tuple(b1.shape):
+        raise ValueError(f"{op} expected B1 to match B0 {list(b0.shape)}, got {list(b1.shape)}")
+    return current_builder().add_node(op, [a, b0, b1], tuple(a.shape[:-1]) + (b0.shape[0],), a.dtype, {"activation": activation})
+
+
+def dual_gemm_rcr_silu(a: Tensor, b0: Tensor, b1: Tensor) -> Tensor:
+    return _dual_gemm("silu", a, b0, b1)
+
+
+def dual_gemm_rcr_fast_gelu(a: Tensor, b0: Tensor, b1: Tensor) -> Tensor:
+    return _dual_gemm("fast_gelu", a, b0, b1)

@@ -199,7 +199,8 @@ class Session:
         consts = {c["name"]: c for c in graph["constants"]}
         for node in graph["nodes"]:
             a = shapes[node["inputs"][0]]
-            shapes[node["outputs"][0]] = tuple(a[:-1]) + (consts[node["inputs"][1]]["shape"][0],)
+            rows = consts[node["inputs"][1]]["shape"][0]
+            shapes[node["outputs"][0]] = tuple(a[:-1]) + (rows // 2 if node["op"].startswith("dual_gemm_rcr_") else rows,)
         return {o["name"]: shapes[o["name"]] for o in graph["outputs"]}
 
     def _pack(self, inputs: Mapping[str, tuple[int, tuple[int, ...], str]], outputs: Mapping[str, tuple[int, tuple[int, ...], str]]):

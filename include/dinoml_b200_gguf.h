@@ -101,6 +101,21 @@ DINOML_B200_API size_t dinoml_b200_gguf_prealloc_scratch_bytes(void);
  * No counterpart in the reference. */
 DINOML_B200_API int dinoml_b200_gguf_device_status(void);
 
+/* ---- gated dual GEMM on two quantized weights --------------------------------------------------------------------
+ * c[M, N] = act(a * dequant(B0)^T) * (a * dequant(B1)^T), act = silu (activation 1) or fast_gelu (2), both products
+ * accumulated in fp32, the activation and the product evaluated in fp32, one rounding to `dtype` - the reference's
+ * dual_gemm_rcr_silu / dual_gemm_rcr_fast_gelu (src/dinoml/kernels/families/dual_gemm.py:93-103,
+ * src/dinoml/lowering/ops/templates/dual_gemm_cpu.cpp.j2:52-75; its CUDA path is a CUTLASS dual GEMM on dense weights,
+ * kernels/cuda/src/cutlass_dual_gemm.cu).  Here B0 and B1 are GGUF weights [N, K] of one qtype handed over as ONE
+ * buffer `b01_interleaved` of 2N rows in which the rows alternate in groups of 8: rows 16t .. 16t+7 are rows 8t .. 8t+7
+ * of B0, rows 16t+8 .. 16t+15 are rows 8t .. 8t+7 of B1 (blocks untouched; a row copy at load time,
+ * dinoml_v2_b200.kernels.interleave_rows8).  With that order a gate row and its up row sit in the same thread of the
+ * mma GEMV and in lanes l / l^8 of the tcgen05 epilogue, so the gate never goes to memory: one launch for the Llama
+ * gate / up pair.  N % 8 == 0; variants mma (M <= 16) and umma (M >= 9) with their usual K / alignment rules; optional
+ * extra destinations as in dinoml_b200_gguf_gemm_rcr_scatter (n_peers = 0: none). */
+DINOML_B200_API int dinoml_b200_gguf_dual_gemm_rcr(const void* a, const void* b01_interleaved, void* c, void* const* peer_c, int n_peers,
+                                                   int qtype, int dtype, int m, int n, int k, int activation, int variant, void* stream);
+
 /* ---- sharded decode over peer memory (no counterpart in the reference, which is single-GPU) ----------------------
  * dinoml_b200_gguf_gemv_rcr_scatter: the mma GEMV (M <= 16, Q4_K / Q6_K, float16 / bfloat16; same checks and codes as
  * dinoml_b200_gguf_gemm_rcr with variant = MMA) whose epilogue stores the [M, N] result to `c` AND to `n_peers` (<= 8)

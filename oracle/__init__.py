@@ -167,3 +167,20 @@ def max_errors(expected: np.ndarray, actual: np.ndarray) -> tuple[float, float, 
     rel = float((diff / np.maximum(1.0, np.abs(e))).max()) if diff.size else 0.0
     norm = float(max_abs / max(np.abs(e).max(), 1e-30)) if diff.size else 0.0
     return max_abs, rel, norm
+
+
+def dual_gemm_quant(a, blocks0, blocks1, qtype, n: int, k: int, activation: str = "silu"):
+    """CPU restatement of the reference's dual GEMM on dequantized weights
+    (src/dinoml/lowering/ops/templates/dual_gemm_cpu.cpp.j2:52-75): two fp32-accumulated products, the left one through
+    silu / fast_gelu, multiplied, all in float32."""
+    left = gemm_quant(a, blocks0, qtype, n, k).astype(np.float32)
+    right = gemm_quant(a, blocks1, qtype, n, k).astype(np.float32)
+    if activation == "silu":
+        with np.errstate(over="ignore"):                 # exp(-left) may be inf for very negative left: the quotient is then -0
+            act = left / (np.float32(1.0) + np.exp(-left, dtype=np.float32))
+    elif activation == "fast_gelu":
+        inner = np.float32(0.7978845608) * left * (np.float32(1.0) + np.float32(0.044715) * left * left)
+        act = np.float32(0.5) * left * (np.float32(1.0) + np.tanh(inner, dtype=np.float32))
+    else:
+        raise ValueError(activation)
+    return (act * right).astype(np.float32)

@@ -219,6 +219,35 @@ def test_gemm_umma_on_two_streams_at_once(dev):
             assert torch.equal(o.view(torch.int16), want.view(torch.int16)), qtype
 
 
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K"])
+@pytest.mark.parametrize("activation", ["silu", "fast_gelu"])
+def test_dual_gemm_gated_epilogue(dev, qtype, activation):
+    """act(a B0^T) * (a B1^T) in one launch on row-interleaved weights, mma GEMV (plain and cluster-sliced shapes) and
+    tcgen05 kernel (whole tiles and tiles finished after a stream-K reduction), against the oracle."""
+    k = 2048
+    for (m, n) in [(1, 8), (1, 104), (2, 64), (4, 200), (8, 48), (16, 64), (16, 2048), (40, 136), (300, 264)]:
+        b0 = S.random_blocks(qtype, n, k, seed=1400 + n)
+        b1 = S.random_blocks(qtype, n, k, seed=1500 + n)
+        x, xf = _activations(m, k, 1600 + m, "bfloat16", dev)
+        ref = oracle.dual_gemm_quant(xf, b0, b1, qtype, n, k, activation)
+        w = kernels.interleave_rows8(torch.from_numpy(b0).to(dev), torch.from_numpy(b1).to(dev))
+        assert np.array_equal(w.cpu().numpy(), kernels.interleave_rows8(b0, b1))
+        y = kernels.dual_gemm_rcr(x, w, qtype, activation)
+        assert y.shape == (m, n) and kernels.device_status() == 0
+        _, _, norm = oracle.max_errors(ref, y.float().cpu().numpy())
+        assert norm <= 2e-2, (qtype, activation, m, n, norm)
+        # the same numbers as two plain launches combined in fp32 (bf16 rounding of the intermediates aside)
+        if m <= 8:
+            g = kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), qtype, variant="mma").float()
+            u = kernels.gemm_rcr(x, torch.from_numpy(b1).to(dev), qtype, variant="mma").float()
+            two = (torch.nn.functional.silu(g) if activation == "silu" else torch.nn.functional.gelu(g, approximate="tanh")) * u
+            assert float((two - y.float()).abs().max()) <= 3e-2 * float(two.abs().max())
+    with pytest.raises(ValueError):
+        kernels.dual_gemm_rcr(x, w[:-8], qtype, activation)             # 2N must be a multiple of 16
+    with pytest.raises(RuntimeError):
+        kernels.dual_gemm_rcr(x.float(), w, qtype, activation)         # fp32 activations have no tensor-core variant
+
+
 def test_gemm_bias_and_batch_dims(dev):
     n, k = 48, 512
     blocks = S.random_blocks("Q4_K", n, k, seed=700)

@@ -78,6 +78,40 @@ def test_session_run_numpy_other_dtypes_and_shape_changes(tmp_path, dtype):
     mod.close()
 
 
+@pytest.mark.parametrize("activation", ["silu", "fast_gelu"])
+def test_session_dual_gemm_matches_oracle(tmp_path, activation):
+    """dual_gemm_rcr_<act> on two GGUF weights through compile -> load -> run, decode and prefill sizes."""
+    from dinoml_v2_b200.constant_sources import GGUFConstant
+    n, k = 136, 2048
+    b0, b1 = S.random_blocks("Q6_K", n, k, 21), S.random_blocks("Q6_K", n, k, 22)
+    op = getattr(dml.ops, f"dual_gemm_rcr_{activation}")
+
+    class Gate(dml.Module):
+        def __init__(self):
+            self.w_gate = dml.Parameter([n, k], dtype="bfloat16")
+            self.w_up = dml.Parameter([n, k], dtype="bfloat16")
+
+        def forward(self, x):
+            return op(x, self.w_gate, self.w_up)
+
+    spec = dml.trace(Gate(), inputs={"x": dml.TensorSpec([dml.Dim("m", 1, 64), k], "bfloat16")},
+                     constants={"w_gate": GGUFConstant.from_blocks(b0, "Q6_K", (n, k), tensor="gate"),
+                                "w_up": GGUFConstant.from_blocks(b1, "Q6_K", (n, k), tensor="up")})
+    art = dml.compile(spec, dml.Target("cuda"), tmp_path / "art")
+    mod = dml.runtime.load(art.path)
+    plan = mod.load_encoded_constants()
+    assert [p["name"] for p in plan] == ["w_gate+w_up.rows8"]
+    sess = mod.create_session()
+    for m in (1, 7, 48):
+        x = S.random_activations(m, k, 30 + m, "float32")
+        xb = S.bf16_bits_to_float32(S.float32_to_bf16_bits(x))
+        y = sess.run_numpy({"x": x})["t0"]
+        ref = oracle.dual_gemm_quant(xb, b0, b1, "Q6_K", n, k, activation)
+        _, _, norm = oracle.max_errors(ref, y)
+        assert y.shape == (m, n) and norm <= 2e-2, (activation, m, norm)
+    mod.close()
+
+
 def test_session_benchmark_and_external_stream(tmp_path):
     n, k = 256, 1024
     art, blocks, _ = _artifact(tmp_path, "Q4_K", n, k)

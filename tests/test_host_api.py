@@ -216,3 +216,40 @@ def test_compile_writes_artifact_and_native_loader_parses_it(tmp_path):
     (art.path / "module_plan.txt").write_text("dinoml_b200_module_plan 1\nconstant w gguf 12 0 100 64 512 manual_runtime_load\n")
     assert lib.dino_module_load_deferred(str(art.path).encode(), ctypes.byref(h)) != 0
     assert b"encoded_nbytes does not match" in lib.dino_get_last_error()
+
+
+def test_dual_gemm_trace_fuses_the_two_weights_and_compiles(tmp_path):
+    """dml.ops.dual_gemm_rcr_silu on two GGUF weights: the traced node reads ONE constant with the rows interleaved in
+    groups of 8, the sources leave the artifact, manifest and launch plan name the gated kernel entry."""
+    n, k = 16, 256
+    b0, b1 = S.random_blocks("Q4_K", n, k, 1), S.random_blocks("Q4_K", n, k, 2)
+
+    class Gate(dml.Module):
+        def __init__(self):
+            self.w_gate = dml.Parameter([n, k], dtype="bfloat16")
+            self.w_up = dml.Parameter([n, k], dtype="bfloat16")
+
+        def forward(self, x):
+            return dml.ops.dual_gemm_rcr_silu(x, self.w_gate, self.w_up)
+
+    consts = {"w_gate": cs.GGUFConstant.from_blocks(b0, "Q4_K", (n, k), tensor="gate"),
+              "w_up": cs.GGUFConstant.from_blocks(b1, "Q4_K", (n, k), tensor="up")}
+    spec = dml.trace(Gate(), inputs={"x": dml.TensorSpec([dml.Dim("m", 1, 8), k], "bfloat16")}, constants=consts)
+    node = spec.graph["nodes"][0]
+    assert node["op"] == "dual_gemm_rcr_silu" and node["inputs"] == ["x", "w_gate+w_up.rows8"] and node["attrs"]["sources"] == ["w_gate", "w_up"]
+    assert [c["name"] for c in spec.graph["constants"]] == ["w_gate+w_up.rows8"]
+    fused = spec.constant_arrays["w_gate+w_up.rows8"].reshape(2 * n, -1)
+    assert np.array_equal(fused[0:8], b0[0:8]) and np.array_equal(fused[8:16], b1[0:8]) and np.array_equal(fused[16:24], b0[8:16])
+    c = spec.graph["constants"][0]
+    assert c["shape"] == [2 * n, k] and c["storage"]["derived"]["kind"] == "interleave_rows8" and c["nbytes"] == 2 * b0.nbytes
+    art = dml.compile(spec, dml.Target("cuda"), tmp_path / "art")
+    item = json.loads((art.path / "kernel_manifest.json").read_text())["required_kernels"][0]
+    assert item["kernel_symbol"] == "dinoml_b200_gguf_dual_gemm_rcr" and not item["has_profiler"]
+    assert [cand["variant"] for cand in item["candidates"]] == ["mma", "umma"]
+    assert item["candidates"][0]["epilogue"] == "left_silu_and_mul"
+    plan = (art.path / "module_plan.txt").read_text()
+    assert "node dual_gemm_rcr_silu x w_gate+w_up.rows8 - t0 0" in plan
+    # mismatched weights are refused at trace time
+    consts["w_up"] = cs.GGUFConstant.from_blocks(S.random_blocks("Q6_K", n, k, 3), "Q6_K", (n, k), tensor="up")
+    with pytest.raises(NotImplementedError):
+        dml.trace(Gate(), inputs={"x": dml.TensorSpec([1, k], "bfloat16")}, constants=consts)

@@ -164,3 +164,24 @@ def test_reference_cpu_kernel_build_matches_golden(gemm_golden):
         _, rel, norm = oracle.max_errors(y_ref, got)
         tol = {"float32": 1e-4, "float16": 2e-3, "bfloat16": 1.6e-2}[dtype]
         assert rel <= tol and norm <= tol, (i, rel, norm)
+
+
+def test_dual_gemm_oracle_and_row_interleave():
+    """silu / fast_gelu gating in float32 as the reference CPU template computes it, and the row order the fused kernels read."""
+    from dinoml_v2_b200 import synthetic as S
+    n, k = 16, 256
+    b0, b1 = S.random_blocks("Q4_K", n, k, 1), S.random_blocks("Q4_K", n, k, 2)
+    x = S.random_activations(3, k, 3, "float32")
+    left = oracle.gemm_quant(x, b0, "Q4_K", n, k).astype(np.float64)
+    right = oracle.gemm_quant(x, b1, "Q4_K", n, k).astype(np.float64)
+    want = left / (1.0 + np.exp(-left)) * right
+    got = oracle.dual_gemm_quant(x, b0, b1, "Q4_K", n, k, "silu")
+    assert got.dtype == np.float32 and np.allclose(got, want, rtol=1e-5, atol=1e-6)
+    gelu = 0.5 * left * (1.0 + np.tanh(0.7978845608 * left * (1.0 + 0.044715 * left * left))) * right
+    assert np.allclose(oracle.dual_gemm_quant(x, b0, b1, "Q4_K", n, k, "fast_gelu"), gelu, rtol=1e-5, atol=1e-6)
+    rows0, rows1 = np.arange(16, dtype=np.uint8).reshape(16, 1), 100 + np.arange(16, dtype=np.uint8).reshape(16, 1)
+    order = [0, 1, 2, 3, 4, 5, 6, 7, 100, 101, 102, 103, 104, 105, 106, 107, 8, 9, 10, 11, 12, 13, 14, 15, 108, 109, 110, 111, 112, 113, 114, 115]
+    # interleave_rows8 needs torch only for tensors; numpy inputs stay on the CPU
+    pytest = __import__("pytest")
+    kernels = pytest.importorskip("dinoml_v2_b200.kernels")
+    assert kernels.interleave_rows8(rows0, rows1).reshape(-1).tolist() == order
