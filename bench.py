@@ -504,12 +504,13 @@ def run_multi(args):
         # Decode sizes go over peer memory (the GEMV kernel stores into every GPU's gather buffer, one small kernel
         # finishes each collective); NCCL is the fallback and is timed beside it.
         step, mode, nccl_ms = step_nccl, "nccl", None
-        if m <= 64:                                         # decode and small-batch sizes: mma GEMV or tcgen05 kernel, both with a scatter epilogue
+        if m <= 64 and os.environ.get("DINOML_B200_PEER_PATH", "1") != "0":   # decode and small-batch sizes: mma GEMV or tcgen05 kernel, both with a scatter epilogue
             try:
                 for f in ffns:
                     f.enable_peer_path(m, torch.bfloat16, share_with=ffns[0] if f is not ffns[0] else None)
                 step_nccl(); step_peer()
                 torch.cuda.synchronize()
+                assert kernels.device_status() == 0, "a bounded device-side wait gave up on the peer path"
                 ref = od.clone()
                 ffns[-1].down_proj(h_slice, od)
                 torch.cuda.synchronize()
