@@ -145,6 +145,39 @@ def bench_gemm(qtype, n, k, m, steps, warmup, l2, variant="auto", copies=None):
             "variant": kernels.select_variant(qtype, "bfloat16", m, n, k) if variant == "auto" else variant}
 
 
+def bench_dual(n, k, m, steps, warmup, l2, qtype="Q4_K"):
+    """silu(x Wgate^T) * (x Wup^T) in one launch on the row-interleaved pair, next to the two plain launches it replaces."""
+    import torch
+
+    from dinoml_v2_b200 import kernels, synthetic
+    from dinoml_v2_b200.gguf_blocks import encoded_nbytes
+    dev = torch.device("cuda")
+    nbytes = 2 * encoded_nbytes(qtype, n, k)
+    r = rotation_copies(nbytes, l2, cap=6)
+    gates = [synthetic.random_blocks_torch(qtype, n, k, 6000 + 2 * i, dev) for i in range(r)]
+    ups = [synthetic.random_blocks_torch(qtype, n, k, 6001 + 2 * i, dev) for i in range(r)]
+    fused = [kernels.interleave_rows8(g, u) for g, u in zip(gates, ups)]
+    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    outs = [torch.empty(m, n, device=dev, dtype=torch.bfloat16) for _ in range(2 * r)]
+
+    def one_launch():
+        for i in range(r):
+            kernels.dual_gemm_rcr(x, fused[i], qtype, "silu", out=outs[i])
+
+    def two_launches():
+        for i in range(r):
+            kernels.gemm_rcr(x, gates[i], qtype, out=outs[i])
+            kernels.gemm_rcr(x, ups[i], qtype, out=outs[r + i])
+
+    stream = torch.cuda.Stream()
+    res = {}
+    for name, fn in (("dual", one_launch), ("two_gemm_rcr", two_launches)):
+        g = graph_of(fn, stream)
+        res[name + "_us"] = time_steps(g.replay, steps, warmup, stream) * 1e3 / (steps * r)
+    res["weight_gbs"] = nbytes / res["dual_us"] / 1e3
+    return res
+
+
 def bench_dequant(qtype, n, k, dtype, steps, warmup):
     import torch
 
@@ -378,6 +411,7 @@ def run_single(args):
                                              "variant": b["variant"]})(bench_gemm("Q8_0", 4096, 4096, 1, extra_steps, extra_warm, l2))
     extras["dequant"] = {f"{q}_{dt}": bench_dequant(q, nn, kk, dt, extra_steps, extra_warm)
                          for (q, nn, kk) in (("Q4_K", 11008, 4096), ("Q6_K", 4096, 14336), ("Q8_0", 4096, 4096)) for dt in ("float16", "float32")}
+    extras["dual_gate_up_q4k_14336x4096"] = {f"m{m}": bench_dual(14336, 4096, m, extra_steps, extra_warm, l2) for m in (1, 16)}
     try:
         extras["cfg4_llama8b_decode_step"] = bench_decode_step(extra_steps, extra_warm)
     except torch.cuda.OutOfMemoryError as exc:       # pragma: no cover - 4.9 GB of weights, not expected on a B200

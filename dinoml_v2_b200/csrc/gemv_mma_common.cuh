@@ -56,6 +56,11 @@ __device__ __forceinline__ float byte_to_float(uint32_t word, int i) {
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
+// 16-byte shared-memory destination of which only the first `bytes` (1..15) are read from global memory; the rest is
+// zero-filled.  Used where a 16-byte chunk would cross the end of the weight buffer.
+__device__ __forceinline__ void cp_async16_partial(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");

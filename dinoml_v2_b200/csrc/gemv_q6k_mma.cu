@@ -15,8 +15,10 @@
 // group), several stages in flight, launched with programmatic stream serialization (weights are prefetched
 // before the wait on the preceding kernel).  210-byte blocks are only 2-byte aligned: a stage copies the
 // 16-byte aligned window around its 840 bytes, and a warp whose block starts 2 bytes off a word boundary
-// (every odd block of a row) rebuilds each 32-bit word from two aligned loads with a byte permute.  Rows must
-// be 16-byte multiples (K % 2048 == 0) so that the window offset is the same for every row.
+// (every odd block of a row) rebuilds each 32-bit word from two aligned loads with a byte permute.  When rows are
+// 16-byte multiples (K % 2048 == 0) the window offset is the same for every row and the phase of a block is known per
+// warp; any other K % 256 == 0 runs the RAGGED instantiation, where every row has its own window offset and every
+// word load decides its phase at run time.
 // Lane (g = lane/4, t = lane%4) feeds rows g and g+8 and, in every 16-wide sub-block, the weights 4t..4t+3.
 //
 // Behavioural ancestor in the reference: the small-M "wave" kernels of the fused prototype
@@ -51,23 +53,30 @@ __device__ __forceinline__ uint32_t q6_center(uint32_t pair) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// 32-bit word at a shared-memory address that is 4-byte aligned (ODD = false) or 2 bytes past alignment.
-template <bool ODD>
+// 32-bit word at a shared-memory address that is 4-byte aligned (MODE 0), 2 bytes past alignment (MODE 1), or either,
+// decided per address at run time (MODE 2: weight rows that are not 16-byte multiples put every row at its own phase).
+enum : int { Q6_ALIGNED = 0, Q6_ODD = 1, Q6_RUNTIME = 2 };
+template <int MODE>
 __device__ __forceinline__ uint32_t lds_word(const uint8_t* p) {
-  if (!ODD) return *reinterpret_cast<const uint32_t*>(p);
-  const uint32_t* q = reinterpret_cast<const uint32_t*>(p - 2);
-  return __byte_perm(q[0], q[1], 0x5432);
+  if (MODE == Q6_ALIGNED) return *reinterpret_cast<const uint32_t*>(p);
+  if (MODE == Q6_ODD) {
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(p - 2);
+    return __byte_perm(q[0], q[1], 0x5432);
+  }
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(a & ~uintptr_t(3));
+  return __byte_perm(q[0], q[1], (a & 2) ? 0x5432u : 0x3210u);
 }
 
-// One super-block of 16 rows on one warp.  st: the warp's block of row 0 in the stage (row r at st + r * pitch).
-template <typename T, int NT, int MC, bool ODD>
-__device__ __forceinline__ void q6k_superblock(const uint8_t* st, float (*sS)[kQ6ScalePitch], const T* const (&xrow)[NT], int sb, int lane,
-                                               float (&res)[NT][4]) {
+// One super-block of 16 rows on one warp.  blk: the staged block of row lane/2 (this lane decodes half of its scales),
+// b0 / b1: the staged blocks of rows lane/4 and lane/4 + 8 (this lane's MMA rows).
+template <typename T, int NT, int MC, int ODD>
+__device__ __forceinline__ void q6k_superblock(const uint8_t* blk, const uint8_t* b0, const uint8_t* b1, float (*sS)[kQ6ScalePitch],
+                                               const T* const (&xrow)[NT], int sb, int lane, float (&res)[NT][4]) {
   using MT = MmaType<T>;
   const int g = lane >> 2, t = lane & 3;
   {   // lane pair (row = lane/2, half = lane%2): 8 int8 scales -> d * sc as floats in shared memory
     const int srow = lane >> 1, shalf = lane & 1;
-    const uint8_t* blk = st + srow * kQ6Pitch;
     const float d = half_bits_to_float(*reinterpret_cast<const uint16_t*>(blk + 208));
     const uint32_t s0 = lds_word<ODD>(blk + 192 + 8 * shalf) ^ 0x80808080u;   // int8 + 128 as unsigned bytes
     const uint32_t s1 = lds_word<ODD>(blk + 196 + 8 * shalf) ^ 0x80808080u;
@@ -80,8 +89,6 @@ __device__ __forceinline__ void q6k_superblock(const uint8_t* st, float (*sS)[kQ
     *reinterpret_cast<float4*>(&sS[srow][8 * shalf + 4]) = hi;
   }
   __syncwarp();
-  const uint8_t* b0 = st + g * kQ6Pitch;             // block of row g; row g+8 is 8 pitches further
-  const uint8_t* b1 = b0 + 8 * kQ6Pitch;
 #pragma unroll
   for (int hb = 0; hb < 2; ++hb) {                   // 128-weight half of the super-block
     const float4 da0 = *reinterpret_cast<const float4*>(&sS[g][8 * hb]), da1 = *reinterpret_cast<const float4*>(&sS[g][8 * hb + 4]);
@@ -129,7 +136,9 @@ __device__ __forceinline__ void q6k_superblock(const uint8_t* st, float (*sS)[kQ
 // sequence of K-stages.  NSTAGE: shared-memory stage slots (dynamic shared memory).
 // SLICED: grid.y K slices per row tile, reduced through the cluster's distributed shared memory (see gemv_mma_common.cuh).
 // SCATTER: the result also goes to the extra destinations in `peers` (see PeerOut).
-template <typename T, int MXC, int NW, int NSTAGE, bool SLICED, bool SCATTER>
+// RAGGED: K is any multiple of 256 - weight rows need not be 16-byte multiples (every row then sits at its own phase
+// inside its staged window) and the last stage may hold fewer than 4 super-blocks.
+template <typename T, int MXC, int NW, int NSTAGE, bool SLICED, bool SCATTER, bool RAGGED>
 __global__ void __launch_bounds__(NW * 32)
 gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y, int m,
                     int n, int k, const PeerOut peers) {
@@ -152,7 +161,7 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   const int g = lane >> 2, t = lane & 3;
   const int r_base = blockIdx.x * kQ6Rows;
   const int nsb = k >> 8;
-  const int nstages_all = nsb / kQ6StageSb;          // K % 2048 == 0: whole stages only
+  const int nstages_all = (nsb + kQ6StageSb - 1) / kQ6StageSb;
   // K slice of this CTA (grid.y = cluster size = slices per row tile)
   const int ks = SLICED ? int(gridDim.y) : 1, kr = SLICED ? int(cluster_rank()) : 0;
   const int per_slice = (nstages_all + ks - 1) / ks;
@@ -165,18 +174,36 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   // Copy assignment inside a warp group: 8 threads per weight row, thread (gtid%8) moves 16-byte chunks
   // (gtid%8) + 8j of the row's window.
   const int cp_row = gtid >> 3, cp_c0 = gtid & 7;
-  const uint8_t* cp_src = w + int64_t(min(r_base + cp_row, n - 1)) * row_bytes;
+  const int64_t cp_row_off = int64_t(min(r_base + cp_row, n - 1)) * row_bytes;   // byte offset of the copied row in w
+  const uint8_t* cp_src = w + cp_row_off;
   const uint32_t cp_dst = sW_u32 + cp_row * kQ6Pitch + cp_c0 * 16;
+  const int64_t total_bytes = int64_t(n) * row_bytes;
   auto issue_stage = [&](int ls) {                                     // ls: stage index inside this CTA's slice
     if (ls < nstages) {
       const int s = s_first + ls;
-      const int start = (s * kQ6StageSrc) & ~15;                       // window start inside the row
-      const uint8_t* src = cp_src + start + cp_c0 * 16;
       const uint32_t dst = cp_dst + (ls % NSTAGE) * kQ6StageBytes;
+      if (!RAGGED) {
+        const int start = (s * kQ6StageSrc) & ~15;                     // window start inside the row
+        const uint8_t* src = cp_src + start + cp_c0 * 16;
 #pragma unroll
-      for (int j = 0; j < 7; ++j) {
-        const int c = cp_c0 + 8 * j;
-        if (c < kQ6Chunks && start + 16 * c < row_bytes) cp_async16(dst + 128 * j, src + 128 * j);
+        for (int j = 0; j < 7; ++j) {
+          const int c = cp_c0 + 8 * j;
+          if (c < kQ6Chunks && start + 16 * c < row_bytes) cp_async16(dst + 128 * j, src + 128 * j);
+        }
+      } else {
+        // window = the 16-byte aligned span of the weight buffer around this row's 840 bytes (w itself is 16-byte
+        // aligned); it may run into the next row, never past the end of the buffer
+        const int64_t start = (cp_row_off + int64_t(s) * kQ6StageSrc) & ~int64_t(15);
+        const uint8_t* src = w + start + cp_c0 * 16;
+#pragma unroll
+        for (int j = 0; j < 7; ++j) {
+          const int c = cp_c0 + 8 * j;
+          const int64_t left = total_bytes - (start + 16 * c);
+          if (c < kQ6Chunks + 1 && left > 0) {
+            if (left >= 16) cp_async16(dst + 128 * j, src + 128 * j);
+            else cp_async16_partial(dst + 128 * j, src + 128 * j, int(left));
+          }
+        }
       }
     }
     cp_async_commit();
@@ -204,11 +231,23 @@ gemv_q6k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
     const int ls = it * SPI + grp;
     if (ls < nstages) {
       const int s = s_first + ls;
-      // the stage window starts (s * 840) % 16 bytes before the stage's first block; block wq follows 210 * wq later
-      const uint8_t* st = sW + (ls % NSTAGE) * kQ6StageBytes + ((s * kQ6StageSrc) & 15) + wq * 210;
+      const uint8_t* slot = sW + (ls % NSTAGE) * kQ6StageBytes;
       const int sb = s * kQ6StageSb + wq;
-      if (wq & 1) q6k_superblock<T, NT, MC, true>(st, sS[warp], xrow, sb, lane, res);
-      else q6k_superblock<T, NT, MC, false>(st, sS[warp], xrow, sb, lane, res);
+      if (RAGGED) {
+        if (sb < nsb) {
+          // row r's window starts (row offset + s * 840) % 16 bytes before its first block of the stage
+          auto block_of = [&](int r) {
+            const int64_t off = int64_t(min(r_base + r, n - 1)) * row_bytes + int64_t(s) * kQ6StageSrc;
+            return slot + r * kQ6Pitch + int(off & 15) + wq * 210;
+          };
+          q6k_superblock<T, NT, MC, Q6_RUNTIME>(block_of(lane >> 1), block_of(g), block_of(g + 8), sS[warp], xrow, sb, lane, res);
+        }
+      } else {
+        // the stage window starts (s * 840) % 16 bytes before the stage's first block; block wq follows 210 * wq later
+        const uint8_t* st = slot + ((s * kQ6StageSrc) & 15) + wq * 210;
+        if (wq & 1) q6k_superblock<T, NT, MC, Q6_ODD>(st + (lane >> 1) * kQ6Pitch, st + g * kQ6Pitch, st + (g + 8) * kQ6Pitch, sS[warp], xrow, sb, lane, res);
+        else q6k_superblock<T, NT, MC, Q6_ALIGNED>(st + (lane >> 1) * kQ6Pitch, st + g * kQ6Pitch, st + (g + 8) * kQ6Pitch, sS[warp], xrow, sb, lane, res);
+      }
     }
   }
   cp_async_wait<0>();
@@ -267,14 +306,16 @@ template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
 static int launch_q6k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
   const int tiles = (n + kQ6Rows - 1) / kQ6Rows;
   constexpr size_t smem = size_t(NSTAGE) * kQ6StageBytes;
-  auto kern = peers.count > 0 ? gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true> : gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false>;
-  static bool opted_in[2] = {false, false};   // dynamic shared memory beyond 48 KB needs the opt-in, once per kernel
-  bool& done = opted_in[peers.count > 0 ? 1 : 0];
+  const bool ragged = k % 2048 != 0;          // rows that are not 16-byte multiples, or a last stage of fewer than 4 super-blocks
+  auto kern = ragged ? (peers.count > 0 ? gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true, true> : gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false, true>)
+                     : (peers.count > 0 ? gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true, false> : gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false, false>);
+  static bool opted_in[4] = {false, false, false, false};   // dynamic shared memory beyond 48 KB needs the opt-in, once per kernel
+  bool& done = opted_in[(peers.count > 0 ? 1 : 0) + (ragged ? 2 : 0)];
   if (!done) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
     done = true;
   }
-  const int ks = SLICED ? gemv_k_slices(tiles, (k >> 8) / kQ6StageSb, NSTAGE) : 1;
+  const int ks = SLICED ? gemv_k_slices(tiles, ((k >> 8) + kQ6StageSb - 1) / kQ6StageSb, NSTAGE) : 1;
   const cudaError_t err = gemv_launch(kern, tiles, ks, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
                                       static_cast<const T*>(bias), static_cast<T*>(c), m, n, k, peers);
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
@@ -302,9 +343,8 @@ static int launch_q6k(const void* a, const void* b, const void* bias, void* c, i
   return launch_q6k_m<T, 16>(a, b, bias, c, m, n, k, peers, s);
 }
 
-// Rows must be 16-byte multiples: 210 * (k / 256) % 16 == 0  <=>  k % 2048 == 0.
 bool gemv_q6k_mma_supports(int dtype, int m, int k) {
-  return (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 16 && k % 2048 == 0;
+  return (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 16 && k % 256 == 0;
 }
 
 int gemv_q6k_mma(const void* a, const void* b, const void* bias, void* c, int dtype, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {

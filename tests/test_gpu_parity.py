@@ -137,11 +137,25 @@ def test_gemv_mma_q6k(dev, dtype):
         bound = 4e-3 if dtype == "bfloat16" else 6e-4     # output rounding of bf16 (2^-9) / fp16 (2^-11)
         assert norm <= bound, (dtype, m, n, k, rel, norm)
         _check(y, ref, dtype, ("mma q6k", m, n, k))
-    # rows that are not 16-byte multiples stay with the simt variant
-    assert kernels.select_variant("Q6_K", dtype, 1, 64, 1024) == "simt"
-    with pytest.raises(RuntimeError, match="alignment"):
-        kernels.gemm_rcr(torch.zeros(1, 1024, device=dev, dtype=TDT[dtype]),
-                         torch.from_numpy(S.random_blocks("Q6_K", 64, 1024, seed=1)).to(dev), "Q6_K", variant="mma")
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_gemv_mma_q6k_ragged_k(dev, dtype):
+    """Any K % 256 == 0: weight rows of 210 * K / 256 bytes that are not 16-byte (or even 4-byte) multiples, last stage
+    with fewer than 4 super-blocks, last row ending right at the end of the buffer."""
+    for (m, n, k) in [(1, 16, 256), (1, 33, 768), (2, 50, 1024), (1, 100, 2816), (4, 47, 1280), (8, 64, 3328), (16, 40, 1792),
+                      (1, 256, 11008), (3, 17, 4352)]:
+        blocks = S.random_blocks("Q6_K", n, k, seed=540 + m + n)
+        x, xf = _activations(m, k, 640 + m, dtype, dev)
+        ref = oracle.gemm_quant(xf, blocks, "Q6_K", n, k)
+        assert kernels.select_variant("Q6_K", dtype, m, n, k) == "mma"
+        # an exact-size device buffer: the kernel must not read past the last row
+        y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev).clone(), "Q6_K", variant="mma")
+        got = y.float().cpu().numpy()
+        _, rel, norm = oracle.max_errors(ref, got)
+        bound = 4e-3 if dtype == "bfloat16" else 6e-4
+        assert norm <= bound, (dtype, m, n, k, rel, norm)
+        _check(y, ref, dtype, ("mma q6k ragged", m, n, k))
 
 
 UMMA_SHAPES = [  # (m, n, k)
