@@ -537,7 +537,7 @@ def run_multi(args):
         stream = torch.cuda.current_stream()
         # Decode sizes go over peer memory (the GEMV kernel stores into every GPU's gather buffer, one small kernel
         # finishes each collective); NCCL is the fallback and is timed beside it.
-        step, mode, nccl_ms = step_nccl, "nccl", None
+        step, mode, nccl_ms, swiglu_ms = step_nccl, "nccl", None, None
         if m <= 64 and os.environ.get("DINOML_B200_PEER_PATH", "1") != "0":   # decode and small-batch sizes: mma GEMV or tcgen05 kernel, both with a scatter epilogue
             try:
                 for f in ffns:
@@ -552,6 +552,11 @@ def run_multi(args):
                 assert float((ref.float() - od.float()).abs().max()) <= 2e-2 * float(od.float().abs().max()), "peer all-reduce differs from NCCL"
                 nccl_ms = time_steps(step_nccl, max(3, K // 2), W, stream, barrier=dist.barrier)
                 step, mode = step_peer, "peer"
+
+                def step_swiglu():                          # extra: the gated MLP with no all-gather at all
+                    for f in ffns:
+                        f.swiglu_mlp_peer(x, od)
+                swiglu_ms = time_steps(step_swiglu, max(3, K // 2), W, stream, barrier=dist.barrier)
             except Exception as exc:                        # pragma: no cover - no symmetric memory on this box
                 if rank == 0:
                     print(f"peer path unavailable ({type(exc).__name__}: {str(exc)[:200]}); using NCCL", file=sys.stderr)
@@ -571,6 +576,10 @@ def run_multi(args):
             tn = torch.tensor([nccl_ms], device=dev, dtype=torch.float64)
             dist.all_reduce(tn, op=dist.ReduceOp.MAX)
             results[m]["nccl_ms_per_ffn"] = float(tn.item()) / max(3, K // 2) / r
+        if swiglu_ms is not None:
+            ts = torch.tensor([swiglu_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+            results[m]["fused_swiglu_mlp_ms_per_ffn"] = float(ts.item()) / max(3, K // 2) / r
         if m == 1:
             clocks = clock_ctx.summary() if clock_ctx else None
         del ffns

@@ -94,6 +94,19 @@ class ShardedFFN:
         self.xchg_down.finish_reduce(out)
         return out
 
+    def swiglu_mlp_peer(self, x, out):
+        """The whole gated MLP, out [M, hidden] = (silu(x Wgate^T) * (x Wup^T)) Wdown^T, in three launches and no
+        all-gather: rank r's rows of gate / up are exactly the K-slice of down it owns, so the gated activations stay
+        local (one dual GEMM on the row-interleaved gate / up shard), and only the down projection's partial sums cross
+        NVLink (scatter epilogue + barrier-and-sum kernel).  Needs `enable_peer_path`."""
+        from . import kernels
+        if not hasattr(self, "gate_up_rows8"):
+            self.gate_up_rows8 = kernels.interleave_rows8(self.gate, self.up)
+        h = kernels.dual_gemm_rcr(x, self.gate_up_rows8, self.qtype, "silu")
+        self.xchg_down.scatter_gemv(h, self.down, self.qtype)
+        self.xchg_down.finish_reduce(out)
+        return out
+
     def down_proj(self, h_slice, out):
         """h_slice [M, ffn/world] = this rank's K-slice of the down-projection input; out [M, hidden] is summed in place."""
         import torch.distributed as dist
