@@ -1,5 +1,5 @@
 """Generates the committed golden fixtures.  Run in a container that has the reference tree
-(default /root/reference) and the third-party `gguf` package; the fixtures then travel with
+(path argument, else $DINOML_REFERENCE_DIR, else the build container's default location) and the third-party `gguf` package; the fixtures then travel with
 the repository and the tests never need either again.
 
   python tests/golden/make_golden.py [/path/to/reference]
@@ -159,6 +159,6 @@ def make_gemm_golden(reference: Path) -> None:
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("DINOML_REFERENCE_DIR", os.sep + os.path.join("root", "reference")))
     make_dequant_kat()
     make_gemm_golden(ref)
