@@ -433,13 +433,13 @@ def run_single(args):
         "roofline": {"kernel": "gemv_q4k_mma_kernel (Q4_K M=1)", "bound": "hbm", "achieved": nbytes / us_launch / 1e3, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": nbytes / us_launch / 1e3 / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind} copy bandwidth",
                      "frac_of_nominal_8tbs": nbytes / us_launch / 1e3 / NOMINAL_HBM_GBS, "us_per_launch": us_launch,
-                     "algorithmic_bytes_per_launch": nbytes, "traffic": 25_384_704,
+                     "algorithmic_bytes_per_launch": nbytes, "traffic": 25_387_776,
                      "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture (profiles/)"},
         "roofline_prefill": {"kernel": "gemm_umma_kernel (Q6_K 4096x14336, M=512)", "bound": "tensor", "achieved": m512["tflops"],
                              "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": m512["frac_of_measured_burst"],
                              "peak_kind": f"of {peak_kind} cuBLAS bf16 burst", "us_per_launch": m512["us_per_launch"],
-                             "frac_of_sustained": m512["frac_of_measured_sustained"], "traffic": 67_533_056,
-                             "traffic_source": "dram bytes read + written of one ncu capture (profiles/): weights 48.2 MB + activations 14.7 MB + output 4.2 MB"},
+                             "frac_of_sustained": m512["frac_of_measured_sustained"], "traffic": 68_747_520,
+                             "traffic_source": "dram bytes read + written of one ncu capture (profiles/): weights 48.2 MB + activations 14.7 MB + output 4.2 MB + spilled partial tiles"},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": K * r, "clocks": clocks.summary(), "extras": extras,
         "device": {"name": props.name, "sms": props.multi_processor_count, "l2_bytes": l2},
     }
