@@ -68,3 +68,28 @@ def test_shard_validation():
         sharding.shard_rows(b, 0, 3)
     s0, k0 = sharding.shard_k(S.random_blocks("Q4_K", 8, 1024, 1), "Q4_K", 1024, 1, 2)
     assert k0 == 512 and s0.shape == (8, 288)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gated_mlp_needs_no_all_gather(world):
+    """The identity behind ShardedFFN.swiglu_mlp_peer: rank r's rows of gate / up are the K-slice of down it owns, so
+    sum over ranks of (silu(x gate_r^T) * (x up_r^T)) down_r^T equals the unsharded gated MLP.  Oracle on every 'rank',
+    the sum stands in for the all-reduce; also checks the row-interleaved weight the dual GEMM reads."""
+    import oracle
+    from dinoml_v2_b200 import kernels, sharding, synthetic as S
+    hidden, ffn, m = 512, 1024, 2
+    gate, up = S.random_blocks("Q4_K", ffn, hidden, 11), S.random_blocks("Q4_K", ffn, hidden, 12)
+    down = S.random_blocks("Q4_K", hidden, ffn, 13)
+    x = S.random_activations(m, hidden, 14, "float32")
+    full_h = oracle.dual_gemm_quant(x, gate, up, "Q4_K", ffn, hidden, "silu")
+    want = oracle.gemm_quant(full_h, down, "Q4_K", hidden, ffn)
+    total = np.zeros_like(want, dtype=np.float64)
+    for r in range(world):
+        g_r, u_r = sharding.shard_rows(gate, r, world), sharding.shard_rows(up, r, world)
+        d_r, k_r = sharding.shard_k(down, "Q4_K", ffn, r, world)
+        fused = kernels.interleave_rows8(g_r, u_r)
+        assert np.array_equal(fused[0:8], g_r[0:8]) and np.array_equal(fused[8:16], u_r[0:8])
+        h_r = oracle.dual_gemm_quant(x, g_r, u_r, "Q4_K", ffn // world, hidden, "silu")
+        assert np.array_equal(h_r, full_h[:, r * k_r:(r + 1) * k_r])
+        total += oracle.gemm_quant(h_r, d_r, "Q4_K", hidden, k_r)
+    assert np.abs(total - want).max() <= 1e-4 * np.abs(want).max()
