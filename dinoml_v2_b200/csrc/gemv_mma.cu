@@ -35,6 +35,8 @@ namespace b200gguf {
 
 int check_gemm_args(const void* a, const void* b, const void* c, int qtype, int dtype, int m, int n, int k);
 bool gemv_q6k_mma_supports(int dtype, int m, int k);
+bool gemv_q8_0_mma_supports(int dtype, int m, int k);
+int gemv_q8_0_mma(const void* a, const void* b, const void* bias, void* c, int dtype, int m, int n, int k, cudaStream_t s);
 int gemv_q6k_mma(const void* a, const void* b, const void* bias, void* c, int dtype, int m, int n, int k, const PeerOut& peers, cudaStream_t s);
 
 constexpr int kGemvWarps = 4;
@@ -313,6 +315,7 @@ static int launch_q4k(const void* a, const void* b, const void* bias, void* c, i
 bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k) {
   (void)n;
   if (qtype == QTYPE_Q6_K) return gemv_q6k_mma_supports(dtype, m, k);
+  if (qtype == QTYPE_Q8_0) return gemv_q8_0_mma_supports(dtype, m, k);
   return qtype == QTYPE_Q4_K && (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 16 && k % 256 == 0;
 }
 
@@ -323,10 +326,14 @@ int gemm_rcr_mma_peers(const void* a, const void* b, const void* bias, void* c, 
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (m > 16) return RC_RANGE;
-  if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
-  if (!gemv_mma_supports(qtype, dtype, m, n, k)) return RC_ALIGN;   // Q6_K rows that are not 16-byte multiples
+  if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K && qtype != QTYPE_Q8_0) return RC_QTYPE;
+  if (!gemv_mma_supports(qtype, dtype, m, n, k)) return RC_ALIGN;   // Q8_0 with K % 256 != 0
   if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;  // 16-byte cp.async sources, vector loads
   if (qtype == QTYPE_Q6_K) return gemv_q6k_mma(a, b, bias, c, dtype, m, n, k, peers, s);
+  if (qtype == QTYPE_Q8_0) {
+    if (peers.count > 0 || peers.act != ACT_NONE) return RC_RANGE;   // no scatter / gated epilogue for Q8_0
+    return gemv_q8_0_mma(a, b, bias, c, dtype, m, n, k, s);
+  }
   return dtype == DINO_BF16 ? launch_q4k<__nv_bfloat16>(a, b, bias, c, m, n, k, peers, s)
                             : launch_q4k<__half>(a, b, bias, c, m, n, k, peers, s);
 }

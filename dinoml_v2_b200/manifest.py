@@ -48,7 +48,7 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
     """Which kernel variants exist for a (qtype, dtype)."""
     variants = ["simt"]
     if dtype in ("float16", "bfloat16"):
-        if qtype in ("Q4_K", "Q6_K"):
+        if qtype in ("Q4_K", "Q6_K", "Q8_0"):
             variants.append("mma")
         if qtype in ("Q4_K", "Q6_K"):
             variants.append("umma")

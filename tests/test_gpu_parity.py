@@ -158,6 +158,27 @@ def test_gemv_mma_q6k_ragged_k(dev, dtype):
         _check(y, ref, dtype, ("mma q6k ragged", m, n, k))
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+def test_gemv_mma_q8_0(dev, dtype):
+    """Q8_0 decode GEMV on mma.sync (int8 split into two exact nibble operands): every M bucket, ragged N, whole and
+    partial K stages, extreme quants (-128 / 127) included by the synthetic distribution's tails plus a forced block."""
+    for (m, n, k) in [(1, 16, 256), (1, 1000, 4096), (2, 50, 512), (3, 129, 1536), (4, 128, 4096), (7, 33, 768), (8, 64, 2048),
+                      (9, 48, 1280), (13, 17, 1024), (16, 160, 4096)]:
+        blocks = S.random_blocks("Q8_0", n, k, seed=560 + m + n)
+        blocks[0, 2:34] = np.frombuffer(np.array([-128, 127] * 16, dtype=np.int8).tobytes(), dtype=np.uint8)   # first block of row 0
+        x, xf = _activations(m, k, 660 + m, dtype, dev)
+        ref = oracle.gemm_quant(xf, blocks, "Q8_0", n, k)
+        assert kernels.select_variant("Q8_0", dtype, m, n, k) == "mma"
+        y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), "Q8_0", variant="mma")
+        got = y.float().cpu().numpy()
+        _, rel, norm = oracle.max_errors(ref, got)
+        bound = 4e-3 if dtype == "bfloat16" else 6e-4     # output rounding of bf16 (2^-9) / fp16 (2^-11)
+        assert norm <= bound, (dtype, m, n, k, rel, norm)
+        _check(y, ref, dtype, ("mma q8_0", m, n, k))
+    # K that is not a multiple of 256 stays with the simt variant
+    assert kernels.select_variant("Q8_0", dtype, 1, 64, 96) == "simt"
+
+
 UMMA_SHAPES = [  # (m, n, k)
     (17, 128, 256), (64, 256, 512), (100, 200, 1024), (128, 384, 768), (200, 130, 512), (256, 128, 2048),
     (300, 512, 4096), (513, 256, 1024), (150, 256, 6144),
