@@ -239,12 +239,25 @@ static int launch_q8_cfg(const void* a, const void* b, const void* bias, void* c
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
+// Few row tiles (all CTAs resident at two per SM): six stage slots per CTA keep more bytes in flight; many row tiles:
+// four slots, so that three CTAs fit on an SM (the rule of the Q6_K kernel).
+template <typename T, int MXC>
+static int launch_q8_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
+  int sm_count = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if ((n + kQ8Rows - 1) / kQ8Rows <= 2 * sm_count) {
+    const int rc = launch_q8_cfg<T, MXC, 8, 6>(a, b, bias, c, m, n, k, s);
+    if (rc != RC_RANGE) return rc;
+  }
+  return launch_q8_cfg<T, MXC, 8, 4>(a, b, bias, c, m, n, k, s);
+}
+
 template <typename T>
 static int launch_q8(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
-  if (m == 1) return launch_q8_cfg<T, 1, 8, 4>(a, b, bias, c, m, n, k, s);
-  if (m == 2) return launch_q8_cfg<T, 2, 8, 4>(a, b, bias, c, m, n, k, s);
-  if (m <= 4) return launch_q8_cfg<T, 4, 8, 4>(a, b, bias, c, m, n, k, s);
-  if (m <= 8) return launch_q8_cfg<T, 8, 8, 4>(a, b, bias, c, m, n, k, s);
+  if (m == 1) return launch_q8_m<T, 1>(a, b, bias, c, m, n, k, s);
+  if (m == 2) return launch_q8_m<T, 2>(a, b, bias, c, m, n, k, s);
+  if (m <= 4) return launch_q8_m<T, 4>(a, b, bias, c, m, n, k, s);
+  if (m <= 8) return launch_q8_m<T, 8>(a, b, bias, c, m, n, k, s);
   return launch_q8_cfg<T, 16, 4, 3>(a, b, bias, c, m, n, k, s);
 }
 
