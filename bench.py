@@ -409,6 +409,11 @@ def run_single(args):
     extras["cfg3_q6k_prefill"] = prefill
     extras["cfg1_q8_0_m1_gpu"] = (lambda b: {"us_per_launch": b["us_per_launch"], "weight_gbs": b["weight_bytes"] / b["us_per_launch"] / 1e3,
                                              "variant": b["variant"]})(bench_gemm("Q8_0", 4096, 4096, 1, extra_steps, extra_warm, l2))
+    extras["cfg1_q8_0_prefill"] = {}
+    for (nn, kk, m) in ((4096, 4096, 512), (4096, 14336, 512)):
+        b = bench_gemm("Q8_0", nn, kk, m, extra_steps, extra_warm, l2, copies=3)
+        extras["cfg1_q8_0_prefill"][f"{nn}x{kk}_m{m}"] = {"us_per_launch": b["us_per_launch"], "variant": b["variant"],
+                                                          "tflops": 2.0 * m * nn * kk / b["us_per_launch"] / 1e6}
     extras["dequant"] = {f"{q}_{dt}": bench_dequant(q, nn, kk, dt, extra_steps, extra_warm)
                          for (q, nn, kk) in (("Q4_K", 11008, 4096), ("Q6_K", 4096, 14336), ("Q8_0", 4096, 4096)) for dt in ("float16", "float32")}
     extras["dual_gate_up_q4k_14336x4096"] = {f"m{m}": bench_dual(14336, 4096, m, extra_steps, extra_warm, l2) for m in (1, 16)}

@@ -84,7 +84,12 @@ int dual_gemm_rcr_peers(const void* a, const void* b01, void* c, const PeerOut& 
   PeerOut peers = dst;
   peers.act = activation;
   const int rows = 2 * n;                                              // rows of the interleaved weight
-  if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, rows, k);
+  if (variant == DINOML_B200_GGUF_VARIANT_AUTO) {
+    variant = select_variant(qtype, dtype, m, rows, k);
+    // the Q8_0 mma GEMV has no gated epilogue: from M = 9 the tcgen05 kernel takes the call instead
+    if (variant == DINOML_B200_GGUF_VARIANT_MMA && qtype == QTYPE_Q8_0 && gemm_umma_supports(qtype, dtype, m, rows, k))
+      variant = DINOML_B200_GGUF_VARIANT_UMMA;
+  }
   if (variant == DINOML_B200_GGUF_VARIANT_MMA) return gemm_rcr_mma_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, &peers, s);
   if (variant == DINOML_B200_GGUF_VARIANT_UMMA) return gemm_rcr_umma_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, &peers, s);
   return RC_RANGE;                                                     // the simt variant has no gated epilogue

@@ -158,6 +158,7 @@ template <> struct Pair<__nv_bfloat16> {
   static constexpr CUtensorMapDataType kTmaType = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   using V = __nv_bfloat162;
   static __device__ __forceinline__ V splat(float f) { return __float2bfloat162_rn(f); }
+  static __device__ __forceinline__ V pack(float lo, float hi) { return __floats2bfloat162_rn(lo, hi); }
   static __device__ __forceinline__ __nv_bfloat16 cvt(float f) { return __float2bfloat16_rn(f); }
   static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); }
 };
@@ -168,6 +169,7 @@ template <> struct Pair<__half> {
   static constexpr CUtensorMapDataType kTmaType = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   using V = __half2;
   static __device__ __forceinline__ V splat(float f) { return __float2half2_rn(f); }
+  static __device__ __forceinline__ V pack(float lo, float hi) { return __floats2half2_rn(lo, hi); }
   static __device__ __forceinline__ __half cvt(float f) { return __float2half_rn(f); }
   static __device__ __forceinline__ float up(__half v) { return __half2float(v); }
 };
@@ -212,23 +214,50 @@ __device__ __forceinline__ void q6k_fetch(const uint8_t* rowbase, int hb, int lh
 
 // Packed super-block window in shared memory: the 16-byte aligned span that contains one block of every row.
 // Q4_K blocks (144 B) are always aligned; a Q6_K block (210 B) starts 0..14 bytes into its window and the last
-// field read (d, through a 32-byte fetch at +208) ends at byte 240.  Both pitches are an odd number of 16-byte
-// chunks, so 16-byte reads of 8 consecutive rows hit all 32 banks.
+// field read (d, through a 32-byte fetch at +208) ends at byte 240.  Eight Q8_0 blocks (272 B per 256 weights, always
+// 16-byte aligned) are wider than a TMA box may be (256 elements), so they travel as two boxes of 144 B: blocks 0..3
+// start at byte 0 of the first, blocks 4..7 at byte 8 of the second (which starts at byte 128 of the 272).  Every pitch
+// is an odd number of 16-byte chunks, so 16-byte reads of 8 consecutive rows hit all 32 banks.
+//   kSuper: packed bytes per 256 weights of a row; kBoxes: TMA boxes per super-block; kSlots: super-blocks in the ring.
 template <int QT> struct RawGeom;
-template <> struct RawGeom<QTYPE_Q4_K> { static constexpr int kPitch = 144; };
-template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240; };
+template <> struct RawGeom<QTYPE_Q4_K> { static constexpr int kPitch = 144, kSuper = 144, kBoxes = 1, kSlots = 3; };
+template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240, kSuper = 210, kBoxes = 1, kSlots = 3; };
+template <> struct RawGeom<QTYPE_Q8_0> { static constexpr int kPitch = 144, kSuper = 272, kBoxes = 2, kSlots = 2; };
+
+// One Q8_0 block (B = 0..7 inside the 256 weights) of a row: 16 of its int8 quants (half LHALF) and its scale.
+// win: this row inside the box that holds blocks 4*(B/4) .. 4*(B/4)+3.
+template <int B>
+__device__ __forceinline__ void q8_fetch(const uint8_t* win, int lhalf, uint32_t* qw, float& d) {
+  constexpr int kStart = 8 * (B >> 2) + 34 * (B & 3);      // block start inside its box
+  constexpr int kPhase = ((kStart + 2) & 15) >> 1;
+  fetch16<kPhase>(win + ((kStart + 2) & ~15) + 16 * lhalf, qw);
+  d = half_bits_to_float(*reinterpret_cast<const uint16_t*>(win + kStart));
+}
+// 4 int8 quants -> two 16-bit pairs of q * d, each rounded once.  With u = q + 128 in byte 1 of a float's mantissa,
+// f = 2^23 + 256 u, and f * (d / 256) - (2^23 + 2^15) * (d / 256) = q * d with every term exact in fp32.
+template <typename T>
+__device__ __forceinline__ void q8_to_pairs(uint32_t u, float d256, float c, uint32_t& p01, uint32_t& p23) {
+  using P = Pair<T>;
+  const uint32_t v = u ^ 0x80808080u;
+  const float f0 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7404));
+  const float f1 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7414));
+  const float f2 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7424));
+  const float f3 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7434));
+  p01 = as_u32<typename P::V>(P::pack(fmaf(f0, d256, c), fmaf(f1, d256, c)));
+  p23 = as_u32<typename P::V>(P::pack(fmaf(f2, d256, c), fmaf(f3, d256, c)));
+}
 
 // Rings: 4 stages = weight-tile slots in TMEM (32 columns each, right after the BM accumulator columns) paired with
-// activation tiles in shared memory, and kRawSlots packed super-blocks in shared memory (both TMA).
+// activation tiles in shared memory, and RawGeom::kSlots packed super-blocks in shared memory (both TMA).
 constexpr int kWSlots = 4;          // = stages per 256-weight super-block: the MMA loop relies on it
 constexpr int kWSlotCols = kBK / 2;     // 64 16-bit values per lane = 32 columns
-constexpr int kRawSlots = 3;
 constexpr int kSmemBudget = 227 * 1024;
 template <int BM> constexpr int x_tile_bytes() { return BM * kBK * 2; }
-template <int QT> constexpr int raw_slot_bytes() { return kRowsW * RawGeom<QT>::kPitch; }
+template <int QT> constexpr int raw_box_bytes() { return kRowsW * RawGeom<QT>::kPitch; }
+template <int QT> constexpr int raw_slot_bytes() { return RawGeom<QT>::kBoxes * raw_box_bytes<QT>(); }
 template <int BM> constexpr int tmem_cols() { return BM + kWSlots * kWSlotCols > 256 ? 512 : 256; }
 template <int QT, int BM> constexpr size_t smem_bytes() {
-  return 1024 + size_t(kWSlots) * x_tile_bytes<BM>() + size_t(kRawSlots) * raw_slot_bytes<QT>() + 512;
+  return 1024 + size_t(kWSlots) * x_tile_bytes<BM>() + size_t(RawGeom<QT>::kSlots) * raw_slot_bytes<QT>() + 512;
 }
 
 struct Params {
@@ -278,12 +307,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const Params p) {
   using P = Pair<T>;
   using V = typename P::V;
-  constexpr int NS = kWSlots, NSR = kRawSlots;    // stage ring (weight tile in TMEM + activation tile in smem), packed ring
+  constexpr int NS = kWSlots, NSR = RawGeom<QT>::kSlots;    // stage ring (weight tile in TMEM + activation tile in smem), packed ring
   constexpr int kXTile = x_tile_bytes<BM>();
   constexpr uint32_t kTmemCols = tmem_cols<BM>();
   constexpr int kPitch = RawGeom<QT>::kPitch;
   constexpr int kRawBytes = raw_slot_bytes<QT>();
-  constexpr int kBlockBytes = QTraits<QT>::kBytes;
+  constexpr int kBlockBytes = RawGeom<QT>::kSuper;
   constexpr uint32_t kIdesc = (1u << 4) | (P::kFormat << 7) | (P::kFormat << 10) | (uint32_t(BM >> 3) << 17) |
                               (uint32_t(kRowsW >> 4) << 24);
   constexpr uint32_t kWarpArrivals = kGroupThreads / 32;     // one elected arrive per producer warp of a group
@@ -474,10 +503,24 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         }
         const uint8_t* rowbase = raw + rslot * kRawBytes + row * kPitch;
         // ---- copy this thread's packed words to registers
-        uint32_t qw[12];
-        float dscale, dmin = 0.f;
-        float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3
-        if (QT == QTYPE_Q4_K) {
+        uint32_t qw[QT == QTYPE_Q8_0 ? 16 : 12];
+        float dscale = 0.f, dmin = 0.f;
+        float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3; Q8_0: d of this thread's four blocks
+        if constexpr (QT == QTYPE_Q8_0) {
+          // blocks 4*grp .. 4*grp+3 sit in box grp of the slot; block 2*ls + h feeds half h of stage 2*grp + ls
+          const uint8_t* win = rowbase + grp * raw_box_bytes<QT>();
+          if (grp == 0) {
+            q8_fetch<0>(win, lhalf, qw, sub_scale[0]);
+            q8_fetch<1>(win, lhalf, qw + 4, sub_scale[1]);
+            q8_fetch<2>(win, lhalf, qw + 8, sub_scale[2]);
+            q8_fetch<3>(win, lhalf, qw + 12, sub_scale[3]);
+          } else {
+            q8_fetch<4>(win, lhalf, qw, sub_scale[0]);
+            q8_fetch<5>(win, lhalf, qw + 4, sub_scale[1]);
+            q8_fetch<6>(win, lhalf, qw + 8, sub_scale[2]);
+            q8_fetch<7>(win, lhalf, qw + 12, sub_scale[3]);
+          }
+        } else if constexpr (QT == QTYPE_Q4_K) {
           const uint4 hdr = *reinterpret_cast<const uint4*>(rowbase);
           dscale = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
           dmin = half_bits_to_float(uint16_t(hdr.x >> 16));
@@ -528,7 +571,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             tcgen05_fence_after();
           }
           const uint32_t tile = tmem_lane + uint32_t(slot * kWSlotCols);   // column k'/2 of this slot
-          if (QT == QTYPE_Q4_K) {
+          if constexpr (QT == QTYPE_Q8_0) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const float d256 = sub_scale[2 * ls + h] * (1.f / 256.f);
+              const float c = -8421376.f * d256;        // -(2^23 + 2^15) * d / 256, exact
+              uint32_t o[8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) q8_to_pairs<T>(qw[8 * ls + 4 * h + i], d256, c, o[2 * i], o[2 * i + 1]);
+              tmem_st8(tile + 16 * h + 8 * lhalf, o);     // k' = 32*h + 16*lhalf .. +15
+            }
+          } else if constexpr (QT == QTYPE_Q4_K) {
             // stage = 64-weight group: low nibbles -> sub-block 2*slot (k' 0..31), high -> 2*slot+1 (k' 32..63)
             const int sh = 16 * ls;
             const float sc0 = float((qw[8] >> sh) & 0xff), sc1 = float((qw[8] >> (sh + 8)) & 0xff);
@@ -624,6 +677,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
           mbar_arrive_expect_tx(rawfull(slot), uint32_t(kRawBytes));
           // x coordinate = block start rounded down to 16 bytes; rows past N and bytes past the row end read as zero
           tma_load_2d(smem_u32(raw + slot * kRawBytes), &w_map, rawfull(slot), (sb * kBlockBytes) & ~15, n0);
+          if constexpr (RawGeom<QT>::kBoxes == 2)     // second half of the super-block: blocks 4..7 start 8 bytes in
+            tma_load_2d(smem_u32(raw + slot * kRawBytes + raw_box_bytes<QT>()), &w_map, rawfull(slot), sb * kBlockBytes + 128, n0);
         }
         __syncwarp();
       }
@@ -776,7 +831,7 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
       return RC_LAUNCH;
   }
   {   // packed weight as bytes [n, row_bytes]: box = the aligned window around one block x 128 rows, no swizzle
-    const cuuint64_t row_bytes = cuuint64_t(k / 256) * QTraits<QT>::kBytes;
+    const cuuint64_t row_bytes = cuuint64_t(k / 256) * RawGeom<QT>::kSuper;
     const cuuint64_t dims[2] = {row_bytes, cuuint64_t(n)};
     const cuuint64_t strides[1] = {row_bytes};
     const cuuint32_t box[2] = {cuuint32_t(RawGeom<QT>::kPitch), cuuint32_t(kRowsW)};
@@ -864,10 +919,15 @@ static int launch_bm(const void* a, const void* b, const void* bias, void* c, in
 
 }  // namespace umma
 
+// Packed bytes per 256 weights of a row, 0 for a qtype this kernel does not unpack.
+static int super_block_bytes(int qtype) {
+  return qtype == QTYPE_Q4_K ? 144 : qtype == QTYPE_Q6_K ? 210 : qtype == QTYPE_Q8_0 ? 272 : 0;
+}
+
 bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k) {
   (void)n;
-  if (!(qtype == QTYPE_Q4_K || qtype == QTYPE_Q6_K) || !(dtype == DINO_BF16 || dtype == DINO_F16) || m < 9 || k % 256 != 0) return false;
-  const int64_t row_bytes = int64_t(k / 256) * (qtype == QTYPE_Q4_K ? 144 : 210);
+  if (super_block_bytes(qtype) == 0 || !(dtype == DINO_BF16 || dtype == DINO_F16) || m < 9 || k % 256 != 0) return false;
+  const int64_t row_bytes = int64_t(k / 256) * super_block_bytes(qtype);
   return row_bytes % 16 == 0;   // the packed-weight tensor map needs 16-byte row pitches
 }
 
@@ -880,15 +940,18 @@ static int gemm_rcr_umma_impl(const void* a, const void* b, const void* bias, vo
                               bool use_static, const PeerOut& peers, cudaStream_t s) {
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
-  if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
+  if (super_block_bytes(qtype) == 0) return RC_QTYPE;
   if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;   // tensor-map bases
   if ((int64_t(k) * 2) & 15) return RC_ALIGN;                       // activation row pitch
-  if ((int64_t(k / 256) * (qtype == QTYPE_Q4_K ? 144 : 210)) & 15) return RC_ALIGN;   // packed-weight row pitch
-  if (dtype == DINO_BF16)
-    return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s)
-                               : umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
-  return qtype == QTYPE_Q4_K ? umma::launch_bm<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s)
-                             : umma::launch_bm<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
+  if ((int64_t(k / 256) * super_block_bytes(qtype)) & 15) return RC_ALIGN;   // packed-weight row pitch
+  if (dtype == DINO_BF16) {
+    if (qtype == QTYPE_Q4_K) return umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
+    if (qtype == QTYPE_Q6_K) return umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
+    return umma::launch_bm<QTYPE_Q8_0, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
+  }
+  if (qtype == QTYPE_Q4_K) return umma::launch_bm<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
+  if (qtype == QTYPE_Q6_K) return umma::launch_bm<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
+  return umma::launch_bm<QTYPE_Q8_0, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
 }
 
 int gemm_rcr_umma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,

@@ -50,7 +50,6 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
     if dtype in ("float16", "bfloat16"):
         if qtype in ("Q4_K", "Q6_K", "Q8_0"):
             variants.append("mma")
-        if qtype in ("Q4_K", "Q6_K"):
             variants.append("umma")
     return variants
 

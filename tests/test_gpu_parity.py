@@ -186,11 +186,11 @@ UMMA_SHAPES = [  # (m, n, k)
 
 
 def _umma_k(qtype, k):
-    """The umma variant needs 16-byte weight rows: any K for Q4_K, K % 2048 == 0 for Q6_K (210-byte blocks)."""
-    return k if qtype == "Q4_K" else -(-k // 2048) * 2048
+    """The umma variant needs 16-byte weight rows: any K for Q4_K and Q8_0, K % 2048 == 0 for Q6_K (210-byte blocks)."""
+    return k if qtype != "Q6_K" else -(-k // 2048) * 2048
 
 
-@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K"])
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0"])
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 def test_gemm_umma(dev, qtype, dtype):
     """tcgen05 / TMEM prefill GEMM against the oracle (fp32 weights, fp32 accumulation)."""
@@ -281,6 +281,23 @@ def test_dual_gemm_gated_epilogue(dev, qtype, activation):
         kernels.dual_gemm_rcr(x, w[:-8], qtype, activation)             # 2N must be a multiple of 16
     with pytest.raises(RuntimeError):
         kernels.dual_gemm_rcr(x.float(), w, qtype, activation)         # fp32 activations have no tensor-core variant
+
+
+def test_dual_gemm_q8_0_runs_on_the_tcgen05_kernel_only(dev):
+    """Q8_0 has the gated epilogue from M = 9 (tcgen05 kernel); below that the call is refused, not computed elsewhere."""
+    k = 1024
+    for (m, n) in [(9, 64), (16, 2048), (40, 136), (300, 264)]:
+        b0 = S.random_blocks("Q8_0", n, k, seed=1700 + n)
+        b1 = S.random_blocks("Q8_0", n, k, seed=1800 + n)
+        x, xf = _activations(m, k, 1900 + m, "bfloat16", dev)
+        ref = oracle.dual_gemm_quant(xf, b0, b1, "Q8_0", n, k, "silu")
+        w = kernels.interleave_rows8(torch.from_numpy(b0).to(dev), torch.from_numpy(b1).to(dev))
+        y = kernels.dual_gemm_rcr(x, w, "Q8_0", "silu")
+        assert y.shape == (m, n) and kernels.device_status() == 0
+        _, _, norm = oracle.max_errors(ref, y.float().cpu().numpy())
+        assert norm <= 2e-2, (m, n, norm)
+    with pytest.raises(RuntimeError):
+        kernels.dual_gemm_rcr(x[:4].contiguous(), w, "Q8_0", "silu")
 
 
 def test_gemm_bias_and_batch_dims(dev):
