@@ -111,7 +111,8 @@ DINOML_B200_API int dinoml_b200_gguf_device_status(void);
  * of B0, rows 16t+8 .. 16t+15 are rows 8t .. 8t+7 of B1 (blocks untouched; a row copy at load time,
  * dinoml_v2_b200.kernels.interleave_rows8).  With that order a gate row and its up row sit in the same thread of the
  * mma GEMV and in lanes l / l^8 of the tcgen05 epilogue, so the gate never goes to memory: one launch for the Llama
- * gate / up pair.  N % 8 == 0; variants mma (M <= 16) and umma (M >= 9) with their usual K / alignment rules; optional
+ * gate / up pair.  N % 8 == 0; variants mma (M <= 16; Q4_K and Q6_K only) and umma (M >= 9) with their usual K /
+ * alignment rules, so Q8_0 is served from M = 9 and refused with code 8 below; optional
  * extra destinations as in dinoml_b200_gguf_gemm_rcr_scatter (n_peers = 0: none). */
 DINOML_B200_API int dinoml_b200_gguf_dual_gemm_rcr(const void* a, const void* b01_interleaved, void* c, void* const* peer_c, int n_peers,
                                                    int qtype, int dtype, int m, int n, int k, int activation, int variant, void* stream);
