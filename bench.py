@@ -457,6 +457,8 @@ PROFILE_CASES = {  # name -> (qtype, n, k, m, variant, weight copies): small, ea
     "gemv_q6k_m1": ("Q6_K", 4096, 14336, 1, "mma", 3),
     "gemm_umma_q6k_m512": ("Q6_K", 4096, 14336, 512, "umma", 3),
     "gemm_umma_q4k_m256": ("Q4_K", 11008, 4096, 256, "umma", 6),
+    "gemm_umma_q8_0_m512": ("Q8_0", 4096, 14336, 512, "umma", 3),
+    "gemv_q8_0_m1": ("Q8_0", 4096, 4096, 1, "mma", 12),
     "dequant_q4k_f16": ("Q4_K", 11008, 4096, 0, "dequant", 3),
 }
 
