@@ -29,6 +29,7 @@ int gemm_rcr_umma_peers(const void* a, const void* b, const void* bias, void* c,
                         const PeerOut* peer_out, cudaStream_t s);
 int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch, const void* slots, void* out, int64_t count, int dtype,
                   cudaStream_t s);
+uint32_t peer_exchange_set_poll_limit(uint32_t polls);
 int gemm_rcr_umma_static(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                          cudaStream_t s);
 size_t gemm_umma_static_scratch_bytes();
@@ -228,6 +229,8 @@ int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, uns
   return set_error(peer_exchange(signal_ptrs, world, rank, epoch, slots, out, count, dtype, static_cast<cudaStream_t>(stream)),
                    "dinoml_b200_peer_exchange");
 }
+
+unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned int polls) { return peer_exchange_set_poll_limit(polls); }
 
 int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k) {
   return select_variant(qtype, dtype, m, n, k);

@@ -278,12 +278,8 @@ static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* 
   const size_t smem = size_t(NSTAGE) * kStageBytes + size_t(k / 32) * MXC * sizeof(float);
   if (smem > 200 * 1024) return RC_RANGE;
   auto kern = peers.count > 0 ? gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true> : gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false>;
-  static size_t opted_in[2] = {0, 0};   // dynamic shared memory beyond 48 KB in total needs the opt-in, once per kernel and size
-  size_t& done = opted_in[peers.count > 0 ? 1 : 0];
-  if (smem > done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
-    done = smem;
-  }
+  static SmemOptIn granted[2];          // per kernel (plain / scatter), per device
+  if (!smem_opt_in(kern, smem, granted[peers.count > 0 ? 1 : 0])) return RC_LAUNCH;
   const int ks = SLICED ? gemv_k_slices(tiles, ((k >> 8) + kStageSb - 1) / kStageSb, NSTAGE) : 1;
   const cudaError_t err = gemv_launch(kern, tiles, ks, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
                                       static_cast<const T*>(bias), static_cast<T*>(c), m, n, k, peers);

@@ -1,5 +1,7 @@
 // Pieces shared by the mma.sync decode GEMV kernels (Q4_K, Q6_K): operand types, cp.async helpers.
 #pragma once
+#include <mutex>
+
 #include "gguf_common.cuh"
 
 namespace b200gguf {
@@ -119,6 +121,26 @@ enum : int { ACT_NONE = 0, ACT_SILU = 1, ACT_FAST_GELU = 2 };
 __device__ __forceinline__ float gate_activation(float g, int act) {
   if (act == ACT_SILU) return g / (1.0f + expf(-g));
   return 0.5f * g * (1.0f + tanhf(0.7978845608f * g * (1.0f + 0.044715f * g * g)));
+}
+
+// Opt-in for more than 48 KB of dynamic shared memory.  cudaFuncSetAttribute applies to the current device only, so the
+// largest size already granted is remembered per device (one SmemOptIn per kernel instantiation), under a lock.
+constexpr int kGemvMaxDevices = 64;
+struct SmemOptIn { size_t bytes[kGemvMaxDevices] = {}; };
+inline std::mutex& smem_opt_in_mutex() {
+  static std::mutex m;
+  return m;
+}
+template <typename Kernel>
+inline bool smem_opt_in(Kernel kern, size_t smem, SmemOptIn& granted) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(smem_opt_in_mutex());
+  const bool tracked = dev >= 0 && dev < kGemvMaxDevices;
+  if (tracked && smem <= granted.bytes[dev]) return true;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return false;
+  if (tracked) granted.bytes[dev] = smem;
+  return true;
 }
 
 // Launch with programmatic stream serialization and, for ks > 1, clusters of ks CTAs along grid.y.

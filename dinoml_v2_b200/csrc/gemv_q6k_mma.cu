@@ -309,12 +309,8 @@ static int launch_q6k_cfg(const void* a, const void* b, const void* bias, void* 
   const bool ragged = k % 2048 != 0;          // rows that are not 16-byte multiples, or a last stage of fewer than 4 super-blocks
   auto kern = ragged ? (peers.count > 0 ? gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true, true> : gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false, true>)
                      : (peers.count > 0 ? gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true, false> : gemv_q6k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false, false>);
-  static bool opted_in[4] = {false, false, false, false};   // dynamic shared memory beyond 48 KB needs the opt-in, once per kernel
-  bool& done = opted_in[(peers.count > 0 ? 1 : 0) + (ragged ? 2 : 0)];
-  if (!done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
-    done = true;
-  }
+  static SmemOptIn granted[4];          // per kernel (plain / scatter, aligned / ragged), per device
+  if (!smem_opt_in(kern, smem, granted[(peers.count > 0 ? 1 : 0) + (ragged ? 2 : 0)])) return RC_LAUNCH;
   const int ks = SLICED ? gemv_k_slices(tiles, ((k >> 8) + kQ6StageSb - 1) / kQ6StageSb, NSTAGE) : 1;
   const cudaError_t err = gemv_launch(kern, tiles, ks, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
                                       static_cast<const T*>(bias), static_cast<T*>(c), m, n, k, peers);

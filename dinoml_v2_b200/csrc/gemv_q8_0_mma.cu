@@ -229,11 +229,8 @@ static int launch_q8_cfg(const void* a, const void* b, const void* bias, void* c
   const size_t smem = size_t(NSTAGE) * kQ8StageBytes + size_t(k / 32) * MXC * sizeof(float);
   if (smem > 200 * 1024) return RC_RANGE;
   auto kern = gemv_q8_0_mma_kernel<T, MXC, NW, NSTAGE>;
-  static size_t opted_in = 0;        // dynamic shared memory beyond 48 KB needs the opt-in, once per size
-  if (smem > opted_in) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
-    opted_in = smem;
-  }
+  static SmemOptIn granted;             // per kernel instantiation, per device
+  if (!smem_opt_in(kern, smem, granted)) return RC_LAUNCH;
   const cudaError_t err = gemv_launch(kern, tiles, 1, NW * 32, smem, s, static_cast<const T*>(a), static_cast<const uint8_t*>(b),
                                       static_cast<const T*>(bias), static_cast<T*>(c), m, n, k);
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;

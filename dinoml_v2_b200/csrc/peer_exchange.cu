@@ -1,5 +1,6 @@
 // Peer-memory exchange for the sharded (tensor-parallel) decode path: one process per GPU, buffers of every rank mapped
-// into every process (CUDA IPC), no library collective.
+// into every process (symmetric-memory allocations: virtual-memory handles the ranks exchange and map for their own
+// GPU), no library collective.
 //
 // The GEMV kernels store their result into slot [rank] of a gather buffer on EVERY GPU (PeerOut in
 // gemv_mma_common.cuh).  What is left of an all-gather is then a barrier, and what is left of an all-reduce is a
@@ -8,15 +9,24 @@
 //     ("everything this GPU wrote before this kernel is complete");
 //   * every block, thread p != rank:  poll word [p] of the local signal array until it reaches `epoch`;
 //   * count > 0:  out[i] = sum over r of slots[r][i] (fp32 accumulation, r ascending - identical on every rank).
-// The poll is bounded: after kSpinLimit tries the kernel records a code in the status word and carries on, so a rank
-// that never arrives cannot hang this GPU.  Epochs increase by one per call on every rank (host-side counter).
+// The poll is bounded: after `poll_limit` tries (default 2^22, 200 ns apart; peer_exchange_set_poll_limit changes it)
+// the kernel records a code in the status word and carries on, so a rank that never arrives cannot hang this GPU.
+// Epochs increase by one per call on every rank (host-side counter).
+//
+// Reuse rule.  A rank leaves this kernel as soon as it has seen every peer's signal for `epoch` and summed its own
+// copy of the slots; it does NOT know that the peers have finished reading theirs.  A caller that reused one slot set
+// for the very next exchange could therefore overwrite a slow peer's slots while that peer still sums them.  The host
+// side (peer.PeerExchange) keeps TWO slot sets and alternates by epoch parity: data for epoch e+1 goes to set (e+1)&1,
+// whose last readers ran in exchange e-1, and every rank signalled epoch e only after its exchange e-1 had completed
+// (stream order) - so a writer is always a full barrier behind any reader of the set it writes.
 //
 // The reference has no distributed code; the N-split / K-split scheme this serves is in dinoml_v2_b200/sharding.py.
 #include "gguf_common.cuh"
 
 namespace b200gguf {
 
-constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls, 200 ns apart: about one second
+constexpr uint32_t kPeerSpinLimitDefault = 1u << 22;   // polls, 200 ns apart: about one second
+static uint32_t g_peer_poll_limit = kPeerSpinLimitDefault;
 enum : int { PEER_ST_TIMEOUT = 6 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -44,7 +54,7 @@ template <> __device__ __forceinline__ float from_f32<float>(float v) { return v
 template <typename T>
 __global__ void __launch_bounds__(256)
 peer_exchange_kernel(const PeerSignals sig, int world, int rank, uint32_t epoch, const T* __restrict__ slots, T* __restrict__ out,
-                     int64_t count, int* status) {
+                     int64_t count, int* status, uint32_t poll_limit) {
   const int tid = threadIdx.x;
   if (tid < world && tid != rank) {
     if (blockIdx.x == 0) {
@@ -52,7 +62,7 @@ peer_exchange_kernel(const PeerSignals sig, int world, int rank, uint32_t epoch,
       st_release_sys(sig.ptr[tid] + rank, epoch);
     }
     bool seen = false;
-    for (uint32_t i = 0; i < kPeerSpinLimit && !seen; ++i) {
+    for (uint32_t i = 0; i < poll_limit && !seen; ++i) {
       seen = int32_t(ld_acquire_sys(sig.ptr[rank] + tid) - epoch) >= 0;     // wrap-safe "reached"
       if (!seen) __nanosleep(200);
     }
@@ -89,25 +99,34 @@ int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch,
   for (int i = 0; i < 8; ++i) sig.ptr[i] = i < world ? static_cast<uint32_t*>(signal_ptrs[i]) : nullptr;
   for (int i = 0; i < world; ++i)
     if (sig.ptr[i] == nullptr) return RC_NULL;
+  const uint32_t limit = g_peer_poll_limit;
   int64_t blocks = (count + 255) / 256;
   if (blocks < 1) blocks = 1;
   if (blocks > 64) blocks = 64;
   switch (dtype) {
     case DINO_BF16:
       peer_exchange_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const __nv_bfloat16*>(slots),
-                                                                             static_cast<__nv_bfloat16*>(out), count, status);
+                                                                             static_cast<__nv_bfloat16*>(out), count, status, limit);
       break;
     case DINO_F16:
       peer_exchange_kernel<__half><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const __half*>(slots),
-                                                                    static_cast<__half*>(out), count, status);
+                                                                    static_cast<__half*>(out), count, status, limit);
       break;
     case DINO_F32:
       peer_exchange_kernel<float><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const float*>(slots),
-                                                                   static_cast<float*>(out), count, status);
+                                                                   static_cast<float*>(out), count, status, limit);
       break;
     default: return RC_DTYPE;
   }
   return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
+}
+
+// Polls a later exchange makes per peer before it gives up (0 restores the default of 2^22, about a second).  For tests of
+// the give-up path and for hosts that want a shorter or longer patience; returns the previous value.
+uint32_t peer_exchange_set_poll_limit(uint32_t polls) {
+  const uint32_t before = g_peer_poll_limit;
+  g_peer_poll_limit = polls == 0 ? kPeerSpinLimitDefault : polls;
+  return before;
 }
 
 // Lets kernels of the current device load / store memory of `peer_device` (needed before a pointer mapped from another

@@ -843,11 +843,9 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
   auto kern = scatter ? gemm_umma_kernel<QT, T, BM, true> : gemm_umma_kernel<QT, T, BM, false>;
   constexpr size_t smem = smem_bytes<QT, BM>();
   static_assert(smem <= size_t(kSmemBudget), "shared-memory rings exceed the per-CTA limit");
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[scatter]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
-    attr_set[scatter] = true;
-  }
+  // The opt-in beyond 48 KB of dynamic shared memory belongs to the current device: set on every launch (a cheap host
+  // call), so that a process driving several GPUs is right on each of them.
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return RC_LAUNCH;
   Params p;
   p.bias = bias;
   p.out = c;
@@ -941,6 +939,9 @@ static int gemm_rcr_umma_impl(const void* a, const void* b, const void* bias, vo
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (super_block_bytes(qtype) == 0) return RC_QTYPE;
+  // The kernel walks whole 256-weight super-blocks and derives the weight row pitch from k / 256: a Q8_0 weight whose K
+  // is only a multiple of 32 would be misaddressed from the second row on.
+  if (k % 256 != 0) return RC_ALIGN;
   if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;   // tensor-map bases
   if ((int64_t(k) * 2) & 15) return RC_ALIGN;                       // activation row pitch
   if ((int64_t(k / 256) * super_block_bytes(qtype)) & 15) return RC_ALIGN;   // packed-weight row pitch
@@ -988,9 +989,13 @@ int umma_device_status() {
       if (value == 0) value = word;
     }
   }
-  if (value == 0 && dev >= 0 && dev < umma::kMaxDevices && umma::g_static[dev].ready) {   // the static-scratch path's word
-    if (cudaMemcpy(&value, umma::g_static[dev].status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (value != 0) cudaMemset(umma::g_static[dev].status, 0, sizeof(int) * (1 + umma::kMaxCtas));
+  if (dev >= 0 && dev < umma::kMaxDevices && umma::g_static[dev].ready) {   // the static-scratch path's word: always read and cleared
+    int word = 0;
+    if (cudaMemcpy(&word, umma::g_static[dev].status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (word != 0) {
+      cudaMemset(umma::g_static[dev].status, 0, sizeof(int) * (1 + umma::kMaxCtas));
+      if (value == 0) value = word;
+    }
   }
   return value;
 }

@@ -4,7 +4,15 @@ ranks exchange and map with access for the local GPU), so that a GEMV kernel can
 other GPUs' memory (`dinoml_b200_gguf_gemv_rcr_scatter`) and a small kernel finishes the collective
 (`dinoml_b200_peer_exchange`).  The reference is single-GPU; nothing here has a counterpart there.
 
-Only plain peer stores / loads are used: no TMA, no multicast, no multimem.  Every device-side wait is bounded."""
+Only plain peer stores / loads are used on peer memory: no TMA from a peer, no multicast, no multimem.  Every device-side
+wait is bounded.
+
+Slot reuse.  The exchange kernel lets a rank go as soon as it has seen every peer's signal and summed its OWN copy of
+the slots; nothing tells it that the peers have finished reading theirs.  So each PeerExchange owns TWO slot sets and
+alternates them by epoch parity: the results for exchange e+1 are stored into set (e+1) & 1 while a slow peer may still
+be summing set e & 1.  The set written for e+1 was last read in exchange e-1, and a rank only signals epoch e after its
+own exchange e-1 has completed, so a full barrier always separates a set's readers from its next writer - one
+PeerExchange may be used back to back (down_proj_peer in a loop, swiglu_mlp_peer) without a race."""
 from __future__ import annotations
 
 import ctypes
@@ -16,7 +24,7 @@ _SIGNAL_BYTES = 256      # 8 signal words, padded so that the slots start on a 2
 
 
 class PeerExchange:
-    """`world` slots of `slot_elems` elements on every rank + 8 signal words, all ranks' copies mapped locally.
+    """Two sets of `world` slots of `slot_elems` elements on every rank + 8 signal words, all ranks' copies mapped locally.
 
     slot r of every rank's buffer receives rank r's GEMV result; `finish_gather` / `finish_reduce` complete the
     collective on the current stream.  All ranks must make the same sequence of calls."""
@@ -35,8 +43,9 @@ class PeerExchange:
         # plain peer stores only: keep the allocation off NVLink multicast objects
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
-        nbytes = _SIGNAL_BYTES + self.world * self.slot_elems * esize
-        self._buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)      # [signals | slot 0 | slot 1 | ...]
+        self._set_bytes = -(-(self.world * self.slot_elems * esize) // 256) * 256   # one slot set, 256-byte aligned
+        nbytes = _SIGNAL_BYTES + 2 * self._set_bytes
+        self._buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)      # [signals | set 0: slot 0 .. | set 1: slot 0 ..]
         self._buffer.zero_()
         torch.cuda.synchronize()
         self._handle = symm_mem.rendezvous(self._buffer, dist.group.WORLD if group is None else group)
@@ -44,22 +53,30 @@ class PeerExchange:
         if len(base) != self.world or base[self.rank] != self._buffer.data_ptr():
             raise RuntimeError("symmetric memory rendezvous returned an unexpected mapping")
         self.signals = self._buffer[:32].view(torch.int32)
-        self.slots = self._buffer[_SIGNAL_BYTES:].view(dtype)
+        used = self.world * self.slot_elems * esize
+        self._sets = [self._buffer[_SIGNAL_BYTES + p * self._set_bytes:_SIGNAL_BYTES + p * self._set_bytes + used].view(dtype)
+                      for p in (0, 1)]
         self._signal_ptrs = (ctypes.c_void_p * self.world)(*base)
         others = [r for r in range(self.world) if r != self.rank]
-        # where THIS rank's result lives in every other rank's buffer
-        self._peer_dst = (ctypes.c_void_p * max(1, len(others)))(
-            *[base[r] + _SIGNAL_BYTES + self.rank * self.slot_elems * esize for r in others])
+        # where THIS rank's result lives in every other rank's buffer, per slot set
+        self._peer_dst = [(ctypes.c_void_p * max(1, len(others)))(
+            *[base[r] + _SIGNAL_BYTES + p * self._set_bytes + self.rank * self.slot_elems * esize for r in others]) for p in (0, 1)]
         self._n_peers = len(others)
         self.epoch = 0
         dist.barrier(group=group)          # every rank has mapped every buffer before anyone writes
 
+    @property
+    def slots(self):
+        """The slot set of the exchange that completed last (after `finish_*`), [world * slot_elems]."""
+        return self._sets[self.epoch & 1]
+
     def local_slot(self):
-        """[slot_elems] view of this rank's slot in its own buffer: the primary output of the scatter GEMV."""
-        return self.slots[self.rank * self.slot_elems:(self.rank + 1) * self.slot_elems]
+        """[slot_elems] view of this rank's slot in the set the NEXT exchange reads: the primary output of the scatter GEMV."""
+        nxt = self._sets[(self.epoch + 1) & 1]
+        return nxt[self.rank * self.slot_elems:(self.rank + 1) * self.slot_elems]
 
     def gathered(self):
-        """[world, slot_elems] view of the local buffer (valid after `finish_gather`)."""
+        """[world, slot_elems] view of the local buffer (valid after `finish_gather`, until the exchange after the next)."""
         return self.slots.view(self.world, self.slot_elems)
 
     def scatter_gemv(self, a, b_quant, qtype, bias=None, variant: str = "auto"):
@@ -75,7 +92,7 @@ class PeerExchange:
         lib = _native.lib()
         rc = lib.dinoml_b200_gguf_gemm_rcr_scatter(
             a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, self.local_slot().data_ptr(),
-            self._peer_dst, self._n_peers, q.value, _native.DINO_DTYPE[str(a.dtype).replace("torch.", "")], m, n, k,
+            self._peer_dst[(self.epoch + 1) & 1], self._n_peers, q.value, _native.DINO_DTYPE[str(a.dtype).replace("torch.", "")], m, n, k,
             _native.VARIANTS[variant], torch.cuda.current_stream().cuda_stream)
         _native.check(rc, "dinoml_b200_gguf_gemm_rcr_scatter")
 

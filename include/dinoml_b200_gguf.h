@@ -79,7 +79,7 @@ DINOML_B200_API int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m
  * No counterpart in the reference.  For callers that are not allowed to allocate device memory - a plugin running
  * inside a host that has already handed every byte of HBM to its own arena (so cudaMalloc would fail), or a serving
  * loop that bans cudaMalloc / cudaFree on its hot path because they can stall the whole device.  It is the tensor-core
- * GEMM of dinoml_b200_gguf_gemm_rcr(variant = UMMA) - same shapes (m >= 17, Q4_K / Q6_K, float16 / bfloat16), same
+ * GEMM of dinoml_b200_gguf_gemm_rcr(variant = UMMA) - same shapes (m >= 17, Q4_K / Q6_K / Q8_0, K % 256 == 0, float16 / bfloat16), same
  * arguments minus `variant`, same results - except that its partial tiles (fp32 sums of K ranges that the kernel's
  * stream-K work split cut between SMs) and its flag / status words live in a 16 MiB array plus a 4 KiB one that is part of the library image on every GPU that loads it (dinoml_b200_gguf_prealloc_scratch_bytes()),
  * and that it calls no cudaMalloc, cudaFree or allocating library routine.  The caller still provides a, b_quant,
@@ -120,8 +120,8 @@ DINOML_B200_API int dinoml_b200_gguf_dual_gemm_rcr(const void* a, const void* b0
 /* ---- sharded decode over peer memory (no counterpart in the reference, which is single-GPU) ----------------------
  * dinoml_b200_gguf_gemv_rcr_scatter: the mma GEMV (M <= 16, Q4_K / Q6_K, float16 / bfloat16; same checks and codes as
  * dinoml_b200_gguf_gemm_rcr with variant = MMA) whose epilogue stores the [M, N] result to `c` AND to `n_peers` (<= 8)
- * further buffers - the same slot of a gather buffer on the other GPUs, mapped into this process (CUDA IPC / peer
- * access).  One kernel computes and distributes; there is no separate all-gather.
+ * further buffers - the same slot of a gather buffer on the other GPUs, mapped into this process (symmetric-memory
+ * allocations whose handles the ranks exchange; plain peer stores).  One kernel computes and distributes; there is no separate all-gather.
  * dinoml_b200_gguf_gemm_rcr_scatter: the same for any M - `variant` as in dinoml_b200_gguf_gemm_rcr (AUTO picks mma or
  * umma by shape; shapes only the simt variant serves are refused with code 8).
  * dinoml_b200_peer_exchange: what remains of the collective.  signal_ptrs[r] = the 8-word signal array of rank r
@@ -129,7 +129,12 @@ DINOML_B200_API int dinoml_b200_gguf_dual_gemm_rcr(const void* a, const void* b0
  * kernel publishes "rank's earlier stores are complete" to every peer, waits (bounded, about a second; a rank that
  * never arrives sets device status 6 instead of hanging the GPU) for every peer's signal, and, if count > 0, writes
  * out[i] = sum over r < world of slots[r * count + i] (fp32 accumulation, fixed order): barrier only = all-gather
- * completion, barrier + sum = one-shot all-reduce of GEMV partial results.
+ * completion, barrier + sum = one-shot all-reduce of GEMV partial results.  A rank leaves the kernel without knowing
+ * that its peers finished reading their slots, so do not refill one slot set for the very next exchange: keep two sets and
+ * alternate them by epoch parity (dinoml_v2_b200.peer.PeerExchange does), which puts a full barrier between any reader of
+ * a set and its next writer.
+ * dinoml_b200_peer_exchange_set_poll_limit: polls (200 ns apart) a later exchange makes per peer before it gives up with
+ * status 6; 0 restores the default 2^22 (about a second); returns the previous value.
  * dinoml_b200_peer_enable_access: cudaDeviceEnablePeerAccess for the current device towards `peer_device` (success if
  * it was enabled already; code 8 if the GPUs are not peers).  Call it once per peer before passing that GPU's memory
  * to the two entry points above. */
@@ -140,6 +145,7 @@ DINOML_B200_API int dinoml_b200_gguf_gemm_rcr_scatter(const void* a, const void*
 DINOML_B200_API int dinoml_b200_peer_enable_access(int peer_device);
 DINOML_B200_API int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, unsigned int epoch, const void* slots,
                                               void* out, int64_t count, int dtype, void* stream);
+DINOML_B200_API unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned int polls);
 
 /* Per-candidate symbols, named like the reference's kernel symbols so a manifest can carry them:
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)

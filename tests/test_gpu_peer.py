@@ -106,3 +106,30 @@ def test_peer_exchange_barrier_and_sum_single_process():
     assert lib.dinoml_b200_peer_exchange(sig, 9, rank, epoch, None, None, 0, BF16, stream) == 8
     torch.cuda.synchronize()
     assert kernels.device_status() == 0
+
+
+def test_peer_exchange_bounded_wait_runs_out():
+    """A peer that never signals: the kernel's poll limit runs out, the call returns, and the device status reads 6 once.
+    One process on one GPU, the "peer" is a signal word that nothing writes; the limit is lowered to a few thousand polls
+    so the wait lasts about a millisecond."""
+    dev = torch.device("cuda:0")
+    lib = _native.lib()
+    lib.dinoml_b200_peer_exchange_set_poll_limit.argtypes = [ctypes.c_uint]
+    lib.dinoml_b200_peer_exchange_set_poll_limit.restype = ctypes.c_uint
+    before = lib.dinoml_b200_peer_exchange_set_poll_limit(4000)
+    try:
+        world, rank, epoch, count = 2, 0, 3, 256
+        local = torch.zeros(8, dtype=torch.int32, device=dev)          # word [1] stays below the epoch: rank 1 never arrives
+        local[1] = epoch - 1
+        fake = torch.zeros(8, dtype=torch.int32, device=dev)
+        sig = (ctypes.c_void_p * 2)(local.data_ptr(), fake.data_ptr())
+        slots = torch.ones(world, count, device=dev, dtype=torch.bfloat16)
+        out = torch.zeros(count, device=dev, dtype=torch.bfloat16)
+        stream = torch.cuda.current_stream().cuda_stream
+        assert lib.dinoml_b200_peer_exchange(sig, world, rank, epoch, slots.data_ptr(), out.data_ptr(), count, BF16, stream) == 0
+        torch.cuda.synchronize()                                        # the kernel came back by itself
+        assert kernels.device_status() == 6
+        assert kernels.device_status() == 0                             # reading clears the word
+        assert fake.cpu().tolist()[0] == epoch                          # its own signal still went out
+    finally:
+        assert lib.dinoml_b200_peer_exchange_set_poll_limit(before) == 4000
