@@ -35,6 +35,11 @@ sys.path.insert(0, str(ROOT))
 CFG2 = {"qtype": "Q4_K", "n": 11008, "k": 4096}
 CFG3 = {"qtype": "Q6_K", "n": 4096, "k": 14336}
 NOMINAL_HBM_GBS = 8000.0
+# One metric string for every line of both arms (the path's headline metric); what a line measures is in `config`.
+METRIC = "GGUF qmatmul weight GB/s at M=1 and TFLOP/s at M=512, % of roofline"
+WORKLOAD_N1 = "cfg2 Q4_K [11008x4096] decode GEMV, M=1, bf16 activations/outputs"
+WORKLOAD_MULTI = ("cfg5 Llama-3-70B FFN, M=1, bf16: Q4_K gate,up [28672x8192] split along N + all-gather; "
+                  "down [8192x28672] split along K + all-reduce")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -47,14 +52,44 @@ def measured_peaks():
 
 # ----------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML every millisecond when the
+    binding is importable (a timed region of a few milliseconds still gets samples), else through nvidia-smi."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.rows, self._stop, self._thread = index, [], threading.Event(), None
+        self._nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nvml = (pynvml, pynvml.nvmlDeviceGetHandleByIndex(int(os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[index])
+                                                                     if os.environ.get("CUDA_VISIBLE_DEVICES", "").replace(",", "").isdigit()
+                                                                     else index))
+        except Exception:
+            self._nvml = None
+
+    def _nvml_loop(self):
+        nv, h = self._nvml
+        try:
+            top = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        except Exception:
+            top = float("nan")
+        bits = [("hw_slowdown", getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8)), ("hw_thermal_slowdown", getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40)),
+                ("sw_thermal_slowdown", getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20)), ("sw_power_cap", getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4))]
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop.is_set():
+            try:
+                sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = int(reasons_fn(h))
+                self.rows.append([str(sm), str(top)] + ["Active" if mask & bit else "Not Active" for _, bit in bits])
+            except Exception:
+                pass
+            self._stop.wait(0.001)
 
     def _loop(self):
+        if self._nvml is not None:
+            return self._nvml_loop()
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
@@ -114,6 +149,17 @@ def time_steps(step, steps, warmup, stream, barrier=None):
         e1.synchronize()
         torch.cuda.synchronize()
     return e0.elapsed_time(e1)
+
+
+def profile_traffic(profile_name):
+    """DRAM bytes per launch recorded in a committed ncu summary (a line `dram_bytes_per_launch: N` in profiles/<name>), or
+    None.  The benchmark reports what the summary on file says; it never carries a typed-in copy of it."""
+    import re
+    path = ROOT / "profiles" / profile_name
+    if not path.exists():
+        return None, None
+    m = re.search(r"^dram_bytes_per_launch:\s*([0-9_,]+)", path.read_text(), flags=re.M)
+    return (int(m.group(1).replace(",", "").replace("_", "")) if m else None), f"profiles/{profile_name}"
 
 
 def rotation_copies(nbytes, l2_bytes, cap=24):
@@ -198,6 +244,46 @@ def bench_dequant(qtype, n, k, dtype, steps, warmup):
     us = ms * 1e3 / (steps * r)
     total = encoded_nbytes(qtype, n, k) + n * k * outs[0].element_size()
     return {"us_per_launch": us, "gbs": total / us / 1e3, "bytes": total}
+
+
+FFN70B = {"hidden": 8192, "ffn": 28672, "qtype": "Q4_K"}
+
+
+def bench_ffn_1gpu(ms, steps, warmup, l2, device=None):
+    """Config 5's FFN on ONE GPU, unsharded: gate and up [28672 x 8192], down [8192 x 28672], three launches per FFN
+    (the baseline the sharded runs are compared with).  Returns {m: {...}}."""
+    import torch
+
+    from dinoml_v2_b200 import kernels, synthetic
+    from dinoml_v2_b200.gguf_blocks import encoded_nbytes
+    dev = device or torch.device("cuda")
+    hidden, ffn, qtype = FFN70B["hidden"], FFN70B["ffn"], FFN70B["qtype"]
+    total = 3 * encoded_nbytes(qtype, ffn, hidden)
+    r = rotation_copies(total, l2, cap=3)
+    sets = [(synthetic.random_blocks_torch(qtype, ffn, hidden, 8000 + 3 * i, dev), synthetic.random_blocks_torch(qtype, ffn, hidden, 8001 + 3 * i, dev),
+             synthetic.random_blocks_torch(qtype, hidden, ffn, 8002 + 3 * i, dev)) for i in range(r)]
+    out = {}
+    stream = torch.cuda.Stream(device=dev)
+    for m in ms:
+        x = torch.randn(m, hidden, device=dev).to(torch.bfloat16)
+        h = torch.randn(m, ffn, device=dev).to(torch.bfloat16)
+        og, ou = (torch.empty(m, ffn, device=dev, dtype=torch.bfloat16) for _ in range(2))
+        od = torch.empty(m, hidden, device=dev, dtype=torch.bfloat16)
+
+        def one_pass():
+            for (gate, up, down) in sets:
+                kernels.gemm_rcr(x, gate, qtype, out=og)
+                kernels.gemm_rcr(x, up, qtype, out=ou)
+                kernels.gemm_rcr(h, down, qtype, out=od)
+
+        g = graph_of(one_pass, stream)
+        ms_ffn = time_steps(g.replay, steps, warmup, stream) / (steps * r)
+        out[m] = {"ms_per_ffn": ms_ffn, "weight_gbs": total / ms_ffn / 1e6, "tflops": 6.0 * m * hidden * ffn / ms_ffn / 1e9,
+                  "launches_per_ffn": 3, "weight_sets": r}
+    assert kernels.device_status() == 0
+    del sets
+    torch.cuda.empty_cache()
+    return out
 
 
 LLAMA8B_LAYER = [("q", "Q4_K", 4096, 4096), ("k", "Q4_K", 1024, 4096), ("v", "Q6_K", 1024, 4096), ("o", "Q4_K", 4096, 4096),
@@ -294,58 +380,79 @@ def _ref_library():
     return (ctypes.CDLL(str(path)), tag) if path.exists() else None
 
 
-def cpu_reference_timing(budget_s, min_iters=3):
-    """Times the reference CPU path on the headline configuration (M = 1, bf16, dense weights = host-dequantized GGUF
-    blocks rounded to bf16, as GGUFConstant.materialize produces on the CPU target).  Bounded: runs until `budget_s`."""
+def _cpu_gemm_call(lib):
+    """call(x, w, y, m, n, k) running the reference CPU kernel (bf16), or the oracle's restatement when it is not built."""
     import oracle
-    from dinoml_v2_b200 import synthetic
-    n, k, qtype = CFG2["n"], CFG2["k"], CFG2["qtype"]
-    blocks = synthetic.random_blocks(qtype, n, k, 1000)
-    wb = oracle.dequantize(blocks, qtype, k, "bfloat16")
-    x = synthetic.random_activations(1, k, 7, "bfloat16")
-    y = np.empty((1, n), dtype=np.uint16)
-    lib = _ref_library()
     if lib is not None:
         fn = lib[0].ref_gemm_rcr_bfloat16
         fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int64] * 3
-        call = lambda: fn(x.ctypes.data, wb.ctypes.data, y.ctypes.data, 1, n, k)
-        kind, detail = "reference", f"gemm_cpu.cpp.j2 kernel built -O3 -ffast-math -fopenmp ({lib[1]})"
+        return (lambda x, w, y, m, n, k: fn(x.ctypes.data, w.ctypes.data, y.ctypes.data, m, n, k)), "reference", \
+            f"gemm_cpu.cpp.j2 kernel built -O3 -ffast-math -fopenmp ({lib[1]})"
+
+    def call(x, w, y, m, n, k):
+        y[...] = oracle.gemm_rcr_dense(x, w, "bfloat16")
+    return call, "port", "C restatement of gemm_cpu.cpp.j2 (strict k order)"
+
+
+def cpu_reference_timing(budget_s, min_iters=3, workload="cfg2"):
+    """Times the reference CPU path (M = 1, bf16, dense weights = host-dequantized GGUF blocks rounded to bf16, as
+    GGUFConstant.materialize produces on the CPU target) on `workload`: "cfg2" = one [11008 x 4096] linear per call,
+    "cfg5" = the three linears of one 70B FFN per call.  Bounded: runs until `budget_s` and at least `min_iters` calls."""
+    import oracle
+    from dinoml_v2_b200 import synthetic
+    if workload == "cfg2":
+        shapes = [(CFG2["qtype"], CFG2["n"], CFG2["k"])]
     else:
-        call = lambda: oracle.gemm_rcr_dense(x, wb, "bfloat16")
-        kind, detail = "port", "C restatement of gemm_cpu.cpp.j2 (strict k order)"
-    call()
+        shapes = [(FFN70B["qtype"], FFN70B["ffn"], FFN70B["hidden"])] * 2 + [(FFN70B["qtype"], FFN70B["hidden"], FFN70B["ffn"])]
+    oracle.set_threads(os.cpu_count() or 1)           # the one-off host dequantization may use every core; the matmul below cannot
+    mats, nbytes = [], 0
+    for i, (qtype, n, k) in enumerate(shapes):
+        blocks = synthetic.random_blocks(qtype, n, k, 1000 + i)
+        nbytes += blocks.nbytes
+        mats.append((oracle.dequantize(blocks, qtype, k, "bfloat16"), synthetic.random_activations(1, k, 7 + i, "bfloat16"),
+                     np.empty((1, n), dtype=np.uint16), n, k))
+        del blocks
+    call, kind, detail = _cpu_gemm_call(_ref_library())
+
+    def one():
+        for (w, x, y, n, k) in mats:
+            call(x, w, y, 1, n, k)
+    one()
     times = []
     t_end = time.perf_counter() + budget_s
     while len(times) < min_iters or time.perf_counter() < t_end:
         t0 = time.perf_counter()
-        call()
+        one()
         times.append(time.perf_counter() - t0)
     med = sorted(times)[len(times) // 2]
+    what = "one Q4_K [11008x4096]" if workload == "cfg2" else "the three Q4_K linears of one 70B FFN (2 x [28672x8192], [8192x28672])"
     # the reference's OpenMP loop runs over the M activation rows (gemm_cpu.cpp.j2:35-38): one row => one core
-    return {"value": blocks.nbytes / med / 1e9, "unit": "GB/s", "cores": 1, "kind": kind, "ms_per_call": med * 1e3,
-            "sample": f"{len(times)} calls of one {qtype} [{n}x{k}] M=1 bf16 gemm_rcr over host-dequantized dense weights "
+    return {"value": nbytes / med / 1e9, "unit": "GB/s", "cores": 1, "kind": kind, "ms_per_call": med * 1e3,
+            "sample": f"{len(times)} calls of {what} M=1 bf16 gemm_rcr over host-dequantized dense weights "
                       f"({detail}); weight bytes counted GGUF-encoded; host has {os.cpu_count()} logical cores, the kernel's "
-                      "OpenMP loop is over M rows so M=1 uses one"}, times
+                      "OpenMP loop is over M rows so M=1 uses one"}, times, nbytes
 
 
 def run_reference_arm(args):
+    """The reference's own CPU implementation of the path on this box's host cores, on the workload the b200 arm runs at
+    the same --gpus: config 2 at one GPU, the config-5 FFN (unsharded: the reference has no distributed code) above."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    base, times = cpu_reference_timing(budget_s=0.0, min_iters=args.warmup + args.steps)
+    multi = args.gpus > 1
+    base, times, nbytes = cpu_reference_timing(budget_s=0.0, min_iters=args.warmup + args.steps, workload="cfg5" if multi else "cfg2")
     timed = times[args.warmup:args.warmup + args.steps]
     total = sum(timed)
-    from dinoml_v2_b200.gguf_blocks import encoded_nbytes
-    nbytes = encoded_nbytes(CFG2["qtype"], CFG2["n"], CFG2["k"])
     value = nbytes * len(timed) / total / 1e9
     base["value"] = value
     print(json.dumps({
-        "impl": "reference", "metric": "GGUF qmatmul weight GB/s at M=1 (Q4_K 11008x4096)", "value": value, "unit": "GB/s",
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / len(timed) * 1e3,
-        "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "strong" if multi else "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": "cfg2 Q4_K [11008x4096] GEMV, M=1, bf16 - reference CPU path (host dequantize once, dense "
-                               "gemm_rcr per step); each step is ONE matmul (bounded sample of the R-copy GPU step)"},
+        "config": {"workload": WORKLOAD_MULTI if multi else WORKLOAD_N1,
+                   "arm": "reference CPU path: host dequantize once, dense gemm_rcr per step; each step is ONE "
+                          + ("FFN (three matmuls, unsharded)" if multi else "matmul") + ", a bounded sample of the GPU arm's step"},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -417,6 +524,7 @@ def run_single(args):
     extras["dequant"] = {f"{q}_{dt}": bench_dequant(q, nn, kk, dt, extra_steps, extra_warm)
                          for (q, nn, kk) in (("Q4_K", 11008, 4096), ("Q6_K", 4096, 14336), ("Q8_0", 4096, 4096)) for dt in ("float16", "float32")}
     extras["dual_gate_up_q4k_14336x4096"] = {f"m{m}": bench_dual(14336, 4096, m, extra_steps, extra_warm, l2) for m in (1, 16)}
+    extras["cfg5_ffn_1gpu"] = {f"m{m}": v for m, v in bench_ffn_1gpu((1, 16, 256), extra_steps, extra_warm, l2).items()}
     try:
         extras["cfg4_llama8b_decode_step"] = bench_decode_step(extra_steps, extra_warm)
     except torch.cuda.OutOfMemoryError as exc:       # pragma: no cover - 4.9 GB of weights, not expected on a B200
@@ -425,26 +533,31 @@ def run_single(args):
 
     with tempfile.TemporaryDirectory() as tmp:
         e2e = bench_e2e(max(3, min(K, 20)), 3, r, Path(tmp) / "artifact")
-    cpu, _ = cpu_reference_timing(budget_s=args.cpu_budget)
+    cpu, _, _ = cpu_reference_timing(budget_s=args.cpu_budget)
 
     m512 = prefill["m512"]
+    variant = kernels.select_variant(qtype, "bfloat16", 1, n, k)
+    gemv_profile = {"stream": "gemv_q4k_stream_m1_q4k_11008x4096.md", "mma": "gemv_q4k_mma_m1_q4k_11008x4096.md"}.get(variant, "")
+    gemv_traffic, gemv_traffic_src = profile_traffic(gemv_profile)
+    gemm_traffic, gemm_traffic_src = profile_traffic("gemm_umma_q6k_4096x14336_m512.md")
     line = {
-        "metric": "GGUF qmatmul weight GB/s at M=1 (Q4_K 11008x4096) [TFLOP/s at M=512 in roofline_prefill]",
+        "metric": METRIC,
         "value": value, "unit": "GB/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "cfg2 Q4_K [11008x4096] decode GEMV, M=1, bf16 activations/outputs", "launches_per_step": r,
+        "config": {"workload": WORKLOAD_N1, "launches_per_step": r,
+                   "value_is": "weight GB/s at M=1 (the TFLOP/s at M=512 half of the metric is in roofline_prefill)",
                    "l2_policy": f"each step walks {r} distinct weight copies ({r * nbytes / 1e6:.0f} MB > 2 x L2 {l2 / 1e6:.0f} MB), so every launch reads cold weights",
-                   "timing": "CUDA graph replay, CUDA events on the launching stream", "variant": kernels.select_variant(qtype, "bfloat16", 1, n, k)},
-        "roofline": {"kernel": "gemv_q4k_mma_kernel (Q4_K M=1)", "bound": "hbm", "achieved": nbytes / us_launch / 1e3, "peak": peaks["hbm_gbs"],
+                   "timing": "CUDA graph replay, CUDA events on the launching stream", "variant": variant},
+        "roofline": {"kernel": f"gemv_q4k_{variant}_kernel (Q4_K M=1)", "bound": "hbm", "achieved": nbytes / us_launch / 1e3, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": nbytes / us_launch / 1e3 / peaks["hbm_gbs"], "peak_kind": f"of {peak_kind} copy bandwidth",
                      "frac_of_nominal_8tbs": nbytes / us_launch / 1e3 / NOMINAL_HBM_GBS, "us_per_launch": us_launch,
-                     "algorithmic_bytes_per_launch": nbytes, "traffic": 25_387_776,
-                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture (profiles/)"},
+                     "algorithmic_bytes_per_launch": nbytes, "traffic": gemv_traffic,
+                     "traffic_source": f"dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture, read from {gemv_traffic_src}"},
         "roofline_prefill": {"kernel": "gemm_umma_kernel (Q6_K 4096x14336, M=512)", "bound": "tensor", "achieved": m512["tflops"],
                              "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": m512["frac_of_measured_burst"],
                              "peak_kind": f"of {peak_kind} cuBLAS bf16 burst", "us_per_launch": m512["us_per_launch"],
-                             "frac_of_sustained": m512["frac_of_measured_sustained"], "traffic": 68_747_520,
-                             "traffic_source": "dram bytes read + written of one ncu capture (profiles/): weights 48.2 MB + activations 14.7 MB + output 4.2 MB + spilled partial tiles"},
+                             "frac_of_sustained": m512["frac_of_measured_sustained"], "traffic": gemm_traffic,
+                             "traffic_source": f"dram bytes read + written of one ncu capture, read from {gemm_traffic_src}: weights 48.2 MB + activations 14.7 MB + output 4.2 MB + spilled partial tiles"},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": K * r, "clocks": clocks.summary(), "extras": extras,
         "device": {"name": props.name, "sms": props.multi_processor_count, "l2_bytes": l2},
     }
@@ -454,6 +567,13 @@ def run_single(args):
 # ----------------------------------------------------------------------------------------------- profiling cases
 PROFILE_CASES = {  # name -> (qtype, n, k, m, variant, weight copies): small, eager, few launches; inputs exceed the L2
     "gemv_q4k_m1": ("Q4_K", 11008, 4096, 1, "mma", 6),
+    "gemv_stream_q4k_m1_c1": ("Q4_K", 11008, 4096, 1, "stream:1", 6),
+    "gemv_stream_q4k_m1_c4": ("Q4_K", 11008, 4096, 1, "stream:4", 6),
+    "gemv_stream_q4k_m1_c5": ("Q4_K", 11008, 4096, 1, "stream:5", 6),
+    "gemv_stream_probe_q4k_c4": ("Q4_K", 11008, 4096, 1, "stream:132", 6),
+    "gemv_q4k_m4": ("Q4_K", 11008, 4096, 4, "mma", 6),
+    "gemm_umma_q4k_m16": ("Q4_K", 11008, 4096, 16, "umma", 6),
+    "gemm_umma_q6k_m64": ("Q6_K", 4096, 14336, 64, "umma", 3),
     "gemv_q6k_m1": ("Q6_K", 4096, 14336, 1, "mma", 3),
     "gemm_umma_q6k_m512": ("Q6_K", 4096, 14336, 512, "umma", 3),
     "gemm_umma_q4k_m256": ("Q4_K", 11008, 4096, 256, "umma", 6),
@@ -495,6 +615,23 @@ def run_profile_case(args):
 
 
 # ----------------------------------------------------------------------------------------------- multi GPU
+def _max_over_ranks(ms, dev):
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _all_ranks_agree(flag: bool, dev) -> bool:
+    """True only if `flag` is true on every rank: the ranks must take the same code path (peer kernels or NCCL)."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([1 if flag else 0], device=dev, dtype=torch.int32)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item())
+
+
 def run_multi(args):
     import torch
     import torch.distributed as dist
@@ -507,13 +644,15 @@ def run_multi(args):
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     l2 = torch.cuda.get_device_properties(local).L2_cache_size
-    hidden, ffn, qtype = 8192, 28672, "Q4_K"
+    hidden, ffn, qtype = FFN70B["hidden"], FFN70B["ffn"], FFN70B["qtype"]
     n_shard, k_shard = ffn // world, ffn // world
     shard_bytes = 2 * encoded_nbytes(qtype, n_shard, hidden) + encoded_nbytes(qtype, hidden, k_shard)
     total_bytes = 3 * encoded_nbytes(qtype, ffn, hidden)
     r = rotation_copies(shard_bytes, l2, cap=8)
     K, W = args.steps, args.warmup
-    results = {}
+    half = max(3, K // 2)
+    use_peer_env = os.environ.get("DINOML_B200_PEER_PATH", "1") != "0"
+    results, clocks, e2e = {}, None, None
     for m in (1, 16, 256):
         ffns = []
         for i in range(r):
@@ -541,77 +680,136 @@ def run_multi(args):
                 f.gate_up_peer(x)
                 f.down_proj_peer(h_slice, od)
 
+        def comm_nccl():                                    # the collectives of step_nccl alone
+            for _ in ffns:
+                dist.all_gather_into_tensor(gg.view(-1, n_shard), og)
+                dist.all_gather_into_tensor(gu.view(-1, n_shard), ou)
+                dist.all_reduce(od)
+
+        def comm_peer():                                    # the exchange kernels of step_peer alone (they sum whatever the slots hold)
+            for f in ffns:
+                f.xchg_gate_up.finish_gather()
+                f.xchg_down.finish_reduce(od)
+
         stream = torch.cuda.current_stream()
         # Decode sizes go over peer memory (the GEMV kernel stores into every GPU's gather buffer, one small kernel
-        # finishes each collective); NCCL is the fallback and is timed beside it.
-        step, mode, nccl_ms, swiglu_ms = step_nccl, "nccl", None, None
-        if m <= 64 and os.environ.get("DINOML_B200_PEER_PATH", "1") != "0":   # decode and small-batch sizes: mma GEMV or tcgen05 kernel, both with a scatter epilogue
+        # finishes each collective); NCCL is the fallback and is timed beside it.  Only a failure to SET UP the peer
+        # buffers falls back; a wrong result or a device-side give-up is an error, and the ranks agree on the mode first.
+        want_peer = m <= 64 and use_peer_env
+        peer_ok = False
+        if want_peer:
             try:
                 for f in ffns:
                     f.enable_peer_path(m, torch.bfloat16, share_with=ffns[0] if f is not ffns[0] else None)
-                step_nccl(); step_peer()
-                torch.cuda.synchronize()
-                assert kernels.device_status() == 0, "a bounded device-side wait gave up on the peer path"
-                ref = od.clone()
-                ffns[-1].down_proj(h_slice, od)
-                torch.cuda.synchronize()
-                # fp32 accumulation in rank order here, NCCL's own order and precision there: equal up to bf16 rounding
-                assert float((ref.float() - od.float()).abs().max()) <= 2e-2 * float(od.float().abs().max()), "peer all-reduce differs from NCCL"
-                nccl_ms = time_steps(step_nccl, max(3, K // 2), W, stream, barrier=dist.barrier)
-                step, mode = step_peer, "peer"
-
-                def step_swiglu():                          # extra: the gated MLP with no all-gather at all
-                    for f in ffns:
-                        f.swiglu_mlp_peer(x, od)
-                swiglu_ms = time_steps(step_swiglu, max(3, K // 2), W, stream, barrier=dist.barrier)
-            except Exception as exc:                        # pragma: no cover - no symmetric memory on this box
+                peer_ok = True
+            except (RuntimeError, ImportError, AttributeError, OSError) as exc:   # no symmetric memory on this box / torch build
                 if rank == 0:
-                    print(f"peer path unavailable ({type(exc).__name__}: {str(exc)[:200]}); using NCCL", file=sys.stderr)
-                step, mode = step_nccl, "nccl"
+                    print(f"peer buffers unavailable ({type(exc).__name__}: {str(exc)[:200]}); using NCCL", file=sys.stderr)
+        mode = "peer" if (want_peer and _all_ranks_agree(peer_ok, dev)) else "nccl"
+        nccl_ms = swiglu_ms = None
+        if mode == "peer":
+            # correctness before timing: the peer all-reduce against NCCL's, several back-to-back calls on one exchange
+            step_nccl()
+            ref = od.clone()
+            for _ in range(3):
+                step_peer()
+            torch.cuda.synchronize()
+            assert kernels.device_status() == 0, "a bounded device-side wait gave up on the peer path"
+            # fp32 accumulation in rank order here, NCCL's own order and precision there: equal up to bf16 rounding
+            assert float((ref.float() - od.float()).abs().max()) <= 2e-2 * float(ref.float().abs().max()), "peer all-reduce differs from NCCL"
+            # the fused gated MLP against the same thing built from the dual GEMM and NCCL, three consecutive calls
+            f0 = ffns[0]
+            hloc = kernels.dual_gemm_rcr(x, kernels.interleave_rows8(f0.gate, f0.up), qtype, "silu")
+            want = torch.empty(m, hidden, device=dev, dtype=torch.bfloat16)
+            f0.down_proj(hloc, want)
+            for _ in range(3):
+                got = torch.empty(m, hidden, device=dev, dtype=torch.bfloat16)
+                f0.swiglu_mlp_peer(x, got)
+                torch.cuda.synchronize()
+                assert float((want.float() - got.float()).abs().max()) <= 2e-2 * float(want.float().abs().max()), "fused gated MLP differs from NCCL"
+            nccl_ms = time_steps(step_nccl, half, W, stream, barrier=dist.barrier)
+
+            def step_swiglu():                              # extra: the gated MLP with no all-gather at all
+                for f in ffns:
+                    f.swiglu_mlp_peer(x, od)
+            swiglu_ms = time_steps(step_swiglu, half, W, stream, barrier=dist.barrier)
+        step, comm = (step_peer, comm_peer) if mode == "peer" else (step_nccl, comm_nccl)
         clock_ctx = ClockSampler(local) if (m == 1 and rank == 0) else None
         if clock_ctx:
             clock_ctx.__enter__()
         ms = time_steps(step, K, W, stream, barrier=dist.barrier)
         if clock_ctx:
             clock_ctx.__exit__(None, None, None)
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)            # max over ranks
-        ms_step = float(t.item()) / K
+            clocks = clock_ctx.summary()
+        ms_step = _max_over_ranks(ms, dev) / K
+        comm_ms = _max_over_ranks(time_steps(comm, half, W, stream, barrier=dist.barrier), dev) / half
         results[m] = {"ms_per_step": ms_step, "ms_per_ffn": ms_step / r, "weight_gbs": r * total_bytes / ms_step / 1e6,
-                      "tflops": r * 6.0 * m * hidden * ffn / ms_step / 1e9, "collectives": mode}
+                      "tflops": r * 6.0 * m * hidden * ffn / ms_step / 1e9, "collectives": mode,
+                      "comm_us_per_ffn": comm_ms * 1e3 / r,
+                      "comm_is": "peer_exchange_kernel x 2 alone" if mode == "peer" else "ncclAllGather x 2 + ncclAllReduce alone",
+                      "bound_by": None}
         if nccl_ms is not None:
-            tn = torch.tensor([nccl_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(tn, op=dist.ReduceOp.MAX)
-            results[m]["nccl_ms_per_ffn"] = float(tn.item()) / max(3, K // 2) / r
+            results[m]["nccl_ms_per_ffn"] = _max_over_ranks(nccl_ms, dev) / half / r
         if swiglu_ms is not None:
-            ts = torch.tensor([swiglu_ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(ts, op=dist.ReduceOp.MAX)
-            results[m]["fused_swiglu_mlp_ms_per_ffn"] = float(ts.item()) / max(3, K // 2) / r
+            results[m]["fused_swiglu_mlp_ms_per_ffn"] = _max_over_ranks(swiglu_ms, dev) / half / r
         if m == 1:
-            clocks = clock_ctx.summary() if clock_ctx else None
+            # end to end: activations start in pinned host memory and the result ends in host memory, every step
+            x_host = x.cpu().pin_memory()
+            h_host = h_slice.cpu().pin_memory()
+            y_host = torch.empty(m, hidden, dtype=torch.bfloat16).pin_memory()
+
+            def step_e2e():
+                x.copy_(x_host, non_blocking=True)
+                h_slice.copy_(h_host, non_blocking=True)
+                step()
+                y_host.copy_(od, non_blocking=True)
+                stream.synchronize()
+            for _ in range(W):
+                step_e2e()
+            dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(K):
+                step_e2e()
+            torch.cuda.synchronize()
+            wall_ms = _max_over_ranks((time.perf_counter() - t0) * 1e3, dev) / K
+            e2e = {"value": r * total_bytes / wall_ms / 1e6, "unit": "GB/s", "h2d_bytes_per_step": (m * hidden + m * k_shard) * 2,
+                   "d2h_bytes_per_step": m * hidden * 2, "ms_per_step": wall_ms,
+                   "api": "ShardedFFN.gate_up[_peer] + down_proj[_peer] per FFN, host activations in, host result out, wall clock, max over ranks"}
         del ffns
         torch.cuda.empty_cache()
     assert kernels.device_status() == 0
+    # the same FFN on one GPU, unsharded, measured by rank 0 in this run: the baseline of the speed-ups below
+    base = bench_ffn_1gpu((1, 16, 256), max(3, min(K, 10)), 3, l2, dev) if rank == 0 else None
+    dist.barrier()
     if rank == 0:
         peaks, peak_kind = measured_peaks()
+        for m, v in results.items():
+            v["one_gpu_ms_per_ffn"] = base[m]["ms_per_ffn"]
+            v["speedup_vs_1gpu"] = base[m]["ms_per_ffn"] / v["ms_per_ffn"]
+            compute_us = v["ms_per_ffn"] * 1e3 - v["comm_us_per_ffn"]
+            v["bound_by"] = ("the collective step (" + v["comm_is"] + ")") if v["comm_us_per_ffn"] > compute_us else \
+                "the quantized matmul kernels (HBM at small M, tensor cores at M=256)"
         r1 = results[1]
         per_gpu = r1["weight_gbs"] / world
+        cpu, _, _ = cpu_reference_timing(budget_s=min(args.cpu_budget, 5.0), workload="cfg5")
         print(json.dumps({
-            "metric": "GGUF qmatmul weight GB/s at M=1 (Llama-70B FFN sharded, Q4_K gate/up/down)", "value": r1["weight_gbs"], "unit": "GB/s",
+            "metric": METRIC, "value": r1["weight_gbs"], "unit": "GB/s",
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": r1["ms_per_step"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "cfg5 Llama-3-70B FFN: Q4_K gate,up [28672x8192] N-split + all-gather; down [8192x28672] K-split + "
-                                   "all-reduce (bf16); M=1; collectives: " + ("GEMV epilogue stores into peer GPUs' buffers + one "
-                                   "barrier / barrier-and-sum kernel each" if r1["collectives"] == "peer" else "NCCL"),
+            "config": {"workload": WORKLOAD_MULTI,
+                       "value_is": "total GGUF-encoded weight bytes of the three matrices / max-over-ranks step time, M=1",
+                       "collectives": ("GEMV epilogue stores into peer GPUs' buffers + one barrier / barrier-and-sum kernel each"
+                                       if r1["collectives"] == "peer" else "NCCL all-gather x 2 + all-reduce"),
                        "parallelism": f"tp{world}", "ffns_per_step": r,
                        "l2_policy": f"each step walks {r} distinct shard sets ({r * shard_bytes / 1e6:.0f} MB per GPU > 2 x L2)",
                        "timing": "eager launches on one stream, CUDA events, max over ranks"},
-            "roofline": {"kernel": "gemv_q4k_mma_kernel (scatter) + peer_exchange_kernel" if r1["collectives"] == "peer" else "gemv_q4k_mma_kernel + NCCL", "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "roofline": {"kernel": ("gemv_q4k kernel (scatter epilogue) + peer_exchange_kernel" if r1["collectives"] == "peer" else "gemv_q4k kernel + NCCL"),
+                         "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / peaks["hbm_gbs"], "peak_kind": f"per GPU, of {peak_kind} copy bandwidth", "traffic": None},
-            "cpu_baseline": None,
-            "e2e": {"value": None, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                    "note": "the artifact / session API is single-GPU; the sharded FFN is measured at the kernel + collective level"},
-            "gpu_launches": K * r * (4 if r1["collectives"] == "peer" else 3), "clocks": clocks, "extras": {f"m{m}": v for m, v in results.items()}}))
+            "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": K * r * (4 if r1["collectives"] == "peer" else 3), "clocks": clocks,
+            "extras": {**{f"m{m}": v for m, v in results.items()}, "one_gpu_unsharded": {f"m{m}": v for m, v in base.items()}}}))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -11,13 +11,23 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "lib" / "libdinoml_b200_gguf.so"
 
-VARIANTS = {"auto": 0, "simt": 1, "mma": 2, "umma": 3}
+VARIANTS = {"auto": 0, "simt": 1, "mma": 2, "umma": 3, "stream": 4}
 VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
 DINO_DTYPE = {"float16": 1, "float32": 2, "bfloat16": 6}
 ACTIVATIONS = {"silu": 1, "fast_gelu": 2}
 DEQUANT_DTYPE = {"float32": 0, "float16": 1, "bfloat16": 2}
 
 _lib = None
+
+
+def variant_code(variant) -> int:
+    """"mma", "stream", ... or "stream:3" (family : tuning configuration) or an int code -> the C ABI's variant code."""
+    if isinstance(variant, int):
+        return variant
+    family, _, config = str(variant).partition(":")
+    if family not in VARIANTS:
+        raise ValueError(f"unknown variant {variant!r}; families: {sorted(VARIANTS)}")
+    return VARIANTS[family] | (int(config) << 8 if config else 0)
 
 
 class NativeLibraryMissing(RuntimeError):
@@ -46,6 +56,10 @@ def lib() -> ctypes.CDLL:
     L.dinoml_b200_gguf_gemm_rcr_workspace.restype = ctypes.c_size_t
     L.dinoml_b200_gguf_gemm_rcr_select.argtypes = [ci, ci, ci, ci, ci]
     L.dinoml_b200_gguf_gemm_rcr_select.restype = ci
+    L.dinoml_b200_gguf_variant_configs.argtypes = [ci]
+    L.dinoml_b200_gguf_variant_configs.restype = ci
+    L.dinoml_b200_gguf_variant_supports.argtypes = [ci, ci, ci, ci, ci, ci]
+    L.dinoml_b200_gguf_variant_supports.restype = ci
     L.dinoml_b200_gguf_device_status.restype = ci
     L.dinoml_b200_gguf_gemv_rcr_scatter.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, ci, ci, ci, ci, ci, vp]
     L.dinoml_b200_gguf_gemv_rcr_scatter.restype = ci

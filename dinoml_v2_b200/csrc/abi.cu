@@ -17,6 +17,9 @@ int gemm_rcr_mma(const void* a, const void* b, const void* bias, void* c, int qt
 int gemm_rcr_umma(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                   cudaStream_t s);
 bool gemv_mma_supports(int qtype, int dtype, int m, int n, int k);
+bool gemv_stream_supports(int qtype, int dtype, int m, int n, int k);
+int gemv_stream_configs();
+int stream_device_status();
 bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k);
 size_t gemm_umma_workspace(int qtype, int dtype, int m, int n, int k);
 int umma_device_status();
@@ -30,6 +33,10 @@ int gemm_rcr_umma_peers(const void* a, const void* b, const void* bias, void* c,
 int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch, const void* slots, void* out, int64_t count, int dtype,
                   cudaStream_t s);
 uint32_t peer_exchange_set_poll_limit(uint32_t polls);
+int gemm_rcr_stream(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,
+                    cudaStream_t s);
+int gemm_rcr_stream_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,
+                          const PeerOut* peer_out, cudaStream_t s);
 int gemm_rcr_umma_static(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                          cudaStream_t s);
 size_t gemm_umma_static_scratch_bytes();
@@ -57,7 +64,25 @@ int set_error_message(int rc, const std::string& message) {
 }
 const char* last_error() { return g_last_error.c_str(); }
 
+// Share of the persistent GEMV's CTA-rounds that do work when `tiles` 16-row tiles are dealt whole to its grid of at most
+// two CTAs per SM (1.0 = every CTA gets the same number of tiles).
+static double stream_split_efficiency(int n) {
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    sm_count = sms > 0 ? sms : 148;
+  }
+  const int tiles = (n + 15) / 16, ctas = tiles < 2 * sm_count ? tiles : 2 * sm_count;
+  const int rounds = (tiles + ctas - 1) / ctas;
+  return double(tiles) / (double(rounds) * ctas);
+}
+
 int select_variant(int qtype, int dtype, int m, int n, int k) {
+  // M <= 8 on Q4_K: the persistent bulk-copy GEMV, measured faster than or level with the tile kernel on every benchmarked
+  // shape for M >= 2 and for M = 1 unless its whole-tile split leaves more than a fifth of the last round idle
+  // ([11008 x 4096]: 688 tiles on 296 CTAs = 2.3 rounds; the tile kernel is 9 % faster there).
+  if (gemv_stream_supports(qtype, dtype, m, n, k) && (m >= 2 || stream_split_efficiency(n) >= 0.8)) return DINOML_B200_GGUF_VARIANT_STREAM;
   // M = 9..16 is served by both tensor-core kernels: the tcgen05 one costs the same whatever M is and wins there once
   // the weight is large enough to spread over the SMs; the mma.sync GEMV does twice the MMA work of M <= 8.
   if (m >= 9 && m <= 16 && n >= 2048 && gemm_umma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_UMMA;
@@ -66,10 +91,16 @@ int select_variant(int qtype, int dtype, int m, int n, int k) {
   return DINOML_B200_GGUF_VARIANT_SIMT;
 }
 
+// A variant code = family (low byte) + tuning configuration (second byte, 0 = the family's default for the shape).
 int gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
              int variant, cudaStream_t s) {
+  if (variant < 0 || variant > 0xffff) return RC_RANGE;
+  const int config = (variant >> 8) & 0xff;
+  variant &= 0xff;
   if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, n, k);
+  if (config != 0 && variant != DINOML_B200_GGUF_VARIANT_STREAM) return RC_RANGE;
   switch (variant) {
+    case DINOML_B200_GGUF_VARIANT_STREAM: return gemm_rcr_stream(a, b, bias, c, qtype, dtype, m, n, k, config, s);
     case DINOML_B200_GGUF_VARIANT_SIMT: return gemm_rcr_simt(a, b, bias, c, qtype, dtype, m, n, k, s);
     case DINOML_B200_GGUF_VARIANT_MMA: return gemm_rcr_mma(a, b, bias, c, qtype, dtype, m, n, k, s);
     case DINOML_B200_GGUF_VARIANT_UMMA: return gemm_rcr_umma(a, b, bias, c, qtype, dtype, m, n, k, s);
@@ -82,6 +113,9 @@ int dual_gemm_rcr_peers(const void* a, const void* b01, void* c, const PeerOut& 
                         int activation, int variant, cudaStream_t s) {
   if (activation != 1 && activation != 2) return RC_RANGE;
   if (n <= 0 || n % 8 != 0 || n > 0x3fffffff) return RC_RANGE;       // whole groups of 8 rows per matrix
+  if (variant < 0 || variant > 0xffff) return RC_RANGE;
+  const int config = (variant >> 8) & 0xff;
+  variant &= 0xff;
   PeerOut peers = dst;
   peers.act = activation;
   const int rows = 2 * n;                                              // rows of the interleaved weight
@@ -91,6 +125,8 @@ int dual_gemm_rcr_peers(const void* a, const void* b01, void* c, const PeerOut& 
     if (variant == DINOML_B200_GGUF_VARIANT_MMA && qtype == QTYPE_Q8_0 && gemm_umma_supports(qtype, dtype, m, rows, k))
       variant = DINOML_B200_GGUF_VARIANT_UMMA;
   }
+  if (variant == DINOML_B200_GGUF_VARIANT_STREAM) return gemm_rcr_stream_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, config, &peers, s);
+  if (config != 0) return RC_RANGE;
   if (variant == DINOML_B200_GGUF_VARIANT_MMA) return gemm_rcr_mma_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, &peers, s);
   if (variant == DINOML_B200_GGUF_VARIANT_UMMA) return gemm_rcr_umma_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, &peers, s);
   return RC_RANGE;                                                     // the simt variant has no gated epilogue
@@ -170,9 +206,10 @@ size_t dinoml_b200_gguf_prealloc_scratch_bytes(void) { return gemm_umma_static_s
 
 int dinoml_b200_gguf_device_status(void) {
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  const int peer = peer_device_status();   // read both so that both are cleared
+  const int peer = peer_device_status();   // read all three so that all are cleared
   const int gemm = umma_device_status();
-  return gemm != 0 ? gemm : peer;
+  const int gemv = stream_device_status();
+  return gemm != 0 ? gemm : gemv != 0 ? gemv : peer;
 }
 
 int dinoml_b200_gguf_gemv_rcr_scatter(const void* a, const void* b_quant, const void* bias, void* c, void* const* peer_c, int n_peers,
@@ -199,8 +236,14 @@ int dinoml_b200_gguf_gemm_rcr_scatter(const void* a, const void* b_quant, const 
   peers.act = 0;
   for (int i = 0; i < n_peers; ++i)
     if (peers.ptr[i] == nullptr) return set_error(RC_NULL, where);
+  if (variant < 0 || variant > 0xffff) return set_error(RC_RANGE, where);
+  const int config = (variant >> 8) & 0xff;
+  variant &= 0xff;
   if (variant == DINOML_B200_GGUF_VARIANT_AUTO) variant = select_variant(qtype, dtype, m, n, k);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (variant == DINOML_B200_GGUF_VARIANT_STREAM)
+    return set_error(gemm_rcr_stream_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, config, &peers, s), where);
+  if (config != 0) return set_error(RC_RANGE, where);
   if (variant == DINOML_B200_GGUF_VARIANT_MMA) return set_error(gemm_rcr_mma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, s), where);
   if (variant == DINOML_B200_GGUF_VARIANT_UMMA) return set_error(gemm_rcr_umma_peers(a, b_quant, bias, c, qtype, dtype, m, n, k, &peers, s), where);
   return set_error(RC_RANGE, where);     // the simt variant has no scatter epilogue
@@ -236,6 +279,23 @@ int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k) 
   return select_variant(qtype, dtype, m, n, k);
 }
 
+int dinoml_b200_gguf_variant_configs(int family) {
+  return family == DINOML_B200_GGUF_VARIANT_STREAM ? gemv_stream_configs() : 0;
+}
+
+int dinoml_b200_gguf_variant_supports(int family, int qtype, int dtype, int m, int n, int k) {
+  if (qtype_block_size(qtype) == 0 || m <= 0 || n <= 0 || k <= 0 || k % qtype_block_size(qtype) != 0) return 0;
+  if (dtype != DINO_F16 && dtype != DINO_BF16 && dtype != DINO_F32) return 0;
+  switch (family) {
+    case DINOML_B200_GGUF_VARIANT_AUTO:
+    case DINOML_B200_GGUF_VARIANT_SIMT: return 1;
+    case DINOML_B200_GGUF_VARIANT_MMA: return gemv_mma_supports(qtype, dtype, m, n, k) ? 1 : 0;
+    case DINOML_B200_GGUF_VARIANT_UMMA: return gemm_umma_supports(qtype, dtype, m, n, k) ? 1 : 0;
+    case DINOML_B200_GGUF_VARIANT_STREAM: return gemv_stream_supports(qtype, dtype, m, n, k) ? 1 : 0;
+    default: return 0;
+  }
+}
+
 #define B200_DEFINE(q, QT, dt, DT, var, VAR)                                                                          \
   int dinoml_b200_gguf_##q##_gemm_rcr_##dt##_##var##_v1(const void* a, const void* b_quant, void* c, int m, int n,    \
                                                         int k, void* stream) {                                        \
@@ -260,7 +320,9 @@ int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k) 
   B200_DEFINE(q, QT, float16, DINO_F16, mma, DINOML_B200_GGUF_VARIANT_MMA)                \
   B200_DEFINE(q, QT, bfloat16, DINO_BF16, mma, DINOML_B200_GGUF_VARIANT_MMA)              \
   B200_DEFINE(q, QT, float16, DINO_F16, umma, DINOML_B200_GGUF_VARIANT_UMMA)              \
-  B200_DEFINE(q, QT, bfloat16, DINO_BF16, umma, DINOML_B200_GGUF_VARIANT_UMMA)
+  B200_DEFINE(q, QT, bfloat16, DINO_BF16, umma, DINOML_B200_GGUF_VARIANT_UMMA)            \
+  B200_DEFINE(q, QT, float16, DINO_F16, stream, DINOML_B200_GGUF_VARIANT_STREAM)          \
+  B200_DEFINE(q, QT, bfloat16, DINO_BF16, stream, DINOML_B200_GGUF_VARIANT_STREAM)
 B200_DEFINE_Q(q8_0, QTYPE_Q8_0)
 B200_DEFINE_Q(q4_k, QTYPE_Q4_K)
 B200_DEFINE_Q(q6_k, QTYPE_Q6_K)

@@ -17,6 +17,16 @@ template <> struct MmaType<__nv_bfloat16> {
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
+  // d = a * b + c with the C tuple in four registers of its own (a CTA-lifetime quad of zeros: no accumulator to clear)
+  static __device__ __forceinline__ void mma_c(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+  }
+  static __device__ __forceinline__ float2 pair_to_float2(uint32_t r) {   // two packed 16-bit values -> two floats (exact)
+    return make_float2(__uint_as_float(r << 16), __uint_as_float(r & 0xffff0000u));
+  }
   static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
   static __device__ __forceinline__ float sum8(const uint4& v) {
@@ -40,6 +50,13 @@ template <> struct MmaType<__half> {
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
   }
+  static __device__ __forceinline__ void mma_c(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, const float (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+  }
+  static __device__ __forceinline__ float2 pair_to_float2(uint32_t r) { return __half22float2(*reinterpret_cast<const __half2*>(&r)); }
   static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
   static __device__ __forceinline__ float sum8(const uint4& v) {
@@ -50,6 +67,12 @@ template <> struct MmaType<__half> {
     return s;
   }
 };
+
+// Four registers holding 0.f whose contents the compiler cannot see through: a stable zero C tuple for mma_c.
+__device__ __forceinline__ void opaque_zero4(float (&z)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) asm volatile("mov.f32 %0, 0f00000000;\n" : "=f"(z[i]));
+}
 
 // Byte -> float without I2F: 0x4B0000bb is 2^23 + bb.
 __device__ __forceinline__ float byte_to_float(uint32_t word, int i) {

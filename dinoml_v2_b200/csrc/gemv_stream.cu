@@ -1,0 +1,435 @@
+// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations, Q4_K weights.
+//
+// C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), W streamed once from HBM as packed GGUF blocks (144 B per 256 weights).
+// Same exact-integer tensor-core arithmetic as the tile kernel in gemv_mma.cu (quants become 16-bit floats 128+q /
+// 1024+q, mma.sync.m16n8k16 with fp32 accumulation, per-sub-block scales applied in fp32, the offsets folded against
+// per-sub-block activation sums); what changes is how the bytes move and how the work is cut:
+//   * grid = one CTA per SM (or two), CTA c owns the contiguous 16-row tiles [tile_begin(c), tile_begin(c+1)) - no tail
+//     wave, one prologue (activation sums) per SM instead of one per tile;
+//   * one producer warp issues, per (tile, K chunk of 8 super-blocks), sixteen 1-D bulk copies (cp.async.bulk, one per
+//     weight row, 1152 B each) into a ring of D shared-memory stages; a stage is "full" when its bytes have landed
+//     (mbarrier transaction count) and "empty" when its 8 consumer warps have arrived.  The ring runs across tile
+//     boundaries.  No thread spends issue slots on per-16-byte copies and no CTA barrier sits in the loop;
+//   * NG groups of 8 consumer warps take the stages round-robin (warp w of a group unpacks super-block w of the chunk
+//     for all 16 rows), accumulate over the chunks of a tile and hand their partial rows to the epilogue warp through
+//     a double-buffered shared-memory area guarded by mbarriers; the epilogue warp adds the partials in a fixed order,
+//     applies bias / the gated activation and stores (also to peer buffers for the sharded path);
+//   * programmatic dependent launch: the producer starts streaming the (constant) weights at once, everything that
+//     reads activations or writes outputs first waits for the preceding kernel (griddepcontrol.wait).  With the
+//     one-CTA-per-SM grid and at most half of an SM's shared memory and registers per CTA, the next launch's CTAs sit
+//     beside this launch's and fill their rings while this one finishes.
+// Every mbarrier wait is bounded; a wait that gives up records a code (11..14) in the library's status word, raises
+// the CTA's abort flag, the producer waits for the copies it has in flight, and every role returns.
+//
+// Behavioural ancestor in the reference: the small-M kernels of the fused prototype
+// (kernels/rocm/src/ck_gguf_q8_gemm.hip:1009-1166); the reference's CUDA path dequantizes the whole weight and runs a
+// dense Sm80 GEMM instead (src/dinoml/lowering/ops/gemm.py:729-749).
+#include <type_traits>
+
+#include "gemv_stream_common.cuh"
+
+namespace b200gguf {
+
+int check_gemm_args(const void* a, const void* b, const void* c, int qtype, int dtype, int m, int n, int k);
+
+namespace stream {
+
+constexpr int kRows = 16;                       // weight rows per tile (one MMA M-tile)
+constexpr int kKC = 8;                          // super-blocks per row per stage: one per consumer warp of a group
+constexpr int kSbBytes = 144;
+constexpr int kPitch = kKC * kSbBytes + 32;     // 1184 B: 8-byte reads of 4 rows x 4 lanes (a half-warp) hit 32 distinct banks
+constexpr int kStageBytes = kRows * kPitch;     // 18944 B per ring slot
+constexpr int kGroupWarps = kKC;
+constexpr int kBarBytes = 256;                  // mbarrier area in front of the ring (up to 32 barriers)
+
+static __device__ int g_stream_status;
+
+template <int MXC, int NCW> struct RedBuf {
+  float red[NCW][kRows][MXC];    // per consumer warp: sum_j ds * S' for (row, activation column)
+  float xt[NCW][kRows][MXC];     // per consumer warp: sum_j (MAGIC * ds + dm) * X
+};
+
+template <int MXC, int NG, int D> constexpr size_t smem_fixed_bytes() {
+  return kBarBytes /* barriers */ + size_t(D) * kStageBytes + 2 * sizeof(RedBuf<MXC, NG * kGroupWarps>);
+}
+
+// MXC: activation rows covered (power of two >= m, <= 8).  NG: groups of 8 consumer warps.  D: ring slots (D % NG == 0).
+// Threads: NG * 8 consumer warps, then the producer warp, then the epilogue warp.
+// PROBE: bandwidth probe - the bytes move through the ring exactly as usual, the consumers skip the arithmetic (the
+// output is all zeros); it measures what the data path alone sustains for a shape.
+template <typename T, int MXC, int NG, int D, bool PROBE>
+__global__ void __launch_bounds__((NG * kGroupWarps + 2) * 32, NG == 1 ? 2 : 1)
+gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
+                       int m, int n, int k, int* status, const PeerOut peers) {
+  using MT = MmaType<T>;
+  constexpr int NCW = NG * kGroupWarps;
+  constexpr int MC = MXC == 1 ? 1 : 2;             // accumulator columns a lane keeps
+  static_assert(D % NG == 0 && D >= 2 * NG, "every group needs its own ring slots, at least two");
+  static_assert(MXC == 1 || MXC == 2 || MXC == 4 || MXC == 8, "MXC");
+  using Red = RedBuf<MXC, NCW>;
+
+  extern __shared__ __align__(128) uint8_t smem_dyn[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_dyn);               // full[D], empty[D], red_full[2], red_empty[2]
+  uint8_t* sW = smem_dyn + kBarBytes;                                         // D x kStageBytes
+  Red* sRed = reinterpret_cast<Red*>(sW + size_t(D) * kStageBytes);      // [2]
+  float* sX = reinterpret_cast<float*>(sRed + 2);                        // [MXC][k/32]
+  __shared__ __align__(16) float sS[NCW][kRows][8];                      // ds per row, sub-block (warp-private scratch)
+  __shared__ float sOut[kRows * MXC];                                    // epilogue warp scratch
+  __shared__ int s_abort;
+  static_assert((2 * D + 4) * 8 <= kBarBytes, "barrier area");
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nsb = k >> 8, nsub = k >> 5;
+  const int nchunks = (nsb + kKC - 1) / kKC;
+  const int tiles = (n + kRows - 1) / kRows;
+  const int t0 = tile_begin(blockIdx.x, tiles, gridDim.x), t1 = tile_begin(blockIdx.x + 1, tiles, gridDim.x);
+  const int ntiles = t1 - t0;
+  const int nunits = ntiles * nchunks;
+  const int64_t row_bytes = int64_t(nsb) * kSbBytes;
+  volatile int* abort_flag = &s_abort;
+
+  const uint32_t bar0 = smem_u32(bars);
+  auto full = [&](int s) { return bar0 + 8u * uint32_t(s); };
+  auto empty = [&](int s) { return bar0 + 8u * uint32_t(D + s); };
+  auto red_full = [&](int b) { return bar0 + 8u * uint32_t(2 * D + b); };
+  auto red_empty = [&](int b) { return bar0 + 8u * uint32_t(2 * D + 2 + b); };
+
+  if (tid == 0) {
+    for (int s = 0; s < D; ++s) {
+      mbar_init(full(s), 1);                    // the producer's arrive.expect_tx; the bytes complete the phase
+      mbar_init(empty(s), kGroupWarps);         // one elected arrive per consumer warp of the slot's group
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(red_full(b), NCW);
+      mbar_init(red_empty(b), 1);
+    }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+
+  if (warp == NCW) {
+    // ------------------------------------------------------------------ producer: weights are constants, no dependency wait
+    bool ok = true;
+    int issued = 0, tile = t0, chunk = 0;
+    const uint32_t sW_u32 = smem_u32(sW);
+    for (int u = 0; u < nunits; ++u) {
+      const int slot = u % D, it = u / D;
+      if (it > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(empty(slot), uint32_t(it - 1) & 1u, abort_flag, status, ST_STREAM_EMPTY) ? 1 : 0) != 0;
+        if (!ok) break;
+      }
+      const int sbs = min(kKC, nsb - chunk * kKC);
+      const int rows_valid = min(kRows, n - tile * kRows);
+      const uint32_t bytes_row = uint32_t(sbs) * kSbBytes;
+      if (lane == 0) mbar_arrive_expect_tx(full(slot), uint32_t(rows_valid) * bytes_row);
+      __syncwarp();
+      if (lane < rows_valid)
+        bulk_load(sW_u32 + uint32_t(slot) * kStageBytes + uint32_t(lane) * kPitch,
+                  w + int64_t(tile * kRows + lane) * row_bytes + int64_t(chunk) * (kKC * kSbBytes), bytes_row, full(slot));
+      issued = u + 1;
+      if (++chunk == nchunks) { chunk = 0; ++tile; }
+    }
+    if (!ok && lane == 0)       // aborting: the copies still in flight must land before this CTA's shared memory goes away
+      for (int v = max(0, issued - D); v < issued; ++v) mbar_wait_plain(full(v % D), uint32_t(v / D) & 1u);
+    return;
+  }
+
+  // Everything below reads activations / writes outputs that a preceding kernel in the stream may still be producing.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+  if (warp == NCW + 1) {
+    // ------------------------------------------------------------------ epilogue warp
+    for (int tl = 0; tl < ntiles; ++tl) {
+      const int buf = tl & 1;
+      if (!(__all_sync(0xffffffffu, mbar_wait(red_full(buf), uint32_t(tl >> 1) & 1u, abort_flag, status, ST_STREAM_RED_FULL) ? 1 : 0))) break;
+      const Red& rb = sRed[buf];
+      for (int idx = lane; idx < kRows * MXC; idx += 32) {
+        const int r = idx & (kRows - 1), c = idx >> 4;
+        float v = 0.f, xs = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < NCW; ++wv) {
+          v += rb.red[wv][r][c];
+          xs += rb.xt[wv][r][c];
+        }
+        sOut[idx] = v - xs;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(red_empty(buf));
+      const int tile = t0 + tl;
+      for (int idx = lane; idx < kRows * MXC; idx += 32) {
+        const int r = idx & (kRows - 1), c = idx >> 4;
+        const int row = tile * kRows + r;
+        if (row >= n || c >= m) continue;
+        float v = sOut[idx];
+        int64_t at = int64_t(c) * n + row;
+        if (peers.act != ACT_NONE) {
+          // gated pair: rows r < 8 of the tile belong to the first matrix, r + 8 to the second; output has n / 2 columns
+          if (r >= 8) continue;
+          v = gate_activation(v, peers.act) * sOut[idx + 8];
+          at = int64_t(c) * (n >> 1) + (tile * 8 + r);
+        } else if (bias != nullptr) {
+          v += MT::to_float(bias[row]);
+        }
+        const T out = MT::from_float(v);
+        y[at] = out;
+#pragma unroll
+        for (int pi = 0; pi < 8; ++pi)
+          if (pi < peers.count) static_cast<T*>(peers.ptr[pi])[at] = out;
+      }
+      __syncwarp();                         // sOut is rewritten for the next tile
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumer warps
+  const int cw = warp, grp = cw / kGroupWarps, wq = cw % kGroupWarps;
+  const int g = lane >> 2, t = lane & 3;
+  const int srow = lane >> 1, shalf = lane & 1;   // scale-decode role of this lane
+
+  // X[c][j] = sum of activations of row c over sub-block j (rows >= m are zero)
+  for (int i = tid; i < nsub * MXC; i += NCW * 32) {
+    const int c = i / nsub, j = i - c * nsub;
+    float s = 0.f;
+    if (c < m) {
+      const uint4* px = reinterpret_cast<const uint4*>(x + int64_t(c) * k + int64_t(j) * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) s += MT::sum8(__ldg(px + q));
+    }
+    sX[i] = s;
+  }
+  named_barrier(1, NCW * 32);
+
+  float res[4] = {0.f, 0.f, 0.f, 0.f};
+  float zero4[4];
+  opaque_zero4(zero4);
+  float xt[MXC];
+#pragma unroll
+  for (int c = 0; c < MXC; ++c) xt[c] = 0.f;
+  const T* xrow = x + int64_t(min(g, m - 1)) * k + 8 * t;
+
+  bool ok = true;
+  int cur_tile = 0;                             // tile (local index) the accumulators belong to
+  auto flush = [&](int tl) {
+    const int buf = tl & 1;
+    if (tl >= 2) ok = __all_sync(0xffffffffu, mbar_wait(red_empty(buf), uint32_t((tl >> 1) - 1) & 1u, abort_flag, status, ST_STREAM_RED_EMPTY) ? 1 : 0) != 0;
+    if (!ok) return;
+    Red& rb = sRed[buf];
+    if (2 * t < MXC) {
+      rb.red[cw][g][2 * t] = res[0];
+      rb.red[cw][g + 8][2 * t] = res[2];
+      if (MC == 2) {
+        rb.red[cw][g][2 * t + 1] = res[1];
+        rb.red[cw][g + 8][2 * t + 1] = res[3];
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < MXC; ++c) {
+      const float both = xt[c] + __shfl_xor_sync(0xffffffffu, xt[c], 1);
+      if (shalf == 0) rb.xt[cw][srow][c] = both;
+      xt[c] = 0.f;
+    }
+    res[0] = res[1] = res[2] = res[3] = 0.f;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(red_full(buf));
+  };
+
+  int tl = 0, chunk = grp;
+  while (chunk >= nchunks && tl < ntiles) { chunk -= nchunks; ++tl; }
+  for (int u = grp; u < nunits && ok; u += NG) {
+    while (cur_tile < tl && ok) { flush(cur_tile); ++cur_tile; }
+    if (!ok) break;
+    const int slot = u % D;
+    ok = __all_sync(0xffffffffu, mbar_wait(full(slot), uint32_t(u / D) & 1u, abort_flag, status, ST_STREAM_FULL) ? 1 : 0) != 0;
+    if (!ok) break;
+    const int sb = chunk * kKC + wq;
+    if (!PROBE && sb < nsb) {
+      const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
+      {  // lane pair (srow, shalf): 4 sub-block scales -> ds to shared memory, min/MAGIC term folded against X
+        const uint4 hdr = *reinterpret_cast<const uint4*>(st + srow * kPitch);
+        const float d = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
+        const float dmin = half_bits_to_float(uint16_t(hdr.x >> 16));
+        // sub-blocks 0..3 keep their 6-bit fields in place; 4..7 are split across two bytes
+        const uint32_t sc_lo = hdr.y & 0x3f3f3f3fu, mn_lo = hdr.z & 0x3f3f3f3fu;
+        const uint32_t sc_hi = (hdr.w & 0x0f0f0f0fu) | (((hdr.y >> 6) & 0x03030303u) << 4);
+        const uint32_t mn_hi = ((hdr.w >> 4) & 0x0f0f0f0fu) | (((hdr.z >> 6) & 0x03030303u) << 4);
+        const uint32_t scb = shalf ? sc_hi : sc_lo, mnb = shalf ? mn_hi : mn_lo;
+        float4 dsv;
+        float kk[4];
+        float* dsf = reinterpret_cast<float*>(&dsv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          dsf[i] = d * byte_to_float(scb, i);
+          kk[i] = fmaf(MT::kMagic, dsf[i], dmin * byte_to_float(mnb, i));
+        }
+        *reinterpret_cast<float4*>(&sS[cw][srow][4 * shalf]) = dsv;
+#pragma unroll
+        for (int c = 0; c < MXC; ++c) {
+          const float4 X = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 8 + 4 * shalf]);
+          xt[c] = fmaf(kk[0], X.x, xt[c]);
+          xt[c] = fmaf(kk[1], X.y, xt[c]);
+          xt[c] = fmaf(kk[2], X.z, xt[c]);
+          xt[c] = fmaf(kk[3], X.w, xt[c]);
+        }
+      }
+      __syncwarp();
+      const float4 dsa0 = *reinterpret_cast<const float4*>(&sS[cw][g][0]);
+      const float4 dsa1 = *reinterpret_cast<const float4*>(&sS[cw][g][4]);
+      const float4 dsb0 = *reinterpret_cast<const float4*>(&sS[cw][g + 8][0]);
+      const float4 dsb1 = *reinterpret_cast<const float4*>(&sS[cw][g + 8][4]);
+      const float ds_a[8] = {dsa0.x, dsa0.y, dsa0.z, dsa0.w, dsa1.x, dsa1.y, dsa1.z, dsa1.w};
+      const float ds_b[8] = {dsb0.x, dsb0.y, dsb0.z, dsb0.w, dsb1.x, dsb1.y, dsb1.z, dsb1.w};
+      const uint8_t* q0p = st + g * kPitch + 16 + 8 * t;
+      const uint8_t* q1p = q0p + 8 * kPitch;
+      const T* xs = xrow + sb * 256;
+#pragma unroll
+      for (int G = 0; G < 4; ++G) {
+        const uint2 q0 = *reinterpret_cast<const uint2*>(q0p + 32 * G);
+        const uint2 q1 = *reinterpret_cast<const uint2*>(q1p + 32 * G);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t n0x = (h ? q0.x >> 4 : q0.x) & 0x0f0f0f0fu, n0y = (h ? q0.y >> 4 : q0.y) & 0x0f0f0f0fu;
+          const uint32_t n1x = (h ? q1.x >> 4 : q1.x) & 0x0f0f0f0fu, n1y = (h ? q1.y >> 4 : q1.y) & 0x0f0f0f0fu;
+          const uint32_t a_lo[4] = {MT::fix(__byte_perm(n0x, MT::kMagicBytes, 0x4140)), MT::fix(__byte_perm(n1x, MT::kMagicBytes, 0x4140)),
+                                    MT::fix(__byte_perm(n0x, MT::kMagicBytes, 0x4342)), MT::fix(__byte_perm(n1x, MT::kMagicBytes, 0x4342))};
+          const uint32_t a_hi[4] = {MT::fix(__byte_perm(n0y, MT::kMagicBytes, 0x4140)), MT::fix(__byte_perm(n1y, MT::kMagicBytes, 0x4140)),
+                                    MT::fix(__byte_perm(n0y, MT::kMagicBytes, 0x4342)), MT::fix(__byte_perm(n1y, MT::kMagicBytes, 0x4342))};
+          // rows >= m read a clamped (valid) row; their accumulator columns are never stored
+          const uint4 xb = __ldg(reinterpret_cast<const uint4*>(xs + 64 * G + 32 * h));
+          float acc[4];
+          MT::mma_c(acc, a_lo, xb.x, xb.y, zero4);
+          MT::mma(acc, a_hi, xb.z, xb.w);
+          const float dsr0 = ds_a[2 * G + h], dsr1 = ds_b[2 * G + h];
+          res[0] = fmaf(dsr0, acc[0], res[0]);
+          res[2] = fmaf(dsr1, acc[2], res[2]);
+          if (MC == 2) {
+            res[1] = fmaf(dsr0, acc[1], res[1]);
+            res[3] = fmaf(dsr1, acc[3], res[3]);
+          }
+        }
+      }
+    }
+    __syncwarp();                              // every lane is done with the stage (and with sS)
+    if (lane == 0) mbar_arrive(empty(slot));
+    chunk += NG;
+    while (chunk >= nchunks) { chunk -= nchunks; ++tl; }
+  }
+  // the tiles this warp has not flushed yet (all of them contribute to every tile's reduction, zeros included)
+  while (cur_tile < ntiles && ok) { flush(cur_tile); ++cur_tile; }
+}
+
+// ---------------------------------------------------------------------------------------- host side
+int* stream_status_ptr() {
+  static int* ptr[kGemvMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kGemvMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_stream_status) != cudaSuccess) return nullptr;
+    ptr[dev] = static_cast<int*>(p);
+  }
+  return ptr[dev];
+}
+
+template <typename T, int MXC, int NG, int D, bool PROBE = false>
+static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int ctas_per_sm, const PeerOut& peers,
+                          cudaStream_t s) {
+  const size_t smem = smem_fixed_bytes<MXC, NG, D>() + size_t(k / 32) * MXC * sizeof(float);
+  if (smem > 216 * 1024) return RC_RANGE;            // + up to 9 KB of static shared memory, under the 227 KB per CTA
+  int* status = stream_status_ptr();
+  if (status == nullptr) return RC_LAUNCH;
+  auto kern = gemv_q4k_stream_kernel<T, MXC, NG, D, PROBE>;
+  static SmemOptIn granted;
+  if (!smem_opt_in(kern, smem, granted)) return RC_LAUNCH;
+  int sm_count = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  const int tiles = (n + kRows - 1) / kRows;
+  const int ctas = min(tiles, sm_count * (ctas_per_sm < 1 ? 1 : ctas_per_sm));
+  const cudaError_t err = gemv_launch(kern, ctas, 1, (NG * kGroupWarps + 2) * 32, smem, s, static_cast<const T*>(a),
+                                      static_cast<const uint8_t*>(b), static_cast<const T*>(bias), static_cast<T*>(c), m, n, k, status, peers);
+  return err == cudaSuccess ? RC_OK : RC_LAUNCH;
+}
+
+// Tuning configurations (the `config` byte of a variant code, see dinoml_b200_gguf.h).  0 = the default for the shape.
+//   1: 8 consumer warps, 5 ring slots (95 KB), one CTA per SM - two launches fit side by side on an SM
+//   2: 16 consumer warps, 6 ring slots, one CTA per SM
+//   3: 16 consumer warps, 8 ring slots, one CTA per SM
+//   4: 8 consumer warps, 4 ring slots, two CTAs per SM
+// Bit 7 of the configuration byte (0x80 | 1..4) selects the bandwidth probe of that configuration (bfloat16, M = 1).
+constexpr int kStreamConfigs = 4;
+constexpr int kProbeBit = 0x80;
+template <typename T, int MXC>
+static int launch_q4k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
+                        cudaStream_t s) {
+  if (config & kProbeBit) {
+    if constexpr (MXC == 1 && std::is_same<T, __nv_bfloat16>::value) {
+      switch (config & ~kProbeBit) {
+        case 1: return launch_q4k_cfg<T, 1, 1, 5, true>(a, b, bias, c, m, n, k, 1, peers, s);
+        case 2: return launch_q4k_cfg<T, 1, 2, 6, true>(a, b, bias, c, m, n, k, 1, peers, s);
+        case 3: return launch_q4k_cfg<T, 1, 2, 8, true>(a, b, bias, c, m, n, k, 1, peers, s);
+        case 4: return launch_q4k_cfg<T, 1, 1, 4, true>(a, b, bias, c, m, n, k, 2, peers, s);
+        default: return RC_RANGE;
+      }
+    }
+    return RC_RANGE;
+  }
+  switch (config) {
+    case 1: return launch_q4k_cfg<T, MXC, 1, 5>(a, b, bias, c, m, n, k, 1, peers, s);
+    case 2: return launch_q4k_cfg<T, MXC, 2, 6>(a, b, bias, c, m, n, k, 1, peers, s);
+    case 3: return launch_q4k_cfg<T, MXC, 2, 8>(a, b, bias, c, m, n, k, 1, peers, s);
+    case 0:                                       // default: measured best or level on every benchmarked shape
+    case 4: return launch_q4k_cfg<T, MXC, 1, 4>(a, b, bias, c, m, n, k, 2, peers, s);
+    default: return RC_RANGE;
+  }
+}
+
+template <typename T>
+static int launch_q4k(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
+                      cudaStream_t s) {
+  if (m == 1) return launch_q4k_m<T, 1>(a, b, bias, c, m, n, k, config, peers, s);
+  if (m == 2) return launch_q4k_m<T, 2>(a, b, bias, c, m, n, k, config, peers, s);
+  if (m <= 4) return launch_q4k_m<T, 4>(a, b, bias, c, m, n, k, config, peers, s);
+  return launch_q4k_m<T, 8>(a, b, bias, c, m, n, k, config, peers, s);
+}
+
+}  // namespace stream
+
+bool gemv_stream_supports(int qtype, int dtype, int m, int n, int k) {
+  (void)n;
+  return qtype == QTYPE_Q4_K && (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 8 && k % 256 == 0;
+}
+int gemv_stream_configs() { return stream::kStreamConfigs; }
+
+// peers: extra destinations of the result / gated epilogue (null = none); config: tuning configuration, 0 = default.
+int gemm_rcr_stream_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,
+                          const PeerOut* peer_out, cudaStream_t s) {
+  const PeerOut peers = peer_out != nullptr ? *peer_out : no_peers();
+  if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
+  if (dtype == DINO_F32) return RC_DTYPE;
+  if (m > 8) return RC_RANGE;
+  if (qtype != QTYPE_Q4_K) return RC_QTYPE;
+  if (!gemv_stream_supports(qtype, dtype, m, n, k)) return RC_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;   // bulk-copy sources, vector loads
+  return dtype == DINO_BF16 ? stream::launch_q4k<__nv_bfloat16>(a, b, bias, c, m, n, k, config, peers, s)
+                            : stream::launch_q4k<__half>(a, b, bias, c, m, n, k, config, peers, s);
+}
+
+int gemm_rcr_stream(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,
+                    cudaStream_t s) {
+  return gemm_rcr_stream_peers(a, b, bias, c, qtype, dtype, m, n, k, config, nullptr, s);
+}
+
+// Reads (and clears) the stream kernels' status word of the current device.
+int stream_device_status() {
+  int* status = stream::stream_status_ptr();
+  int value = 0;
+  if (status == nullptr) return -1;
+  if (cudaMemcpy(&value, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (value != 0) cudaMemset(status, 0, sizeof(int));
+  return value;
+}
+
+}  // namespace b200gguf

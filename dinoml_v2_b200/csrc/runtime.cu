@@ -208,12 +208,12 @@ int parse_plan(DinoModule* mod, const std::string& path) {
       if (n.a < 0 || n.out < 0 || n.b < 0 || (bias != "-" && n.bias < 0)) return fail(where + "node references an unknown tensor");
       if (!mod->constants[n.b].encoded) return fail(where + "gemm weight must be a GGUF-encoded constant");
       if (n.bias >= 0 && mod->constants[n.bias].encoded) return fail(where + "bias must be a dense constant");
-      if (n.variant < 0 || n.variant > 3) return fail(where + "bad variant");
+      if (n.variant < 0 || (n.variant & 0xff) > 4 || n.variant > 0xffff) return fail(where + "bad variant");   // family | config << 8
       mod->nodes.push_back(n);
     } else if (kind == "dispatch") {
       DispatchSpec d;
       if (!(ls >> d.node >> d.m >> d.n >> d.k >> d.variant) || d.node < 0 || size_t(d.node) >= mod->nodes.size() ||
-          d.variant < 1 || d.variant > 3)
+          (d.variant & 0xff) < 1 || (d.variant & 0xff) > 4 || d.variant > 0xffff)
         return fail(where + "malformed dispatch record");
       mod->dispatch.push_back(d);
     } else {

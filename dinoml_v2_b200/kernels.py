@@ -61,7 +61,7 @@ def gemm_rcr(a: torch.Tensor, b_quant: torch.Tensor, qtype, bias: torch.Tensor |
     _require_cuda(out, "out")
     rc = _native.lib().dinoml_b200_gguf_gemm_rcr(
         a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(), q.value,
-        _native.DINO_DTYPE[dtype], m, n, k, _native.VARIANTS[variant], _stream_ptr(stream))
+        _native.DINO_DTYPE[dtype], m, n, k, _native.variant_code(variant), _stream_ptr(stream))
     _native.check(rc, "dinoml_b200_gguf_gemm_rcr")
     return out
 
@@ -99,7 +99,7 @@ def dual_gemm_rcr(a: torch.Tensor, b01_interleaved: torch.Tensor, qtype, activat
     _require_cuda(out, "out")
     rc = _native.lib().dinoml_b200_gguf_dual_gemm_rcr(
         a.data_ptr(), b01_interleaved.data_ptr(), out.data_ptr(), None, 0, q.value, _native.DINO_DTYPE[_DTYPE_NAME[a.dtype]], m, n, k,
-        _native.ACTIVATIONS[activation], _native.VARIANTS[variant], _stream_ptr(stream))
+        _native.ACTIVATIONS[activation], _native.variant_code(variant), _stream_ptr(stream))
     _native.check(rc, "dinoml_b200_gguf_dual_gemm_rcr")
     return out
 
@@ -110,13 +110,25 @@ def profile_gemm_rcr(a, b_quant, qtype, out, *, variant: str, iterations: int, b
     k = a.shape[-1]
     return float(_native.lib().dinoml_profile_b200_gguf_gemm_rcr(
         a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, out.data_ptr(), q.value,
-        _native.DINO_DTYPE[_DTYPE_NAME[a.dtype]], a.numel() // k, b_quant.shape[0], k, _native.VARIANTS[variant],
+        _native.DINO_DTYPE[_DTYPE_NAME[a.dtype]], a.numel() // k, b_quant.shape[0], k, _native.variant_code(variant),
         int(iterations), _stream_ptr(stream)))
 
 
 def select_variant(qtype, dtype: str, m: int, n: int, k: int) -> str:
     q = qtype_of(qtype)
     return _native.VARIANT_NAMES[_native.lib().dinoml_b200_gguf_gemm_rcr_select(q.value, _native.DINO_DTYPE[dtype], m, n, k)]
+
+
+def variant_supports(variant: str, qtype, dtype: str, m: int, n: int, k: int) -> bool:
+    """The library's own predicate: does this variant family serve the problem?"""
+    q = qtype_of(qtype)
+    family = _native.variant_code(variant) & 0xff
+    return bool(_native.lib().dinoml_b200_gguf_variant_supports(family, q.value, _native.DINO_DTYPE[dtype], m, n, k))
+
+
+def variant_configs(variant: str) -> int:
+    """Number of tuning configurations of a variant family (valid: "family:1" .. "family:N")."""
+    return int(_native.lib().dinoml_b200_gguf_variant_configs(_native.variant_code(variant) & 0xff))
 
 
 def device_status() -> int:

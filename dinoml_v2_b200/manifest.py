@@ -24,12 +24,19 @@ PROFILE_CACHE_SCHEMA_VERSION = 9
 EXECUTION_PLAN_KERNEL_LIBRARIES = (KERNEL_LIBRARY,)          # src/dinoml/kernels/manifest.py:98-105
 SUPPORTED_OPS = ("gemm_rcr", "gemm_rcr_bias", "dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu")
 DUAL_OPS = ("dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu")
-VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3}
+VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3, "stream": 4}
+# Tuning configurations of the persistent GEMV (csrc/gemv_stream.cu): each is a candidate of its own, as the tile / stage /
+# warp entries of the reference's CUTLASS catalogue are (src/dinoml/kernels/providers/cutlass/gemm.py:19-127).
+STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": 5, "ctas_per_sm": 1}, 2: {"consumer_warps": 16, "ring_slots": 6, "ctas_per_sm": 1},
+                  3: {"consumer_warps": 16, "ring_slots": 8, "ctas_per_sm": 1}, 4: {"consumer_warps": 8, "ring_slots": 4, "ctas_per_sm": 2}}
+STREAM_QTYPES = ("Q4_K",)
 
 _B200_TUNING = {
     "simt": {"kind": "gemv_simt", "rows_per_warp": 1, "activation_rows_per_pass": 4, "staging": "ldg", "tensor_cores": "none"},
     "mma": {"kind": "gemv", "rows_per_cta": 16, "stage_super_blocks": 4, "stages": [3, 4, 6], "staging": "cp_async16",
             "k_slices": "cluster_dsmem for m > 2", "tensor_cores": "mma.sync.m16n8k16", "max_m": 16},
+    "stream": {"kind": "gemv_persistent", "rows_per_tile": 16, "stage_super_blocks": 8, "staging": "cp.async.bulk + mbarrier ring",
+               "work_split": "contiguous 16-row tiles per CTA", "tensor_cores": "mma.sync.m16n8k16", "max_m": 8},
     "umma": {"kind": "umma_gemm", "tile_n": 128, "tile_m": [64, 128, 256], "tile_k": 64, "stages": 4, "staging": "tma",
              "tensor_cores": "tcgen05.mma.cta_group::1.kind::f16", "weight_operand": "tmem", "accumulator": "tmem",
              "work_split": "stream_k", "min_m": 9},
@@ -51,11 +58,27 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
         if qtype in ("Q4_K", "Q6_K", "Q8_0"):
             variants.append("mma")
             variants.append("umma")
+        if qtype in STREAM_QTYPES:
+            variants += [f"stream:{c}" for c in sorted(STREAM_CONFIGS)]
     return variants
 
 
-def variant_supports(variant: str, m: int) -> bool:
-    return {"simt": True, "mma": 1 <= m <= 16, "umma": m >= 9}[variant]
+def variant_code(variant: str) -> int:
+    """"stream:4" -> family code | configuration << 8 (the C ABI's variant argument)."""
+    family, _, config = variant.partition(":")
+    return VARIANT_CODES[family] | (int(config) << 8 if config else 0)
+
+
+def variant_supports(variant: str, m: int, *, qtype: str | None = None, dtype: str | None = None, n: int | None = None,
+                     k: int | None = None) -> bool:
+    """Does the variant serve the problem?  With the full problem given this is the library's own predicate
+    (dinoml_b200_gguf_variant_supports: M range, K multiples, row-pitch alignment per qtype); with M alone, the M range."""
+    family = variant.partition(":")[0]
+    if None not in (qtype, dtype, n, k):
+        from . import _native
+        return bool(_native.lib().dinoml_b200_gguf_variant_supports(VARIANT_CODES[family], qtype_of(qtype).value, _native.DINO_DTYPE[dtype],
+                                                                    int(m), int(n), int(k)))
+    return {"simt": True, "mma": 1 <= m <= 16, "umma": m >= 9, "stream": 1 <= m <= 8}[family]
 
 
 def kernel_symbol(qtype: str, op: str, dtype: str, variant: str, *, profile: bool = False) -> str:
@@ -67,9 +90,14 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
     q = qtype_of(qtype)
     has_bias = op.endswith("_bias")
     dual_act = op[len("dual_gemm_rcr_"):] if op.startswith("dual_gemm_rcr_") else None
+    family, _, config = variant.partition(":")
+    tag = family + (f"_c{config}" if config else "")
+    tuning = dict(_B200_TUNING[family])
+    if config:
+        tuning.update(STREAM_CONFIGS[int(config)], config=int(config))
     cand = {
-        "candidate_id": f"b200_gguf_{q.symbol}_{dtype}_{variant}_v1",
-        "symbol_id": f"{q.symbol}_{variant}_v1",
+        "candidate_id": f"b200_gguf_{q.symbol}_{dtype}_{tag}_v1",
+        "symbol_id": f"{q.symbol}_{tag}_v1",
         "provider": KERNEL_LIBRARY, "family": "gemm", "op": op, "dtype": dtype, "qtype": q.name,
         "layouts": {"a": "row", "b": "column", "c": "row"},
         "epilogue": "linear_combination_bias" if has_bias else "linear_combination",
@@ -79,10 +107,11 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
         "accumulator_dtype": "float32", "optional": variant != "simt",
         "launch_abi": "gguf_gemm_rcr_bias_v1" if has_bias else "gguf_gemm_rcr_v1",
         "split_k_values": [1], "split_k_default": 1, "supports_split_k": False, "workspace_nbytes": 0,
-        "b200": dict(_B200_TUNING[variant]),
-        "kernel_symbol": kernel_symbol(q.name, op, dtype, variant),
-        "profiler_symbol": kernel_symbol(q.name, "gemm_rcr", dtype, variant, profile=True),
-        "variant": variant, "variant_code": VARIANT_CODES[variant],
+        "b200": tuning,
+        # a tuning configuration has no symbol of its own: it is the generic entry point with its variant code
+        "kernel_symbol": "dinoml_b200_gguf_gemm_rcr" if config else kernel_symbol(q.name, op, dtype, family),
+        "profiler_symbol": "dinoml_profile_b200_gguf_gemm_rcr" if config else kernel_symbol(q.name, "gemm_rcr", dtype, family, profile=True),
+        "variant": variant, "variant_code": variant_code(variant),
     }
     if dual_act:      # one generic entry point (activation and variant are arguments); epilogue named as in the reference
         cand.update({"family": "dual_gemm", "layouts": {"a": "row", "b0": "column", "b1": "column", "c": "row"},

@@ -93,7 +93,7 @@ class PeerExchange:
         rc = lib.dinoml_b200_gguf_gemm_rcr_scatter(
             a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, self.local_slot().data_ptr(),
             self._peer_dst[(self.epoch + 1) & 1], self._n_peers, q.value, _native.DINO_DTYPE[str(a.dtype).replace("torch.", "")], m, n, k,
-            _native.VARIANTS[variant], torch.cuda.current_stream().cuda_stream)
+            _native.variant_code(variant), torch.cuda.current_stream().cuda_stream)
         _native.check(rc, "dinoml_b200_gguf_gemm_rcr_scatter")
 
     def _exchange(self, out, count):

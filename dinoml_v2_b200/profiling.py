@@ -128,7 +128,8 @@ def profile_artifact(artifact_dir: str | Path, *, shapes: Mapping[str, Sequence[
             x = (torch.randn(m, k, device=dev) * 0.125).to(getattr(torch, item["dtype"]))
             out = torch.empty(m, n, device=dev, dtype=x.dtype)
             for cand in item["candidates"]:
-                if not mf.variant_supports(cand["variant"], m):
+                # the library's own predicate for the whole problem (M range, K multiples, row alignment), not M alone
+                if not mf.variant_supports(cand["variant"], m, qtype=item["qtype"], dtype=item["dtype"], n=n, k=k):
                     continue
                 key = profile_key(manifest["target"], fp_key, item, cand, shape)
                 cached = cache.get(key, iterations, repeats) if cache else None

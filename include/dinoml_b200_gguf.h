@@ -33,13 +33,19 @@ extern "C" {
 #define DINOML_B200_API
 #endif
 
-/* Kernel variants of the fused gemm ("candidates" of provider b200_gguf_gemm). */
+/* Kernel variants of the fused gemm ("candidates" of provider b200_gguf_gemm).  A `variant` argument carries the
+ * family in its low byte and a tuning configuration of that family in the second byte (variant | config << 8); config 0
+ * is the family's default for the shape.  Configurations exist for STREAM (1 .. dinoml_b200_gguf_variant_configs(4)):
+ * consumer warps, ring slots and CTAs per SM of the persistent GEMV - the counterpart of the tile / stage / warp entries
+ * of the reference's CUTLASS catalogue (src/dinoml/kernels/providers/cutlass/gemm.py:19-127), ranked by the profiler. */
 enum DinoB200GgufVariant {
-  DINOML_B200_GGUF_VARIANT_AUTO = 0, /* shape-guarded dispatch: mma for M<=16, umma above, simt for float32 */
-  DINOML_B200_GGUF_VARIANT_SIMT = 1, /* CUDA-core warp-per-row, any dtype, any M */
-  DINOML_B200_GGUF_VARIANT_MMA = 2,  /* decode GEMV, M = 1..16, float16 / bfloat16 */
-  DINOML_B200_GGUF_VARIANT_UMMA = 3, /* prefill GEMM on tcgen05 / TMEM, float16 / bfloat16 */
+  DINOML_B200_GGUF_VARIANT_AUTO = 0,   /* shape-guarded dispatch: stream / mma for small M, umma above, simt for float32 */
+  DINOML_B200_GGUF_VARIANT_SIMT = 1,   /* CUDA-core warp-per-row, any dtype, any M */
+  DINOML_B200_GGUF_VARIANT_MMA = 2,    /* decode GEMV, one CTA per 16-row tile, M = 1..16, float16 / bfloat16 */
+  DINOML_B200_GGUF_VARIANT_UMMA = 3,   /* prefill GEMM on tcgen05 / TMEM, float16 / bfloat16 */
+  DINOML_B200_GGUF_VARIANT_STREAM = 4, /* persistent decode GEMV: bulk-copy (TMA) ring + mbarriers, M = 1..8 */
 };
+#define DINOML_B200_GGUF_VARIANT_CODE(family, config) ((family) | ((config) << 8))
 
 DINOML_B200_API int dinoml_b200_gguf_kernel_abi_version(void);
 
@@ -74,6 +80,12 @@ DINOML_B200_API size_t dinoml_b200_gguf_gemm_rcr_workspace(int qtype, int dtype,
 /* Which variant AUTO resolves to for a problem (the shape-guarded dispatch the reference emits as
  * if/else text, src/dinoml/lowering/ops/gemm.py:656-698). */
 DINOML_B200_API int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k);
+
+/* Number of tuning configurations of a variant family (0 for families that have none); valid config values are
+ * 1 .. that number.  Counterpart of the length of the reference's per-op candidate list. */
+DINOML_B200_API int dinoml_b200_gguf_variant_configs(int family);
+/* 1 if the family serves the problem (the predicate the dispatcher and the profiler filter candidates with), else 0. */
+DINOML_B200_API int dinoml_b200_gguf_variant_supports(int family, int qtype, int dtype, int m, int n, int k);
 
 /* ---- allocation-free prefill GEMM ---------------------------------------------------------------
  * No counterpart in the reference.  For callers that are not allowed to allocate device memory - a plugin running
@@ -151,8 +163,9 @@ DINOML_B200_API unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned i
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_bias_<dtype>_<variant>_v1(a, b_quant, bias, c, m, n, k, stream)
  *   float dinoml_profile_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, iterations, stream)
- * with <q> in {q8_0,q4_k,q6_k}, <dtype> in {float16,bfloat16,float32}, <variant> in {simt,mma,umma}
- * (mma / umma exist for float16 and bfloat16 only). */
+ * with <q> in {q8_0,q4_k,q6_k}, <dtype> in {float16,bfloat16,float32}, <variant> in {simt,mma,umma,stream}
+ * (mma / umma / stream exist for float16 and bfloat16 only; a symbol runs its family's default tuning configuration, the
+ * other configurations are reached through dinoml_b200_gguf_gemm_rcr with a variant code). */
 #define DINOML_B200_GGUF_DECLARE(q, dt, var)                                                                       \
   DINOML_B200_API int dinoml_b200_gguf_##q##_gemm_rcr_##dt##_##var##_v1(const void* a, const void* b_quant, void* c, int m, int n, \
                                                         int k, void* stream);                                      \
@@ -167,7 +180,9 @@ DINOML_B200_API unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned i
   DINOML_B200_GGUF_DECLARE(q, float16, mma)   \
   DINOML_B200_GGUF_DECLARE(q, bfloat16, mma)  \
   DINOML_B200_GGUF_DECLARE(q, float16, umma)  \
-  DINOML_B200_GGUF_DECLARE(q, bfloat16, umma)
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, umma) \
+  DINOML_B200_GGUF_DECLARE(q, float16, stream) \
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, stream)
 DINOML_B200_GGUF_DECLARE_Q(q8_0)
 DINOML_B200_GGUF_DECLARE_Q(q4_k)
 DINOML_B200_GGUF_DECLARE_Q(q6_k)

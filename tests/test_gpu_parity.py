@@ -368,3 +368,28 @@ def test_error_paths(dev):
         kernels.gemm_rcr(torch.randn(17, 256, device=dev, dtype=torch.bfloat16), blocks, "Q4_K", variant="mma")
     with pytest.raises(RuntimeError, match="unsupported dtype"):
         kernels.gemm_rcr(x.float(), blocks, "Q4_K", variant="mma")
+
+
+def test_umma_refuses_k_that_is_not_a_multiple_of_256(dev):
+    """Q8_0 only needs K % 32 == 0, but the tcgen05 kernel walks whole 256-weight super-blocks: asking for it explicitly with
+    K = 288 or 896 is refused (alignment code), not computed wrongly; so are the per-candidate symbol and the allocation-free
+    entry; the profiler's predicate says the same, and AUTO serves the shape on another variant."""
+    import ctypes
+
+    from dinoml_v2_b200 import _native, manifest as mf
+    lib = _native.lib()
+    for k in (288, 896):
+        m, n = 32, 64
+        bq = torch.from_numpy(S.random_blocks("Q8_0", n, k, seed=k)).to(dev)
+        x, xf = _activations(m, k, k + 1, "bfloat16", dev)
+        with pytest.raises(RuntimeError, match="alignment"):
+            kernels.gemm_rcr(x, bq, "Q8_0", variant="umma")
+        y = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        sym = _native.candidate_symbol("q8_0", "bfloat16", "umma")
+        assert sym(x.data_ptr(), bq.data_ptr(), y.data_ptr(), m, n, k, None) == 7
+        lib.dinoml_b200_gguf_gemm_rcr_prealloc.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 5 + [ctypes.c_void_p]
+        assert lib.dinoml_b200_gguf_gemm_rcr_prealloc(x.data_ptr(), bq.data_ptr(), None, y.data_ptr(), 8, 6, m, n, k, None) == 7
+        assert not mf.variant_supports("umma", m, qtype="Q8_0", dtype="bfloat16", n=n, k=k)
+        assert kernels.select_variant("Q8_0", "bfloat16", m, n, k) == "simt"
+        got = kernels.gemm_rcr(x, bq, "Q8_0")
+        _check(got, oracle.gemm_quant(xf, bq.cpu().numpy(), "Q8_0", n, k), "bfloat16", ("auto", k))

@@ -61,9 +61,17 @@ def test_gguf_file_round_trip_and_hint_validation(tmp_path):
         cs.materialize_gguf_encoded_constant(dml.gguf_constant(tmp_path / "m.gguf", "t.Q6_K", qtype="Q4_K"), "float16", (8, 512))
     with pytest.raises(ValueError, match="not found"):
         cs.materialize_gguf_encoded_constant(dml.gguf_constant(tmp_path / "m.gguf", "nope"), "float16", (8, 512))
+    # an independent reader (the `gguf` package) sees the same file: names, ggml types, shapes, data offsets and every byte
     gguf = pytest.importorskip("gguf")
     r = gguf.GGUFReader(str(tmp_path / "m.gguf"))
     assert {t.name for t in r.tensors} == {"t.Q8_0", "t.Q4_K", "t.Q6_K"}
+    with gguf_file.open_gguf(tmp_path / "m.gguf") as f:
+        for t in r.tensors:
+            info = f.get_tensor(t.name)
+            assert int(t.tensor_type) == info.qtype_value and t.tensor_type.name == info.qtype
+            assert tuple(int(d) for d in t.shape) == info.shape                     # both innermost-first
+            assert int(t.data_offset) == info.data_offset and int(t.n_bytes) == info.nbytes
+            assert np.array_equal(np.asarray(t.data).reshape(-1).view(np.uint8), np.frombuffer(f.read_tensor_bytes(info), np.uint8))
 
 
 def test_trace_produces_reference_shaped_ir(tmp_path):
@@ -102,7 +110,11 @@ def test_kernel_manifest_and_plan_text(tmp_path):
     man = mf.build_kernel_manifest(spec.graph, dml.Target().as_dict())
     item = man["required_kernels"][0]
     assert item["kernel_library"] == "b200_gguf_gemm" and item["qtype"] == "Q4_K" and man["session_resources"] == []
-    assert [c["variant"] for c in item["candidates"]] == ["simt", "mma", "umma"]
+    assert [c["variant"] for c in item["candidates"]] == ["simt", "mma", "umma", "stream:1", "stream:2", "stream:3", "stream:4"]
+    tuned = item["candidates"][-1]          # a tuning configuration is a candidate of its own: generic entry + variant code
+    assert tuned["variant_code"] == 4 | (4 << 8) and tuned["kernel_symbol"] == "dinoml_b200_gguf_gemm_rcr"
+    assert tuned["b200"]["ctas_per_sm"] == 2 and tuned["candidate_id"].endswith("stream_c4_v1")
+    assert len({c["candidate_config_key"] for c in item["candidates"]}) == len(item["candidates"])
     for key in ("candidate_id", "symbol_id", "provider", "family", "op", "dtype", "layouts", "epilogue", "accumulator_dtype",
                 "launch_abi", "kernel_symbol", "profiler_symbol", "candidate_config_key"):       # providers/cutlass/gemm.py:526-553
         assert key in item["candidates"][0]
@@ -245,7 +257,7 @@ def test_dual_gemm_trace_fuses_the_two_weights_and_compiles(tmp_path):
     art = dml.compile(spec, dml.Target("cuda"), tmp_path / "art")
     item = json.loads((art.path / "kernel_manifest.json").read_text())["required_kernels"][0]
     assert item["kernel_symbol"] == "dinoml_b200_gguf_dual_gemm_rcr" and not item["has_profiler"]
-    assert [cand["variant"] for cand in item["candidates"]] == ["mma", "umma"]
+    assert [cand["variant"] for cand in item["candidates"]] == ["mma", "umma", "stream:1", "stream:2", "stream:3", "stream:4"]
     assert item["candidates"][0]["epilogue"] == "left_silu_and_mul"
     plan = (art.path / "module_plan.txt").read_text()
     assert "node dual_gemm_rcr_silu x w_gate+w_up.rows8 - t0 0" in plan
@@ -253,3 +265,16 @@ def test_dual_gemm_trace_fuses_the_two_weights_and_compiles(tmp_path):
     consts["w_up"] = cs.GGUFConstant.from_blocks(S.random_blocks("Q6_K", n, k, 3), "Q6_K", (n, k), tensor="up")
     with pytest.raises(NotImplementedError):
         dml.trace(Gate(), inputs={"x": dml.TensorSpec([1, k], "bfloat16")}, constants=consts)
+
+
+def test_variant_predicate_is_the_librarys_own():
+    """Candidates are filtered with the native predicate for the whole problem, not by M alone (a Q8_0 weight whose K is a
+    multiple of 32 but not of 256 has no tensor-core variant; Q6_K rows must be 16-byte multiples for the tcgen05 kernel)."""
+    assert mf.variant_supports("umma", 32)                                             # M range only
+    assert not mf.variant_supports("umma", 32, qtype="Q8_0", dtype="bfloat16", n=64, k=288)
+    assert mf.variant_supports("umma", 32, qtype="Q8_0", dtype="bfloat16", n=64, k=512)
+    assert not mf.variant_supports("umma", 32, qtype="Q6_K", dtype="bfloat16", n=64, k=1024)
+    assert mf.variant_supports("stream:4", 8, qtype="Q4_K", dtype="float16", n=64, k=512)
+    assert not mf.variant_supports("stream:4", 9, qtype="Q4_K", dtype="float16", n=64, k=512)
+    assert not mf.variant_supports("mma", 4, qtype="Q4_K", dtype="float32", n=64, k=512)
+    assert mf.variant_code("stream:3") == 4 | (3 << 8) and mf.variant_code("umma") == 3
