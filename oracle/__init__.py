@@ -169,6 +169,27 @@ def max_errors(expected: np.ndarray, actual: np.ndarray) -> tuple[float, float, 
     return max_abs, rel, norm
 
 
+def dot_noise(a: np.ndarray, blocks: np.ndarray, qtype, k: int) -> np.ndarray:
+    """sqrt(sum_k (a[m,k] * w[n,k])^2) per output [m, n]: the scale of what rounding every weight (or product) by a
+    relative u adds to a dot product, u * dot_noise for independent roundings.  Tests use it as the element-wise noise
+    floor of kernels whose tensor-core operands are 16-bit (the reference's own CPU path multiplies weights rounded to
+    the storage dtype too, src/dinoml/constant_sources.py:72)."""
+    w = dequantize(blocks, qtype, k).astype(np.float64)
+    a = np.asarray(a, dtype=np.float64)
+    return np.sqrt((a * a) @ (w * w).T)
+
+
+OPERAND_ULP = {"bfloat16": 2.0 ** -8, "float16": 2.0 ** -11}
+
+
+def within_operand_noise(expected, actual, noise, dtype: str, tol: float, sigmas: float = 6.0) -> bool:
+    """|d| <= tol * max(1, |e|) + sigmas * ulp(dtype) * noise, element-wise: the reference harness metric
+    (tools/bench_ck_gguf_q8_gemm.hip:798-808) plus the noise floor of 16-bit operand rounding."""
+    e = np.asarray(expected, dtype=np.float64)
+    d = np.abs(e - np.asarray(actual, dtype=np.float64))
+    return bool(np.all(d <= tol * np.maximum(1.0, np.abs(e)) + sigmas * OPERAND_ULP[dtype] * np.asarray(noise)))
+
+
 def dual_gemm_quant(a, blocks0, blocks1, qtype, n: int, k: int, activation: str = "silu"):
     """CPU restatement of the reference's dual GEMM on dequantized weights
     (src/dinoml/lowering/ops/templates/dual_gemm_cpu.cpp.j2:52-75): two fp32-accumulated products, the left one through

@@ -101,7 +101,7 @@ def test_gemm_small_shapes(dev, qtype, dtype, variant):
         if kernels.select_variant(qtype, dtype, m, n, k) == "umma" and variant == "auto":
             # 16-bit operand tiles (weights rounded like the reference CPU path rounds them): normalised bar only
             _, _, norm = oracle.max_errors(ref, y.float().cpu().numpy())
-            assert norm <= 2e-2, (qtype, dtype, variant, m, n, k, norm)
+            assert norm <= TOL[dtype], (qtype, dtype, variant, m, n, k, norm)
         else:
             _check(y, ref, dtype, (qtype, dtype, variant, m, n, k))
 
@@ -203,10 +203,11 @@ def test_gemm_umma(dev, qtype, dtype):
         assert kernels.device_status() == 0, "a bounded device-side wait gave up"
         got = y.float().cpu().numpy()
         max_abs, rel, norm = oracle.max_errors(ref, got)
-        # operands are 16-bit (weights rounded like the reference CPU path rounds them): 2e-2 bar on the
-        # normalised error, and the reference harness rule for the element-wise one
-        assert norm <= 2e-2, (qtype, dtype, m, n, k, norm)
-        assert max_abs <= 1e-1 * max(1.0, float(np.abs(ref).max()) / 16) or rel <= 3e-2, (qtype, dtype, m, n, k, max_abs, rel)
+        # operands are 16-bit (weights rounded like the reference CPU path rounds them): the stated bars on the normalised
+        # error (2e-2 bfloat16, 1e-3 float16), and element-wise the reference harness metric above the operands' noise floor
+        assert norm <= TOL[dtype], (qtype, dtype, m, n, k, norm)
+        noise = oracle.dot_noise(xf, blocks, qtype, k)
+        assert oracle.within_operand_noise(ref, got, noise, dtype, TOL[dtype]), (qtype, dtype, m, n, k, max_abs, rel)
         # against bf16/f16-rounded weights (what the reference CPU path multiplies) the agreement is tighter
         code = {"float16": 1, "bfloat16": 2}[dtype]
         ref_r = oracle.gemm_quant(xf, blocks, qtype, n, k, round_w=code)

@@ -7,6 +7,7 @@ import pytest
 
 torch = pytest.importorskip("torch")
 
+import oracle                                                  # noqa: E402
 from dinoml_v2_b200 import _native, kernels, synthetic as S   # noqa: E402
 from dinoml_v2_b200.gguf_blocks import qtype_of                # noqa: E402
 
@@ -55,6 +56,20 @@ def test_scatter_gemv_full_size_shard_shapes():
             assert rc == 0, _native.last_error()
             torch.cuda.synchronize()
             assert torch.equal(dst[0].view(torch.int16), want.view(torch.int16)) and torch.equal(dst[1].view(torch.int16), want.view(torch.int16))
+            # the same shapes through the entry point the sharded FFN uses (variant chosen by shape: the persistent GEMV here),
+            # every destination against the CPU oracle on a sample of weight rows
+            dst2 = [torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(2)]
+            peers2 = (ctypes.c_void_p * 1)(dst2[1].data_ptr())
+            rc = lib.dinoml_b200_gguf_gemm_rcr_scatter(x.data_ptr(), w.data_ptr(), None, dst2[0].data_ptr(), peers2, 1, 12, BF16, m, n, k, 0, stream)
+            assert rc == 0, _native.last_error()
+            torch.cuda.synchronize()
+            assert kernels.device_status() == 0
+            rows = np.unique(np.r_[0:16, n // 2:n // 2 + 16, n - 16:n, np.random.default_rng(5).choice(n, 80, replace=False)])
+            ridx = torch.from_numpy(rows).to(dev)
+            ref = oracle.gemm_quant(x.float().cpu().numpy(), w[ridx].cpu().numpy(), "Q4_K", len(rows), k)
+            for t in (dst[0], dst2[0], dst2[1]):
+                _, rel, norm = oracle.max_errors(ref, t[:, ridx].float().cpu().numpy())
+                assert rel <= 2e-2 and norm <= 2e-2, (n, k, m, rel, norm)
 
 
 def test_scatter_gemm_umma_writes_every_destination():

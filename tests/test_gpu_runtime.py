@@ -1,4 +1,7 @@
 """GPU tests of the artifact / session path: compile -> load -> upload encoded constants -> run, against the oracle."""
+import json
+from pathlib import Path
+
 import numpy as np
 import pytest
 import torch
@@ -10,7 +13,7 @@ from dinoml_v2_b200 import gguf_file, profiling, synthetic as S
 pytestmark = pytest.mark.gpu
 
 
-def _artifact(tmp_path, qtype, n, k, dtype="bfloat16", bias=False, buckets=(1, 16, 64)):
+def _artifact(tmp_path, qtype, n, k, dtype="bfloat16", bias=False, buckets=(1, 16, 64), max_m=64):
     blocks = S.random_blocks(qtype, n, k, 7)
     gguf_file.write_gguf(tmp_path / "w.gguf", {"w": (qtype, (n, k), blocks)})
     lin = dml.nn.Linear(k, n, bias=bias, dtype=dtype)
@@ -19,7 +22,7 @@ def _artifact(tmp_path, qtype, n, k, dtype="bfloat16", bias=False, buckets=(1, 1
     if bias:
         bias_v = np.random.default_rng(3).standard_normal(n).astype(np.float32)
         consts["bias"] = bias_v
-    spec = dml.trace(lin, inputs={"x": dml.TensorSpec([dml.Dim("m", 1, 64, buckets=buckets), k], dtype)}, constants=consts)
+    spec = dml.trace(lin, inputs={"x": dml.TensorSpec([dml.Dim("m", 1, max_m, buckets=buckets), k], dtype)}, constants=consts)
     art = dml.compile(spec, dml.Target("cuda"), tmp_path / "art")
     return art, blocks, bias_v
 
@@ -140,7 +143,7 @@ def test_profile_then_execution_plan_dispatch(tmp_path):
     assert {r["shape"]["m"] for r in report["results"]} == {1, 32, 64}
     plan = profiling.build_execution_plan(report)
     sel = {s["shape"]["m"]: s["selected_candidate_id"] for s in plan["selections"]}
-    assert sel[1].endswith(("mma_v1", "simt_v1")) and sel[64].endswith(("umma_v1", "simt_v1"))
+    assert ("_stream_c" in sel[1] or sel[1].endswith(("mma_v1", "simt_v1"))) and sel[64].endswith(("umma_v1", "simt_v1"))
     again = profiling.profile_artifact(art.path, iterations=5, repeats=3, cache=cache)      # served from the SQLite cache
     assert [r["median_ms"] for r in again["results"]] == [r["median_ms"] for r in report["results"]]
     # re-compile with the plan: dispatch records reach the native module and results stay correct
@@ -160,3 +163,40 @@ def test_profile_then_execution_plan_dispatch(tmp_path):
         _, _, norm = oracle.max_errors(ref, y)
         assert norm <= 2e-2, (m, norm)
     mod.close()
+
+
+def test_profiled_plan_dispatches_several_tuning_configurations(tmp_path):
+    """The benchmark's decode weight (Q4_K [11008 x 4096]) profiled over M buckets 1 .. 2048: the plan ranks the tuning
+    configurations of the persistent GEMV next to the other variants per shape, the chosen variant codes (family | config
+    << 8) reach the native module as dispatch records, and the dispatched kernels give the oracle's results."""
+    n, k = 11008, 4096
+    art, blocks, _ = _artifact(tmp_path, "Q4_K", n, k, buckets=(1, 4, 16, 64, 512), max_m=2048)
+    report = profiling.profile_artifact(art.path, iterations=10, repeats=3)
+    timed = {(r["shape"]["m"], r["candidate_id"]) for r in report["results"]}
+    assert any("_stream_c" in cid for (m, cid) in timed if m == 4) and not any("_stream_c" in cid for (m, cid) in timed if m == 16)
+    plan = profiling.build_execution_plan(report)
+    chosen = {s["shape"]["m"]: s["selected_candidate_id"] for s in plan["selections"]}
+    assert set(chosen) == {1, 4, 16, 64, 512, 2048}
+    assert len(set(chosen.values())) >= 2 and chosen[2048].endswith("umma_v1")
+    gguf_path = tmp_path / "w.gguf"
+    lin = dml.nn.Linear(k, n, bias=False, dtype="bfloat16")
+    spec = dml.trace(lin, inputs={"x": dml.TensorSpec([dml.Dim("m", 1, 2048, buckets=(1, 4, 16, 64, 512)), k], "bfloat16")},
+                     constants={"weight": dml.gguf_constant(gguf_path, "w")})
+    art2 = dml.compile(spec, dml.Target("cuda"), tmp_path / "art2", execution_plan=plan)
+    text = (art2.path / "module_plan.txt").read_text()
+    codes = {int(line.split()[-1]) for line in text.splitlines() if line.startswith("dispatch ")}
+    assert len(codes) >= 2 and all((c & 0xff) in (1, 2, 3, 4) for c in codes)
+    mod = dml.runtime.load(art2.path)
+    mod.load_encoded_constants()
+    sess = mod.create_session()
+    rows = np.r_[0:32, n - 32:n]
+    for m in (1, 4, 16):
+        x = S.random_activations(m, k, 50 + m, "float32")
+        y = sess.run_numpy({"x": x})["t0"]
+        ref = oracle.gemm_quant(S.bf16_bits_to_float32(S.float32_to_bf16_bits(x)), blocks[rows], "Q4_K", len(rows), k)
+        _, _, norm = oracle.max_errors(ref, y[:, rows])
+        assert norm <= 2e-2, (m, norm)
+    mod.close()
+    out = Path(__file__).resolve().parent.parent / "gpurun_out"
+    if out.is_dir():                                    # keep the selection next to the other GPU-run outputs
+        (out / "plan_cfg2.json").write_text(json.dumps(chosen, indent=1))

@@ -11,6 +11,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from dinoml_v2_b200 import _native, synthetic as S
 from dinoml_v2_b200.gguf_blocks import qtype_of
 
@@ -25,13 +26,15 @@ def _entry_points():
     lib.dinoml_b200_gguf_gemm_rcr_prealloc.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp]
     lib.dinoml_b200_gguf_gemm_rcr_prealloc.restype = ci
     lib.dinoml_b200_gguf_prealloc_scratch_bytes.restype = ctypes.c_size_t
+    lib.dinoml_b200_gguf_gemm_rcr_workspace.restype = ctypes.c_size_t
     return lib
 
 
 def _run_pair(lib, qtype, m, n, k, seed, bias):
     dev = torch.device("cuda:0")
     q = qtype_of(qtype)
-    w = torch.from_numpy(S.random_blocks(qtype, n, k, seed)).to(dev)
+    blocks = S.random_blocks(qtype, n, k, seed)
+    w = torch.from_numpy(blocks).to(dev)
     x = torch.from_numpy(S.random_activations(m, k, seed + 1, "float32")).to(dev).to(torch.bfloat16)
     b = torch.randn(n, device=dev).to(torch.bfloat16) if bias else None
     want = torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16)
@@ -39,10 +42,23 @@ def _run_pair(lib, qtype, m, n, k, seed, bias):
     stream = torch.cuda.current_stream().cuda_stream
     bp = b.data_ptr() if b is not None else None
     assert lib.dinoml_b200_gguf_gemm_rcr(x.data_ptr(), w.data_ptr(), bp, want.data_ptr(), q.value, BF16, m, n, k, UMMA, stream) == 0
+    torch.cuda.synchronize()
+    # "allocates nothing": the driver's free-memory figure is the same before and after the call, although this shape
+    # needs partial-tile scratch (the ordinary entry point grows a cudaMalloc'ed workspace for it)
+    need = lib.dinoml_b200_gguf_gemm_rcr_workspace(q.value, BF16, m, n, k, UMMA)
+    assert need > 0
+    free_before = torch.cuda.mem_get_info()[0]
     rc = lib.dinoml_b200_gguf_gemm_rcr_prealloc(x.data_ptr(), w.data_ptr(), bp, got.data_ptr(), q.value, BF16, m, n, k, stream)
     assert rc == 0, _native.last_error()
     torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
     assert lib.dinoml_b200_gguf_device_status() == 0
+    # against the CPU oracle too, not only against the sibling entry point
+    ref = oracle.gemm_quant(x.float().cpu().numpy(), blocks, qtype, n, k)
+    if b is not None:
+        ref = ref + b.float().cpu().numpy()
+    _, _, norm_oracle = oracle.max_errors(ref, got.float().cpu().numpy())
+    assert norm_oracle <= 2e-2, (qtype, m, n, k, norm_oracle)
     a, e = got.float().cpu().numpy(), want.float().cpu().numpy()
     assert np.isfinite(a).all() and np.isfinite(e).all()
     norm = float(np.abs(a - e).max() / max(np.abs(e).max(), 1e-30))
