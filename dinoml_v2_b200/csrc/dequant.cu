@@ -200,11 +200,17 @@ int dequantize_rows(const void* dev_in, int64_t qtype, int64_t rows, int64_t n_p
   if (bs == 0) return RC_QTYPE;
   if (n_per_row % bs) return RC_KBLOCK;
   const uintptr_t in_a = reinterpret_cast<uintptr_t>(dev_in), out_a = reinterpret_cast<uintptr_t>(dev_out);
-  if ((in_a & (qtype == QTYPE_Q4_K ? 3 : 1)) || (out_a & 15)) return RC_ALIGN;
+  if ((in_a & uintptr_t(qtype_alignment(qtype) - 1)) || (out_a & 15)) return RC_ALIGN;
   switch (qtype) {
     case QTYPE_Q8_0: return launch_dequant_dtype<QTYPE_Q8_0>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
     case QTYPE_Q4_K: return launch_dequant_dtype<QTYPE_Q4_K>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
     case QTYPE_Q6_K: return launch_dequant_dtype<QTYPE_Q6_K>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
+    case QTYPE_Q4_0: return launch_dequant_dtype<QTYPE_Q4_0>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
+    case QTYPE_Q5_K: return launch_dequant_dtype<QTYPE_Q5_K>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
+    case QTYPE_Q2_K: return launch_dequant_dtype<QTYPE_Q2_K>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
+    case QTYPE_Q3_K: return launch_dequant_dtype<QTYPE_Q3_K>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
+    case QTYPE_MXFP4: return launch_dequant_dtype<QTYPE_MXFP4>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
+    case QTYPE_NVFP4: return launch_dequant_dtype<QTYPE_NVFP4>(dev_in, dev_out, rows, n_per_row, output_dtype, stream);
     default: return RC_QTYPE;
   }
 }

@@ -120,7 +120,8 @@ int check_gemm_args(const void* a, const void* b, const void* c, int qtype, int 
   if (dtype != DINO_F32 && dtype != DINO_F16 && dtype != DINO_BF16) return RC_DTYPE;
   const uintptr_t aa = reinterpret_cast<uintptr_t>(a), ba = reinterpret_cast<uintptr_t>(b);
   const int64_t row_bytes = int64_t(k / bs) * qtype_block_bytes(qtype);
-  if ((aa & 15) || (ba & (qtype == QTYPE_Q4_K ? 3 : 1)) || (qtype == QTYPE_Q4_K && (row_bytes & 3))) return RC_ALIGN;
+  const uintptr_t wmask = uintptr_t(qtype_alignment(qtype) - 1);
+  if ((aa & 15) || (ba & wmask) || (uintptr_t(row_bytes) & wmask)) return RC_ALIGN;
   return RC_OK;
 }
 
@@ -131,6 +132,12 @@ int gemm_rcr_simt(const void* a, const void* b, const void* bias, void* c, int q
     case QTYPE_Q8_0: return launch_simt_q<QTYPE_Q8_0>(a, b, bias, c, dtype, m, n, k, s);
     case QTYPE_Q4_K: return launch_simt_q<QTYPE_Q4_K>(a, b, bias, c, dtype, m, n, k, s);
     case QTYPE_Q6_K: return launch_simt_q<QTYPE_Q6_K>(a, b, bias, c, dtype, m, n, k, s);
+    case QTYPE_Q4_0: return launch_simt_q<QTYPE_Q4_0>(a, b, bias, c, dtype, m, n, k, s);
+    case QTYPE_Q5_K: return launch_simt_q<QTYPE_Q5_K>(a, b, bias, c, dtype, m, n, k, s);
+    case QTYPE_Q2_K: return launch_simt_q<QTYPE_Q2_K>(a, b, bias, c, dtype, m, n, k, s);
+    case QTYPE_Q3_K: return launch_simt_q<QTYPE_Q3_K>(a, b, bias, c, dtype, m, n, k, s);
+    case QTYPE_MXFP4: return launch_simt_q<QTYPE_MXFP4>(a, b, bias, c, dtype, m, n, k, s);
+    case QTYPE_NVFP4: return launch_simt_q<QTYPE_NVFP4>(a, b, bias, c, dtype, m, n, k, s);
     default: return RC_QTYPE;
   }
 }

@@ -1,7 +1,9 @@
-"""GGUF block-layout tables for the three quantization types on the hot path.
+"""GGUF block-layout tables: the three quantization types of the benchmark configurations (Q8_0, Q4_K, Q6_K) and the six
+further ones the reference's fused prototype decodes (Q4_0, Q5_K, Q2_K, Q3_K, MXFP4, NVFP4).
 
 The byte layouts are the ones the reference declares in
-kernels/rocm/src/ck_gguf_q8_gemm.hip:20-25 (Q8_0), :34-41 (Q4_K), :71-78 (Q6_K);
+kernels/rocm/src/ck_gguf_q8_gemm.hip:20-25 (Q8_0), :27-32 (Q4_0), :34-41 (Q4_K), :43-51 (Q5_K), :53-60 (Q2_K),
+:62-69 (Q3_K), :71-78 (Q6_K), :80-85 (MXFP4), :87-92 (NVFP4);
 `qtype_value` is the ggml type id the reference records in constant storage
 metadata (src/dinoml/constant_sources.py:88-108).
 """
@@ -12,7 +14,7 @@ from dataclasses import dataclass
 
 @dataclass(frozen=True)
 class QType:
-    name: str          # "Q8_0" | "Q4_K" | "Q6_K"
+    name: str          # "Q8_0", "Q4_K", ...
     value: int         # ggml enum
     block_size: int    # weights per block
     block_bytes: int   # bytes per block
@@ -22,8 +24,16 @@ class QType:
 Q8_0 = QType("Q8_0", 8, 32, 34, "q8_0")
 Q4_K = QType("Q4_K", 12, 256, 144, "q4_k")
 Q6_K = QType("Q6_K", 14, 256, 210, "q6_k")
+Q4_0 = QType("Q4_0", 2, 32, 18, "q4_0")
+Q2_K = QType("Q2_K", 10, 256, 84, "q2_k")
+Q3_K = QType("Q3_K", 11, 256, 110, "q3_k")
+Q5_K = QType("Q5_K", 13, 256, 176, "q5_k")
+MXFP4 = QType("MXFP4", 39, 32, 17, "mxfp4")
+NVFP4 = QType("NVFP4", 40, 64, 36, "nvfp4")
 
-QTYPES = {q.name: q for q in (Q8_0, Q4_K, Q6_K)}
+QTYPES = {q.name: q for q in (Q8_0, Q4_K, Q6_K, Q4_0, Q5_K, Q2_K, Q3_K, MXFP4, NVFP4)}
+# the types with tensor-core kernels (decode GEMV + tcgen05 GEMM); the others run on the CUDA-core kernel
+TENSOR_CORE_QTYPES = ("Q8_0", "Q4_K", "Q6_K")
 QTYPES_BY_VALUE = {q.value: q for q in QTYPES.values()}
 
 

@@ -23,8 +23,9 @@ DEFAULT_ALIGNMENT = 32
 
 # ggml type id -> (name, block size, block bytes)
 GGML_TYPES = {
-    0: ("F32", 1, 4), 1: ("F16", 1, 2), 8: ("Q8_0", 32, 34), 12: ("Q4_K", 256, 144), 14: ("Q6_K", 256, 210),
-    30: ("BF16", 1, 2),
+    0: ("F32", 1, 4), 1: ("F16", 1, 2), 2: ("Q4_0", 32, 18), 8: ("Q8_0", 32, 34), 10: ("Q2_K", 256, 84), 11: ("Q3_K", 256, 110),
+    12: ("Q4_K", 256, 144), 13: ("Q5_K", 256, 176), 14: ("Q6_K", 256, 210), 30: ("BF16", 1, 2), 39: ("MXFP4", 32, 17),
+    40: ("NVFP4", 64, 36),
 }
 _TYPE_ID = {name: tid for tid, (name, _, _) in GGML_TYPES.items()}
 

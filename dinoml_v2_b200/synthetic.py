@@ -12,6 +12,10 @@ sizes and per-field distributions of the Llama-shaped configurations:
   kernels/rocm/src/ck_gguf_q8_gemm.hip:924-938, ``scales ~ U{-64..63}``,
   ``d = fp16(|N(0,1)| * 0.002)``
 
+* Q4_0, Q5_K, Q2_K, Q3_K, MXFP4, NVFP4 (not in the benchmark configurations): every packed field uniform random bytes, as
+  the reference's bench tool fills them (tools/bench_ck_gguf_q8_gemm.hip:2191-2345), fp16 scales ``fp16(|N(0,1)| * c)``,
+  the MXFP4 exponent byte ``~ U{117..122}`` and the NVFP4 ue4m3 scale bytes ``~ U{32..48}`` (the tool's ranges)
+
 `pack_*` take explicit field arrays (used by tests for edge cases), `random_*`
 draw them from ``numpy.random.Generator(PCG64(seed))``.  `random_blocks_torch`
 produces the same distributions directly on a CUDA device for multi-GB cases.
@@ -22,7 +26,9 @@ import numpy as np
 
 from .gguf_blocks import Q4_K, Q6_K, Q8_0, qtype_of, row_bytes
 
-D_SCALE = {"Q8_0": 0.01, "Q4_K": 0.005, "Q6_K": 0.002}
+D_SCALE = {"Q8_0": 0.01, "Q4_K": 0.005, "Q6_K": 0.002, "Q4_0": 0.01, "Q5_K": 0.003, "Q2_K": 0.005, "Q3_K": 0.005}
+# byte offsets of the fp16 scale fields (d, then dmin where the layout has one) inside a block of the further types
+_HALF_FIELDS = {"Q4_0": (0,), "Q5_K": (0, 2), "Q2_K": (80, 82), "Q3_K": (108,)}
 
 
 def _rng(seed) -> np.random.Generator:
@@ -108,8 +114,15 @@ def random_blocks(qtype, rows: int, n_per_row: int, seed) -> np.ndarray:
         blocks = pack_q6_k(_half_scale(rng, shape, D_SCALE["Q6_K"]),
                            rng.integers(-64, 64, size=shape + (16,), dtype=np.int8),
                            rng.integers(0, 64, size=shape + (256,), dtype=np.uint8))
-    else:  # pragma: no cover - qtype_of already rejects
-        raise ValueError(q)
+    else:
+        blocks = rng.integers(0, 256, size=shape + (q.block_bytes,), dtype=np.uint8)
+        if q.name == "MXFP4":
+            blocks[..., 0] = rng.integers(117, 123, size=shape, dtype=np.uint8)
+        elif q.name == "NVFP4":
+            blocks[..., 0:4] = rng.integers(32, 49, size=shape + (4,), dtype=np.uint8)
+        else:
+            for off in _HALF_FIELDS[q.name]:
+                blocks[..., off:off + 2] = _half_scale(rng, shape, D_SCALE[q.name])[..., None].view(np.uint8)
     return np.ascontiguousarray(blocks.reshape(rows, rb))
 
 
@@ -163,6 +176,13 @@ def random_blocks_torch(qtype, rows: int, n_per_row: int, seed: int, device):
     elif q is Q4_K:
         blocks[..., 0:2] = half_bytes(D_SCALE["Q4_K"])
         blocks[..., 2:4] = half_bytes(D_SCALE["Q4_K"])
+    elif q.name == "MXFP4":
+        blocks[..., 0] = torch.randint(117, 123, (rows, nb), dtype=torch.uint8, device=device, generator=g)
+    elif q.name == "NVFP4":
+        blocks[..., 0:4] = torch.randint(32, 49, (rows, nb, 4), dtype=torch.uint8, device=device, generator=g)
+    elif q.name in _HALF_FIELDS:
+        for off in _HALF_FIELDS[q.name]:
+            blocks[..., off:off + 2] = half_bytes(D_SCALE[q.name])
     else:
         sc = torch.randint(-64, 64, (rows, nb, 16), dtype=torch.int8, device=device, generator=g)
         blocks[..., 192:208] = sc.view(torch.uint8)

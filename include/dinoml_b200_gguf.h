@@ -11,7 +11,8 @@
  * dino_get_last_error().
  *
  * qtype is the ggml type id the reference stores as `qtype_value` (Q8_0 = 8, Q4_K = 12, Q6_K = 14;
- * src/dinoml/constant_sources.py:88-108).  dtype is a DinoDtype (float16 = 1, float32 = 2,
+ * src/dinoml/constant_sources.py:88-108; also Q4_0 = 2, Q2_K = 10, Q3_K = 11, Q5_K = 13, MXFP4 = 39, NVFP4 = 40, which the
+ * dequantizer and the CUDA-core gemm variant decode).  dtype is a DinoDtype (float16 = 1, float32 = 2,
  * bfloat16 = 6; runtime/include/dinoml/abi.h:14-23).  Activations, bias and output share one dtype,
  * as gemm_rcr requires (src/dinoml/ops/gemm.py:46-60).
  */
@@ -163,7 +164,7 @@ DINOML_B200_API unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned i
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_bias_<dtype>_<variant>_v1(a, b_quant, bias, c, m, n, k, stream)
  *   float dinoml_profile_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, iterations, stream)
- * with <q> in {q8_0,q4_k,q6_k}, <dtype> in {float16,bfloat16,float32}, <variant> in {simt,mma,umma,stream}
+ * with <q> in {q8_0,q4_k,q6_k} (and the simt symbols of q4_0,q5_k,q2_k,q3_k,mxfp4,nvfp4), <dtype> in {float16,bfloat16,float32}, <variant> in {simt,mma,umma,stream}
  * (mma / umma / stream exist for float16 and bfloat16 only; a symbol runs its family's default tuning configuration, the
  * other configurations are reached through dinoml_b200_gguf_gemm_rcr with a variant code). */
 #define DINOML_B200_GGUF_DECLARE(q, dt, var)                                                                       \
@@ -186,6 +187,18 @@ DINOML_B200_API unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned i
 DINOML_B200_GGUF_DECLARE_Q(q8_0)
 DINOML_B200_GGUF_DECLARE_Q(q4_k)
 DINOML_B200_GGUF_DECLARE_Q(q6_k)
+/* The six further types of the reference's fused prototype (kernels/rocm/src/ck_gguf_q8_gemm.hip:27-32, 43-69, 80-92; symbol
+ * family :1910-1940 per type): dequantize bit-exact, fused gemm on the CUDA-core variant only. */
+#define DINOML_B200_GGUF_DECLARE_SIMT_Q(q)    \
+  DINOML_B200_GGUF_DECLARE(q, float32, simt)  \
+  DINOML_B200_GGUF_DECLARE(q, float16, simt)  \
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, simt)
+DINOML_B200_GGUF_DECLARE_SIMT_Q(q4_0)
+DINOML_B200_GGUF_DECLARE_SIMT_Q(q5_k)
+DINOML_B200_GGUF_DECLARE_SIMT_Q(q2_k)
+DINOML_B200_GGUF_DECLARE_SIMT_Q(q3_k)
+DINOML_B200_GGUF_DECLARE_SIMT_Q(mxfp4)
+DINOML_B200_GGUF_DECLARE_SIMT_Q(nvfp4)
 
 /* Last error message of the calling thread ("" if none); same contract as the reference's
  * dino_get_last_error (runtime/src/runtime_common.cpp:5-20). */

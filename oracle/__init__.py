@@ -29,8 +29,8 @@ _HERE = Path(__file__).resolve().parent
 _LIB_PATH = _HERE / "libgguf_oracle.so"
 _lib = None
 
-QTYPE_VALUE = {"Q8_0": 8, "Q4_K": 12, "Q6_K": 14}
-BLOCK = {8: (32, 34), 12: (256, 144), 14: (256, 210)}
+QTYPE_VALUE = {"Q4_0": 2, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "MXFP4": 39, "NVFP4": 40}
+BLOCK = {2: (32, 18), 8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210), 39: (32, 17), 40: (64, 36)}
 DTYPE_CODE = {"float32": 0, "float16": 1, "bfloat16": 2}
 
 

@@ -32,6 +32,7 @@ sys.path.insert(0, str(ROOT))
 
 import oracle  # noqa: E402
 from dinoml_v2_b200 import synthetic as S  # noqa: E402
+from oracle import build_ref  # noqa: E402
 
 F16_EDGE = np.array([0x0000, 0x0001, 0x03FF, 0x0400, 0x7BFF, 0x8001, 0xBC00, 0x3C00], dtype=np.uint16).view(np.float16)
 
@@ -63,24 +64,59 @@ def edge_blocks(qtype: str) -> np.ndarray:
         scales[2], q[2] = -128, 0
         scales[3] = -128
         return S.pack_q6_k(F16_EDGE, scales, q).reshape(1, -1)
-    raise ValueError(qtype)
+    # the further types: random bytes everywhere, then the edge scales and extreme quant fields in the first blocks
+    q = S.qtype_of(qtype)
+    blocks = rng.integers(0, 256, size=(n, q.block_bytes), dtype=np.uint8)
+    if qtype == "MXFP4":
+        blocks[:, 0] = np.array([0, 1, 2, 117, 127, 200, 254, 255], dtype=np.uint8)      # e8m0 exponents incl. the two sub-2 cases
+        blocks[0, 1:] = 0x00
+        blocks[1, 1:] = 0xFF
+        blocks[2, 1:] = 0x7F
+    elif qtype == "NVFP4":
+        blocks[:, 0:4] = np.array([[0x00, 0x7F, 0x01, 0x07], [0x08, 0x38, 0x7E, 0xFF], [0x80, 0x47, 0x20, 0x30]] + [[32, 40, 48, 56]] * 5,
+                                  dtype=np.uint8)
+        blocks[0, 4:] = 0x00
+        blocks[1, 4:] = 0xFF
+    else:
+        for off in S._HALF_FIELDS[qtype]:
+            blocks[:, off:off + 2] = F16_EDGE[:, None].view(np.uint8)
+        lo = {"Q4_0": 2, "Q5_K": 4, "Q2_K": 0, "Q3_K": 0}[qtype]
+        hi = {"Q4_0": 18, "Q5_K": 176, "Q2_K": 80, "Q3_K": 108}[qtype]
+        blocks[0, lo:hi] = 0x00
+        blocks[1, lo:hi] = 0xFF
+    return blocks.reshape(1, -1)
+
+
+def reference_host_dequantize(blocks: np.ndarray, qtype: str, k: int):
+    """The reference's own `<qtype>_value_host` functions (oracle/_ref/libref_gguf_host.so, built by oracle/build_ref.py), or None."""
+    import ctypes
+    path = ROOT / "oracle" / "_ref" / "libref_gguf_host.so"
+    if not path.exists():
+        return None
+    lib = ctypes.CDLL(str(path))
+    out = np.empty((blocks.shape[0], k), dtype=np.float32)
+    rc = lib.ref_gguf_dequantize_rows(blocks.ctypes.data_as(ctypes.c_void_p), oracle.QTYPE_VALUE[qtype], ctypes.c_int64(blocks.shape[0]),
+                                      ctypes.c_int64(k), out.ctypes.data_as(ctypes.c_void_p))
+    assert rc == 0, rc
+    return out
 
 
 def make_dequant_kat() -> None:
     import gguf
     from gguf import GGMLQuantizationType as T
 
-    gg = {"Q8_0": T.Q8_0, "Q4_K": T.Q4_K, "Q6_K": T.Q6_K}
     out = {}
-    for i, qtype in enumerate(("Q8_0", "Q4_K", "Q6_K")):
+    for i, qtype in enumerate(("Q8_0", "Q4_K", "Q6_K", "Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4")):
         bs = oracle.BLOCK[oracle.QTYPE_VALUE[qtype]][0]
         k = 8 * bs
         blocks = np.concatenate([edge_blocks(qtype), S.random_blocks(qtype, 3, k, seed=4100 + i)], axis=0)
         w = oracle.dequantize(blocks, qtype, k, "float32")
-        w_np = oracle.dequantize_numpy(blocks, qtype, k)
-        w_gg = gguf.quants.dequantize(blocks, gg[qtype]).astype(np.float32)
-        assert np.array_equal(w.view(np.uint32), w_np.view(np.uint32)), qtype
+        w_gg = gguf.quants.dequantize(blocks, getattr(T, qtype)).astype(np.float32)
+        if qtype in ("Q8_0", "Q4_K", "Q6_K"):
+            assert np.array_equal(w.view(np.uint32), oracle.dequantize_numpy(blocks, qtype, k).view(np.uint32)), qtype
         assert np.array_equal(w.view(np.uint32), w_gg.view(np.uint32)), qtype
+        ref = reference_host_dequantize(blocks, qtype, k)
+        assert ref is None or np.array_equal(w.view(np.uint32), ref.view(np.uint32)), qtype
         out[f"{qtype}_blocks"] = blocks
         out[f"{qtype}_n_per_row"] = np.int64(k)
         out[f"{qtype}_f32_bits"] = w.view(np.uint32)
@@ -127,6 +163,8 @@ def make_gemm_golden(reference: Path) -> None:
         ("Q6_K", "bfloat16", 4, 24, 768),
         ("Q6_K", "float32", 2, 24, 512),
         ("Q4_K", "float16", 2, 32, 512),
+        ("Q4_K", "bfloat16", 4, 512, 4096),
+        ("Q6_K", "bfloat16", 64, 256, 2048),
     ]
     out = {"cases": np.array(["|".join(map(str, c)) for c in cases])}
     with tempfile.TemporaryDirectory() as tmp:
@@ -160,5 +198,6 @@ def make_gemm_golden(reference: Path) -> None:
 
 if __name__ == "__main__":
     ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(os.environ.get("DINOML_REFERENCE_DIR", os.sep + os.path.join("root", "reference")))
+    build_ref.build(ref)                      # the reference-authored decode functions the vectors are checked against
     make_dequant_kat()
     make_gemm_golden(ref)

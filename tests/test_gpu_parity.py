@@ -15,6 +15,7 @@ from dinoml_v2_b200.gguf_blocks import qtype_of
 pytestmark = pytest.mark.gpu
 
 QT = ("Q8_0", "Q4_K", "Q6_K")
+QT_MORE = ("Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4")     # decoded by the dequantizer and the CUDA-core gemm variant
 TOL = {"float32": 1e-3, "float16": 1e-3, "bfloat16": 2e-2}
 TDT = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
 
@@ -31,7 +32,7 @@ def _bits(t: torch.Tensor) -> np.ndarray:
     return t.view(torch.int16).cpu().numpy().view(np.uint16)
 
 
-@pytest.mark.parametrize("qtype", QT)
+@pytest.mark.parametrize("qtype", QT + QT_MORE)
 def test_dequant_golden_bit_exact(dev, golden_dir, qtype):
     kat = np.load(golden_dir / "gguf_dequant_kat.npz")
     blocks = torch.from_numpy(kat[f"{qtype}_blocks"]).to(dev)
@@ -41,7 +42,7 @@ def test_dequant_golden_bit_exact(dev, golden_dir, qtype):
         assert np.array_equal(_bits(got), kat[f"{qtype}_{key}"]), (qtype, dtype)
 
 
-@pytest.mark.parametrize("qtype", QT)
+@pytest.mark.parametrize("qtype", QT + QT_MORE)
 @pytest.mark.parametrize("rows,nblk", [(1, 1), (3, 5), (257, 7), (64, 16)])
 def test_dequant_random_bit_exact(dev, qtype, rows, nblk):
     k = nblk * qtype_of(qtype).block_size
@@ -66,6 +67,42 @@ def test_dequant_full_size_checksum(dev):
     assert torch.equal(got.view(torch.int32), again.view(torch.int32))
     want_all = oracle.dequantize(blocks, "Q4_K", k)
     assert int(got.view(torch.int32).to(torch.int64).sum().item()) == int(want_all.view(np.int32).astype(np.int64).sum())
+
+
+@pytest.mark.parametrize("qtype", QT_MORE)
+def test_dequant_random_bytes_bit_exact(dev, qtype):
+    """Blocks of uniformly random BYTES: every scale bit pattern (NaN, Inf, subnormals) and every packed field value;
+    compared as bit patterns, at an odd device address for the types that need no alignment."""
+    q = qtype_of(qtype)
+    k = 5 * q.block_size
+    raw = np.random.default_rng(31).integers(0, 256, (37, 5 * q.block_bytes), dtype=np.uint8)
+    want = oracle.dequantize(raw, qtype, k)
+    got = kernels.dequantize_rows(torch.from_numpy(raw).to(dev), qtype, k, "float32")
+    a, b = _bits(got), want.view(np.uint32)
+    nan = np.isnan(want)
+    assert np.array_equal(a[~nan], b[~nan]) and np.isnan(got.cpu().numpy()[nan]).all(), qtype
+    if qtype == "MXFP4":                                 # 17-byte blocks: any byte address is legal
+        pad = torch.zeros(raw.size + 1, dtype=torch.uint8, device=dev)
+        pad[1:] = torch.from_numpy(raw.reshape(-1)).to(dev)
+        got2 = kernels.dequantize_rows(pad[1:].view(37, -1), qtype, k, "float32")
+        assert torch.equal(got2.view(torch.int32), got.view(torch.int32))
+
+
+@pytest.mark.parametrize("qtype", QT_MORE)
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+def test_gemm_further_qtypes(dev, qtype, dtype):
+    """Fused gemm on the six further types (CUDA-core variant, every dtype, small and mid M, with bias) against the oracle."""
+    q = qtype_of(qtype)
+    for (m, n, k) in [(1, 16, 256), (1, 1000, 1024), (3, 33, 512), (4, 64, 2048), (17, 24, 768), (64, 40, 512)]:
+        assert kernels.select_variant(qtype, dtype, m, n, k) == "simt"
+        blocks = S.random_blocks(qtype, n, k, seed=3100 + m + n)
+        x, xf = _activations(m, k, 3200 + m, dtype, dev)
+        bias = torch.randn(n, device=dev).to(TDT[dtype])
+        ref = oracle.gemm_quant(xf, blocks, qtype, n, k) + bias.float().cpu().numpy()
+        y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), qtype, bias)
+        _check(y, ref, dtype, (qtype, dtype, m, n, k))
+    with pytest.raises(RuntimeError):                   # no tensor-core variant for these types
+        kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), qtype, variant="mma")
 
 
 def _activations(m, k, seed, dtype, dev):

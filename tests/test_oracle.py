@@ -7,7 +7,8 @@ import oracle
 from dinoml_v2_b200 import synthetic as S
 from dinoml_v2_b200.gguf_blocks import QTYPES, encoded_nbytes, qtype_of, row_bytes
 
-QT = ("Q8_0", "Q4_K", "Q6_K")
+QT3 = ("Q8_0", "Q4_K", "Q6_K")                                  # the benchmark types (they also have a numpy twin)
+QT = QT3 + ("Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4")     # + the six further types of the reference prototype
 
 
 @pytest.fixture(scope="module")
@@ -23,7 +24,10 @@ def gemm_golden(golden_dir):
 def test_block_tables_match_reference_struct_sizes():
     # sizes pinned by the reference's own test, tests/backends/test_ck_gguf_q8_gemm_kernel.py:59,82-89
     assert (QTYPES["Q8_0"].block_bytes, QTYPES["Q4_K"].block_bytes, QTYPES["Q6_K"].block_bytes) == (34, 144, 210)
-    assert [QTYPES[q].value for q in QT] == [8, 12, 14]
+    assert [QTYPES[q].value for q in QT] == [8, 12, 14, 2, 13, 10, 11, 39, 40]
+    # tools/bench_ck_gguf_q8_gemm.hip:39,46,55,65,74,83,92,99,106 (static_asserts on the block structs)
+    assert [QTYPES[q].block_bytes for q in QT] == [34, 144, 210, 18, 176, 84, 110, 17, 36]
+    assert [QTYPES[q].block_size for q in QT] == [32, 256, 256, 32, 256, 256, 256, 32, 64]
     assert row_bytes("Q4_K", 4096) == 2304 and row_bytes("Q6_K", 14336) == 11760 and row_bytes("Q8_0", 4096) == 4352
     assert encoded_nbytes("Q4_K", 11008, 4096) == 25_362_432
     assert encoded_nbytes("Q6_K", 4096, 14336) == 48_168_960
@@ -31,7 +35,7 @@ def test_block_tables_match_reference_struct_sizes():
     with pytest.raises(ValueError):
         row_bytes("Q4_K", 4000)
     with pytest.raises(ValueError):
-        qtype_of("Q5_K")
+        qtype_of("IQ4_XS")
 
 
 @pytest.mark.parametrize("qtype", QT)
@@ -40,7 +44,8 @@ def test_oracle_matches_golden_dequant(kat, qtype):
     assert np.array_equal(oracle.dequantize(blocks, qtype, k, "float32").view(np.uint32), kat[f"{qtype}_f32_bits"])
     assert np.array_equal(oracle.dequantize(blocks, qtype, k, "float16").view(np.uint16), kat[f"{qtype}_f16_bits"])
     assert np.array_equal(oracle.dequantize(blocks, qtype, k, "bfloat16"), kat[f"{qtype}_bf16_bits"])
-    assert np.array_equal(oracle.dequantize_numpy(blocks, qtype, k).view(np.uint32), kat[f"{qtype}_f32_bits"])
+    if qtype in QT3:
+        assert np.array_equal(oracle.dequantize_numpy(blocks, qtype, k).view(np.uint32), kat[f"{qtype}_f32_bits"])
 
 
 @pytest.mark.parametrize("qtype", QT)
@@ -53,7 +58,85 @@ def test_oracle_matches_gguf_package(qtype):
     assert np.array_equal(oracle.dequantize(blocks, qtype, k).view(np.uint32), want.view(np.uint32))
 
 
+def _reference_host_library():
+    """oracle/_ref/libref_gguf_host.so: the reference's own host decode functions, lifted and built by oracle/build_ref.py
+    where the reference tree is present.  Absent on a machine without that tree (the committed fixtures cover it there)."""
+    import ctypes
+    from pathlib import Path
+    path = Path(oracle.__file__).resolve().parent / "_ref" / "libref_gguf_host.so"
+    if not path.exists():
+        pytest.skip("oracle/_ref/libref_gguf_host.so not built (no reference tree on this machine)")
+    lib = ctypes.CDLL(str(path))
+    lib.ref_half_bits_to_float.restype = ctypes.c_float
+    lib.ref_half_bits_to_float.argtypes = [ctypes.c_uint16]
+    lib.ref_float_to_half_bits.restype = ctypes.c_uint16
+    lib.ref_float_to_half_bits.argtypes = [ctypes.c_float]
+    return lib
+
+
 @pytest.mark.parametrize("qtype", QT)
+def test_oracle_matches_the_references_own_host_functions(qtype, kat):
+    """Bit for bit against `<qtype>_value_host` and `reference_gemm_quant` of tools/bench_ck_gguf_q8_gemm.hip (compiled from the
+    reference's source with -ffp-contract=off): golden edge blocks, seeded synthetic blocks and blocks of uniformly random
+    BYTES (every scale bit pattern, NaN and Inf included - compared as bit patterns)."""
+    import ctypes
+    lib = _reference_host_library()
+    q = qtype_of(qtype)
+    bs, bb = ctypes.c_int(), ctypes.c_int()
+    assert lib.ref_gguf_block_geometry(q.value, ctypes.byref(bs), ctypes.byref(bb)) == 0
+    assert (bs.value, bb.value) == (q.block_size, q.block_bytes)
+    k = 4 * q.block_size
+    rng = np.random.default_rng(2024)
+    for blocks in (kat[f"{qtype}_blocks"], S.random_blocks(qtype, 9, k, seed=5), rng.integers(0, 256, (7, 4 * q.block_bytes), dtype=np.uint8)):
+        kk = blocks.shape[1] // q.block_bytes * q.block_size
+        mine = oracle.dequantize(blocks, qtype, kk)
+        ref = np.empty_like(mine)
+        assert lib.ref_gguf_dequantize_rows(blocks.ctypes.data_as(ctypes.c_void_p), q.value, ctypes.c_int64(blocks.shape[0]),
+                                            ctypes.c_int64(kk), ref.ctypes.data_as(ctypes.c_void_p)) == 0
+        assert np.array_equal(mine.view(np.uint32), ref.view(np.uint32)), qtype
+    # the quantized matmul: same accumulation order => identical bits with fp32 weights.  With f16_dequant the bench tool rounds
+    # each weight through ITS float_to_half_bits, which rounds ties upward (mant + 0x1000, tools/bench_ck_gguf_q8_gemm.hip:411-437);
+    # the oracle rounds to nearest even like the GPU's cvt.rn and numpy, so the two differ by one fp16 ulp on tied weights only.
+    n, m = 11, 3
+    blocks = S.random_blocks(qtype, n, k, seed=6)
+    a = S.random_activations(m, k, 7, "float32")
+    for f16 in (0, 1):
+        ref = np.empty((m, n), dtype=np.float32)
+        assert lib.ref_gguf_gemm_quant(a.ctypes.data_as(ctypes.c_void_p), blocks.ctypes.data_as(ctypes.c_void_p), q.value, m, n, k, f16,
+                                       ref.ctypes.data_as(ctypes.c_void_p)) == 0
+        mine = oracle.gemm_quant(a, blocks, qtype, n, k, round_w=f16)
+        if f16 == 0:
+            assert np.array_equal(mine.view(np.uint32), ref.view(np.uint32)), qtype
+        else:
+            assert oracle.max_errors(ref, mine)[2] <= 1e-3, qtype
+
+
+def test_oracle_half_conversions_and_error_metric_match_the_reference():
+    import ctypes
+    lib = _reference_host_library()
+    L = oracle.lib()
+    L.oracle_half_to_float.restype = ctypes.c_float
+    L.oracle_half_to_float.argtypes = [ctypes.c_uint16]
+    for h in range(0, 65536, 7):                      # every seventh fp16 bit pattern, plus the edges
+        assert np.float32(L.oracle_half_to_float(h)).view(np.uint32) == np.float32(lib.ref_half_bits_to_float(h)).view(np.uint32), h
+    for h in (0, 1, 0x03ff, 0x0400, 0x7bff, 0x7c00, 0x7e00, 0x8000, 0xfbff, 0xffff):
+        assert np.float32(L.oracle_half_to_float(h)).view(np.uint32) == np.float32(lib.ref_half_bits_to_float(h)).view(np.uint32), h
+    # float -> half: identical wherever the value is not a tie between two halves (the tool rounds ties up, the oracle to even)
+    L.oracle_float_to_half.restype = ctypes.c_uint16
+    L.oracle_float_to_half.argtypes = [ctypes.c_float]
+    vals = (S.random_activations(1, 2000, 8, "float32").reshape(-1) * np.float32(3.7)).astype(np.float32)
+    not_tie = (vals.view(np.uint32) & 0x1fff) != 0x1000
+    for v in vals[not_tie]:
+        assert L.oracle_float_to_half(float(v)) == lib.ref_float_to_half_bits(float(v)), float(v)
+    e = S.random_activations(1, 4096, 3, "float32").reshape(-1) * 10
+    a = e + S.random_activations(1, 4096, 4, "float32").reshape(-1) * 0.01
+    ma, mr = ctypes.c_float(), ctypes.c_float()
+    lib.ref_gguf_max_errors(e.ctypes.data_as(ctypes.c_void_p), a.ctypes.data_as(ctypes.c_void_p), ctypes.c_int64(e.size), ctypes.byref(ma), ctypes.byref(mr))
+    max_abs, rel, _ = oracle.max_errors(e, a)
+    assert abs(max_abs - ma.value) <= 1e-6 * max_abs and abs(rel - mr.value) <= 1e-6 * rel
+
+
+@pytest.mark.parametrize("qtype", QT3)
 def test_numpy_twin_equals_c_on_random_blocks(qtype):
     k = 3 * qtype_of(qtype).block_size
     blocks = S.random_blocks(qtype, 17, k, seed=11)
