@@ -52,71 +52,83 @@ def measured_peaks():
 
 # ----------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clocks and throttle reasons while the timed region runs: through NVML every millisecond when the
-    binding is importable (a timed region of a few milliseconds still gets samples), else through nvidia-smi."""
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML about every millisecond when the
+    binding works (a timed region of a few milliseconds still gets samples; the context waits for the first sample before
+    the region starts and takes a last one when it ends), else through nvidia-smi every 50 ms."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index, self.rows, self._stop, self._thread = index, [], threading.Event(), None
+        self._first = threading.Event()
+        self.source, self.error = "nvidia-smi", None
         self._nvml = None
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            self._nvml = (pynvml, pynvml.nvmlDeviceGetHandleByIndex(int(os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[index])
-                                                                     if os.environ.get("CUDA_VISIBLE_DEVICES", "").replace(",", "").isdigit()
-                                                                     else index))
-        except Exception:
-            self._nvml = None
+            import pynvml as nv
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = visible.split(",") if visible else []
+            if index < len(ids) and ids[index].strip().isdigit():
+                handle = nv.nvmlDeviceGetHandleByIndex(int(ids[index]))
+            elif index < len(ids) and ids[index].strip().startswith("GPU-"):
+                handle = nv.nvmlDeviceGetHandleByUUID(ids[index].strip())
+            else:
+                handle = nv.nvmlDeviceGetHandleByIndex(index)
+            self._nvml, self.source = (nv, handle), "nvml"
+        except Exception as exc:                          # no binding / no NVML: fall back to nvidia-smi
+            self.error = f"{type(exc).__name__}: {exc}"[:120]
 
-    def _nvml_loop(self):
+    def _nvml_sample(self):
         nv, h = self._nvml
-        try:
-            top = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
-        except Exception:
-            top = float("nan")
-        bits = [("hw_slowdown", getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8)), ("hw_thermal_slowdown", getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40)),
-                ("sw_thermal_slowdown", getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20)), ("sw_power_cap", getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4))]
         reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
-        while not self._stop.is_set():
-            try:
-                sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                mask = int(reasons_fn(h))
-                self.rows.append([str(sm), str(top)] + ["Active" if mask & bit else "Not Active" for _, bit in bits])
-            except Exception:
-                pass
-            self._stop.wait(0.001)
+        bits = [0x8, 0x40, 0x20, 0x4]                     # hw slowdown, hw thermal slowdown, sw thermal slowdown, sw power cap
+        sm = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+        top = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        mask = int(reasons_fn(h))
+        self.rows.append([str(sm), str(top)] + ["Active" if mask & bit else "Not Active" for bit in bits])
+
+    def _smi_sample(self):
+        out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout.strip()
+        if out:
+            self.rows.append([c.strip() for c in out.splitlines()[0].split(",")])
+
+    def _sample(self):
+        try:
+            if self._nvml is not None:
+                self._nvml_sample()
+            else:
+                self._smi_sample()
+        except Exception as exc:
+            self.error = f"{type(exc).__name__}: {exc}"[:120]
+            if self._nvml is not None:                    # NVML answered with an error: use nvidia-smi from here on
+                self._nvml, self.source = None, "nvidia-smi"
 
     def _loop(self):
-        if self._nvml is not None:
-            return self._nvml_loop()
         while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.splitlines()[0].split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.05)
+            self._sample()
+            self._first.set()
+            self._stop.wait(0.001 if self._nvml is not None else 0.05)
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._loop, daemon=True)
         self._thread.start()
+        self._first.wait(timeout=6)                       # the timed region starts with one sample on record
         return self
 
     def __exit__(self, *exc):
         self._stop.set()
         self._thread.join(timeout=6)
+        self._sample()                                    # and ends with one
 
     def summary(self):
         if not self.rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "source": self.source, "error": self.error}
         sm = sorted(float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(self.NAMES) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": float(self.rows[0][1]) if self.rows[0][1].replace(".", "").isdigit() else None,
-                "reasons": reasons, "samples": len(self.rows)}
+                "reasons": reasons, "samples": len(self.rows), "source": self.source}
 
 
 # ----------------------------------------------------------------------------------------------- GPU helpers

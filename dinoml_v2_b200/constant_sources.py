@@ -38,14 +38,19 @@ GGUF_MATERIALIZATION_POLICIES: Mapping[str, str] = {
     GGUF_MATERIALIZATION_DEQUANTIZE_ON_GPU_BEFORE_LAUNCH: "future",    # superseded by the fused kernels
     GGUF_MATERIALIZATION_DIRECT_DEQUANTIZE_IN_KERNEL: "runtime_supported",
 }
+# The three host-residency policies are only declared by the reference ("future", src/dinoml/constant_sources.py:29-33); here
+# they are implemented in the native runtime (csrc/runtime.cu): the encoded bytes live in pinned host memory and reach the
+# device on first use (cpu_until_first_use) or are streamed through two device slots ahead of their launches, one
+# constant (sequential_offload) or one group of constants (grouped_offload) at a time.
 GGUF_RESIDENCY_POLICIES: Mapping[str, str] = {
-    GGUF_RESIDENCY_EAGER_DENSE_DEVICE: "future",
-    GGUF_RESIDENCY_CPU_UNTIL_FIRST_USE: "future",
-    GGUF_RESIDENCY_SEQUENTIAL_OFFLOAD: "future",
-    GGUF_RESIDENCY_GROUPED_OFFLOAD: "future",
+    GGUF_RESIDENCY_EAGER_DENSE_DEVICE: "future",       # a dense device copy: what the fused kernels make unnecessary
+    GGUF_RESIDENCY_CPU_UNTIL_FIRST_USE: "runtime_supported",
+    GGUF_RESIDENCY_SEQUENTIAL_OFFLOAD: "runtime_supported",
+    GGUF_RESIDENCY_GROUPED_OFFLOAD: "runtime_supported",
     GGUF_RESIDENCY_MANUAL_RUNTIME_LOAD: "runtime_supported",
     GGUF_RESIDENCY_EAGER_ENCODED_DEVICE: "runtime_supported",
 }
+HOST_RESIDENCIES = (GGUF_RESIDENCY_CPU_UNTIL_FIRST_USE, GGUF_RESIDENCY_SEQUENTIAL_OFFLOAD, GGUF_RESIDENCY_GROUPED_OFFLOAD)
 
 
 def validate_gguf_constant_policy(materialization: str, residency: str, *, require_runtime_supported: bool = False) -> None:
@@ -87,21 +92,24 @@ class GGUFConstant:
     n_per_row: int | None = None
     materialization: str = GGUF_MATERIALIZATION_DIRECT_DEQUANTIZE_IN_KERNEL
     residency: str = GGUF_RESIDENCY_MANUAL_RUNTIME_LOAD
+    offload_group: int | None = None      # grouped_offload: constants with the same number travel to the device together
     _blocks: np.ndarray | None = field(default=None, repr=False, compare=False)   # in-memory source (from_blocks)
 
     def __post_init__(self) -> None:
         validate_gguf_constant_policy(self.materialization, self.residency)
+        if self.offload_group is not None and (self.residency != GGUF_RESIDENCY_GROUPED_OFFLOAD or int(self.offload_group) < 0):
+            raise ValueError("offload_group is a non-negative group number for residency 'grouped_offload' only")
 
     @staticmethod
     def from_blocks(blocks: np.ndarray, qtype, shape: Sequence[int], *, tensor: str = "weight", logical_dtype: str | None = None,
                     materialization: str = GGUF_MATERIALIZATION_DIRECT_DEQUANTIZE_IN_KERNEL,
-                    residency: str = GGUF_RESIDENCY_MANUAL_RUNTIME_LOAD) -> "GGUFConstant":
+                    residency: str = GGUF_RESIDENCY_MANUAL_RUNTIME_LOAD, offload_group: int | None = None) -> "GGUFConstant":
         q = qtype_of(qtype)
         n, k = (int(d) for d in shape)
         blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(n, row_bytes(q, k))
         return GGUFConstant(path="<memory>", tensor=tensor, logical_dtype=logical_dtype, shape=(n, k), qtype=q.name,
                             encoded_nbytes=int(blocks.nbytes), n_per_row=k, materialization=materialization, residency=residency,
-                            _blocks=blocks)
+                            offload_group=offload_group, _blocks=blocks)
 
     def materialize(self, dtype: str, shape: Sequence[int]) -> MaterializedConstant:
         """The reference dequantizes on the host here (src/dinoml/constant_sources.py:58-79).  This runtime has no
@@ -145,6 +153,8 @@ class GGUFConstant:
         for key in ("qtype", "qtype_value", "encoded_nbytes", "gguf_shape", "data_offset", "n_per_row"):
             if observed.get(key) is not None:
                 metadata[key] = observed[key]
+        if self.offload_group is not None:
+            metadata["offload_group"] = int(self.offload_group)
         return metadata
 
     def _validate_observed_hints(self, observed: Mapping[str, Any]) -> None:
@@ -157,9 +167,10 @@ class GGUFConstant:
 def gguf_constant(path: str | Path, tensor: str, *, logical_dtype: str | None = None, shape: Sequence[int] | None = None,
                   qtype: str | None = None, encoded_nbytes: int | None = None, n_per_row: int | None = None,
                   materialization: str = GGUF_MATERIALIZATION_DIRECT_DEQUANTIZE_IN_KERNEL,
-                  residency: str = GGUF_RESIDENCY_MANUAL_RUNTIME_LOAD) -> GGUFConstant:
+                  residency: str = GGUF_RESIDENCY_MANUAL_RUNTIME_LOAD, offload_group: int | None = None) -> GGUFConstant:
     return GGUFConstant(path=path, tensor=tensor, logical_dtype=logical_dtype, shape=shape, qtype=qtype,
-                        encoded_nbytes=encoded_nbytes, n_per_row=n_per_row, materialization=materialization, residency=residency)
+                        encoded_nbytes=encoded_nbytes, n_per_row=n_per_row, materialization=materialization, residency=residency,
+                        offload_group=offload_group)
 
 
 def materialize_gguf_encoded_constant(source: GGUFConstant, dtype: str, shape: Sequence[int]) -> MaterializedConstant:

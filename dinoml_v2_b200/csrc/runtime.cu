@@ -15,10 +15,22 @@
 //   node gemm_rcr <a> <b> <bias|-> <out> <variant>                       also gemm_rcr_bias; dual_gemm_rcr_silu / _fast_gelu with
 //                                                                         <b> = the two weights' rows interleaved in groups of 8
 //   dispatch <node_index> <m> <n> <k> <variant>                          shape-guarded selection
+//
+// Where an encoded constant lives (its <residency>; policy names of src/dinoml/constant_sources.py:17-34, which the
+// reference declares but does not implement):
+//   manual_runtime_load / eager_encoded_device   on the device from load time on;
+//   cpu_until_first_use    in pinned host memory until the first run that needs it, then on the device for good;
+//   sequential_offload     in pinned host memory; a run streams each weight into one of two device slots just ahead of
+//                          its launch (the next weight is copied on a second stream while the current one computes);
+//   grouped_offload        the same at the granularity of groups of constants (one group = e.g. one layer).
+// Steady state: dino_session_set_graph_replay(session, 1) makes dino_session_run capture the launch sequence of a
+// (shapes, pointers) combination the second time it sees it and replay the graph from then on.
+// DINOML_PROFILE_RUN[_VERBOSE|_SECTIONS] time every launch with events, as src/dinoml/templates/gpu_module.cu.j2:785-983.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
+#include <map>
 #include <sstream>
 #include <string>
 #include <vector>
@@ -76,6 +88,31 @@ struct ConstantSpec {
   std::string residency;
   void* device = nullptr;
   bool loaded = false;
+  // host residency (cpu_until_first_use / sequential_offload / grouped_offload)
+  int policy = 0;               // 0 device-resident, 1 first use, 2 offloaded through the module's two device slots
+  void* host = nullptr;         // pinned copy of the encoded bytes, owned by the module
+  int group = -1;               // offload group (policy 2)
+  size_t slot_offset = 0;       // offset of this constant inside its group's slot image
+};
+
+enum : int { RES_DEVICE = 0, RES_FIRST_USE = 1, RES_OFFLOAD = 2 };
+int residency_policy(const std::string& r) {
+  if (r == "cpu_until_first_use") return RES_FIRST_USE;
+  if (r == "sequential_offload" || r == "grouped_offload") return RES_OFFLOAD;
+  return RES_DEVICE;
+}
+
+struct OffloadGroup { std::vector<int> constants; size_t bytes = 0; };
+struct OffloadState {
+  std::map<int, OffloadGroup> groups;         // by group id
+  void* slot[2] = {nullptr, nullptr};
+  size_t slot_bytes = 0;
+  int resident[2] = {-1, -1};                 // group whose upload was last issued into each slot
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ready[2] = {nullptr, nullptr};  // recorded on the copy stream after an upload
+  cudaEvent_t freed[2] = {nullptr, nullptr};  // recorded on a compute stream after the last launch that read the slot
+  bool freed_valid[2] = {false, false};
+  size_t uploads = 0, upload_bytes = 0, host_bytes = 0;
 };
 
 struct NodeSpec {
@@ -95,6 +132,8 @@ struct DinoModule {
   std::vector<ConstantSpec> constants;
   std::vector<NodeSpec> nodes;
   std::vector<DispatchSpec> dispatch;
+  OffloadState offload;
+  size_t generation = 0;        // bumped whenever constant buffers are released: captured graphs of older generations are dropped
 };
 
 struct DinoSession {
@@ -104,6 +143,12 @@ struct DinoSession {
   std::vector<void*> temps;                         // per tensor index (temp role only)
   std::vector<std::vector<int64_t>> shapes;         // per tensor index, as of the last run
   std::vector<bool> output_shape_valid;
+  // steady-state replay: one captured graph per (input shapes, input / output pointers) seen at least twice
+  bool graph_replay = false;
+  struct CachedGraph { cudaGraphExec_t exec = nullptr; int seen = 0; std::vector<std::vector<int64_t>> out_shapes; };
+  std::map<std::vector<int64_t>, CachedGraph> graphs;
+  size_t graph_launches = 0;
+  size_t graph_generation = 0;
 };
 
 namespace {
@@ -189,6 +234,12 @@ int parse_plan(DinoModule* mod, const std::string& path) {
         if (size_t(rows) * size_t(npr / bs) * size_t(b200gguf::qtype_block_bytes(c.qtype)) != c.nbytes)
           return fail(where + "encoded_nbytes does not match rows x n_per_row");
         c.shape = {rows, npr};
+        static const char* const kResidencies[] = {"manual_runtime_load", "eager_encoded_device", "cpu_until_first_use", "sequential_offload",
+                                                   "grouped_offload"};
+        bool known = false;
+        for (const char* r : kResidencies) known = known || c.residency == r;
+        if (!known) return fail(where + "unknown residency " + c.residency);
+        c.policy = residency_policy(c.residency);
       } else {
         return fail(where + "unknown constant storage " + storage);
       }
@@ -287,6 +338,136 @@ int check_tensor(const TensorSpec& spec, const DinoTensor& t, const char* what, 
 
 void* tensor_ptr(const DinoTensor& t) { return static_cast<uint8_t*>(t.data) + t.byte_offset; }
 
+// ---- host-resident encoded constants -------------------------------------------------------------------------------
+constexpr size_t kSlotAlign = 256;
+
+// Lays the offload groups out (slot image offsets), sizes the two device slots for the largest group and creates the
+// copy stream and events.  Called at the start of a run; cheap when nothing changed.
+int prepare_offload(DinoModule& mod) {
+  OffloadState& o = mod.offload;
+  if (o.groups.empty()) return 0;
+  size_t need = 0;
+  for (auto& entry : o.groups) {
+    size_t at = 0;
+    for (int ci : entry.second.constants) {
+      mod.constants[ci].slot_offset = at;
+      at += (mod.constants[ci].nbytes + kSlotAlign - 1) / kSlotAlign * kSlotAlign;
+    }
+    entry.second.bytes = at;
+    if (at > need) need = at;
+  }
+  if (o.copy_stream == nullptr) {
+    cudaError_t err = cudaStreamCreateWithFlags(&o.copy_stream, cudaStreamNonBlocking);
+    for (int i = 0; i < 2 && err == cudaSuccess; ++i) {
+      err = cudaEventCreateWithFlags(&o.ready[i], cudaEventDisableTiming);
+      if (err == cudaSuccess) err = cudaEventCreateWithFlags(&o.freed[i], cudaEventDisableTiming);
+    }
+    if (err != cudaSuccess) return cuda_fail("offload stream / events", err);
+  }
+  if (need > o.slot_bytes) {
+    cudaDeviceSynchronize();                      // nothing may still read or fill the old slots
+    for (int i = 0; i < 2; ++i) {
+      if (o.slot[i] != nullptr) cudaFree(o.slot[i]);
+      o.slot[i] = nullptr;
+      const cudaError_t err = cudaMalloc(&o.slot[i], need);
+      if (err != cudaSuccess) return cuda_fail("cudaMalloc (offload slot)", err);
+      o.resident[i] = -1;
+      o.freed_valid[i] = false;
+    }
+    o.slot_bytes = need;
+  }
+  return 0;
+}
+
+// Copies group g into slot sl on the copy stream, after the last kernel that read the slot.
+int issue_upload(DinoModule& mod, int g, int sl) {
+  OffloadState& o = mod.offload;
+  if (o.freed_valid[sl]) {
+    const cudaError_t err = cudaStreamWaitEvent(o.copy_stream, o.freed[sl], 0);
+    if (err != cudaSuccess) return cuda_fail("cudaStreamWaitEvent (offload slot free)", err);
+  }
+  for (int ci : o.groups[g].constants) {
+    const ConstantSpec& c = mod.constants[ci];
+    const cudaError_t err = cudaMemcpyAsync(static_cast<uint8_t*>(o.slot[sl]) + c.slot_offset, c.host, c.nbytes, cudaMemcpyHostToDevice, o.copy_stream);
+    if (err != cudaSuccess) return cuda_fail("cudaMemcpyAsync (offloaded constant)", err);
+    ++o.uploads;
+    o.upload_bytes += c.nbytes;
+  }
+  const cudaError_t err = cudaEventRecord(o.ready[sl], o.copy_stream);
+  if (err != cudaSuccess) return cuda_fail("cudaEventRecord (offload ready)", err);
+  o.resident[sl] = g;
+  return 0;
+}
+
+// Makes group g available to kernels on `stream`; returns its slot.  `keep` is the slot that must not be overwritten (the
+// one the caller is computing from), or -1.
+int acquire_group(DinoModule& mod, int g, int keep, cudaStream_t stream, int* slot) {
+  OffloadState& o = mod.offload;
+  int sl = o.resident[0] == g ? 0 : o.resident[1] == g ? 1 : -1;
+  if (sl < 0) {
+    sl = keep == 0 ? 1 : keep == 1 ? 0 : (o.resident[0] < 0 ? 0 : o.resident[1] < 0 ? 1 : 0);
+    if (int rc = issue_upload(mod, g, sl)) return rc;
+  }
+  const cudaError_t err = cudaStreamWaitEvent(stream, o.ready[sl], 0);
+  if (err != cudaSuccess) return cuda_fail("cudaStreamWaitEvent (offload ready)", err);
+  *slot = sl;
+  return 0;
+}
+
+// cpu_until_first_use: allocate the device buffer and copy the bytes on the run's stream, ahead of the first launch that
+// reads them; the constant stays on the device afterwards.
+int first_use_upload(ConstantSpec& c, cudaStream_t stream) {
+  if (c.host == nullptr) return fail("constant '" + c.name + "' has no host copy to upload");
+  cudaError_t err = cudaMalloc(&c.device, c.nbytes);
+  if (err != cudaSuccess) return cuda_fail("cudaMalloc (first-use constant)", err);
+  err = cudaMemcpyAsync(c.device, c.host, c.nbytes, cudaMemcpyHostToDevice, stream);
+  return err == cudaSuccess ? 0 : cuda_fail("cudaMemcpyAsync (first-use constant)", err);
+}
+
+void release_offload(DinoModule& mod) {
+  OffloadState& o = mod.offload;
+  for (int i = 0; i < 2; ++i) {
+    if (o.slot[i] != nullptr) cudaFree(o.slot[i]);
+    if (o.ready[i] != nullptr) cudaEventDestroy(o.ready[i]);
+    if (o.freed[i] != nullptr) cudaEventDestroy(o.freed[i]);
+  }
+  if (o.copy_stream != nullptr) cudaStreamDestroy(o.copy_stream);
+  for (ConstantSpec& c : mod.constants) { c.group = -1; c.policy = residency_policy(c.residency) == RES_DEVICE ? RES_DEVICE : c.policy; }
+  mod.offload = OffloadState();
+}
+
+bool module_streams_constants(const DinoModule& mod) {
+  for (const ConstantSpec& c : mod.constants)
+    if (c.policy == RES_OFFLOAD || (c.policy == RES_FIRST_USE && c.device == nullptr)) return true;
+  return false;
+}
+
+// ---- DINOML_PROFILE_RUN: per-launch event timing -------------------------------------------------------------------
+struct ProfileSection { std::string name; int start = -1, end = -1; cudaEvent_t e0 = nullptr, e1 = nullptr; bool started = false, stopped = false; };
+int parse_profile_sections(const char* env, std::vector<ProfileSection>* out) {
+  const char* cursor = env;
+  while (cursor != nullptr && *cursor != '\0') {
+    const char* colon = std::strchr(cursor, ':');
+    if (colon == nullptr) return fail("DINOML_PROFILE_RUN_SECTIONS entry is missing first ':'");
+    char* end1 = nullptr;
+    const long a = std::strtol(colon + 1, &end1, 10);
+    if (end1 == colon + 1 || *end1 != ':') return fail("DINOML_PROFILE_RUN_SECTIONS entry has invalid start launch");
+    char* end2 = nullptr;
+    const long b = std::strtol(end1 + 1, &end2, 10);
+    if (end2 == end1 + 1) return fail("DINOML_PROFILE_RUN_SECTIONS entry has invalid end launch");
+    if (a < 0 || b < a) return fail("DINOML_PROFILE_RUN_SECTIONS requires non-negative start <= end");
+    ProfileSection sec;
+    sec.name.assign(cursor, size_t(colon - cursor));
+    sec.start = int(a);
+    sec.end = int(b);
+    out->push_back(sec);
+    if (*end2 == ',') cursor = end2 + 1;
+    else if (*end2 == '\0') cursor = end2;
+    else return fail("DINOML_PROFILE_RUN_SECTIONS entries must be comma-separated");
+  }
+  return 0;
+}
+
 // One pass over the plan.  `launch == false` only validates and computes shapes.
 int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTensor* outputs, size_t num_outputs,
              bool validate) {
@@ -298,8 +479,27 @@ int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTe
     for (size_t i = 0; i < num_inputs; ++i)
       if (int rc = check_tensor(mod.tensors[mod.inputs[i]], inputs[i], "input", &s->shapes[mod.inputs[i]])) return rc;
     for (const ConstantSpec& c : mod.constants)
-      if (!c.loaded) return fail("constant '" + c.name + "' is not loaded" + (c.encoded ? " (call dino_module_set_encoded_constant)" : ""));
+      if (!c.loaded)
+        return fail("constant '" + c.name + "' is not loaded" +
+                    (!c.encoded ? "" : c.policy == RES_DEVICE ? " (call dino_module_set_encoded_constant)" : " (call dino_module_set_offloaded_encoded_constant)"));
   }
+  if (int rc = prepare_offload(mod)) return rc;
+  // per-launch timing on request (environment contract of the reference's generated module)
+  const bool profile_run = std::getenv("DINOML_PROFILE_RUN") != nullptr;
+  const bool profile_verbose = std::getenv("DINOML_PROFILE_RUN_VERBOSE") != nullptr;
+  std::vector<ProfileSection> sections;
+  if (const char* env = std::getenv("DINOML_PROFILE_RUN_SECTIONS"))
+    if (int rc = parse_profile_sections(env, &sections)) return rc;
+  for (ProfileSection& sec : sections)
+    if (cudaEventCreate(&sec.e0) != cudaSuccess || cudaEventCreate(&sec.e1) != cudaSuccess) return fail("cudaEventCreate failed");
+  std::vector<cudaEvent_t> ev0, ev1;
+  std::vector<int> ev_node;
+  cudaEvent_t total0 = nullptr, total1 = nullptr;
+  if (profile_run) {
+    if (cudaEventCreate(&total0) != cudaSuccess || cudaEventCreate(&total1) != cudaSuccess) return fail("cudaEventCreate failed");
+    cudaEventRecord(total0, s->stream);
+  }
+  int launch_index = 0, busy_slot = -1;
   std::vector<void*> ptr(mod.tensors.size(), nullptr);
   for (size_t i = 0; i < num_inputs; ++i) ptr[mod.inputs[i]] = tensor_ptr(inputs[i]);
   for (size_t i = 0; i < num_outputs; ++i) ptr[mod.outputs[i]] = outputs[i].data ? tensor_ptr(outputs[i]) : nullptr;
@@ -307,7 +507,7 @@ int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTe
 
   for (size_t ni = 0; ni < mod.nodes.size(); ++ni) {
     const NodeSpec& node = mod.nodes[ni];
-    const ConstantSpec& w = mod.constants[node.b];
+    ConstantSpec& w = mod.constants[node.b];
     const std::vector<int64_t>& ashape = s->shapes[node.a];
     if (ashape.empty()) return fail("node " + std::to_string(ni) + " consumes a tensor that has no shape yet");
     const int64_t k = ashape.back();
@@ -338,17 +538,93 @@ int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTe
       if (d.node == int(ni) && d.m == m && d.n == n && d.k == k) { variant = d.variant; break; }
     const void* bias = node.bias >= 0 ? mod.constants[node.bias].device : nullptr;
     if (node.bias >= 0 && mod.constants[node.bias].shape.back() != n) return fail("bias length does not match N");
+    // where the weight bytes are for this launch
+    const void* wptr = w.device;
+    int slot = -1;
+    if (w.policy == RES_FIRST_USE && w.device == nullptr) {
+      if (int rc = first_use_upload(w, s->stream)) return rc;
+      wptr = w.device;
+    } else if (w.policy == RES_OFFLOAD) {
+      if (int rc = acquire_group(mod, w.group, busy_slot, s->stream, &slot)) return rc;
+      wptr = static_cast<const uint8_t*>(mod.offload.slot[slot]) + w.slot_offset;
+      busy_slot = slot;
+    }
+    for (ProfileSection& sec : sections)
+      if (sec.start == launch_index) { cudaEventRecord(sec.e0, s->stream); sec.started = true; }
+    if (profile_run) {
+      cudaEvent_t a = nullptr, b = nullptr;
+      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return fail("cudaEventCreate failed");
+      ev0.push_back(a); ev1.push_back(b); ev_node.push_back(int(ni));
+      cudaEventRecord(a, s->stream);
+    }
     const int rc = node.activation != 0
-                       ? b200gguf::dual_gemm_rcr(ptr[node.a], w.device, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
+                       ? b200gguf::dual_gemm_rcr(ptr[node.a], wptr, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
                                                  node.activation, variant, s->stream)
-                       : b200gguf::gemm_rcr(ptr[node.a], w.device, bias, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
+                       : b200gguf::gemm_rcr(ptr[node.a], wptr, bias, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
                                             variant, s->stream);
+    if (profile_run) cudaEventRecord(ev1.back(), s->stream);
+    for (ProfileSection& sec : sections)
+      if (sec.end == launch_index) { cudaEventRecord(sec.e1, s->stream); sec.stopped = true; }
+    ++launch_index;
+    if (slot >= 0 && rc == 0) {
+      // the slot is free again once this launch has read it; then stream the next group into the other slot while this
+      // one computes
+      OffloadState& o = mod.offload;
+      cudaEventRecord(o.freed[slot], s->stream);
+      o.freed_valid[slot] = true;
+      for (size_t nj = ni + 1; nj < mod.nodes.size(); ++nj) {
+        const ConstantSpec& nw = mod.constants[mod.nodes[nj].b];
+        if (nw.policy != RES_OFFLOAD || nw.group == w.group) continue;
+        if (o.resident[0] != nw.group && o.resident[1] != nw.group)
+          if (int rc2 = issue_upload(mod, nw.group, slot ^ 1)) return rc2;
+        break;
+      }
+    }
     if (rc != 0) {
       static const char* const kText[] = {"ok", "null pointer", "non-positive dimension", "k not a multiple of the block",
                                           "CUDA launch failed", "unsupported qtype", "unsupported dtype", "alignment",
                                           "shape outside variant range", "device wait gave up"};
       return fail("gemm_rcr node " + std::to_string(ni) + " failed: " + (rc < 10 ? kText[rc] : "error"));
     }
+  }
+  if (profile_run || !sections.empty()) {
+    if (profile_run) cudaEventRecord(total1, s->stream);
+    if (cudaStreamSynchronize(s->stream) != cudaSuccess) return fail("profile run: stream synchronize failed");
+    if (profile_run) {
+      double op_ms[3] = {0, 0, 0};
+      size_t op_count[3] = {0, 0, 0};
+      static const char* const kOp[3] = {"gemm_rcr", "dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu"};
+      for (size_t i = 0; i < ev0.size(); ++i) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, ev0[i], ev1[i]);
+        const NodeSpec& node = mod.nodes[ev_node[i]];
+        op_ms[node.activation] += ms;
+        ++op_count[node.activation];
+        if (profile_verbose)
+          std::fprintf(stderr, "[dinoml_profile_launch] label=node%d:%s:%s ms=%.6f\n", ev_node[i], kOp[node.activation],
+                       mod.tensors[node.out].name.c_str(), double(ms));
+        cudaEventDestroy(ev0[i]);
+        cudaEventDestroy(ev1[i]);
+      }
+      float total = 0.f;
+      cudaEventElapsedTime(&total, total0, total1);
+      std::fprintf(stderr, "[dinoml_profile] total_gpu_ms=%.6f\n", double(total));
+      for (int op = 0; op < 3; ++op)
+        if (op_count[op] != 0)
+          std::fprintf(stderr, "[dinoml_profile] op=%s count=%zu total_ms=%.6f mean_ms=%.6f\n", kOp[op], op_count[op], op_ms[op],
+                       op_ms[op] / double(op_count[op]));
+      cudaEventDestroy(total0);
+      cudaEventDestroy(total1);
+    }
+    for (ProfileSection& sec : sections) {
+      if (!sec.started || !sec.stopped) return fail("DINOML_PROFILE_RUN_SECTIONS range did not match generated launch indices");
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, sec.e0, sec.e1);
+      std::fprintf(stderr, "[dinoml_profile_section] name=%s start=%d end=%d ms=%.6f\n", sec.name.c_str(), sec.start, sec.end, double(ms));
+      cudaEventDestroy(sec.e0);
+      cudaEventDestroy(sec.e1);
+    }
+    std::fflush(stderr);
   }
   return 0;
 }
@@ -392,6 +668,7 @@ int dino_module_load_constants(DinoModule* module, const char* constants_path) {
   std::vector<char> staging;
   for (ConstantSpec& c : module->constants) {
     if (c.encoded && c.residency == "manual_runtime_load") continue;   // uploaded by dino_module_set_encoded_constant
+    if (c.encoded && residency_policy(c.residency) != RES_DEVICE) continue;   // registered by dino_module_set_offloaded_encoded_constant
     staging.resize(c.nbytes);
     in.seekg(std::streamoff(c.offset));
     if (!in.read(staging.data(), std::streamsize(c.nbytes))) return fail("constants file is too short for '" + c.name + "'");
@@ -408,9 +685,13 @@ int dino_module_unload_constants(DinoModule* module) {
   cudaDeviceSynchronize();
   for (ConstantSpec& c : module->constants) {
     if (c.device != nullptr) cudaFree(c.device);
+    if (c.host != nullptr) cudaFreeHost(c.host);
     c.device = nullptr;
+    c.host = nullptr;
     c.loaded = false;
   }
+  release_offload(*module);
+  ++module->generation;
   return 0;
 }
 
@@ -449,8 +730,63 @@ int dino_module_set_encoded_constant(DinoModule* module, const char* name, const
 
 int dino_module_free(DinoModule* module) {
   if (module == nullptr) return 0;
-  for (ConstantSpec& c : module->constants) if (c.device != nullptr) cudaFree(c.device);
+  cudaDeviceSynchronize();
+  for (ConstantSpec& c : module->constants) {
+    if (c.device != nullptr) cudaFree(c.device);
+    if (c.host != nullptr) cudaFreeHost(c.host);
+  }
+  release_offload(*module);
   delete module;
+  return 0;
+}
+
+int dino_module_set_offloaded_encoded_constant(DinoModule* module, const char* name, const void* host_bytes, size_t nbytes, int group) {
+  if (module == nullptr || name == nullptr || host_bytes == nullptr) return fail("dino_module_set_offloaded_encoded_constant received null pointer");
+  const int idx = find_constant(*module, name);
+  if (idx < 0) return fail(std::string("unknown constant '") + name + "'");
+  ConstantSpec& c = module->constants[idx];
+  if (!c.encoded) return fail(std::string("constant '") + name + "' is not GGUF-encoded");
+  const int policy = residency_policy(c.residency);
+  if (policy == RES_DEVICE)
+    return fail(std::string("constant '") + name + "' has residency " + c.residency + ": it lives on the device (use dino_module_set_encoded_constant)");
+  if (nbytes != c.nbytes)
+    return fail(std::string("constant '") + name + "' expects exactly " + std::to_string(c.nbytes) + " encoded bytes, got " + std::to_string(nbytes));
+  if (policy == RES_OFFLOAD && group < 0) return fail("offload group must be non-negative");
+  if (c.host == nullptr) {
+    const cudaError_t err = cudaMallocHost(&c.host, nbytes);
+    if (err != cudaSuccess) return cuda_fail("cudaMallocHost (host-resident constant)", err);
+    module->offload.host_bytes += nbytes;
+  }
+  std::memcpy(c.host, host_bytes, nbytes);
+  if (c.device != nullptr) {            // a first-use constant that was already uploaded: refresh the device copy too
+    const cudaError_t err = cudaMemcpy(c.device, c.host, nbytes, cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) return cuda_fail("cudaMemcpy (first-use constant refresh)", err);
+  }
+  if (policy == RES_OFFLOAD) {
+    OffloadState& o = module->offload;
+    if (c.group >= 0 && c.group != group) return fail(std::string("constant '") + name + "' is already in offload group " + std::to_string(c.group));
+    if (c.group < 0) {
+      c.group = group;
+      o.groups[group].constants.push_back(idx);
+    }
+    for (int i = 0; i < 2; ++i)
+      if (o.resident[i] == group) o.resident[i] = -1;      // the slot image of this group is stale
+  }
+  c.policy = policy;
+  c.loaded = true;
+  return 0;
+}
+
+int dino_module_get_residency_stats(DinoModule* module, size_t* device_resident_bytes, size_t* device_slot_bytes, size_t* pinned_host_bytes,
+                                    size_t* uploads, size_t* upload_bytes) {
+  if (module == nullptr) return fail("dino_module_get_residency_stats received null pointer");
+  size_t resident = 0;
+  for (const ConstantSpec& c : module->constants) if (c.encoded && c.device != nullptr) resident += c.nbytes;
+  if (device_resident_bytes) *device_resident_bytes = resident;
+  if (device_slot_bytes) *device_slot_bytes = 2 * module->offload.slot_bytes;
+  if (pinned_host_bytes) *pinned_host_bytes = module->offload.host_bytes;
+  if (uploads) *uploads = module->offload.uploads;
+  if (upload_bytes) *upload_bytes = module->offload.upload_bytes;
   return 0;
 }
 
@@ -482,6 +818,8 @@ int dino_session_destroy(DinoSession* session) {
     cudaStreamSynchronize(session->owned_stream);
     cudaStreamDestroy(session->owned_stream);
   }
+  for (auto& entry : session->graphs)
+    if (entry.second.exec != nullptr) cudaGraphExecDestroy(entry.second.exec);
   for (void* p : session->temps) if (p != nullptr) cudaFree(p);
   delete session;
   return 0;
@@ -505,14 +843,109 @@ int dino_session_get_output_shape(DinoSession* session, size_t output_index, int
   return 0;
 }
 
+int dino_session_set_graph_replay(DinoSession* session, int enabled) {
+  if (session == nullptr) return fail("dino_session_set_graph_replay received null pointer");
+  session->graph_replay = enabled != 0;
+  return 0;
+}
+
+int dino_session_get_graph_stats(DinoSession* session, size_t* cached_graphs, size_t* graph_launches) {
+  if (session == nullptr) return fail("dino_session_get_graph_stats received null pointer");
+  size_t n = 0;
+  for (const auto& entry : session->graphs) n += entry.second.exec != nullptr ? 1 : 0;
+  if (cached_graphs) *cached_graphs = n;
+  if (graph_launches) *graph_launches = session->graph_launches;
+  return 0;
+}
+
+// Steady-state path of dino_session_run: the launch sequence of one (input shapes, input / output pointers) combination is
+// captured the second time it is seen and replayed afterwards; validation ran when it was captured.  Returns 1 if the
+// call was served (rc in *rc_out), 0 if the caller should run the plan the ordinary way.
+static int run_replayed(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTensor* outputs, size_t num_outputs, int* rc_out) {
+  DinoModule& mod = *s->module;
+  if (!s->graph_replay || module_streams_constants(mod) || std::getenv("DINOML_PROFILE_RUN") != nullptr ||
+      std::getenv("DINOML_PROFILE_RUN_SECTIONS") != nullptr)
+    return 0;
+  if (num_inputs != mod.inputs.size() || num_outputs != mod.outputs.size() || (num_inputs && !inputs) || (num_outputs && !outputs)) return 0;
+  if (s->graph_generation != mod.generation) {             // constant buffers were released since: every captured pointer is stale
+    for (auto& entry : s->graphs) if (entry.second.exec != nullptr) cudaGraphExecDestroy(entry.second.exec);
+    s->graphs.clear();
+    s->graph_generation = mod.generation;
+  }
+  std::vector<int64_t> key;
+  for (size_t i = 0; i < num_inputs; ++i) {
+    if (inputs[i].shape == nullptr || inputs[i].data == nullptr) return 0;
+    key.push_back(int64_t(reinterpret_cast<intptr_t>(tensor_ptr(inputs[i]))));
+    key.push_back(int64_t(inputs[i].ndim));
+    key.insert(key.end(), inputs[i].shape, inputs[i].shape + inputs[i].ndim);
+  }
+  for (size_t i = 0; i < num_outputs; ++i) {
+    if (outputs[i].data == nullptr) return 0;
+    key.push_back(int64_t(reinterpret_cast<intptr_t>(tensor_ptr(outputs[i]))));
+  }
+  DinoSession::CachedGraph& cg = s->graphs[key];
+  if (cg.exec != nullptr) {
+    s->shapes = cg.out_shapes;
+    std::fill(s->output_shape_valid.begin(), s->output_shape_valid.end(), true);
+    const cudaError_t err = cudaGraphLaunch(cg.exec, s->stream);
+    ++s->graph_launches;
+    *rc_out = err == cudaSuccess ? 0 : cuda_fail("cudaGraphLaunch", err);
+    return 1;
+  }
+  if (cg.seen < 0 || ++cg.seen < 2) return 0;              // first sight (or capture failed before): ordinary run
+  cudaGraph_t graph = nullptr;
+  if (cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); cg.seen = -1; return 0; }
+  const int rc = run_plan(s, inputs, num_inputs, outputs, num_outputs, true);
+  const bool ended = cudaStreamEndCapture(s->stream, &graph) == cudaSuccess && graph != nullptr;
+  if (rc != 0) { if (graph) cudaGraphDestroy(graph); cg.seen = -1; *rc_out = rc; return 1; }
+  bool ok = ended && cudaGraphInstantiate(&cg.exec, graph, 0) == cudaSuccess;
+  if (graph) cudaGraphDestroy(graph);
+  if (!ok) { cudaGetLastError(); cg.exec = nullptr; cg.seen = -1; return 0; }
+  cg.out_shapes = s->shapes;
+  const cudaError_t err = cudaGraphLaunch(cg.exec, s->stream);
+  ++s->graph_launches;
+  *rc_out = err == cudaSuccess ? 0 : cuda_fail("cudaGraphLaunch", err);
+  return 1;
+}
+
 int dino_session_run(DinoSession* session, const DinoTensor* inputs, size_t num_inputs, DinoTensor* outputs, size_t num_outputs) {
   if (session == nullptr) return fail("dino_session_run received null session");
-  if (int rc = run_plan(session, inputs, num_inputs, outputs, num_outputs, true)) return rc;
+  int replay_rc = 0;
+  if (run_replayed(session, inputs, num_inputs, outputs, num_outputs, &replay_rc)) {
+    if (replay_rc != 0) return replay_rc;
+  } else if (int rc = run_plan(session, inputs, num_inputs, outputs, num_outputs, true)) {
+    return rc;
+  }
   if (!session->external_stream) {
     const cudaError_t err = cudaStreamSynchronize(session->stream);
     if (err != cudaSuccess) return cuda_fail("dino_session_run synchronize", err);
   }
   return 0;
+}
+
+int dino_session_run_staged(DinoSession* session, const void* host_in, void* device_in, size_t in_bytes, const DinoTensor* inputs,
+                            size_t num_inputs, DinoTensor* outputs, size_t num_outputs, const void* device_out, void* host_out,
+                            size_t out_bytes) {
+  if (session == nullptr) return fail("dino_session_run_staged received null session");
+  if ((in_bytes && (host_in == nullptr || device_in == nullptr)) || (out_bytes && (host_out == nullptr || device_out == nullptr)))
+    return fail("dino_session_run_staged received a null staging buffer");
+  cudaStream_t stream = session->stream;
+  if (in_bytes) {
+    const cudaError_t err = cudaMemcpyAsync(device_in, host_in, in_bytes, cudaMemcpyHostToDevice, stream);
+    if (err != cudaSuccess) return cuda_fail("cudaMemcpyAsync (staged inputs)", err);
+  }
+  int replay_rc = 0;
+  if (run_replayed(session, inputs, num_inputs, outputs, num_outputs, &replay_rc)) {
+    if (replay_rc != 0) return replay_rc;
+  } else if (int rc = run_plan(session, inputs, num_inputs, outputs, num_outputs, true)) {
+    return rc;
+  }
+  if (out_bytes) {
+    const cudaError_t err = cudaMemcpyAsync(host_out, device_out, out_bytes, cudaMemcpyDeviceToHost, stream);
+    if (err != cudaSuccess) return cuda_fail("cudaMemcpyAsync (staged outputs)", err);
+  }
+  const cudaError_t err = cudaStreamSynchronize(stream);
+  return err == cudaSuccess ? 0 : cuda_fail("dino_session_run_staged synchronize", err);
 }
 
 int dino_session_benchmark(DinoSession* session, const DinoTensor* inputs, size_t num_inputs, DinoTensor* outputs,
@@ -530,7 +963,7 @@ int dino_session_benchmark(DinoSession* session, const DinoTensor* inputs, size_
   // Graph replay on the owned stream (skipped on an external stream, as the reference does); set
   // DINOML_REQUIRE_BENCHMARK_GRAPH to turn a capture failure into an error instead of direct launches.
   cudaGraphExec_t exec = nullptr;
-  if (!session->external_stream) {
+  if (!session->external_stream && !module_streams_constants(*session->module)) {   // weights streamed from the host: direct launches
     cudaGraph_t graph = nullptr;
     bool ok = cudaStreamBeginCapture(session->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
     if (ok) {

@@ -44,6 +44,10 @@ def _configure(lib: ctypes.CDLL) -> None:
         "dino_session_run": [vp, T, sz, T, sz],
         "dino_session_benchmark": [vp, T, sz, T, sz, sz, sz, ctypes.POINTER(ctypes.c_double), sz],
         "dino_device_malloc": [ctypes.POINTER(vp), sz], "dino_device_free": [vp], "dino_copy_host_to_device": [vp, vp, sz],
+        "dino_module_set_offloaded_encoded_constant": [vp, ctypes.c_char_p, vp, sz, ci],
+        "dino_module_get_residency_stats": [vp] + [ctypes.POINTER(sz)] * 5,
+        "dino_session_run_staged": [vp, vp, vp, sz, T, sz, T, sz, vp, vp, sz],
+        "dino_session_set_graph_replay": [vp, ci], "dino_session_get_graph_stats": [vp, ctypes.POINTER(sz), ctypes.POINTER(sz)],
     }.items():
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = args, ci
@@ -79,6 +83,7 @@ class RuntimeModule:
             raise RuntimeError(f"module.so reports ABI {self._lib.dino_abi_version()}, expected {RUNTIME_ABI_VERSION}")
         self._handle = ctypes.c_void_p()
         self._sessions: "weakref.WeakSet[Session]" = weakref.WeakSet()
+        self.offload_group_size = 2           # grouped_offload constants that name no group: this many consecutive ones per group
         self._check(self._lib.dino_module_load_deferred(str(self.path).encode(), ctypes.byref(self._handle)))
         try:
             self.metadata = json.loads(self._lib.dino_module_get_metadata_json(self._handle).decode())
@@ -108,10 +113,18 @@ class RuntimeModule:
             st = c.get("storage") or {}
             if st.get("kind") != "gguf":
                 continue
-            plan.append({"name": c["name"], "qtype": st["qtype"], "encoded_nbytes": c["nbytes"], "offset": c["offset"],
-                         "residency": st["residency"], "materialization": st["materialization"],
-                         "action": "upload_encoded" if st["residency"] == "manual_runtime_load" else "loaded_with_constants",
-                         "status": "runtime_supported"})
+            host = st["residency"] in ("cpu_until_first_use", "sequential_offload", "grouped_offload")
+            entry = {"name": c["name"], "qtype": st["qtype"], "encoded_nbytes": c["nbytes"], "offset": c["offset"],
+                     "residency": st["residency"], "materialization": st["materialization"],
+                     "action": "register_host_resident" if host else "upload_encoded" if st["residency"] == "manual_runtime_load"
+                     else "loaded_with_constants", "status": "runtime_supported"}
+            if st["residency"] == "sequential_offload":
+                entry["offload_group"] = sum(1 for p in plan if p["residency"] == "sequential_offload")      # one constant per group
+            elif st["residency"] == "grouped_offload":
+                # group numbers of the two policies are kept apart (grouped ones start at 2^20)
+                entry["offload_group"] = (1 << 20) + (int(st["offload_group"]) if "offload_group" in st else
+                                                      sum(1 for p in plan if p["residency"] == "grouped_offload") // self.offload_group_size)
+            plan.append(entry)
         return plan
 
     def load_encoded_constants(self, sources: Mapping[str, np.ndarray] | None = None) -> list[dict[str, Any]]:
@@ -120,15 +133,27 @@ class RuntimeModule:
         buffer), free the staging buffer."""
         done = []
         for entry in self.encoded_constant_load_plan():
-            if entry["action"] != "upload_encoded":
+            if entry["action"] not in ("upload_encoded", "register_host_resident"):
                 continue
             if sources is not None and entry["name"] in sources:
                 raw = np.ascontiguousarray(sources[entry["name"]], dtype=np.uint8).reshape(-1)
             else:
                 raw = np.fromfile(self.path / "constants.bin", dtype=np.uint8, count=entry["encoded_nbytes"], offset=entry["offset"])
-            self.set_encoded_constant_host_bytes(entry["name"], raw)
+            if entry["action"] == "upload_encoded":
+                self.set_encoded_constant_host_bytes(entry["name"], raw)
+            else:       # host-resident policies: the module keeps a pinned copy and moves the bytes itself at run time
+                self._check(self._lib.dino_module_set_offloaded_encoded_constant(self._handle, entry["name"].encode(), raw.ctypes.data,
+                                                                                 raw.nbytes, int(entry.get("offload_group", 0))))
             done.append(entry)
         return done
+
+    def residency_stats(self) -> dict[str, int]:
+        """Where the encoded constants are right now and how much a run has streamed: bytes resident on the device, bytes
+        of the two offload slots, pinned host bytes, host-to-device uploads and their bytes since load."""
+        vals = [ctypes.c_size_t() for _ in range(5)]
+        self._check(self._lib.dino_module_get_residency_stats(self._handle, *[ctypes.byref(v) for v in vals]))
+        keys = ("device_resident_bytes", "device_slot_bytes", "pinned_host_bytes", "uploads", "upload_bytes")
+        return {k: int(v.value) for k, v in zip(keys, vals)}
 
     def set_encoded_constant_host_bytes(self, name: str, raw: np.ndarray) -> None:
         staging = ctypes.c_void_p()
@@ -177,6 +202,8 @@ class Session:
         self._pinned: dict[str, Any] = {}
         self._numpy_plans: dict[Any, dict[str, Any]] = {}
         self._user_stream = 0
+        self._graph_replay = False
+        self.numpy_graph_replay = True        # run_numpy keeps its arenas, so its launch sequences are replayed as CUDA graphs
 
     def close(self) -> None:
         if self._handle:
@@ -189,6 +216,17 @@ class Session:
 
     def _set_stream_raw(self, stream_ptr: int) -> None:
         self.module._check(self._lib.dino_session_set_stream(self._handle, ctypes.c_void_p(stream_ptr)))
+
+    def set_graph_replay(self, enabled: bool) -> None:
+        """Steady-state replay for run_device_pointers / run_torch: a combination of shapes and device pointers seen twice is
+        captured as a CUDA graph and replayed afterwards.  Keep the buffers you pass stable while it is on."""
+        self._graph_replay = bool(enabled)
+        self.module._check(self._lib.dino_session_set_graph_replay(self._handle, int(self._graph_replay)))
+
+    def graph_stats(self) -> dict[str, int]:
+        cached, launches = ctypes.c_size_t(), ctypes.c_size_t()
+        self.module._check(self._lib.dino_session_get_graph_stats(self._handle, ctypes.byref(cached), ctypes.byref(launches)))
+        return {"cached_graphs": int(cached.value), "graph_launches": int(launches.value)}
 
     # -- shapes
     def _output_shapes(self, in_shapes: Mapping[str, tuple[int, ...]]) -> dict[str, tuple[int, ...]]:
@@ -246,23 +284,30 @@ class Session:
                 view[...] = arr if arr.dtype == np.uint16 else _f32_to_bf16_bits(arr)
             else:
                 view[...] = arr                                   # numpy converts to the view's dtype
-        stream = plan["stream"]
-        import torch
-        # run on the plan's stream: the copies and the kernels are ordered on it and the host waits once at the end
-        self._set_stream_raw(stream.cuda_stream)
+        # one native call: H2D of the input arena, the launches (a replayed graph in steady state), D2H of the output arena,
+        # one wait - all on the plan's stream
+        self._set_stream_raw(plan["stream"].cuda_stream)
+        if self.numpy_graph_replay and not self._graph_replay:
+            self.module._check(self._lib.dino_session_set_graph_replay(self._handle, 1))
         try:
-            with torch.cuda.stream(stream):
-                plan["dev_in"].copy_(plan["pin_in"], non_blocking=True)
-                self.module._check(self._lib.dino_session_run(self._handle, plan["ins"], len(plan["ins"]), plan["outs"], len(plan["outs"])))
-                plan["pin_out"].copy_(plan["dev_out"], non_blocking=True)
-            stream.synchronize()
+            self.module._check(self._lib.dino_session_run_staged(
+                self._handle, plan["pin_in_ptr"], plan["dev_in_ptr"], plan["in_bytes"], plan["ins"], len(plan["ins"]), plan["outs"],
+                len(plan["outs"]), plan["dev_out_ptr"], plan["pin_out_ptr"], plan["out_bytes"]))
         finally:
             self._set_stream_raw(self._user_stream)
+            if self.numpy_graph_replay and not self._graph_replay:
+                self._lib.dino_session_set_graph_replay(self._handle, 0)
+        if plan["any_bf16"]:
+            # bfloat16 -> float32 for the whole output arena at once: the 16 bits become the high half of each float
+            wide = plan["pin_out"].numpy().view(np.uint16).astype(np.uint32)
+            np.left_shift(wide, 16, out=wide)
+            wide = wide.view(np.float32)
         out = {}
         for o in meta["outputs"]:
             view = plan["out_views"][o["name"]]
             if o["dtype"] == "bfloat16":
-                out[o["name"]] = (view.astype(np.uint32) << np.uint32(16)).view(np.float32)
+                off = plan["out_off"][o["name"]] // 2
+                out[o["name"]] = wide[off:off + view.size].reshape(view.shape)
             else:
                 out[o["name"]] = view.copy()
         return out
@@ -296,6 +341,9 @@ class Session:
                     for name, shape, dtype in entries}
 
         plan["in_views"], plan["out_views"] = views(in_entries, in_off, host_in), views(out_entries, out_off, host_out)
+        plan.update(in_bytes=in_bytes, out_bytes=out_bytes, out_off=out_off, pin_in_ptr=plan["pin_in"].data_ptr(),
+                    dev_in_ptr=plan["dev_in"].data_ptr(), pin_out_ptr=plan["pin_out"].data_ptr(), dev_out_ptr=plan["dev_out"].data_ptr(),
+                    any_bf16=any(o["dtype"] == "bfloat16" for o in meta["outputs"]))
         plan["ins"] = (_DinoTensor * len(in_entries))(*[_tensor_struct(plan["dev_in"].data_ptr() + in_off[n], s, d, plan["keep"])
                                                         for n, s, d in in_entries])
         plan["outs"] = (_DinoTensor * len(out_entries))(*[_tensor_struct(plan["dev_out"].data_ptr() + out_off[n], s, d, plan["keep"])
@@ -317,6 +365,35 @@ class Session:
         self.module._check(self._lib.dino_session_benchmark(self._handle, ins, len(ins), outs, len(outs), warmup, iterations, ms, iterations))
         return summarize_ms(list(ms), native_entrypoint="dino_session_benchmark", timing_source="cuda_events", graph_replay=True,
                             warmup=warmup)
+
+
+    def benchmark_device_pointers(self, inputs, outputs, *, warmup: int = 5, iterations: int = 20) -> dict[str, Any]:
+        """Native benchmark on caller-owned device buffers: name -> (device pointer, shape, dtype name), as run_device_pointers
+        (src/dinoml/runtime.py:1194-1217)."""
+        ins, outs, keep = self._pack(inputs, outputs)
+        ms = (ctypes.c_double * iterations)()
+        self.module._check(self._lib.dino_session_benchmark(self._handle, ins, len(ins), outs, len(outs), warmup, iterations, ms, iterations))
+        return summarize_ms(list(ms), native_entrypoint="dino_session_benchmark", timing_source="cuda_events", graph_replay=True, warmup=warmup)
+
+    def benchmark_numpy(self, inputs: Mapping[str, np.ndarray], *, warmup: int = 5, iterations: int = 20) -> dict[str, Any]:
+        """Host arrays in: they are uploaded once (the arenas of run_numpy), then the native benchmark loop runs on the device
+        copies - device time per run, without the host copies (src/dinoml/runtime.py:966-977)."""
+        meta = self.module.metadata
+        arrays = {spec["name"]: np.asarray(inputs[spec["name"]]) for spec in meta["inputs"]}
+        key = tuple((name, arr.shape) for name, arr in arrays.items())
+        plan = self._numpy_plans.get(key)
+        if plan is None:
+            plan = self._numpy_plans[key] = self._make_numpy_plan(arrays)
+        for spec in meta["inputs"]:
+            arr, view = arrays[spec["name"]], plan["in_views"][spec["name"]]
+            view[...] = (arr if arr.dtype == np.uint16 else _f32_to_bf16_bits(arr)) if spec["dtype"] == "bfloat16" else arr
+        plan["dev_in"].copy_(plan["pin_in"])
+        import torch
+        torch.cuda.synchronize()
+        ms = (ctypes.c_double * iterations)()
+        self.module._check(self._lib.dino_session_benchmark(self._handle, plan["ins"], len(plan["ins"]), plan["outs"], len(plan["outs"]),
+                                                            warmup, iterations, ms, iterations))
+        return summarize_ms(list(ms), native_entrypoint="dino_session_benchmark", timing_source="cuda_events", graph_replay=True, warmup=warmup)
 
 
 def _f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:

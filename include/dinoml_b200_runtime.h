@@ -70,6 +70,19 @@ DINOML_B200_API int dino_module_set_constant(struct DinoModule* module, const ch
 /* gpu_module.cu.j2:362-391 - exact-size check, allocate once, device-to-device copy of raw GGUF bytes. */
 DINOML_B200_API int dino_module_set_encoded_constant(struct DinoModule* module, const char* name, const void* device_bytes,
                                                      size_t nbytes);
+/* Host-resident encoded constants - the residency policies the reference declares (src/dinoml/constant_sources.py:17-34:
+ * cpu_until_first_use, sequential_offload, grouped_offload) and leaves "future".  The module copies `host_bytes` into pinned
+ * host memory of its own.  cpu_until_first_use: uploaded on the stream of the first run that needs the constant, on the device
+ * from then on.  sequential_offload / grouped_offload: never resident; a run copies each offload group (`group` >= 0; give
+ * every constant its own group for sequential) into one of two device slots just ahead of its launches, the next group on
+ * a second stream while the current one computes - device memory held is twice the largest group.  One session at a time
+ * may run a module that streams constants.  Optional symbols, like the reference's set_temp_arena_policy pair. */
+DINOML_B200_API int dino_module_set_offloaded_encoded_constant(struct DinoModule* module, const char* name, const void* host_bytes,
+                                                               size_t nbytes, int group);
+/* Bytes of encoded constants resident on the device, bytes of the two offload slots, pinned host bytes held, and the number /
+ * bytes of host-to-device uploads made so far by runs.  Any pointer may be NULL. */
+DINOML_B200_API int dino_module_get_residency_stats(struct DinoModule* module, size_t* device_resident_bytes, size_t* device_slot_bytes,
+                                                    size_t* pinned_host_bytes, size_t* uploads, size_t* upload_bytes);
 DINOML_B200_API int dino_module_free(struct DinoModule* module);                       /* :436 */
 DINOML_B200_API const char* dino_module_get_metadata_json(struct DinoModule* module);  /* :449 */
 
@@ -81,9 +94,25 @@ DINOML_B200_API int dino_session_set_stream(struct DinoSession* session, void* s
 /* :630 - shape of output `output_index` as of the last run. */
 DINOML_B200_API int dino_session_get_output_shape(struct DinoSession* session, size_t output_index, int64_t* out_shape,
                                                   size_t* inout_ndim);
-/* :995 / :706-993 - validates every tensor, then launches the plan on the session stream. */
+/* Steady-state replay for dino_session_run (off by default; no counterpart in the reference, whose per-run path re-validates
+ * and re-launches every time, gpu_module.cu.j2:706-993): with it on, the launch sequence of a combination of input shapes and
+ * input / output device pointers is captured into a CUDA graph the second time the combination is seen and replayed from
+ * then on (validation ran at capture).  Callers keep their buffers stable (Session.run_numpy's arenas are).  Modules that
+ * stream constants from the host and DINOML_PROFILE_RUN runs always take the ordinary path. */
+DINOML_B200_API int dino_session_set_graph_replay(struct DinoSession* session, int enabled);
+DINOML_B200_API int dino_session_get_graph_stats(struct DinoSession* session, size_t* cached_graphs, size_t* graph_launches);
+/* :995 / :706-993 - validates every tensor, then launches the plan on the session stream.  With DINOML_PROFILE_RUN set every
+ * launch is bracketed by events and "[dinoml_profile] ..." lines go to stderr (DINOML_PROFILE_RUN_VERBOSE: one line per launch;
+ * DINOML_PROFILE_RUN_SECTIONS=name:first:last,...: elapsed time of launch ranges), as gpu_module.cu.j2:785-983. */
 DINOML_B200_API int dino_session_run(struct DinoSession* session, const struct DinoTensor* inputs, size_t num_inputs,
                                      struct DinoTensor* outputs, size_t num_outputs);
+/* dino_session_run with host staging in one call: copies `in_bytes` from pinned host memory `host_in` to `device_in` on the
+ * session stream, runs (`inputs` / `outputs` describe tensors inside the two device arenas), copies `out_bytes` from
+ * `device_out` to pinned `host_out`, and waits once.  What Session.run_numpy does per call; the reference's loader issues
+ * the copies from Python (src/dinoml/runtime.py:1371-1431). */
+DINOML_B200_API int dino_session_run_staged(struct DinoSession* session, const void* host_in, void* device_in, size_t in_bytes,
+                                            const struct DinoTensor* inputs, size_t num_inputs, struct DinoTensor* outputs,
+                                            size_t num_outputs, const void* device_out, void* host_out, size_t out_bytes);
 /* :1011-1170 - warm-ups, CUDA-graph capture of one run on the owned stream, then per-iteration
  * event / graph launch / event; elapsed milliseconds per measured run are written to out_elapsed_ms. */
 DINOML_B200_API int dino_session_benchmark(struct DinoSession* session, const struct DinoTensor* inputs, size_t num_inputs,

@@ -200,3 +200,138 @@ def test_profiled_plan_dispatches_several_tuning_configurations(tmp_path):
     out = Path(__file__).resolve().parent.parent / "gpurun_out"
     if out.is_dir():                                    # keep the selection next to the other GPU-run outputs
         (out / "plan_cfg2.json").write_text(json.dumps(chosen, indent=1))
+
+
+def _bank_artifact(tmp_path, residency, count=4, n=192, k=1024, groups=None):
+    """`count` independent quantized linears on one input (mixed qtypes), all weights with the given residency."""
+    qtypes = ["Q4_K", "Q6_K", "Q8_0", "Q4_K", "Q5_K", "Q4_K"][:count]
+    blocks = [S.random_blocks(q, n, k, 70 + i) for i, q in enumerate(qtypes)]
+
+    class Bank(dml.Module):
+        def __init__(self):
+            for i in range(count):
+                setattr(self, f"w{i}", dml.Parameter([n, k], dtype="bfloat16"))
+
+        def forward(self, x):
+            return [dml.ops.gemm_rcr(x, getattr(self, f"w{i}")) for i in range(count)]
+
+    consts = {f"w{i}": dml.GGUFConstant.from_blocks(blocks[i], qtypes[i], (n, k), tensor=f"w{i}", residency=residency,
+                                                   offload_group=None if groups is None else groups[i]) for i in range(count)}
+    spec = dml.trace(Bank(), inputs={"x": dml.TensorSpec([dml.Dim("m", 1, 8), k], "bfloat16")}, constants=consts)
+    art = dml.compile(spec, dml.Target("cuda"), tmp_path / f"art_{residency}")
+    return art, qtypes, blocks
+
+
+def _check_bank(sess, qtypes, blocks, m, seed):
+    n, k = blocks[0].shape[0], 1024
+    x = S.random_activations(m, k, seed, "float32")
+    xb = S.bf16_bits_to_float32(S.float32_to_bf16_bits(x))
+    out = sess.run_numpy({"x": x})
+    names = sorted(out, key=lambda s: int("".join(ch for ch in s if ch.isdigit()) or 0))
+    assert len(names) == len(qtypes)
+    for name, q, b in zip(names, qtypes, blocks):
+        _, _, norm = oracle.max_errors(oracle.gemm_quant(xb, b, q, n, k), out[name])
+        assert norm <= 2e-2, (name, q, m, norm)
+
+
+def test_residency_cpu_until_first_use(tmp_path):
+    art, qtypes, blocks = _bank_artifact(tmp_path, "cpu_until_first_use")
+    mod = dml.runtime.load(art.path)
+    plan = mod.load_encoded_constants()
+    assert [p["action"] for p in plan] == ["register_host_resident"] * 4
+    total = sum(b.nbytes for b in blocks)
+    st = mod.residency_stats()
+    assert st["device_resident_bytes"] == 0 and st["pinned_host_bytes"] == total        # nothing on the device before the first run
+    sess = mod.create_session()
+    _check_bank(sess, qtypes, blocks, 1, 81)
+    assert mod.residency_stats()["device_resident_bytes"] == total                      # uploaded on first use, resident from then on
+    _check_bank(sess, qtypes, blocks, 5, 82)
+    assert mod.residency_stats()["device_resident_bytes"] == total
+    mod.close()
+
+
+def test_residency_sequential_offload(tmp_path):
+    art, qtypes, blocks = _bank_artifact(tmp_path, "sequential_offload")
+    mod = dml.runtime.load(art.path)
+    assert [p["offload_group"] for p in mod.load_encoded_constants()] == [0, 1, 2, 3]
+    sess = mod.create_session()
+    for run, m in enumerate((1, 3, 8)):
+        _check_bank(sess, qtypes, blocks, m, 90 + m)
+        st = mod.residency_stats()
+        # never resident: two slots of the largest weight hold whatever is in flight; every run streams all four weights
+        assert st["device_resident_bytes"] == 0 and st["device_slot_bytes"] >= 2 * max(b.nbytes for b in blocks)
+        assert st["device_slot_bytes"] < sum(b.nbytes for b in blocks)
+        assert st["uploads"] in (4 * (run + 1), 4 * (run + 1) - 1)      # the weight left in a slot by the last run may be reused
+    mod.close()
+
+
+def test_residency_grouped_offload(tmp_path):
+    # explicit groups: {w0, w1} {w2} {w3, w4, w5}; three groups through two slots
+    art, qtypes, blocks = _bank_artifact(tmp_path, "grouped_offload", count=6, groups=[0, 0, 1, 2, 2, 2])
+    mod = dml.runtime.load(art.path)
+    plan = mod.load_encoded_constants()
+    assert [p["offload_group"] - (1 << 20) for p in plan] == [0, 0, 1, 2, 2, 2]
+    sess = mod.create_session()
+    for m in (2, 7):
+        _check_bank(sess, qtypes, blocks, m, 100 + m)
+    st = mod.residency_stats()
+    assert st["device_resident_bytes"] == 0 and st["uploads"] >= 6
+    largest = max(sum(-(-b.nbytes // 256) * 256 for b, g in zip(blocks, [0, 0, 1, 2, 2, 2]) if g == gid) for gid in (0, 1, 2))
+    assert st["device_slot_bytes"] == 2 * largest
+    mod.close()
+    # two groups fit the two slots: after the first run nothing is uploaded again
+    art2, qtypes2, blocks2 = _bank_artifact(tmp_path / "b", "grouped_offload", count=4)
+    mod2 = dml.runtime.load(art2.path)
+    mod2.load_encoded_constants()                    # default grouping: two consecutive constants per group
+    sess2 = mod2.create_session()
+    _check_bank(sess2, qtypes2, blocks2, 1, 111)
+    first = mod2.residency_stats()["uploads"]
+    _check_bank(sess2, qtypes2, blocks2, 4, 112)
+    assert first == 4 and mod2.residency_stats()["uploads"] == 4
+    mod2.close()
+
+
+def test_run_numpy_replays_a_graph_in_steady_state(tmp_path):
+    n, k = 256, 1024
+    art, blocks, _ = _artifact(tmp_path, "Q4_K", n, k)
+    mod = dml.runtime.load(art.path)
+    mod.load_encoded_constants()
+    sess = mod.create_session()
+    x = S.random_activations(4, k, 5, "float32")
+    outs = [sess.run_numpy({"x": x})["t0"] for _ in range(5)]
+    st = sess.graph_stats()
+    assert st["cached_graphs"] == 1 and st["graph_launches"] == 4            # first call eager, captured on the second, replayed after
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+    ref = oracle.gemm_quant(S.bf16_bits_to_float32(S.float32_to_bf16_bits(x)), blocks, "Q4_K", n, k)
+    assert oracle.max_errors(ref, outs[-1])[2] <= 2e-2
+    y2 = sess.run_numpy({"x": S.random_activations(9, k, 6, "float32")})["t0"]      # another shape: its own plan and graph
+    assert y2.shape == (9, n) and sess.graph_stats()["cached_graphs"] == 1
+    sess.numpy_graph_replay = False
+    assert np.array_equal(sess.run_numpy({"x": x})["t0"], outs[0]) and sess.graph_stats()["graph_launches"] == 4
+    # the benchmark helpers of the reference loader
+    s1 = sess.benchmark_numpy({"x": x}, warmup=2, iterations=4)
+    xt = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    yt = torch.empty(4, n, device="cuda", dtype=torch.bfloat16)
+    s2 = sess.benchmark_device_pointers({"x": (xt.data_ptr(), (4, k), "bfloat16")}, {"t0": (yt.data_ptr(), (4, n), "bfloat16")}, warmup=2, iterations=4)
+    assert s1["iterations"] == 4 and s2["iterations"] == 4 and s1["min_ms"] > 0 and s2["min_ms"] > 0
+    mod.close()
+
+
+def test_profile_run_environment_contract(tmp_path, capfd, monkeypatch):
+    art, qtypes, blocks = _bank_artifact(tmp_path, "manual_runtime_load", count=3)
+    mod = dml.runtime.load(art.path)
+    mod.load_encoded_constants()
+    sess = mod.create_session()
+    monkeypatch.setenv("DINOML_PROFILE_RUN", "1")
+    monkeypatch.setenv("DINOML_PROFILE_RUN_VERBOSE", "1")
+    monkeypatch.setenv("DINOML_PROFILE_RUN_SECTIONS", "first_two:0:1,last:2:2")
+    _check_bank(sess, qtypes, blocks, 2, 120)
+    err = capfd.readouterr().err
+    assert "[dinoml_profile] total_gpu_ms=" in err and "[dinoml_profile] op=gemm_rcr count=3" in err
+    assert err.count("[dinoml_profile_launch] label=node") == 3
+    assert "[dinoml_profile_section] name=first_two start=0 end=1 ms=" in err and "[dinoml_profile_section] name=last start=2 end=2" in err
+    monkeypatch.setenv("DINOML_PROFILE_RUN_SECTIONS", "bad:5:9")
+    with pytest.raises(RuntimeError, match="did not match"):
+        sess.run_numpy({"x": S.random_activations(2, 1024, 1, "float32")})
+    mod.close()

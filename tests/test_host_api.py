@@ -38,6 +38,13 @@ def test_policy_tables_and_descriptor():
         c.materialize("float16", (1, 256))            # no host dequantizer: refuses instead of falling back
     with pytest.raises(NotImplementedError):
         cs.validate_gguf_constant_policy("dequantize_full_before_launch", "eager_dense_device", require_runtime_supported=True)
+    # the host-residency policies the reference only declares (src/dinoml/constant_sources.py:29-33) are implemented here
+    for residency in ("cpu_until_first_use", "sequential_offload", "grouped_offload", "manual_runtime_load", "eager_encoded_device"):
+        cs.validate_gguf_constant_policy("direct_dequantize_in_kernel", residency, require_runtime_supported=True)
+    g = dml.gguf_constant("x.gguf", "t", residency="grouped_offload", offload_group=3)
+    assert g.offload_group == 3
+    with pytest.raises(ValueError):
+        dml.gguf_constant("x.gguf", "t", residency="sequential_offload", offload_group=1)   # group numbers belong to grouped_offload
 
 
 def test_gguf_file_round_trip_and_hint_validation(tmp_path):
