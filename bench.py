@@ -661,6 +661,8 @@ def run_multi(args):
     from dinoml_v2_b200.gguf_blocks import encoded_nbytes
     _native.lib()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"                   # keep NCCL's version banner off stdout: rank 0 prints one JSON line
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
@@ -716,7 +718,7 @@ def run_multi(args):
         # Decode sizes go over peer memory (the GEMV kernel stores into every GPU's gather buffer, one small kernel
         # finishes each collective); NCCL is the fallback and is timed beside it.  Only a failure to SET UP the peer
         # buffers falls back; a wrong result or a device-side give-up is an error, and the ranks agree on the mode first.
-        want_peer = m <= 64 and use_peer_env
+        want_peer = use_peer_env
         peer_ok = False
         if want_peer:
             try:
@@ -727,7 +729,7 @@ def run_multi(args):
                 if rank == 0:
                     print(f"peer buffers unavailable ({type(exc).__name__}: {str(exc)[:200]}); using NCCL", file=sys.stderr)
         mode = "peer" if (want_peer and _all_ranks_agree(peer_ok, dev)) else "nccl"
-        nccl_ms = swiglu_ms = None
+        nccl_ms = peer_ms = swiglu_ms = None
         if mode == "peer":
             # correctness before timing: the peer all-reduce against NCCL's, several back-to-back calls on one exchange
             step_nccl()
@@ -748,7 +750,10 @@ def run_multi(args):
                 f0.swiglu_mlp_peer(x, got)
                 torch.cuda.synchronize()
                 assert float((want.float() - got.float()).abs().max()) <= 2e-2 * float(want.float().abs().max()), "fused gated MLP differs from NCCL"
-            nccl_ms = time_steps(step_nccl, half, W, stream, barrier=dist.barrier)
+            nccl_ms = _max_over_ranks(time_steps(step_nccl, half, W, stream, barrier=dist.barrier), dev)
+            peer_ms = _max_over_ranks(time_steps(step_peer, half, W, stream, barrier=dist.barrier), dev)
+            if nccl_ms < peer_ms:                           # large batches on few GPUs: NCCL's bandwidth-optimal rings win
+                mode = "nccl"
 
             def step_swiglu():                              # extra: the gated MLP with no all-gather at all
                 for f in ffns:
@@ -770,7 +775,8 @@ def run_multi(args):
                       "comm_is": "peer_exchange_kernel x 2 alone" if mode == "peer" else "ncclAllGather x 2 + ncclAllReduce alone",
                       "bound_by": None}
         if nccl_ms is not None:
-            results[m]["nccl_ms_per_ffn"] = _max_over_ranks(nccl_ms, dev) / half / r
+            results[m]["nccl_ms_per_ffn"] = nccl_ms / half / r
+            results[m]["peer_ms_per_ffn"] = peer_ms / half / r
         if swiglu_ms is not None:
             results[m]["fused_swiglu_mlp_ms_per_ffn"] = _max_over_ranks(swiglu_ms, dev) / half / r
         if m == 1:

@@ -64,25 +64,22 @@ int set_error_message(int rc, const std::string& message) {
 }
 const char* last_error() { return g_last_error.c_str(); }
 
-// Share of the persistent GEMV's CTA-rounds that do work when `tiles` 16-row tiles are dealt whole to its grid of at most
-// two CTAs per SM (1.0 = every CTA gets the same number of tiles).
-static double stream_split_efficiency(int n) {
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    sm_count = sms > 0 ? sms : 148;
-  }
-  const int tiles = (n + 15) / 16, ctas = tiles < 2 * sm_count ? tiles : 2 * sm_count;
-  const int rounds = (tiles + ctas - 1) / ctas;
-  return double(tiles) / (double(rounds) * ctas);
-}
-
 int select_variant(int qtype, int dtype, int m, int n, int k) {
-  // M <= 8 on Q4_K: the persistent bulk-copy GEMV, measured faster than or level with the tile kernel on every benchmarked
-  // shape for M >= 2 and for M = 1 unless its whole-tile split leaves more than a fifth of the last round idle
-  // ([11008 x 4096]: 688 tiles on 296 CTAs = 2.3 rounds; the tile kernel is 9 % faster there).
-  if (gemv_stream_supports(qtype, dtype, m, n, k) && (m >= 2 || stream_split_efficiency(n) >= 0.8)) return DINOML_B200_GGUF_VARIANT_STREAM;
+  // M <= 8 on Q4_K: the persistent bulk-copy GEMV - measured faster than the tile kernel for every M >= 2 and, at M = 1,
+  // wherever the tile kernel's grid (three CTAs of 16 rows per SM) leaves more than a quarter of its last wave idle or
+  // does not fill one wave; where the tile kernel's waves are fuller it keeps a 2 - 10 % lead at M = 1
+  // ([11008 x 4096]: 9.4 us against 10.5 us) and is chosen.  A profiled execution plan overrides this per shape.
+  if (gemv_stream_supports(qtype, dtype, m, n, k)) {
+    bool tile_kernel = false;
+    if (m == 1) {
+      int sms = 148, dev = 0;
+      if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      const int tiles = (n + 15) / 16, slots = 3 * (sms > 0 ? sms : 148);
+      const int waves = (tiles + slots - 1) / slots;
+      tile_kernel = tiles >= slots && double(tiles) / (double(waves) * slots) >= 0.75;
+    }
+    if (!tile_kernel) return DINOML_B200_GGUF_VARIANT_STREAM;
+  }
   // M = 9..16 is served by both tensor-core kernels: the tcgen05 one costs the same whatever M is and wins there once
   // the weight is large enough to spread over the SMs; the mma.sync GEMV does twice the MMA work of M <= 8.
   if (m >= 9 && m <= 16 && n >= 2048 && gemm_umma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_UMMA;

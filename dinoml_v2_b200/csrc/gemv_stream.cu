@@ -4,8 +4,14 @@
 // Same exact-integer tensor-core arithmetic as the tile kernel in gemv_mma.cu (quants become 16-bit floats 128+q /
 // 1024+q, mma.sync.m16n8k16 with fp32 accumulation, per-sub-block scales applied in fp32, the offsets folded against
 // per-sub-block activation sums); what changes is how the bytes move and how the work is cut:
-//   * grid = one CTA per SM (or two), CTA c owns the contiguous 16-row tiles [tile_begin(c), tile_begin(c+1)) - no tail
-//     wave, one prologue (activation sums) per SM instead of one per tile;
+//   * grid = one CTA per SM (or two).  The work of a launch is a line of units (16-row tile t, K chunk of 8 super-blocks),
+//     tile-major; CTA c owns the contiguous range [c * U / G, (c + 1) * U / G), so every CTA moves the same number of bytes
+//     whatever the tile count (688 tiles on 296 CTAs would otherwise be 2 or 3 tiles each).  A CTA walks its range from
+//     the highest unit down: a tile cut between two CTAs is the FIRST thing the lower-numbered CTA computes (it leaves
+//     its partial sums, 16 x M floats, in a small global workspace and raises a flag) and the LAST thing the
+//     higher-numbered one computes (it adds the partial, lowers the flag and stores) - no waiting in practice, the
+//     dependency points to a lower-numbered CTA, which is dispatched first, and the summation order is fixed.  One
+//     prologue (activation sums) per CTA instead of one per tile;
 //   * one producer warp issues, per (tile, K chunk of 8 super-blocks), sixteen 1-D bulk copies (cp.async.bulk, one per
 //     weight row, 1152 B each) into a ring of D shared-memory stages; a stage is "full" when its bytes have landed
 //     (mbarrier transaction count) and "empty" when its 8 consumer warps have arrived.  The ring runs across tile
@@ -18,12 +24,13 @@
 //     reads activations or writes outputs first waits for the preceding kernel (griddepcontrol.wait).  With the
 //     one-CTA-per-SM grid and at most half of an SM's shared memory and registers per CTA, the next launch's CTAs sit
 //     beside this launch's and fill their rings while this one finishes.
-// Every mbarrier wait is bounded; a wait that gives up records a code (11..14) in the library's status word, raises
-// the CTA's abort flag, the producer waits for the copies it has in flight, and every role returns.
+// Every wait (mbarriers, the partial-tile flag) is bounded; one that gives up records a code (11..15) in the library's
+// status word, raises the CTA's abort flag, the producer waits for the copies it has in flight, and every role returns.
 //
 // Behavioural ancestor in the reference: the small-M kernels of the fused prototype
 // (kernels/rocm/src/ck_gguf_q8_gemm.hip:1009-1166); the reference's CUDA path dequantizes the whole weight and runs a
 // dense Sm80 GEMM instead (src/dinoml/lowering/ops/gemm.py:729-749).
+#include <map>
 #include <type_traits>
 
 #include "gemv_stream_common.cuh"
@@ -60,7 +67,7 @@ template <int MXC, int NG, int D> constexpr size_t smem_fixed_bytes() {
 template <typename T, int MXC, int NG, int D, bool PROBE>
 __global__ void __launch_bounds__((NG * kGroupWarps + 2) * 32, NG == 1 ? 2 : 1)
 gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
-                       int m, int n, int k, int* status, const PeerOut peers) {
+                       int m, int n, int k, int* status, float* __restrict__ partial, int* __restrict__ flags, int mode, const PeerOut peers) {
   using MT = MmaType<T>;
   constexpr int NCW = NG * kGroupWarps;
   constexpr int MC = MXC == 1 ? 1 : 2;             // accumulator columns a lane keeps
@@ -82,9 +89,19 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
   const int nsb = k >> 8, nsub = k >> 5;
   const int nchunks = (nsb + kKC - 1) / kKC;
   const int tiles = (n + kRows - 1) / kRows;
-  const int t0 = tile_begin(blockIdx.x, tiles, gridDim.x), t1 = tile_begin(blockIdx.x + 1, tiles, gridDim.x);
-  const int ntiles = t1 - t0;
-  const int nunits = ntiles * nchunks;
+  // this CTA's units [u0, u1) of the tile-major line; walked from u1 - 1 down
+  const int64_t total_units = int64_t(tiles) * nchunks;
+  const bool descending = (mode & 1) != 0, unit_split = (mode & 2) != 0;
+  const int u0 = unit_split ? int((int64_t(blockIdx.x) * total_units) / gridDim.x) : tile_begin(blockIdx.x, tiles, gridDim.x) * nchunks;
+  const int u1 = unit_split ? int((int64_t(blockIdx.x + 1) * total_units) / gridDim.x) : tile_begin(blockIdx.x + 1, tiles, gridDim.x) * nchunks;
+  const int nunits = u1 - u0;
+  const int t_hi = (u1 - 1) / nchunks, t_lo = u0 / nchunks;
+  const int ntiles = t_hi - t_lo + 1;               // tiles touched
+  // a tile cut between two CTAs: the CTA that walks it FIRST leaves a partial, the one that walks it LAST adds it and stores
+  const bool hi_cut = u1 % nchunks != 0, lo_cut = u0 % nchunks != 0;
+  const bool first_cut = descending ? hi_cut : lo_cut, last_cut = descending ? lo_cut : hi_cut;
+  const int other = descending ? int(blockIdx.x) - 1 : int(blockIdx.x) + 1;     // the CTA whose partial this one adds
+  const int g_first = descending ? u1 - 1 : u0, dir = descending ? -1 : 1;
   const int64_t row_bytes = int64_t(nsb) * kSbBytes;
   volatile int* abort_flag = &s_abort;
 
@@ -112,7 +129,7 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
   if (warp == NCW) {
     // ------------------------------------------------------------------ producer: weights are constants, no dependency wait
     bool ok = true;
-    int issued = 0, tile = t0, chunk = 0;
+    int issued = 0, tile = g_first / nchunks, chunk = g_first % nchunks;
     const uint32_t sW_u32 = smem_u32(sW);
     for (int u = 0; u < nunits; ++u) {
       const int slot = u % D, it = u / D;
@@ -129,7 +146,9 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
         bulk_load(sW_u32 + uint32_t(slot) * kStageBytes + uint32_t(lane) * kPitch,
                   w + int64_t(tile * kRows + lane) * row_bytes + int64_t(chunk) * (kKC * kSbBytes), bytes_row, full(slot));
       issued = u + 1;
-      if (++chunk == nchunks) { chunk = 0; ++tile; }
+      chunk += dir;
+      if (chunk < 0) { chunk = nchunks - 1; --tile; }
+      else if (chunk == nchunks) { chunk = 0; ++tile; }
     }
     if (!ok && lane == 0)       // aborting: the copies still in flight must land before this CTA's shared memory goes away
       for (int v = max(0, issued - D); v < issued; ++v) mbar_wait_plain(full(v % D), uint32_t(v / D) & 1u);
@@ -141,8 +160,35 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
 
   if (warp == NCW + 1) {
     // ------------------------------------------------------------------ epilogue warp
+    __shared__ float sPart[kRows * 8];      // the neighbouring CTA's partial sums of the cut tile, fetched as soon as they exist
+    bool have_partial = !last_cut;
+    // Fetches the neighbour's partial if its flag is up (blocking = keep polling, bounded); all lanes return the same answer.
+    auto fetch_partial = [&](bool blocking) -> bool {
+      const int* flag = flags + other;
+      int seen = 0;
+      if (lane == 0) {
+        seen = ld_acquire_gpu(flag) != 0;
+        if (!seen && blocking) {
+          const uint64_t start = globaltimer_ns();
+          for (uint32_t i = 0; i < kSpinLimit && !seen; ++i) {
+            __nanosleep(40);
+            seen = ld_acquire_gpu(flag) != 0;
+            if (!seen && (i & 63u) == 63u && (*abort_flag || globaltimer_ns() - start > kWaitLimitNs)) break;
+          }
+          if (!seen) { *abort_flag = 1; atomicCAS(status, 0, ST_STREAM_PARTIAL); }
+        }
+      }
+      seen = __shfl_sync(0xffffffffu, seen, 0);
+      if (!seen) return false;
+      const float* theirs = partial + size_t(other) * (kRows * 8);
+      for (int idx = lane; idx < kRows * MXC; idx += 32) sPart[idx] = __ldcg(theirs + idx);
+      __syncwarp();
+      if (lane == 0) st_release_gpu(flags + other, 0);      // lowered by its only reader: nothing to clear between launches
+      return true;
+    };
     for (int tl = 0; tl < ntiles; ++tl) {
       const int buf = tl & 1;
+      if (!have_partial) have_partial = fetch_partial(false);      // off the critical path: the neighbour wrote it at its start
       if (!(__all_sync(0xffffffffu, mbar_wait(red_full(buf), uint32_t(tl >> 1) & 1u, abort_flag, status, ST_STREAM_RED_FULL) ? 1 : 0))) break;
       const Red& rb = sRed[buf];
       for (int idx = lane; idx < kRows * MXC; idx += 32) {
@@ -157,7 +203,23 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(red_empty(buf));
-      const int tile = t0 + tl;
+      const int tile = descending ? t_hi - tl : t_lo + tl;
+      if (tl == 0 && first_cut) {
+        // the rest of this tile belongs to the neighbouring CTA, which reaches it last: leave the partial sums, raise the flag
+        float* mine = partial + size_t(blockIdx.x) * (kRows * 8);
+        for (int idx = lane; idx < kRows * MXC; idx += 32) mine[idx] = sOut[idx];
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(flags + blockIdx.x, 1);
+        continue;
+      }
+      if (tl == ntiles - 1 && last_cut) {
+        // the other chunks of this tile were computed by the neighbouring CTA at the start of its walk
+        if (!have_partial) have_partial = fetch_partial(true);
+        if (!have_partial) break;
+        for (int idx = lane; idx < kRows * MXC; idx += 32) sOut[idx] += sPart[idx];
+        __syncwarp();
+      }
       for (int idx = lane; idx < kRows * MXC; idx += 32) {
         const int r = idx & (kRows - 1), c = idx >> 4;
         const int row = tile * kRows + r;
@@ -235,7 +297,9 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
     if (lane == 0) mbar_arrive(red_full(buf));
   };
 
-  int tl = 0, chunk = grp;
+  // local unit u is global unit g_first + dir * u: its chunk moves by dir, its local tile index counts up
+  int tl = 0, chunk = g_first % nchunks + dir * grp;
+  while (chunk < 0 && tl < ntiles) { chunk += nchunks; ++tl; }
   while (chunk >= nchunks && tl < ntiles) { chunk -= nchunks; ++tl; }
   for (int u = grp; u < nunits && ok; u += NG) {
     while (cur_tile < tl && ok) { flush(cur_tile); ++cur_tile; }
@@ -312,7 +376,8 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
     }
     __syncwarp();                              // every lane is done with the stage (and with sS)
     if (lane == 0) mbar_arrive(empty(slot));
-    chunk += NG;
+    chunk += dir * NG;
+    while (chunk < 0) { chunk += nchunks; ++tl; }
     while (chunk >= nchunks) { chunk -= nchunks; ++tl; }
   }
   // the tiles this warp has not flushed yet (all of them contribute to every tile's reduction, zeros included)
@@ -334,9 +399,38 @@ int* stream_status_ptr() {
   return ptr[dev];
 }
 
+// Partial-tile workspace and flags: one set per (device, stream) - launches on one stream are ordered (a launch writes its
+// partials only after the preceding kernel has completed, see griddepcontrol.wait above) and may share it, launches on
+// different streams may overlap and must not.  kMaxCtas partial tiles of 16 x 8 floats and as many flag words, zeroed
+// once; every flag a launch raises is lowered again by the CTA that consumes it.
+constexpr int kMaxCtas = 1024;
+struct Scratch { float* partial = nullptr; int* flags = nullptr; };
+struct ScratchKey {
+  int dev;
+  cudaStream_t stream;
+  bool operator<(const ScratchKey& o) const { return dev != o.dev ? dev < o.dev : stream < o.stream; }
+};
+static std::mutex g_scratch_mutex;
+static std::map<ScratchKey, Scratch> g_scratch;
+
+static int stream_scratch(cudaStream_t stream, Scratch* out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return RC_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  Scratch& sc = g_scratch[ScratchKey{dev, stream}];
+  if (sc.partial == nullptr) {
+    // allocated outside of stream capture only: callers warm a shape up once before capturing a graph
+    if (cudaMalloc(&sc.partial, size_t(kMaxCtas) * kRows * 8 * sizeof(float)) != cudaSuccess) return RC_LAUNCH;
+    if (cudaMalloc(&sc.flags, size_t(kMaxCtas) * sizeof(int)) != cudaSuccess) { cudaFree(sc.partial); sc.partial = nullptr; return RC_LAUNCH; }
+    cudaMemset(sc.flags, 0, size_t(kMaxCtas) * sizeof(int));
+  }
+  *out = sc;
+  return RC_OK;
+}
+
 template <typename T, int MXC, int NG, int D, bool PROBE = false>
 static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int ctas_per_sm, const PeerOut& peers,
-                          cudaStream_t s) {
+                          cudaStream_t s, int mode = 3) {     // mode: bit 0 = walk downwards, bit 1 = split at unit granularity
   const size_t smem = smem_fixed_bytes<MXC, NG, D>() + size_t(k / 32) * MXC * sizeof(float);
   if (smem > 216 * 1024) return RC_RANGE;            // + up to 9 KB of static shared memory, under the 227 KB per CTA
   int* status = stream_status_ptr();
@@ -347,9 +441,13 @@ static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* 
   int sm_count = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = (n + kRows - 1) / kRows;
-  const int ctas = min(tiles, sm_count * (ctas_per_sm < 1 ? 1 : ctas_per_sm));
+  // never more CTAs than tiles: a CTA then owns at least one tile's worth of units, so a tile is cut between two CTAs at most
+  const int ctas = min(min(tiles, sm_count * (ctas_per_sm < 1 ? 1 : ctas_per_sm)), kMaxCtas);
+  Scratch sc;
+  if (int rc = stream_scratch(s, &sc)) return rc;
   const cudaError_t err = gemv_launch(kern, ctas, 1, (NG * kGroupWarps + 2) * 32, smem, s, static_cast<const T*>(a),
-                                      static_cast<const uint8_t*>(b), static_cast<const T*>(bias), static_cast<T*>(c), m, n, k, status, peers);
+                                      static_cast<const uint8_t*>(b), static_cast<const T*>(bias), static_cast<T*>(c), m, n, k, status,
+                                      sc.partial, sc.flags, mode, peers);
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
@@ -428,7 +526,15 @@ int stream_device_status() {
   int value = 0;
   if (status == nullptr) return -1;
   if (cudaMemcpy(&value, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  if (value != 0) cudaMemset(status, 0, sizeof(int));
+  if (value != 0) {
+    // a launch that gave up may have left partial-tile flags raised: lower them with the word
+    cudaMemset(status, 0, sizeof(int));
+    int dev = -1;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(stream::g_scratch_mutex);
+    for (auto& entry : stream::g_scratch)
+      if (entry.first.dev == dev && entry.second.flags != nullptr) cudaMemset(entry.second.flags, 0, size_t(stream::kMaxCtas) * sizeof(int));
+  }
   return value;
 }
 

@@ -17,7 +17,7 @@ namespace stream {
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // a wait gives up after two seconds of wall time ...
 constexpr uint32_t kSpinLimit = 1u << 28;           // ... or this many polls, whichever comes first
-enum : int { ST_STREAM_FULL = 11, ST_STREAM_EMPTY = 12, ST_STREAM_RED_FULL = 13, ST_STREAM_RED_EMPTY = 14 };
+enum : int { ST_STREAM_FULL = 11, ST_STREAM_EMPTY = 12, ST_STREAM_RED_FULL = 13, ST_STREAM_RED_EMPTY = 14, ST_STREAM_PARTIAL = 15 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -82,6 +82,12 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                "r"(bytes), "r"(bar)
                : "memory");
 }
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) { asm volatile("st.release.gpu.global.s32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
 }
