@@ -590,7 +590,8 @@ PROFILE_CASES = {  # name -> (qtype, n, k, m, variant, weight copies): small, ea
     "gemv_q4k_m1": ("Q4_K", 11008, 4096, 1, "mma", 6),
     "gemv_stream_q4k_m1_c1": ("Q4_K", 11008, 4096, 1, "stream:1", 6),
     "gemv_stream_q4k_m1_c4": ("Q4_K", 11008, 4096, 1, "stream:4", 6),
-    "gemv_stream_q4k_m1_c5": ("Q4_K", 11008, 4096, 1, "stream:5", 6),
+    "gemv_stream_q4k_m4": ("Q4_K", 11008, 4096, 4, "stream", 6),
+    "gemv_stream_q6k_m1": ("Q6_K", 4096, 14336, 1, "stream", 3),
     "gemv_stream_probe_q4k_c4": ("Q4_K", 11008, 4096, 1, "stream:132", 6),
     "gemv_q4k_m4": ("Q4_K", 11008, 4096, 4, "mma", 6),
     "gemm_umma_q4k_m16": ("Q4_K", 11008, 4096, 16, "umma", 6),

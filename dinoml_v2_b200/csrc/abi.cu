@@ -65,18 +65,22 @@ int set_error_message(int rc, const std::string& message) {
 const char* last_error() { return g_last_error.c_str(); }
 
 int select_variant(int qtype, int dtype, int m, int n, int k) {
-  // M <= 8 on Q4_K: the persistent bulk-copy GEMV - measured faster than the tile kernel for every M >= 2 and, at M = 1,
-  // wherever the tile kernel's grid (three CTAs of 16 rows per SM) leaves more than a quarter of its last wave idle or
-  // does not fill one wave; where the tile kernel's waves are fuller it keeps a 2 - 10 % lead at M = 1
-  // ([11008 x 4096]: 9.4 us against 10.5 us) and is chosen.  A profiled execution plan overrides this per shape.
+  // M <= 8 on Q4_K / Q6_K: the persistent bulk-copy GEMV, except where the tile kernel measured faster:
+  //   Q4_K, M = 1, when the tile kernel's grid (three CTAs of 16 rows per SM) fills at least three quarters of its last wave
+  //   ([11008 x 4096]: 9.4 us against 10.5 us; with emptier waves or less than one wave the persistent kernel wins);
+  //   Q6_K, M >= 3, on weights below 32 M elements ([4096 x 4096], M = 4: 6.5 us against 6.8 us), where the launch is too short
+  //   for the ring to pay off (at M <= 2 and on larger weights it is 7 - 30 % faster: [4096 x 14336], M = 1: 15.0 us against 21.1 us).
+  // A profiled execution plan overrides this per shape.
   if (gemv_stream_supports(qtype, dtype, m, n, k)) {
     bool tile_kernel = false;
-    if (m == 1) {
+    if (qtype == QTYPE_Q4_K && m == 1) {
       int sms = 148, dev = 0;
       if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       const int tiles = (n + 15) / 16, slots = 3 * (sms > 0 ? sms : 148);
       const int waves = (tiles + slots - 1) / slots;
-      tile_kernel = tiles >= slots && double(tiles) / (double(waves) * slots) >= 0.75;
+      tile_kernel = tiles <= sms || (tiles >= slots && double(tiles) / (double(waves) * slots) >= 0.75);   // also: fewer tiles than SMs
+    } else if (qtype == QTYPE_Q6_K && m >= 3) {
+      tile_kernel = int64_t(n) * k < (int64_t(32) << 20);
     }
     if (!tile_kernel) return DINOML_B200_GGUF_VARIANT_STREAM;
   }

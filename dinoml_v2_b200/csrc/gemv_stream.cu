@@ -1,7 +1,8 @@
-// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations, Q4_K weights.
+// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations, Q4_K and Q6_K weights.
 //
-// C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), W streamed once from HBM as packed GGUF blocks (144 B per 256 weights).
-// Same exact-integer tensor-core arithmetic as the tile kernel in gemv_mma.cu (quants become 16-bit floats 128+q /
+// C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), W streamed once from HBM as packed GGUF blocks (Q4_K 144 B, Q6_K 210 B per
+// 256 weights; Q6_K needs K % 2048 == 0 so that every row piece starts on a 16-byte boundary, other K stay with the tile
+// kernel).  Same exact-integer tensor-core arithmetic as the tile kernels in gemv_mma.cu / gemv_q6k_mma.cu (quants become 16-bit floats 128+q /
 // 1024+q, mma.sync.m16n8k16 with fp32 accumulation, per-sub-block scales applied in fp32, the offsets folded against
 // per-sub-block activation sums); what changes is how the bytes move and how the work is cut:
 //   * grid = one CTA per SM (or two).  The work of a launch is a line of units (16-row tile t, K chunk of 8 super-blocks),
@@ -33,6 +34,7 @@
 #include <map>
 #include <type_traits>
 
+#include "gemv_q6k_common.cuh"
 #include "gemv_stream_common.cuh"
 
 namespace b200gguf {
@@ -43,9 +45,12 @@ namespace stream {
 
 constexpr int kRows = 16;                       // weight rows per tile (one MMA M-tile)
 constexpr int kKC = 8;                          // super-blocks per row per stage: one per consumer warp of a group
-constexpr int kSbBytes = 144;
-constexpr int kPitch = kKC * kSbBytes + 32;     // 1184 B: 8-byte reads of 4 rows x 4 lanes (a half-warp) hit 32 distinct banks
-constexpr int kStageBytes = kRows * kPitch;     // 18944 B per ring slot
+// Bytes per super-block and shared-memory row pitch of a stage.  Q4_K: 8 x 144 + 32 = 1184 B, so that the 8-byte reads of 4
+// rows x 4 lanes (a half-warp) hit 32 distinct banks.  Q6_K: 8 x 210 = 1680 B is 16 (mod 128) by itself, which spreads the
+// 4-byte reads of 8 rows x 4 lanes over all banks; a block starts 2 bytes off a word boundary in every odd super-block.
+template <int QT> struct Geom;
+template <> struct Geom<QTYPE_Q4_K> { static constexpr int kSbBytes = 144, kPitch = kKC * 144 + 32; };
+template <> struct Geom<QTYPE_Q6_K> { static constexpr int kSbBytes = 210, kPitch = kKC * 210; };
 constexpr int kGroupWarps = kKC;
 constexpr int kBarBytes = 256;                  // mbarrier area in front of the ring (up to 32 barriers)
 
@@ -56,21 +61,23 @@ template <int MXC, int NCW> struct RedBuf {
   float xt[NCW][kRows][MXC];     // per consumer warp: sum_j (MAGIC * ds + dm) * X
 };
 
-template <int MXC, int NG, int D> constexpr size_t smem_fixed_bytes() {
-  return kBarBytes /* barriers */ + size_t(D) * kStageBytes + 2 * sizeof(RedBuf<MXC, NG * kGroupWarps>);
+template <int QT, int MXC, int NG, int D> constexpr size_t smem_fixed_bytes() {
+  return kBarBytes /* barriers */ + size_t(D) * kRows * Geom<QT>::kPitch + 2 * sizeof(RedBuf<MXC, NG * kGroupWarps>);
 }
 
 // MXC: activation rows covered (power of two >= m, <= 8).  NG: groups of 8 consumer warps.  D: ring slots (D % NG == 0).
 // Threads: NG * 8 consumer warps, then the producer warp, then the epilogue warp.
 // PROBE: bandwidth probe - the bytes move through the ring exactly as usual, the consumers skip the arithmetic (the
 // output is all zeros); it measures what the data path alone sustains for a shape.
-template <typename T, int MXC, int NG, int D, bool PROBE>
+template <int QT, typename T, int MXC, int NG, int D, bool PROBE>
 __global__ void __launch_bounds__((NG * kGroupWarps + 2) * 32, NG == 1 ? 2 : 1)
-gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
+gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
                        int m, int n, int k, int* status, float* __restrict__ partial, int* __restrict__ flags, int mode, const PeerOut peers) {
   using MT = MmaType<T>;
   constexpr int NCW = NG * kGroupWarps;
   constexpr int MC = MXC == 1 ? 1 : 2;             // accumulator columns a lane keeps
+  constexpr int kSbBytes = Geom<QT>::kSbBytes, kPitch = Geom<QT>::kPitch, kStageBytes = kRows * kPitch;
+  constexpr bool kMinTerm = QT == QTYPE_Q4_K;      // Q4_K folds its mins and the operand offset against activation sums; Q6_K has neither
   static_assert(D % NG == 0 && D >= 2 * NG, "every group needs its own ring slots, at least two");
   static_assert(MXC == 1 || MXC == 2 || MXC == 4 || MXC == 8, "MXC");
   using Red = RedBuf<MXC, NCW>;
@@ -80,7 +87,7 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
   uint8_t* sW = smem_dyn + kBarBytes;                                         // D x kStageBytes
   Red* sRed = reinterpret_cast<Red*>(sW + size_t(D) * kStageBytes);      // [2]
   float* sX = reinterpret_cast<float*>(sRed + 2);                        // [MXC][k/32]
-  __shared__ __align__(16) float sS[NCW][kRows][8];                      // ds per row, sub-block (warp-private scratch)
+  __shared__ __align__(16) float sS[NCW][kRows][QT == QTYPE_Q6_K ? kQ6ScalePitch : 8];   // d * sc per row, sub-block (warp-private scratch)
   __shared__ float sOut[kRows * MXC];                                    // epilogue warp scratch
   __shared__ int s_abort;
   static_assert((2 * D + 4) * 8 <= kBarBytes, "barrier area");
@@ -251,7 +258,7 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
   const int srow = lane >> 1, shalf = lane & 1;   // scale-decode role of this lane
 
   // X[c][j] = sum of activations of row c over sub-block j (rows >= m are zero)
-  for (int i = tid; i < nsub * MXC; i += NCW * 32) {
+  for (int i = tid; kMinTerm && i < nsub * MXC; i += NCW * 32) {
     const int c = i / nsub, j = i - c * nsub;
     float s = 0.f;
     if (c < m) {
@@ -263,13 +270,14 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
   }
   named_barrier(1, NCW * 32);
 
-  float res[4] = {0.f, 0.f, 0.f, 0.f};
+  float res[1][4] = {{0.f, 0.f, 0.f, 0.f}};
   float zero4[4];
   opaque_zero4(zero4);
   float xt[MXC];
 #pragma unroll
   for (int c = 0; c < MXC; ++c) xt[c] = 0.f;
-  const T* xrow = x + int64_t(min(g, m - 1)) * k + 8 * t;
+  const T* xbase = x + int64_t(min(g, m - 1)) * k;   // rows >= m read a clamped (valid) row; their columns are never stored
+  const T* xrow = xbase + 8 * t;
 
   bool ok = true;
   int cur_tile = 0;                             // tile (local index) the accumulators belong to
@@ -279,20 +287,20 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
     if (!ok) return;
     Red& rb = sRed[buf];
     if (2 * t < MXC) {
-      rb.red[cw][g][2 * t] = res[0];
-      rb.red[cw][g + 8][2 * t] = res[2];
+      rb.red[cw][g][2 * t] = res[0][0];
+      rb.red[cw][g + 8][2 * t] = res[0][2];
       if (MC == 2) {
-        rb.red[cw][g][2 * t + 1] = res[1];
-        rb.red[cw][g + 8][2 * t + 1] = res[3];
+        rb.red[cw][g][2 * t + 1] = res[0][1];
+        rb.red[cw][g + 8][2 * t + 1] = res[0][3];
       }
     }
 #pragma unroll
     for (int c = 0; c < MXC; ++c) {
-      const float both = xt[c] + __shfl_xor_sync(0xffffffffu, xt[c], 1);
+      const float both = kMinTerm ? xt[c] + __shfl_xor_sync(0xffffffffu, xt[c], 1) : 0.f;
       if (shalf == 0) rb.xt[cw][srow][c] = both;
       xt[c] = 0.f;
     }
-    res[0] = res[1] = res[2] = res[3] = 0.f;
+    res[0][0] = res[0][1] = res[0][2] = res[0][3] = 0.f;
     __syncwarp();
     if (lane == 0) mbar_arrive(red_full(buf));
   };
@@ -308,7 +316,17 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
     ok = __all_sync(0xffffffffu, mbar_wait(full(slot), uint32_t(u / D) & 1u, abort_flag, status, ST_STREAM_FULL) ? 1 : 0) != 0;
     if (!ok) break;
     const int sb = chunk * kKC + wq;
-    if (!PROBE && sb < nsb) {
+    if (!PROBE && sb < nsb && QT == QTYPE_Q6_K) {
+      if constexpr (QT == QTYPE_Q6_K) {
+        // row pitch and stage size are multiples of 4, so a block's phase against a word boundary is that of wq * 210
+        const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
+        const T* const xr[1] = {xbase + 4 * t};                // this lane's four K positions of every 16-wide sub-block
+        if (wq & 1)
+          q6k_superblock<T, 1, MC, Q6_ODD>(st + srow * kPitch, st + g * kPitch, st + (g + 8) * kPitch, sS[cw], xr, sb, lane, res);
+        else
+          q6k_superblock<T, 1, MC, Q6_ALIGNED>(st + srow * kPitch, st + g * kPitch, st + (g + 8) * kPitch, sS[cw], xr, sb, lane, res);
+      }
+    } else if (!PROBE && sb < nsb) {
       const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
       {  // lane pair (srow, shalf): 4 sub-block scales -> ds to shared memory, min/MAGIC term folded against X
         const uint4 hdr = *reinterpret_cast<const uint4*>(st + srow * kPitch);
@@ -365,11 +383,11 @@ gemv_q4k_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, c
           MT::mma_c(acc, a_lo, xb.x, xb.y, zero4);
           MT::mma(acc, a_hi, xb.z, xb.w);
           const float dsr0 = ds_a[2 * G + h], dsr1 = ds_b[2 * G + h];
-          res[0] = fmaf(dsr0, acc[0], res[0]);
-          res[2] = fmaf(dsr1, acc[2], res[2]);
+          res[0][0] = fmaf(dsr0, acc[0], res[0][0]);
+          res[0][2] = fmaf(dsr1, acc[2], res[0][2]);
           if (MC == 2) {
-            res[1] = fmaf(dsr0, acc[1], res[1]);
-            res[3] = fmaf(dsr1, acc[3], res[3]);
+            res[0][1] = fmaf(dsr0, acc[1], res[0][1]);
+            res[0][3] = fmaf(dsr1, acc[3], res[0][3]);
           }
         }
       }
@@ -428,14 +446,14 @@ static int stream_scratch(cudaStream_t stream, Scratch* out) {
   return RC_OK;
 }
 
-template <typename T, int MXC, int NG, int D, bool PROBE = false>
-static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int ctas_per_sm, const PeerOut& peers,
+template <int QT, typename T, int MXC, int NG, int D, bool PROBE = false>
+static int launch_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int ctas_per_sm, const PeerOut& peers,
                           cudaStream_t s, int mode = 3) {     // mode: bit 0 = walk downwards, bit 1 = split at unit granularity
-  const size_t smem = smem_fixed_bytes<MXC, NG, D>() + size_t(k / 32) * MXC * sizeof(float);
+  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + (QT == QTYPE_Q4_K ? size_t(k / 32) * MXC * sizeof(float) : 0);
   if (smem > 216 * 1024) return RC_RANGE;            // + up to 9 KB of static shared memory, under the 227 KB per CTA
   int* status = stream_status_ptr();
   if (status == nullptr) return RC_LAUNCH;
-  auto kern = gemv_q4k_stream_kernel<T, MXC, NG, D, PROBE>;
+  auto kern = gemv_stream_kernel<QT, T, MXC, NG, D, PROBE>;
   static SmemOptIn granted;
   if (!smem_opt_in(kern, smem, granted)) return RC_LAUNCH;
   int sm_count = 148, dev = 0;
@@ -452,52 +470,62 @@ static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* 
 }
 
 // Tuning configurations (the `config` byte of a variant code, see dinoml_b200_gguf.h).  0 = the default for the shape.
-//   1: 8 consumer warps, 5 ring slots (95 KB), one CTA per SM - two launches fit side by side on an SM
-//   2: 16 consumer warps, 6 ring slots, one CTA per SM
-//   3: 16 consumer warps, 8 ring slots, one CTA per SM
-//   4: 8 consumer warps, 4 ring slots, two CTAs per SM
+//   1: 8 consumer warps, 5 ring slots (Q6_K: 4), one CTA per SM - two launches fit side by side on an SM
+//   2: 16 consumer warps, 6 ring slots (Q6_K: 4), one CTA per SM
+//   3: 16 consumer warps, 8 ring slots (Q6_K: 6), one CTA per SM
+//   4: 8 consumer warps, 4 ring slots (Q6_K: 3), two CTAs per SM
+// A Q6_K stage is 26.3 KB against 18.5 KB for Q4_K, hence the shallower rings.
 // Bit 7 of the configuration byte (0x80 | 1..4) selects the bandwidth probe of that configuration (bfloat16, M = 1).
 constexpr int kStreamConfigs = 4;
 constexpr int kProbeBit = 0x80;
-template <typename T, int MXC>
-static int launch_q4k_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
-                        cudaStream_t s) {
+template <int QT, typename T, int MXC>
+static int launch_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
+                    cudaStream_t s) {
+  constexpr bool Q6 = QT == QTYPE_Q6_K;
   if (config & kProbeBit) {
     if constexpr (MXC == 1 && std::is_same<T, __nv_bfloat16>::value) {
       switch (config & ~kProbeBit) {
-        case 1: return launch_q4k_cfg<T, 1, 1, 5, true>(a, b, bias, c, m, n, k, 1, peers, s);
-        case 2: return launch_q4k_cfg<T, 1, 2, 6, true>(a, b, bias, c, m, n, k, 1, peers, s);
-        case 3: return launch_q4k_cfg<T, 1, 2, 8, true>(a, b, bias, c, m, n, k, 1, peers, s);
-        case 4: return launch_q4k_cfg<T, 1, 1, 4, true>(a, b, bias, c, m, n, k, 2, peers, s);
+        case 1: return launch_cfg<QT, T, 1, 1, Q6 ? 4 : 5, true>(a, b, bias, c, m, n, k, 1, peers, s);
+        case 2: return launch_cfg<QT, T, 1, 2, Q6 ? 4 : 6, true>(a, b, bias, c, m, n, k, 1, peers, s);
+        case 3: return launch_cfg<QT, T, 1, 2, Q6 ? 6 : 8, true>(a, b, bias, c, m, n, k, 1, peers, s);
+        case 4: return launch_cfg<QT, T, 1, 1, Q6 ? 3 : 4, true>(a, b, bias, c, m, n, k, 2, peers, s);
         default: return RC_RANGE;
       }
     }
     return RC_RANGE;
   }
+  if (config == 0) {
+    // default: two CTAs of 8 consumer warps per SM; a weight with fewer tiles than SMs runs one CTA of 16 consumer warps each
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    config = (n + kRows - 1) / kRows <= sms ? 2 : 4;
+  }
   switch (config) {
-    case 1: return launch_q4k_cfg<T, MXC, 1, 5>(a, b, bias, c, m, n, k, 1, peers, s);
-    case 2: return launch_q4k_cfg<T, MXC, 2, 6>(a, b, bias, c, m, n, k, 1, peers, s);
-    case 3: return launch_q4k_cfg<T, MXC, 2, 8>(a, b, bias, c, m, n, k, 1, peers, s);
-    case 0:                                       // default: measured best or level on every benchmarked shape
-    case 4: return launch_q4k_cfg<T, MXC, 1, 4>(a, b, bias, c, m, n, k, 2, peers, s);
+    case 1: return launch_cfg<QT, T, MXC, 1, Q6 ? 4 : 5>(a, b, bias, c, m, n, k, 1, peers, s);
+    case 2: return launch_cfg<QT, T, MXC, 2, Q6 ? 4 : 6>(a, b, bias, c, m, n, k, 1, peers, s);
+    case 3: return launch_cfg<QT, T, MXC, 2, Q6 ? 6 : 8>(a, b, bias, c, m, n, k, 1, peers, s);
+    case 4: return launch_cfg<QT, T, MXC, 1, Q6 ? 3 : 4>(a, b, bias, c, m, n, k, 2, peers, s);
     default: return RC_RANGE;
   }
 }
 
-template <typename T>
-static int launch_q4k(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
-                      cudaStream_t s) {
-  if (m == 1) return launch_q4k_m<T, 1>(a, b, bias, c, m, n, k, config, peers, s);
-  if (m == 2) return launch_q4k_m<T, 2>(a, b, bias, c, m, n, k, config, peers, s);
-  if (m <= 4) return launch_q4k_m<T, 4>(a, b, bias, c, m, n, k, config, peers, s);
-  return launch_q4k_m<T, 8>(a, b, bias, c, m, n, k, config, peers, s);
+template <int QT, typename T>
+static int launch_q(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
+                    cudaStream_t s) {
+  if (m == 1) return launch_m<QT, T, 1>(a, b, bias, c, m, n, k, config, peers, s);
+  if (m == 2) return launch_m<QT, T, 2>(a, b, bias, c, m, n, k, config, peers, s);
+  if (m <= 4) return launch_m<QT, T, 4>(a, b, bias, c, m, n, k, config, peers, s);
+  return launch_m<QT, T, 8>(a, b, bias, c, m, n, k, config, peers, s);
 }
 
 }  // namespace stream
 
 bool gemv_stream_supports(int qtype, int dtype, int m, int n, int k) {
   (void)n;
-  return qtype == QTYPE_Q4_K && (dtype == DINO_BF16 || dtype == DINO_F16) && m >= 1 && m <= 8 && k % 256 == 0;
+  if (!(dtype == DINO_BF16 || dtype == DINO_F16) || m < 1 || m > 8) return false;
+  if (qtype == QTYPE_Q4_K) return k % 256 == 0;
+  if (qtype == QTYPE_Q6_K) return k % 2048 == 0;      // 210-byte blocks: row pieces start on 16-byte boundaries only then
+  return false;
 }
 int gemv_stream_configs() { return stream::kStreamConfigs; }
 
@@ -508,11 +536,14 @@ int gemm_rcr_stream_peers(const void* a, const void* b, const void* bias, void* 
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (m > 8) return RC_RANGE;
-  if (qtype != QTYPE_Q4_K) return RC_QTYPE;
+  if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
   if (!gemv_stream_supports(qtype, dtype, m, n, k)) return RC_ALIGN;
   if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;   // bulk-copy sources, vector loads
-  return dtype == DINO_BF16 ? stream::launch_q4k<__nv_bfloat16>(a, b, bias, c, m, n, k, config, peers, s)
-                            : stream::launch_q4k<__half>(a, b, bias, c, m, n, k, config, peers, s);
+  if (qtype == QTYPE_Q6_K)
+    return dtype == DINO_BF16 ? stream::launch_q<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, config, peers, s)
+                              : stream::launch_q<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, config, peers, s);
+  return dtype == DINO_BF16 ? stream::launch_q<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, config, peers, s)
+                            : stream::launch_q<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, config, peers, s);
 }
 
 int gemm_rcr_stream(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,

@@ -149,6 +149,7 @@ struct DinoSession {
   std::map<std::vector<int64_t>, CachedGraph> graphs;
   size_t graph_launches = 0;
   size_t graph_generation = 0;
+  std::vector<int64_t> pending_key;     // combination of the run in progress; counted as seen once that run has succeeded
 };
 
 namespace {
@@ -584,7 +585,10 @@ int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTe
       static const char* const kText[] = {"ok", "null pointer", "non-positive dimension", "k not a multiple of the block",
                                           "CUDA launch failed", "unsupported qtype", "unsupported dtype", "alignment",
                                           "shape outside variant range", "device wait gave up"};
-      return fail("gemm_rcr node " + std::to_string(ni) + " failed: " + (rc < 10 ? kText[rc] : "error"));
+      std::string why = rc < 10 ? kText[rc] : "error";
+      if (rc == 4) why += std::string(" (") + cudaGetErrorString(cudaPeekAtLastError()) + ")";
+      return fail("gemm_rcr node " + std::to_string(ni) + " (m=" + std::to_string(m) + ", n=" + std::to_string(n) + ", k=" + std::to_string(k) +
+                  ", variant " + std::to_string(variant) + ") failed: " + why);
     }
   }
   if (profile_run || !sections.empty()) {
@@ -883,6 +887,10 @@ static int run_replayed(DinoSession* s, const DinoTensor* inputs, size_t num_inp
     if (outputs[i].data == nullptr) return 0;
     key.push_back(int64_t(reinterpret_cast<intptr_t>(tensor_ptr(outputs[i]))));
   }
+  if (s->graphs.size() > 64 && s->graphs.find(key) == s->graphs.end()) {     // callers that pass ever-changing buffers: start over
+    for (auto& entry : s->graphs) if (entry.second.exec != nullptr) cudaGraphExecDestroy(entry.second.exec);
+    s->graphs.clear();
+  }
   DinoSession::CachedGraph& cg = s->graphs[key];
   if (cg.exec != nullptr) {
     s->shapes = cg.out_shapes;
@@ -892,15 +900,23 @@ static int run_replayed(DinoSession* s, const DinoTensor* inputs, size_t num_inp
     *rc_out = err == cudaSuccess ? 0 : cuda_fail("cudaGraphLaunch", err);
     return 1;
   }
-  if (cg.seen < 0 || ++cg.seen < 2) return 0;              // first sight (or capture failed before): ordinary run
+  if (cg.seen < 1) {                 // not yet run successfully the ordinary way (or a capture failed before): ordinary run
+    if (cg.seen == 0) s->pending_key = key;
+    return 0;
+  }
+  // seen once, and that run succeeded (every lazily created workspace of the kernels exists): capture this one
   cudaGraph_t graph = nullptr;
   if (cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); cg.seen = -1; return 0; }
   const int rc = run_plan(s, inputs, num_inputs, outputs, num_outputs, true);
   const bool ended = cudaStreamEndCapture(s->stream, &graph) == cudaSuccess && graph != nullptr;
-  if (rc != 0) { if (graph) cudaGraphDestroy(graph); cg.seen = -1; *rc_out = rc; return 1; }
-  bool ok = ended && cudaGraphInstantiate(&cg.exec, graph, 0) == cudaSuccess;
+  bool ok = rc == 0 && ended && cudaGraphInstantiate(&cg.exec, graph, 0) == cudaSuccess;
   if (graph) cudaGraphDestroy(graph);
-  if (!ok) { cudaGetLastError(); cg.exec = nullptr; cg.seen = -1; return 0; }
+  if (!ok) {                         // nothing was launched: forget the capture and let the caller run the plan directly
+    cudaGetLastError();
+    cg.exec = nullptr;
+    cg.seen = -1;
+    return 0;
+  }
   cg.out_shapes = s->shapes;
   const cudaError_t err = cudaGraphLaunch(cg.exec, s->stream);
   ++s->graph_launches;
@@ -908,13 +924,24 @@ static int run_replayed(DinoSession* s, const DinoTensor* inputs, size_t num_inp
   return 1;
 }
 
+// A combination counts as seen once a run of it has succeeded the ordinary way.
+static void note_ordinary_run(DinoSession* s) {
+  if (s->pending_key.empty()) return;
+  auto it = s->graphs.find(s->pending_key);
+  if (it != s->graphs.end() && it->second.seen == 0) it->second.seen = 1;
+  s->pending_key.clear();
+}
+
 int dino_session_run(DinoSession* session, const DinoTensor* inputs, size_t num_inputs, DinoTensor* outputs, size_t num_outputs) {
   if (session == nullptr) return fail("dino_session_run received null session");
   int replay_rc = 0;
+  session->pending_key.clear();
   if (run_replayed(session, inputs, num_inputs, outputs, num_outputs, &replay_rc)) {
     if (replay_rc != 0) return replay_rc;
   } else if (int rc = run_plan(session, inputs, num_inputs, outputs, num_outputs, true)) {
     return rc;
+  } else {
+    note_ordinary_run(session);
   }
   if (!session->external_stream) {
     const cudaError_t err = cudaStreamSynchronize(session->stream);
@@ -935,10 +962,13 @@ int dino_session_run_staged(DinoSession* session, const void* host_in, void* dev
     if (err != cudaSuccess) return cuda_fail("cudaMemcpyAsync (staged inputs)", err);
   }
   int replay_rc = 0;
+  session->pending_key.clear();
   if (run_replayed(session, inputs, num_inputs, outputs, num_outputs, &replay_rc)) {
     if (replay_rc != 0) return replay_rc;
   } else if (int rc = run_plan(session, inputs, num_inputs, outputs, num_outputs, true)) {
     return rc;
+  } else {
+    note_ordinary_run(session);
   }
   if (out_bytes) {
     const cudaError_t err = cudaMemcpyAsync(host_out, device_out, out_bytes, cudaMemcpyDeviceToHost, stream);

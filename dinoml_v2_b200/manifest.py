@@ -27,9 +27,11 @@ DUAL_OPS = ("dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu")
 VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3, "stream": 4}
 # Tuning configurations of the persistent GEMV (csrc/gemv_stream.cu): each is a candidate of its own, as the tile / stage /
 # warp entries of the reference's CUTLASS catalogue are (src/dinoml/kernels/providers/cutlass/gemm.py:19-127).
-STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": 5, "ctas_per_sm": 1}, 2: {"consumer_warps": 16, "ring_slots": 6, "ctas_per_sm": 1},
-                  3: {"consumer_warps": 16, "ring_slots": 8, "ctas_per_sm": 1}, 4: {"consumer_warps": 8, "ring_slots": 4, "ctas_per_sm": 2}}
-STREAM_QTYPES = ("Q4_K",)
+STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": {"Q4_K": 5, "Q6_K": 4}, "ctas_per_sm": 1},
+                  2: {"consumer_warps": 16, "ring_slots": {"Q4_K": 6, "Q6_K": 4}, "ctas_per_sm": 1},
+                  3: {"consumer_warps": 16, "ring_slots": {"Q4_K": 8, "Q6_K": 6}, "ctas_per_sm": 1},
+                  4: {"consumer_warps": 8, "ring_slots": {"Q4_K": 4, "Q6_K": 3}, "ctas_per_sm": 2}}
+STREAM_QTYPES = ("Q4_K", "Q6_K")
 
 _B200_TUNING = {
     "simt": {"kind": "gemv_simt", "rows_per_warp": 1, "activation_rows_per_pass": 4, "staging": "ldg", "tensor_cores": "none"},
@@ -95,6 +97,7 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
     tuning = dict(_B200_TUNING[family])
     if config:
         tuning.update(STREAM_CONFIGS[int(config)], config=int(config))
+        tuning["ring_slots"] = tuning["ring_slots"][q.name]
     cand = {
         "candidate_id": f"b200_gguf_{q.symbol}_{dtype}_{tag}_v1",
         "symbol_id": f"{q.symbol}_{tag}_v1",

@@ -167,7 +167,7 @@ def test_gemv_mma_q6k(dev, dtype):
         blocks = S.random_blocks("Q6_K", n, k, seed=520 + m + n)
         x, xf = _activations(m, k, 620 + m, dtype, dev)
         ref = oracle.gemm_quant(xf, blocks, "Q6_K", n, k)
-        assert kernels.select_variant("Q6_K", dtype, m, n, k) == "mma"
+        assert kernels.select_variant("Q6_K", dtype, m, n, k) in ("mma", "stream")      # both decode kernels serve K % 2048 == 0
         y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), "Q6_K", variant="mma")
         got = y.float().cpu().numpy()
         _, rel, norm = oracle.max_errors(ref, got)

@@ -26,26 +26,30 @@ def _configs():
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
-def test_stream_gemv_q4k_against_oracle(dtype):
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K"])
+def test_stream_gemv_against_oracle(dtype, qtype):
     dev = torch.device("cuda:0")
     shapes = [(1, 16, 256), (1, 1000, 1024), (2, 50, 512), (3, 129, 4096), (4, 128, 4096), (5, 4000, 2048), (7, 33, 768), (8, 64, 2048),
               (1, 2400, 4096), (2, 5000, 11008), (8, 2368, 6144), (1, 7, 512)]
+    if qtype == "Q6_K":                                   # 16-byte row pieces need K % 2048 == 0; other K stay with the tile kernel
+        assert not kernels.variant_supports("stream", "Q6_K", dtype, 1, 64, 1024)
+        shapes = [(m, n, -(-k // 2048) * 2048) for (m, n, k) in shapes] + [(1, 4096, 14336), (4, 300, 14336)]
     for (m, n, k) in shapes:
-        blocks = S.random_blocks("Q4_K", n, k, seed=2500 + m + n)
+        blocks = S.random_blocks(qtype, n, k, seed=2500 + m + n)
         bq = torch.from_numpy(blocks).to(dev)
         x, xf = _x(m, k, 2600 + m, dtype, dev)
-        ref = oracle.gemm_quant(xf, blocks, "Q4_K", n, k)
+        ref = oracle.gemm_quant(xf, blocks, qtype, n, k)
         bound = 4e-3 if dtype == "bfloat16" else 6e-4        # output rounding of bf16 (2^-9) / fp16 (2^-11)
         for variant in _configs():
             try:
-                y = kernels.gemm_rcr(x, bq, "Q4_K", variant=variant)
+                y = kernels.gemm_rcr(x, bq, qtype, variant=variant)
             except RuntimeError as exc:
                 # a configuration may refuse a shape (the 8-bit-float ones keep K * M activation bytes in shared memory)
                 assert "shape outside" in str(exc) and ":" in variant, (variant, m, n, k, str(exc))
                 continue
             assert kernels.device_status() == 0, (variant, m, n, k)
             _, rel, norm = oracle.max_errors(ref, y.float().cpu().numpy())
-            assert norm <= bound and rel <= (2e-2 if dtype == "bfloat16" else 1e-3), (dtype, variant, m, n, k, rel, norm)
+            assert norm <= bound and rel <= (2e-2 if dtype == "bfloat16" else 1e-3), (qtype, dtype, variant, m, n, k, rel, norm)
 
 
 def test_stream_gemv_repeated_launches_are_bit_identical():
@@ -66,32 +70,34 @@ def test_stream_gemv_repeated_launches_are_bit_identical():
         assert float((outs[0].float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
 
 
-def test_stream_gemv_bias_gated_and_scatter_epilogues():
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K"])
+def test_stream_gemv_bias_gated_and_scatter_epilogues(qtype):
     dev = torch.device("cuda:0")
     lib = _native.lib()
     k = 2048
+    qv = {"Q4_K": 12, "Q6_K": 14}[qtype]
     for (m, n) in [(1, 104), (2, 64), (4, 200), (8, 48), (1, 3000)]:
-        b0 = S.random_blocks("Q4_K", n, k, seed=2700 + n)
-        b1 = S.random_blocks("Q4_K", n, k, seed=2800 + n)
+        b0 = S.random_blocks(qtype, n, k, seed=2700 + n)
+        b1 = S.random_blocks(qtype, n, k, seed=2800 + n)
         x, xf = _x(m, k, 2900 + m, "bfloat16", dev)
         # bias
         bias = torch.randn(n, device=dev, dtype=torch.bfloat16)
-        ref = oracle.gemm_quant(xf, b0, "Q4_K", n, k) + bias.float().cpu().numpy()
-        y = kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), "Q4_K", bias, variant="stream")
+        ref = oracle.gemm_quant(xf, b0, qtype, n, k) + bias.float().cpu().numpy()
+        y = kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), qtype, bias, variant="stream")
         _, _, norm = oracle.max_errors(ref, y.float().cpu().numpy())
         assert norm <= 4e-3, ("bias", m, n, norm)
         # gated dual GEMM on the row-interleaved pair
         w = kernels.interleave_rows8(torch.from_numpy(b0).to(dev), torch.from_numpy(b1).to(dev))
         for act in ("silu", "fast_gelu"):
-            refg = oracle.dual_gemm_quant(xf, b0, b1, "Q4_K", n, k, act)
-            yg = kernels.dual_gemm_rcr(x, w, "Q4_K", act, variant="stream")
+            refg = oracle.dual_gemm_quant(xf, b0, b1, qtype, n, k, act)
+            yg = kernels.dual_gemm_rcr(x, w, qtype, act, variant="stream")
             _, _, norm = oracle.max_errors(refg, yg.float().cpu().numpy())
             assert yg.shape == (m, n) and norm <= 2e-2, (act, m, n, norm)
         # scatter: the same values in every extra destination
-        want = kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), "Q4_K", variant="stream")
+        want = kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), qtype, variant="stream")
         dst = [torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(3)]
         peers = (ctypes.c_void_p * 2)(dst[1].data_ptr(), dst[2].data_ptr())
-        rc = lib.dinoml_b200_gguf_gemm_rcr_scatter(x.data_ptr(), torch.from_numpy(b0).to(dev).data_ptr(), None, dst[0].data_ptr(), peers, 2, 12, 6,
+        rc = lib.dinoml_b200_gguf_gemm_rcr_scatter(x.data_ptr(), torch.from_numpy(b0).to(dev).data_ptr(), None, dst[0].data_ptr(), peers, 2, qv, 6,
                                                    m, n, k, _native.variant_code("stream"), torch.cuda.current_stream().cuda_stream)
         assert rc == 0, _native.last_error()
         torch.cuda.synchronize()
