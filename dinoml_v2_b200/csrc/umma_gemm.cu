@@ -81,10 +81,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false (after flagging) if the phase never completes or the CTA is aborting.
+// The non-blocking test comes first: on the MMA-issuing warp most waits find their phase already complete, and
+// there test_wait measured ~90 cycles less than a try_wait that succeeds at once.
 // Only one lane per warp polls (18 pollers per CTA), so there is no sleep back-off: try_wait itself suspends the
 // thread for a hardware-defined slice.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_test_wait(bar, parity)) return true;
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
@@ -247,17 +259,32 @@ __device__ __forceinline__ void q8_to_pairs(uint32_t u, float d256, float c, uin
   p23 = as_u32<typename P::V>(P::pack(fmaf(f2, d256, c), fmaf(f3, d256, c)));
 }
 
-// Rings: 4 stages = weight-tile slots in TMEM (32 columns each, right after the BM accumulator columns) paired with
-// activation tiles in shared memory, and RawGeom::kSlots packed super-blocks in shared memory (both TMA).
-constexpr int kWSlots = 4;          // = stages per 256-weight super-block: the MMA loop relies on it
+// Rings.  A super-block (256 weights of every row) is kStagesPerSb = 4 K stages; a stage is a weight-tile slot in TMEM (32
+// columns, right after the BM accumulator columns) paired with an activation tile in shared memory.
+//   BM = 256: the ring is one super-block of stages, each with its own full / empty barrier pair - the MMAs of one stage
+//     (512 tensor cycles) are longer than the barrier handling on the issuing warp, fine-grained hand-over keeps the
+//     tensor pipe fed.
+//   BM <= 128: the MMAs of a stage are shorter than one wait + commit on the issuing warp (~300 cycles), which then paces
+//     the whole CTA.  There the hand-over is per SUPER-BLOCK (one wait, 16 MMAs, one commit) and the ring is
+//     stage_units<BM>() super-blocks deep, so that the round trip commit -> empty -> tcgen05.st -> full is hidden.
+// Packed ring: raw_slots<QT, BM>() super-blocks of packed bytes in shared memory (TMA), as many as fit up to 6 when the
+// super-blocks are short-lived.
+constexpr int kStagesPerSb = 4;         // 256 weights / kBK: the MMA loop relies on it
 constexpr int kWSlotCols = kBK / 2;     // 64 16-bit values per lane = 32 columns
 constexpr int kSmemBudget = 227 * 1024;
+template <int BM> constexpr bool coarse_handover() { return BM < 256; }
+template <int BM> constexpr int stage_units() { return BM >= 256 ? 1 : BM >= 128 ? 2 : 3; }
 template <int BM> constexpr int x_tile_bytes() { return BM * kBK * 2; }
 template <int QT> constexpr int raw_box_bytes() { return kRowsW * RawGeom<QT>::kPitch; }
 template <int QT> constexpr int raw_slot_bytes() { return RawGeom<QT>::kBoxes * raw_box_bytes<QT>(); }
-template <int BM> constexpr int tmem_cols() { return BM + kWSlots * kWSlotCols > 256 ? 512 : 256; }
+template <int BM> constexpr int tmem_cols() { return BM + stage_units<BM>() * kStagesPerSb * kWSlotCols > 256 ? 512 : 256; }
+template <int QT, int BM> constexpr int raw_slots() {
+  constexpr int fit = (kSmemBudget - 1024 - 512 - stage_units<BM>() * kStagesPerSb * x_tile_bytes<BM>()) / raw_slot_bytes<QT>();
+  constexpr int want = BM >= 256 ? RawGeom<QT>::kSlots : 6;
+  return fit < want ? fit : want;
+}
 template <int QT, int BM> constexpr size_t smem_bytes() {
-  return 1024 + size_t(kWSlots) * x_tile_bytes<BM>() + size_t(RawGeom<QT>::kSlots) * raw_slot_bytes<QT>() + 512;
+  return 1024 + size_t(stage_units<BM>() * kStagesPerSb) * x_tile_bytes<BM>() + size_t(raw_slots<QT, BM>()) * raw_slot_bytes<QT>() + 512;
 }
 
 struct Params {
@@ -307,7 +334,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const Params p) {
   using P = Pair<T>;
   using V = typename P::V;
-  constexpr int NS = kWSlots, NSR = RawGeom<QT>::kSlots;    // stage ring (weight tile in TMEM + activation tile in smem), packed ring
+  constexpr bool COARSE = coarse_handover<BM>();
+  constexpr int U = stage_units<BM>(), NS = U * kStagesPerSb, NSR = raw_slots<QT, BM>();    // stage ring (weight tile in TMEM + activation tile in smem), packed ring
+  constexpr int NB = COARSE ? U : NS;          // full / empty barrier pairs: one per super-block slot or one per stage
+  static_assert(COARSE || U == 1, "per-stage hand-over runs on a ring of one super-block");
+  static_assert(NSR >= 2 && BM + NS * kWSlotCols <= 512 && (2 * NB + 2 * NSR + 4) * 8 + 8 <= 512, "rings");
   constexpr int kXTile = x_tile_bytes<BM>();
   constexpr uint32_t kTmemCols = tmem_cols<BM>();
   constexpr int kPitch = RawGeom<QT>::kPitch;
@@ -322,18 +353,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   uint8_t* xtiles = smem;                                              // NS x [BM][128 B]
   uint8_t* raw = xtiles + NS * kXTile;                                 // NSR x [128][kPitch]
   uint64_t* bars = reinterpret_cast<uint64_t*>(raw + NSR * kRawBytes);
-  // bars: full[NS], empty[NS], rawfull[NSR], rawfree[NSR], accumulator full, accumulator free, drain, epilogue.  A stage is "full"
+  // bars: full[NB], empty[NB], rawfull[NSR], rawfree[NSR], accumulator full, accumulator free, drain, epilogue.  A stage is "full"
   // when its 8 producer warps have written the weight tile AND the activation tile's bytes have landed (one barrier, one
   // wait for the MMA warp); it is "empty" when the MMAs that read it have completed (one tcgen05.commit, watched by
   // producers and TMA).
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NS + 2 * NSR + 4);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NB + 2 * NSR + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
-  auto empty = [&](int s) { return bar0 + 8u * (NS + s); };
-  auto rawfull = [&](int s) { return bar0 + 8u * (2 * NS + s); };
-  auto rawfree = [&](int s) { return bar0 + 8u * (2 * NS + NSR + s); };
-  const uint32_t accbar = bar0 + 8u * (2 * NS + 2 * NSR), accfree = accbar + 8u, drainbar = accbar + 16u, epibar = accbar + 24u;
+  auto empty = [&](int s) { return bar0 + 8u * (NB + s); };
+  auto rawfull = [&](int s) { return bar0 + 8u * (2 * NB + s); };
+  auto rawfree = [&](int s) { return bar0 + 8u * (2 * NB + NSR + s); };
+  const uint32_t accbar = bar0 + 8u * (2 * NB + 2 * NSR), accfree = accbar + 8u, drainbar = accbar + 16u, epibar = accbar + 24u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x, ctas = gridDim.x;
@@ -346,8 +377,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   const int tile_hi = has_work ? walk.tile_hi() : -1, tile_lo = has_work ? walk.tile_lo() : 0;
 
   if (tid == 0) {
-    for (int s = 0; s < NS; ++s) {
-      mbar_init(full(s), kWarpArrivals + 1);   // + the TMA lane's arrive.expect_tx
+    for (int s = 0; s < NB; ++s) {
+      mbar_init(full(s), (COARSE ? 2 : 1) * kWarpArrivals + 1);   // the producer warps that fill it + the TMA lane's arrive.expect_tx
       mbar_init(empty(s), 1);
     }
     for (int s = 0; s < NSR; ++s) {
@@ -560,43 +591,31 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         }
         __syncwarp();                          // every lane holds its words: the ring slot may be refilled
         if (lane == 0) mbar_arrive(rawfree(rslot));
-#pragma unroll
-        for (int ls = 0; ls < 2; ++ls) {
-          const int slot = 2 * grp + ls;       // stage ring slot = K stage inside the super-block
-          if (it > 0) {                        // one lane polls the barrier, the warp follows
-            int ok = 1;
-            if (lane == 0) ok = mbar_wait(empty(slot), uint32_t(it - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) { alive = false; break; }
-            tcgen05_fence_after();
-          }
-          const uint32_t tile = tmem_lane + uint32_t(slot * kWSlotCols);   // column k'/2 of this slot
+        // K stage ls (0 / 1) of this thread's half of the super-block -> two groups of 8 words: 16 values each for
+        // k' = 16*lhalf .. +15 and k' = 32 + 16*lhalf .. +15 of the 64-wide stage.
+        auto unpack_stage = [&](int ls, uint32_t (&o0)[8], uint32_t (&o1)[8]) {
           if constexpr (QT == QTYPE_Q8_0) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const float d256 = sub_scale[2 * ls + h] * (1.f / 256.f);
               const float c = -8421376.f * d256;        // -(2^23 + 2^15) * d / 256, exact
-              uint32_t o[8];
+              uint32_t (&o)[8] = h == 0 ? o0 : o1;
 #pragma unroll
               for (int i = 0; i < 4; ++i) q8_to_pairs<T>(qw[8 * ls + 4 * h + i], d256, c, o[2 * i], o[2 * i + 1]);
-              tmem_st8(tile + 16 * h + 8 * lhalf, o);     // k' = 32*h + 16*lhalf .. +15
             }
           } else if constexpr (QT == QTYPE_Q4_K) {
-            // stage = 64-weight group: low nibbles -> sub-block 2*slot (k' 0..31), high -> 2*slot+1 (k' 32..63)
+            // stage = 64-weight group: low nibbles -> its first sub-block (k' 0..31), high nibbles -> its second (k' 32..63)
             const int sh = 16 * ls;
             const float sc0 = float((qw[8] >> sh) & 0xff), sc1 = float((qw[8] >> (sh + 8)) & 0xff);
             const float mn0 = float((qw[9] >> sh) & 0xff), mn1 = float((qw[9] >> (sh + 8)) & 0xff);
             const V off = P::splat(P::kMagic);
             const V s_lo = P::splat(dscale * sc0), a_lo = P::splat(-(dmin * mn0));
             const V s_hi = P::splat(dscale * sc1), a_hi = P::splat(-(dmin * mn1));
-            uint32_t lo[8], hi[8];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              bytes_to_pairs<T>(qw[4 * ls + i] & 0x0f0f0f0fu, off, s_lo, a_lo, lo[2 * i], lo[2 * i + 1]);
-              bytes_to_pairs<T>((qw[4 * ls + i] >> 4) & 0x0f0f0f0fu, off, s_hi, a_hi, hi[2 * i], hi[2 * i + 1]);
+              bytes_to_pairs<T>(qw[4 * ls + i] & 0x0f0f0f0fu, off, s_lo, a_lo, o0[2 * i], o0[2 * i + 1]);
+              bytes_to_pairs<T>((qw[4 * ls + i] >> 4) & 0x0f0f0f0fu, off, s_hi, a_hi, o1[2 * i], o1[2 * i + 1]);
             }
-            tmem_st8(tile + 8 * lhalf, lo);            // k' = 16*lhalf .. +15
-            tmem_st8(tile + 16 + 8 * lhalf, hi);       // k' = 32 + 16*lhalf .. +15
           } else {
             // stage = (half block grp, quad pair ls): quads 2*ls (k' 0..31) and 2*ls+1 (k' 32..63)
             const V off = P::splat(P::kMagic + 32.f);
@@ -605,7 +624,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             for (int qo = 0; qo < 2; ++qo) {
               const int quad = 2 * ls + qo;
               const V s2 = P::splat(dscale * sub_scale[quad]);
-              uint32_t o[8];
+              uint32_t (&o)[8] = qo == 0 ? o0 : o1;
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const uint32_t l4 = (qw[4 * qo + i] >> (4 * ls)) & 0x0f0f0f0fu;
@@ -613,13 +632,49 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
                 const uint32_t hs = quad == 0 ? qw[8 + i] << 4 : quad == 1 ? qw[8 + i] << 2 : quad == 2 ? qw[8 + i] : qw[8 + i] >> 2;
                 bytes_to_pairs<T>(l4 | (hs & 0x30303030u), off, s2, zero, o[2 * i], o[2 * i + 1]);
               }
-              tmem_st8(tile + 16 * qo + 8 * lhalf, o);   // k' = 32*qo + 16*lhalf .. +15
             }
+          }
+        };
+        // one lane polls the barrier, the warp follows
+        auto wait_empty = [&](int b, int trip) -> bool {
+          int ok = 1;
+          if (lane == 0) ok = mbar_wait(empty(b), uint32_t(trip - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (ok) tcgen05_fence_after();
+          return ok != 0;
+        };
+        if constexpr (COARSE) {
+          // hand-over per super-block: unpack both stages (no TMEM slot needed yet), then wait for the slot, store, signal once
+          const int ub = it % U, trip = it / U;
+          uint32_t ow[2][2][8];
+          unpack_stage(0, ow[0][0], ow[0][1]);
+          unpack_stage(1, ow[1][0], ow[1][1]);
+          if (trip > 0 && !wait_empty(ub, trip)) { alive = false; break; }
+#pragma unroll
+          for (int ls = 0; ls < 2; ++ls) {
+            const uint32_t tile = tmem_lane + uint32_t((ub * kStagesPerSb + 2 * grp + ls) * kWSlotCols);
+            tmem_st8(tile + 8 * lhalf, ow[ls][0]);
+            tmem_st8(tile + 16 + 8 * lhalf, ow[ls][1]);
           }
           tmem_st_wait();
           tcgen05_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(full(slot));
+          if (lane == 0) mbar_arrive(full(ub));
+        } else {
+#pragma unroll
+          for (int ls = 0; ls < 2; ++ls) {
+            const int slot = 2 * grp + ls;       // stage ring slot = K stage inside the super-block
+            if (it > 0 && !wait_empty(slot, it)) { alive = false; break; }
+            const uint32_t tile = tmem_lane + uint32_t(slot * kWSlotCols);   // column k'/2 of this slot
+            uint32_t o0[8], o1[8];
+            unpack_stage(ls, o0, o1);
+            tmem_st8(tile + 8 * lhalf, o0);            // k' = 16*lhalf .. +15
+            tmem_st8(tile + 16 + 8 * lhalf, o1);       // k' = 32 + 16*lhalf .. +15
+            tmem_st_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full(slot));
+          }
         }
         if (!alive) break;
         // The previous segment's epilogue runs only now, after the first super-block of this segment has been unpacked:
@@ -646,14 +701,26 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
       walk.segment(t, sb_b, sb_e);
       const int m0 = (t % p.m_tiles) * BM;
       for (int sb = sb_b; sb < sb_e && ok; ++sb, ++it) {
-#pragma unroll
-        for (int slot = 0; slot < NS; ++slot) {
-          if (it > 0 && !warp_wait(empty(slot), uint32_t(it - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) { ok = false; break; }
+        if constexpr (COARSE) {
+          const int ub = it % U, trip = it / U;
+          if (trip > 0 && !warp_wait(empty(ub), uint32_t(trip - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) { ok = false; break; }
           if (elect_one()) {
-            mbar_arrive_expect_tx(full(slot), uint32_t(kXTile));
-            tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, full(slot), sb * 256 + slot * kBK, m0);
+            mbar_arrive_expect_tx(full(ub), uint32_t(kStagesPerSb * kXTile));
+#pragma unroll
+            for (int st = 0; st < kStagesPerSb; ++st)
+              tma_load_2d(smem_u32(xtiles + (ub * kStagesPerSb + st) * kXTile), &x_map, full(ub), sb * 256 + st * kBK, m0);
           }
           __syncwarp();
+        } else {
+#pragma unroll
+          for (int slot = 0; slot < NS; ++slot) {
+            if (it > 0 && !warp_wait(empty(slot), uint32_t(it - 1) & 1u, abort_flag, p.status, ST_EMPTY_TIMEOUT)) { ok = false; break; }
+            if (elect_one()) {
+              mbar_arrive_expect_tx(full(slot), uint32_t(kXTile));
+              tma_load_2d(smem_u32(xtiles + slot * kXTile), &x_map, full(slot), sb * 256 + slot * kBK, m0);
+            }
+            __syncwarp();
+          }
         }
       }
     }
@@ -699,21 +766,41 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         if (!ok) break;
         tcgen05_fence_after();
       }
-      // one super-block = NS stages per trip: slot numbers, TMEM columns and descriptor offsets are compile-time constants
       for (int sb = sb_b; sb < sb_e && ok; ++sb, ++it) {
-#pragma unroll
-        for (int slot = 0; slot < NS; ++slot) {
-          ok = warp_wait(full(slot), uint32_t(it) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
+        if constexpr (COARSE) {
+          // one wait, sixteen MMAs, one commit per super-block
+          const int ub = it % U;
+          ok = warp_wait(full(ub), uint32_t(it / U) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
           if (!ok) break;
           tcgen05_fence_after();
           if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < kBK / 16; ++kk)      // 16 K values = 8 TMEM columns of A, 32 bytes of each B row
-              umma_f16_ts(tmem_base, tmem_base + uint32_t(BM + slot * kWSlotCols + 8 * kk), db0 + uint64_t((slot * kXTile) >> 4) + uint64_t(2 * kk),
-                          kIdesc, (sb > sb_b || slot > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(empty(slot));
+            for (int st = 0; st < kStagesPerSb; ++st) {
+              const int slot = ub * kStagesPerSb + st;
+#pragma unroll
+              for (int kk = 0; kk < kBK / 16; ++kk)
+                umma_f16_ts(tmem_base, tmem_base + uint32_t(BM + slot * kWSlotCols + 8 * kk), db0 + uint64_t((slot * kXTile) >> 4) + uint64_t(2 * kk),
+                            kIdesc, (sb > sb_b || st > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit(empty(ub));
           }
           __syncwarp();
+        } else {
+          // one super-block = NS stages per trip: slot numbers, TMEM columns and descriptor offsets are compile-time constants
+#pragma unroll
+          for (int slot = 0; slot < NS; ++slot) {
+            ok = warp_wait(full(slot), uint32_t(it) & 1u, abort_flag, p.status, ST_FULL_TIMEOUT);
+            if (!ok) break;
+            tcgen05_fence_after();
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = 0; kk < kBK / 16; ++kk)      // 16 K values = 8 TMEM columns of A, 32 bytes of each B row
+                umma_f16_ts(tmem_base, tmem_base + uint32_t(BM + slot * kWSlotCols + 8 * kk), db0 + uint64_t((slot * kXTile) >> 4) + uint64_t(2 * kk),
+                            kIdesc, (sb > sb_b || slot > 0 || kk > 0) ? 1u : 0u);
+              umma_commit(empty(slot));
+            }
+            __syncwarp();
+          }
         }
       }
       if (ok && elect_one()) umma_commit(accbar);
