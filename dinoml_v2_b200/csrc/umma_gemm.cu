@@ -400,6 +400,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch.  The next kernel in the stream may begin once every CTA of this grid is past this
+  // point; its CTAs take over an SM as soon as one of ours exits.  In the other direction, the packed weights are
+  // constants: the weight TMA, the unpack and the tcgen05.st of this grid run ahead of `griddepcontrol.wait`, which only
+  // the activation TMA warp (before its first load) and the producers (before their first epilogue: outputs, partial
+  // tiles and flags are shared with the preceding launch) execute.
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 
   if (warp < 16) {
     // ------------------------------------------------------------------ producers
@@ -422,7 +428,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
       return __shfl_sync(0xffffffffu, ok, 0) != 0;
     };
     // Epilogue of one segment (tile t, super-blocks [sb_b, sb_e), the segi-th of this CTA).  false = a wait gave up.
+    bool dep_waited = false;
     auto epilogue = [&](int t, int sb_b, int sb_e, int segi) -> bool {
+      if (!dep_waited) {
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        dep_waited = true;
+      }
       {
         int ok = 1;
         if (lane == 0) ok = mbar_wait(accbar, uint32_t(segi) & 1u, abort_flag, p.status, ST_ACC_TIMEOUT) ? 1 : 0;
@@ -690,6 +701,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     if (alive && pend_t >= 0) epilogue(pend_t, pend_b, pend_e, segi - 1);
   } else if (warp == 16) {
     // ------------------------------------------------------------------ activation TMA
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");     // the activations may be the preceding kernel's output
     // The three control warps stay converged: every lane runs the loop and polls the barriers, one elected lane issues
     // the asynchronous instructions.  Inside a divergent `if (lane == 0)` region the compiler cannot keep descriptors,
     // coordinates and barrier addresses in uniform registers, and each tcgen05.mma / bulk copy then costs tens of cycles
@@ -943,7 +955,8 @@ static int launch(const void* a, const void* b, const void* bias, void* c, int m
   p.m_tiles = pl.m_tiles;
   p.units = pl.units;
   p.peers = peers;
-  kern<<<pl.ctas, kThreads, smem, s>>>(x_map, w_map, p);
+  // programmatic stream serialization: see the griddepcontrol notes in the kernel
+  if (gemv_launch(kern, pl.ctas, 1, kThreads, smem, s, x_map, w_map, p) != cudaSuccess) return RC_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
