@@ -21,7 +21,7 @@
 // (stream order) - so a writer is always a full barrier behind any reader of the set it writes.
 //
 // The reference has no distributed code; the N-split / K-split scheme this serves is in dinoml_v2_b200/sharding.py.
-#include "gguf_common.cuh"
+#include "gemv_mma_common.cuh"
 
 namespace b200gguf {
 
@@ -56,6 +56,12 @@ __global__ void __launch_bounds__(256)
 peer_exchange_kernel(const PeerSignals sig, int world, int rank, uint32_t epoch, const T* __restrict__ slots, T* __restrict__ out,
                      int64_t count, int* status, uint32_t poll_limit) {
   const int tid = threadIdx.x;
+  // Programmatic dependent launch on both sides.  The kernel that follows in the stream (the next GEMV) may start at once:
+  // it streams its constant weights while this kernel waits for the peers, and blocks before it reads what this kernel
+  // produces.  This kernel itself is resident before its predecessor (the scatter GEMV) has finished and must not
+  // publish "my stores are complete" - nor read the slots - until it has.
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
   if (tid < world && tid != rank) {
     if (blockIdx.x == 0) {
       __threadfence_system();
@@ -103,22 +109,23 @@ int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch,
   int64_t blocks = (count + 255) / 256;
   if (blocks < 1) blocks = 1;
   if (blocks > 64) blocks = 64;
+  cudaError_t err = cudaSuccess;
   switch (dtype) {
     case DINO_BF16:
-      peer_exchange_kernel<__nv_bfloat16><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const __nv_bfloat16*>(slots),
-                                                                             static_cast<__nv_bfloat16*>(out), count, status, limit);
+      err = gemv_launch(peer_exchange_kernel<__nv_bfloat16>, int(blocks), 1, 256, 0, s, sig, world, rank, epoch, static_cast<const __nv_bfloat16*>(slots),
+                        static_cast<__nv_bfloat16*>(out), count, status, limit);
       break;
     case DINO_F16:
-      peer_exchange_kernel<__half><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const __half*>(slots),
-                                                                    static_cast<__half*>(out), count, status, limit);
+      err = gemv_launch(peer_exchange_kernel<__half>, int(blocks), 1, 256, 0, s, sig, world, rank, epoch, static_cast<const __half*>(slots),
+                        static_cast<__half*>(out), count, status, limit);
       break;
     case DINO_F32:
-      peer_exchange_kernel<float><<<unsigned(blocks), 256, 0, s>>>(sig, world, rank, epoch, static_cast<const float*>(slots),
-                                                                   static_cast<float*>(out), count, status, limit);
+      err = gemv_launch(peer_exchange_kernel<float>, int(blocks), 1, 256, 0, s, sig, world, rank, epoch, static_cast<const float*>(slots),
+                        static_cast<float*>(out), count, status, limit);
       break;
     default: return RC_DTYPE;
   }
-  return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
+  return err == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
 // Polls a later exchange makes per peer before it gives up (0 restores the default of 2^22, about a second).  For tests of
