@@ -59,8 +59,26 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, index: int):
+    # The same NVML loop as a child process: it shares no interpreter lock with a timed region whose launches are issued
+    # from Python (the multi-GPU step), where a sampling thread would slow down what it observes.
+    _CHILD = (
+        "import sys, time\n"
+        "import pynvml as nv\n"
+        "nv.nvmlInit()\n"
+        "spec, path = sys.argv[1], sys.argv[2]\n"
+        "h = nv.nvmlDeviceGetHandleByUUID(spec) if spec.startswith('GPU-') else nv.nvmlDeviceGetHandleByIndex(int(spec))\n"
+        "fn = getattr(nv, 'nvmlDeviceGetCurrentClocksEventReasons', None) or getattr(nv, 'nvmlDeviceGetCurrentClocksThrottleReasons')\n"
+        "f = open(path, 'w')\n"
+        "while True:\n"
+        "    mask = int(fn(h))\n"
+        "    row = [str(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))), str(float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)))]\n"
+        "    row += ['Active' if mask & b else 'Not Active' for b in (0x8, 0x40, 0x20, 0x4)]\n"
+        "    f.write(','.join(row) + '\\n'); f.flush()\n"
+        "    time.sleep(0.001)\n")
+
+    def __init__(self, index: int, isolated: bool = False):
         self.index, self.rows, self._stop, self._thread = index, [], threading.Event(), None
+        self._isolated, self._child, self._child_path, self._spec = isolated, None, None, str(index)
         self._first = threading.Event()
         self.source, self.error = "nvidia-smi", None
         self._nvml = None
@@ -70,8 +88,10 @@ class ClockSampler:
             visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
             ids = visible.split(",") if visible else []
             if index < len(ids) and ids[index].strip().isdigit():
+                self._spec = ids[index].strip()
                 handle = nv.nvmlDeviceGetHandleByIndex(int(ids[index]))
             elif index < len(ids) and ids[index].strip().startswith("GPU-"):
+                self._spec = ids[index].strip()
                 handle = nv.nvmlDeviceGetHandleByUUID(ids[index].strip())
             else:
                 handle = nv.nvmlDeviceGetHandleByIndex(index)
@@ -111,13 +131,52 @@ class ClockSampler:
             self._first.set()
             self._stop.wait(0.001 if self._nvml is not None else 0.05)
 
+    def _start_child(self) -> bool:
+        import tempfile
+        fd, self._child_path = tempfile.mkstemp(prefix="clocks_", suffix=".csv")
+        os.close(fd)
+        try:
+            self._child = subprocess.Popen([sys.executable, "-c", self._CHILD, self._spec, self._child_path],
+                                           stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+        except OSError:
+            self._child = None
+            return False
+        deadline = time.time() + 10
+        while time.time() < deadline and self._child.poll() is None and os.path.getsize(self._child_path) == 0:
+            time.sleep(0.01)
+        if os.path.getsize(self._child_path) == 0:          # the child never sampled: stop it, use the thread
+            self._stop_child()
+            return False
+        self.source = "nvml (child process)"
+        return True
+
+    def _stop_child(self):
+        if self._child is not None:
+            self._child.terminate()
+            try:
+                self._child.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._child.kill()
+            self._child = None
+        if self._child_path and os.path.exists(self._child_path):
+            with open(self._child_path) as f:
+                self.rows += [line.strip().split(",") for line in f if line.count(",") >= 5]
+            os.unlink(self._child_path)
+        self._child_path = None
+
     def __enter__(self):
+        if self._isolated and self._nvml is not None and self._start_child():
+            return self
         self._thread = threading.Thread(target=self._loop, daemon=True)
         self._thread.start()
         self._first.wait(timeout=6)                       # the timed region starts with one sample on record
         return self
 
     def __exit__(self, *exc):
+        if self._thread is None:                          # child-process mode
+            self._stop_child()
+            self._sample()
+            return
         self._stop.set()
         self._thread.join(timeout=6)
         self._sample()                                    # and ends with one
@@ -761,7 +820,7 @@ def run_multi(args):
                     f.swiglu_mlp_peer(x, od)
             swiglu_ms = time_steps(step_swiglu, half, W, stream, barrier=dist.barrier)
         step, comm = (step_peer, comm_peer) if mode == "peer" else (step_nccl, comm_nccl)
-        clock_ctx = ClockSampler(local) if (m == 1 and rank == 0) else None
+        clock_ctx = ClockSampler(local, isolated=True) if (m == 1 and rank == 0) else None
         if clock_ctx:
             clock_ctx.__enter__()
         ms = time_steps(step, K, W, stream, barrier=dist.barrier)

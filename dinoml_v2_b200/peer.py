@@ -21,6 +21,7 @@ import os
 from . import _native
 
 _SIGNAL_BYTES = 256      # 8 signal words, padded so that the slots start on a 256-byte boundary
+_QTYPE_VALUE: dict = {}  # qtype (name or enum) -> ggml id, filled on first use
 
 
 class PeerExchange:
@@ -62,6 +63,13 @@ class PeerExchange:
         self._peer_dst = [(ctypes.c_void_p * max(1, len(others)))(
             *[base[r] + _SIGNAL_BYTES + p * self._set_bytes + self.rank * self.slot_elems * esize for r in others]) for p in (0, 1)]
         self._n_peers = len(others)
+        # raw addresses and codes, so that a launch costs one ctypes call and no tensor views (decode steps are a few
+        # microseconds of device time: the host side must not be the slower one)
+        self._set_ptr = [int(t.data_ptr()) for t in self._sets]
+        self._local_ptr = [ptr + self.rank * self.slot_elems * esize for ptr in self._set_ptr]
+        self._dtype_code = _native.DINO_DTYPE[str(dtype).replace("torch.", "")]
+        self._lib = _native.lib()
+        self._auto = _native.variant_code("auto")
         self.epoch = 0
         dist.barrier(group=group)          # every rank has mapped every buffer before anyone writes
 
@@ -82,29 +90,33 @@ class PeerExchange:
     def scatter_gemv(self, a, b_quant, qtype, bias=None, variant: str = "auto"):
         """y = a @ dequant(b_quant)^T stored into slot [rank] of every rank's buffer, by one kernel (mma or umma variant)."""
         import torch
-
-        from .gguf_blocks import qtype_of
-        q = qtype_of(qtype)
+        qv = _QTYPE_VALUE.get(qtype)
+        if qv is None:
+            from .gguf_blocks import qtype_of
+            qv = _QTYPE_VALUE[qtype] = qtype_of(qtype).value
         m, k = a.shape
         n = b_quant.shape[0]
         if m * n != self.slot_elems:
             raise ValueError(f"result [{m}, {n}] does not fill a slot of {self.slot_elems} elements")
-        lib = _native.lib()
-        rc = lib.dinoml_b200_gguf_gemm_rcr_scatter(
-            a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, self.local_slot().data_ptr(),
-            self._peer_dst[(self.epoch + 1) & 1], self._n_peers, q.value, _native.DINO_DTYPE[str(a.dtype).replace("torch.", "")], m, n, k,
-            _native.variant_code(variant), torch.cuda.current_stream().cuda_stream)
-        _native.check(rc, "dinoml_b200_gguf_gemm_rcr_scatter")
+        if a.dtype != self.dtype:
+            raise ValueError("activation dtype differs from the exchange buffers'")
+        nxt = (self.epoch + 1) & 1                    # the set the NEXT exchange reads
+        rc = self._lib.dinoml_b200_gguf_gemm_rcr_scatter(
+            a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, self._local_ptr[nxt],
+            self._peer_dst[nxt], self._n_peers, qv, self._dtype_code, m, n, k,
+            self._auto if variant == "auto" else _native.variant_code(variant), torch.cuda.current_stream().cuda_stream)
+        if rc:
+            _native.check(rc, "dinoml_b200_gguf_gemm_rcr_scatter")
 
     def _exchange(self, out, count):
         import torch
         self.epoch += 1
-        lib = _native.lib()
-        rc = lib.dinoml_b200_peer_exchange(self._signal_ptrs, self.world, self.rank, self.epoch, self.slots.data_ptr() if count else None,
-                                           out.data_ptr() if count else None, count,
-                                           _native.DINO_DTYPE[str(self.dtype).replace("torch.", "")],
-                                           torch.cuda.current_stream().cuda_stream)
-        _native.check(rc, "dinoml_b200_peer_exchange")
+        rc = self._lib.dinoml_b200_peer_exchange(self._signal_ptrs, self.world, self.rank, self.epoch,
+                                                 self._set_ptr[self.epoch & 1] if count else None,
+                                                 out.data_ptr() if count else None, count, self._dtype_code,
+                                                 torch.cuda.current_stream().cuda_stream)
+        if rc:
+            _native.check(rc, "dinoml_b200_peer_exchange")
 
     def finish_gather(self):
         """Completes an all-gather: after this kernel every rank's slot in the local buffer is final."""
