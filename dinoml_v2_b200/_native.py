@@ -67,6 +67,8 @@ def lib() -> ctypes.CDLL:
     L.dinoml_b200_gguf_gemm_rcr_scatter.restype = ci
     L.dinoml_b200_gguf_dual_gemm_rcr.argtypes = [vp, vp, vp, ctypes.POINTER(vp), ci, ci, ci, ci, ci, ci, ci, ci, vp]
     L.dinoml_b200_gguf_dual_gemm_rcr.restype = ci
+    L.dinoml_b200_gguf_dual_gemm_rcr_bias.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, ci, ci, ci, ci, ci, ci, ci, vp]
+    L.dinoml_b200_gguf_dual_gemm_rcr_bias.restype = ci
     L.dinoml_b200_peer_exchange.argtypes = [ctypes.POINTER(vp), ci, ci, ctypes.c_uint, vp, vp, i64, ci, vp]
     L.dinoml_b200_peer_exchange.restype = ci
     L.dinoml_b200_peer_enable_access.argtypes = [ci]

@@ -63,7 +63,7 @@ def render_module_plan(graph: Mapping[str, Any], manifest: Mapping[str, Any]) ->
     items = {i["node_id"]: i for i in manifest["required_kernels"]}
     for idx, node in enumerate(graph["nodes"]):
         item = items[node["id"]]
-        bias = node["inputs"][2] if len(node["inputs"]) > 2 and not node["op"].startswith("dual_") else "-"
+        bias = node["inputs"][2] if len(node["inputs"]) > 2 else "-"
         variant = 0
         if item.get("selected_candidate_id"):
             variant = next(c["variant_code"] for c in item["candidates"] if c["candidate_id"] == item["selected_candidate_id"])

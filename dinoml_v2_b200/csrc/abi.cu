@@ -110,8 +110,9 @@ int gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype,
 }
 
 // Gated dual GEMM on a row-interleaved weight (see dinoml_b200_gguf_dual_gemm_rcr in the header); n = output columns.
-int dual_gemm_rcr_peers(const void* a, const void* b01, void* c, const PeerOut& dst, int qtype, int dtype, int m, int n, int k,
-                        int activation, int variant, cudaStream_t s) {
+// bias01: null, or 2n values in the activation dtype interleaved like the rows (bias0 of 8 gate rows, bias1 of their up rows).
+int dual_gemm_rcr_peers(const void* a, const void* b01, const void* bias01, void* c, const PeerOut& dst, int qtype, int dtype, int m, int n,
+                        int k, int activation, int variant, cudaStream_t s) {
   if (activation != 1 && activation != 2) return RC_RANGE;
   if (n <= 0 || n % 8 != 0 || n > 0x3fffffff) return RC_RANGE;       // whole groups of 8 rows per matrix
   if (variant < 0 || variant > 0xffff) return RC_RANGE;
@@ -122,23 +123,24 @@ int dual_gemm_rcr_peers(const void* a, const void* b01, void* c, const PeerOut& 
   const int rows = 2 * n;                                              // rows of the interleaved weight
   if (variant == DINOML_B200_GGUF_VARIANT_AUTO) {
     variant = select_variant(qtype, dtype, m, rows, k);
-    // the Q8_0 mma GEMV has no gated epilogue: from M = 9 the tcgen05 kernel takes the call instead
-    if (variant == DINOML_B200_GGUF_VARIANT_MMA && qtype == QTYPE_Q8_0 && gemm_umma_supports(qtype, dtype, m, rows, k))
+    // the Q8_0 mma GEMV has no gated epilogue: the tcgen05 kernel takes the call instead, whatever M is (its 64-row
+    // activation tile is zero-filled past M)
+    if (variant == DINOML_B200_GGUF_VARIANT_MMA && qtype == QTYPE_Q8_0 && gemm_umma_supports(qtype, dtype, m < 9 ? 9 : m, rows, k))
       variant = DINOML_B200_GGUF_VARIANT_UMMA;
   }
-  if (variant == DINOML_B200_GGUF_VARIANT_STREAM) return gemm_rcr_stream_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, config, &peers, s);
+  if (variant == DINOML_B200_GGUF_VARIANT_STREAM) return gemm_rcr_stream_peers(a, b01, bias01, c, qtype, dtype, m, rows, k, config, &peers, s);
   if (config != 0) return RC_RANGE;
-  if (variant == DINOML_B200_GGUF_VARIANT_MMA) return gemm_rcr_mma_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, &peers, s);
-  if (variant == DINOML_B200_GGUF_VARIANT_UMMA) return gemm_rcr_umma_peers(a, b01, nullptr, c, qtype, dtype, m, rows, k, &peers, s);
+  if (variant == DINOML_B200_GGUF_VARIANT_MMA) return gemm_rcr_mma_peers(a, b01, bias01, c, qtype, dtype, m, rows, k, &peers, s);
+  if (variant == DINOML_B200_GGUF_VARIANT_UMMA) return gemm_rcr_umma_peers(a, b01, bias01, c, qtype, dtype, m, rows, k, &peers, s);
   return RC_RANGE;                                                     // the simt variant has no gated epilogue
 }
-int dual_gemm_rcr(const void* a, const void* b01, void* c, int qtype, int dtype, int m, int n, int k, int activation, int variant,
-                  cudaStream_t s) {
+int dual_gemm_rcr(const void* a, const void* b01, const void* bias01, void* c, int qtype, int dtype, int m, int n, int k, int activation,
+                  int variant, cudaStream_t s) {
   PeerOut none;
   for (int i = 0; i < 8; ++i) none.ptr[i] = nullptr;
   none.count = 0;
   none.act = 0;
-  return dual_gemm_rcr_peers(a, b01, c, none, qtype, dtype, m, n, k, activation, variant, s);
+  return dual_gemm_rcr_peers(a, b01, bias01, c, none, qtype, dtype, m, n, k, activation, variant, s);
 }
 
 float profile_gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n,
@@ -252,6 +254,12 @@ int dinoml_b200_gguf_gemm_rcr_scatter(const void* a, const void* b_quant, const 
 
 int dinoml_b200_gguf_dual_gemm_rcr(const void* a, const void* b01_interleaved, void* c, void* const* peer_c, int n_peers, int qtype,
                                    int dtype, int m, int n, int k, int activation, int variant, void* stream) {
+  return dinoml_b200_gguf_dual_gemm_rcr_bias(a, b01_interleaved, nullptr, c, peer_c, n_peers, qtype, dtype, m, n, k, activation, variant, stream);
+}
+
+int dinoml_b200_gguf_dual_gemm_rcr_bias(const void* a, const void* b01_interleaved, const void* bias01_interleaved, void* c,
+                                        void* const* peer_c, int n_peers, int qtype, int dtype, int m, int n, int k, int activation,
+                                        int variant, void* stream) {
   const char* where = "dinoml_b200_gguf_dual_gemm_rcr";
   if (n_peers < 0 || n_peers > 8 || (n_peers > 0 && peer_c == nullptr)) return set_error(RC_RANGE, where);
   PeerOut peers;
@@ -260,7 +268,7 @@ int dinoml_b200_gguf_dual_gemm_rcr(const void* a, const void* b01_interleaved, v
   peers.act = 0;
   for (int i = 0; i < n_peers; ++i)
     if (peers.ptr[i] == nullptr) return set_error(RC_NULL, where);
-  return set_error(dual_gemm_rcr_peers(a, b01_interleaved, c, peers, qtype, dtype, m, n, k, activation, variant,
+  return set_error(dual_gemm_rcr_peers(a, b01_interleaved, bias01_interleaved, c, peers, qtype, dtype, m, n, k, activation, variant,
                                        static_cast<cudaStream_t>(stream)), where);
 }
 

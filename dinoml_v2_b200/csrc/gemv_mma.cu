@@ -255,6 +255,10 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
         float u = sOut[idx + 8];
         if (SLICED)
           for (int peer = 1; peer < ks; ++peer) u += ld_cluster_f32(&sOut[idx + 8], uint32_t(peer));
+        if (bias != nullptr) {             // interleaved like the rows: bias0 of the gate row, bias1 of its up row
+          v += MT::to_float(bias[row]);
+          u += MT::to_float(bias[row + 8]);
+        }
         v = gate_activation(v, peers.act) * u;
         at = int64_t(c) * (n >> 1) + (blockIdx.x * 8 + r);
       } else if (bias != nullptr) {

@@ -236,7 +236,12 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
         if (peers.act != ACT_NONE) {
           // gated pair: rows r < 8 of the tile belong to the first matrix, r + 8 to the second; output has n / 2 columns
           if (r >= 8) continue;
-          v = gate_activation(v, peers.act) * sOut[idx + 8];
+          float u = sOut[idx + 8];
+          if (bias != nullptr) {           // interleaved like the rows: bias0 of the gate row, bias1 of its up row
+            v += MT::to_float(bias[row]);
+            u += MT::to_float(bias[row + 8]);
+          }
+          v = gate_activation(v, peers.act) * u;
           at = int64_t(c) * (n >> 1) + (tile * 8 + r);
         } else if (bias != nullptr) {
           v += MT::to_float(bias[row]);

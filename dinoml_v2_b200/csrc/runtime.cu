@@ -41,8 +41,8 @@
 namespace b200gguf {
 int set_error_message(int rc, const std::string& message);
 const char* last_error();
-int dual_gemm_rcr(const void* a, const void* b01, void* c, int qtype, int dtype, int m, int n, int k, int activation, int variant,
-                  cudaStream_t s);
+int dual_gemm_rcr(const void* a, const void* b01, const void* bias01, void* c, int qtype, int dtype, int m, int n, int k, int activation,
+                  int variant, cudaStream_t s);
 int gemm_rcr(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
              int variant, cudaStream_t s);
 }  // namespace b200gguf
@@ -249,10 +249,11 @@ int parse_plan(DinoModule* mod, const std::string& path) {
       std::string op, a, b, bias, out;
       NodeSpec n;
       if (!(ls >> op >> a >> b >> bias >> out >> n.variant)) return fail(where + "malformed node record");
-      if (op == "dual_gemm_rcr_silu") n.activation = 1;
-      else if (op == "dual_gemm_rcr_fast_gelu") n.activation = 2;
+      if (op == "dual_gemm_rcr_silu" || op == "dual_gemm_rcr_bias_silu") n.activation = 1;
+      else if (op == "dual_gemm_rcr_fast_gelu" || op == "dual_gemm_rcr_bias_fast_gelu") n.activation = 2;
       else if (op != "gemm_rcr" && op != "gemm_rcr_bias") return fail(where + "unsupported op " + op);
-      if (n.activation != 0 && bias != "-") return fail(where + "dual_gemm_rcr takes no bias");
+      if (n.activation != 0 && (bias != "-") != (op.find("_bias_") != std::string::npos))
+        return fail(where + op + (bias == "-" ? " needs its interleaved bias constant" : " takes no bias"));
       n.a = find_tensor(*mod, a);
       n.out = find_tensor(*mod, out);
       n.b = find_constant(*mod, b);
@@ -538,7 +539,8 @@ int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTe
     for (const DispatchSpec& d : mod.dispatch)
       if (d.node == int(ni) && d.m == m && d.n == n && d.k == k) { variant = d.variant; break; }
     const void* bias = node.bias >= 0 ? mod.constants[node.bias].device : nullptr;
-    if (node.bias >= 0 && mod.constants[node.bias].shape.back() != n) return fail("bias length does not match N");
+    if (node.bias >= 0 && mod.constants[node.bias].shape.back() != (node.activation != 0 ? 2 * n : n))
+      return fail(node.activation != 0 ? "interleaved dual-GEMM bias must hold 2N values" : "bias length does not match N");
     // where the weight bytes are for this launch
     const void* wptr = w.device;
     int slot = -1;
@@ -559,7 +561,7 @@ int run_plan(DinoSession* s, const DinoTensor* inputs, size_t num_inputs, DinoTe
       cudaEventRecord(a, s->stream);
     }
     const int rc = node.activation != 0
-                       ? b200gguf::dual_gemm_rcr(ptr[node.a], wptr, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
+                       ? b200gguf::dual_gemm_rcr(ptr[node.a], wptr, bias, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
                                                  node.activation, variant, s->stream)
                        : b200gguf::gemm_rcr(ptr[node.a], wptr, bias, ptr[node.out], w.qtype, ospec.dtype, int(m), int(n), int(k),
                                             variant, s->stream);

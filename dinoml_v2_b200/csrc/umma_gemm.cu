@@ -489,7 +489,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             const int64_t n_out = p.n >> 1;
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-              const float mine = __uint_as_float(r[j]);
+              const float mine = __uint_as_float(r[j]) + bias_v;       // bias interleaved like the rows (0 without one)
               const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
               if ((lane & 8) == 0 && n_row < p.n && m0 + col + j < p.m) {
                 const T v = P::cvt(gate_activation(mine, p.peers.act) * other);

@@ -142,23 +142,40 @@ def _fuse_dual_gemm_weights(nodes: list[dict[str, Any]], bound: dict[str, tuple]
     for node in nodes:
         if not node["op"].startswith("dual_gemm_rcr_"):
             continue
-        _, n0, n1 = node["inputs"]
+        n0, n1 = node["inputs"][1], node["inputs"][2]
         (dt0, sh0, a0, st0), (dt1, sh1, a1, st1) = bound[n0], bound[n1]
         if not (st0 and st1 and st0.get("kind") == "gguf" and st1.get("kind") == "gguf"):
             raise NotImplementedError(f"{node['op']}: both weights must be GGUF-encoded constants")
-        if st0["qtype"] != st1["qtype"] or sh0 != sh1 or dt0 != dt1 or sh0[0] % 8:
-            raise NotImplementedError(f"{node['op']}: the two weights need one qtype, one shape and N % 8 == 0")
+        broadcast = tuple(sh1) == (1, sh0[1]) and sh0[0] != 1           # B1 [1, K]: its one row is repeated for every output column
+        if st0["qtype"] != st1["qtype"] or (tuple(sh0) != tuple(sh1) and not broadcast) or dt0 != dt1 or sh0[0] % 8:
+            raise NotImplementedError(f"{node['op']}: the two weights need one qtype, one shape (or B1 [1, K]) and N % 8 == 0")
         n, k = sh0
         rb = a0.size // n
-        fused = np.ascontiguousarray(np.stack((a0.reshape(n // 8, 8, rb), a1.reshape(n // 8, 8, rb)), axis=1).reshape(-1))
+        rows1 = np.broadcast_to(a1.reshape(1, rb), (n, rb)) if broadcast else a1.reshape(n, rb)
+        fused = np.ascontiguousarray(np.stack((a0.reshape(n // 8, 8, rb), rows1.reshape(n // 8, 8, rb)), axis=1).reshape(-1))
         storage = dict(st0)
         storage.update({"tensor": f"{st0['tensor']}+{st1['tensor']}", "shape": [2 * n, k], "encoded_nbytes": int(fused.nbytes),
                         "gguf_shape": [k, 2 * n], "derived": {"kind": "interleave_rows8", "sources": [n0, n1],
                                                                "source_paths": [st0.get("path"), st1.get("path")]}})
         name = f"{n0}+{n1}.rows8"
         bound[name] = (dt0, (2 * n, k), fused, storage)
-        node["inputs"] = [node["inputs"][0], name]
-        node["attrs"]["sources"] = [n0, n1]
+        sources = [n0, n1]
+        fused_inputs = [node["inputs"][0], name]
+        if len(node["inputs"]) == 5:          # the _bias_ forms: bias0 [N] and bias1 [N] (or [1]) become ONE dense vector in the same order
+            nb0, nb1 = node["inputs"][3], node["inputs"][4]
+            (bdt0, _, v0, bst0), (bdt1, _, v1, bst1) = bound[nb0], bound[nb1]
+            if bst0 or bst1 or bdt0 != dt0 or bdt1 != dt0:
+                raise NotImplementedError(f"{node['op']}: bias0 / bias1 must be dense constants of the activation dtype")
+            v0, v1 = np.asarray(v0).reshape(-1), np.asarray(v1).reshape(-1)
+            if v0.size != n or v1.size != (1 if broadcast else n):
+                raise ValueError(f"{node['op']}: bias0 needs {n} elements and bias1 {1 if broadcast else n}")
+            v1 = np.broadcast_to(v1, (n,))
+            bias_name = f"{nb0}+{nb1}.rows8"
+            bound[bias_name] = (dt0, (2 * n,), np.ascontiguousarray(np.stack((v0.reshape(n // 8, 8), v1.reshape(n // 8, 8)), axis=1).reshape(-1)), None)
+            fused_inputs.append(bias_name)
+            sources += [nb0, nb1]
+        node["inputs"] = fused_inputs
+        node["attrs"]["sources"] = sources
     used = {name for node in nodes for name in node["inputs"]}
     for node in nodes:
         for src in node["attrs"].get("sources", []):

@@ -68,21 +68,31 @@ def gemm_rcr(a: torch.Tensor, b_quant: torch.Tensor, qtype, bias: torch.Tensor |
 
 def interleave_rows8(b0, b1):
     """Row order the gated dual GEMM expects: rows 16t..16t+7 = rows 8t..8t+7 of b0, rows 16t+8..16t+15 = of b1.
-    b0, b1: uint8 [N, row_bytes] (torch tensors or numpy arrays), N % 8 == 0.  Blocks are not touched."""
+    b0, b1: [N, row_bytes] (torch tensors or numpy arrays), N % 8 == 0; a b1 of ONE row (the reference's [1, K] broadcast,
+    src/dinoml/kernels/families/dual_gemm.py:60-66) is repeated N times.  Blocks are not touched."""
+    if b1.shape[0] == 1 and b0.shape[0] != 1 and b1.shape[1:] == b0.shape[1:]:
+        b1 = b1.expand(b0.shape[0], -1) if isinstance(b1, torch.Tensor) else __import__("numpy").broadcast_to(b1, b0.shape)
     if b0.shape != b1.shape or b0.shape[0] % 8:
-        raise ValueError("both weights must have the same shape and a row count that is a multiple of 8")
+        raise ValueError("both weights must have the same shape (or b1 one row) and a row count that is a multiple of 8")
     n, rb = b0.shape
     if isinstance(b0, torch.Tensor):
-        return torch.stack((b0.view(n // 8, 8, rb), b1.view(n // 8, 8, rb)), dim=1).reshape(2 * n, rb).contiguous()
+        return torch.stack((b0.reshape(n // 8, 8, rb), b1.reshape(n // 8, 8, rb)), dim=1).reshape(2 * n, rb).contiguous()
     import numpy as np
     return np.ascontiguousarray(np.stack((b0.reshape(n // 8, 8, rb), b1.reshape(n // 8, 8, rb)), axis=1).reshape(2 * n, rb))
 
 
+def interleave_bias8(bias0, bias1):
+    """[2N] bias vector of the gated dual GEMM with bias: 8 values of bias0, the 8 matching values of bias1, ... - the order of
+    `interleave_rows8`.  bias1 of one element (B1 [1, K]) is repeated."""
+    return interleave_rows8(bias0.reshape(-1, 1), bias1.reshape(-1, 1)).reshape(-1)
+
+
 def dual_gemm_rcr(a: torch.Tensor, b01_interleaved: torch.Tensor, qtype, activation: str = "silu", *, variant: str = "auto",
-                  out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
-    """act(a @ dequant(B0)^T) * (a @ dequant(B1)^T) in one launch; `b01_interleaved` = interleave_rows8(B0, B1).
-    a [..., K] -> [..., N] with N = rows of each matrix.  Mirrors dml.ops.dual_gemm_rcr_silu / _fast_gelu of the reference
-    (src/dinoml/ops/gemm.py:63-121) for GGUF weights."""
+                  out: torch.Tensor | None = None, stream=None, bias01_interleaved: torch.Tensor | None = None) -> torch.Tensor:
+    """act(a @ dequant(B0)^T [+ bias0]) * (a @ dequant(B1)^T [+ bias1]) in one launch; `b01_interleaved` =
+    interleave_rows8(B0, B1), `bias01_interleaved` = interleave_bias8(bias0, bias1) in the activation dtype.
+    a [..., K] -> [..., N] with N = rows of each matrix.  Mirrors dml.ops.dual_gemm_rcr_silu / _fast_gelu and their
+    _bias_ forms of the reference (src/dinoml/ops/gemm.py:63-121) for GGUF weights."""
     q = qtype_of(qtype)
     _require_cuda(a, "a")
     _require_cuda(b01_interleaved, "b01_interleaved")
@@ -97,8 +107,13 @@ def dual_gemm_rcr(a: torch.Tensor, b01_interleaved: torch.Tensor, qtype, activat
     if out is None:
         out = torch.empty(a.shape[:-1] + (n,), dtype=a.dtype, device=a.device)
     _require_cuda(out, "out")
-    rc = _native.lib().dinoml_b200_gguf_dual_gemm_rcr(
-        a.data_ptr(), b01_interleaved.data_ptr(), out.data_ptr(), None, 0, q.value, _native.DINO_DTYPE[_DTYPE_NAME[a.dtype]], m, n, k,
+    if bias01_interleaved is not None:
+        _require_cuda(bias01_interleaved, "bias01_interleaved")
+        if bias01_interleaved.dtype != a.dtype or bias01_interleaved.numel() != 2 * n:
+            raise ValueError("bias01_interleaved must have the activation dtype and 2N elements")
+    rc = _native.lib().dinoml_b200_gguf_dual_gemm_rcr_bias(
+        a.data_ptr(), b01_interleaved.data_ptr(), bias01_interleaved.data_ptr() if bias01_interleaved is not None else None,
+        out.data_ptr(), None, 0, q.value, _native.DINO_DTYPE[_DTYPE_NAME[a.dtype]], m, n, k,
         _native.ACTIVATIONS[activation], _native.variant_code(variant), _stream_ptr(stream))
     _native.check(rc, "dinoml_b200_gguf_dual_gemm_rcr")
     return out

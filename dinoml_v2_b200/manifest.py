@@ -22,8 +22,8 @@ KERNEL_MANIFEST_SCHEMA_VERSION = 4
 KERNEL_ABI_VERSION = 1
 PROFILE_CACHE_SCHEMA_VERSION = 9
 EXECUTION_PLAN_KERNEL_LIBRARIES = (KERNEL_LIBRARY,)          # src/dinoml/kernels/manifest.py:98-105
-SUPPORTED_OPS = ("gemm_rcr", "gemm_rcr_bias", "dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu")
-DUAL_OPS = ("dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu")
+DUAL_OPS = ("dual_gemm_rcr_silu", "dual_gemm_rcr_fast_gelu", "dual_gemm_rcr_bias_silu", "dual_gemm_rcr_bias_fast_gelu")
+SUPPORTED_OPS = ("gemm_rcr", "gemm_rcr_bias") + DUAL_OPS
 VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3, "stream": 4}
 # Tuning configurations of the persistent GEMV (csrc/gemv_stream.cu): each is a candidate of its own, as the tile / stage /
 # warp entries of the reference's CUTLASS catalogue are (src/dinoml/kernels/providers/cutlass/gemm.py:19-127).
@@ -92,6 +92,9 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
     q = qtype_of(qtype)
     has_bias = op.endswith("_bias")
     dual_act = op[len("dual_gemm_rcr_"):] if op.startswith("dual_gemm_rcr_") else None
+    dual_bias = bool(dual_act) and dual_act.startswith("bias_")
+    if dual_bias:
+        dual_act = dual_act[len("bias_"):]
     family, _, config = variant.partition(":")
     tag = family + (f"_c{config}" if config else "")
     tuning = dict(_B200_TUNING[family])
@@ -117,11 +120,16 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
         "variant": variant, "variant_code": variant_code(variant),
     }
     if dual_act:      # one generic entry point (activation and variant are arguments); epilogue named as in the reference
+        # names of the reference's epilogues: left_<act>_and_mul / left_bias_<act>_and_mul (kernels/families/dual_gemm.py:93-135)
+        epi = f"left_{'bias_' if dual_bias else ''}{dual_act}_and_mul"
+        abi = "gguf_dual_gemm_rcr_bias_v1" if dual_bias else "gguf_dual_gemm_rcr_v1"
         cand.update({"family": "dual_gemm", "layouts": {"a": "row", "b0": "column", "b1": "column", "c": "row"},
-                     "epilogue": f"left_{dual_act}_and_mul", "launch_abi": "gguf_dual_gemm_rcr_v1",
-                     "kernel_symbol": "dinoml_b200_gguf_dual_gemm_rcr", "profiler_symbol": None})
-        cand["epilogue_config"] = {"name": f"left_{dual_act}_and_mul", "inputs": [], "activation": dual_act, "bias_axis": None,
-                                   "accumulator_dtype": "float32", "output_dtype": dtype, "launch_abi": "gguf_dual_gemm_rcr_v1",
+                     "epilogue": epi, "launch_abi": abi,
+                     "kernel_symbol": "dinoml_b200_gguf_dual_gemm_rcr_bias" if dual_bias else "dinoml_b200_gguf_dual_gemm_rcr",
+                     "profiler_symbol": None})
+        cand["epilogue_config"] = {"name": epi, "inputs": ["bias0", "bias1"] if dual_bias else [], "activation": dual_act,
+                                   "bias_axis": "n" if dual_bias else None,
+                                   "accumulator_dtype": "float32", "output_dtype": dtype, "launch_abi": abi,
                                    "weight_rows": "interleave_rows8"}
     cand["candidate_config_key"] = sha256_of({k: cand[k] for k in ("provider", "op", "dtype", "qtype", "variant", "b200", "launch_abi")})
     return cand
@@ -182,7 +190,8 @@ def build_kernel_manifest(graph: Mapping[str, Any], target: Mapping[str, Any]) -
                 raise NotImplementedError(f"{node['op']} needs a tensor-core variant: {qtype} / {dtype} has none")
         required.append({
             "node_id": node["id"], "op": node["op"], "dtype": dtype, "qtype": qtype,
-            "kernel_symbol": "dinoml_b200_gguf_dual_gemm_rcr" if dual else "dinoml_b200_gguf_gemm_rcr", "kernel_library": KERNEL_LIBRARY,
+            "kernel_symbol": ("dinoml_b200_gguf_dual_gemm_rcr_bias" if "_bias_" in node["op"] else "dinoml_b200_gguf_dual_gemm_rcr") if dual
+                             else "dinoml_b200_gguf_gemm_rcr", "kernel_library": KERNEL_LIBRARY,
             "profiler_symbol": None if dual else "dinoml_profile_b200_gguf_gemm_rcr", "has_profiler": not dual,
             "support_archive": "libdinoml_b200_gguf.so",
             "selected_candidate_id": None, "selection": "shape_guarded_auto",

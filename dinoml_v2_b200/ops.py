@@ -40,10 +40,12 @@ def gemm_rcr_bias(a: Tensor, b: Tensor, bias: Tensor) -> Tensor:
 DUAL_GEMM_ACTIVATIONS = ("silu", "fast_gelu")     # the two the reference's CPU template implements (dual_gemm_cpu.cpp.j2:66-70)
 
 
-def _dual_gemm(activation: str, a: Tensor, b0: Tensor, b1: Tensor) -> Tensor:
-    """act(a @ b0^T) * (a @ b1^T) - dml.ops.dual_gemm_rcr_<activation> (src/dinoml/ops/gemm.py:63-121,
-    src/dinoml/kernels/families/dual_gemm.py:36-76).  Here b0 and b1 must both be [N, K] (no [1, K] broadcast)."""
-    op = f"dual_gemm_rcr_{activation}"
+def _dual_gemm(activation: str, a: Tensor, b0: Tensor, b1: Tensor, bias0: Tensor | None = None, bias1: Tensor | None = None) -> Tensor:
+    """act(a @ b0^T [+ bias0]) * (a @ b1^T [+ bias1]) - dml.ops.dual_gemm_rcr_[bias_]<activation> (src/dinoml/ops/gemm.py:63-121,
+    src/dinoml/kernels/families/dual_gemm.py:36-76).  b1 is [N, K] or [1, K] (then bias1 has one element): the shape rules
+    of DualGemmOpSpec.validate_shapes."""
+    has_bias = bias0 is not None or bias1 is not None
+    op = f"dual_gemm_rcr_{'bias_' if has_bias else ''}{activation}"
     if len(a.shape) < 1 or len(b0.shape) != 2 or len(b1.shape) != 2:
         raise ValueError(f"{op} expects A[..., K] and rank-2 B0 / B1 tensors")
     if a.dtype not in GEMM_SUPPORTED_DTYPES or a.dtype != b0.dtype or a.dtype != b1.dtype:
@@ -51,9 +53,18 @@ def _dual_gemm(activation: str, a: Tensor, b0: Tensor, b1: Tensor) -> Tensor:
     k = _static(a.shape[-1])
     if k is None or k != _static(b0.shape[1]) or k != _static(b1.shape[1]):
         raise ValueError(f"{op} expected B0[N, K] and B1[N, K] with K = {a.shape[-1]}, got {b0.shape} and {b1.shape}")
-    if tuple(b0.shape) != tuple(b1.shape):
-        raise ValueError(f"{op} expected B1 to match B0 {list(b0.shape)}, got {list(b1.shape)}")
-    return current_builder().add_node(op, [a, b0, b1], tuple(a.shape[:-1]) + (b0.shape[0],), a.dtype, {"activation": activation})
+    n, b1_n = _static(b0.shape[0]), _static(b1.shape[0])
+    if b1_n != n and b1_n != 1:
+        raise ValueError(f"{op} expected B1[N, K] or B1[1, K] matching N={n}, got {list(b1.shape)}")
+    inputs = [a, b0, b1]
+    if has_bias:
+        if bias0 is None or bias1 is None:
+            raise ValueError(f"{op} expects both bias0 and bias1")
+        for name, bias, want in (("bias0", bias0, n), ("bias1", bias1, b1_n)):
+            if bias.dtype != a.dtype or _static(bias.shape[-1]) != want or any(_static(d) != 1 for d in bias.shape[:-1]):
+                raise ValueError(f"{op} expected {name} with {want} elements of dtype {a.dtype}, got {list(bias.shape)} {bias.dtype}")
+        inputs += [bias0, bias1]
+    return current_builder().add_node(op, inputs, tuple(a.shape[:-1]) + (b0.shape[0],), a.dtype, {"activation": activation})
 
 
 def dual_gemm_rcr_silu(a: Tensor, b0: Tensor, b1: Tensor) -> Tensor:
@@ -62,3 +73,11 @@ def dual_gemm_rcr_silu(a: Tensor, b0: Tensor, b1: Tensor) -> Tensor:
 
 def dual_gemm_rcr_fast_gelu(a: Tensor, b0: Tensor, b1: Tensor) -> Tensor:
     return _dual_gemm("fast_gelu", a, b0, b1)
+
+
+def dual_gemm_rcr_bias_silu(a: Tensor, b0: Tensor, b1: Tensor, bias0: Tensor, bias1: Tensor) -> Tensor:
+    return _dual_gemm("silu", a, b0, b1, bias0, bias1)
+
+
+def dual_gemm_rcr_bias_fast_gelu(a: Tensor, b0: Tensor, b1: Tensor, bias0: Tensor, bias1: Tensor) -> Tensor:
+    return _dual_gemm("fast_gelu", a, b0, b1, bias0, bias1)

@@ -124,11 +124,19 @@ DINOML_B200_API int dinoml_b200_gguf_device_status(void);
  * of B0, rows 16t+8 .. 16t+15 are rows 8t .. 8t+7 of B1 (blocks untouched; a row copy at load time,
  * dinoml_v2_b200.kernels.interleave_rows8).  With that order a gate row and its up row sit in the same thread of the
  * mma GEMV and in lanes l / l^8 of the tcgen05 epilogue, so the gate never goes to memory: one launch for the Llama
- * gate / up pair.  N % 8 == 0; variants mma (M <= 16; Q4_K and Q6_K only) and umma (M >= 9) with their usual K /
- * alignment rules, so Q8_0 is served from M = 9 and refused with code 8 below; optional
- * extra destinations as in dinoml_b200_gguf_gemm_rcr_scatter (n_peers = 0: none). */
+ * gate / up pair.  N % 8 == 0; variants stream (M <= 8) and mma (M <= 16) for Q4_K and Q6_K, umma for every type with
+ * its usual K / alignment rules; AUTO sends Q8_0 to the umma variant at every M.  Optional extra destinations as in
+ * dinoml_b200_gguf_gemm_rcr_scatter (n_peers = 0: none).
+ * dinoml_b200_gguf_dual_gemm_rcr_bias is the reference's dual_gemm_rcr_bias_<act> (left_bias_<act>_and_mul,
+ * dual_gemm.py:105-135; dual_gemm_cpu.cpp.j2:66-69): c = act(a B0^T + bias0) * (a B1^T + bias1).  `bias01_interleaved`
+ * holds 2N values in `dtype`, interleaved in groups of 8 exactly like the rows (8 values of bias0, the 8 matching values
+ * of bias1, ...); null = no bias.  A B1 / bias1 of one row ([1, K] broadcast in the reference) is passed as N copies of
+ * that row: the host side repeats the row when it builds the interleaved constant. */
 DINOML_B200_API int dinoml_b200_gguf_dual_gemm_rcr(const void* a, const void* b01_interleaved, void* c, void* const* peer_c, int n_peers,
                                                    int qtype, int dtype, int m, int n, int k, int activation, int variant, void* stream);
+DINOML_B200_API int dinoml_b200_gguf_dual_gemm_rcr_bias(const void* a, const void* b01_interleaved, const void* bias01_interleaved, void* c,
+                                                        void* const* peer_c, int n_peers, int qtype, int dtype, int m, int n, int k,
+                                                        int activation, int variant, void* stream);
 
 /* ---- sharded decode over peer memory (no counterpart in the reference, which is single-GPU) ----------------------
  * dinoml_b200_gguf_gemv_rcr_scatter: the mma GEMV (M <= 16, Q4_K / Q6_K, float16 / bfloat16; same checks and codes as

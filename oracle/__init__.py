@@ -190,12 +190,16 @@ def within_operand_noise(expected, actual, noise, dtype: str, tol: float, sigmas
     return bool(np.all(d <= tol * np.maximum(1.0, np.abs(e)) + sigmas * OPERAND_ULP[dtype] * np.asarray(noise)))
 
 
-def dual_gemm_quant(a, blocks0, blocks1, qtype, n: int, k: int, activation: str = "silu"):
+def dual_gemm_quant(a, blocks0, blocks1, qtype, n: int, k: int, activation: str = "silu", bias0=None, bias1=None):
     """CPU restatement of the reference's dual GEMM on dequantized weights
-    (src/dinoml/lowering/ops/templates/dual_gemm_cpu.cpp.j2:52-75): two fp32-accumulated products, the left one through
-    silu / fast_gelu, multiplied, all in float32."""
+    (src/dinoml/lowering/ops/templates/dual_gemm_cpu.cpp.j2:52-75): two fp32-accumulated products (plus bias0 / bias1,
+    :66-69), the left one through silu / fast_gelu, multiplied, all in float32.  blocks1 (and bias1) may hold ONE row:
+    the right factor is then the same for every column (:58-59, the [1, K] broadcast)."""
     left = gemm_quant(a, blocks0, qtype, n, k).astype(np.float32)
-    right = gemm_quant(a, blocks1, qtype, n, k).astype(np.float32)
+    right = gemm_quant(a, blocks1, qtype, int(np.asarray(blocks1).shape[0]), k).astype(np.float32)
+    if bias0 is not None:
+        left = left + np.asarray(bias0, dtype=np.float32).reshape(1, -1)
+        right = right + np.asarray(bias1, dtype=np.float32).reshape(1, -1)
     if activation == "silu":
         with np.errstate(over="ignore"):                 # exp(-left) may be inf for very negative left: the quotient is then -0
             act = left / (np.float32(1.0) + np.exp(-left, dtype=np.float32))

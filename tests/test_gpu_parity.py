@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import oracle
-from dinoml_v2_b200 import kernels, synthetic as S
+from dinoml_v2_b200 import kernels, manifest as mf, synthetic as S
 from dinoml_v2_b200.gguf_blocks import qtype_of
 
 pytestmark = pytest.mark.gpu
@@ -321,10 +321,40 @@ def test_dual_gemm_gated_epilogue(dev, qtype, activation):
         kernels.dual_gemm_rcr(x.float(), w, qtype, activation)         # fp32 activations have no tensor-core variant
 
 
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0"])
+@pytest.mark.parametrize("activation", ["silu", "fast_gelu"])
+def test_dual_gemm_bias_and_b1_broadcast(dev, qtype, activation):
+    """The reference's _bias_ forms and its B1 [1, K] broadcast: act(a B0^T + bias0) * (a B1^T + bias1) on every kernel that has
+    the gated epilogue (persistent GEMV, tile GEMV, tcgen05 kernel), against the oracle."""
+    k = 2048
+    rng = np.random.Generator(np.random.PCG64(77))
+    for (m, n) in [(1, 104), (4, 200), (8, 48), (16, 64), (40, 136), (300, 264)]:
+        for b1_rows in (n, 1):
+            b0 = S.random_blocks(qtype, n, k, seed=2400 + n)
+            b1 = S.random_blocks(qtype, b1_rows, k, seed=2500 + n)
+            bias0 = rng.standard_normal(n).astype(np.float32)
+            bias1 = rng.standard_normal(b1_rows).astype(np.float32)
+            x, xf = _activations(m, k, 2600 + m, "bfloat16", dev)
+            bias0_t, bias1_t = (torch.from_numpy(v).to(dev).to(torch.bfloat16) for v in (bias0, bias1))
+            ref = oracle.dual_gemm_quant(xf, b0, b1, qtype, n, k, activation, bias0_t.float().cpu().numpy(), bias1_t.float().cpu().numpy())
+            w = kernels.interleave_rows8(torch.from_numpy(b0).to(dev), torch.from_numpy(b1).to(dev))
+            bias = kernels.interleave_bias8(bias0_t, bias1_t)
+            assert w.shape[0] == 2 * n and bias.numel() == 2 * n
+            variants = ["auto"] + [v for v in ("stream", "mma", "umma") if mf.variant_supports(v, m, qtype=qtype, dtype="bfloat16", n=2 * n, k=k)
+                                   and not (qtype == "Q8_0" and v == "mma")]
+            for variant in variants:
+                y = kernels.dual_gemm_rcr(x, w, qtype, activation, bias01_interleaved=bias, variant=variant)
+                assert y.shape == (m, n) and kernels.device_status() == 0
+                _, _, norm = oracle.max_errors(ref, y.float().cpu().numpy())
+                assert norm <= 2e-2, (qtype, activation, variant, m, n, b1_rows, norm)
+    with pytest.raises(ValueError):
+        kernels.dual_gemm_rcr(x, w, qtype, activation, bias01_interleaved=bias[:-1])
+
+
 def test_dual_gemm_q8_0_runs_on_the_tcgen05_kernel_only(dev):
-    """Q8_0 has the gated epilogue from M = 9 (tcgen05 kernel); below that the call is refused, not computed elsewhere."""
+    """Q8_0 has the gated epilogue on the tcgen05 kernel only; AUTO sends every M there (the activation tile is zero-filled past M)."""
     k = 1024
-    for (m, n) in [(9, 64), (16, 2048), (40, 136), (300, 264)]:
+    for (m, n) in [(1, 64), (4, 136), (9, 64), (16, 2048), (40, 136), (300, 264)]:
         b0 = S.random_blocks("Q8_0", n, k, seed=1700 + n)
         b1 = S.random_blocks("Q8_0", n, k, seed=1800 + n)
         x, xf = _activations(m, k, 1900 + m, "bfloat16", dev)
@@ -335,7 +365,7 @@ def test_dual_gemm_q8_0_runs_on_the_tcgen05_kernel_only(dev):
         _, _, norm = oracle.max_errors(ref, y.float().cpu().numpy())
         assert norm <= 2e-2, (m, n, norm)
     with pytest.raises(RuntimeError):
-        kernels.dual_gemm_rcr(x[:4].contiguous(), w, "Q8_0", "silu")
+        kernels.dual_gemm_rcr(x[:4].contiguous(), w, "Q8_0", "silu", variant="mma")       # its tile GEMV has no gated epilogue
 
 
 def test_gemm_bias_and_batch_dims(dev):

@@ -115,6 +115,41 @@ def test_session_dual_gemm_matches_oracle(tmp_path, activation):
     mod.close()
 
 
+def test_session_dual_gemm_bias_broadcast_matches_oracle(tmp_path):
+    """dual_gemm_rcr_bias_silu with B1 [1, K] / bias1 [1] through compile -> load -> run."""
+    from dinoml_v2_b200.constant_sources import GGUFConstant
+    n, k = 72, 1024
+    b0, b1 = S.random_blocks("Q4_K", n, k, 41), S.random_blocks("Q4_K", 1, k, 42)
+    bias0 = np.linspace(-2, 2, n).astype(np.float32)
+    bias1 = np.array([0.5], dtype=np.float32)
+
+    class Gate(dml.Module):
+        def __init__(self):
+            self.w_gate = dml.Parameter([n, k], dtype="bfloat16")
+            self.w_up = dml.Parameter([1, k], dtype="bfloat16")
+            self.b_gate = dml.Parameter([n], dtype="bfloat16")
+            self.b_up = dml.Parameter([1], dtype="bfloat16")
+
+        def forward(self, x):
+            return dml.ops.dual_gemm_rcr_bias_silu(x, self.w_gate, self.w_up, self.b_gate, self.b_up)
+
+    spec = dml.trace(Gate(), inputs={"x": dml.TensorSpec([dml.Dim("m", 1, 64), k], "bfloat16")},
+                     constants={"w_gate": GGUFConstant.from_blocks(b0, "Q4_K", (n, k), tensor="gate"),
+                                "w_up": GGUFConstant.from_blocks(b1, "Q4_K", (1, k), tensor="up"), "b_gate": bias0, "b_up": bias1})
+    art = dml.compile(spec, dml.Target("cuda"), tmp_path / "art")
+    mod = dml.runtime.load(art.path)
+    mod.load_encoded_constants()
+    sess = mod.create_session()
+    rb = lambda v: S.bf16_bits_to_float32(S.float32_to_bf16_bits(v))
+    for m in (1, 5, 33):
+        x = S.random_activations(m, k, 50 + m, "float32")
+        y = sess.run_numpy({"x": x})["t0"]
+        ref = oracle.dual_gemm_quant(rb(x), b0, b1, "Q4_K", n, k, "silu", rb(bias0), rb(bias1))
+        _, _, norm = oracle.max_errors(ref, y)
+        assert y.shape == (m, n) and norm <= 2e-2, (m, norm)
+    mod.close()
+
+
 def test_session_benchmark_and_external_stream(tmp_path):
     n, k = 256, 1024
     art, blocks, _ = _artifact(tmp_path, "Q4_K", n, k)

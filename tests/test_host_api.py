@@ -274,6 +274,41 @@ def test_dual_gemm_trace_fuses_the_two_weights_and_compiles(tmp_path):
         dml.trace(Gate(), inputs={"x": dml.TensorSpec([1, k], "bfloat16")}, constants=consts)
 
 
+def test_dual_gemm_bias_and_b1_broadcast_trace(tmp_path):
+    """dual_gemm_rcr_bias_fast_gelu with B1 [1, K] and bias1 [1] (the reference's broadcast form): the one row and the one bias
+    value are repeated when the interleaved constants are built; the plan names the fused bias."""
+    n, k = 16, 256
+    b0, b1 = S.random_blocks("Q4_K", n, k, 1), S.random_blocks("Q4_K", 1, k, 2)
+    bias0, bias1 = np.arange(n, dtype=np.float32), np.array([5.0], dtype=np.float32)
+
+    class Gate(dml.Module):
+        def __init__(self):
+            self.w_gate = dml.Parameter([n, k], dtype="bfloat16")
+            self.w_up = dml.Parameter([1, k], dtype="bfloat16")
+            self.b_gate = dml.Parameter([n], dtype="bfloat16")
+            self.b_up = dml.Parameter([1], dtype="bfloat16")
+
+        def forward(self, x):
+            return dml.ops.dual_gemm_rcr_bias_fast_gelu(x, self.w_gate, self.w_up, self.b_gate, self.b_up)
+
+    consts = {"w_gate": cs.GGUFConstant.from_blocks(b0, "Q4_K", (n, k), tensor="gate"),
+              "w_up": cs.GGUFConstant.from_blocks(b1, "Q4_K", (1, k), tensor="up"), "b_gate": bias0, "b_up": bias1}
+    spec = dml.trace(Gate(), inputs={"x": dml.TensorSpec([dml.Dim("m", 1, 8), k], "bfloat16")}, constants=consts)
+    node = spec.graph["nodes"][0]
+    assert node["op"] == "dual_gemm_rcr_bias_fast_gelu" and node["inputs"] == ["x", "w_gate+w_up.rows8", "b_gate+b_up.rows8"]
+    fused = spec.constant_arrays["w_gate+w_up.rows8"].reshape(2 * n, -1)
+    assert np.array_equal(fused[0:8], b0[0:8]) and all(np.array_equal(fused[8 + i], b1[0]) for i in range(8)) and np.array_equal(fused[16:24], b0[8:16])
+    fb = S.bf16_bits_to_float32(np.asarray(spec.constant_arrays["b_gate+b_up.rows8"]).reshape(-1))
+    assert fb.tolist() == [0, 1, 2, 3, 4, 5, 6, 7] + [5.0] * 8 + [8, 9, 10, 11, 12, 13, 14, 15] + [5.0] * 8
+    art = dml.compile(spec, dml.Target("cuda"), tmp_path / "art")
+    item = json.loads((art.path / "kernel_manifest.json").read_text())["required_kernels"][0]
+    assert item["kernel_symbol"] == "dinoml_b200_gguf_dual_gemm_rcr_bias"
+    assert item["candidates"][0]["epilogue"] == "left_bias_fast_gelu_and_mul" and item["candidates"][0]["epilogue_config"]["inputs"] == ["bias0", "bias1"]
+    assert "node dual_gemm_rcr_bias_fast_gelu x w_gate+w_up.rows8 b_gate+b_up.rows8 t0 0" in (art.path / "module_plan.txt").read_text()
+    with pytest.raises(ValueError):
+        dml.trace(Gate(), inputs={"x": dml.TensorSpec([1, k], "bfloat16")}, constants=dict(consts, b_up=np.zeros(3, dtype=np.float32)))
+
+
 def test_variant_predicate_is_the_librarys_own():
     """Candidates are filtered with the native predicate for the whole problem, not by M alone (a Q8_0 weight whose K is a
     multiple of 32 but not of 256 has no tensor-core variant; Q6_K rows must be 16-byte multiples for the tcgen05 kernel)."""

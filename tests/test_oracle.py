@@ -262,6 +262,12 @@ def test_dual_gemm_oracle_and_row_interleave():
     assert got.dtype == np.float32 and np.allclose(got, want, rtol=1e-5, atol=1e-6)
     gelu = 0.5 * left * (1.0 + np.tanh(0.7978845608 * left * (1.0 + 0.044715 * left * left))) * right
     assert np.allclose(oracle.dual_gemm_quant(x, b0, b1, "Q4_K", n, k, "fast_gelu"), gelu, rtol=1e-5, atol=1e-6)
+    # the _bias_ forms and the B1 [1, K] broadcast (dual_gemm_cpu.cpp.j2:58-69)
+    bias0, bias1 = np.linspace(-1, 1, n).astype(np.float32), np.array([0.25], dtype=np.float32)
+    lb, rb = left + bias0, right[:, :1] + bias1
+    want_b = lb / (1.0 + np.exp(-lb)) * rb
+    got_b = oracle.dual_gemm_quant(x, b0, b1[:1], "Q4_K", n, k, "silu", bias0, bias1)
+    assert got_b.shape == (3, n) and np.allclose(got_b, want_b, rtol=1e-5, atol=1e-6)
     rows0, rows1 = np.arange(16, dtype=np.uint8).reshape(16, 1), 100 + np.arange(16, dtype=np.uint8).reshape(16, 1)
     order = [0, 1, 2, 3, 4, 5, 6, 7, 100, 101, 102, 103, 104, 105, 106, 107, 8, 9, 10, 11, 12, 13, 14, 15, 108, 109, 110, 111, 112, 113, 114, 115]
     # interleave_rows8 needs torch only for tensors; numpy inputs stay on the CPU
