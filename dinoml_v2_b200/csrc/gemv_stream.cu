@@ -1,4 +1,5 @@
-// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations, Q4_K and Q6_K weights.
+// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations: Q4_K and Q6_K weights on tensor cores,
+// and the six further block layouts (Q4_0, Q5_K, Q2_K, Q3_K, MXFP4, NVFP4) on the same data path with fp32 FMA arithmetic.
 //
 // C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), W streamed once from HBM as packed GGUF blocks (Q4_K 144 B, Q6_K 210 B per
 // 256 weights; Q6_K needs K % 2048 == 0 so that every row piece starts on a 16-byte boundary, other K stay with the tile
@@ -51,6 +52,29 @@ constexpr int kKC = 8;                          // super-blocks per row per stag
 template <int QT> struct Geom;
 template <> struct Geom<QTYPE_Q4_K> { static constexpr int kSbBytes = 144, kPitch = kKC * 144 + 32; };
 template <> struct Geom<QTYPE_Q6_K> { static constexpr int kSbBytes = 210, kPitch = kKC * 210; };
+// The further types: packed bytes per 256 weights of a row; the pitch is the stage piece rounded up to 128 B, plus 16, so
+// that the byte reads of 16 rows spread over the banks and every row starts 16-byte aligned (bulk-copy destination).
+template <int BYTES> struct GenericGeom { static constexpr int kSbBytes = BYTES, kPitch = (kKC * BYTES + 127) / 128 * 128 + 16; };
+template <> struct Geom<QTYPE_Q4_0> : GenericGeom<8 * 18> {};
+template <> struct Geom<QTYPE_Q5_K> : GenericGeom<176> {};
+template <> struct Geom<QTYPE_Q2_K> : GenericGeom<84> {};
+template <> struct Geom<QTYPE_Q3_K> : GenericGeom<110> {};
+template <> struct Geom<QTYPE_MXFP4> : GenericGeom<8 * 17> {};
+template <> struct Geom<QTYPE_NVFP4> : GenericGeom<4 * 36> {};
+template <int QT> constexpr bool is_generic() { return QT != QTYPE_Q4_K && QT != QTYPE_Q6_K; }
+
+// 8 consecutive activations as floats.
+template <typename T> __device__ __forceinline__ void x8_to_float(const uint4 v, float (&x)[8]);
+template <> __device__ __forceinline__ void x8_to_float<__nv_bfloat16>(const uint4 v, float (&x)[8]) {
+  const uint32_t r[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { x[2 * i] = __uint_as_float(r[i] << 16); x[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u); }
+}
+template <> __device__ __forceinline__ void x8_to_float<__half>(const uint4 v, float (&x)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
+}
 constexpr int kGroupWarps = kKC;
 constexpr int kBarBytes = 256;                  // mbarrier area in front of the ring (up to 32 barriers)
 
@@ -78,6 +102,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   constexpr int MC = MXC == 1 ? 1 : 2;             // accumulator columns a lane keeps
   constexpr int kSbBytes = Geom<QT>::kSbBytes, kPitch = Geom<QT>::kPitch, kStageBytes = kRows * kPitch;
   constexpr bool kMinTerm = QT == QTYPE_Q4_K;      // Q4_K folds its mins and the operand offset against activation sums; Q6_K has neither
+  constexpr bool kGeneric = is_generic<QT>();      // decoded value by value (decode8), fp32 FMA, no tensor cores
   static_assert(D % NG == 0 && D >= 2 * NG, "every group needs its own ring slots, at least two");
   static_assert(MXC == 1 || MXC == 2 || MXC == 4 || MXC == 8, "MXC");
   using Red = RedBuf<MXC, NCW>;
@@ -87,7 +112,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   uint8_t* sW = smem_dyn + kBarBytes;                                         // D x kStageBytes
   Red* sRed = reinterpret_cast<Red*>(sW + size_t(D) * kStageBytes);      // [2]
   float* sX = reinterpret_cast<float*>(sRed + 2);                        // [MXC][k/32]
-  __shared__ __align__(16) float sS[NCW][kRows][QT == QTYPE_Q6_K ? kQ6ScalePitch : 8];   // d * sc per row, sub-block (warp-private scratch)
+  __shared__ __align__(16) float sS[kGeneric ? 1 : NCW][kGeneric ? 1 : kRows][QT == QTYPE_Q6_K ? kQ6ScalePitch : kGeneric ? 4 : 8];   // d * sc per row, sub-block (warp-private scratch)
   __shared__ float sOut[kRows * MXC];                                    // epilogue warp scratch
   __shared__ int s_abort;
   static_assert((2 * D + 4) * 8 <= kBarBytes, "barrier area");
@@ -276,6 +301,9 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   named_barrier(1, NCW * 32);
 
   float res[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+  float gacc[kGeneric ? MXC : 1];               // generic types: this lane's half of row `srow`, per activation row
+#pragma unroll
+  for (int c = 0; c < (kGeneric ? MXC : 1); ++c) gacc[c] = 0.f;
   float zero4[4];
   opaque_zero4(zero4);
   float xt[MXC];
@@ -291,6 +319,17 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
     if (tl >= 2) ok = __all_sync(0xffffffffu, mbar_wait(red_empty(buf), uint32_t((tl >> 1) - 1) & 1u, abort_flag, status, ST_STREAM_RED_EMPTY) ? 1 : 0) != 0;
     if (!ok) return;
     Red& rb = sRed[buf];
+    if constexpr (kGeneric) {
+#pragma unroll
+      for (int c = 0; c < MXC; ++c) {
+        const float both = gacc[c] + __shfl_xor_sync(0xffffffffu, gacc[c], 1);
+        if (shalf == 0) { rb.red[cw][srow][c] = both; rb.xt[cw][srow][c] = 0.f; }
+        gacc[c] = 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(red_full(buf));
+      return;
+    }
     if (2 * t < MXC) {
       rb.red[cw][g][2 * t] = res[0][0];
       rb.red[cw][g + 8][2 * t] = res[0][2];
@@ -321,7 +360,29 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
     ok = __all_sync(0xffffffffu, mbar_wait(full(slot), uint32_t(u / D) & 1u, abort_flag, status, ST_STREAM_FULL) ? 1 : 0) != 0;
     if (!ok) break;
     const int sb = chunk * kKC + wq;
-    if (!PROBE && sb < nsb && QT == QTYPE_Q6_K) {
+    if constexpr (kGeneric) {
+      if (!PROBE && sb < nsb) {
+        // lane pair (srow, shalf): weights shalf * 128 .. + 127 of this warp's super-block of row srow, 8 at a time
+        constexpr int kUnitsPerBlock = QTraits<QT>::kBlock / 8;
+        const uint8_t* rowp = sW + size_t(slot) * kStageBytes + srow * kPitch + wq * kSbBytes;
+        const T* xs = x + int64_t(sb) * 256 + shalf * 128;
+#pragma unroll 2
+        for (int u = 0; u < 16; ++u) {
+          const int uu = shalf * 16 + u;
+          float w8[8];
+          decode8<QT>(rowp + (uu / kUnitsPerBlock) * QTraits<QT>::kBytes, (uu % kUnitsPerBlock) * 8, w8);
+#pragma unroll
+          for (int c = 0; c < MXC; ++c) {
+            if (c < m) {
+              float x8[8];
+              x8_to_float<T>(__ldg(reinterpret_cast<const uint4*>(xs + int64_t(c) * k + u * 8)), x8);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) gacc[c] = fmaf(x8[j], w8[j], gacc[c]);
+            }
+          }
+        }
+      }
+    } else if (!PROBE && sb < nsb && QT == QTYPE_Q6_K) {
       if constexpr (QT == QTYPE_Q6_K) {
         // row pitch and stage size are multiples of 4, so a block's phase against a word boundary is that of wq * 210
         const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
@@ -487,6 +548,11 @@ template <int QT, typename T, int MXC>
 static int launch_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
                     cudaStream_t s) {
   constexpr bool Q6 = QT == QTYPE_Q6_K;
+  if constexpr (is_generic<QT>()) {
+    // the further types have one configuration: 8 consumer warps, two CTAs per SM, 3 or 4 ring slots by stage size
+    if (config != 0 && config != 4) return RC_RANGE;
+    return launch_cfg<QT, T, MXC, 1, (Geom<QT>::kPitch > 1300 ? 3 : 4)>(a, b, bias, c, m, n, k, 2, peers, s);
+  }
   if (config & kProbeBit) {
     if constexpr (MXC == 1 && std::is_same<T, __nv_bfloat16>::value) {
       switch (config & ~kProbeBit) {
@@ -530,7 +596,18 @@ bool gemv_stream_supports(int qtype, int dtype, int m, int n, int k) {
   if (!(dtype == DINO_BF16 || dtype == DINO_F16) || m < 1 || m > 8) return false;
   if (qtype == QTYPE_Q4_K) return k % 256 == 0;
   if (qtype == QTYPE_Q6_K) return k % 2048 == 0;      // 210-byte blocks: row pieces start on 16-byte boundaries only then
-  return false;
+  // the further types: whole 256-weight groups and weight rows that are multiples of 16 bytes (bulk-copy sources)
+  int sb_bytes = 0;
+  switch (qtype) {
+    case QTYPE_Q4_0: sb_bytes = 8 * 18; break;
+    case QTYPE_Q5_K: sb_bytes = 176; break;
+    case QTYPE_Q2_K: sb_bytes = 84; break;
+    case QTYPE_Q3_K: sb_bytes = 110; break;
+    case QTYPE_MXFP4: sb_bytes = 8 * 17; break;
+    case QTYPE_NVFP4: sb_bytes = 4 * 36; break;
+    default: return false;
+  }
+  return k % 256 == 0 && (int64_t(k / 256) * sb_bytes) % 16 == 0;
 }
 int gemv_stream_configs() { return stream::kStreamConfigs; }
 
@@ -541,12 +618,21 @@ int gemm_rcr_stream_peers(const void* a, const void* b, const void* bias, void* 
   if (int rc = check_gemm_args(a, b, c, qtype, dtype, m, n, k)) return rc;
   if (dtype == DINO_F32) return RC_DTYPE;
   if (m > 8) return RC_RANGE;
-  if (qtype != QTYPE_Q4_K && qtype != QTYPE_Q6_K) return RC_QTYPE;
+  if (qtype == QTYPE_Q8_0) return RC_QTYPE;
   if (!gemv_stream_supports(qtype, dtype, m, n, k)) return RC_ALIGN;
   if ((reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(a)) & 15) return RC_ALIGN;   // bulk-copy sources, vector loads
-  if (qtype == QTYPE_Q6_K)
-    return dtype == DINO_BF16 ? stream::launch_q<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, config, peers, s)
-                              : stream::launch_q<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, config, peers, s);
+#define B200_STREAM_QTYPE(QT)                                                                                        \
+  if (qtype == QT)                                                                                                    \
+    return dtype == DINO_BF16 ? stream::launch_q<QT, __nv_bfloat16>(a, b, bias, c, m, n, k, config, peers, s)        \
+                              : stream::launch_q<QT, __half>(a, b, bias, c, m, n, k, config, peers, s);
+  B200_STREAM_QTYPE(QTYPE_Q6_K)
+  B200_STREAM_QTYPE(QTYPE_Q4_0)
+  B200_STREAM_QTYPE(QTYPE_Q5_K)
+  B200_STREAM_QTYPE(QTYPE_Q2_K)
+  B200_STREAM_QTYPE(QTYPE_Q3_K)
+  B200_STREAM_QTYPE(QTYPE_MXFP4)
+  B200_STREAM_QTYPE(QTYPE_NVFP4)
+#undef B200_STREAM_QTYPE
   return dtype == DINO_BF16 ? stream::launch_q<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, config, peers, s)
                             : stream::launch_q<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, config, peers, s);
 }

@@ -32,6 +32,8 @@ STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": {"Q4_K": 5, "Q6_K": 4},
                   3: {"consumer_warps": 16, "ring_slots": {"Q4_K": 8, "Q6_K": 6}, "ctas_per_sm": 1},
                   4: {"consumer_warps": 8, "ring_slots": {"Q4_K": 4, "Q6_K": 3}, "ctas_per_sm": 2}}
 STREAM_QTYPES = ("Q4_K", "Q6_K")
+# the six further layouts run on the same persistent data path with fp32 arithmetic, in ONE configuration (4)
+STREAM_FP32_QTYPES = ("Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4")
 
 _B200_TUNING = {
     "simt": {"kind": "gemv_simt", "rows_per_warp": 1, "activation_rows_per_pass": 4, "staging": "ldg", "tensor_cores": "none"},
@@ -62,6 +64,8 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
             variants.append("umma")
         if qtype in STREAM_QTYPES:
             variants += [f"stream:{c}" for c in sorted(STREAM_CONFIGS)]
+        elif qtype in STREAM_FP32_QTYPES:
+            variants.append("stream:4")
     return variants
 
 
@@ -100,7 +104,10 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
     tuning = dict(_B200_TUNING[family])
     if config:
         tuning.update(STREAM_CONFIGS[int(config)], config=int(config))
-        tuning["ring_slots"] = tuning["ring_slots"][q.name]
+        if q.name in STREAM_FP32_QTYPES:
+            tuning.update(ring_slots=3 if q.name == "Q5_K" else 4, tensor_cores="none", arithmetic="fp32 fma on values decoded 8 at a time")
+        else:
+            tuning["ring_slots"] = tuning["ring_slots"][q.name]
     cand = {
         "candidate_id": f"b200_gguf_{q.symbol}_{dtype}_{tag}_v1",
         "symbol_id": f"{q.symbol}_{tag}_v1",

@@ -94,13 +94,15 @@ def test_gemm_further_qtypes(dev, qtype, dtype):
     """Fused gemm on the six further types (CUDA-core variant, every dtype, small and mid M, with bias) against the oracle."""
     q = qtype_of(qtype)
     for (m, n, k) in [(1, 16, 256), (1, 1000, 1024), (3, 33, 512), (4, 64, 2048), (17, 24, 768), (64, 40, 512)]:
-        assert kernels.select_variant(qtype, dtype, m, n, k) == "simt"
+        # AUTO: the CUDA-core kernel, or (16-bit dtypes, M <= 8, 16-byte rows) the fp32 path of the persistent GEMV
+        assert kernels.select_variant(qtype, dtype, m, n, k) in (("simt",) if dtype == "float32" or m > 8 else ("simt", "stream"))
         blocks = S.random_blocks(qtype, n, k, seed=3100 + m + n)
         x, xf = _activations(m, k, 3200 + m, dtype, dev)
         bias = torch.randn(n, device=dev).to(TDT[dtype])
         ref = oracle.gemm_quant(xf, blocks, qtype, n, k) + bias.float().cpu().numpy()
-        y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), qtype, bias)
-        _check(y, ref, dtype, (qtype, dtype, m, n, k))
+        for variant in ("auto", "simt"):
+            y = kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), qtype, bias, variant=variant)
+            _check(y, ref, dtype, (qtype, dtype, variant, m, n, k))
     with pytest.raises(RuntimeError):                   # no tensor-core variant for these types
         kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), qtype, variant="mma")
 

@@ -119,3 +119,52 @@ def test_stream_variant_refusals():
         kernels.gemm_rcr(torch.zeros(1, 512, device=dev, dtype=torch.float32), bq, "Q4_K", variant="stream")
     assert not kernels.variant_supports("stream", "Q4_K", "bfloat16", 9, 32, 512)
     assert kernels.variant_supports("stream", "Q4_K", "bfloat16", 8, 32, 512)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("qtype", ["Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4"])
+def test_stream_gemv_further_qtypes(dtype, qtype):
+    """The six further layouts on the persistent data path (values decoded 8 at a time, fp32 FMA): against the oracle and
+    against the simt kernel, which decodes the same values; bias and the gated epilogue; shapes whose rows are not 16-byte
+    multiples are refused (they stay with the simt kernel)."""
+    dev = torch.device("cuda:0")
+    bound = 4e-3 if dtype == "bfloat16" else 6e-4
+    for (m, n, k) in [(1, 16, 2048), (1, 1000, 2048), (2, 50, 4096), (3, 129, 2048), (5, 2400, 2048), (8, 64, 6144), (4, 7, 2048), (1, 4096, 4096)]:
+        blocks = S.random_blocks(qtype, n, k, seed=3500 + m + n)
+        bq = torch.from_numpy(blocks).to(dev)
+        x, xf = _x(m, k, 3600 + m, dtype, dev)
+        ref = oracle.gemm_quant(xf, blocks, qtype, n, k)
+        assert kernels.variant_supports("stream", qtype, dtype, m, n, k) and kernels.variant_supports("stream:4", qtype, dtype, m, n, k)
+        for variant in ("stream", "stream:4"):
+            y = kernels.gemm_rcr(x, bq, qtype, variant=variant)
+            assert kernels.device_status() == 0, (variant, m, n, k)
+            _, rel, norm = oracle.max_errors(ref, y.float().cpu().numpy())
+            assert norm <= bound and rel <= (2e-2 if dtype == "bfloat16" else 1e-3), (qtype, dtype, variant, m, n, k, rel, norm)
+        ys = kernels.gemm_rcr(x, bq, qtype, variant="simt")
+        assert float((ys.float() - y.float()).abs().max()) <= 2 * bound * float(np.abs(ref).max())
+        auto = kernels.select_variant(qtype, dtype, m, n, k)
+        assert auto == ("simt" if (m == 1 and qtype in ("Q5_K", "Q2_K", "Q3_K")) else "stream"), (qtype, m, auto)
+    # bias and the gated dual epilogue
+    m, n, k = 3, 72, 2048
+    b0, b1 = S.random_blocks(qtype, n, k, seed=3700), S.random_blocks(qtype, n, k, seed=3701)
+    x, xf = _x(m, k, 3702, dtype, dev)
+    bias = torch.linspace(-1, 1, n, device=dev).to(TDT[dtype])
+    yb = kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), qtype, bias, variant="stream")
+    refb = oracle.gemm_quant(xf, b0, qtype, n, k) + bias.float().cpu().numpy()[None, :]
+    assert oracle.max_errors(refb, yb.float().cpu().numpy())[2] <= bound
+    w = kernels.interleave_rows8(torch.from_numpy(b0).to(dev), torch.from_numpy(b1).to(dev))
+    yg = kernels.dual_gemm_rcr(x, w, qtype, "silu", variant="stream")
+    refg = oracle.dual_gemm_quant(xf, b0, b1, qtype, n, k, "silu")
+    assert oracle.max_errors(refg, yg.float().cpu().numpy())[2] <= (2e-2 if dtype == "bfloat16" else 2e-3)
+    assert kernels.device_status() == 0
+    # rows that are not multiples of 16 bytes, other configurations, M > 8
+    bad_k = {"Q2_K": 768, "Q3_K": 1024, "MXFP4": 768}.get(qtype)
+    if bad_k:
+        assert not kernels.variant_supports("stream", qtype, dtype, 1, 64, bad_k)
+        xk = torch.zeros(1, bad_k, device=dev, dtype=TDT[dtype])
+        with pytest.raises(RuntimeError):
+            kernels.gemm_rcr(xk, S.random_blocks_torch(qtype, 64, bad_k, 1, dev), qtype, variant="stream")
+        assert kernels.select_variant(qtype, dtype, 1, 64, bad_k) == "simt"
+    with pytest.raises(RuntimeError):
+        kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), qtype, variant="stream:2")
+    assert not kernels.variant_supports("stream", qtype, dtype, 9, n, k)
