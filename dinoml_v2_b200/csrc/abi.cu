@@ -65,22 +65,34 @@ int set_error_message(int rc, const std::string& message) {
 const char* last_error() { return g_last_error.c_str(); }
 
 int select_variant(int qtype, int dtype, int m, int n, int k) {
+  // Shape guard written from measurements on B200 (us per launch, graph replay, cold weights); a profiled execution plan
+  // overrides it per shape.
+  const int64_t weights = int64_t(n) * k;
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  const int tiles = (n + 15) / 16;
+  // M = 8 on a large weight: the tcgen05 kernel costs the same for any M <= 64 and overtakes the GEMVs there
+  //   ([8192 x 14336] Q4_K: 27.6 us against 33.9 persistent / 58.2 tile; [4096 x 4096]: 10.4 against 8.9 persistent).
+  if (m == 8 && weights >= (int64_t(32) << 20) && (qtype == QTYPE_Q4_K || qtype == QTYPE_Q6_K) && gemm_umma_supports(qtype, dtype, 9, n, k))
+    return DINOML_B200_GGUF_VARIANT_UMMA;
   // M <= 8 on Q4_K / Q6_K: the persistent bulk-copy GEMV, except where the tile kernel measured faster:
   //   Q4_K, M = 1, when the tile kernel's grid (three CTAs of 16 rows per SM) fills at least three quarters of its last wave
   //   ([11008 x 4096]: 9.4 us against 10.5 us; with emptier waves or less than one wave the persistent kernel wins);
-  //   Q6_K, M >= 3, on weights below 32 M elements ([4096 x 4096], M = 4: 6.5 us against 6.8 us), where the launch is too short
+  //   Q4_K, M >= 2, with fewer row tiles than half the SMs: the tile kernel cuts K across a cluster and so uses more SMs
+  //   ([256 x 14336], M = 8: 6.3 us against 13.4 us; [1024 x 4096], M = 8: a tie; [2048 x 4096], M = 8: 8.4 against 6.5);
+  //   Q6_K, M >= 3, on weights below 32 M elements ([4096 x 4096], M = 4: 6.3 us against 6.8 us), where the launch is too short
   //   for the ring to pay off (at M <= 2 and on larger weights it is 7 - 30 % faster: [4096 x 14336], M = 1: 15.0 us against 21.1 us).
-  // A profiled execution plan overrides this per shape.
   if (gemv_stream_supports(qtype, dtype, m, n, k)) {
     bool tile_kernel = false;
     if (qtype == QTYPE_Q4_K && m == 1) {
-      int sms = 148, dev = 0;
-      if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      const int tiles = (n + 15) / 16, slots = 3 * (sms > 0 ? sms : 148);
+      const int slots = 3 * sms;
       const int waves = (tiles + slots - 1) / slots;
       tile_kernel = tiles <= sms || (tiles >= slots && double(tiles) / (double(waves) * slots) >= 0.75);   // also: fewer tiles than SMs
+    } else if (qtype == QTYPE_Q4_K) {
+      tile_kernel = 2 * tiles <= sms;
     } else if (qtype == QTYPE_Q6_K && m >= 3) {
-      tile_kernel = int64_t(n) * k < (int64_t(32) << 20);
+      tile_kernel = weights < (int64_t(32) << 20);
     } else if (qtype == QTYPE_Q5_K || qtype == QTYPE_Q2_K || qtype == QTYPE_Q3_K) {
       // fp32 decode on the persistent data path: [4096 x 4096], M = 1 / 4: Q4_0 10.3 / 14.7 us against 15.7 / 19.1 us on the simt
       // kernel, MXFP4 13.9 / 18.6 against 16.9 / 22.8, NVFP4 14.4 / 19.5 against 20.6 / 24.9; the three K-quants only win from
@@ -89,9 +101,14 @@ int select_variant(int qtype, int dtype, int m, int n, int k) {
     }
     if (!tile_kernel) return DINOML_B200_GGUF_VARIANT_STREAM;
   }
-  // M = 9..16 is served by both tensor-core kernels: the tcgen05 one costs the same whatever M is and wins there once
-  // the weight is large enough to spread over the SMs; the mma.sync GEMV does twice the MMA work of M <= 8.
-  if (m >= 9 && m <= 16 && n >= 2048 && gemm_umma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_UMMA;
+  // M = 9..16 is served by both tensor-core kernels: the tcgen05 one costs the same whatever M is (about 8.5 us at least),
+  // the mma.sync GEMV does twice the MMA work of M <= 8.  Crossover by weight size: Q4_K from 4 M elements
+  //   ([1024 x 4096], M = 9: 8.6 us against 11.4; [512 x 4096]: 8.5 against 8.3); Q6_K, whose tile kernel is the quicker of the
+  //   two, from 32 M elements, or from 8 M at M >= 12 ([4096 x 4096], M = 9: 11.1 us against 9.8, M = 16: 10.8 against 11.3).
+  if (m >= 9 && m <= 16 && gemm_umma_supports(qtype, dtype, m, n, k)) {
+    const int64_t from = qtype == QTYPE_Q6_K ? (m >= 12 ? int64_t(8) << 20 : int64_t(32) << 20) : int64_t(4) << 20;
+    if (weights >= from || !gemv_mma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_UMMA;
+  }
   if (gemv_mma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_MMA;
   if (gemm_umma_supports(qtype, dtype, m, n, k)) return DINOML_B200_GGUF_VARIANT_UMMA;
   return DINOML_B200_GGUF_VARIANT_SIMT;

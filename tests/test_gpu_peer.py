@@ -77,7 +77,7 @@ def test_scatter_gemm_umma_writes_every_destination():
     dev = torch.device("cuda:0")
     lib = _native.lib()
     stream = torch.cuda.current_stream().cuda_stream
-    for (qtype, m, n, k) in (("Q4_K", 16, 2048, 1024), ("Q4_K", 64, 384, 4096), ("Q6_K", 200, 130, 2048)):
+    for (qtype, m, n, k) in (("Q4_K", 16, 2048, 2048), ("Q4_K", 64, 384, 4096), ("Q6_K", 200, 130, 2048)):
         w = torch.from_numpy(S.random_blocks(qtype, n, k, seed=31)).to(dev)
         x = torch.from_numpy(S.random_activations(m, k, 32, "float32")).to(dev).to(torch.bfloat16)
         want = kernels.gemm_rcr(x, w, qtype, variant="umma")
