@@ -249,20 +249,17 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
       if (SLICED)
         for (int peer = 1; peer < ks; ++peer) v += ld_cluster_f32(&sOut[idx], uint32_t(peer));
       int64_t at = int64_t(c) * n + row;
+      if (bias != nullptr) v += MT::to_float(bias[row]);
       if (peers.act != ACT_NONE) {
         // gated pair: rows r < 8 of the tile belong to the first matrix, r + 8 to the second; output has n / 2 columns
         if (r >= 8) continue;
         float u = sOut[idx + 8];
         if (SLICED)
           for (int peer = 1; peer < ks; ++peer) u += ld_cluster_f32(&sOut[idx + 8], uint32_t(peer));
-        if (bias != nullptr) {             // interleaved like the rows: bias0 of the gate row, bias1 of its up row
-          v += MT::to_float(bias[row]);
-          u += MT::to_float(bias[row + 8]);
-        }
+        // bias interleaved like the rows: bias0 of the gate row (added above), bias1 of its up row
+        if (bias != nullptr) u += MT::to_float(bias[row + 8]);
         v = gate_activation(v, peers.act) * u;
         at = int64_t(c) * (n >> 1) + (blockIdx.x * 8 + r);
-      } else if (bias != nullptr) {
-        v += MT::to_float(bias[row]);
       }
       const T out = MT::from_float(v);
       y[at] = out;
