@@ -980,6 +980,40 @@ int dino_session_run_staged(DinoSession* session, const void* host_in, void* dev
   return err == cudaSuccess ? 0 : cuda_fail("dino_session_run_staged synchronize", err);
 }
 
+int dino_session_run_staged_on(DinoSession* session, void* stream, int graph_replay, const void* host_in, void* device_in, size_t in_bytes,
+                               const DinoTensor* inputs, size_t num_inputs, DinoTensor* outputs, size_t num_outputs,
+                               const void* device_out, void* host_out, size_t out_bytes) {
+  if (session == nullptr) return fail("dino_session_run_staged_on received null session");
+  // this call's stream and replay setting; the session's own come back afterwards, whatever the outcome
+  const cudaStream_t saved_stream = session->stream;
+  const bool saved_external = session->external_stream, saved_replay = session->graph_replay;
+  if (stream != nullptr) { session->stream = static_cast<cudaStream_t>(stream); session->external_stream = true; }
+  session->graph_replay = graph_replay != 0;
+  const int rc = dino_session_run_staged(session, host_in, device_in, in_bytes, inputs, num_inputs, outputs, num_outputs, device_out, host_out,
+                                         out_bytes);
+  session->stream = saved_stream;
+  session->external_stream = saved_external;
+  session->graph_replay = saved_replay;
+  return rc;
+}
+
+// float32 <-> bfloat16 bit patterns on the host, for callers whose arrays are float32 (numpy has no bfloat16): round to
+// nearest even exactly as the reference's Python does (src/dinoml/ir.py:68-73: bits + 0x7FFF + lsb, high half), NaN kept
+// a NaN; widening is the 16 bits followed by 16 zeros.
+void dino_convert_f32_to_bf16(const float* src, uint16_t* dst, size_t count) {
+  for (size_t i = 0; i < count; ++i) {
+    uint32_t bits;
+    std::memcpy(&bits, src + i, sizeof(bits));
+    dst[i] = uint16_t((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
+  }
+}
+void dino_convert_bf16_to_f32(const uint16_t* src, float* dst, size_t count) {
+  for (size_t i = 0; i < count; ++i) {
+    const uint32_t bits = uint32_t(src[i]) << 16;
+    std::memcpy(dst + i, &bits, sizeof(bits));
+  }
+}
+
 int dino_session_benchmark(DinoSession* session, const DinoTensor* inputs, size_t num_inputs, DinoTensor* outputs,
                            size_t num_outputs, size_t warmup_runs, size_t measured_runs, double* out_elapsed_ms,
                            size_t out_elapsed_count) {

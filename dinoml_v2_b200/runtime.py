@@ -47,10 +47,13 @@ def _configure(lib: ctypes.CDLL) -> None:
         "dino_module_set_offloaded_encoded_constant": [vp, ctypes.c_char_p, vp, sz, ci],
         "dino_module_get_residency_stats": [vp] + [ctypes.POINTER(sz)] * 5,
         "dino_session_run_staged": [vp, vp, vp, sz, T, sz, T, sz, vp, vp, sz],
+        "dino_session_run_staged_on": [vp, vp, ci, vp, vp, sz, T, sz, T, sz, vp, vp, sz],
         "dino_session_set_graph_replay": [vp, ci], "dino_session_get_graph_stats": [vp, ctypes.POINTER(sz), ctypes.POINTER(sz)],
     }.items():
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = args, ci
+    for name in ("dino_convert_f32_to_bf16", "dino_convert_bf16_to_f32"):
+        getattr(lib, name).argtypes, getattr(lib, name).restype = [vp, vp, sz], None
     lib.dino_module_get_metadata_json.argtypes = [vp]
     lib.dino_module_get_metadata_json.restype = ctypes.c_char_p
 
@@ -204,6 +207,7 @@ class Session:
         self._user_stream = 0
         self._graph_replay = False
         self.numpy_graph_replay = True        # run_numpy keeps its arenas, so its launch sequences are replayed as CUDA graphs
+        self.numpy_zero_copy_bytes = 65536    # run_numpy: results up to this size are stored by the kernels into pinned host memory
 
     def close(self) -> None:
         if self._handle:
@@ -278,36 +282,30 @@ class Session:
         plan = self._numpy_plans.get(key)
         if plan is None:
             plan = self._numpy_plans[key] = self._make_numpy_plan(arrays)
+        lib = self._lib
         for spec in meta["inputs"]:
             arr, view = arrays[spec["name"]], plan["in_views"][spec["name"]]
             if spec["dtype"] == "bfloat16":
-                view[...] = arr if arr.dtype == np.uint16 else _f32_to_bf16_bits(arr)
+                if arr.dtype == np.float32 and arr.flags.c_contiguous:      # rounded natively, straight into the pinned arena
+                    lib.dino_convert_f32_to_bf16(arr.ctypes.data, plan["in_ptrs"][spec["name"]], arr.size)
+                else:
+                    view[...] = arr if arr.dtype == np.uint16 else _f32_to_bf16_bits(arr)
             else:
                 view[...] = arr                                   # numpy converts to the view's dtype
-        # one native call: H2D of the input arena, the launches (a replayed graph in steady state), D2H of the output arena,
-        # one wait - all on the plan's stream
-        self._set_stream_raw(plan["stream"].cuda_stream)
-        if self.numpy_graph_replay and not self._graph_replay:
-            self.module._check(self._lib.dino_session_set_graph_replay(self._handle, 1))
-        try:
-            self.module._check(self._lib.dino_session_run_staged(
-                self._handle, plan["pin_in_ptr"], plan["dev_in_ptr"], plan["in_bytes"], plan["ins"], len(plan["ins"]), plan["outs"],
-                len(plan["outs"]), plan["dev_out_ptr"], plan["pin_out_ptr"], plan["out_bytes"]))
-        finally:
-            self._set_stream_raw(self._user_stream)
-            if self.numpy_graph_replay and not self._graph_replay:
-                self._lib.dino_session_set_graph_replay(self._handle, 0)
-        if plan["any_bf16"]:
-            # bfloat16 -> float32 for the whole output arena at once: the 16 bits become the high half of each float
-            wide = plan["pin_out"].numpy().view(np.uint16).astype(np.uint32)
-            np.left_shift(wide, 16, out=wide)
-            wide = wide.view(np.float32)
+        # one native call: H2D of the input arena, the launches (a replayed graph in steady state), D2H of the output arena
+        # (none when the outputs are small: the kernels then store straight into the pinned arena), one wait - all on the
+        # plan's stream, with graph replay on for this call unless the user switched it on for the session anyway
+        self.module._check(lib.dino_session_run_staged_on(
+            self._handle, plan["stream_ptr"], int(self.numpy_graph_replay or self._graph_replay), plan["pin_in_ptr"], plan["dev_in_ptr"],
+            plan["in_bytes"], plan["ins"], len(plan["ins"]), plan["outs"], len(plan["outs"]), plan["dev_out_ptr"], plan["pin_out_ptr"],
+            plan["copy_out_bytes"]))
         out = {}
         for o in meta["outputs"]:
             view = plan["out_views"][o["name"]]
             if o["dtype"] == "bfloat16":
-                off = plan["out_off"][o["name"]] // 2
-                out[o["name"]] = wide[off:off + view.size].reshape(view.shape)
+                res = np.empty(view.shape, dtype=np.float32)      # the 16 bits become the high half of each float
+                lib.dino_convert_bf16_to_f32(plan["out_ptrs"][o["name"]], res.ctypes.data, res.size)
+                out[o["name"]] = res
             else:
                 out[o["name"]] = view.copy()
         return out
@@ -346,8 +344,14 @@ class Session:
                     any_bf16=any(o["dtype"] == "bfloat16" for o in meta["outputs"]))
         plan["ins"] = (_DinoTensor * len(in_entries))(*[_tensor_struct(plan["dev_in"].data_ptr() + in_off[n], s, d, plan["keep"])
                                                         for n, s, d in in_entries])
-        plan["outs"] = (_DinoTensor * len(out_entries))(*[_tensor_struct(plan["dev_out"].data_ptr() + out_off[n], s, d, plan["keep"])
-                                                          for n, s, d in out_entries])
+        # Decode-sized results (up to 64 KB in all) are written by the kernels straight into the pinned host arena (mapped into
+        # the device's address space at the same address): no device-to-host copy node, one hop less before the host may read.
+        zero_copy = out_bytes <= self.numpy_zero_copy_bytes
+        out_base = plan["pin_out"].data_ptr() if zero_copy else plan["dev_out"].data_ptr()
+        plan["outs"] = (_DinoTensor * len(out_entries))(*[_tensor_struct(out_base + out_off[n], s, d, plan["keep"]) for n, s, d in out_entries])
+        plan.update(copy_out_bytes=0 if zero_copy else out_bytes, stream_ptr=plan["stream"].cuda_stream,
+                    in_ptrs={n: plan["pin_in"].data_ptr() + in_off[n] for n, _, _ in in_entries},
+                    out_ptrs={n: plan["pin_out"].data_ptr() + out_off[n] for n, _, _ in out_entries})
         return plan
 
     # -- benchmark

@@ -113,6 +113,17 @@ DINOML_B200_API int dino_session_run(struct DinoSession* session, const struct D
 DINOML_B200_API int dino_session_run_staged(struct DinoSession* session, const void* host_in, void* device_in, size_t in_bytes,
                                             const struct DinoTensor* inputs, size_t num_inputs, struct DinoTensor* outputs,
                                             size_t num_outputs, const void* device_out, void* host_out, size_t out_bytes);
+/* The same with this call's stream (null = the session's) and graph-replay setting as arguments, so that a host needs one
+ * call per run; the session's own stream and setting are untouched.  `outputs` may point into mapped pinned host memory
+ * (then pass out_bytes = 0): the kernels' epilogues store over the bus and no device-to-host copy is issued - worth it for
+ * decode-sized results. */
+DINOML_B200_API int dino_session_run_staged_on(struct DinoSession* session, void* stream, int graph_replay, const void* host_in,
+                                               void* device_in, size_t in_bytes, const struct DinoTensor* inputs, size_t num_inputs,
+                                               struct DinoTensor* outputs, size_t num_outputs, const void* device_out, void* host_out,
+                                               size_t out_bytes);
+/* Host-side float32 <-> bfloat16 conversion (round to nearest even as src/dinoml/ir.py:68-73; numpy has no bfloat16). */
+DINOML_B200_API void dino_convert_f32_to_bf16(const float* src, uint16_t* dst, size_t count);
+DINOML_B200_API void dino_convert_bf16_to_f32(const uint16_t* src, float* dst, size_t count);
 /* :1011-1170 - warm-ups, CUDA-graph capture of one run on the owned stream, then per-iteration
  * event / graph launch / event; elapsed milliseconds per measured run are written to out_elapsed_ms. */
 DINOML_B200_API int dino_session_benchmark(struct DinoSession* session, const struct DinoTensor* inputs, size_t num_inputs,
