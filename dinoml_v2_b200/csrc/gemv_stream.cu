@@ -52,16 +52,18 @@ constexpr int kKC = 8;                          // super-blocks per row per stag
 template <int QT> struct Geom;
 template <> struct Geom<QTYPE_Q4_K> { static constexpr int kSbBytes = 144, kPitch = kKC * 144 + 32; };
 template <> struct Geom<QTYPE_Q6_K> { static constexpr int kSbBytes = 210, kPitch = kKC * 210; };
+// Q5_K = the Q4_K block with 32 more bytes (one high bit per weight) between the scales and the nibbles: same 8-byte reads,
+// 8 x 176 + 32 = 1440 B is 32 (mod 128) like the Q4_K pitch.
+template <> struct Geom<QTYPE_Q5_K> { static constexpr int kSbBytes = 176, kPitch = kKC * 176 + 32; };
 // The further types: packed bytes per 256 weights of a row; the pitch is the stage piece rounded up to 128 B, plus 16, so
 // that the byte reads of 16 rows spread over the banks and every row starts 16-byte aligned (bulk-copy destination).
 template <int BYTES> struct GenericGeom { static constexpr int kSbBytes = BYTES, kPitch = (kKC * BYTES + 127) / 128 * 128 + 16; };
 template <> struct Geom<QTYPE_Q4_0> : GenericGeom<8 * 18> {};
-template <> struct Geom<QTYPE_Q5_K> : GenericGeom<176> {};
 template <> struct Geom<QTYPE_Q2_K> : GenericGeom<84> {};
 template <> struct Geom<QTYPE_Q3_K> : GenericGeom<110> {};
 template <> struct Geom<QTYPE_MXFP4> : GenericGeom<8 * 17> {};
 template <> struct Geom<QTYPE_NVFP4> : GenericGeom<4 * 36> {};
-template <int QT> constexpr bool is_generic() { return QT != QTYPE_Q4_K && QT != QTYPE_Q6_K; }
+template <int QT> constexpr bool is_generic() { return QT != QTYPE_Q4_K && QT != QTYPE_Q6_K && QT != QTYPE_Q5_K; }
 
 // 8 consecutive activations as floats.
 template <typename T> __device__ __forceinline__ void x8_to_float(const uint4 v, float (&x)[8]);
@@ -101,7 +103,9 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   constexpr int NCW = NG * kGroupWarps;
   constexpr int MC = MXC == 1 ? 1 : 2;             // accumulator columns a lane keeps
   constexpr int kSbBytes = Geom<QT>::kSbBytes, kPitch = Geom<QT>::kPitch, kStageBytes = kRows * kPitch;
-  constexpr bool kMinTerm = QT == QTYPE_Q4_K;      // Q4_K folds its mins and the operand offset against activation sums; Q6_K has neither
+  constexpr bool kMinTerm = QT == QTYPE_Q4_K || QT == QTYPE_Q5_K;      // Q4_K / Q5_K fold their mins and the operand offset against activation sums; Q6_K has neither
+  constexpr bool kQ5 = QT == QTYPE_Q5_K;           // Q4_K arithmetic plus the fifth bit of every quant
+  constexpr int kQsOff = kQ5 ? 48 : 16;            // where the nibbles start inside a block
   constexpr bool kGeneric = is_generic<QT>();      // decoded value by value (decode8), fp32 FMA, no tensor cores
   static_assert(D % NG == 0 && D >= 2 * NG, "every group needs its own ring slots, at least two");
   static_assert(MXC == 1 || MXC == 2 || MXC == 4 || MXC == 8, "MXC");
@@ -428,17 +432,30 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
       const float4 dsb1 = *reinterpret_cast<const float4*>(&sS[cw][g + 8][4]);
       const float ds_a[8] = {dsa0.x, dsa0.y, dsa0.z, dsa0.w, dsa1.x, dsa1.y, dsa1.z, dsa1.w};
       const float ds_b[8] = {dsb0.x, dsb0.y, dsb0.z, dsb0.w, dsb1.x, dsb1.y, dsb1.z, dsb1.w};
-      const uint8_t* q0p = st + g * kPitch + 16 + 8 * t;
+      const uint8_t* q0p = st + g * kPitch + kQsOff + 8 * t;
       const uint8_t* q1p = q0p + 8 * kPitch;
       const T* xs = xrow + sb * 256;
+      // Q5_K: bit 2G+h of qh byte l is the fifth bit of weight l of sub-block 2G+h; this lane's eight l are bytes 8t .. 8t+7
+      uint2 qh0 = make_uint2(0u, 0u), qh1 = make_uint2(0u, 0u);
+      if constexpr (kQ5) {
+        qh0 = *reinterpret_cast<const uint2*>(st + g * kPitch + 16 + 8 * t);
+        qh1 = *reinterpret_cast<const uint2*>(st + (g + 8) * kPitch + 16 + 8 * t);
+      }
 #pragma unroll
       for (int G = 0; G < 4; ++G) {
         const uint2 q0 = *reinterpret_cast<const uint2*>(q0p + 32 * G);
         const uint2 q1 = *reinterpret_cast<const uint2*>(q1p + 32 * G);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint32_t n0x = (h ? q0.x >> 4 : q0.x) & 0x0f0f0f0fu, n0y = (h ? q0.y >> 4 : q0.y) & 0x0f0f0f0fu;
-          const uint32_t n1x = (h ? q1.x >> 4 : q1.x) & 0x0f0f0f0fu, n1y = (h ? q1.y >> 4 : q1.y) & 0x0f0f0f0fu;
+          uint32_t n0x = (h ? q0.x >> 4 : q0.x) & 0x0f0f0f0fu, n0y = (h ? q0.y >> 4 : q0.y) & 0x0f0f0f0fu;
+          uint32_t n1x = (h ? q1.x >> 4 : q1.x) & 0x0f0f0f0fu, n1y = (h ? q1.y >> 4 : q1.y) & 0x0f0f0f0fu;
+          if constexpr (kQ5) {               // q = nibble + 16 * bit: still an exact 128 + q operand (q <= 31)
+            constexpr uint32_t kBit = 0x01010101u;
+            n0x |= ((qh0.x >> (2 * G + h)) & kBit) * 16u;
+            n0y |= ((qh0.y >> (2 * G + h)) & kBit) * 16u;
+            n1x |= ((qh1.x >> (2 * G + h)) & kBit) * 16u;
+            n1y |= ((qh1.y >> (2 * G + h)) & kBit) * 16u;
+          }
           const uint32_t a_lo[4] = {MT::fix(__byte_perm(n0x, MT::kMagicBytes, 0x4140)), MT::fix(__byte_perm(n1x, MT::kMagicBytes, 0x4140)),
                                     MT::fix(__byte_perm(n0x, MT::kMagicBytes, 0x4342)), MT::fix(__byte_perm(n1x, MT::kMagicBytes, 0x4342))};
           const uint32_t a_hi[4] = {MT::fix(__byte_perm(n0y, MT::kMagicBytes, 0x4140)), MT::fix(__byte_perm(n1y, MT::kMagicBytes, 0x4140)),
@@ -515,7 +532,7 @@ static int stream_scratch(cudaStream_t stream, Scratch* out) {
 template <int QT, typename T, int MXC, int NG, int D, bool PROBE = false>
 static int launch_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int ctas_per_sm, const PeerOut& peers,
                           cudaStream_t s, int mode = 3) {     // mode: bit 0 = walk downwards, bit 1 = split at unit granularity
-  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + (QT == QTYPE_Q4_K ? size_t(k / 32) * MXC * sizeof(float) : 0);
+  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + ((QT == QTYPE_Q4_K || QT == QTYPE_Q5_K) ? size_t(k / 32) * MXC * sizeof(float) : 0);
   if (smem > 216 * 1024) return RC_RANGE;            // + up to 9 KB of static shared memory, under the 227 KB per CTA
   int* status = stream_status_ptr();
   if (status == nullptr) return RC_LAUNCH;
@@ -547,7 +564,7 @@ constexpr int kProbeBit = 0x80;
 template <int QT, typename T, int MXC>
 static int launch_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
                     cudaStream_t s) {
-  constexpr bool Q6 = QT == QTYPE_Q6_K;
+  constexpr bool Q6 = QT == QTYPE_Q6_K || QT == QTYPE_Q5_K;      // the larger stages (26.3 / 23.0 KB): shallower rings
   if constexpr (is_generic<QT>()) {
     // the further types have one configuration: 8 consumer warps, two CTAs per SM, 3 or 4 ring slots by stage size
     if (config != 0 && config != 4) return RC_RANGE;
@@ -594,13 +611,12 @@ static int launch_q(const void* a, const void* b, const void* bias, void* c, int
 bool gemv_stream_supports(int qtype, int dtype, int m, int n, int k) {
   (void)n;
   if (!(dtype == DINO_BF16 || dtype == DINO_F16) || m < 1 || m > 8) return false;
-  if (qtype == QTYPE_Q4_K) return k % 256 == 0;
+  if (qtype == QTYPE_Q4_K || qtype == QTYPE_Q5_K) return k % 256 == 0;      // 144 / 176-byte blocks: rows are always 16-byte multiples
   if (qtype == QTYPE_Q6_K) return k % 2048 == 0;      // 210-byte blocks: row pieces start on 16-byte boundaries only then
   // the further types: whole 256-weight groups and weight rows that are multiples of 16 bytes (bulk-copy sources)
   int sb_bytes = 0;
   switch (qtype) {
     case QTYPE_Q4_0: sb_bytes = 8 * 18; break;
-    case QTYPE_Q5_K: sb_bytes = 176; break;
     case QTYPE_Q2_K: sb_bytes = 84; break;
     case QTYPE_Q3_K: sb_bytes = 110; break;
     case QTYPE_MXFP4: sb_bytes = 8 * 17; break;

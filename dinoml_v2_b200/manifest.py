@@ -27,13 +27,13 @@ SUPPORTED_OPS = ("gemm_rcr", "gemm_rcr_bias") + DUAL_OPS
 VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3, "stream": 4}
 # Tuning configurations of the persistent GEMV (csrc/gemv_stream.cu): each is a candidate of its own, as the tile / stage /
 # warp entries of the reference's CUTLASS catalogue are (src/dinoml/kernels/providers/cutlass/gemm.py:19-127).
-STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": {"Q4_K": 5, "Q6_K": 4}, "ctas_per_sm": 1},
-                  2: {"consumer_warps": 16, "ring_slots": {"Q4_K": 6, "Q6_K": 4}, "ctas_per_sm": 1},
-                  3: {"consumer_warps": 16, "ring_slots": {"Q4_K": 8, "Q6_K": 6}, "ctas_per_sm": 1},
-                  4: {"consumer_warps": 8, "ring_slots": {"Q4_K": 4, "Q6_K": 3}, "ctas_per_sm": 2}}
-STREAM_QTYPES = ("Q4_K", "Q6_K")
-# the six further layouts run on the same persistent data path with fp32 arithmetic, in ONE configuration (4)
-STREAM_FP32_QTYPES = ("Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4")
+STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": {"Q4_K": 5, "Q6_K": 4, "Q5_K": 4}, "ctas_per_sm": 1},
+                  2: {"consumer_warps": 16, "ring_slots": {"Q4_K": 6, "Q6_K": 4, "Q5_K": 4}, "ctas_per_sm": 1},
+                  3: {"consumer_warps": 16, "ring_slots": {"Q4_K": 8, "Q6_K": 6, "Q5_K": 6}, "ctas_per_sm": 1},
+                  4: {"consumer_warps": 8, "ring_slots": {"Q4_K": 4, "Q6_K": 3, "Q5_K": 3}, "ctas_per_sm": 2}}
+STREAM_QTYPES = ("Q4_K", "Q6_K", "Q5_K")
+# five further layouts run on the same persistent data path with fp32 arithmetic, in ONE configuration (4)
+STREAM_FP32_QTYPES = ("Q4_0", "Q2_K", "Q3_K", "MXFP4", "NVFP4")
 
 _B200_TUNING = {
     "simt": {"kind": "gemv_simt", "rows_per_warp": 1, "activation_rows_per_pass": 4, "staging": "ldg", "tensor_cores": "none"},
@@ -105,7 +105,7 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
     if config:
         tuning.update(STREAM_CONFIGS[int(config)], config=int(config))
         if q.name in STREAM_FP32_QTYPES:
-            tuning.update(ring_slots=3 if q.name == "Q5_K" else 4, tensor_cores="none", arithmetic="fp32 fma on values decoded 8 at a time")
+            tuning.update(ring_slots=4, tensor_cores="none", arithmetic="fp32 fma on values decoded 8 at a time")
         else:
             tuning["ring_slots"] = tuning["ring_slots"][q.name]
     cand = {
