@@ -233,6 +233,7 @@ __device__ __forceinline__ void q6k_fetch(const uint8_t* rowbase, int hb, int lh
 //   kSuper: packed bytes per 256 weights of a row; kBoxes: TMA boxes per super-block; kSlots: super-blocks in the ring.
 template <int QT> struct RawGeom;
 template <> struct RawGeom<QTYPE_Q4_K> { static constexpr int kPitch = 144, kSuper = 144, kBoxes = 1, kSlots = 3; };
+template <> struct RawGeom<QTYPE_Q5_K> { static constexpr int kPitch = 176, kSuper = 176, kBoxes = 1, kSlots = 3; };   // Q4_K + 32 bytes of fifth bits
 template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240, kSuper = 210, kBoxes = 1, kSlots = 3; };
 template <> struct RawGeom<QTYPE_Q8_0> { static constexpr int kPitch = 144, kSuper = 272, kBoxes = 2, kSlots = 2; };
 
@@ -545,7 +546,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         }
         const uint8_t* rowbase = raw + rslot * kRawBytes + row * kPitch;
         // ---- copy this thread's packed words to registers
-        uint32_t qw[QT == QTYPE_Q8_0 ? 16 : 12];
+        uint32_t qw[(QT == QTYPE_Q8_0 || QT == QTYPE_Q5_K) ? 16 : 12];
         float dscale = 0.f, dmin = 0.f;
         float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3; Q8_0: d of this thread's four blocks
         if constexpr (QT == QTYPE_Q8_0) {
@@ -562,7 +563,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             q8_fetch<6>(win, lhalf, qw + 8, sub_scale[2]);
             q8_fetch<7>(win, lhalf, qw + 12, sub_scale[3]);
           }
-        } else if constexpr (QT == QTYPE_Q4_K) {
+        } else if constexpr (QT == QTYPE_Q4_K || QT == QTYPE_Q5_K) {
+          constexpr int kQsOff = QT == QTYPE_Q5_K ? 48 : 16;      // Q5_K keeps 32 bytes of fifth bits between the scales and the nibbles
           const uint4 hdr = *reinterpret_cast<const uint4*>(rowbase);
           dscale = half_bits_to_float(uint16_t(hdr.x & 0xffffu));
           dmin = half_bits_to_float(uint16_t(hdr.x >> 16));
@@ -573,8 +575,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
           qw[9] = mnw;
 #pragma unroll
           for (int ls = 0; ls < 2; ++ls) {
-            const uint4 q = *reinterpret_cast<const uint4*>(rowbase + 16 + 64 * grp + 32 * ls + 16 * lhalf);
+            const uint4 q = *reinterpret_cast<const uint4*>(rowbase + kQsOff + 64 * grp + 32 * ls + 16 * lhalf);
             qw[4 * ls] = q.x; qw[4 * ls + 1] = q.y; qw[4 * ls + 2] = q.z; qw[4 * ls + 3] = q.w;
+          }
+          if constexpr (QT == QTYPE_Q5_K) {     // bit 2*(2*grp+ls) + {0, 1} of qh byte l: fifth bit of weight l in the low / high sub-block
+            const uint4 qh = *reinterpret_cast<const uint4*>(rowbase + 16 + 16 * lhalf);
+            qw[12] = qh.x; qw[13] = qh.y; qw[14] = qh.z; qw[15] = qh.w;
           }
           sub_scale[0] = sub_scale[1] = sub_scale[2] = sub_scale[3] = 0.f;
         } else {
@@ -614,7 +620,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
 #pragma unroll
               for (int i = 0; i < 4; ++i) q8_to_pairs<T>(qw[8 * ls + 4 * h + i], d256, c, o[2 * i], o[2 * i + 1]);
             }
-          } else if constexpr (QT == QTYPE_Q4_K) {
+          } else if constexpr (QT == QTYPE_Q4_K || QT == QTYPE_Q5_K) {
             // stage = 64-weight group: low nibbles -> its first sub-block (k' 0..31), high nibbles -> its second (k' 32..63)
             const int sh = 16 * ls;
             const float sc0 = float((qw[8] >> sh) & 0xff), sc1 = float((qw[8] >> (sh + 8)) & 0xff);
@@ -624,8 +630,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             const V s_hi = P::splat(dscale * sc1), a_hi = P::splat(-(dmin * mn1));
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              bytes_to_pairs<T>(qw[4 * ls + i] & 0x0f0f0f0fu, off, s_lo, a_lo, o0[2 * i], o0[2 * i + 1]);
-              bytes_to_pairs<T>((qw[4 * ls + i] >> 4) & 0x0f0f0f0fu, off, s_hi, a_hi, o1[2 * i], o1[2 * i + 1]);
+              uint32_t lo = qw[4 * ls + i] & 0x0f0f0f0fu, hi = (qw[4 * ls + i] >> 4) & 0x0f0f0f0fu;
+              if constexpr (QT == QTYPE_Q5_K) {
+                const int j = 2 * (2 * grp + ls);
+                lo |= ((qw[12 + i] >> j) & 0x01010101u) * 16u;
+                hi |= ((qw[12 + i] >> (j + 1)) & 0x01010101u) * 16u;
+              }
+              bytes_to_pairs<T>(lo, off, s_lo, a_lo, o0[2 * i], o0[2 * i + 1]);
+              bytes_to_pairs<T>(hi, off, s_hi, a_hi, o1[2 * i], o1[2 * i + 1]);
             }
           } else {
             // stage = (half block grp, quad pair ls): quads 2*ls (k' 0..31) and 2*ls+1 (k' 32..63)
@@ -1019,7 +1031,7 @@ static int launch_bm(const void* a, const void* b, const void* bias, void* c, in
 
 // Packed bytes per 256 weights of a row, 0 for a qtype this kernel does not unpack.
 static int super_block_bytes(int qtype) {
-  return qtype == QTYPE_Q4_K ? 144 : qtype == QTYPE_Q6_K ? 210 : qtype == QTYPE_Q8_0 ? 272 : 0;
+  return qtype == QTYPE_Q4_K ? 144 : qtype == QTYPE_Q5_K ? 176 : qtype == QTYPE_Q6_K ? 210 : qtype == QTYPE_Q8_0 ? 272 : 0;
 }
 
 bool gemm_umma_supports(int qtype, int dtype, int m, int n, int k) {
@@ -1048,10 +1060,12 @@ static int gemm_rcr_umma_impl(const void* a, const void* b, const void* bias, vo
   if (dtype == DINO_BF16) {
     if (qtype == QTYPE_Q4_K) return umma::launch_bm<QTYPE_Q4_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
     if (qtype == QTYPE_Q6_K) return umma::launch_bm<QTYPE_Q6_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
+    if (qtype == QTYPE_Q5_K) return umma::launch_bm<QTYPE_Q5_K, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
     return umma::launch_bm<QTYPE_Q8_0, __nv_bfloat16>(a, b, bias, c, m, n, k, use_static, peers, s);
   }
   if (qtype == QTYPE_Q4_K) return umma::launch_bm<QTYPE_Q4_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
   if (qtype == QTYPE_Q6_K) return umma::launch_bm<QTYPE_Q6_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
+  if (qtype == QTYPE_Q5_K) return umma::launch_bm<QTYPE_Q5_K, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
   return umma::launch_bm<QTYPE_Q8_0, __half>(a, b, bias, c, m, n, k, use_static, peers, s);
 }
 

@@ -62,6 +62,8 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
         if qtype in ("Q4_K", "Q6_K", "Q8_0"):
             variants.append("mma")
             variants.append("umma")
+        elif qtype == "Q5_K":                       # tensor-core paths: the persistent GEMV (below) and the tcgen05 GEMM
+            variants.append("umma")
         if qtype in STREAM_QTYPES:
             variants += [f"stream:{c}" for c in sorted(STREAM_CONFIGS)]
         elif qtype in STREAM_FP32_QTYPES:
