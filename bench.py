@@ -763,6 +763,16 @@ def run_multi(args):
                 f.gate_up_peer(x)
                 f.down_proj_peer(h_slice, od)
 
+        def step_pull():                                    # peer memory, pulled: GEMMs store locally, one kernel per gather / two per reduce
+            for f in ffns:
+                f.gate_up_pull(x)
+                f.down_proj_pull(h_slice, od)
+
+        def comm_pull():
+            for f in ffns:
+                f.xchg_gate_up.pull_gather()
+                f.xchg_down.pull_all_reduce(od)
+
         def comm_nccl():                                    # the collectives of step_nccl alone
             for _ in ffns:
                 dist.all_gather_into_tensor(gg.view(-1, n_shard), og)
@@ -789,7 +799,7 @@ def run_multi(args):
                 if rank == 0:
                     print(f"peer buffers unavailable ({type(exc).__name__}: {str(exc)[:200]}); using NCCL", file=sys.stderr)
         mode = "peer" if (want_peer and _all_ranks_agree(peer_ok, dev)) else "nccl"
-        nccl_ms = peer_ms = swiglu_ms = None
+        nccl_ms = peer_ms = pull_ms = swiglu_ms = None
         if mode == "peer":
             # correctness before timing: the peer all-reduce against NCCL's, several back-to-back calls on one exchange
             step_nccl()
@@ -810,16 +820,22 @@ def run_multi(args):
                 f0.swiglu_mlp_peer(x, got)
                 torch.cuda.synchronize()
                 assert float((want.float() - got.float()).abs().max()) <= 2e-2 * float(want.float().abs().max()), "fused gated MLP differs from NCCL"
+            # the pull path against the same reference, two consecutive calls
+            for _ in range(2):
+                step_pull()
+            torch.cuda.synchronize()
+            assert kernels.device_status() == 0, "a bounded device-side wait gave up on the pull path"
+            assert float((ref.float() - od.float()).abs().max()) <= 2e-2 * float(ref.float().abs().max()), "pull all-reduce differs from NCCL"
             nccl_ms = _max_over_ranks(time_steps(step_nccl, half, W, stream, barrier=dist.barrier), dev)
             peer_ms = _max_over_ranks(time_steps(step_peer, half, W, stream, barrier=dist.barrier), dev)
-            if nccl_ms < peer_ms:                           # large batches on few GPUs: NCCL's bandwidth-optimal rings win
-                mode = "nccl"
+            pull_ms = _max_over_ranks(time_steps(step_pull, half, W, stream, barrier=dist.barrier), dev)
+            mode = min((peer_ms, "peer"), (pull_ms, "pull"), (nccl_ms, "nccl"))[1]      # every rank sees the same three maxima
 
             def step_swiglu():                              # extra: the gated MLP with no all-gather at all
                 for f in ffns:
                     f.swiglu_mlp_peer(x, od)
             swiglu_ms = time_steps(step_swiglu, half, W, stream, barrier=dist.barrier)
-        step, comm = (step_peer, comm_peer) if mode == "peer" else (step_nccl, comm_nccl)
+        step, comm = {"peer": (step_peer, comm_peer), "pull": (step_pull, comm_pull), "nccl": (step_nccl, comm_nccl)}[mode]
         clock_ctx = ClockSampler(local, isolated=True) if (m == 1 and rank == 0) else None
         if clock_ctx:
             clock_ctx.__enter__()
@@ -832,11 +848,13 @@ def run_multi(args):
         results[m] = {"ms_per_step": ms_step, "ms_per_ffn": ms_step / r, "weight_gbs": r * total_bytes / ms_step / 1e6,
                       "tflops": r * 6.0 * m * hidden * ffn / ms_step / 1e9, "collectives": mode,
                       "comm_us_per_ffn": comm_ms * 1e3 / r,
-                      "comm_is": "peer_exchange_kernel x 2 alone" if mode == "peer" else "ncclAllGather x 2 + ncclAllReduce alone",
+                      "comm_is": {"peer": "peer_exchange_kernel x 2 alone", "pull": "peer_pull_kernel x 3 alone (gather, reduce slice, gather)",
+                                  "nccl": "ncclAllGather x 2 + ncclAllReduce alone"}[mode],
                       "bound_by": None}
         if nccl_ms is not None:
             results[m]["nccl_ms_per_ffn"] = nccl_ms / half / r
             results[m]["peer_ms_per_ffn"] = peer_ms / half / r
+            results[m]["pull_ms_per_ffn"] = pull_ms / half / r
         if swiglu_ms is not None:
             results[m]["fused_swiglu_mlp_ms_per_ffn"] = _max_over_ranks(swiglu_ms, dev) / half / r
         if m == 1:
@@ -886,16 +904,18 @@ def run_multi(args):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD_MULTI,
                        "value_is": "total GGUF-encoded weight bytes of the three matrices / max-over-ranks step time, M=1",
-                       "collectives": ("GEMV epilogue stores into peer GPUs' buffers + one barrier / barrier-and-sum kernel each"
-                                       if r1["collectives"] == "peer" else "NCCL all-gather x 2 + all-reduce"),
+                       "collectives": {"peer": "GEMV epilogue stores into peer GPUs' buffers + one barrier / barrier-and-sum kernel each",
+                                       "pull": "GEMV stores locally + one pull kernel per gather, two per all-reduce (16-byte peer loads)",
+                                       "nccl": "NCCL all-gather x 2 + all-reduce"}[r1["collectives"]],
                        "parallelism": f"tp{world}", "ffns_per_step": r,
                        "l2_policy": f"each step walks {r} distinct shard sets ({r * shard_bytes / 1e6:.0f} MB per GPU > 2 x L2)",
                        "timing": "eager launches on one stream, CUDA events, max over ranks"},
-            "roofline": {"kernel": ("gemv_q4k kernel (scatter epilogue) + peer_exchange_kernel" if r1["collectives"] == "peer" else "gemv_q4k kernel + NCCL"),
+            "roofline": {"kernel": {"peer": "gemv_q4k kernel (scatter epilogue) + peer_exchange_kernel", "pull": "gemv_q4k kernel + peer_pull_kernel",
+                                    "nccl": "gemv_q4k kernel + NCCL"}[r1["collectives"]],
                          "bound": "hbm", "achieved": per_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": per_gpu / peaks["hbm_gbs"], "peak_kind": f"per GPU, of {peak_kind} copy bandwidth", "traffic": None},
             "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": K * r * (4 if r1["collectives"] == "peer" else 3), "clocks": clocks,
+            "gpu_launches": K * r * {"peer": 4, "pull": 5, "nccl": 3}[r1["collectives"]], "clocks": clocks,
             "extras": {**{f"m{m}": v for m, v in results.items()}, "one_gpu_unsharded": {f"m{m}": v for m, v in base.items()}}}))
     dist.barrier()
     dist.destroy_process_group()

@@ -71,6 +71,8 @@ def lib() -> ctypes.CDLL:
     L.dinoml_b200_gguf_dual_gemm_rcr_bias.restype = ci
     L.dinoml_b200_peer_exchange.argtypes = [ctypes.POINTER(vp), ci, ci, ctypes.c_uint, vp, vp, i64, ci, vp]
     L.dinoml_b200_peer_exchange.restype = ci
+    L.dinoml_b200_peer_pull.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), ci, ci, ctypes.c_uint, ci, i64, i64, i64, i64, ci, vp]
+    L.dinoml_b200_peer_pull.restype = ci
     L.dinoml_b200_peer_enable_access.argtypes = [ci]
     L.dinoml_b200_peer_enable_access.restype = ci
     _lib = L

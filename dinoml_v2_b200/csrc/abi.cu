@@ -33,6 +33,8 @@ int gemm_rcr_umma_peers(const void* a, const void* b, const void* bias, void* c,
 int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch, const void* slots, void* out, int64_t count, int dtype,
                   cudaStream_t s);
 uint32_t peer_exchange_set_poll_limit(uint32_t polls);
+int peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, uint32_t epoch, int mode, int64_t off, int64_t chunk,
+              int64_t region_stride, int64_t dst_off, int dtype, cudaStream_t s);
 int gemm_rcr_stream(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,
                     cudaStream_t s);
 int gemm_rcr_stream_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,
@@ -305,6 +307,13 @@ int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, uns
 }
 
 unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned int polls) { return peer_exchange_set_poll_limit(polls); }
+
+int dinoml_b200_peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, unsigned int epoch, int mode, long long offset,
+                          long long chunk_bytes, long long region_stride, long long dst_offset, int dtype, void* stream) {
+  return set_error(peer_pull(signal_ptrs, buffer_ptrs, world, rank, epoch, mode, offset, chunk_bytes, region_stride, dst_offset, dtype,
+                             static_cast<cudaStream_t>(stream)),
+                   "dinoml_b200_peer_pull");
+}
 
 int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k) {
   return select_variant(qtype, dtype, m, n, k);

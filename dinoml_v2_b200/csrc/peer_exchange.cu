@@ -128,6 +128,114 @@ int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch,
   return err == cudaSuccess ? RC_OK : RC_LAUNCH;
 }
 
+// ---- pull exchanges for large results -----------------------------------------------------------------------------
+// For prefill-sized results the scatter epilogue (every CTA storing its tile to every GPU, 2 bytes at a time) is the
+// wrong tool; here the GEMM stores to local memory only and one kernel with a CTA per SM moves the data with 16-byte loads
+// from the peers' (symmetric) buffers:
+//   PULL_GATHER:  after the barrier, copy bytes [p * chunk, (p + 1) * chunk) of region `off` of rank p's buffer into the same
+//                 place of the local buffer, for every p != rank.  All-gather of per-rank shards (chunk = shard bytes) and
+//                 second half of the all-reduce (chunk = slice bytes of the reduced result).
+//   PULL_REDUCE:  after the barrier, out_slice = sum over ranks r (ascending, fp32) of slice `rank` of rank r's partial
+//                 result (region `off` + r * region_stride of rank r's buffer), written as slice `rank` of the local
+//                 result region `dst_off`.  First half of the all-reduce (reduce-scatter): each slice is summed once, by
+//                 its owner, so every rank ends up with identical bits after the gather.
+// The barrier is the one of peer_exchange_kernel (publish epoch, poll bounded, status 6 on give-up), run by every CTA.
+struct PeerBases {
+  uint8_t* ptr[8];        // buffer of every rank, mapped here; ptr[rank] is the local one
+};
+enum : int { PULL_GATHER = 0, PULL_REDUCE = 1 };
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+peer_pull_kernel(const PeerSignals sig, const PeerBases base, int world, int rank, uint32_t epoch, int mode, int64_t off, int64_t chunk,
+                 int64_t region_stride, int64_t dst_off, int* status, uint32_t poll_limit) {
+  const int tid = threadIdx.x;
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");          // the GEMM that produced the local data has completed
+  if (tid < world && tid != rank) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys(sig.ptr[tid] + rank, epoch);
+    }
+    bool seen = false;
+    for (uint32_t i = 0; i < poll_limit && !seen; ++i) {
+      seen = int32_t(ld_acquire_sys(sig.ptr[rank] + tid) - epoch) >= 0;
+      if (!seen) __nanosleep(200);
+    }
+    if (!seen) atomicCAS(status, 0, PEER_ST_TIMEOUT);
+  }
+  __syncthreads();
+  const int64_t vecs = chunk >> 4;                               // 16-byte units per chunk (chunk % 16 == 0)
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  if (mode == PULL_GATHER) {
+    for (int pi = 1; pi < world; ++pi) {
+      const int p = (rank + pi) % world;                         // every rank starts with a different peer
+      const uint4* src = reinterpret_cast<const uint4*>(base.ptr[p] + off + int64_t(p) * chunk);
+      uint4* dst = reinterpret_cast<uint4*>(base.ptr[rank] + off + int64_t(p) * chunk);
+      for (int64_t i = int64_t(blockIdx.x) * blockDim.x + tid; i < vecs; i += stride) dst[i] = __ldcv(src + i);
+    }
+  } else {
+    uint4* dst = reinterpret_cast<uint4*>(base.ptr[rank] + dst_off + int64_t(rank) * chunk);
+    constexpr int E = 16 / int(sizeof(T));
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + tid; i < vecs; i += stride) {
+      float acc[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] = 0.f;
+      for (int r = 0; r < world; ++r) {
+        const uint4 v = __ldcv(reinterpret_cast<const uint4*>(base.ptr[r] + off + int64_t(r) * region_stride + int64_t(rank) * chunk) + i);
+        const T* tv = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] += to_f32<T>(tv[e]);
+      }
+      uint4 o;
+      T* to = reinterpret_cast<T*>(&o);
+#pragma unroll
+      for (int e = 0; e < E; ++e) to[e] = from_f32<T>(acc[e]);
+      dst[i] = o;
+    }
+  }
+}
+
+int peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, uint32_t epoch, int mode, int64_t off, int64_t chunk,
+              int64_t region_stride, int64_t dst_off, int dtype, cudaStream_t s) {
+  if (signal_ptrs == nullptr || buffer_ptrs == nullptr || world < 1 || world > 8 || rank < 0 || rank >= world) return RC_RANGE;
+  if (mode != PULL_GATHER && mode != PULL_REDUCE) return RC_RANGE;
+  if (chunk <= 0 || (chunk & 15) || (off & 15) || (dst_off & 15) || (region_stride & 15) || off < 0 || dst_off < 0) return RC_ALIGN;
+  int* status = peer_status_ptr();
+  if (status == nullptr) return RC_LAUNCH;
+  PeerSignals sig;
+  PeerBases base;
+  for (int i = 0; i < 8; ++i) {
+    sig.ptr[i] = i < world ? static_cast<uint32_t*>(signal_ptrs[i]) : nullptr;
+    base.ptr[i] = i < world ? static_cast<uint8_t*>(buffer_ptrs[i]) : nullptr;
+    if (i < world && (sig.ptr[i] == nullptr || base.ptr[i] == nullptr)) return RC_NULL;
+    if (i < world && (reinterpret_cast<uintptr_t>(base.ptr[i]) & 15)) return RC_ALIGN;
+  }
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int64_t blocks = (chunk / 16 + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 2 * sms) blocks = 2 * sms;
+  const uint32_t limit = g_peer_poll_limit;
+  cudaError_t err;
+  switch (dtype) {
+    case DINO_BF16:
+      err = gemv_launch(peer_pull_kernel<__nv_bfloat16>, int(blocks), 1, 256, 0, s, sig, base, world, rank, epoch, mode, off, chunk, region_stride,
+                        dst_off, status, limit);
+      break;
+    case DINO_F16:
+      err = gemv_launch(peer_pull_kernel<__half>, int(blocks), 1, 256, 0, s, sig, base, world, rank, epoch, mode, off, chunk, region_stride, dst_off,
+                        status, limit);
+      break;
+    case DINO_F32:
+      err = gemv_launch(peer_pull_kernel<float>, int(blocks), 1, 256, 0, s, sig, base, world, rank, epoch, mode, off, chunk, region_stride, dst_off,
+                        status, limit);
+      break;
+    default: return RC_DTYPE;
+  }
+  return err == cudaSuccess ? RC_OK : RC_LAUNCH;
+}
+
 // Polls a later exchange makes per peer before it gives up (0 restores the default of 2^22, about a second).  For tests of
 // the give-up path and for hosts that want a shorter or longer patience; returns the previous value.
 uint32_t peer_exchange_set_poll_limit(uint32_t polls) {

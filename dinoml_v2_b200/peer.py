@@ -12,7 +12,12 @@ the slots; nothing tells it that the peers have finished reading theirs.  So eac
 alternates them by epoch parity: the results for exchange e+1 are stored into set (e+1) & 1 while a slow peer may still
 be summing set e & 1.  The set written for e+1 was last read in exchange e-1, and a rank only signals epoch e after its
 own exchange e-1 has completed, so a full barrier always separates a set's readers from its next writer - one
-PeerExchange may be used back to back (down_proj_peer in a loop, swiglu_mlp_peer) without a race."""
+PeerExchange may be used back to back (down_proj_peer in a loop, swiglu_mlp_peer) without a race.
+
+Pull path (prefill-sized results).  `pull_gather` / `pull_all_reduce` leave the GEMM's result in LOCAL memory and move
+it with `dinoml_b200_peer_pull` (one CTA per SM, 16-byte loads from the peers' buffers): an all-gather is one kernel, an
+all-reduce is two (every rank sums its own slice of all partial results in rank order, then the slices are gathered from
+an extra slot of the set), so every rank ends with identical bits.  A collective, not a kernel, advances the slot set."""
 from __future__ import annotations
 
 import ctypes
@@ -44,7 +49,9 @@ class PeerExchange:
         # plain peer stores only: keep the allocation off NVLink multicast objects
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
-        self._set_bytes = -(-(self.world * self.slot_elems * esize) // 256) * 256   # one slot set, 256-byte aligned
+        self._slot_bytes = self.slot_elems * esize
+        # one slot set = `world` slots + one more for the reduced result of the pull all-reduce, 256-byte aligned
+        self._set_bytes = -(-((self.world + 1) * self._slot_bytes) // 256) * 256
         nbytes = _SIGNAL_BYTES + 2 * self._set_bytes
         self._buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)      # [signals | set 0: slot 0 .. | set 1: slot 0 ..]
         self._buffer.zero_()
@@ -70,17 +77,22 @@ class PeerExchange:
         self._dtype_code = _native.DINO_DTYPE[str(dtype).replace("torch.", "")]
         self._lib = _native.lib()
         self._auto = _native.variant_code("auto")
-        self.epoch = 0
+        self._buffer_ptrs = (ctypes.c_void_p * self.world)(*base)
+        self._set_off = [_SIGNAL_BYTES + p * self._set_bytes for p in (0, 1)]
+        self._result = [self._buffer[off + self.world * self._slot_bytes:off + (self.world + 1) * self._slot_bytes].view(dtype)
+                        for off in self._set_off]
+        self.epoch = 0          # signal counter: one per exchange KERNEL
+        self.round = 0          # collectives completed: its parity picks the slot set
         dist.barrier(group=group)          # every rank has mapped every buffer before anyone writes
 
     @property
     def slots(self):
         """The slot set of the exchange that completed last (after `finish_*`), [world * slot_elems]."""
-        return self._sets[self.epoch & 1]
+        return self._sets[self.round & 1]
 
     def local_slot(self):
         """[slot_elems] view of this rank's slot in the set the NEXT exchange reads: the primary output of the scatter GEMV."""
-        nxt = self._sets[(self.epoch + 1) & 1]
+        nxt = self._sets[(self.round + 1) & 1]
         return nxt[self.rank * self.slot_elems:(self.rank + 1) * self.slot_elems]
 
     def gathered(self):
@@ -100,7 +112,7 @@ class PeerExchange:
             raise ValueError(f"result [{m}, {n}] does not fill a slot of {self.slot_elems} elements")
         if a.dtype != self.dtype:
             raise ValueError("activation dtype differs from the exchange buffers'")
-        nxt = (self.epoch + 1) & 1                    # the set the NEXT exchange reads
+        nxt = (self.round + 1) & 1                    # the set the NEXT exchange reads
         rc = self._lib.dinoml_b200_gguf_gemm_rcr_scatter(
             a.data_ptr(), b_quant.data_ptr(), bias.data_ptr() if bias is not None else None, self._local_ptr[nxt],
             self._peer_dst[nxt], self._n_peers, qv, self._dtype_code, m, n, k,
@@ -111,8 +123,9 @@ class PeerExchange:
     def _exchange(self, out, count):
         import torch
         self.epoch += 1
+        self.round += 1
         rc = self._lib.dinoml_b200_peer_exchange(self._signal_ptrs, self.world, self.rank, self.epoch,
-                                                 self._set_ptr[self.epoch & 1] if count else None,
+                                                 self._set_ptr[self.round & 1] if count else None,
                                                  out.data_ptr() if count else None, count, self._dtype_code,
                                                  torch.cuda.current_stream().cuda_stream)
         if rc:
@@ -129,3 +142,38 @@ class PeerExchange:
             raise ValueError("output does not match the slot size")
         self._exchange(out, self.slot_elems)
         return out
+
+    # ---- pull path: the GEMM writes local memory only -----------------------------------------------------------------
+    def _pull(self, mode: int, off: int, chunk: int, region_stride: int, dst_off: int):
+        import torch
+        self.epoch += 1
+        rc = self._lib.dinoml_b200_peer_pull(self._signal_ptrs, self._buffer_ptrs, self.world, self.rank, self.epoch, mode, off, chunk,
+                                             region_stride, dst_off, self._dtype_code, torch.cuda.current_stream().cuda_stream)
+        if rc:
+            _native.check(rc, "dinoml_b200_peer_pull")
+
+    def pull_gather(self):
+        """Completes an all-gather whose shards every rank stored into `local_slot()` of its own buffer: one kernel pulls the
+        other ranks' shards over NVLink.  Returns the [world, slot_elems] view."""
+        if self._slot_bytes % 16:
+            raise ValueError("pull exchanges need slots that are multiples of 16 bytes")
+        self.round += 1
+        self._pull(0, self._set_off[self.round & 1], self._slot_bytes, 0, 0)
+        return self.gathered()
+
+    def pull_all_reduce(self, out=None):
+        """Two-shot all-reduce of the partial results every rank stored into `local_slot()`: every rank sums slice `rank` of all
+        partial results (rank order, fp32), then the slices are gathered.  Returns the reduced [slot_elems] tensor (a view of
+        this rank's buffer, valid until the collective after the next) or copies it into `out`."""
+        if self._slot_bytes % (16 * self.world):
+            raise ValueError("the pull all-reduce needs slots that split into 16-byte multiples per rank")
+        self.round += 1
+        s = self.round & 1
+        off, res_off, slice_bytes = self._set_off[s], self._set_off[s] + self.world * self._slot_bytes, self._slot_bytes // self.world
+        self._pull(1, off, slice_bytes, self._slot_bytes, res_off)       # reduce-scatter: partial of rank r = slot r of ITS buffer
+        self._pull(0, res_off, slice_bytes, 0, 0)                        # all-gather of the reduced slices
+        res = self._result[s]
+        if out is not None:
+            out.view(-1).copy_(res)
+            return out
+        return res

@@ -94,6 +94,21 @@ class ShardedFFN:
         self.xchg_down.finish_reduce(out)
         return out
 
+    def gate_up_pull(self, x):
+        """The peer path for prefill-sized batches: the GEMM stores its shard locally, one pull kernel gathers the others."""
+        from . import kernels
+        xg = self.xchg_gate_up
+        kernels.gemm_rcr(x, self.gate_up_stacked, self.qtype, out=xg.local_slot().view(self.peer_m, self.gate_up_stacked.shape[0]))
+        g = xg.pull_gather()
+        return g.view(self.world, self.peer_m, self.gate_up_stacked.shape[0])
+
+    def down_proj_pull(self, h_slice, out=None):
+        """Down projection with the two-shot pull all-reduce (identical bits on every rank)."""
+        from . import kernels
+        xd = self.xchg_down
+        kernels.gemm_rcr(h_slice, self.down, self.qtype, out=xd.local_slot().view(self.peer_m, self.hidden))
+        return xd.pull_all_reduce(out)
+
     def swiglu_mlp_peer(self, x, out):
         """The whole gated MLP, out [M, hidden] = (silu(x Wgate^T) * (x Wup^T)) Wdown^T, in three launches and no
         all-gather: rank r's rows of gate / up are exactly the K-slice of down it owns, so the gated activations stay

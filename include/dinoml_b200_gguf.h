@@ -167,6 +167,19 @@ DINOML_B200_API int dinoml_b200_peer_enable_access(int peer_device);
 DINOML_B200_API int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, unsigned int epoch, const void* slots,
                                               void* out, int64_t count, int dtype, void* stream);
 DINOML_B200_API unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned int polls);
+/* Pull exchanges for prefill-sized results: the GEMM stores to local memory only, then one kernel (a CTA per SM, 16-byte
+ * loads from the peers' buffers over NVLink) does the barrier of dinoml_b200_peer_exchange and moves the data.
+ * buffer_ptrs[r] = the (symmetric) buffer of rank r mapped into this process; offsets and sizes in bytes, multiples of 16.
+ *   mode 0 (gather): for every p != rank copy bytes [offset + p * chunk_bytes, + chunk_bytes) of rank p's buffer into the
+ *     same place of the local buffer - an all-gather of per-rank shards laid out rank-major.
+ *   mode 1 (reduce slice): slice `rank` (chunk_bytes) of the sum over ranks r, ascending, fp32, of the partial result that
+ *     rank r keeps at offset + r * region_stride of ITS buffer, written to dst_offset + rank * chunk_bytes of the local
+ *     buffer.  Followed by a mode-0 call on the result region this is a two-shot all-reduce in which every slice is summed
+ *     once, by its owner: identical bits on every rank.
+ * Same epoch / reuse rules as dinoml_b200_peer_exchange (each call is one exchange: one epoch). */
+DINOML_B200_API int dinoml_b200_peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, unsigned int epoch, int mode,
+                                          long long offset, long long chunk_bytes, long long region_stride, long long dst_offset, int dtype,
+                                          void* stream);
 
 /* Per-candidate symbols, named like the reference's kernel symbols so a manifest can carry them:
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)

@@ -148,3 +148,48 @@ def test_peer_exchange_bounded_wait_runs_out():
         assert fake.cpu().tolist()[0] == epoch                          # its own signal still went out
     finally:
         assert lib.dinoml_b200_peer_exchange_set_poll_limit(before) == 4000
+
+
+def test_peer_pull_gather_and_reduce_single_process():
+    """The pull exchanges with three "ranks" that are local buffers (signals pre-written): gather copies every other rank's
+    shard into place, reduce-slice sums this rank's slice of all partial results in rank order with fp32 accumulation."""
+    dev = torch.device("cuda:0")
+    lib = _native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    world, rank, epoch = 3, 1, 5
+    slot_elems = 3 * 8 * 1000                              # divisible into 16-byte multiples per rank
+    slot_bytes = slot_elems * 2
+    region = (world + 1) * slot_bytes
+    bufs = [torch.zeros(256 + region, dtype=torch.uint8, device=dev) for _ in range(world)]
+    sigs = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(world)]
+    sigs[rank][0], sigs[rank][2] = epoch, epoch + 3        # what ranks 0 and 2 would have stored by now
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    shards = [torch.randn(slot_elems, device=dev, generator=gen).to(torch.bfloat16) for _ in range(world)]
+    for r in range(world):                                 # rank r's shard sits in slot r of ITS buffer
+        bufs[r][256 + r * slot_bytes:256 + (r + 1) * slot_bytes].view(torch.bfloat16).copy_(shards[r])
+    sig_ptrs = (ctypes.c_void_p * world)(*[s.data_ptr() for s in sigs])
+    buf_ptrs = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    lib.dinoml_b200_peer_pull.restype = ctypes.c_int
+    rc = lib.dinoml_b200_peer_pull(sig_ptrs, buf_ptrs, world, rank, epoch, 0, 256, slot_bytes, 0, 0, BF16, stream)
+    assert rc == 0, _native.last_error()
+    torch.cuda.synchronize()
+    assert kernels.device_status() == 0
+    mine = bufs[rank][256:256 + world * slot_bytes].view(torch.bfloat16).view(world, slot_elems)
+    for r in range(world):
+        assert torch.equal(mine[r], shards[r]), r
+    # reduce-slice: partial of rank r = slot r of rank r's buffer; this rank's slice of the sum lands in its result slot
+    slice_elems = slot_elems // world
+    rc = lib.dinoml_b200_peer_pull(sig_ptrs, buf_ptrs, world, rank, epoch, 1, 256, slot_bytes // world, slot_bytes, 256 + world * slot_bytes,
+                                   BF16, stream)
+    assert rc == 0, _native.last_error()
+    torch.cuda.synchronize()
+    want = sum(s[rank * slice_elems:(rank + 1) * slice_elems].float() for s in shards).to(torch.bfloat16)
+    res = bufs[rank][256 + world * slot_bytes:256 + (world + 1) * slot_bytes].view(torch.bfloat16)
+    assert torch.equal(res[rank * slice_elems:(rank + 1) * slice_elems], want)
+    assert int(res[:rank * slice_elems].float().abs().sum()) == 0      # other slices are the other ranks' business
+    # argument checks
+    assert lib.dinoml_b200_peer_pull(sig_ptrs, buf_ptrs, world, rank, epoch, 0, 256, slot_bytes + 8, 0, 0, BF16, stream) == 7
+    assert lib.dinoml_b200_peer_pull(sig_ptrs, buf_ptrs, world, rank, epoch, 2, 256, slot_bytes, 0, 0, BF16, stream) == 8
+    assert lib.dinoml_b200_peer_pull(sig_ptrs, buf_ptrs, 9, rank, epoch, 0, 256, slot_bytes, 0, 0, BF16, stream) == 8
+    assert kernels.device_status() == 0
