@@ -73,6 +73,10 @@ def lib() -> ctypes.CDLL:
     L.dinoml_b200_peer_exchange.restype = ci
     L.dinoml_b200_peer_pull.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), ci, ci, ctypes.c_uint, ci, i64, i64, i64, i64, ci, vp]
     L.dinoml_b200_peer_pull.restype = ci
+    L.dinoml_b200_peer_exchange_ctr.argtypes = [ctypes.POINTER(vp), ci, ci, vp, vp, vp, i64, ci, vp]
+    L.dinoml_b200_peer_exchange_ctr.restype = ci
+    L.dinoml_b200_peer_pull_ctr.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(vp), ci, ci, vp, ci, i64, i64, i64, i64, ci, vp]
+    L.dinoml_b200_peer_pull_ctr.restype = ci
     L.dinoml_b200_peer_enable_access.argtypes = [ci]
     L.dinoml_b200_peer_enable_access.restype = ci
     _lib = L

@@ -31,10 +31,10 @@ int gemm_rcr_mma_peers(const void* a, const void* b, const void* bias, void* c, 
 int gemm_rcr_umma_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k,
                         const PeerOut* peer_out, cudaStream_t s);
 int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch, const void* slots, void* out, int64_t count, int dtype,
-                  cudaStream_t s);
+                  cudaStream_t s, uint32_t* epoch_ctr);
 uint32_t peer_exchange_set_poll_limit(uint32_t polls);
 int peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, uint32_t epoch, int mode, int64_t off, int64_t chunk,
-              int64_t region_stride, int64_t dst_off, int dtype, cudaStream_t s);
+              int64_t region_stride, int64_t dst_off, int dtype, cudaStream_t s, uint32_t* epoch_ctr);
 int gemm_rcr_stream(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,
                     cudaStream_t s);
 int gemm_rcr_stream_peers(const void* a, const void* b, const void* bias, void* c, int qtype, int dtype, int m, int n, int k, int config,
@@ -302,8 +302,15 @@ int dinoml_b200_peer_enable_access(int peer_device) {
 
 int dinoml_b200_peer_exchange(void* const* signal_ptrs, int world, int rank, unsigned int epoch, const void* slots, void* out,
                               int64_t count, int dtype, void* stream) {
-  return set_error(peer_exchange(signal_ptrs, world, rank, epoch, slots, out, count, dtype, static_cast<cudaStream_t>(stream)),
+  return set_error(peer_exchange(signal_ptrs, world, rank, epoch, slots, out, count, dtype, static_cast<cudaStream_t>(stream), nullptr),
                    "dinoml_b200_peer_exchange");
+}
+
+int dinoml_b200_peer_exchange_ctr(void* const* signal_ptrs, int world, int rank, unsigned int* epoch_counter, const void* slots, void* out,
+                                  int64_t count, int dtype, void* stream) {
+  if (epoch_counter == nullptr) return set_error(RC_NULL, "dinoml_b200_peer_exchange_ctr");
+  return set_error(peer_exchange(signal_ptrs, world, rank, 0, slots, out, count, dtype, static_cast<cudaStream_t>(stream), epoch_counter),
+                   "dinoml_b200_peer_exchange_ctr");
 }
 
 unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned int polls) { return peer_exchange_set_poll_limit(polls); }
@@ -311,8 +318,16 @@ unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned int polls) { retu
 int dinoml_b200_peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, unsigned int epoch, int mode, long long offset,
                           long long chunk_bytes, long long region_stride, long long dst_offset, int dtype, void* stream) {
   return set_error(peer_pull(signal_ptrs, buffer_ptrs, world, rank, epoch, mode, offset, chunk_bytes, region_stride, dst_offset, dtype,
-                             static_cast<cudaStream_t>(stream)),
+                             static_cast<cudaStream_t>(stream), nullptr),
                    "dinoml_b200_peer_pull");
+}
+
+int dinoml_b200_peer_pull_ctr(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, unsigned int* epoch_counter, int mode,
+                              long long offset, long long chunk_bytes, long long region_stride, long long dst_offset, int dtype, void* stream) {
+  if (epoch_counter == nullptr) return set_error(RC_NULL, "dinoml_b200_peer_pull_ctr");
+  return set_error(peer_pull(signal_ptrs, buffer_ptrs, world, rank, 0, mode, offset, chunk_bytes, region_stride, dst_offset, dtype,
+                             static_cast<cudaStream_t>(stream), epoch_counter),
+                   "dinoml_b200_peer_pull_ctr");
 }
 
 int dinoml_b200_gguf_gemm_rcr_select(int qtype, int dtype, int m, int n, int k) {

@@ -51,10 +51,24 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 
+// Last block out stores the epoch this launch used into the device counter ([0] = epoch, [1] = blocks finished).
+__device__ __forceinline__ void advance_epoch(uint32_t* epoch_ctr, uint32_t epoch) {
+  if (epoch_ctr == nullptr) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(epoch_ctr + 1, 1u) == gridDim.x - 1) {
+      epoch_ctr[1] = 0u;
+      __threadfence();
+      epoch_ctr[0] = epoch;
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 peer_exchange_kernel(const PeerSignals sig, int world, int rank, uint32_t epoch, const T* __restrict__ slots, T* __restrict__ out,
-                     int64_t count, int* status, uint32_t poll_limit) {
+                     int64_t count, int* status, uint32_t poll_limit, uint32_t* epoch_ctr) {
   const int tid = threadIdx.x;
   // Programmatic dependent launch on both sides.  The kernel that follows in the stream (the next GEMV) may start at once:
   // it streams its constant weights while this kernel waits for the peers, and blocks before it reads what this kernel
@@ -62,6 +76,10 @@ peer_exchange_kernel(const PeerSignals sig, int world, int rank, uint32_t epoch,
   // publish "my stores are complete" - nor read the slots - until it has.
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  // Device-resident epoch (for launches replayed from a CUDA graph, whose arguments are frozen): every exchange on this
+  // counter uses its value + 1 and the last block to finish stores it back.  Read after the dependency wait: every
+  // earlier kernel of the stream, the previous exchange included, has completed by then.
+  if (epoch_ctr != nullptr) epoch = ld_acquire_sys(epoch_ctr) + 1u;
   if (tid < world && tid != rank) {
     if (blockIdx.x == 0) {
       __threadfence_system();
@@ -80,6 +98,7 @@ peer_exchange_kernel(const PeerSignals sig, int world, int rank, uint32_t epoch,
     for (int r = 0; r < world; ++r) acc += to_f32<T>(__ldcg(slots + int64_t(r) * count + i));
     out[i] = from_f32<T>(acc);
   }
+  advance_epoch(epoch_ctr, epoch);
 }
 
 static __device__ int g_peer_status;
@@ -96,7 +115,7 @@ static int* peer_status_ptr() {
 }
 
 int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch, const void* slots, void* out, int64_t count, int dtype,
-                  cudaStream_t s) {
+                  cudaStream_t s, uint32_t* epoch_ctr) {
   if (signal_ptrs == nullptr || world < 1 || world > 8 || rank < 0 || rank >= world) return RC_RANGE;
   if (count < 0 || (count > 0 && (slots == nullptr || out == nullptr))) return RC_NULL;
   int* status = peer_status_ptr();
@@ -113,15 +132,15 @@ int peer_exchange(void* const* signal_ptrs, int world, int rank, uint32_t epoch,
   switch (dtype) {
     case DINO_BF16:
       err = gemv_launch(peer_exchange_kernel<__nv_bfloat16>, int(blocks), 1, 256, 0, s, sig, world, rank, epoch, static_cast<const __nv_bfloat16*>(slots),
-                        static_cast<__nv_bfloat16*>(out), count, status, limit);
+                        static_cast<__nv_bfloat16*>(out), count, status, limit, epoch_ctr);
       break;
     case DINO_F16:
       err = gemv_launch(peer_exchange_kernel<__half>, int(blocks), 1, 256, 0, s, sig, world, rank, epoch, static_cast<const __half*>(slots),
-                        static_cast<__half*>(out), count, status, limit);
+                        static_cast<__half*>(out), count, status, limit, epoch_ctr);
       break;
     case DINO_F32:
       err = gemv_launch(peer_exchange_kernel<float>, int(blocks), 1, 256, 0, s, sig, world, rank, epoch, static_cast<const float*>(slots),
-                        static_cast<float*>(out), count, status, limit);
+                        static_cast<float*>(out), count, status, limit, epoch_ctr);
       break;
     default: return RC_DTYPE;
   }
@@ -148,10 +167,11 @@ enum : int { PULL_GATHER = 0, PULL_REDUCE = 1 };
 template <typename T>
 __global__ void __launch_bounds__(256)
 peer_pull_kernel(const PeerSignals sig, const PeerBases base, int world, int rank, uint32_t epoch, int mode, int64_t off, int64_t chunk,
-                 int64_t region_stride, int64_t dst_off, int* status, uint32_t poll_limit) {
+                 int64_t region_stride, int64_t dst_off, int* status, uint32_t poll_limit, uint32_t* epoch_ctr) {
   const int tid = threadIdx.x;
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   asm volatile("griddepcontrol.wait;\n" ::: "memory");          // the GEMM that produced the local data has completed
+  if (epoch_ctr != nullptr) epoch = ld_acquire_sys(epoch_ctr) + 1u;
   if (tid < world && tid != rank) {
     if (blockIdx.x == 0) {
       __threadfence_system();
@@ -194,10 +214,11 @@ peer_pull_kernel(const PeerSignals sig, const PeerBases base, int world, int ran
       dst[i] = o;
     }
   }
+  advance_epoch(epoch_ctr, epoch);
 }
 
 int peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, uint32_t epoch, int mode, int64_t off, int64_t chunk,
-              int64_t region_stride, int64_t dst_off, int dtype, cudaStream_t s) {
+              int64_t region_stride, int64_t dst_off, int dtype, cudaStream_t s, uint32_t* epoch_ctr) {
   if (signal_ptrs == nullptr || buffer_ptrs == nullptr || world < 1 || world > 8 || rank < 0 || rank >= world) return RC_RANGE;
   if (mode != PULL_GATHER && mode != PULL_REDUCE) return RC_RANGE;
   if (chunk <= 0 || (chunk & 15) || (off & 15) || (dst_off & 15) || (region_stride & 15) || off < 0 || dst_off < 0) return RC_ALIGN;
@@ -221,15 +242,15 @@ int peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int
   switch (dtype) {
     case DINO_BF16:
       err = gemv_launch(peer_pull_kernel<__nv_bfloat16>, int(blocks), 1, 256, 0, s, sig, base, world, rank, epoch, mode, off, chunk, region_stride,
-                        dst_off, status, limit);
+                        dst_off, status, limit, epoch_ctr);
       break;
     case DINO_F16:
       err = gemv_launch(peer_pull_kernel<__half>, int(blocks), 1, 256, 0, s, sig, base, world, rank, epoch, mode, off, chunk, region_stride, dst_off,
-                        status, limit);
+                        status, limit, epoch_ctr);
       break;
     case DINO_F32:
       err = gemv_launch(peer_pull_kernel<float>, int(blocks), 1, 256, 0, s, sig, base, world, rank, epoch, mode, off, chunk, region_stride, dst_off,
-                        status, limit);
+                        status, limit, epoch_ctr);
       break;
     default: return RC_DTYPE;
   }

@@ -35,7 +35,7 @@ class PeerExchange:
     slot r of every rank's buffer receives rank r's GEMV result; `finish_gather` / `finish_reduce` complete the
     collective on the current stream.  All ranks must make the same sequence of calls."""
 
-    def __init__(self, slot_elems: int, dtype, group=None):
+    def __init__(self, slot_elems: int, dtype, group=None, device_epoch: bool = False):
         import torch
         import torch.distributed as dist
         self.group = group
@@ -81,6 +81,9 @@ class PeerExchange:
         self._set_off = [_SIGNAL_BYTES + p * self._set_bytes for p in (0, 1)]
         self._result = [self._buffer[off + self.world * self._slot_bytes:off + (self.world + 1) * self._slot_bytes].view(dtype)
                         for off in self._set_off]
+        # device_epoch: the kernels keep the signal counter in device memory, so a captured CUDA graph of exchanges can be
+        # replayed (capture an even number of collectives: the slot-set parity of a replay is then the captured one)
+        self._epoch_ctr = torch.zeros(2, dtype=torch.int32, device=dev) if device_epoch else None
         self.epoch = 0          # signal counter: one per exchange KERNEL
         self.round = 0          # collectives completed: its parity picks the slot set
         dist.barrier(group=group)          # every rank has mapped every buffer before anyone writes
@@ -124,10 +127,16 @@ class PeerExchange:
         import torch
         self.epoch += 1
         self.round += 1
-        rc = self._lib.dinoml_b200_peer_exchange(self._signal_ptrs, self.world, self.rank, self.epoch,
-                                                 self._set_ptr[self.round & 1] if count else None,
-                                                 out.data_ptr() if count else None, count, self._dtype_code,
-                                                 torch.cuda.current_stream().cuda_stream)
+        if self._epoch_ctr is not None:
+            rc = self._lib.dinoml_b200_peer_exchange_ctr(self._signal_ptrs, self.world, self.rank, self._epoch_ctr.data_ptr(),
+                                                         self._set_ptr[self.round & 1] if count else None,
+                                                         out.data_ptr() if count else None, count, self._dtype_code,
+                                                         torch.cuda.current_stream().cuda_stream)
+        else:
+            rc = self._lib.dinoml_b200_peer_exchange(self._signal_ptrs, self.world, self.rank, self.epoch,
+                                                     self._set_ptr[self.round & 1] if count else None,
+                                                     out.data_ptr() if count else None, count, self._dtype_code,
+                                                     torch.cuda.current_stream().cuda_stream)
         if rc:
             _native.check(rc, "dinoml_b200_peer_exchange")
 
@@ -147,8 +156,12 @@ class PeerExchange:
     def _pull(self, mode: int, off: int, chunk: int, region_stride: int, dst_off: int):
         import torch
         self.epoch += 1
-        rc = self._lib.dinoml_b200_peer_pull(self._signal_ptrs, self._buffer_ptrs, self.world, self.rank, self.epoch, mode, off, chunk,
-                                             region_stride, dst_off, self._dtype_code, torch.cuda.current_stream().cuda_stream)
+        if self._epoch_ctr is not None:
+            rc = self._lib.dinoml_b200_peer_pull_ctr(self._signal_ptrs, self._buffer_ptrs, self.world, self.rank, self._epoch_ctr.data_ptr(), mode,
+                                                     off, chunk, region_stride, dst_off, self._dtype_code, torch.cuda.current_stream().cuda_stream)
+        else:
+            rc = self._lib.dinoml_b200_peer_pull(self._signal_ptrs, self._buffer_ptrs, self.world, self.rank, self.epoch, mode, off, chunk,
+                                                 region_stride, dst_off, self._dtype_code, torch.cuda.current_stream().cuda_stream)
         if rc:
             _native.check(rc, "dinoml_b200_peer_pull")
 

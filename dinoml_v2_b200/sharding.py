@@ -67,7 +67,7 @@ class ShardedFFN:
         return gathered_gate, gathered_up
 
     # ---- peer-memory path (decode and small batches; the variant is chosen by shape as for gemm_rcr) ----------------------------------------------------------------------
-    def enable_peer_path(self, m: int, dtype, share_with=None):
+    def enable_peer_path(self, m: int, dtype, share_with=None, device_epoch: bool = False):
         """Stacks gate and up into one [2 * ffn / world, hidden] weight (one launch, one gather) and maps the exchange
         buffers of all ranks (or reuses those of `share_with`, another ShardedFFN of the same shape that runs on the
         same stream).  Collective call: every rank must make it."""
@@ -79,8 +79,8 @@ class ShardedFFN:
         if share_with is not None:
             self.xchg_gate_up, self.xchg_down = share_with.xchg_gate_up, share_with.xchg_down
         else:
-            self.xchg_gate_up = PeerExchange(self.peer_m * self.gate_up_stacked.shape[0], dtype, self.group)
-            self.xchg_down = PeerExchange(self.peer_m * self.hidden, dtype, self.group)
+            self.xchg_gate_up = PeerExchange(self.peer_m * self.gate_up_stacked.shape[0], dtype, self.group, device_epoch=device_epoch)
+            self.xchg_down = PeerExchange(self.peer_m * self.hidden, dtype, self.group, device_epoch=device_epoch)
 
     def gate_up_peer(self, x):
         """Returns [world, M, 2 * ffn / world]: per rank, its gate rows then its up rows."""

@@ -180,6 +180,15 @@ DINOML_B200_API unsigned int dinoml_b200_peer_exchange_set_poll_limit(unsigned i
 DINOML_B200_API int dinoml_b200_peer_pull(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, unsigned int epoch, int mode,
                                           long long offset, long long chunk_bytes, long long region_stride, long long dst_offset, int dtype,
                                           void* stream);
+/* The same two kernels with the epoch kept on the DEVICE: `epoch_counter` points to two zero-initialised 32-bit words owned
+ * by the caller (one pair per signal array); each launch uses counter + 1 and the last block out stores it back.  For launch
+ * sequences captured in a CUDA graph, whose arguments are frozen: every replay still signals a fresh epoch.  Capture an even
+ * number of collectives per graph so that the alternation of the two slot sets is the same in every replay. */
+DINOML_B200_API int dinoml_b200_peer_exchange_ctr(void* const* signal_ptrs, int world, int rank, unsigned int* epoch_counter, const void* slots,
+                                                  void* out, int64_t count, int dtype, void* stream);
+DINOML_B200_API int dinoml_b200_peer_pull_ctr(void* const* signal_ptrs, void* const* buffer_ptrs, int world, int rank, unsigned int* epoch_counter,
+                                              int mode, long long offset, long long chunk_bytes, long long region_stride, long long dst_offset,
+                                              int dtype, void* stream);
 
 /* Per-candidate symbols, named like the reference's kernel symbols so a manifest can carry them:
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)
