@@ -193,3 +193,42 @@ def test_peer_pull_gather_and_reduce_single_process():
     assert lib.dinoml_b200_peer_pull(sig_ptrs, buf_ptrs, world, rank, epoch, 2, 256, slot_bytes, 0, 0, BF16, stream) == 8
     assert lib.dinoml_b200_peer_pull(sig_ptrs, buf_ptrs, 9, rank, epoch, 0, 256, slot_bytes, 0, 0, BF16, stream) == 8
     assert kernels.device_status() == 0
+
+
+def test_peer_exchange_device_epoch_in_a_replayed_graph():
+    """Exchanges captured in a CUDA graph keep their epoch in device memory: every replay signals the next value, the last
+    block out stores it back; the "peers" here are local signal arrays pre-written far ahead."""
+    dev = torch.device("cuda:0")
+    lib = _native.lib()
+    world, rank, count = 3, 1, 5000
+    local = torch.full((8,), 1000, dtype=torch.int32, device=dev)      # ranks 0 and 2 are "far ahead": every wait passes
+    fakes = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(2)]
+    sig = (ctypes.c_void_p * world)(fakes[0].data_ptr(), local.data_ptr(), fakes[1].data_ptr())
+    ctr = torch.zeros(2, dtype=torch.int32, device=dev)
+    slots = torch.randn(world, count, device=dev).to(torch.bfloat16)
+    out = torch.zeros(count, device=dev, dtype=torch.bfloat16)
+    side = torch.cuda.Stream(device=dev)
+
+    def two_exchanges():
+        s = torch.cuda.current_stream().cuda_stream
+        assert lib.dinoml_b200_peer_exchange_ctr(sig, world, rank, ctr.data_ptr(), None, None, 0, BF16, s) == 0, _native.last_error()
+        assert lib.dinoml_b200_peer_exchange_ctr(sig, world, rank, ctr.data_ptr(), slots.data_ptr(), out.data_ptr(), count, BF16, s) == 0
+
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        two_exchanges()                                   # epochs 1, 2
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            two_exchanges()
+    torch.cuda.synchronize()
+    assert ctr.cpu().tolist() == [2, 0] and fakes[0].cpu().tolist()[rank] == 2
+    for replay in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ctr.cpu().tolist() == [4 + 2 * replay, 0]
+        for f in fakes:
+            assert f.cpu().tolist()[rank] == 4 + 2 * replay               # the signal of the last exchange of the replay
+    want = slots.float().sum(dim=0).to(torch.bfloat16)
+    assert torch.equal(out, want) and kernels.device_status() == 0
+    assert lib.dinoml_b200_peer_exchange_ctr(sig, world, rank, None, None, None, 0, BF16, None) == 1      # null counter
