@@ -849,6 +849,24 @@ int dino_session_get_output_shape(DinoSession* session, size_t output_index, int
   return 0;
 }
 
+// The three optional session entries of the reference's generated module.  This runtime keeps no per-session temporary arena
+// (the fused kernels need no dense scratch) and the quantized-linear graphs have no state tensors, so the arena calls
+// validate their arguments and succeed, and no state index is valid.
+int dino_session_set_temp_arena_policy(DinoSession* session, int policy) {
+  if (session == nullptr) return fail("dino_session_set_temp_arena_policy received null session");
+  if (policy < 0 || policy > 2) return fail("Unsupported temp arena allocation policy");
+  return 0;
+}
+int dino_session_release_temp_arena(DinoSession* session) {
+  if (session == nullptr) return fail("dino_session_release_temp_arena received null session");
+  return 0;
+}
+int dino_session_get_state_pointer(DinoSession* session, size_t state_index, void** out_data) {
+  (void)state_index;
+  if (session == nullptr || out_data == nullptr) return fail("dino_session_get_state_pointer received null argument");
+  return fail("dino_session_get_state_pointer received invalid state index");
+}
+
 int dino_session_set_graph_replay(DinoSession* session, int enabled) {
   if (session == nullptr) return fail("dino_session_set_graph_replay received null pointer");
   session->graph_replay = enabled != 0;

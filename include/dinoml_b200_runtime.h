@@ -99,6 +99,12 @@ DINOML_B200_API int dino_session_get_output_shape(struct DinoSession* session, s
  * input / output device pointers is captured into a CUDA graph the second time the combination is seen and replayed from
  * then on (validation ran at capture).  Callers keep their buffers stable (Session.run_numpy's arenas are).  Modules that
  * stream constants from the host and DINOML_PROFILE_RUN runs always take the ordinary path. */
+/* Optional entries of the reference's module (gpu_module.cu.j2:589-615, 662-678).  No per-session temporary arena exists here
+ * (no dense dequant scratch) and these graphs have no state tensors: the arena calls check their arguments (policy 0..2)
+ * and succeed, every state index is invalid. */
+DINOML_B200_API int dino_session_set_temp_arena_policy(struct DinoSession* session, int policy);
+DINOML_B200_API int dino_session_release_temp_arena(struct DinoSession* session);
+DINOML_B200_API int dino_session_get_state_pointer(struct DinoSession* session, size_t state_index, void** out_data);
 DINOML_B200_API int dino_session_set_graph_replay(struct DinoSession* session, int enabled);
 DINOML_B200_API int dino_session_get_graph_stats(struct DinoSession* session, size_t* cached_graphs, size_t* graph_launches);
 /* :995 / :706-993 - validates every tensor, then launches the plan on the session stream.  With DINOML_PROFILE_RUN set every
