@@ -34,6 +34,8 @@ STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": {"Q4_K": 5, "Q6_K": 4, 
 STREAM_QTYPES = ("Q4_K", "Q6_K", "Q5_K")
 # five further layouts run on the same persistent data path with fp32 arithmetic, in ONE configuration (4)
 STREAM_FP32_QTYPES = ("Q4_0", "Q2_K", "Q3_K", "MXFP4", "NVFP4")
+# further types the tcgen05 GEMM unpacks (besides Q4_K, Q6_K, Q8_0); MXFP4 and NVFP4 become exact 16-bit operands
+UMMA_MORE_QTYPES = ("Q5_K", "Q4_0", "MXFP4", "NVFP4")
 
 _B200_TUNING = {
     "simt": {"kind": "gemv_simt", "rows_per_warp": 1, "activation_rows_per_pass": 4, "staging": "ldg", "tensor_cores": "none"},
@@ -62,7 +64,7 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
         if qtype in ("Q4_K", "Q6_K", "Q8_0"):
             variants.append("mma")
             variants.append("umma")
-        elif qtype == "Q5_K":                       # tensor-core paths: the persistent GEMV (below) and the tcgen05 GEMM
+        elif qtype in UMMA_MORE_QTYPES:             # further types with a tcgen05 GEMM (Q5_K also has the tensor-core persistent GEMV)
             variants.append("umma")
         if qtype in STREAM_QTYPES:
             variants += [f"stream:{c}" for c in sorted(STREAM_CONFIGS)]

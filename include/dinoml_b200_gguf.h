@@ -194,7 +194,8 @@ DINOML_B200_API int dinoml_b200_peer_pull_ctr(void* const* signal_ptrs, void* co
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_bias_<dtype>_<variant>_v1(a, b_quant, bias, c, m, n, k, stream)
  *   float dinoml_profile_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, iterations, stream)
- * with <q> in {q8_0,q4_k,q6_k} (and the simt symbols of q4_0,q5_k,q2_k,q3_k,mxfp4,nvfp4), <dtype> in {float16,bfloat16,float32}, <variant> in {simt,mma,umma,stream}
+ * with <q> in {q8_0,q4_k,q6_k} (the six further types: simt and stream for all, umma for q4_0,q5_k,mxfp4,nvfp4),
+ * <dtype> in {float16,bfloat16,float32}, <variant> in {simt,mma,umma,stream}
  * (mma / umma / stream exist for float16 and bfloat16 only; a symbol runs its family's default tuning configuration, the
  * other configurations are reached through dinoml_b200_gguf_gemm_rcr with a variant code). */
 #define DINOML_B200_GGUF_DECLARE(q, dt, var)                                                                       \
@@ -218,11 +219,21 @@ DINOML_B200_GGUF_DECLARE_Q(q8_0)
 DINOML_B200_GGUF_DECLARE_Q(q4_k)
 DINOML_B200_GGUF_DECLARE_Q(q6_k)
 /* The six further types of the reference's fused prototype (kernels/rocm/src/ck_gguf_q8_gemm.hip:27-32, 43-69, 80-92; symbol
- * family :1910-1940 per type): dequantize bit-exact, fused gemm on the CUDA-core variant only. */
+ * family :1910-1940 per type): dequantize bit-exact; fused gemm on the CUDA-core variant for every dtype, on the persistent
+ * GEMV (M <= 8) for the 16-bit dtypes, and - Q4_0, Q5_K, MXFP4, NVFP4 - on the tcgen05 GEMM (M >= 9). */
 #define DINOML_B200_GGUF_DECLARE_SIMT_Q(q)    \
   DINOML_B200_GGUF_DECLARE(q, float32, simt)  \
   DINOML_B200_GGUF_DECLARE(q, float16, simt)  \
-  DINOML_B200_GGUF_DECLARE(q, bfloat16, simt)
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, simt) \
+  DINOML_B200_GGUF_DECLARE(q, float16, stream) \
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, stream)
+#define DINOML_B200_GGUF_DECLARE_UMMA_Q(q)    \
+  DINOML_B200_GGUF_DECLARE(q, float16, umma)  \
+  DINOML_B200_GGUF_DECLARE(q, bfloat16, umma)
+DINOML_B200_GGUF_DECLARE_UMMA_Q(q4_0)
+DINOML_B200_GGUF_DECLARE_UMMA_Q(q5_k)
+DINOML_B200_GGUF_DECLARE_UMMA_Q(mxfp4)
+DINOML_B200_GGUF_DECLARE_UMMA_Q(nvfp4)
 DINOML_B200_GGUF_DECLARE_SIMT_Q(q4_0)
 DINOML_B200_GGUF_DECLARE_SIMT_Q(q5_k)
 DINOML_B200_GGUF_DECLARE_SIMT_Q(q2_k)

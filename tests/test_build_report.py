@@ -17,8 +17,8 @@ HOT = [
     ("ptxas_gemv_q6k_mma.log", "gemv_q6k_mma_kernelI13__nv_bfloat16Li1ELi8ELi6ELb0ELb0ELb0E", 256, 2, 0),
     ("ptxas_gemv_stream.log", "gemv_stream_kernelILi12E13__nv_bfloat16Li1ELi1ELi4ELb0E", 320, 2, 0),      # persistent GEMV, Q4_K, configuration 4
     ("ptxas_gemv_stream.log", "gemv_stream_kernelILi14E13__nv_bfloat16Li1ELi1ELi3ELb0E", 320, 2, 0),      # persistent GEMV, Q6_K
-    ("ptxas_umma_gemm.log", "gemm_umma_kernelILi14E13__nv_bfloat16Li256ELb0E", 608, 1, 64),                # BASELINE config 3, M = 512
-    ("ptxas_umma_gemm.log", "gemm_umma_kernelILi12E13__nv_bfloat16Li64ELb0E", 608, 1, 64),
+    ("ptxas_umma_gemm_q6_k.log", "gemm_umma_kernelILi14E13__nv_bfloat16Li256ELb0E", 608, 1, 64),                # BASELINE config 3, M = 512
+    ("ptxas_umma_gemm_q4_k.log", "gemm_umma_kernelILi12E13__nv_bfloat16Li64ELb0E", 608, 1, 64),
 ]
 
 
