@@ -594,7 +594,7 @@ def run_single(args):
                                                           "tflops": 2.0 * m * nn * kk / b["us_per_launch"] / 1e6}
     extras["dequant"] = {f"{q}_{dt}": bench_dequant(q, nn, kk, dt, extra_steps, extra_warm)
                          for (q, nn, kk) in (("Q4_K", 11008, 4096), ("Q6_K", 4096, 14336), ("Q8_0", 4096, 4096)) for dt in ("float16", "float32")}
-    # the six further types of the reference prototype: dequantizer and CUDA-core GEMV on a [4096 x 4096] weight
+    # the six further types of the reference prototype: dequantizer, decode GEMV and (where built) prefill GEMM on a [4096 x 4096] weight
     extras["further_qtypes_4096x4096"] = {}
     for q in ("Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4"):
         dq = bench_dequant(q, 4096, 4096, "float16", extra_steps, extra_warm)
@@ -603,6 +603,10 @@ def run_single(args):
                                                  "gemv_m1_us": gv["us_per_launch"], "gemv_m1_weight_gbs": gv["weight_bytes"] / gv["us_per_launch"] / 1e3,
                                                  "gemv_m1_frac_of_measured_hbm": gv["weight_bytes"] / gv["us_per_launch"] / 1e3 / peaks["hbm_gbs"],
                                                  "variant": gv["variant"]}
+        if q in ("Q4_0", "Q5_K", "MXFP4", "NVFP4"):      # the four with a tcgen05 GEMM: prefill on the same weight
+            pf = bench_gemm(q, 4096, 4096, 512, extra_steps, extra_warm, l2)
+            extras["further_qtypes_4096x4096"][q].update({"gemm_m512_us": pf["us_per_launch"], "gemm_m512_variant": pf["variant"],
+                                                          "gemm_m512_tflops": 2.0 * 512 * 4096 * 4096 / pf["us_per_launch"] / 1e6})
     extras["dual_gate_up_q4k_14336x4096"] = {f"m{m}": bench_dual(14336, 4096, m, extra_steps, extra_warm, l2) for m in (1, 16)}
     extras["cfg5_ffn_1gpu"] = {f"m{m}": v for m, v in bench_ffn_1gpu((1, 16, 256), extra_steps, extra_warm, l2).items()}
     try:
