@@ -1,5 +1,5 @@
-// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations: Q4_K and Q6_K weights on tensor cores,
-// and the six further block layouts (Q4_0, Q5_K, Q2_K, Q3_K, MXFP4, NVFP4) on the same data path with fp32 FMA arithmetic.
+// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations: Q4_K, Q5_K, Q6_K, Q4_0 and MXFP4 weights on
+// tensor cores, and three further block layouts (Q2_K, Q3_K, NVFP4) on the same data path with fp32 FMA arithmetic.
 //
 // C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), W streamed once from HBM as packed GGUF blocks (Q4_K 144 B, Q6_K 210 B per
 // 256 weights; Q6_K needs K % 2048 == 0 so that every row piece starts on a 16-byte boundary, other K stay with the tile
@@ -63,7 +63,37 @@ template <> struct Geom<QTYPE_Q2_K> : GenericGeom<84> {};
 template <> struct Geom<QTYPE_Q3_K> : GenericGeom<110> {};
 template <> struct Geom<QTYPE_MXFP4> : GenericGeom<8 * 17> {};
 template <> struct Geom<QTYPE_NVFP4> : GenericGeom<4 * 36> {};
-template <int QT> constexpr bool is_generic() { return QT != QTYPE_Q4_K && QT != QTYPE_Q6_K && QT != QTYPE_Q5_K; }
+// Q4_0 and MXFP4 (32-weight blocks: a scale and 16 bytes of nibbles) run on tensor cores like Q4_K; Q2_K, Q3_K and NVFP4 are
+// decoded value by value.
+template <int QT> constexpr bool is_blk32() { return QT == QTYPE_Q4_0 || QT == QTYPE_MXFP4; }
+template <int QT> constexpr bool is_generic() { return QT != QTYPE_Q4_K && QT != QTYPE_Q6_K && QT != QTYPE_Q5_K && !is_blk32<QT>(); }
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {     // selector bit 3 of a nibble: replicate the byte's sign bit
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+// Eight FP4 (e2m1) codes of one 32-bit word -> their exact values as 16-bit MMA operand pairs: lo01 / lo23 = the low nibbles of
+// bytes (0, 1) / (2, 3), hi01 / hi23 = the high nibbles.  Magnitudes come from byte look-up tables held in two registers
+// (prmt with the codes as selector), the sign bit is OR-ed in.  No offset, no rounding: every e2m1 value is a 16-bit float.
+template <typename T>
+__device__ __forceinline__ void fp4x8_operands(uint32_t w, uint32_t& lo01, uint32_t& lo23, uint32_t& hi01, uint32_t& hi23) {
+  const uint32_t m = w & 0x77777777u, w4 = w << 4;
+  // sign of [b0.lo, b0.hi, b1.lo, b1.hi] and of [b2.lo, b2.hi, b3.lo, b3.hi] on bit 7 of a byte each
+  const uint32_t sa = prmt(w4, w, 0xD9C8u) & 0x80808080u, sb = prmt(w4, w, 0xFBEAu) & 0x80808080u;
+  if constexpr (std::is_same<T, __half>::value) {
+    // 0, .5, 1, 1.5, 2, 3, 4, 6 as fp16: high bytes 00 38 3C 3E 40 42 44 46, low bytes zero
+    const uint32_t ha = prmt(0x3E3C3800u, 0x46444240u, m) | sa, hb = prmt(0x3E3C3800u, 0x46444240u, m >> 16) | sb;
+    lo01 = prmt(ha, 0u, 0x2404u); hi01 = prmt(ha, 0u, 0x3414u);
+    lo23 = prmt(hb, 0u, 0x2404u); hi23 = prmt(hb, 0u, 0x3414u);
+  } else {
+    // as bf16: 0000 3F00 3F80 3FC0 4000 4040 4080 40C0
+    const uint32_t ha = prmt(0x3F3F3F00u, 0x40404040u, m) | sa, hb = prmt(0x3F3F3F00u, 0x40404040u, m >> 16) | sb;
+    const uint32_t la = prmt(0xC0800000u, 0xC0804000u, m), lb = prmt(0xC0800000u, 0xC0804000u, m >> 16);
+    lo01 = prmt(la, ha, 0x6240u); hi01 = prmt(la, ha, 0x7351u);
+    lo23 = prmt(lb, hb, 0x6240u); hi23 = prmt(lb, hb, 0x7351u);
+  }
+}
 
 // 8 consecutive activations as floats.
 template <typename T> __device__ __forceinline__ void x8_to_float(const uint4 v, float (&x)[8]);
@@ -103,7 +133,8 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   constexpr int NCW = NG * kGroupWarps;
   constexpr int MC = MXC == 1 ? 1 : 2;             // accumulator columns a lane keeps
   constexpr int kSbBytes = Geom<QT>::kSbBytes, kPitch = Geom<QT>::kPitch, kStageBytes = kRows * kPitch;
-  constexpr bool kMinTerm = QT == QTYPE_Q4_K || QT == QTYPE_Q5_K;      // Q4_K / Q5_K fold their mins and the operand offset against activation sums; Q6_K has neither
+  constexpr bool kB32 = is_blk32<QT>();            // Q4_0 / MXFP4: one scale per 32 weights, two MMAs per block
+  constexpr bool kMinTerm = QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0;   // these fold their mins / offsets against activation sums; Q6_K and MXFP4 have none
   constexpr bool kQ5 = QT == QTYPE_Q5_K;           // Q4_K arithmetic plus the fifth bit of every quant
   constexpr int kQsOff = kQ5 ? 48 : 16;            // where the nibbles start inside a block
   constexpr bool kGeneric = is_generic<QT>();      // decoded value by value (decode8), fp32 FMA, no tensor cores
@@ -386,6 +417,77 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
           }
         }
       }
+    } else if (!PROBE && sb < nsb && kB32) {
+      if constexpr (kB32) {
+        constexpr int BB = QT == QTYPE_Q4_0 ? 18 : 17, QOFF = BB - 16;       // block bytes, where its 16 nibble bytes start
+        const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
+        {  // lane pair (srow, shalf): the scales of blocks 4*shalf .. +3 of row srow -> shared memory; Q4_0's offset folded against X
+          const uint8_t* sp = st + srow * kPitch + 4 * shalf * BB;
+          float4 dsv;
+          float* dsf = reinterpret_cast<float*>(&dsv);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if constexpr (QT == QTYPE_Q4_0) dsf[i] = half_bits_to_float(*reinterpret_cast<const uint16_t*>(sp + BB * i));
+            else dsf[i] = __fmul_rn(e8m0_half(sp[BB * i]), 2.f);             // 2^(e - 127): the operands are the e2m1 values themselves
+          }
+          *reinterpret_cast<float4*>(&sS[cw][srow][4 * shalf]) = dsv;
+          if constexpr (kMinTerm) {
+            constexpr float kOff = MT::kMagic + 8.f;                          // operand = MAGIC + q, weight = d * (q - 8)
+#pragma unroll
+            for (int c = 0; c < MXC; ++c) {
+              const float4 X = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 8 + 4 * shalf]);
+              xt[c] = fmaf(kOff * dsf[0], X.x, xt[c]);
+              xt[c] = fmaf(kOff * dsf[1], X.y, xt[c]);
+              xt[c] = fmaf(kOff * dsf[2], X.z, xt[c]);
+              xt[c] = fmaf(kOff * dsf[3], X.w, xt[c]);
+            }
+          }
+        }
+        __syncwarp();
+        const float4 dsa0 = *reinterpret_cast<const float4*>(&sS[cw][g][0]);
+        const float4 dsa1 = *reinterpret_cast<const float4*>(&sS[cw][g][4]);
+        const float4 dsb0 = *reinterpret_cast<const float4*>(&sS[cw][g + 8][0]);
+        const float4 dsb1 = *reinterpret_cast<const float4*>(&sS[cw][g + 8][4]);
+        const float ds_a[8] = {dsa0.x, dsa0.y, dsa0.z, dsa0.w, dsa1.x, dsa1.y, dsa1.z, dsa1.w};
+        const float ds_b[8] = {dsb0.x, dsb0.y, dsb0.z, dsb0.w, dsb1.x, dsb1.y, dsb1.z, dsb1.w};
+        // Byte j of a block holds weight j (low nibble) and weight 16 + j (high nibble).  Lane t takes bytes 4t .. 4t+3 of rows g
+        // and g + 8: its low nibbles are weights 4t .. 4t+3 (first MMA of the block: K slots 2t, 2t+1 and 2t+8, 2t+9), its high
+        // nibbles weights 16 + 4t .. (second MMA); the activations follow the same order (two 8-byte loads per block).
+        const uint8_t* r0 = st + g * kPitch + 4 * t;
+        const uint8_t* r1 = r0 + 8 * kPitch;
+        const T* xs = xbase + 4 * t + sb * 256;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const int o = BB * b + QOFF, oa = o & ~3, sh = 8 * (o & 3);         // constants after unrolling; blocks are 1- / 2-byte aligned
+          uint32_t w0 = *reinterpret_cast<const uint32_t*>(r0 + oa), w1 = *reinterpret_cast<const uint32_t*>(r1 + oa);
+          if (sh != 0) {
+            w0 = __funnelshift_r(w0, *reinterpret_cast<const uint32_t*>(r0 + oa + 4), sh);
+            w1 = __funnelshift_r(w1, *reinterpret_cast<const uint32_t*>(r1 + oa + 4), sh);
+          }
+          uint32_t a_lo[4], a_hi[4];
+          if constexpr (QT == QTYPE_Q4_0) {
+            const uint32_t l0 = w0 & 0x0f0f0f0fu, h0 = (w0 >> 4) & 0x0f0f0f0fu, l1 = w1 & 0x0f0f0f0fu, h1 = (w1 >> 4) & 0x0f0f0f0fu;
+            a_lo[0] = MT::fix(__byte_perm(l0, MT::kMagicBytes, 0x4140)); a_lo[1] = MT::fix(__byte_perm(l1, MT::kMagicBytes, 0x4140));
+            a_lo[2] = MT::fix(__byte_perm(l0, MT::kMagicBytes, 0x4342)); a_lo[3] = MT::fix(__byte_perm(l1, MT::kMagicBytes, 0x4342));
+            a_hi[0] = MT::fix(__byte_perm(h0, MT::kMagicBytes, 0x4140)); a_hi[1] = MT::fix(__byte_perm(h1, MT::kMagicBytes, 0x4140));
+            a_hi[2] = MT::fix(__byte_perm(h0, MT::kMagicBytes, 0x4342)); a_hi[3] = MT::fix(__byte_perm(h1, MT::kMagicBytes, 0x4342));
+          } else {
+            fp4x8_operands<T>(w0, a_lo[0], a_lo[2], a_hi[0], a_hi[2]);
+            fp4x8_operands<T>(w1, a_lo[1], a_lo[3], a_hi[1], a_hi[3]);
+          }
+          const uint2 xa = __ldg(reinterpret_cast<const uint2*>(xs + 32 * b));
+          const uint2 xb = __ldg(reinterpret_cast<const uint2*>(xs + 32 * b + 16));
+          float acc[4];
+          MT::mma_c(acc, a_lo, xa.x, xa.y, zero4);
+          MT::mma(acc, a_hi, xb.x, xb.y);
+          res[0][0] = fmaf(ds_a[b], acc[0], res[0][0]);
+          res[0][2] = fmaf(ds_b[b], acc[2], res[0][2]);
+          if (MC == 2) {
+            res[0][1] = fmaf(ds_a[b], acc[1], res[0][1]);
+            res[0][3] = fmaf(ds_b[b], acc[3], res[0][3]);
+          }
+        }
+      }
     } else if (!PROBE && sb < nsb && QT == QTYPE_Q6_K) {
       if constexpr (QT == QTYPE_Q6_K) {
         // row pitch and stage size are multiples of 4, so a block's phase against a word boundary is that of wq * 210
@@ -396,7 +498,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
         else
           q6k_superblock<T, 1, MC, Q6_ALIGNED>(st + srow * kPitch, st + g * kPitch, st + (g + 8) * kPitch, sS[cw], xr, sb, lane, res);
       }
-    } else if (!PROBE && sb < nsb) {
+    } else if (!PROBE && sb < nsb && !kB32) {
       const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
       {  // lane pair (srow, shalf): 4 sub-block scales -> ds to shared memory, min/MAGIC term folded against X
         const uint4 hdr = *reinterpret_cast<const uint4*>(st + srow * kPitch);
@@ -532,7 +634,7 @@ static int stream_scratch(cudaStream_t stream, Scratch* out) {
 template <int QT, typename T, int MXC, int NG, int D, bool PROBE = false>
 static int launch_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int ctas_per_sm, const PeerOut& peers,
                           cudaStream_t s, int mode = 3) {     // mode: bit 0 = walk downwards, bit 1 = split at unit granularity
-  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + ((QT == QTYPE_Q4_K || QT == QTYPE_Q5_K) ? size_t(k / 32) * MXC * sizeof(float) : 0);
+  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + ((QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0) ? size_t(k / 32) * MXC * sizeof(float) : 0);
   if (smem > 216 * 1024) return RC_RANGE;            // + up to 9 KB of static shared memory, under the 227 KB per CTA
   int* status = stream_status_ptr();
   if (status == nullptr) return RC_LAUNCH;

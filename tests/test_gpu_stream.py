@@ -26,7 +26,7 @@ def _configs():
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
-@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q5_K"])
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4"])
 def test_stream_gemv_against_oracle(dtype, qtype):
     dev = torch.device("cuda:0")
     shapes = [(1, 16, 256), (1, 1000, 1024), (2, 50, 512), (3, 129, 4096), (4, 128, 4096), (5, 4000, 2048), (7, 33, 768), (8, 64, 2048),
@@ -34,6 +34,9 @@ def test_stream_gemv_against_oracle(dtype, qtype):
     if qtype == "Q6_K":                                   # 16-byte row pieces need K % 2048 == 0; other K stay with the tile kernel
         assert not kernels.variant_supports("stream", "Q6_K", dtype, 1, 64, 1024)
         shapes = [(m, n, -(-k // 2048) * 2048) for (m, n, k) in shapes] + [(1, 4096, 14336), (4, 300, 14336)]
+    if qtype == "MXFP4":                                  # 136 bytes per 256 weights: 16-byte rows need K % 512 == 0
+        assert not kernels.variant_supports("stream", "MXFP4", dtype, 1, 64, 768)
+        shapes = [(m, n, -(-k // 512) * 512) for (m, n, k) in shapes]
     for (m, n, k) in shapes:
         blocks = S.random_blocks(qtype, n, k, seed=2500 + m + n)
         bq = torch.from_numpy(blocks).to(dev)
@@ -70,12 +73,12 @@ def test_stream_gemv_repeated_launches_are_bit_identical():
         assert float((outs[0].float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
 
 
-@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q5_K"])
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4"])
 def test_stream_gemv_bias_gated_and_scatter_epilogues(qtype):
     dev = torch.device("cuda:0")
     lib = _native.lib()
     k = 2048
-    qv = {"Q4_K": 12, "Q6_K": 14, "Q5_K": 13}[qtype]
+    qv = {"Q4_K": 12, "Q6_K": 14, "Q5_K": 13, "Q4_0": 2, "MXFP4": 39}[qtype]
     for (m, n) in [(1, 104), (2, 64), (4, 200), (8, 48), (1, 3000)]:
         b0 = S.random_blocks(qtype, n, k, seed=2700 + n)
         b1 = S.random_blocks(qtype, n, k, seed=2800 + n)
@@ -122,9 +125,9 @@ def test_stream_variant_refusals():
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
-@pytest.mark.parametrize("qtype", ["Q4_0", "Q2_K", "Q3_K", "MXFP4", "NVFP4"])
+@pytest.mark.parametrize("qtype", ["Q2_K", "Q3_K", "NVFP4"])
 def test_stream_gemv_further_qtypes(dtype, qtype):
-    """Five further layouts on the persistent data path (values decoded 8 at a time, fp32 FMA): against the oracle and
+    """Three further layouts on the persistent data path (values decoded 8 at a time, fp32 FMA): against the oracle and
     against the simt kernel, which decodes the same values; bias and the gated epilogue; shapes whose rows are not 16-byte
     multiples are refused (they stay with the simt kernel)."""
     dev = torch.device("cuda:0")
@@ -158,7 +161,7 @@ def test_stream_gemv_further_qtypes(dtype, qtype):
     assert oracle.max_errors(refg, yg.float().cpu().numpy())[2] <= (2e-2 if dtype == "bfloat16" else 2e-3)
     assert kernels.device_status() == 0
     # rows that are not multiples of 16 bytes, other configurations, M > 8
-    bad_k = {"Q2_K": 768, "Q3_K": 1024, "MXFP4": 768}.get(qtype)
+    bad_k = {"Q2_K": 768, "Q3_K": 1024}.get(qtype)
     if bad_k:
         assert not kernels.variant_supports("stream", qtype, dtype, 1, 64, bad_k)
         xk = torch.zeros(1, bad_k, device=dev, dtype=TDT[dtype])
