@@ -1,5 +1,5 @@
-// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations: Q4_K, Q5_K, Q6_K, Q4_0 and MXFP4 weights on
-// tensor cores, and three further block layouts (Q2_K, Q3_K, NVFP4) on the same data path with fp32 FMA arithmetic.
+// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations: Q4_K, Q5_K, Q6_K, Q4_0, MXFP4 and NVFP4
+// weights on tensor cores, and two further block layouts (Q2_K, Q3_K) on the same data path with fp32 FMA arithmetic.
 //
 // C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), W streamed once from HBM as packed GGUF blocks (Q4_K 144 B, Q6_K 210 B per
 // 256 weights; Q6_K needs K % 2048 == 0 so that every row piece starts on a 16-byte boundary, other K stay with the tile
@@ -63,15 +63,34 @@ template <> struct Geom<QTYPE_Q2_K> : GenericGeom<84> {};
 template <> struct Geom<QTYPE_Q3_K> : GenericGeom<110> {};
 template <> struct Geom<QTYPE_MXFP4> : GenericGeom<8 * 17> {};
 template <> struct Geom<QTYPE_NVFP4> : GenericGeom<4 * 36> {};
-// Q4_0 and MXFP4 (32-weight blocks: a scale and 16 bytes of nibbles) run on tensor cores like Q4_K; Q2_K, Q3_K and NVFP4 are
+// Q4_0 and MXFP4 (32-weight blocks: a scale and 16 bytes of nibbles) and NVFP4 run on tensor cores like Q4_K; Q2_K and Q3_K are
 // decoded value by value.
 template <int QT> constexpr bool is_blk32() { return QT == QTYPE_Q4_0 || QT == QTYPE_MXFP4; }
-template <int QT> constexpr bool is_generic() { return QT != QTYPE_Q4_K && QT != QTYPE_Q6_K && QT != QTYPE_Q5_K && !is_blk32<QT>(); }
+template <int QT> constexpr bool is_generic() { return QT == QTYPE_Q2_K || QT == QTYPE_Q3_K; }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {     // selector bit 3 of a nibble: replicate the byte's sign bit
   uint32_t d;
   asm("prmt.b32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
   return d;
+}
+// 16-bit pair times 16-bit pair (one rounding per element; exact for the FP4 value x block scale products it is used for).
+template <typename T> __device__ __forceinline__ uint32_t mul_pair(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t mul_pair<__half>(uint32_t a, uint32_t b) {
+  const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t mul_pair<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <typename T> __device__ __forceinline__ uint32_t splat_pair(float f);
+template <> __device__ __forceinline__ uint32_t splat_pair<__half>(float f) {
+  const __half2 v = __float2half2_rn(f);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t splat_pair<__nv_bfloat16>(float f) {
+  const __nv_bfloat162 v = __float2bfloat162_rn(f);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 // Eight FP4 (e2m1) codes of one 32-bit word -> their exact values as 16-bit MMA operand pairs: lo01 / lo23 = the low nibbles of
 // bytes (0, 1) / (2, 3), hi01 / hi23 = the high nibbles.  Magnitudes come from byte look-up tables held in two registers
@@ -134,6 +153,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   constexpr int MC = MXC == 1 ? 1 : 2;             // accumulator columns a lane keeps
   constexpr int kSbBytes = Geom<QT>::kSbBytes, kPitch = Geom<QT>::kPitch, kStageBytes = kRows * kPitch;
   constexpr bool kB32 = is_blk32<QT>();            // Q4_0 / MXFP4: one scale per 32 weights, two MMAs per block
+  constexpr bool kNv = QT == QTYPE_NVFP4;          // a ue4m3 scale per 16 weights, multiplied into the operand (exact)
   constexpr bool kMinTerm = QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0;   // these fold their mins / offsets against activation sums; Q6_K and MXFP4 have none
   constexpr bool kQ5 = QT == QTYPE_Q5_K;           // Q4_K arithmetic plus the fifth bit of every quant
   constexpr int kQsOff = kQ5 ? 48 : 16;            // where the nibbles start inside a block
@@ -488,6 +508,49 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
           }
         }
       }
+    } else if (!PROBE && sb < nsb && kNv) {
+      if constexpr (kNv) {
+        // Four blocks of 64 weights (four ue4m3 scales, 32 bytes of nibbles).  Lane t owns sub-block t of every block for rows g
+        // and g + 8: 8 bytes whose byte i holds weights i (low nibble) and 8 + i (high nibble).  Value x scale is exact in either
+        // 16-bit type (2 + 4 significant bits), so the operand is the dequantized weight itself and nothing is applied after
+        // the MMA; the four MMAs of a block take weights 4j .. 4j+3 of every sub-block (K slots 2t, 2t+1, 2t+8, 2t+9), the
+        // activations follow the same order: 16 consecutive values per lane and block.
+        const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
+        const uint8_t* r0 = st + g * kPitch;
+        const uint8_t* r1 = r0 + 8 * kPitch;
+        const T* xs = xbase + sb * 256 + 16 * t;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const uint32_t s0 = splat_pair<T>(__fmul_rn(ue4m3_half(r0[36 * b + t]), 2.f));
+          const uint32_t s1 = splat_pair<T>(__fmul_rn(ue4m3_half(r1[36 * b + t]), 2.f));
+          uint32_t a[4][4];           // [MMA j][fragment register]
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {   // word i: low nibbles -> MMA i, high nibbles -> MMA 2 + i
+            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(r0 + 36 * b + 4 + 8 * t + 4 * i);
+            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(r1 + 36 * b + 4 + 8 * t + 4 * i);
+            fp4x8_operands<T>(w0, a[i][0], a[i][2], a[2 + i][0], a[2 + i][2]);
+            fp4x8_operands<T>(w1, a[i][1], a[i][3], a[2 + i][1], a[2 + i][3]);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            a[j][0] = mul_pair<T>(a[j][0], s0); a[j][2] = mul_pair<T>(a[j][2], s0);
+            a[j][1] = mul_pair<T>(a[j][1], s1); a[j][3] = mul_pair<T>(a[j][3], s1);
+          }
+          const uint4 xa = __ldg(reinterpret_cast<const uint4*>(xs + 64 * b));
+          const uint4 xb = __ldg(reinterpret_cast<const uint4*>(xs + 64 * b + 8));
+          float acc[4];
+          MT::mma_c(acc, a[0], xa.x, xa.y, zero4);
+          MT::mma(acc, a[1], xa.z, xa.w);
+          MT::mma(acc, a[2], xb.x, xb.y);
+          MT::mma(acc, a[3], xb.z, xb.w);
+          res[0][0] += acc[0];
+          res[0][2] += acc[2];
+          if (MC == 2) {
+            res[0][1] += acc[1];
+            res[0][3] += acc[3];
+          }
+        }
+      }
     } else if (!PROBE && sb < nsb && QT == QTYPE_Q6_K) {
       if constexpr (QT == QTYPE_Q6_K) {
         // row pitch and stage size are multiples of 4, so a block's phase against a word boundary is that of wq * 210
@@ -498,7 +561,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
         else
           q6k_superblock<T, 1, MC, Q6_ALIGNED>(st + srow * kPitch, st + g * kPitch, st + (g + 8) * kPitch, sS[cw], xr, sb, lane, res);
       }
-    } else if (!PROBE && sb < nsb && !kB32) {
+    } else if (!PROBE && sb < nsb && !kB32 && !kNv) {
       const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
       {  // lane pair (srow, shalf): 4 sub-block scales -> ds to shared memory, min/MAGIC term folded against X
         const uint4 hdr = *reinterpret_cast<const uint4*>(st + srow * kPitch);
