@@ -42,9 +42,10 @@ extern "C" {
 enum DinoB200GgufVariant {
   DINOML_B200_GGUF_VARIANT_AUTO = 0,   /* shape-guarded dispatch: stream / mma for small M, umma above, simt for float32 */
   DINOML_B200_GGUF_VARIANT_SIMT = 1,   /* CUDA-core warp-per-row, any dtype, any M */
-  DINOML_B200_GGUF_VARIANT_MMA = 2,    /* decode GEMV, one CTA per 16-row tile, M = 1..16, float16 / bfloat16 */
-  DINOML_B200_GGUF_VARIANT_UMMA = 3,   /* prefill GEMM on tcgen05 / TMEM, float16 / bfloat16 */
-  DINOML_B200_GGUF_VARIANT_STREAM = 4, /* persistent decode GEMV: bulk-copy (TMA) ring + mbarriers, M = 1..8 */
+  DINOML_B200_GGUF_VARIANT_MMA = 2,    /* decode GEMV, one CTA per 16-row tile, M = 1..16, float16 / bfloat16; Q8_0, Q4_K, Q6_K */
+  DINOML_B200_GGUF_VARIANT_UMMA = 3,   /* prefill GEMM on tcgen05 / TMEM, M >= 9, float16 / bfloat16; every type but Q2_K, Q3_K */
+  DINOML_B200_GGUF_VARIANT_STREAM = 4, /* persistent decode GEMV: bulk-copy (TMA) ring + mbarriers, M = 1..8; every type but Q8_0
+                                          (Q2_K, Q3_K with fp32 arithmetic, the others on tensor cores) */
 };
 #define DINOML_B200_GGUF_VARIANT_CODE(family, config) ((family) | ((config) << 8))
 
