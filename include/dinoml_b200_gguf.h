@@ -93,13 +93,15 @@ DINOML_B200_API int dinoml_b200_gguf_variant_supports(int family, int qtype, int
  * No counterpart in the reference.  For callers that are not allowed to allocate device memory - a plugin running
  * inside a host that has already handed every byte of HBM to its own arena (so cudaMalloc would fail), or a serving
  * loop that bans cudaMalloc / cudaFree on its hot path because they can stall the whole device.  It is the tensor-core
- * GEMM of dinoml_b200_gguf_gemm_rcr(variant = UMMA) - same shapes (m >= 17, Q4_K / Q6_K / Q8_0, K % 256 == 0, float16 / bfloat16), same
+ * GEMM of dinoml_b200_gguf_gemm_rcr(variant = UMMA) - same shapes (m >= 17, the tcgen05 kernel's weight types, K % 256 == 0, float16 / bfloat16), same
  * arguments minus `variant`, same results - except that its partial tiles (fp32 sums of K ranges that the kernel's
  * stream-K work split cut between SMs) and its flag / status words live in a 16 MiB array plus a 4 KiB one that is part of the library image on every GPU that loads it (dinoml_b200_gguf_prealloc_scratch_bytes()),
  * and that it calls no cudaMalloc, cudaFree or allocating library routine.  The caller still provides a, b_quant,
  * bias and c.  A problem whose partial sums do not fit is refused with code 8 and a message naming both sizes.
- * The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device current); make
- * that first call before starting any stream capture.  All calls on a device share the one array: the kernel
+ * The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device current); with the
+ * CUDA runtime's lazy module loading that is also when the driver places the library's device image (kernel code and these
+ * arrays) on that GPU - module loading, not an allocation call, but free device memory drops by the image size then and
+ * never again.  Make that first call at start-up, before any stream capture.  All calls on a device share the one array: the kernel
  * overwrites the part it uses before reading it back and lowers every flag it raised, so nothing needs clearing
  * between calls, but two calls that overlap on the GPU (different streams, no dependency) race on it - serialize
  * them. */

@@ -47,6 +47,12 @@ def _run_pair(lib, qtype, m, n, k, seed, bias):
     # needs partial-tile scratch (the ordinary entry point grows a cudaMalloc'ed workspace for it)
     need = lib.dinoml_b200_gguf_gemm_rcr_workspace(q.value, BF16, m, n, k, UMMA)
     assert need > 0
+    # the first call on a device makes the driver place the library's device image (kernel code, the static scratch) on the GPU -
+    # lazy module loading, which the documentation tells callers to get over with at start-up: warm up, then measure
+    assert lib.dinoml_b200_gguf_gemm_rcr_prealloc(x.data_ptr(), w.data_ptr(), bp, got.data_ptr(), q.value, BF16, m, n, k, stream) == 0
+    torch.cuda.synchronize()
+    got.fill_(float("nan"))
+    torch.cuda.synchronize()
     free_before = torch.cuda.mem_get_info()[0]
     rc = lib.dinoml_b200_gguf_gemm_rcr_prealloc(x.data_ptr(), w.data_ptr(), bp, got.data_ptr(), q.value, BF16, m, n, k, stream)
     assert rc == 0, _native.last_error()
