@@ -664,6 +664,9 @@ PROFILE_CASES = {  # name -> (qtype, n, k, m, variant, weight copies): small, ea
     "gemm_umma_q4k_m256": ("Q4_K", 11008, 4096, 256, "umma", 6),
     "gemm_umma_q8_0_m512": ("Q8_0", 4096, 14336, 512, "umma", 3),
     "gemv_q8_0_m1": ("Q8_0", 4096, 4096, 1, "mma", 12),
+    "gemm_umma_mxfp4_m512": ("MXFP4", 4096, 14336, 512, "umma", 4),
+    "gemv_stream_mxfp4_m1": ("MXFP4", 11008, 4096, 1, "stream", 6),
+    "gemv_stream_nvfp4_m1": ("NVFP4", 11008, 4096, 1, "stream", 6),
     "dequant_q4k_f16": ("Q4_K", 11008, 4096, 0, "dequant", 3),
 }
 
