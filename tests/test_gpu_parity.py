@@ -114,6 +114,47 @@ def test_gemm_further_qtypes(dev, qtype, dtype):
         kernels.gemm_rcr(x, torch.from_numpy(blocks).to(dev), qtype, variant="mma")
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("qtype", ["MXFP4", "NVFP4"])
+def test_fp4_scale_codes_across_their_range(dev, qtype, dtype):
+    """The tensor-core paths build their operands from the scale CODES: e8m0 exponents from the subnormal codes 0 / 1 up to
+    large ones; ue4m3 zero, subnormals (exponent field 0), the largest values, 0x7f (decodes to 0) and codes with the unused
+    top bit set.  One class of codes per weight row, checked row by row (a whole-matrix norm would only see the large rows);
+    rows whose results lie below the output type's normal range are only required to be finite."""
+    q = qtype_of(qtype)
+    n, k = 64, 2048
+    rng = np.random.Generator(np.random.PCG64(4101))
+    blocks = S.random_blocks(qtype, n, k, seed=4100).reshape(n, -1, q.block_bytes).copy()
+    if qtype == "MXFP4":
+        classes = [[0], [1], [2, 3], [30, 31], [90, 91], [108, 110], [117, 119, 122], [127, 128], [131, 132]]
+        for r in range(n):
+            blocks[r, :, 0] = rng.choice(classes[r % len(classes)], size=blocks.shape[1])
+    else:
+        classes = [[0x00], [1, 2, 3, 4, 5, 6, 7], [8, 9, 15], [0x30, 0x33, 0x38], [0x70, 0x77, 0x7e], [0x7f], [0x7f, 0x38], [0xb0, 0xb8, 0x80, 0xff]]
+        for r in range(n):
+            blocks[r, :, 0:4] = rng.choice(classes[r % len(classes)], size=(blocks.shape[1], 4))
+    blocks = np.ascontiguousarray(blocks.reshape(n, -1))
+    floor = 1e-30 if dtype == "bfloat16" else 1e-3
+    tol = 2e-2 if dtype == "bfloat16" else 2e-3
+    bq = torch.from_numpy(blocks).to(dev)
+    for (m, variant) in [(3, "simt"), (3, "stream"), (1, "stream"), (8, "stream:2"), (20, "umma"), (200, "umma"), (20, "auto")]:
+        xf = (S.random_activations(m, k, 4200 + m, "float32") * 0.05).astype(np.float32)
+        x = torch.from_numpy(xf).to(dev).to(TDT[dtype])
+        ref = oracle.gemm_quant(x.float().cpu().numpy(), blocks, qtype, n, k)
+        got = kernels.gemm_rcr(x, bq, qtype, variant=variant).float().cpu().numpy()
+        assert kernels.device_status() == 0
+        assert np.isfinite(got).all(), (qtype, dtype, variant, m)
+        checked = 0
+        for r in range(n):
+            top = float(np.abs(ref[:, r]).max())
+            if top < floor:
+                continue
+            checked += 1
+            err = float(np.abs(got[:, r] - ref[:, r]).max())
+            assert err <= tol * top, (qtype, dtype, variant, m, r, err, top)
+        assert checked >= n // 4, (qtype, dtype, variant, checked)
+
+
 def _activations(m, k, seed, dtype, dev):
     x = S.random_activations(m, k, seed, "float32")
     xt = torch.from_numpy(x).to(dev).to(TDT[dtype])
