@@ -95,13 +95,9 @@ int select_variant(int qtype, int dtype, int m, int n, int k) {
       tile_kernel = 2 * tiles <= sms;
     } else if (qtype == QTYPE_Q6_K && m >= 3) {
       tile_kernel = weights < (int64_t(32) << 20);
-    } else if (qtype == QTYPE_Q2_K || qtype == QTYPE_Q3_K) {
-      // fp32 decode on the persistent data path: [4096 x 4096], M = 1 / 4: NVFP4 14.4 / 19.5 us against 20.6 / 24.9 on the simt
-      // kernel; Q2_K and Q3_K only win from M = 2 (M = 4: 16.1 / 24.0 us against 19.9 / 26.9; M = 1: 16.2 / 24.2 against 14.6 / 21.9).
-      // Q5_K, Q4_0 and MXFP4 run on tensor cores there ([4096 x 4096], M = 1 / 8: Q4_0 5.3 / 10.1 us, MXFP4 6.0 / 7.9 us, against
-      // 15.4 / 32.8 and 16.8 / 37.9 on the simt kernel).
-      tile_kernel = m == 1;
     }
+    // The further types run on tensor cores there too ([4096 x 4096], M = 1 / 8: Q4_0 5.3 / 10.1 us, MXFP4 6.0 / 7.9 us, NVFP4 6.4 / 7.4 us
+    // against 15.4 / 32.8, 16.8 / 37.9 and 20.5 / 36.0 on the simt kernel).
     if (!tile_kernel) return DINOML_B200_GGUF_VARIANT_STREAM;
   }
   // M = 9..16 is served by both tensor-core kernels: the tcgen05 one costs the same whatever M is (about 8.5 us at least),

@@ -1,5 +1,5 @@
-// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations: Q4_K, Q5_K, Q6_K, Q4_0, MXFP4 and NVFP4
-// weights on tensor cores, and two further block layouts (Q2_K, Q3_K) on the same data path with fp32 FMA arithmetic.
+// Persistent decode GEMV ("stream" variant), M = 1..8, float16 / bfloat16 activations, tensor cores: Q4_K, Q5_K, Q6_K, Q4_0, Q2_K,
+// Q3_K, MXFP4 and NVFP4 weights.
 //
 // C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), W streamed once from HBM as packed GGUF blocks (Q4_K 144 B, Q6_K 210 B per
 // 256 weights; Q6_K needs K % 2048 == 0 so that every row piece starts on a 16-byte boundary, other K stay with the tile
@@ -63,10 +63,10 @@ template <> struct Geom<QTYPE_Q2_K> : GenericGeom<84> {};
 template <> struct Geom<QTYPE_Q3_K> : GenericGeom<110> {};
 template <> struct Geom<QTYPE_MXFP4> : GenericGeom<8 * 17> {};
 template <> struct Geom<QTYPE_NVFP4> : GenericGeom<4 * 36> {};
-// Q4_0 and MXFP4 (32-weight blocks: a scale and 16 bytes of nibbles) and NVFP4 run on tensor cores like Q4_K; Q2_K and Q3_K are
-// decoded value by value.
+// Q4_0 and MXFP4 (32-weight blocks: a scale and 16 bytes of nibbles), NVFP4, Q2_K and Q3_K run on tensor cores like Q4_K.
 template <int QT> constexpr bool is_blk32() { return QT == QTYPE_Q4_0 || QT == QTYPE_MXFP4; }
-template <int QT> constexpr bool is_generic() { return QT == QTYPE_Q2_K || QT == QTYPE_Q3_K; }
+template <int QT> constexpr bool is_q23() { return QT == QTYPE_Q2_K || QT == QTYPE_Q3_K; }     // 2- / 3-bit quants, a scale per 16 weights
+template <int QT> constexpr bool is_generic() { return false; }    // the value-by-value fp32 branch (decode8 + FMA) serves no type any more
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {     // selector bit 3 of a nibble: replicate the byte's sign bit
   uint32_t d;
@@ -154,7 +154,9 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   constexpr int kSbBytes = Geom<QT>::kSbBytes, kPitch = Geom<QT>::kPitch, kStageBytes = kRows * kPitch;
   constexpr bool kB32 = is_blk32<QT>();            // Q4_0 / MXFP4: one scale per 32 weights, two MMAs per block
   constexpr bool kNv = QT == QTYPE_NVFP4;          // a ue4m3 scale per 16 weights, multiplied into the operand (exact)
-  constexpr bool kMinTerm = QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0;   // these fold their mins / offsets against activation sums; Q6_K and MXFP4 have none
+  constexpr bool kQ23 = is_q23<QT>();              // Q2_K / Q3_K: one MMA per 16-weight sub-block, offsets folded against 16-wide activation sums
+  constexpr int kXG = kQ23 ? 16 : 32;              // activations per entry of the sum table sX
+  constexpr bool kMinTerm = QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0 || kQ23;   // these fold their mins / offsets against activation sums; Q6_K and the FP4 types have none
   constexpr bool kQ5 = QT == QTYPE_Q5_K;           // Q4_K arithmetic plus the fifth bit of every quant
   constexpr int kQsOff = kQ5 ? 48 : 16;            // where the nibbles start inside a block
   constexpr bool kGeneric = is_generic<QT>();      // decoded value by value (decode8), fp32 FMA, no tensor cores
@@ -167,13 +169,13 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   uint8_t* sW = smem_dyn + kBarBytes;                                         // D x kStageBytes
   Red* sRed = reinterpret_cast<Red*>(sW + size_t(D) * kStageBytes);      // [2]
   float* sX = reinterpret_cast<float*>(sRed + 2);                        // [MXC][k/32]
-  __shared__ __align__(16) float sS[kGeneric ? 1 : NCW][kGeneric ? 1 : kRows][QT == QTYPE_Q6_K ? kQ6ScalePitch : kGeneric ? 4 : 8];   // d * sc per row, sub-block (warp-private scratch)
+  __shared__ __align__(16) float sS[kGeneric ? 1 : NCW][kGeneric ? 1 : kRows][(QT == QTYPE_Q6_K || kQ23) ? kQ6ScalePitch : kGeneric ? 4 : 8];   // d * sc per row, sub-block (warp-private scratch)
   __shared__ float sOut[kRows * MXC];                                    // epilogue warp scratch
   __shared__ int s_abort;
   static_assert((2 * D + 4) * 8 <= kBarBytes, "barrier area");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nsb = k >> 8, nsub = k >> 5;
+  const int nsb = k >> 8, nsub = k / kXG;
   const int nchunks = (nsb + kKC - 1) / kKC;
   const int tiles = (n + kRows - 1) / kRows;
   // this CTA's units [u0, u1) of the tile-major line; walked from u1 - 1 down
@@ -347,9 +349,9 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
     const int c = i / nsub, j = i - c * nsub;
     float s = 0.f;
     if (c < m) {
-      const uint4* px = reinterpret_cast<const uint4*>(x + int64_t(c) * k + int64_t(j) * 32);
+      const uint4* px = reinterpret_cast<const uint4*>(x + int64_t(c) * k + int64_t(j) * kXG);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) s += MT::sum8(__ldg(px + q));
+      for (int q = 0; q < kXG / 8; ++q) s += MT::sum8(__ldg(px + q));
     }
     sX[i] = s;
   }
@@ -508,6 +510,92 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
           }
         }
       }
+    } else if (!PROBE && sb < nsb && kQ23) {
+      if constexpr (kQ23) {
+        // Q2_K: scales[16] (4-bit scale, 4-bit min per 16 weights), qs[64], d, dmin.  Q3_K: hmask[32], qs[64], scales[12] (6-bit), d.
+        // Weight 128*hb + 32*j + l is bits 2j, 2j+1 of qs[32*hb + l] (Q3_K: plus bit 4*hb + j of hmask[l] as a third bit, less 4);
+        // sub-block (hb, j, h16) = its weights l = 16*h16 .. +15, scale index 8*hb + 2*j + h16.  One MMA per sub-block.
+        constexpr int kQs = QT == QTYPE_Q2_K ? 16 : 32;
+        const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
+        {  // lane pair (srow, shalf): the eight sub-block scales of half-block shalf of row srow
+          const uint8_t* blk = st + srow * kPitch;
+          float dsf[8], kk[8];
+          if constexpr (QT == QTYPE_Q2_K) {
+            const float d = half_at(blk + 80), dmin = half_at(blk + 82);
+            const uint32_t* scp = reinterpret_cast<const uint32_t*>(blk + 8 * shalf);   // blocks (84 B) are word aligned, not more
+            const uint32_t sc0 = scp[0], sc1 = scp[1];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t b = ((i < 4 ? sc0 : sc1) >> (8 * (i & 3))) & 0xffu;
+              dsf[i] = d * float(b & 0x0fu);
+              kk[i] = fmaf(MT::kMagic, dsf[i], dmin * float(b >> 4));
+            }
+          } else {
+            const float d = half_at(blk + 108);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              dsf[i] = d * float(q3k_scale(blk + 96, 8 * shalf + i) - 32);
+              kk[i] = (MT::kMagic + 4.f) * dsf[i];                                    // operand = MAGIC + (q + 4)
+            }
+          }
+          *reinterpret_cast<float4*>(&sS[cw][srow][8 * shalf]) = make_float4(dsf[0], dsf[1], dsf[2], dsf[3]);
+          *reinterpret_cast<float4*>(&sS[cw][srow][8 * shalf + 4]) = make_float4(dsf[4], dsf[5], dsf[6], dsf[7]);
+#pragma unroll
+          for (int c = 0; c < MXC; ++c) {
+            const float4 X0 = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 16 + 8 * shalf]);
+            const float4 X1 = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 16 + 8 * shalf + 4]);
+            const float X[8] = {X0.x, X0.y, X0.z, X0.w, X1.x, X1.y, X1.z, X1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xt[c] = fmaf(kk[i], X[i], xt[c]);
+          }
+        }
+        __syncwarp();
+        // Lane t takes bytes 4t .. 4t+3 of every 16-byte run of rows g and g + 8: four weights of each of the four sub-blocks
+        // (j = 0..3) that share those bytes; K slots 2t, 2t+1 and 2t+8, 2t+9 carry them, the activations follow the same order.
+        // Q3_K blocks (110 B) sit 2 bytes off a word boundary in every odd super-block: two aligned loads and a funnel shift.
+        const uint32_t sh = (QT == QTYPE_Q3_K) ? 16u * uint32_t(wq & 1) : 0u;
+        auto word = [&](const uint8_t* p) -> uint32_t {      // 4 bytes at p, p being `sh / 8` bytes past a word boundary
+          if constexpr (QT == QTYPE_Q3_K) {
+            const uint32_t* a = reinterpret_cast<const uint32_t*>(p - (sh >> 3));
+            return __funnelshift_r(a[0], a[1], sh);
+          } else {
+            return *reinterpret_cast<const uint32_t*>(p);
+          }
+        };
+        const uint8_t* r0 = st + g * kPitch + 4 * t;
+        const uint8_t* r1 = r0 + 8 * kPitch;
+        const T* xs = xbase + 4 * t + sb * 256;
+#pragma unroll
+        for (int h16 = 0; h16 < 2; ++h16) {
+          uint32_t hm0 = 0, hm1 = 0;
+          if constexpr (QT == QTYPE_Q3_K) { hm0 = word(r0 + 16 * h16); hm1 = word(r1 + 16 * h16); }
+#pragma unroll
+          for (int hb = 0; hb < 2; ++hb) {
+            const uint32_t w0 = word(r0 + kQs + 32 * hb + 16 * h16), w1 = word(r1 + kQs + 32 * hb + 16 * h16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t n0 = (w0 >> (2 * j)) & 0x03030303u, n1 = (w1 >> (2 * j)) & 0x03030303u;
+              if constexpr (QT == QTYPE_Q3_K) {
+                n0 |= ((hm0 >> (4 * hb + j)) & 0x01010101u) << 2;
+                n1 |= ((hm1 >> (4 * hb + j)) & 0x01010101u) << 2;
+              }
+              const uint32_t a[4] = {MT::fix(__byte_perm(n0, MT::kMagicBytes, 0x4140)), MT::fix(__byte_perm(n1, MT::kMagicBytes, 0x4140)),
+                                     MT::fix(__byte_perm(n0, MT::kMagicBytes, 0x4342)), MT::fix(__byte_perm(n1, MT::kMagicBytes, 0x4342))};
+              const uint2 xa = __ldg(reinterpret_cast<const uint2*>(xs + 128 * hb + 32 * j + 16 * h16));
+              float acc[4];
+              MT::mma_c(acc, a, xa.x, xa.y, zero4);
+              const int idx = 8 * hb + 2 * j + h16;
+              const float da = sS[cw][g][idx], db = sS[cw][g + 8][idx];      // 16 scales per row: read where used, not held in registers
+              res[0][0] = fmaf(da, acc[0], res[0][0]);
+              res[0][2] = fmaf(db, acc[2], res[0][2]);
+              if (MC == 2) {
+                res[0][1] = fmaf(da, acc[1], res[0][1]);
+                res[0][3] = fmaf(db, acc[3], res[0][3]);
+              }
+            }
+          }
+        }
+      }
     } else if (!PROBE && sb < nsb && kNv) {
       if constexpr (kNv) {
         // Four blocks of 64 weights (four ue4m3 scales, 32 bytes of nibbles).  Lane t owns sub-block t of every block for rows g
@@ -561,7 +649,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
         else
           q6k_superblock<T, 1, MC, Q6_ALIGNED>(st + srow * kPitch, st + g * kPitch, st + (g + 8) * kPitch, sS[cw], xr, sb, lane, res);
       }
-    } else if (!PROBE && sb < nsb && !kB32 && !kNv) {
+    } else if (!PROBE && sb < nsb && !kB32 && !kNv && !kQ23) {
       const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
       {  // lane pair (srow, shalf): 4 sub-block scales -> ds to shared memory, min/MAGIC term folded against X
         const uint4 hdr = *reinterpret_cast<const uint4*>(st + srow * kPitch);
@@ -697,7 +785,7 @@ static int stream_scratch(cudaStream_t stream, Scratch* out) {
 template <int QT, typename T, int MXC, int NG, int D, bool PROBE = false>
 static int launch_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int ctas_per_sm, const PeerOut& peers,
                           cudaStream_t s, int mode = 3) {     // mode: bit 0 = walk downwards, bit 1 = split at unit granularity
-  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + ((QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0) ? size_t(k / 32) * MXC * sizeof(float) : 0);
+  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + ((QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0) ? size_t(k / 32) * MXC * sizeof(float) : is_q23<QT>() ? size_t(k / 16) * MXC * sizeof(float) : 0);
   if (smem > 216 * 1024) return RC_RANGE;            // + up to 9 KB of static shared memory, under the 227 KB per CTA
   int* status = stream_status_ptr();
   if (status == nullptr) return RC_LAUNCH;

@@ -27,13 +27,13 @@ SUPPORTED_OPS = ("gemm_rcr", "gemm_rcr_bias") + DUAL_OPS
 VARIANT_CODES = {"simt": 1, "mma": 2, "umma": 3, "stream": 4}
 # Tuning configurations of the persistent GEMV (csrc/gemv_stream.cu): each is a candidate of its own, as the tile / stage /
 # warp entries of the reference's CUTLASS catalogue are (src/dinoml/kernels/providers/cutlass/gemm.py:19-127).
-STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": {"Q4_K": 5, "Q6_K": 4, "Q5_K": 4, "Q4_0": 5, "MXFP4": 5, "NVFP4": 5}, "ctas_per_sm": 1},
-                  2: {"consumer_warps": 16, "ring_slots": {"Q4_K": 6, "Q6_K": 4, "Q5_K": 4, "Q4_0": 6, "MXFP4": 6, "NVFP4": 6}, "ctas_per_sm": 1},
-                  3: {"consumer_warps": 16, "ring_slots": {"Q4_K": 8, "Q6_K": 6, "Q5_K": 6, "Q4_0": 8, "MXFP4": 8, "NVFP4": 8}, "ctas_per_sm": 1},
-                  4: {"consumer_warps": 8, "ring_slots": {"Q4_K": 4, "Q6_K": 3, "Q5_K": 3, "Q4_0": 4, "MXFP4": 4, "NVFP4": 4}, "ctas_per_sm": 2}}
-STREAM_QTYPES = ("Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4", "NVFP4")
+STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": {"Q4_K": 5, "Q6_K": 4, "Q5_K": 4, "Q4_0": 5, "MXFP4": 5, "NVFP4": 5, "Q2_K": 5, "Q3_K": 5}, "ctas_per_sm": 1},
+                  2: {"consumer_warps": 16, "ring_slots": {"Q4_K": 6, "Q6_K": 4, "Q5_K": 4, "Q4_0": 6, "MXFP4": 6, "NVFP4": 6, "Q2_K": 6, "Q3_K": 6}, "ctas_per_sm": 1},
+                  3: {"consumer_warps": 16, "ring_slots": {"Q4_K": 8, "Q6_K": 6, "Q5_K": 6, "Q4_0": 8, "MXFP4": 8, "NVFP4": 8, "Q2_K": 8, "Q3_K": 8}, "ctas_per_sm": 1},
+                  4: {"consumer_warps": 8, "ring_slots": {"Q4_K": 4, "Q6_K": 3, "Q5_K": 3, "Q4_0": 4, "MXFP4": 4, "NVFP4": 4, "Q2_K": 4, "Q3_K": 4}, "ctas_per_sm": 2}}
+STREAM_QTYPES = ("Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K")
 # two further layouts run on the same persistent data path with fp32 arithmetic, in ONE configuration (4)
-STREAM_FP32_QTYPES = ("Q2_K", "Q3_K")
+STREAM_FP32_QTYPES = ()
 # further types the tcgen05 GEMM unpacks (besides Q4_K, Q6_K, Q8_0); MXFP4 and NVFP4 become exact 16-bit operands
 UMMA_MORE_QTYPES = ("Q5_K", "Q4_0", "MXFP4", "NVFP4")
 

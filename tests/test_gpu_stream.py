@@ -26,7 +26,7 @@ def _configs():
 
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
-@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4", "NVFP4"])
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K"])
 def test_stream_gemv_against_oracle(dtype, qtype):
     dev = torch.device("cuda:0")
     shapes = [(1, 16, 256), (1, 1000, 1024), (2, 50, 512), (3, 129, 4096), (4, 128, 4096), (5, 4000, 2048), (7, 33, 768), (8, 64, 2048),
@@ -34,9 +34,10 @@ def test_stream_gemv_against_oracle(dtype, qtype):
     if qtype == "Q6_K":                                   # 16-byte row pieces need K % 2048 == 0; other K stay with the tile kernel
         assert not kernels.variant_supports("stream", "Q6_K", dtype, 1, 64, 1024)
         shapes = [(m, n, -(-k // 2048) * 2048) for (m, n, k) in shapes] + [(1, 4096, 14336), (4, 300, 14336)]
-    if qtype == "MXFP4":                                  # 136 bytes per 256 weights: 16-byte rows need K % 512 == 0
-        assert not kernels.variant_supports("stream", "MXFP4", dtype, 1, 64, 768)
-        shapes = [(m, n, -(-k // 512) * 512) for (m, n, k) in shapes]
+    if qtype in ("MXFP4", "Q2_K", "Q3_K"):                # 136 / 84 / 110 bytes per 256 weights: 16-byte rows need K % 512 / 1024 / 2048 == 0
+        step = {"MXFP4": 512, "Q2_K": 1024, "Q3_K": 2048}[qtype]
+        assert not kernels.variant_supports("stream", qtype, dtype, 1, 64, 768)
+        shapes = [(m, n, -(-k // step) * step) for (m, n, k) in shapes]
     for (m, n, k) in shapes:
         blocks = S.random_blocks(qtype, n, k, seed=2500 + m + n)
         bq = torch.from_numpy(blocks).to(dev)
@@ -73,12 +74,12 @@ def test_stream_gemv_repeated_launches_are_bit_identical():
         assert float((outs[0].float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
 
 
-@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4", "NVFP4"])
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K"])
 def test_stream_gemv_bias_gated_and_scatter_epilogues(qtype):
     dev = torch.device("cuda:0")
     lib = _native.lib()
     k = 2048
-    qv = {"Q4_K": 12, "Q6_K": 14, "Q5_K": 13, "Q4_0": 2, "MXFP4": 39, "NVFP4": 40}[qtype]
+    qv = {"Q4_K": 12, "Q6_K": 14, "Q5_K": 13, "Q4_0": 2, "MXFP4": 39, "NVFP4": 40, "Q2_K": 10, "Q3_K": 11}[qtype]
     for (m, n) in [(1, 104), (2, 64), (4, 200), (8, 48), (1, 3000)]:
         b0 = S.random_blocks(qtype, n, k, seed=2700 + n)
         b1 = S.random_blocks(qtype, n, k, seed=2800 + n)
@@ -124,50 +125,12 @@ def test_stream_variant_refusals():
     assert kernels.variant_supports("stream", "Q4_K", "bfloat16", 8, 32, 512)
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
-@pytest.mark.parametrize("qtype", ["Q2_K", "Q3_K"])
-def test_stream_gemv_further_qtypes(dtype, qtype):
-    """Two further layouts on the persistent data path (values decoded 8 at a time, fp32 FMA): against the oracle and
-    against the simt kernel, which decodes the same values; bias and the gated epilogue; shapes whose rows are not 16-byte
-    multiples are refused (they stay with the simt kernel)."""
+@pytest.mark.parametrize("qtype", ["Q2_K", "Q3_K", "MXFP4"])
+def test_stream_gemv_rows_that_are_not_16_byte_multiples_stay_with_simt(qtype):
     dev = torch.device("cuda:0")
-    bound = 4e-3 if dtype == "bfloat16" else 6e-4
-    for (m, n, k) in [(1, 16, 2048), (1, 1000, 2048), (2, 50, 4096), (3, 129, 2048), (5, 2400, 2048), (8, 64, 6144), (4, 7, 2048), (1, 4096, 4096)]:
-        blocks = S.random_blocks(qtype, n, k, seed=3500 + m + n)
-        bq = torch.from_numpy(blocks).to(dev)
-        x, xf = _x(m, k, 3600 + m, dtype, dev)
-        ref = oracle.gemm_quant(xf, blocks, qtype, n, k)
-        assert kernels.variant_supports("stream", qtype, dtype, m, n, k) and kernels.variant_supports("stream:4", qtype, dtype, m, n, k)
-        for variant in ("stream", "stream:4"):
-            y = kernels.gemm_rcr(x, bq, qtype, variant=variant)
-            assert kernels.device_status() == 0, (variant, m, n, k)
-            _, rel, norm = oracle.max_errors(ref, y.float().cpu().numpy())
-            assert norm <= bound and rel <= (2e-2 if dtype == "bfloat16" else 1e-3), (qtype, dtype, variant, m, n, k, rel, norm)
-        ys = kernels.gemm_rcr(x, bq, qtype, variant="simt")
-        assert float((ys.float() - y.float()).abs().max()) <= 2 * bound * float(np.abs(ref).max())
-        auto = kernels.select_variant(qtype, dtype, m, n, k)
-        assert auto == ("simt" if (m == 1 and qtype in ("Q2_K", "Q3_K")) else "stream"), (qtype, m, auto)
-    # bias and the gated dual epilogue
-    m, n, k = 3, 72, 2048
-    b0, b1 = S.random_blocks(qtype, n, k, seed=3700), S.random_blocks(qtype, n, k, seed=3701)
-    x, xf = _x(m, k, 3702, dtype, dev)
-    bias = torch.linspace(-1, 1, n, device=dev).to(TDT[dtype])
-    yb = kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), qtype, bias, variant="stream")
-    refb = oracle.gemm_quant(xf, b0, qtype, n, k) + bias.float().cpu().numpy()[None, :]
-    assert oracle.max_errors(refb, yb.float().cpu().numpy())[2] <= bound
-    w = kernels.interleave_rows8(torch.from_numpy(b0).to(dev), torch.from_numpy(b1).to(dev))
-    yg = kernels.dual_gemm_rcr(x, w, qtype, "silu", variant="stream")
-    refg = oracle.dual_gemm_quant(xf, b0, b1, qtype, n, k, "silu")
-    assert oracle.max_errors(refg, yg.float().cpu().numpy())[2] <= (2e-2 if dtype == "bfloat16" else 2e-3)
-    assert kernels.device_status() == 0
-    # rows that are not multiples of 16 bytes, other configurations, M > 8
-    bad_k = {"Q2_K": 768, "Q3_K": 1024}.get(qtype)
-    if bad_k:
-        assert not kernels.variant_supports("stream", qtype, dtype, 1, 64, bad_k)
-        xk = torch.zeros(1, bad_k, device=dev, dtype=TDT[dtype])
-        with pytest.raises(RuntimeError):
-            kernels.gemm_rcr(xk, S.random_blocks_torch(qtype, 64, bad_k, 1, dev), qtype, variant="stream")
-        assert kernels.select_variant(qtype, dtype, 1, 64, bad_k) == "simt"
+    bad_k = {"Q2_K": 768, "Q3_K": 1024, "MXFP4": 768}[qtype]
+    assert not kernels.variant_supports("stream", qtype, "bfloat16", 1, 64, bad_k)
+    xk = torch.zeros(1, bad_k, device=dev, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):
-        kernels.gemm_rcr(x, torch.from_numpy(b0).to(dev), qtype, variant="stream:2")
-    assert not kernels.variant_supports("stream", qtype, dtype, 9, n, k)
+        kernels.gemm_rcr(xk, S.random_blocks_torch(qtype, 64, bad_k, 1, dev), qtype, variant="stream")
+    assert kernels.select_variant(qtype, "bfloat16", 1, 64, bad_k) == "simt"
