@@ -603,7 +603,7 @@ def run_single(args):
                                                  "gemv_m1_us": gv["us_per_launch"], "gemv_m1_weight_gbs": gv["weight_bytes"] / gv["us_per_launch"] / 1e3,
                                                  "gemv_m1_frac_of_measured_hbm": gv["weight_bytes"] / gv["us_per_launch"] / 1e3 / peaks["hbm_gbs"],
                                                  "variant": gv["variant"]}
-        if q in ("Q4_0", "Q5_K", "MXFP4", "NVFP4"):      # the four with a tcgen05 GEMM: prefill on the same weight
+        if True:                                         # prefill on the same weight (tcgen05 GEMM)
             pf = bench_gemm(q, 4096, 4096, 512, extra_steps, extra_warm, l2)
             extras["further_qtypes_4096x4096"][q].update({"gemm_m512_us": pf["us_per_launch"], "gemm_m512_variant": pf["variant"],
                                                           "gemm_m512_tflops": 2.0 * 512 * 4096 * 4096 / pf["us_per_launch"] / 1e6})

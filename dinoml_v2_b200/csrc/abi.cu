@@ -378,7 +378,7 @@ int dinoml_b200_gguf_variant_supports(int family, int qtype, int dtype, int m, i
 B200_DEFINE_Q(q8_0, QTYPE_Q8_0)
 B200_DEFINE_Q(q4_k, QTYPE_Q4_K)
 B200_DEFINE_Q(q6_k, QTYPE_Q6_K)
-// the further types: CUDA-core kernel and persistent GEMV for all six, the tcgen05 GEMM for four of them
+// the further types: CUDA-core kernel, persistent GEMV and tcgen05 GEMM for all six
 #define B200_DEFINE_SIMT_Q(q, QT)                                                         \
   B200_DEFINE(q, QT, float32, DINO_F32, simt, DINOML_B200_GGUF_VARIANT_SIMT)              \
   B200_DEFINE(q, QT, float16, DINO_F16, simt, DINOML_B200_GGUF_VARIANT_SIMT)              \
@@ -392,6 +392,8 @@ B200_DEFINE_UMMA_Q(q4_0, QTYPE_Q4_0)
 B200_DEFINE_UMMA_Q(q5_k, QTYPE_Q5_K)
 B200_DEFINE_UMMA_Q(mxfp4, QTYPE_MXFP4)
 B200_DEFINE_UMMA_Q(nvfp4, QTYPE_NVFP4)
+B200_DEFINE_UMMA_Q(q2_k, QTYPE_Q2_K)
+B200_DEFINE_UMMA_Q(q3_k, QTYPE_Q3_K)
 B200_DEFINE_SIMT_Q(q4_0, QTYPE_Q4_0)
 B200_DEFINE_SIMT_Q(q5_k, QTYPE_Q5_K)
 B200_DEFINE_SIMT_Q(q2_k, QTYPE_Q2_K)

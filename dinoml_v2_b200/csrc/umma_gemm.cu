@@ -118,6 +118,8 @@ static int launch_bm(int qtype, int dtype, const void* a, const void* b, const v
     case QTYPE_Q4_0: return launch_q4_0(dtype, a, b, bias, c, m, n, k, pl, sc, peers, s);
     case QTYPE_MXFP4: return launch_mxfp4(dtype, a, b, bias, c, m, n, k, pl, sc, peers, s);
     case QTYPE_NVFP4: return launch_nvfp4(dtype, a, b, bias, c, m, n, k, pl, sc, peers, s);
+    case QTYPE_Q2_K: return launch_q2_k(dtype, a, b, bias, c, m, n, k, pl, sc, peers, s);
+    case QTYPE_Q3_K: return launch_q3_k(dtype, a, b, bias, c, m, n, k, pl, sc, peers, s);
     default: return RC_QTYPE;
   }
 }
@@ -132,6 +134,8 @@ static int super_block_bytes(int qtype) {
     case QTYPE_Q6_K: return 210;
     case QTYPE_Q8_0: return 272;
     case QTYPE_MXFP4: return 136;
+    case QTYPE_Q2_K: return 84;
+    case QTYPE_Q3_K: return 110;
     default: return 0;
   }
 }

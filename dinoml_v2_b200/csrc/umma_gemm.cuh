@@ -1,6 +1,6 @@
 // Fused GGUF prefill GEMM ("umma" variant) on tcgen05 tensor cores with TMEM accumulators, M >= 9.
 //
-// C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), float16 / bfloat16; Q4_K, Q5_K, Q6_K, Q8_0, Q4_0, MXFP4 and NVFP4 weights
+// C[M,N] = A[M,K] * dequant(W[N,K])^T (+ bias), float16 / bfloat16; all nine weight types (Q8_0, Q4_0, Q2_K .. Q6_K, MXFP4, NVFP4)
 // (the kernel template lives in this header; umma_gemm_<type>.cu instantiates it per weight type).
 // Tensor-core bound for M >= 512 (Q6_K 4096x14336: 1248 FLOP per weight byte at M = 512).
 //
@@ -30,7 +30,8 @@
 // finished by the CTA that holds its end: the others leave fp32 partial tiles in a library-owned workspace and raise a
 // flag, the finisher adds them in a fixed order (see Walk below).  No second kernel, bit-reproducible results.
 // The packed-weight tensor map needs weight rows that are multiples of 16 bytes: any K % 256 == 0 for the types whose 256
-// weights take a multiple of 16 bytes, K % 512 == 0 for MXFP4 (136 bytes), K % 2048 == 0 for Q6_K (210 bytes).  Other
+// weights take a multiple of 16 bytes, K % 512 == 0 for MXFP4 (136 bytes), K % 1024 == 0 for Q2_K (84), K % 2048 == 0 for
+// Q6_K (210) and Q3_K (110).  Other
 // shapes are served by the other variants.
 //
 // Every mbarrier wait is bounded: after kSpinLimit polls the waiter records a code in a device status
@@ -245,6 +246,8 @@ template <> struct RawGeom<QTYPE_Q6_K> { static constexpr int kPitch = 240, kSup
 template <> struct RawGeom<QTYPE_Q8_0> { static constexpr int kPitch = 144, kSuper = 272, kBoxes = 2, kSlots = 2; };
 template <> struct RawGeom<QTYPE_Q4_0> { static constexpr int kPitch = 144, kSuper = 144, kBoxes = 1, kSlots = 3; };   // 8 blocks of 18 B
 template <> struct RawGeom<QTYPE_MXFP4> { static constexpr int kPitch = 144, kSuper = 136, kBoxes = 1, kSlots = 3; };  // 8 x 17 B, starts 0 / 8 bytes into its window
+template <> struct RawGeom<QTYPE_Q2_K> { static constexpr int kPitch = 112, kSuper = 84, kBoxes = 1, kSlots = 3; };    // starts 0 / 4 / 8 / 12 bytes into its window
+template <> struct RawGeom<QTYPE_Q3_K> { static constexpr int kPitch = 144, kSuper = 110, kBoxes = 1, kSlots = 3; };   // any even phase, like Q6_K
 template <> struct RawGeom<QTYPE_NVFP4> { static constexpr int kPitch = 144, kSuper = 144, kBoxes = 1, kSlots = 3; };  // 4 blocks of 36 B
 
 // One Q8_0 block (B = 0..7 inside the 256 weights) of a row: 16 of its int8 quants (half LHALF) and its scale.
@@ -268,6 +271,22 @@ __device__ __forceinline__ void q8_to_pairs(uint32_t u, float d256, float c, uin
   const float f3 = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7434));
   p01 = as_u32<typename P::V>(P::pack(fmaf(f0, d256, c), fmaf(f1, d256, c)));
   p23 = as_u32<typename P::V>(P::pack(fmaf(f2, d256, c), fmaf(f3, d256, c)));
+}
+
+// ---- Q2_K (scales[16], qs[64], d, dmin: 84 B) and Q3_K (hmask[32], qs[64], scales[12], d: 110 B).  Weight 128*hb + 32*j + l of a
+// super-block is bits 2j, 2j+1 of qs[32*hb + l] (Q3_K: plus bit 4*hb + j of hmask[l] as a third bit, less 4); its scale index is
+// 8*hb + 2*j + l/16.  Thread (hb, h16) of a row takes the 16 qs bytes l = 16*h16 .. +15 of half-block hb: all four j of them.
+template <int S>
+__device__ __forceinline__ void q2k_fetch(const uint8_t* rowbase, int hb, int h16, uint32_t* qw, uint32_t* scw, uint32_t* tail) {
+  fetch16<S>(rowbase + 16 + 32 * hb + 16 * h16, qw);
+  fetch16<S>(rowbase, scw);            // 16 bytes: 4-bit scale | 4-bit min << 4 per sub-block
+  fetch16<S>(rowbase + 80, tail);      // d, dmin in the first word
+}
+template <int S>
+__device__ __forceinline__ void q3k_fetch(const uint8_t* rowbase, int hb, int h16, uint32_t* qw, uint32_t* scw) {
+  fetch16<S>(rowbase + 32 + 32 * hb + 16 * h16, qw);
+  fetch16<S>(rowbase + 16 * h16, qw + 4);     // the third bits of weights l = 16*h16 .. +15, one bit position per (hb, j)
+  fetch16<S>(rowbase + 96, scw);              // 12 scale bytes, then d
 }
 
 // ---- the 4-bit types with 32-weight blocks (Q4_0: u16 d + 16 bytes of nibbles, 18 B; MXFP4: u8 e + the same, 17 B).
@@ -614,6 +633,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         uint32_t qw[(QT == QTYPE_Q8_0 || QT == QTYPE_Q5_K) ? 16 : 12];
         float dscale = 0.f, dmin = 0.f;
         float sub_scale[4];                   // Q6_K: int8 scales of quads 0..3; Q8_0: d of this thread's four blocks
+        float sub_min[4] = {0.f, 0.f, 0.f, 0.f};   // Q2_K: -dmin * min of the thread's four sub-blocks
         if constexpr (QT == QTYPE_Q8_0) {
           // blocks 4*grp .. 4*grp+3 sit in box grp of the slot; block 2*ls + h feeds half h of stage 2*grp + ls
           const uint8_t* win = rowbase + grp * raw_box_bytes<QT>();
@@ -664,6 +684,44 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
           for (int b = 0; b < 4; ++b)
             sub_scale[b] = QT == QTYPE_Q4_0 ? half_bits_to_float(uint16_t(scw[b] & 0xffffu))
                                             : __fmul_rn(e8m0_half(scw[b] & 0xffu), 2.f * P::kFp4Rest);    // 2^(e - 127), less what k1 already gave
+        } else if constexpr (QT == QTYPE_Q2_K) {
+          uint32_t scw[4], tail[4];
+          switch (((sb * kBlockBytes) & 15) >> 2) {        // 84-byte blocks: the phase inside the window is a multiple of 4
+            case 0: q2k_fetch<0>(rowbase, grp, lhalf, qw, scw, tail); break;
+            case 1: q2k_fetch<2>(rowbase, grp, lhalf, qw, scw, tail); break;
+            case 2: q2k_fetch<4>(rowbase, grp, lhalf, qw, scw, tail); break;
+            default: q2k_fetch<6>(rowbase, grp, lhalf, qw, scw, tail); break;
+          }
+          dscale = half_bits_to_float(uint16_t(tail[0] & 0xffffu));
+          dmin = half_bits_to_float(uint16_t(tail[0] >> 16));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {       // scale byte 8*grp + 2*j + lhalf
+            const uint32_t b = ((grp ? scw[2 + (j >> 1)] : scw[j >> 1]) >> (8 * (2 * (j & 1) + lhalf))) & 0xffu;
+            sub_scale[j] = dscale * float(b & 0x0fu);
+            sub_min[j] = -(dmin * float(b >> 4));
+          }
+        } else if constexpr (QT == QTYPE_Q3_K) {
+          uint32_t scw[4];
+          switch (((sb * kBlockBytes) & 15) >> 1) {
+            case 0: q3k_fetch<0>(rowbase, grp, lhalf, qw, scw); break;
+            case 1: q3k_fetch<1>(rowbase, grp, lhalf, qw, scw); break;
+            case 2: q3k_fetch<2>(rowbase, grp, lhalf, qw, scw); break;
+            case 3: q3k_fetch<3>(rowbase, grp, lhalf, qw, scw); break;
+            case 4: q3k_fetch<4>(rowbase, grp, lhalf, qw, scw); break;
+            case 5: q3k_fetch<5>(rowbase, grp, lhalf, qw, scw); break;
+            case 6: q3k_fetch<6>(rowbase, grp, lhalf, qw, scw); break;
+            default: q3k_fetch<7>(rowbase, grp, lhalf, qw, scw); break;
+          }
+          dscale = half_bits_to_float(uint16_t(scw[3] & 0xffffu));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // 6-bit scale number is = 8*grp + 2*j + lhalf = 4*q + i4: low nibble in byte (is % 8) (its high half for is >= 8), the two
+            // high bits in byte 8 + i4 at bit 2*q
+            const int i4 = 2 * (j & 1) + lhalf, q = 2 * grp + (j >> 1);
+            const uint32_t low = (scw[j >> 1] >> (8 * i4 + 4 * grp)) & 0x0fu;
+            const uint32_t high = (scw[2] >> (8 * i4 + 2 * q)) & 0x03u;
+            sub_scale[j] = dscale * float(int(low | (high << 4)) - 32);
+          }
         } else if constexpr (QT == QTYPE_NVFP4) {
           // stage 2*grp + ls is block 2*grp + ls (four ue4m3 scales, 32 bytes of nibbles); sub-blocks 2*lhalf and 2*lhalf + 1
           // (bytes 16*lhalf .. +15: weights 32*lhalf .. +31 of the stage) are this thread's
@@ -735,6 +793,21 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
               }
               bytes_to_pairs<T>(lo, off, s_lo, a_lo, o0[2 * i], o0[2 * i + 1]);
               bytes_to_pairs<T>(hi, off, s_hi, a_hi, o1[2 * i], o1[2 * i + 1]);
+            }
+          } else if constexpr (QT == QTYPE_Q2_K || QT == QTYPE_Q3_K) {
+            // stage 2*grp + ls = (half-block grp, j = 2*ls and 2*ls + 1): both halves come from the same 16 bytes at bit 2j
+            const V off = P::splat(P::kMagic + (QT == QTYPE_Q3_K ? 4.f : 0.f));
+#pragma unroll
+            for (int qo = 0; qo < 2; ++qo) {
+              const int j = 2 * ls + qo;
+              uint32_t (&o)[8] = qo == 0 ? o0 : o1;
+              const V s2 = P::splat(sub_scale[j]), a2 = P::splat(sub_min[j]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint32_t nq = (qw[i] >> (2 * j)) & 0x03030303u;
+                if constexpr (QT == QTYPE_Q3_K) nq |= ((qw[4 + i] >> (4 * grp + j)) & 0x01010101u) << 2;
+                bytes_to_pairs<T>(nq, off, s2, a2, o[2 * i], o[2 * i + 1]);
+              }
             }
           } else if constexpr (QT == QTYPE_Q4_0) {
             // o0 / o1 = blocks 2*ls, 2*ls+1 of this thread's four: [0..3] the low nibbles (weights 8*lhalf .. +7 of the block),
@@ -1093,6 +1166,8 @@ int launch_q8_0(B200_UMMA_LAUNCH_ARGS);
 int launch_q4_0(B200_UMMA_LAUNCH_ARGS);
 int launch_mxfp4(B200_UMMA_LAUNCH_ARGS);
 int launch_nvfp4(B200_UMMA_LAUNCH_ARGS);
+int launch_q2_k(B200_UMMA_LAUNCH_ARGS);
+int launch_q3_k(B200_UMMA_LAUNCH_ARGS);
 
 }  // namespace umma
 }  // namespace b200gguf

@@ -35,7 +35,7 @@ STREAM_QTYPES = ("Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K
 # two further layouts run on the same persistent data path with fp32 arithmetic, in ONE configuration (4)
 STREAM_FP32_QTYPES = ()
 # further types the tcgen05 GEMM unpacks (besides Q4_K, Q6_K, Q8_0); MXFP4 and NVFP4 become exact 16-bit operands
-UMMA_MORE_QTYPES = ("Q5_K", "Q4_0", "MXFP4", "NVFP4")
+UMMA_MORE_QTYPES = ("Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K")
 
 _B200_TUNING = {
     "simt": {"kind": "gemv_simt", "rows_per_warp": 1, "activation_rows_per_pass": 4, "staging": "ldg", "tensor_cores": "none"},

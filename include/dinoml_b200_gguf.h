@@ -43,9 +43,8 @@ enum DinoB200GgufVariant {
   DINOML_B200_GGUF_VARIANT_AUTO = 0,   /* shape-guarded dispatch: stream / mma for small M, umma above, simt for float32 */
   DINOML_B200_GGUF_VARIANT_SIMT = 1,   /* CUDA-core warp-per-row, any dtype, any M */
   DINOML_B200_GGUF_VARIANT_MMA = 2,    /* decode GEMV, one CTA per 16-row tile, M = 1..16, float16 / bfloat16; Q8_0, Q4_K, Q6_K */
-  DINOML_B200_GGUF_VARIANT_UMMA = 3,   /* prefill GEMM on tcgen05 / TMEM, M >= 9, float16 / bfloat16; every type but Q2_K, Q3_K */
-  DINOML_B200_GGUF_VARIANT_STREAM = 4, /* persistent decode GEMV: bulk-copy (TMA) ring + mbarriers, M = 1..8; every type but Q8_0
-                                          (Q2_K, Q3_K with fp32 arithmetic, the others on tensor cores) */
+  DINOML_B200_GGUF_VARIANT_UMMA = 3,   /* prefill GEMM on tcgen05 / TMEM, M >= 9, float16 / bfloat16; every type */
+  DINOML_B200_GGUF_VARIANT_STREAM = 4, /* persistent decode GEMV on tensor cores: bulk-copy (TMA) ring + mbarriers, M = 1..8; every type but Q8_0 */
 };
 #define DINOML_B200_GGUF_VARIANT_CODE(family, config) ((family) | ((config) << 8))
 
@@ -197,7 +196,7 @@ DINOML_B200_API int dinoml_b200_peer_pull_ctr(void* const* signal_ptrs, void* co
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, stream)
  *   int   dinoml_b200_gguf_<q>_gemm_rcr_bias_<dtype>_<variant>_v1(a, b_quant, bias, c, m, n, k, stream)
  *   float dinoml_profile_b200_gguf_<q>_gemm_rcr_<dtype>_<variant>_v1(a, b_quant, c, m, n, k, iterations, stream)
- * with <q> in {q8_0,q4_k,q6_k} (the six further types: simt and stream for all, umma for q4_0,q5_k,mxfp4,nvfp4),
+ * with <q> in {q8_0,q4_k,q6_k} (the six further types q4_0,q5_k,q2_k,q3_k,mxfp4,nvfp4: simt, stream and umma),
  * <dtype> in {float16,bfloat16,float32}, <variant> in {simt,mma,umma,stream}
  * (mma / umma / stream exist for float16 and bfloat16 only; a symbol runs its family's default tuning configuration, the
  * other configurations are reached through dinoml_b200_gguf_gemm_rcr with a variant code). */
@@ -223,7 +222,7 @@ DINOML_B200_GGUF_DECLARE_Q(q4_k)
 DINOML_B200_GGUF_DECLARE_Q(q6_k)
 /* The six further types of the reference's fused prototype (kernels/rocm/src/ck_gguf_q8_gemm.hip:27-32, 43-69, 80-92; symbol
  * family :1910-1940 per type): dequantize bit-exact; fused gemm on the CUDA-core variant for every dtype, on the persistent
- * GEMV (M <= 8) for the 16-bit dtypes, and - Q4_0, Q5_K, MXFP4, NVFP4 - on the tcgen05 GEMM (M >= 9). */
+ * GEMV (M <= 8) and the tcgen05 GEMM (M >= 9) for the 16-bit dtypes. */
 #define DINOML_B200_GGUF_DECLARE_SIMT_Q(q)    \
   DINOML_B200_GGUF_DECLARE(q, float32, simt)  \
   DINOML_B200_GGUF_DECLARE(q, float16, simt)  \
@@ -237,6 +236,8 @@ DINOML_B200_GGUF_DECLARE_UMMA_Q(q4_0)
 DINOML_B200_GGUF_DECLARE_UMMA_Q(q5_k)
 DINOML_B200_GGUF_DECLARE_UMMA_Q(mxfp4)
 DINOML_B200_GGUF_DECLARE_UMMA_Q(nvfp4)
+DINOML_B200_GGUF_DECLARE_UMMA_Q(q2_k)
+DINOML_B200_GGUF_DECLARE_UMMA_Q(q3_k)
 DINOML_B200_GGUF_DECLARE_SIMT_Q(q4_0)
 DINOML_B200_GGUF_DECLARE_SIMT_Q(q5_k)
 DINOML_B200_GGUF_DECLARE_SIMT_Q(q2_k)

@@ -94,7 +94,7 @@ def test_gemm_further_qtypes(dev, qtype, dtype):
     """Fused gemm on the six further types (CUDA-core variant, every dtype, small and mid M, with bias) against the oracle."""
     q = qtype_of(qtype)
     for (m, n, k) in [(1, 16, 256), (1, 1000, 1024), (3, 33, 512), (4, 64, 2048), (17, 24, 768), (64, 40, 512)]:
-        # AUTO: the CUDA-core kernel, or (16-bit dtypes, M <= 8, 16-byte rows) the persistent GEMV; four of the types also have the tcgen05 GEMM
+        # AUTO: the CUDA-core kernel, or (16-bit dtypes, 16-byte rows) the persistent GEMV up to M = 8 and the tcgen05 GEMM above
         allowed = ("simt",) if dtype == "float32" else ("simt", "stream") if m <= 8 else ("simt", "umma") if qtype in mf.UMMA_MORE_QTYPES else ("simt",)
         assert kernels.select_variant(qtype, dtype, m, n, k) in allowed
         blocks = S.random_blocks(qtype, n, k, seed=3100 + m + n)
@@ -273,13 +273,13 @@ UMMA_SHAPES = [  # (m, n, k)
 
 
 def _umma_k(qtype, k):
-    """The umma variant needs 16-byte weight rows: K % 2048 == 0 for Q6_K (210 bytes per 256 weights), K % 512 == 0 for MXFP4
-    (136 bytes), any K % 256 == 0 for the others."""
-    step = {"Q6_K": 2048, "MXFP4": 512}.get(qtype, 256)
+    """The umma variant needs 16-byte weight rows: K % 2048 == 0 for Q6_K and Q3_K (210 / 110 bytes per 256 weights), K % 1024 == 0
+    for Q2_K (84), K % 512 == 0 for MXFP4 (136), any K % 256 == 0 for the others."""
+    step = {"Q6_K": 2048, "Q3_K": 2048, "Q2_K": 1024, "MXFP4": 512}.get(qtype, 256)
     return -(-k // step) * step
 
 
-@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q5_K", "Q4_0", "MXFP4", "NVFP4"])
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K"])
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 def test_gemm_umma(dev, qtype, dtype):
     """tcgen05 / TMEM prefill GEMM against the oracle (fp32 weights, fp32 accumulation)."""
@@ -373,7 +373,7 @@ def test_dual_gemm_gated_epilogue(dev, qtype, activation):
         kernels.dual_gemm_rcr(x.float(), w, qtype, activation)         # fp32 activations have no tensor-core variant
 
 
-@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q5_K", "Q4_0", "MXFP4", "NVFP4"])
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K"])
 @pytest.mark.parametrize("activation", ["silu", "fast_gelu"])
 def test_dual_gemm_bias_and_b1_broadcast(dev, qtype, activation):
     """The reference's _bias_ forms and its B1 [1, K] broadcast: act(a B0^T + bias0) * (a B1^T + bias1) on every kernel that has
