@@ -603,10 +603,9 @@ def run_single(args):
                                                  "gemv_m1_us": gv["us_per_launch"], "gemv_m1_weight_gbs": gv["weight_bytes"] / gv["us_per_launch"] / 1e3,
                                                  "gemv_m1_frac_of_measured_hbm": gv["weight_bytes"] / gv["us_per_launch"] / 1e3 / peaks["hbm_gbs"],
                                                  "variant": gv["variant"]}
-        if True:                                         # prefill on the same weight (tcgen05 GEMM)
-            pf = bench_gemm(q, 4096, 4096, 512, extra_steps, extra_warm, l2)
-            extras["further_qtypes_4096x4096"][q].update({"gemm_m512_us": pf["us_per_launch"], "gemm_m512_variant": pf["variant"],
-                                                          "gemm_m512_tflops": 2.0 * 512 * 4096 * 4096 / pf["us_per_launch"] / 1e6})
+        pf = bench_gemm(q, 4096, 4096, 512, extra_steps, extra_warm, l2)      # prefill on the same weight (tcgen05 GEMM)
+        extras["further_qtypes_4096x4096"][q].update({"gemm_m512_us": pf["us_per_launch"], "gemm_m512_variant": pf["variant"],
+                                                      "gemm_m512_tflops": 2.0 * 512 * 4096 * 4096 / pf["us_per_launch"] / 1e6})
     extras["dual_gate_up_q4k_14336x4096"] = {f"m{m}": bench_dual(14336, 4096, m, extra_steps, extra_warm, l2) for m in (1, 16)}
     extras["cfg5_ffn_1gpu"] = {f"m{m}": v for m, v in bench_ffn_1gpu((1, 16, 256), extra_steps, extra_warm, l2).items()}
     try:

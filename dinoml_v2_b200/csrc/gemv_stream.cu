@@ -55,18 +55,17 @@ template <> struct Geom<QTYPE_Q6_K> { static constexpr int kSbBytes = 210, kPitc
 // Q5_K = the Q4_K block with 32 more bytes (one high bit per weight) between the scales and the nibbles: same 8-byte reads,
 // 8 x 176 + 32 = 1440 B is 32 (mod 128) like the Q4_K pitch.
 template <> struct Geom<QTYPE_Q5_K> { static constexpr int kSbBytes = 176, kPitch = kKC * 176 + 32; };
-// The further types: packed bytes per 256 weights of a row; the pitch is the stage piece rounded up to 128 B, plus 16, so
-// that the byte reads of 16 rows spread over the banks and every row starts 16-byte aligned (bulk-copy destination).
-template <int BYTES> struct GenericGeom { static constexpr int kSbBytes = BYTES, kPitch = (kKC * BYTES + 127) / 128 * 128 + 16; };
-template <> struct Geom<QTYPE_Q4_0> : GenericGeom<8 * 18> {};
-template <> struct Geom<QTYPE_Q2_K> : GenericGeom<84> {};
-template <> struct Geom<QTYPE_Q3_K> : GenericGeom<110> {};
-template <> struct Geom<QTYPE_MXFP4> : GenericGeom<8 * 17> {};
-template <> struct Geom<QTYPE_NVFP4> : GenericGeom<4 * 36> {};
+// The further types: packed bytes per 256 weights of a row; the pitch is the stage piece rounded up to 128 B, plus 16 (4 words:
+// the 4-byte reads of 8 rows x 4 lanes hit 32 distinct banks) and every row starts 16-byte aligned (bulk-copy destination).
+template <int BYTES> struct PaddedGeom { static constexpr int kSbBytes = BYTES, kPitch = (kKC * BYTES + 127) / 128 * 128 + 16; };
+template <> struct Geom<QTYPE_Q4_0> : PaddedGeom<8 * 18> {};
+template <> struct Geom<QTYPE_Q2_K> : PaddedGeom<84> {};
+template <> struct Geom<QTYPE_Q3_K> : PaddedGeom<110> {};
+template <> struct Geom<QTYPE_MXFP4> : PaddedGeom<8 * 17> {};
+template <> struct Geom<QTYPE_NVFP4> : PaddedGeom<4 * 36> {};
 // Q4_0 and MXFP4 (32-weight blocks: a scale and 16 bytes of nibbles), NVFP4, Q2_K and Q3_K run on tensor cores like Q4_K.
 template <int QT> constexpr bool is_blk32() { return QT == QTYPE_Q4_0 || QT == QTYPE_MXFP4; }
 template <int QT> constexpr bool is_q23() { return QT == QTYPE_Q2_K || QT == QTYPE_Q3_K; }     // 2- / 3-bit quants, a scale per 16 weights
-template <int QT> constexpr bool is_generic() { return false; }    // the value-by-value fp32 branch (decode8 + FMA) serves no type any more
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {     // selector bit 3 of a nibble: replicate the byte's sign bit
   uint32_t d;
@@ -114,18 +113,6 @@ __device__ __forceinline__ void fp4x8_operands(uint32_t w, uint32_t& lo01, uint3
   }
 }
 
-// 8 consecutive activations as floats.
-template <typename T> __device__ __forceinline__ void x8_to_float(const uint4 v, float (&x)[8]);
-template <> __device__ __forceinline__ void x8_to_float<__nv_bfloat16>(const uint4 v, float (&x)[8]) {
-  const uint32_t r[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { x[2 * i] = __uint_as_float(r[i] << 16); x[2 * i + 1] = __uint_as_float(r[i] & 0xffff0000u); }
-}
-template <> __device__ __forceinline__ void x8_to_float<__half>(const uint4 v, float (&x)[8]) {
-  const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
-}
 constexpr int kGroupWarps = kKC;
 constexpr int kBarBytes = 256;                  // mbarrier area in front of the ring (up to 32 barriers)
 
@@ -159,7 +146,6 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   constexpr bool kMinTerm = QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0 || kQ23;   // these fold their mins / offsets against activation sums; Q6_K and the FP4 types have none
   constexpr bool kQ5 = QT == QTYPE_Q5_K;           // Q4_K arithmetic plus the fifth bit of every quant
   constexpr int kQsOff = kQ5 ? 48 : 16;            // where the nibbles start inside a block
-  constexpr bool kGeneric = is_generic<QT>();      // decoded value by value (decode8), fp32 FMA, no tensor cores
   static_assert(D % NG == 0 && D >= 2 * NG, "every group needs its own ring slots, at least two");
   static_assert(MXC == 1 || MXC == 2 || MXC == 4 || MXC == 8, "MXC");
   using Red = RedBuf<MXC, NCW>;
@@ -169,7 +155,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   uint8_t* sW = smem_dyn + kBarBytes;                                         // D x kStageBytes
   Red* sRed = reinterpret_cast<Red*>(sW + size_t(D) * kStageBytes);      // [2]
   float* sX = reinterpret_cast<float*>(sRed + 2);                        // [MXC][k/32]
-  __shared__ __align__(16) float sS[kGeneric ? 1 : NCW][kGeneric ? 1 : kRows][(QT == QTYPE_Q6_K || kQ23) ? kQ6ScalePitch : kGeneric ? 4 : 8];   // d * sc per row, sub-block (warp-private scratch)
+  __shared__ __align__(16) float sS[NCW][kRows][(QT == QTYPE_Q6_K || kQ23) ? kQ6ScalePitch : 8];   // d * sc per row, sub-block (warp-private scratch)
   __shared__ float sOut[kRows * MXC];                                    // epilogue warp scratch
   __shared__ int s_abort;
   static_assert((2 * D + 4) * 8 <= kBarBytes, "barrier area");
@@ -358,9 +344,6 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   named_barrier(1, NCW * 32);
 
   float res[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-  float gacc[kGeneric ? MXC : 1];               // generic types: this lane's half of row `srow`, per activation row
-#pragma unroll
-  for (int c = 0; c < (kGeneric ? MXC : 1); ++c) gacc[c] = 0.f;
   float zero4[4];
   opaque_zero4(zero4);
   float xt[MXC];
@@ -376,17 +359,6 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
     if (tl >= 2) ok = __all_sync(0xffffffffu, mbar_wait(red_empty(buf), uint32_t((tl >> 1) - 1) & 1u, abort_flag, status, ST_STREAM_RED_EMPTY) ? 1 : 0) != 0;
     if (!ok) return;
     Red& rb = sRed[buf];
-    if constexpr (kGeneric) {
-#pragma unroll
-      for (int c = 0; c < MXC; ++c) {
-        const float both = gacc[c] + __shfl_xor_sync(0xffffffffu, gacc[c], 1);
-        if (shalf == 0) { rb.red[cw][srow][c] = both; rb.xt[cw][srow][c] = 0.f; }
-        gacc[c] = 0.f;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(red_full(buf));
-      return;
-    }
     if (2 * t < MXC) {
       rb.red[cw][g][2 * t] = res[0][0];
       rb.red[cw][g + 8][2 * t] = res[0][2];
@@ -417,29 +389,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
     ok = __all_sync(0xffffffffu, mbar_wait(full(slot), uint32_t(u / D) & 1u, abort_flag, status, ST_STREAM_FULL) ? 1 : 0) != 0;
     if (!ok) break;
     const int sb = chunk * kKC + wq;
-    if constexpr (kGeneric) {
-      if (!PROBE && sb < nsb) {
-        // lane pair (srow, shalf): weights shalf * 128 .. + 127 of this warp's super-block of row srow, 8 at a time
-        constexpr int kUnitsPerBlock = QTraits<QT>::kBlock / 8;
-        const uint8_t* rowp = sW + size_t(slot) * kStageBytes + srow * kPitch + wq * kSbBytes;
-        const T* xs = x + int64_t(sb) * 256 + shalf * 128;
-#pragma unroll 2
-        for (int u = 0; u < 16; ++u) {
-          const int uu = shalf * 16 + u;
-          float w8[8];
-          decode8<QT>(rowp + (uu / kUnitsPerBlock) * QTraits<QT>::kBytes, (uu % kUnitsPerBlock) * 8, w8);
-#pragma unroll
-          for (int c = 0; c < MXC; ++c) {
-            if (c < m) {
-              float x8[8];
-              x8_to_float<T>(__ldg(reinterpret_cast<const uint4*>(xs + int64_t(c) * k + u * 8)), x8);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) gacc[c] = fmaf(x8[j], w8[j], gacc[c]);
-            }
-          }
-        }
-      }
-    } else if (!PROBE && sb < nsb && kB32) {
+    if (!PROBE && sb < nsb && kB32) {
       if constexpr (kB32) {
         constexpr int BB = QT == QTYPE_Q4_0 ? 18 : 17, QOFF = BB - 16;       // block bytes, where its 16 nibble bytes start
         const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
@@ -818,11 +768,6 @@ template <int QT, typename T, int MXC>
 static int launch_m(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int config, const PeerOut& peers,
                     cudaStream_t s) {
   constexpr bool Q6 = QT == QTYPE_Q6_K || QT == QTYPE_Q5_K;      // the larger stages (26.3 / 23.0 KB): shallower rings
-  if constexpr (is_generic<QT>()) {
-    // the further types have one configuration: 8 consumer warps, two CTAs per SM, 3 or 4 ring slots by stage size
-    if (config != 0 && config != 4) return RC_RANGE;
-    return launch_cfg<QT, T, MXC, 1, (Geom<QT>::kPitch > 1300 ? 3 : 4)>(a, b, bias, c, m, n, k, 2, peers, s);
-  }
   if (config & kProbeBit) {
     if constexpr (MXC == 1 && std::is_same<T, __nv_bfloat16>::value) {
       switch (config & ~kProbeBit) {

@@ -32,8 +32,6 @@ STREAM_CONFIGS = {1: {"consumer_warps": 8, "ring_slots": {"Q4_K": 5, "Q6_K": 4, 
                   3: {"consumer_warps": 16, "ring_slots": {"Q4_K": 8, "Q6_K": 6, "Q5_K": 6, "Q4_0": 8, "MXFP4": 8, "NVFP4": 8, "Q2_K": 8, "Q3_K": 8}, "ctas_per_sm": 1},
                   4: {"consumer_warps": 8, "ring_slots": {"Q4_K": 4, "Q6_K": 3, "Q5_K": 3, "Q4_0": 4, "MXFP4": 4, "NVFP4": 4, "Q2_K": 4, "Q3_K": 4}, "ctas_per_sm": 2}}
 STREAM_QTYPES = ("Q4_K", "Q6_K", "Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K")
-# two further layouts run on the same persistent data path with fp32 arithmetic, in ONE configuration (4)
-STREAM_FP32_QTYPES = ()
 # further types the tcgen05 GEMM unpacks (besides Q4_K, Q6_K, Q8_0); MXFP4 and NVFP4 become exact 16-bit operands
 UMMA_MORE_QTYPES = ("Q5_K", "Q4_0", "MXFP4", "NVFP4", "Q2_K", "Q3_K")
 
@@ -64,12 +62,10 @@ def candidate_variants(qtype: str, dtype: str) -> list[str]:
         if qtype in ("Q4_K", "Q6_K", "Q8_0"):
             variants.append("mma")
             variants.append("umma")
-        elif qtype in UMMA_MORE_QTYPES:             # further types with a tcgen05 GEMM (Q5_K also has the tensor-core persistent GEMV)
+        elif qtype in UMMA_MORE_QTYPES:             # the further types: tcgen05 GEMM and persistent GEMV, no tile GEMV
             variants.append("umma")
         if qtype in STREAM_QTYPES:
             variants += [f"stream:{c}" for c in sorted(STREAM_CONFIGS)]
-        elif qtype in STREAM_FP32_QTYPES:
-            variants.append("stream:4")
     return variants
 
 
@@ -108,10 +104,7 @@ def gguf_candidate(qtype: str, op: str, dtype: str, variant: str) -> dict[str, A
     tuning = dict(_B200_TUNING[family])
     if config:
         tuning.update(STREAM_CONFIGS[int(config)], config=int(config))
-        if q.name in STREAM_FP32_QTYPES:
-            tuning.update(ring_slots=4, tensor_cores="none", arithmetic="fp32 fma on values decoded 8 at a time")
-        else:
-            tuning["ring_slots"] = tuning["ring_slots"][q.name]
+        tuning["ring_slots"] = tuning["ring_slots"][q.name]
     cand = {
         "candidate_id": f"b200_gguf_{q.symbol}_{dtype}_{tag}_v1",
         "symbol_id": f"{q.symbol}_{tag}_v1",
