@@ -103,6 +103,15 @@ def test_config5_shard_shapes(world, m):
         _run_case(f"cfg5_g{world}_{part}_m{m}", "Q4_K", m, n, k, "bfloat16", expect, 9500 + world * 10 + m % 7, sample=64 if m == 256 else 160)
 
 
+@pytest.mark.parametrize("qtype", ["Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4"])
+@pytest.mark.parametrize("m,dtype", [(1, "bfloat16"), (8, "float16"), (512, "bfloat16"), (64, "float16")])
+def test_further_qtypes_at_full_size(qtype, m, dtype):
+    """The six further types of the reference prototype on a Llama-8B down-projection shape [4096 x 14336]: decode rows on the
+    persistent GEMV, prefill rows on the tcgen05 GEMM (K = 14336 gives 16-byte weight rows for every one of them)."""
+    expect = "stream" if m <= 8 else "umma"
+    _run_case(f"more_{qtype}_m{m}_{dtype}", qtype, m, 4096, 14336, dtype, expect, 9600 + m, sample=64 if m >= 64 else 256)
+
+
 def test_zz_write_error_record():
     """Writes the measured errors of the cases above into $DINOML_TEST_REPORT_DIR (when set and existing)."""
     out = os.environ.get("DINOML_TEST_REPORT_DIR")

@@ -28,7 +28,7 @@ def _artifact(tmp_path, qtype, n, k, dtype="bfloat16", bias=False, buckets=(1, 1
     return art, blocks, bias_v
 
 
-@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0"])
+@pytest.mark.parametrize("qtype", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4"])
 def test_session_run_numpy_matches_oracle(tmp_path, qtype):
     n, k = 96, 1024
     art, blocks, bias = _artifact(tmp_path, qtype, n, k, bias=True)
