@@ -142,6 +142,25 @@ def test_kernel_manifest_and_plan_text(tmp_path):
     assert k4 != profiling.profile_key(man["target"], "hw", item6, item["candidates"][0], {"m": 1, "n": 64, "k": 512})
 
 
+def test_candidates_of_the_further_types():
+    """Every further type of the reference prototype: the CUDA-core kernel, the tcgen05 GEMM and the four configurations of the
+    persistent GEMV - no tile GEMV; float32 activations keep the CUDA-core kernel only.  The symbols the candidates name exist."""
+    import ctypes
+
+    from dinoml_v2_b200 import _native
+    lib = ctypes.CDLL(str(_native.LIB_PATH)) if _native.LIB_PATH.exists() else None
+    for q in ("Q4_0", "Q5_K", "Q2_K", "Q3_K", "MXFP4", "NVFP4"):
+        assert mf.candidate_variants(q, "bfloat16") == ["simt", "umma", "stream:1", "stream:2", "stream:3", "stream:4"]
+        assert mf.candidate_variants(q, "float32") == ["simt"]
+        for variant in ("simt", "umma", "stream"):
+            cand = mf.gguf_candidate(q, "gemm_rcr_bias", "float16", variant)
+            assert cand["qtype"] == q and cand["kernel_symbol"].endswith(f"_gemm_rcr_bias_float16_{variant}_v1")
+            if lib is not None:
+                assert hasattr(lib, cand["kernel_symbol"]), cand["kernel_symbol"]
+        tuned = mf.gguf_candidate(q, "gemm_rcr", "bfloat16", "stream:3")
+        assert tuned["b200"]["ring_slots"] == (6 if q == "Q5_K" else 8) and tuned["b200"]["consumer_warps"] == 16   # Q5_K stages are 23 KB
+
+
 def test_admission_rules(tmp_path):
     spec, _ = _linear_spec(tmp_path)
     with pytest.raises(NotImplementedError):
