@@ -10,6 +10,7 @@
 //   Q6_K: a thread owns 8 positions l of one 128-weight half: 8 ql bytes, the 8 ql bytes 32 further, 8 qh bytes ->
 //         four runs of 8 weights (one per quad); 8 threads per block;
 //   Q8_0: a thread owns 8 consecutive weights.
+//   the six further types: see dequant_items_kernel below.
 // Decoding uses explicitly rounded fp32 operations (bit-exact), and each run of 8 outputs is one 32-byte (f32) or
 // 16-byte (f16 / bf16) streaming store.  Float outputs (write bound) keep the simpler one-unit-per-thread kernel, which
 // measured faster there (Q4_K -> f32 4.77 vs 4.35 TB/s); 16-bit outputs gain 8 % (Q4_K) to 35 % (Q6_K).
@@ -156,6 +157,120 @@ dequant_q6k_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_t 
   }
 }
 
+// The six further types, 16-bit outputs: item = 8 consecutive packed bytes and every run of 8 weights they hold, so that each
+// packed byte is loaded once (the one-unit-per-thread kernel loads a nibble byte twice, a Q2_K byte four times and a Q3_K
+// mask byte eight times).  Arithmetic is decode8<QT>'s, operation for operation.
+//   Q4_0 / MXFP4: item = (block, half p of its 16 bytes): low nibbles = weights 8p .., high nibbles = weights 16 + 8p ..
+//   NVFP4:        item = (block, sub-block s): low nibbles = its first 8 weights, high nibbles = the other 8
+//   Q5_K:         item = (block, 64-weight group g, piece of 8 bytes): as Q4_K, plus bits 2g, 2g+1 of 8 bytes of qh
+//   Q2_K / Q3_K:  item = (block, half hb, 8 positions l0 ..): four runs (bit pairs j = 0..3) of 8 weights 32 apart
+// A: alignment the launcher found for the packed buffer (blocks of these types are only 1-, 2- or 4-byte multiples).
+template <int QT> struct ItemGeom;
+template <> struct ItemGeom<QTYPE_Q4_0> { static constexpr int kItems = 2, kAlign = 2; };
+template <> struct ItemGeom<QTYPE_MXFP4> { static constexpr int kItems = 2, kAlign = 1; };
+template <> struct ItemGeom<QTYPE_NVFP4> { static constexpr int kItems = 4, kAlign = 4; };
+template <> struct ItemGeom<QTYPE_Q5_K> { static constexpr int kItems = 16, kAlign = 4; };
+template <> struct ItemGeom<QTYPE_Q2_K> { static constexpr int kItems = 8, kAlign = 4; };
+template <> struct ItemGeom<QTYPE_Q3_K> { static constexpr int kItems = 8, kAlign = 2; };
+template <int QT> constexpr bool has_item_kernel() {
+  return QT == QTYPE_Q4_0 || QT == QTYPE_MXFP4 || QT == QTYPE_NVFP4 || QT == QTYPE_Q5_K || QT == QTYPE_Q2_K || QT == QTYPE_Q3_K;
+}
+
+template <int A>
+__device__ __forceinline__ uint2 ld8(const uint8_t* p) {      // 8 bytes at an A-byte aligned address
+  if (A >= 4) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(p);
+    return make_uint2(__ldg(w), __ldg(w + 1));
+  }
+  if (A == 2) return make_uint2(ld_u32_a2(p), ld_u32_a2(p + 4));
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { lo |= uint32_t(p[i]) << (8 * i); hi |= uint32_t(p[4 + i]) << (8 * i); }
+  return make_uint2(lo, hi);
+}
+__device__ __forceinline__ uint32_t byte_of(const uint2& q, int e) { return ((e < 4 ? q.x : q.y) >> (8 * (e & 3))) & 0xffu; }
+
+template <int QT, typename T, int A>
+__global__ void __launch_bounds__(kDequantThreads)
+dequant_items_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_t total_items) {
+  constexpr int kBytes = QTraits<QT>::kBytes, kBlock = QTraits<QT>::kBlock;
+  const int64_t base = (int64_t(blockIdx.x) * 2) * kDequantThreads + threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int64_t it = base + int64_t(i) * kDequantThreads;
+    if (it >= total_items) continue;
+    const int64_t blk = it / ItemGeom<QT>::kItems;
+    const int item = int(it - blk * ItemGeom<QT>::kItems);
+    const uint8_t* b = in + blk * kBytes;
+    T* dst = out + blk * kBlock;
+    float w[8];
+    if constexpr (QT == QTYPE_Q4_0 || QT == QTYPE_MXFP4) {
+      const float d = QT == QTYPE_Q4_0 ? half_at(b) : e8m0_half(b[0]);
+      const uint2 q = ld8<A>(b + (kBytes - 16) + 8 * item);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const uint32_t nib = (byte_of(q, e) >> (4 * h)) & 0x0fu;
+          w[e] = QT == QTYPE_Q4_0 ? __fmul_rn(d, float(int(nib) - 8)) : __fmul_rn(d, float(fp4_code_value(nib)));
+        }
+        Pack8<T>::store(dst + 8 * item + 16 * h, w);
+      }
+    } else if constexpr (QT == QTYPE_NVFP4) {
+      const float d = ue4m3_half(b[item]);
+      const uint2 q = ld8<A>(b + 4 + 8 * item);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = __fmul_rn(d, float(fp4_code_value((byte_of(q, e) >> (4 * h)) & 0x0fu)));
+        Pack8<T>::store(dst + 16 * item + 8 * h, w);
+      }
+    } else if constexpr (QT == QTYPE_Q5_K) {
+      const int g = item >> 2, piece = item & 3;
+      const float d = half_at(b), dmin = half_at(b + 2);
+      const uint2 q = ld8<A>(b + 48 + 32 * g + 8 * piece), qh = ld8<A>(b + 16 + 8 * piece);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        int sc, mn;
+        k4_scale_min(2 * g + h, b + 4, sc, mn);
+        const float ds = __fmul_rn(d, float(sc)), dm = __fmul_rn(dmin, float(mn));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int qv = int((byte_of(q, e) >> (4 * h)) & 0x0fu) + (((byte_of(qh, e) >> (2 * g + h)) & 1u) ? 16 : 0);
+          w[e] = __fsub_rn(__fmul_rn(ds, float(qv)), dm);
+        }
+        Pack8<T>::store(dst + 64 * g + 32 * h + 8 * piece, w);
+      }
+    } else {
+      const int hb = item >> 2, l0 = 8 * (item & 3);
+      constexpr int kQs = QT == QTYPE_Q2_K ? 16 : 32;
+      const uint2 q = ld8<A>(b + kQs + 32 * hb + l0);
+      uint2 hm = make_uint2(0u, 0u);
+      if constexpr (QT == QTYPE_Q3_K) hm = ld8<A>(b + l0);
+      const float d = half_at(b + (QT == QTYPE_Q2_K ? 80 : 108));
+      const float dmin = QT == QTYPE_Q2_K ? half_at(b + 82) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int is = 8 * hb + 2 * j + (l0 >= 16 ? 1 : 0);
+        if constexpr (QT == QTYPE_Q2_K) {
+          const uint32_t scale = b[is];
+          const float ds = __fmul_rn(d, float(scale & 0x0fu)), dm = __fmul_rn(dmin, float(scale >> 4));
+#pragma unroll
+          for (int e = 0; e < 8; ++e) w[e] = __fsub_rn(__fmul_rn(ds, float(int(byte_of(q, e) >> (2 * j)) & 3)), dm);
+        } else {
+          const float ds = __fmul_rn(d, float(q3k_scale(b + 96, is) - 32));
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int low = int(byte_of(q, e) >> (2 * j)) & 3;
+            w[e] = __fmul_rn(ds, float(low - (((byte_of(hm, e) >> (4 * hb + j)) & 1u) ? 0 : 4)));
+          }
+        }
+        Pack8<T>::store(dst + 128 * hb + 32 * j + l0, w);
+      }
+    }
+  }
+}
+
 template <int QT, typename T>
 static int launch_dequant(const void* in, void* out, int64_t rows, int64_t n_per_row, cudaStream_t stream) {
   const int64_t weights = rows * n_per_row;
@@ -170,6 +285,19 @@ static int launch_dequant(const void* in, void* out, int64_t rows, int64_t n_per
       dequant_q4k_kernel<T><<<dim3(unsigned(grid)), kDequantThreads, 0, stream>>>(static_cast<const uint8_t*>(in), static_cast<T*>(out), items);
     else
       dequant_q6k_kernel<T><<<dim3(unsigned(grid)), kDequantThreads, 0, stream>>>(static_cast<const uint8_t*>(in), static_cast<T*>(out), items);
+    return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
+  }
+  if constexpr (has_item_kernel<QT>() && sizeof(T) == 2) {
+    const int64_t items = weights / QTraits<QT>::kBlock * ItemGeom<QT>::kItems;
+    const int64_t per_cta = int64_t(kDequantThreads) * 2;
+    const int64_t grid = (items + per_cta - 1) / per_cta;
+    if (grid > 0x7fffffffLL) return RC_RANGE;
+    const uint8_t* src = static_cast<const uint8_t*>(in);
+    // word loads where the packed buffer allows them (these types accept any byte address), byte loads otherwise
+    if (ItemGeom<QT>::kAlign > 1 && reinterpret_cast<uintptr_t>(in) % ItemGeom<QT>::kAlign == 0)
+      dequant_items_kernel<QT, T, ItemGeom<QT>::kAlign><<<dim3(unsigned(grid)), kDequantThreads, 0, stream>>>(src, static_cast<T*>(out), items);
+    else
+      dequant_items_kernel<QT, T, 1><<<dim3(unsigned(grid)), kDequantThreads, 0, stream>>>(src, static_cast<T*>(out), items);
     return cudaGetLastError() == cudaSuccess ? RC_OK : RC_LAUNCH;
   }
   const int64_t total_units = weights / 8;
