@@ -427,7 +427,7 @@ def bench_e2e(steps, warmup, copies, tmp_dir):
     mod.close()
     wbytes = copies * blocks[0].nbytes
     return {"value": wbytes / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": copies * k * 2, "d2h_bytes_per_step": copies * n * 2,
-            "ms_per_step": dt * 1e3, "api": "dml.compile -> runtime.load -> Session.run_numpy", "linears_per_step": copies}
+            "ms_per_step": dt * 1e3, "steps": steps, "api": "dml.compile -> runtime.load -> Session.run_numpy", "linears_per_step": copies}
 
 
 # ----------------------------------------------------------------------------------------------- CPU reference arm
@@ -615,7 +615,8 @@ def run_single(args):
     torch.cuda.empty_cache()
 
     with tempfile.TemporaryDirectory() as tmp:
-        e2e = bench_e2e(max(3, min(K, 20)), 3, r, Path(tmp) / "artifact")
+        # a step is ~0.2 ms of host + device work: enough of them that scheduler noise on the host averages out
+        e2e = bench_e2e(max(20, min(8 * K, 400)), 10, r, Path(tmp) / "artifact")
     cpu, _, _ = cpu_reference_timing(budget_s=args.cpu_budget)
 
     m512 = prefill["m512"]
