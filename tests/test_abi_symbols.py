@@ -68,3 +68,24 @@ def test_versions_and_pure_host_entry_points(library):
     assert d(16, 12, 4, 100, 0, 16, None) == 3       # n_per_row not a multiple of 256
     assert d(16, 99, 4, 256, 0, 16, None) == 5
     assert d(16, 12, 0, 256, 0, 16, None) == 2
+
+
+def test_host_conversions_round_like_the_reference(library):
+    """float32 -> bfloat16 bits: round to nearest even, the integer formula of the reference's Python (src/dinoml/ir.py:68-73);
+    bfloat16 -> float32: the 16 bits followed by 16 zeros.  Every length around the vector width, odd addresses included."""
+    import numpy as np
+    vp = ctypes.c_void_p
+    narrow, widen = library.dino_convert_f32_to_bf16, library.dino_convert_bf16_to_f32
+    for fn in (narrow, widen):
+        fn.argtypes, fn.restype = [vp, vp, ctypes.c_size_t], None
+    rng = np.random.Generator(np.random.PCG64(3))
+    for count in (0, 1, 7, 8, 9, 31, 4096, 11009):
+        x = (rng.standard_normal(count + 1) * np.float32(10.0) ** rng.integers(-20, 20, count + 1)).astype(np.float32)[1:]   # 4-byte, not 16-byte aligned
+        x[: min(count, 6)] = np.array([0.0, -0.0, np.inf, -np.inf, 1.00390625, 1.01171875], np.float32)[: min(count, 6)]         # ties to even both ways
+        bits = np.empty(count + 1, np.uint16)[1:]
+        narrow(x.ctypes.data, bits.ctypes.data, count)
+        b = x.view(np.uint32).astype(np.uint64)
+        assert np.array_equal(bits, (((b + 0x7FFF + ((b >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)), count
+        back = np.empty(count + 1, np.float32)[1:]
+        widen(bits.ctypes.data, back.ctypes.data, count)
+        assert np.array_equal(back.view(np.uint32), bits.astype(np.uint32) << 16), count
