@@ -227,12 +227,22 @@ dequant_items_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_
       }
     } else if constexpr (QT == QTYPE_Q5_K) {
       const int g = item >> 2, piece = item & 3;
-      const float d = half_at(b), dmin = half_at(b + 2);
       const uint2 q = ld8<A>(b + 48 + 32 * g + 8 * piece), qh = ld8<A>(b + 16 + 8 * piece);
+      // the 16-byte header (d, dmin, 12 bytes of 6-bit scales and mins) as four words where the buffer is word aligned
+      const uint2 h01 = ld8<A>(b), h23 = ld8<A>(b + 8);
+      const float d = half_bits_to_float(uint16_t(h01.x & 0xffffu)), dmin = half_bits_to_float(uint16_t(h01.x >> 16));
+      const uint32_t s0 = h01.y, s1 = h23.x, s2 = h23.y;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
+        const int j = 2 * g + h;
         int sc, mn;
-        k4_scale_min(2 * g + h, b + 4, sc, mn);
+        if (j < 4) {
+          sc = int(s0 >> (8 * j)) & 63;
+          mn = int(s1 >> (8 * j)) & 63;
+        } else {
+          sc = (int(s2 >> (8 * (j - 4))) & 0x0f) | ((int(s0 >> (8 * (j - 4))) >> 6 & 3) << 4);
+          mn = (int(s2 >> (8 * (j - 4))) >> 4 & 0x0f) | ((int(s1 >> (8 * (j - 4))) >> 6 & 3) << 4);
+        }
         const float ds = __fmul_rn(d, float(sc)), dm = __fmul_rn(dmin, float(mn));
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -249,6 +259,12 @@ dequant_items_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_
       if constexpr (QT == QTYPE_Q3_K) hm = ld8<A>(b + l0);
       const float d = half_at(b + (QT == QTYPE_Q2_K ? 80 : 108));
       const float dmin = QT == QTYPE_Q2_K ? half_at(b + 82) : 0.f;
+      uint2 s01 = make_uint2(0u, 0u);          // Q3_K: the 12 scale bytes in three words (the third in s2)
+      uint32_t s2 = 0u;
+      if constexpr (QT == QTYPE_Q3_K) {
+        s01 = ld8<A>(b + 96);
+        s2 = A >= 2 ? ld_u32_a2(b + 104) : (uint32_t(b[104]) | (uint32_t(b[105]) << 8) | (uint32_t(b[106]) << 16) | (uint32_t(b[107]) << 24));
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int is = 8 * hb + 2 * j + (l0 >= 16 ? 1 : 0);
@@ -258,7 +274,11 @@ dequant_items_kernel(const uint8_t* __restrict__ in, T* __restrict__ out, int64_
 #pragma unroll
           for (int e = 0; e < 8; ++e) w[e] = __fsub_rn(__fmul_rn(ds, float(int(byte_of(q, e) >> (2 * j)) & 3)), dm);
         } else {
-          const float ds = __fmul_rn(d, float(q3k_scale(b + 96, is) - 32));
+          // 6-bit scale `is` = 4*qd + i4: low nibble in byte is % 8 (its high half for is >= 8), two high bits in byte 8 + i4 at bit 2*qd
+          const int i4 = is & 3, qd = is >> 2;
+          const uint32_t low = (((qd & 1) ? s01.y : s01.x) >> (8 * i4 + 4 * (qd >> 1))) & 0x0fu;
+          const uint32_t high = (s2 >> (8 * i4 + 2 * qd)) & 0x03u;
+          const float ds = __fmul_rn(d, float(int(low | (high << 4)) - 32));
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const int low = int(byte_of(q, e) >> (2 * j)) & 3;
