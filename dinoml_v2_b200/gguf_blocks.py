@@ -32,8 +32,9 @@ MXFP4 = QType("MXFP4", 39, 32, 17, "mxfp4")
 NVFP4 = QType("NVFP4", 40, 64, 36, "nvfp4")
 
 QTYPES = {q.name: q for q in (Q8_0, Q4_K, Q6_K, Q4_0, Q5_K, Q2_K, Q3_K, MXFP4, NVFP4)}
-# the types with tensor-core kernels (decode GEMV + tcgen05 GEMM); the others run on the CUDA-core kernel
-TENSOR_CORE_QTYPES = ("Q8_0", "Q4_K", "Q6_K")
+# every type has tensor-core kernels (a decode GEMV and the tcgen05 GEMM); float32 activations and weight rows that are not
+# multiples of 16 bytes run on the CUDA-core kernel
+TENSOR_CORE_QTYPES = tuple(QTYPES)
 QTYPES_BY_VALUE = {q.value: q for q in QTYPES.values()}
 
 
