@@ -9,6 +9,7 @@ namespace b200gguf {
 template <typename T> struct MmaType;
 template <> struct MmaType<__nv_bfloat16> {
   static constexpr uint32_t kMagicBytes = 0x43434343u;  // bf16 0x43qq = 128 + q
+  static constexpr uint32_t kOnePair = 0x3F803F80u;     // (1.0, 1.0)
   static constexpr float kMagic = 128.f;                // offset left in the MMA operand
   static __device__ __forceinline__ uint32_t fix(uint32_t pair) { return pair; }
   static __device__ __forceinline__ void mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -39,6 +40,7 @@ template <> struct MmaType<__nv_bfloat16> {
 };
 template <> struct MmaType<__half> {
   static constexpr uint32_t kMagicBytes = 0x64646464u;  // fp16 0x64qq = 1024 + q ...
+  static constexpr uint32_t kOnePair = 0x3C003C00u;     // (1.0, 1.0)
   static constexpr float kMagic = 0.f;                  // ... and the 1024 is removed exactly before the MMA
   static __device__ __forceinline__ uint32_t fix(uint32_t pair) {
     const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&pair), __half2half2(__ushort_as_half(0x6400)));

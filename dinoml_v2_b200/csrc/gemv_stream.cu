@@ -145,6 +145,11 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   constexpr int kXG = kQ23 ? 16 : 32;              // activations per entry of the sum table sX
   constexpr bool kMinTerm = QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0 || kQ23;   // these fold their mins / offsets against activation sums; Q6_K and the FP4 types have none
   constexpr bool kQ5 = QT == QTYPE_Q5_K;           // Q4_K arithmetic plus the fifth bit of every quant
+  // From four activation rows on, the types with folded offsets take the per-sub-block activation sums from the tensor cores (an MMA of the same
+  // activation fragment against an all-ones operand) instead of a table that every CTA builds from the whole activation
+  // matrix before it starts: that prologue grows with M * K per CTA and cost a third of the launch at M = 8, K = 14336.
+  constexpr bool kOnes = kMinTerm && MXC >= 4;
+  constexpr bool kNeedK = kOnes && (QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q2_K);   // types with a min besides the operand offset
   constexpr int kQsOff = kQ5 ? 48 : 16;            // where the nibbles start inside a block
   static_assert(D % NG == 0 && D >= 2 * NG, "every group needs its own ring slots, at least two");
   static_assert(MXC == 1 || MXC == 2 || MXC == 4 || MXC == 8, "MXC");
@@ -156,6 +161,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   Red* sRed = reinterpret_cast<Red*>(sW + size_t(D) * kStageBytes);      // [2]
   float* sX = reinterpret_cast<float*>(sRed + 2);                        // [MXC][k/32]
   __shared__ __align__(16) float sS[NCW][kRows][(QT == QTYPE_Q6_K || kQ23) ? kQ6ScalePitch : 8];   // d * sc per row, sub-block (warp-private scratch)
+  __shared__ __align__(16) float sK[kNeedK ? NCW : 1][kNeedK ? kRows : 1][QT == QTYPE_Q2_K ? kQ6ScalePitch : 8];   // kOnes: MAGIC * d * sc + dmin * min (Q2_K: dmin * min) per row, sub-block
   __shared__ float sOut[kRows * MXC];                                    // epilogue warp scratch
   __shared__ int s_abort;
   static_assert((2 * D + 4) * 8 <= kBarBytes, "barrier area");
@@ -331,7 +337,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
   const int srow = lane >> 1, shalf = lane & 1;   // scale-decode role of this lane
 
   // X[c][j] = sum of activations of row c over sub-block j (rows >= m are zero)
-  for (int i = tid; kMinTerm && i < nsub * MXC; i += NCW * 32) {
+  for (int i = tid; kMinTerm && !kOnes && i < nsub * MXC; i += NCW * 32) {
     const int c = i / nsub, j = i - c * nsub;
     float s = 0.f;
     if (c < m) {
@@ -369,7 +375,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
     }
 #pragma unroll
     for (int c = 0; c < MXC; ++c) {
-      const float both = kMinTerm ? xt[c] + __shfl_xor_sync(0xffffffffu, xt[c], 1) : 0.f;
+      const float both = (kMinTerm && !kOnes) ? xt[c] + __shfl_xor_sync(0xffffffffu, xt[c], 1) : 0.f;
       if (shalf == 0) rb.xt[cw][srow][c] = both;
       xt[c] = 0.f;
     }
@@ -403,7 +409,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
             else dsf[i] = __fmul_rn(e8m0_half(sp[BB * i]), 2.f);             // 2^(e - 127): the operands are the e2m1 values themselves
           }
           *reinterpret_cast<float4*>(&sS[cw][srow][4 * shalf]) = dsv;
-          if constexpr (kMinTerm) {
+          if constexpr (kMinTerm && !kOnes) {
             constexpr float kOff = MT::kMagic + 8.f;                          // operand = MAGIC + q, weight = d * (q - 8)
 #pragma unroll
             for (int c = 0; c < MXC; ++c) {
@@ -452,6 +458,19 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
           float acc[4];
           MT::mma_c(acc, a_lo, xa.x, xa.y, zero4);
           MT::mma(acc, a_hi, xb.x, xb.y);
+          if constexpr (kOnes) {               // Q4_0: sum of (MAGIC + q) x  ->  sum of (q - 8) x with the block's activation sums
+            const uint32_t ones[4] = {MT::kOnePair, MT::kOnePair, MT::kOnePair, MT::kOnePair};
+            float sx[4];
+            MT::mma_c(sx, ones, xa.x, xa.y, zero4);
+            MT::mma(sx, ones, xb.x, xb.y);
+            constexpr float kOff = MT::kMagic + 8.f;
+            acc[0] = fmaf(-kOff, sx[0], acc[0]);
+            acc[2] = fmaf(-kOff, sx[0], acc[2]);
+            if (MC == 2) {
+              acc[1] = fmaf(-kOff, sx[1], acc[1]);
+              acc[3] = fmaf(-kOff, sx[1], acc[3]);
+            }
+          }
           res[0][0] = fmaf(ds_a[b], acc[0], res[0][0]);
           res[0][2] = fmaf(ds_b[b], acc[2], res[0][2]);
           if (MC == 2) {
@@ -469,7 +488,7 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
         const uint8_t* st = sW + size_t(slot) * kStageBytes + wq * kSbBytes;
         {  // lane pair (srow, shalf): the eight sub-block scales of half-block shalf of row srow
           const uint8_t* blk = st + srow * kPitch;
-          float dsf[8], kk[8];
+          float dsf[8], kk[8], dmv[8];         // d * scale; folded offset + min; Q2_K: dmin * min alone
           if constexpr (QT == QTYPE_Q2_K) {
             const float d = half_at(blk + 80), dmin = half_at(blk + 82);
             const uint32_t* scp = reinterpret_cast<const uint32_t*>(blk + 8 * shalf);   // blocks (84 B) are word aligned, not more
@@ -478,20 +497,26 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
             for (int i = 0; i < 8; ++i) {
               const uint32_t b = ((i < 4 ? sc0 : sc1) >> (8 * (i & 3))) & 0xffu;
               dsf[i] = d * float(b & 0x0fu);
-              kk[i] = fmaf(MT::kMagic, dsf[i], dmin * float(b >> 4));
+              dmv[i] = dmin * float(b >> 4);
+              kk[i] = fmaf(MT::kMagic, dsf[i], dmv[i]);
             }
           } else {
             const float d = half_at(blk + 108);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               dsf[i] = d * float(q3k_scale(blk + 96, 8 * shalf + i) - 32);
+              dmv[i] = 0.f;
               kk[i] = (MT::kMagic + 4.f) * dsf[i];                                    // operand = MAGIC + (q + 4)
             }
           }
           *reinterpret_cast<float4*>(&sS[cw][srow][8 * shalf]) = make_float4(dsf[0], dsf[1], dsf[2], dsf[3]);
           *reinterpret_cast<float4*>(&sS[cw][srow][8 * shalf + 4]) = make_float4(dsf[4], dsf[5], dsf[6], dsf[7]);
+          if constexpr (kNeedK) {                 // Q2_K: dmin * min, applied to the sums from the tensor cores below
+            *reinterpret_cast<float4*>(&sK[cw][srow][8 * shalf]) = make_float4(dmv[0], dmv[1], dmv[2], dmv[3]);
+            *reinterpret_cast<float4*>(&sK[cw][srow][8 * shalf + 4]) = make_float4(dmv[4], dmv[5], dmv[6], dmv[7]);
+          }
 #pragma unroll
-          for (int c = 0; c < MXC; ++c) {
+          for (int c = 0; c < (kOnes ? 0 : MXC); ++c) {
             const float4 X0 = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 16 + 8 * shalf]);
             const float4 X1 = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 16 + 8 * shalf + 4]);
             const float X[8] = {X0.x, X0.y, X0.z, X0.w, X1.x, X1.y, X1.z, X1.w};
@@ -536,6 +561,27 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
               MT::mma_c(acc, a, xa.x, xa.y, zero4);
               const int idx = 8 * hb + 2 * j + h16;
               const float da = sS[cw][g][idx], db = sS[cw][g + 8][idx];      // 16 scales per row: read where used, not held in registers
+              if constexpr (kOnes) {             // the operand offset (and Q2_K's min) against the sub-block's activation sums
+                const uint32_t ones[4] = {MT::kOnePair, MT::kOnePair, MT::kOnePair, MT::kOnePair};
+                float sx[4];
+                MT::mma_c(sx, ones, xa.x, xa.y, zero4);
+                constexpr float kOff = MT::kMagic + (QT == QTYPE_Q3_K ? 4.f : 0.f);
+                acc[0] = fmaf(-kOff, sx[0], acc[0]);
+                acc[2] = fmaf(-kOff, sx[0], acc[2]);
+                if (MC == 2) {
+                  acc[1] = fmaf(-kOff, sx[1], acc[1]);
+                  acc[3] = fmaf(-kOff, sx[1], acc[3]);
+                }
+                if constexpr (QT == QTYPE_Q2_K) {
+                  const float ma = sK[cw][g][idx], mb = sK[cw][g + 8][idx];
+                  res[0][0] = fmaf(-ma, sx[0], res[0][0]);
+                  res[0][2] = fmaf(-mb, sx[0], res[0][2]);
+                  if (MC == 2) {
+                    res[0][1] = fmaf(-ma, sx[1], res[0][1]);
+                    res[0][3] = fmaf(-mb, sx[1], res[0][3]);
+                  }
+                }
+              }
               res[0][0] = fmaf(da, acc[0], res[0][0]);
               res[0][2] = fmaf(db, acc[2], res[0][2]);
               if (MC == 2) {
@@ -619,13 +665,17 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
           kk[i] = fmaf(MT::kMagic, dsf[i], dmin * byte_to_float(mnb, i));
         }
         *reinterpret_cast<float4*>(&sS[cw][srow][4 * shalf]) = dsv;
+        if constexpr (kOnes) {
+          *reinterpret_cast<float4*>(&sK[cw][srow][4 * shalf]) = make_float4(kk[0], kk[1], kk[2], kk[3]);
+        } else {
 #pragma unroll
-        for (int c = 0; c < MXC; ++c) {
-          const float4 X = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 8 + 4 * shalf]);
-          xt[c] = fmaf(kk[0], X.x, xt[c]);
-          xt[c] = fmaf(kk[1], X.y, xt[c]);
-          xt[c] = fmaf(kk[2], X.z, xt[c]);
-          xt[c] = fmaf(kk[3], X.w, xt[c]);
+          for (int c = 0; c < MXC; ++c) {
+            const float4 X = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 8 + 4 * shalf]);
+            xt[c] = fmaf(kk[0], X.x, xt[c]);
+            xt[c] = fmaf(kk[1], X.y, xt[c]);
+            xt[c] = fmaf(kk[2], X.z, xt[c]);
+            xt[c] = fmaf(kk[3], X.w, xt[c]);
+          }
         }
       }
       __syncwarp();
@@ -674,6 +724,20 @@ gemv_stream_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, const
           if (MC == 2) {
             res[0][1] = fmaf(dsr0, acc[1], res[0][1]);
             res[0][3] = fmaf(dsr1, acc[3], res[0][3]);
+          }
+          if constexpr (kOnes) {
+            // the sub-block's activation sums of columns 2t, 2t+1 (the same in every row of the tile), then the folded offsets
+            const uint32_t ones[4] = {MT::kOnePair, MT::kOnePair, MT::kOnePair, MT::kOnePair};
+            float sx[4];
+            MT::mma_c(sx, ones, xb.x, xb.y, zero4);
+            MT::mma(sx, ones, xb.z, xb.w);
+            const float kk0 = sK[cw][g][2 * G + h], kk1 = sK[cw][g + 8][2 * G + h];
+            res[0][0] = fmaf(-kk0, sx[0], res[0][0]);
+            res[0][2] = fmaf(-kk1, sx[0], res[0][2]);
+            if (MC == 2) {
+              res[0][1] = fmaf(-kk0, sx[1], res[0][1]);
+              res[0][3] = fmaf(-kk1, sx[1], res[0][3]);
+            }
           }
         }
       }
@@ -735,7 +799,8 @@ static int stream_scratch(cudaStream_t stream, Scratch* out) {
 template <int QT, typename T, int MXC, int NG, int D, bool PROBE = false>
 static int launch_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, int ctas_per_sm, const PeerOut& peers,
                           cudaStream_t s, int mode = 3) {     // mode: bit 0 = walk downwards, bit 1 = split at unit granularity
-  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + ((QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0) ? size_t(k / 32) * MXC * sizeof(float) : is_q23<QT>() ? size_t(k / 16) * MXC * sizeof(float) : 0);
+  const size_t smem = smem_fixed_bytes<QT, MXC, NG, D>() + (MXC >= 4 ? 0 : (QT == QTYPE_Q4_K || QT == QTYPE_Q5_K || QT == QTYPE_Q4_0) ? size_t(k / 32) * MXC * sizeof(float)
+                      : is_q23<QT>() ? size_t(k / 16) * MXC * sizeof(float) : 0);      // the activation-sum table of the types that keep one
   if (smem > 216 * 1024) return RC_RANGE;            // + up to 9 KB of static shared memory, under the 227 KB per CTA
   int* status = stream_status_ptr();
   if (status == nullptr) return RC_LAUNCH;
