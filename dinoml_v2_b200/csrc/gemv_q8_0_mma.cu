@@ -9,8 +9,9 @@
 // 16-bit floats MAGIC + l and MAGIC + 8 + h (bf16 MAGIC = 128; fp16 1024, removed exactly before the MMA) and feed
 // two mma.sync.m16n8k16 per 16 weights against the unmodified activations, fp32 accumulation; per 32-weight block
 //     y[n,m] += d[n] * (16 * S_h + S_l)  -  d[n] * (16 * (MAGIC' + 8) + MAGIC') * X[m]
-// with S_* the MMA sums, X[m] the sum of the block's activations (computed once per CTA) and MAGIC' the part of the
-// magic that is still in the operand (128 for bf16, 0 for fp16).
+// with S_* the MMA sums, X[m] the sum of the block's activations (M <= 2: a table computed once per CTA; M >= 4: one more
+// MMA of the activation fragment against an all-ones operand) and MAGIC' the part of the magic that is still in the
+// operand (128 for bf16, 0 for fp16).
 //
 // Data movement follows the Q4_K kernel: a CTA owns 16 consecutive weight rows and stages their packed bytes
 // HBM -> shared memory with 16-byte cp.async copies in K-stages of 4 x 256 weights (one 272-byte unit of 8 blocks per
@@ -41,9 +42,18 @@ __device__ __forceinline__ uint32_t q8_word(const uint8_t* p) {
 }
 
 // One block (32 weights) of rows g and g+8: four MMAs per activation tile, then the fp32 scaling.
-template <typename T, int NT, int MC, bool ODD>
+// ONES: the block's activation sums come from one more MMA per 16 weights (the activation fragment against an all-ones
+// operand) and the offset is folded here; otherwise the caller folds it against a table of sums.
+template <typename T, int NT, int MC, bool ODD, bool ONES>
 __device__ __forceinline__ void q8_block(const uint8_t* b0, const uint8_t* b1, const T* const (&xp)[NT], int t, float (&res)[NT][4]) {
   using MT = MmaType<T>;
+  constexpr float kOffset = 17.f * MT::kMagic + 128.f;   // 16 * (MAGIC' + 8) + MAGIC': what one unit of X is worth
+  const uint32_t ones[4] = {MT::kOnePair, MT::kOnePair, MT::kOnePair, MT::kOnePair};
+  float sx[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sx[nt][i] = 0.f;
   const float d0 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(b0));
   const float d1 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(b1));
   float lo[NT][4], hi[NT][4];
@@ -66,6 +76,18 @@ __device__ __forceinline__ void q8_block(const uint8_t* b0, const uint8_t* b1, c
       const uint2 xb = __ldg(reinterpret_cast<const uint2*>(xp[nt] + 16 * c));
       MT::mma(lo[nt], a_lo, xb.x, xb.y);
       MT::mma(hi[nt], a_hi, xb.x, xb.y);
+      if constexpr (ONES) MT::mma(sx[nt], ones, xb.x, xb.y);
+    }
+  }
+  if constexpr (ONES) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      lo[nt][0] = fmaf(-kOffset, sx[nt][0], lo[nt][0]);
+      lo[nt][2] = fmaf(-kOffset, sx[nt][0], lo[nt][2]);
+      if (MC == 2) {
+        lo[nt][1] = fmaf(-kOffset, sx[nt][1], lo[nt][1]);
+        lo[nt][3] = fmaf(-kOffset, sx[nt][1], lo[nt][3]);
+      }
     }
   }
 #pragma unroll
@@ -92,6 +114,9 @@ gemv_q8_0_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, con
   constexpr int SPI = NW / 4;                // stages per iteration (one per warp group)
   constexpr int D = NSTAGE / SPI;            // stage slots per warp group
   constexpr float kOffset = 17.f * MT::kMagic + 128.f;   // 16 * (MAGIC' + 8) + MAGIC': what one unit of X is worth
+  // From four activation rows on the activation sums come from the tensor cores (see q8_block): building the table costs
+  // every 16-row CTA M * K activation reads, as many bytes as its weights at M = 8.
+  constexpr bool kOnes = MXC >= 4;
   static_assert(NSTAGE % SPI == 0 && D >= 2, "each warp group needs at least two stage slots");
   extern __shared__ __align__(16) uint8_t smem_dyn[];
   uint8_t* sW = smem_dyn;                                                   // staged packed weights, NSTAGE x kQ8StageBytes
@@ -135,7 +160,7 @@ gemv_q8_0_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, con
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
   // X[c][j] = sum of activations of row c over block j (rows >= m are zero).
-  for (int idx = tid; idx < nblk * MXC; idx += NW * 32) {
+  for (int idx = tid; !kOnes && idx < nblk * MXC; idx += NW * 32) {
     const int c = idx / nblk, j = idx - c * nblk;
     float s = 0.f;
     if (c < m) {
@@ -167,7 +192,7 @@ gemv_q8_0_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, con
     const int unit = s * kQ8StageUnits + wq;
     if (s < nstages && unit < nunits) {
       const uint8_t* st = sW + (s % NSTAGE) * kQ8StageBytes + wq * kQ8UnitBytes;
-      {   // offset term: d * X of four blocks of one row, folded per activation row
+      if constexpr (!kOnes) {   // offset term: d * X of four blocks of one row, folded per activation row
         const uint8_t* hb = st + srow * kQ8Pitch + 34 * 4 * shalf;
         float dv[4];
 #pragma unroll
@@ -188,8 +213,8 @@ gemv_q8_0_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, con
         const T* xp[NT];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) xp[nt] = xrow[nt] + unit * 256 + 32 * i;
-        if (i & 1) q8_block<T, NT, MC, false>(b0 + 34 * i, b1 + 34 * i, xp, t, res);
-        else q8_block<T, NT, MC, true>(b0 + 34 * i, b1 + 34 * i, xp, t, res);
+        if (i & 1) q8_block<T, NT, MC, false, kOnes>(b0 + 34 * i, b1 + 34 * i, xp, t, res);
+        else q8_block<T, NT, MC, true, kOnes>(b0 + 34 * i, b1 + 34 * i, xp, t, res);
       }
     }
   }
@@ -226,7 +251,7 @@ gemv_q8_0_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, con
 template <typename T, int MXC, int NW, int NSTAGE>
 static int launch_q8_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, cudaStream_t s) {
   const int tiles = (n + kQ8Rows - 1) / kQ8Rows;
-  const size_t smem = size_t(NSTAGE) * kQ8StageBytes + size_t(k / 32) * MXC * sizeof(float);
+  const size_t smem = size_t(NSTAGE) * kQ8StageBytes + (MXC >= 4 ? 0 : size_t(k / 32) * MXC * sizeof(float));   // the sum table of M <= 2
   if (smem > 200 * 1024) return RC_RANGE;
   auto kern = gemv_q8_0_mma_kernel<T, MXC, NW, NSTAGE>;
   static SmemOptIn granted;             // per kernel instantiation, per device
