@@ -82,7 +82,7 @@ int select_variant(int qtype, int dtype, int m, int n, int k) {
   //   Q4_K, M = 1, when the tile kernel's grid (three CTAs of 16 rows per SM) fills at least three quarters of its last wave
   //   ([11008 x 4096]: 9.4 us against 10.5 us; with emptier waves or less than one wave the persistent kernel wins);
   //   Q4_K, M >= 2, with fewer row tiles than half the SMs: the tile kernel cuts K across a cluster and so uses more SMs
-  //   ([256 x 14336], M = 8: 6.3 us against 13.4 us; [1024 x 4096], M = 8: a tie; [2048 x 4096], M = 8: 8.4 against 6.5);
+  //   ([256 x 14336], M = 8: 4.9 us against 9.3 us; [2048 x 4096], M = 8: 6.3 against 5.9);
   //   Q6_K, M >= 3, on weights below 32 M elements ([4096 x 4096], M = 4: 6.3 us against 6.8 us), where the launch is too short
   //   for the ring to pay off (at M <= 2 and on larger weights it is 7 - 30 % faster: [4096 x 14336], M = 1: 15.0 us against 21.1 us).
   if (gemv_stream_supports(qtype, dtype, m, n, k)) {
@@ -94,7 +94,9 @@ int select_variant(int qtype, int dtype, int m, int n, int k) {
       // where its ring keeps more bytes in flight per SM ([1024 x 14336]: 7.2 us against 8.9; [256 x 14336]: 7.0 against 8.5)
       tile_kernel = (tiles <= sms && k < 8192) || (tiles >= slots && double(tiles) / (double(waves) * slots) >= 0.75);
     } else if (qtype == QTYPE_Q4_K) {
-      tile_kernel = 2 * tiles <= sms;
+      // ... on a long K; on K = 4096 the persistent kernel (16 consumer warps per CTA) is ahead from M = 4 since both kernels take
+      // their activation sums from the tensor cores ([1024 x 4096], M = 8: 4.6 us against 5.5; [1024 x 14336]: 9.6 against 7.6)
+      tile_kernel = 2 * tiles <= sms && (m < 4 || k >= 8192);
     } else if (qtype == QTYPE_Q6_K && m >= 3) {
       tile_kernel = weights < (int64_t(32) << 20);
     }

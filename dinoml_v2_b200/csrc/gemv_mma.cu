@@ -67,6 +67,11 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
   uint8_t* sW = smem_dyn;                                                 // staged packed weights, NSTAGE x kStageBytes
   float* sX = reinterpret_cast<float*>(smem_dyn + NSTAGE * kStageBytes);  // [MXC][k/32]
   __shared__ __align__(16) float sS[NW][kGemvRows][8];                    // ds per row, sub-block
+  // From four activation rows on, the per-sub-block activation sums come from the tensor cores (one more MMA pair per
+  // sub-block: the activation fragment against an all-ones operand) instead of a table every CTA builds from M * K
+  // activations before its first stage; the folded offsets (MAGIC * ds + dmin * min) then wait in sK.
+  constexpr bool kOnes = MXC >= 4;
+  __shared__ __align__(16) float sK[kOnes ? NW : 1][kOnes ? kGemvRows : 1][8];
   // the cross-warp reduction buffers reuse the stage slots once every warp is done with them
   float (*sRed)[kGemvRows][kCols] = reinterpret_cast<float (*)[kGemvRows][kCols]>(smem_dyn);
   float (*sXt)[kGemvRows][2][MXC] = reinterpret_cast<float (*)[kGemvRows][2][MXC]>(smem_dyn + NW * kGemvRows * kCols * sizeof(float));
@@ -113,7 +118,7 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
 
   // X[c][j] = sum of activations of row c over sub-block j (rows >= m are zero), for the sub-blocks of this K slice.
   const int j_first = s_first * (kStageSb * 8), j_count = min(nsub - j_first, nstages * (kStageSb * 8));
-  for (int i = tid; i < j_count * MXC; i += NW * 32) {
+  for (int i = tid; !kOnes && i < j_count * MXC; i += NW * 32) {
     const int c = i / j_count, j = j_first + (i - c * j_count);
     const int idx = c * nsub + j;
     float s = 0.f;
@@ -165,13 +170,17 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
           kk[i] = fmaf(MT::kMagic, dsf[i], dmin * byte_to_float(mnb, i));
         }
         *reinterpret_cast<float4*>(&sS[warp][srow][4 * shalf]) = dsv;
+        if constexpr (kOnes) {
+          *reinterpret_cast<float4*>(&sK[warp][srow][4 * shalf]) = make_float4(kk[0], kk[1], kk[2], kk[3]);
+        } else {
 #pragma unroll
-        for (int c = 0; c < MXC; ++c) {
-          const float4 X = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 8 + 4 * shalf]);
-          xt[c] = fmaf(kk[0], X.x, xt[c]);
-          xt[c] = fmaf(kk[1], X.y, xt[c]);
-          xt[c] = fmaf(kk[2], X.z, xt[c]);
-          xt[c] = fmaf(kk[3], X.w, xt[c]);
+          for (int c = 0; c < MXC; ++c) {
+            const float4 X = *reinterpret_cast<const float4*>(&sX[c * nsub + sb * 8 + 4 * shalf]);
+            xt[c] = fmaf(kk[0], X.x, xt[c]);
+            xt[c] = fmaf(kk[1], X.y, xt[c]);
+            xt[c] = fmaf(kk[2], X.z, xt[c]);
+            xt[c] = fmaf(kk[3], X.w, xt[c]);
+          }
         }
       }
       __syncwarp();
@@ -209,10 +218,23 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
               res[nt][1] = fmaf(dsr0, acc[1], res[nt][1]);
               res[nt][3] = fmaf(dsr1, acc[3], res[nt][3]);
             }
+            if constexpr (kOnes) {
+              const uint32_t ones[4] = {MT::kOnePair, MT::kOnePair, MT::kOnePair, MT::kOnePair};
+              float sx[4] = {0.f, 0.f, 0.f, 0.f};
+              MT::mma(sx, ones, xb.x, xb.y);
+              MT::mma(sx, ones, xb.z, xb.w);
+              const float kk0 = sK[warp][g][2 * G + h], kk1 = sK[warp][g + 8][2 * G + h];
+              res[nt][0] = fmaf(-kk0, sx[0], res[nt][0]);
+              res[nt][2] = fmaf(-kk1, sx[0], res[nt][2]);
+              if (MC == 2) {
+                res[nt][1] = fmaf(-kk0, sx[1], res[nt][1]);
+                res[nt][3] = fmaf(-kk1, sx[1], res[nt][3]);
+              }
+            }
           }
         }
       }
-      __syncwarp();                        // sS is rewritten in the next iteration
+      __syncwarp();                        // sS (and sK) are rewritten in the next iteration
     }
   }
   cp_async_wait<0>();
@@ -276,7 +298,7 @@ gemv_q4k_mma_kernel(const T* __restrict__ x, const uint8_t* __restrict__ w, cons
 template <typename T, int MXC, int NW, int NSTAGE, bool SLICED>
 static int launch_q4k_cfg(const void* a, const void* b, const void* bias, void* c, int m, int n, int k, const PeerOut& peers, cudaStream_t s) {
   const int tiles = (n + kGemvRows - 1) / kGemvRows;
-  const size_t smem = size_t(NSTAGE) * kStageBytes + size_t(k / 32) * MXC * sizeof(float);
+  const size_t smem = size_t(NSTAGE) * kStageBytes + (MXC >= 4 ? 0 : size_t(k / 32) * MXC * sizeof(float));   // the sum table of M <= 2
   if (smem > 200 * 1024) return RC_RANGE;
   auto kern = peers.count > 0 ? gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, true> : gemv_q4k_mma_kernel<T, MXC, NW, NSTAGE, SLICED, false>;
   static SmemOptIn granted[2];          // per kernel (plain / scatter), per device
