@@ -57,6 +57,16 @@ def test_versions_and_pure_host_entry_points(library):
     sel.argtypes = [ctypes.c_int] * 5
     assert sel(12, 6, 1, 11008, 4096) == 2           # Q4_K bf16 M=1 -> mma GEMV
     assert sel(12, 2, 1, 11008, 4096) == 1           # float32 activations -> simt
+    # the shape guard without a GPU (148 SMs assumed): Q4_K M=1 with few row tiles - tile GEMV on a short K, persistent one on a long K
+    assert sel(12, 6, 1, 1024, 4096) == 2 and sel(12, 6, 1, 1024, 14336) == 4
+    # Q4_K M=8 with few row tiles: persistent GEMV on K = 4096, K-sliced tile GEMV on a long K
+    assert sel(12, 6, 8, 1024, 4096) == 4 and sel(12, 6, 8, 256, 14336) == 2
+    # the further types: persistent GEMV up to M = 8, tcgen05 GEMM above, CUDA-core kernel when rows are not 16-byte multiples
+    for q, bad_k in ((2, None), (13, None), (10, 768), (11, 1024), (39, 768), (40, None)):
+        assert sel(q, 6, 1, 4096, 4096) == 4 and sel(q, 6, 8, 4096, 4096) == 4 and sel(q, 6, 16, 4096, 4096) == 3, q
+        assert sel(q, 2, 4, 4096, 4096) == 1, q
+        if bad_k:
+            assert sel(q, 6, 1, 64, bad_k) == 1 and sel(q, 6, 64, 64, bad_k) == 1, q
     # argument validation happens before any CUDA call
     f = library.dinoml_b200_gguf_gemm_rcr
     f.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 6 + [ctypes.c_void_p]
